@@ -1,0 +1,360 @@
+#!/usr/bin/env python
+"""Headline benchmark: MoE-layer tokens/s (forward + backward) and dispatch+combine time on the
+single-MoE-layer configuration (bf16, d_model 4096, 64 SwiGLU experts of hidden 1408, top-6,
+4 routing groups, M = 2, 4096 tokens per GPU, x ~ N(0,1), router W ~ N(0, 0.02)).
+
+    python bench.py --gpus N --steps K --warmup W [--impl ours|reference]
+
+For N > 1 it is launched under ``python -m torch.distributed.run`` (one rank per GPU, NCCL).
+Per-GPU work is fixed as N grows (weak scaling): 4096 tokens per GPU, 64 experts in total
+spread over the N GPUs.  Logical two-hop groups: N=8 -> 4 groups of 2 GPUs, N=4 -> 4 groups of
+1, N=2 -> 2 groups of 1; N=1 runs the experts locally.  One step = router + routed experts
+(dispatch, grouped SwiGLU GEMMs, combine), forward and backward down to the gradients of x, the
+router weight and both expert weights.  Both the one-hop and the two-hop path are timed; the
+headline value is the faster of the two and ``config.path`` names it.
+
+Timing: CUDA events on the launching stream, max over ranks, barrier + synchronize on both
+sides; the 2.2 GB of expert weights per step exceed the 126 MB L2, so no L2 flush is needed.
+The ``e2e`` entry repeats the measurement through the public API with a pinned-host -> device
+copy of the step's tokens and a device -> host read of the loss inside every timed step.
+``--impl reference`` runs the unmodified reference (``baseline/_ref``: a plain copy of its
+``terrace`` package, it has no build system to install) through ``ep_moe_forward`` /
+``ta2a_moe_forward`` on NCCL for the same configuration.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+
+D_MODEL, N_EXPERTS, D_EXPERT, TOP_K, TOP_GROUPS, TOKENS = 4096, 64, 1408, 6, 2, 4096
+ROUTING_GROUPS = {1: 4, 2: 2, 4: 4, 8: 4}
+RPN = {1: 1, 2: 1, 4: 1, 8: 2}
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+
+    QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+             "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.gpu = gpu_index
+        self.proc = None
+        self.lines: list[str] = []
+        self.thread = None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--id={self.gpu}", f"--query-gpu={self.QUERY}",
+                 "--format=csv,noheader,nounits", "-lms", "100"],
+                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except OSError:
+            self.proc = None
+            return
+
+        def pump():
+            for line in self.proc.stdout:
+                self.lines.append(line.strip())
+        self.thread = threading.Thread(target=pump, daemon=True)
+        self.thread.start()
+
+    def stop(self) -> dict:
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm, smax, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in self.lines:
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) < 9:
+                continue
+            try:
+                sm.append(float(parts[1]))
+                smax.append(float(parts[2]))
+            except ValueError:
+                continue
+            for name, val in zip(names, parts[5:9]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": statistics.median(sm) if sm else None,
+                "sm_max_mhz": max(smax) if smax else None, "samples": len(sm),
+                "reasons": sorted(reasons)}
+
+
+def setup_dist(n_gpus: int, force: bool):
+    import torch
+    import torch.distributed as dist
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if world != n_gpus:
+        raise SystemExit(f"--gpus {n_gpus} but WORLD_SIZE={world}: launch with torch.distributed.run")
+    torch.cuda.set_device(local)
+    if world > 1 or force:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        os.environ.setdefault("MASTER_PORT", "29533")
+        dist.init_process_group("nccl", rank=rank, world_size=world,
+                                device_id=torch.device("cuda", local))
+    return rank, world, local
+
+
+def timed(fn, steps: int, warmup: int, world: int, sampler: ClockSampler | None):
+    """W warm-up steps, then exactly K steps between CUDA events; returns max-over-ranks ms."""
+    import torch
+    import torch.distributed as dist
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize()
+    if sampler:
+        sampler.start()
+    t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    t0.record()
+    for _ in range(steps):
+        fn()
+    t1.record()
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize()
+    clocks = sampler.stop() if sampler else None
+    ms = torch.tensor([t0.elapsed_time(t1)], device="cuda")
+    if world > 1:
+        dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+    return ms.item(), clocks
+
+
+def make_problem(rank: int, world: int, device):
+    import torch
+    g = torch.Generator(device="cpu").manual_seed(1234)
+    router_w = (torch.randn(N_EXPERTS, D_MODEL, generator=g) * 0.02)
+    epr = N_EXPERTS // world
+    # every rank draws the full weight stream so shards are consistent, keeps only its own
+    w13_shard = w2_shard = None
+    for r in range(world):
+        a = torch.randn(epr, D_MODEL, 2 * D_EXPERT, generator=g) * D_MODEL ** -0.5
+        b = torch.randn(epr, D_EXPERT, D_MODEL, generator=g) * D_EXPERT ** -0.5
+        if r == rank:
+            w13_shard, w2_shard = a, b
+    gx = torch.Generator(device="cpu").manual_seed(100 + rank)
+    x_host = torch.randn(TOKENS, D_MODEL, generator=gx).bfloat16().pin_memory()
+    gy = torch.randn(TOKENS, D_MODEL, generator=gx).bfloat16().to(device)
+    return (router_w.bfloat16().to(device), w13_shard.bfloat16().to(device),
+            w2_shard.bfloat16().to(device), x_host, gy)
+
+
+def run_ours(args, rank, world, local):
+    import torch
+    sys.path.insert(0, ROOT)
+    from terracemoe_simulator_b200 import ops
+    from terracemoe_simulator_b200.ops import native
+    from terracemoe_simulator_b200.parallel.moe_layer import MoELayerRunner
+    from terracemoe_simulator_b200.routing import TRouteConfig
+
+    assert ops.custom_ops_enabled(), "native library missing: run __graft_entry__.build()"
+    device = torch.device("cuda", local)
+    router_w, w13, w2, x_host, gy = make_problem(rank, world, device)
+    cfg = TRouteConfig(N_EXPERTS, ROUTING_GROUPS[world], TOP_K, TOP_GROUPS)
+    params = [t.requires_grad_(True) for t in (router_w, w13, w2)]
+    runners = {}
+    paths = ["local"] if world == 1 else ["one_hop", "two_hop"]
+    for path in paths:
+        runners[path] = MoELayerRunner(cfg, D_MODEL, D_EXPERT, TOKENS, world=world, rank=rank,
+                                       rpn=RPN[world], mode=path, fused=not args.nccl_arm,
+                                       device=device)
+    x_dev = x_host.to(device).requires_grad_(True)
+
+    def make_step(path, e2e: bool):
+        runner = runners[path]
+
+        def step():
+            for p in params:
+                p.grad = None
+            if e2e:
+                x = x_host.to(device, non_blocking=True).requires_grad_(True)
+            else:
+                x = x_dev
+                x.grad = None
+            y = runner(x, *params)
+            if e2e:
+                loss = (y.float() * gy.float()).mean()
+                loss.backward()
+                return loss.item()                      # device -> host read of the result
+            y.backward(gy)
+            return None
+        return step
+
+    results = {}
+    clocks = None
+    for path in paths:
+        native.LAUNCHES[0] = 0
+        ms, clk = timed(make_step(path, False), args.steps, args.warmup, world,
+                        ClockSampler(local) if rank == 0 else None)
+        launches = native.LAUNCHES[0] * args.steps // (args.steps + args.warmup)
+        dc = runners[path].time_dispatch_combine(x_dev.detach(), args.steps, args.warmup)
+        results[path] = {"ms_per_step": ms / args.steps, "launches": launches,
+                         "dispatch_combine_us": dc, "status": native.take_status(local)}
+        clocks = clocks or clk
+    best = min(paths, key=lambda p: results[p]["ms_per_step"])
+    e2e_ms, _ = timed(make_step(best, True), args.steps, args.warmup, world, None)
+    tokens = TOKENS * world
+    value = tokens / (results[best]["ms_per_step"] * 1e-3)
+    peaks = {}
+    try:
+        with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
+            peaks = json.load(f)
+    except OSError:
+        pass
+    flops = 3 * 2 * 3 * TOKENS * TOP_K * D_MODEL * D_EXPERT          # fwd + 2x bwd, 3 matrices
+    peak_tf = peaks.get("bf16_tflops_sustained", 1400.0)
+    out = {
+        "metric": "moe_layer_tokens_per_s", "value": value, "unit": "tokens/s", "n_gpus": world,
+        "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": results[best]["ms_per_step"], "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "impl": "ours",
+        "config": {"model": "single MoE layer d4096 E64x1408 top6 M2", "global_batch": tokens,
+                   "seq_len": TOKENS, "parallelism": f"ep{world}", "path": best,
+                   "routing_groups": ROUTING_GROUPS[world], "rpn": RPN[world],
+                   "step": "router+dispatch+experts+combine fwd+bwd",
+                   "l2": "inputs larger than L2 (expert weights 2.2 GB per step)",
+                   "transport": "nccl all_to_all" if args.nccl_arm else "fused peer-memory kernels"},
+        "paths": results,
+        "gemm_frac_of_measured_sustained": flops / (results[best]["ms_per_step"] * 1e-3) / (peak_tf * 1e12),
+        "clocks": clocks,
+        "e2e": {"value": tokens / (e2e_ms / args.steps * 1e-3), "unit": "tokens/s",
+                "h2d_bytes_per_step": x_host.numel() * 2, "d2h_bytes_per_step": 4},
+        "gpu_launches": results[best]["launches"] * args.steps,
+    }
+    return out
+
+
+def run_reference(args, rank, world, local):
+    import torch
+    import torch.distributed as dist
+    ref_root = os.path.join(ROOT, "baseline", "_ref")
+    if not os.path.isdir(os.path.join(ref_root, "terrace")):
+        return {"impl": "reference", "unavailable": "baseline/_ref/terrace is missing"}
+    sys.path.insert(0, ref_root)
+    from terrace.ep_dist import ep_moe_forward            # noqa: E402  (reference code)
+    from terrace.routing import TRouteConfig, t_route     # noqa: E402
+    from terrace.ta2a_fwd import init_ta2a_groups, ta2a_moe_forward  # noqa: E402
+
+    device = torch.device("cuda", local)
+    router_w, w13, w2, x_host, gy = make_problem(rank, world, device)
+    cfg = TRouteConfig(N_EXPERTS, ROUTING_GROUPS[world], TOP_K, TOP_GROUPS)
+    params = [t.requires_grad_(True) for t in (router_w, w13, w2)]
+    bias = torch.zeros(N_EXPERTS, device=device)
+    rpn = RPN[world]
+    paths = ["one_hop"]
+    if world // rpn >= 2:
+        init_ta2a_groups(world, rpn)
+        paths.append("two_hop")
+    x_dev = x_host.to(device).requires_grad_(True)
+
+    def make_step(path, e2e):
+        def step():
+            for p in params:
+                p.grad = None
+            if e2e:
+                x = x_host.to(device, non_blocking=True).requires_grad_(True)
+            else:
+                x = x_dev
+                x.grad = None
+            aff = torch.sigmoid(x @ router_w.t())
+            idx, gates, _ = t_route(aff, bias, cfg, "full")
+            if path == "one_hop":
+                y = ep_moe_forward(x, idx, gates.to(x.dtype), w13, w2, world, N_EXPERTS)
+            else:
+                y = ta2a_moe_forward(x, idx, gates.to(x.dtype), w13, w2, world, N_EXPERTS,
+                                     rpn=rpn, groups_m=TOP_GROUPS)
+            if e2e:
+                loss = (y.float() * gy.float()).mean()
+                loss.backward()
+                return loss.item()
+            y.backward(gy)
+            return None
+        return step
+
+    results = {}
+    clocks = None
+    for path in paths:
+        ms, clk = timed(make_step(path, False), args.steps, args.warmup, world,
+                        ClockSampler(local) if rank == 0 else None)
+        results[path] = {"ms_per_step": ms / args.steps}
+        clocks = clocks or clk
+    best = min(paths, key=lambda p: results[p]["ms_per_step"])
+    e2e_ms, _ = timed(make_step(best, True), args.steps, args.warmup, world, None)
+    tokens = TOKENS * world
+    return {
+        "metric": "moe_layer_tokens_per_s",
+        "value": tokens / (results[best]["ms_per_step"] * 1e-3), "unit": "tokens/s",
+        "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": results[best]["ms_per_step"], "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "bf16", "data": "synthetic", "impl": "reference",
+        "config": {"model": "single MoE layer d4096 E64x1408 top6 M2", "global_batch": tokens,
+                   "seq_len": TOKENS, "parallelism": f"ep{world}", "path": best,
+                   "routing_groups": ROUTING_GROUPS[world], "rpn": rpn,
+                   "step": "router+dispatch+experts+combine fwd+bwd",
+                   "l2": "inputs larger than L2 (expert weights 2.2 GB per step)",
+                   "transport": "reference torch ops over NCCL all_to_all_single + cuBLAS"},
+        "paths": results, "clocks": clocks,
+        "e2e": {"value": tokens / (e2e_ms / args.steps * 1e-3), "unit": "tokens/s",
+                "h2d_bytes_per_step": x_host.numel() * 2, "d2h_bytes_per_step": 4},
+        "gpu_launches": 0,
+    }
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--nccl-arm", action="store_true",
+                    help="ours, but dispatch/combine over NCCL all_to_all instead of fused kernels")
+    args = ap.parse_args()
+    if args.gpus not in ROUTING_GROUPS:
+        raise SystemExit("--gpus must be 1, 2, 4 or 8")
+    import torch
+    if not torch.cuda.is_available():
+        if args.impl == "reference":
+            print(json.dumps({"impl": "reference", "unavailable": "no CUDA device on this host"}))
+            return 0
+        raise SystemExit("bench.py needs a CUDA device")
+    rank, world, local = setup_dist(args.gpus, force=args.impl == "reference" or args.nccl_arm)
+    try:
+        out = run_reference(args, rank, world, local) if args.impl == "reference" \
+            else run_ours(args, rank, world, local)
+    except Exception as exc:  # noqa: BLE001
+        if args.impl == "reference":
+            out = {"impl": "reference", "unavailable": f"{type(exc).__name__}: {exc}"[:300]}
+        else:
+            raise
+    if rank == 0:
+        print(json.dumps(out))
+    import torch.distributed as dist
+    if dist.is_initialized():
+        dist.barrier()
+        dist.destroy_process_group()
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

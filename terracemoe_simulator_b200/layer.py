@@ -164,7 +164,8 @@ class TerracedMoE(nn.Module):
 
     def _experts_native(self, x, expert_idx, gates, y):
         from . import ops
-        return y + ops.moe_experts_local(x, expert_idx, gates, self.w13, self.w2)
+        return y + ops.moe_experts_local(x, expert_idx, gates, self.w13, self.w2,
+                                         self.cfg.group_size)
 
     def _experts(self, x, expert_idx, gates, y):
         backend = self.expert_backend

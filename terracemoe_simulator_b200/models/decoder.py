@@ -81,18 +81,22 @@ class Attention(nn.Module):
     def forward(self, x, cos, sin):
         from .. import ops
         B, T, D = x.shape
-        if x.is_cuda and ops.custom_ops_enabled() and ops.attention_supported(x, self.nh):
+        native = x.is_cuda and ops.custom_ops_enabled()
+        if native and ops.attention_supported(x, self.nh):
             qkv = ops.linear(x.reshape(B * T, D), self.wqkv.weight)
             o = ops.causal_attention_rope(qkv.view(B, T, 3, self.nh, self.hd), cos, sin)
             return ops.linear(o.reshape(B * T, D), self.wo.weight).view(B, T, D)
-        q, k, v = self.wqkv(x).chunk(3, dim=-1)
+        proj = native and ops.dense_supported(x, self.wqkv.weight)
+        qkv = ops.linear(x, self.wqkv.weight) if proj else self.wqkv(x)
+        q, k, v = qkv.chunk(3, dim=-1)
         q = q.view(B, T, self.nh, self.hd).transpose(1, 2)
         k = k.view(B, T, self.nh, self.hd).transpose(1, 2)
         v = v.view(B, T, self.nh, self.hd).transpose(1, 2)
         q = _rope(q, cos, sin).to(v.dtype)
         k = _rope(k, cos, sin).to(v.dtype)
         o = F.scaled_dot_product_attention(q, k, v, is_causal=True)
-        return self.wo(o.transpose(1, 2).reshape(B, T, D))
+        o = o.transpose(1, 2).reshape(B, T, D)
+        return ops.linear(o, self.wo.weight) if proj else self.wo(o)
 
 
 class Block(nn.Module):

@@ -1,0 +1,420 @@
+// torch bindings: TORCH_LIBRARY(terrace) with CUDA and Meta implementations.
+//
+// Same op schemas as the reference's library for the three ops it defines
+// (terrace/ops/csrc/terrace_ops.cpp:228-233, terrace_k2_pack.cpp:207-212):
+//   terrace::passthrough(Tensor x) -> Tensor
+//   terrace::k1_arrival(Tensor rx, Tensor rslot, Tensor rgate, int quota, int epr, int rpn,
+//                       int my_local) -> (Tensor, Tensor, Tensor, Tensor, Tensor)
+//   terrace::k2_pack(Tensor hidden, Tensor expert_idx, Tensor gates, int world, int n_experts,
+//                    int rpn, int groups_m) -> (Tensor, Tensor, Tensor, Tensor, Tensor)
+// plus the compute ops of the MoE layer (norm, route, plan, scatter, combine, grouped GEMMs).
+// Host-side validation fails loudly (TORCH_CHECK) before anything is launched; device-side
+// containment problems are reported through a per-device status word (terrace::take_status).
+#include <ATen/ATen.h>
+#include <ATen/cuda/CUDAContext.h>
+#include <c10/cuda/CUDAGuard.h>
+#include <torch/library.h>
+
+#include <mutex>
+#include <tuple>
+#include <vector>
+
+#include "launch.h"
+#include "symm.h"
+
+namespace {
+
+using at::Tensor;
+
+long long* i64(const Tensor& t) { return reinterpret_cast<long long*>(t.data_ptr<int64_t>()); }
+
+cudaStream_t cur_stream() { return at::cuda::getCurrentCUDAStream().stream(); }
+
+void check_rc(int rc, const char* what) {
+  TORCH_CHECK(rc == TB200_OK, what, " failed with terrace_b200 error code ", rc);
+}
+
+// One int32 status word per device; kernels CAS their first problem code into it.
+Tensor& status_word(int device) {
+  static std::mutex mu;
+  static std::vector<Tensor> words(64);
+  std::lock_guard<std::mutex> lock(mu);
+  TORCH_CHECK(device >= 0 && device < 64, "device index out of range");
+  if (!words[device].defined()) {
+    words[device] = at::zeros({1}, at::TensorOptions().dtype(at::kInt).device(at::kCUDA, device));
+  }
+  return words[device];
+}
+int* status_ptr(const Tensor& like) { return status_word(like.get_device()).data_ptr<int>(); }
+
+int64_t take_status(int64_t device) {
+  Tensor& w = status_word(static_cast<int>(device));
+  const int v = w.item<int>();
+  if (v != 0) w.zero_();
+  return v;
+}
+
+#define CHECK_CUDA_CONTIG(t) \
+  TORCH_CHECK((t).is_cuda() && (t).is_contiguous(), #t " must be a contiguous CUDA tensor")
+
+// ---------------------------------------------------------------------------------------------
+Tensor passthrough_cuda(const Tensor& x) {
+  c10::cuda::CUDAGuard guard(x.device());
+  Tensor src = x.contiguous();
+  Tensor out = at::empty_like(src);
+  check_rc(tb200_passthrough(src.data_ptr(), out.data_ptr(), src.nbytes(), cur_stream()),
+           "passthrough");
+  return out;
+}
+Tensor passthrough_meta(const Tensor& x) { return at::empty_like(x); }
+
+// ---------------------------------------------------------------------------------------------
+using Tup5 = std::tuple<Tensor, Tensor, Tensor, Tensor, Tensor>;
+
+void k1_checks(const Tensor& rx, const Tensor& rslot, const Tensor& rgate, int64_t quota,
+               int64_t epr, int64_t rpn, int64_t my_local) {
+  TORCH_CHECK(rx.dim() == 2 && rslot.dim() == 2 && rgate.dim() == 2, "k1_arrival: 2-D inputs");
+  TORCH_CHECK(rslot.scalar_type() == at::kLong, "k1_arrival: rslot must be int64");
+  TORCH_CHECK(rgate.scalar_type() == rx.scalar_type(),
+              "k1_arrival: rgate dtype must equal rx dtype");
+  TORCH_CHECK(rslot.size(0) == rx.size(0) && rgate.sizes() == rslot.sizes(),
+              "k1_arrival: rslot/rgate must be [R, quota]");
+  TORCH_CHECK(rslot.size(1) == quota, "k1_arrival: rslot has ", rslot.size(1),
+              " columns but quota is ", quota);
+  TORCH_CHECK(epr >= 1 && rpn >= 1 && rpn <= 1024, "k1_arrival: bad epr/rpn");
+  TORCH_CHECK(my_local >= 0 && my_local < rpn, "k1_arrival: my_local outside [0, rpn)");
+}
+
+Tup5 k1_arrival_cuda(const Tensor& rx_, const Tensor& rslot_, const Tensor& rgate_, int64_t quota,
+                     int64_t epr, int64_t rpn, int64_t my_local) {
+  k1_checks(rx_, rslot_, rgate_, quota, epr, rpn, my_local);
+  c10::cuda::CUDAGuard guard(rx_.device());
+  Tensor rx = rx_.contiguous(), rslot = rslot_.contiguous(), rgate = rgate_.contiguous();
+  const int64_t R = rx.size(0), H = rx.size(1), P = R * quota;
+  auto lopt = rx.options().dtype(at::kLong);
+  Tensor send_buf = at::empty({P, H}, rx.options());
+  Tensor gate_pairs = at::empty({P}, rx.options());
+  Tensor r_idx = at::zeros({P}, lopt), slot_idx = at::zeros({P}, lopt);
+  Tensor i_send = at::zeros({rpn}, lopt);
+  if (P == 0) return {send_buf, gate_pairs, r_idx, slot_idx, i_send};
+  Tensor scratch = at::empty({static_cast<int64_t>(tb200_k1_scratch_ints(R, quota, rpn))},
+                             rx.options().dtype(at::kInt));
+  check_rc(tb200_k1_arrival(rx.data_ptr(), i64(rslot), rgate.data_ptr(),
+                            send_buf.data_ptr(), gate_pairs.data_ptr(), i64(r_idx),
+                            i64(slot_idx), i64(i_send),
+                            scratch.data_ptr<int>(), R, quota, epr, rpn,
+                            static_cast<int>(H * rx.element_size()),
+                            static_cast<int>(rx.element_size()), status_ptr(rx), cur_stream()),
+           "k1_arrival");
+  return {send_buf, gate_pairs, r_idx, slot_idx, i_send};
+}
+
+Tup5 k1_arrival_meta(const Tensor& rx, const Tensor& rslot, const Tensor& rgate, int64_t quota,
+                     int64_t epr, int64_t rpn, int64_t my_local) {
+  const int64_t P = rx.size(0) * quota;
+  auto lopt = rx.options().dtype(at::kLong);
+  return {at::empty({P, rx.size(1)}, rx.options()), at::empty({P}, rx.options()),
+          at::empty({P}, lopt), at::empty({P}, lopt), at::empty({rpn}, lopt)};
+}
+
+void k2_checks(const Tensor& hidden, const Tensor& expert_idx, const Tensor& gates, int64_t world,
+               int64_t n_experts, int64_t rpn, int64_t groups_m) {
+  TORCH_CHECK(hidden.dim() == 2 && expert_idx.dim() == 2 && gates.dim() == 2, "k2_pack: 2-D inputs");
+  TORCH_CHECK(expert_idx.scalar_type() == at::kLong, "k2_pack: expert_idx must be int64");
+  TORCH_CHECK(gates.scalar_type() == hidden.scalar_type(),
+              "k2_pack: gates dtype must equal hidden dtype");
+  TORCH_CHECK(hidden.size(0) == expert_idx.size(0) && gates.sizes() == expert_idx.sizes(),
+              "k2_pack: geometry mismatch");
+  TORCH_CHECK(world > 0 && rpn > 0 && groups_m > 0 && n_experts > 0, "k2_pack: bad scalars");
+  TORCH_CHECK(world % rpn == 0 && n_experts % world == 0 && expert_idx.size(1) % groups_m == 0,
+              "k2_pack: world/rpn/n_experts/k/groups_m do not divide");
+  TORCH_CHECK(world / rpn <= 1024 && expert_idx.size(1) <= 32, "k2_pack: N_g <= 1024, k <= 32");
+  TORCH_CHECK(n_experts < (1LL << 31) && expert_idx.numel() < (1LL << 31), "k2_pack: id range");
+}
+
+Tup5 k2_pack_cuda(const Tensor& hidden_, const Tensor& expert_idx_, const Tensor& gates_,
+                  int64_t world, int64_t n_experts, int64_t rpn, int64_t groups_m) {
+  k2_checks(hidden_, expert_idx_, gates_, world, n_experts, rpn, groups_m);
+  c10::cuda::CUDAGuard guard(hidden_.device());
+  Tensor hidden = hidden_.contiguous(), eidx = expert_idx_.contiguous(), gates = gates_.contiguous();
+  const int64_t T = eidx.size(0), k = eidx.size(1), H = hidden.size(1);
+  const int64_t q = k / groups_m, P = T * groups_m, n_nodes = world / rpn;
+  const int64_t slots = (n_experts / world) * rpn;
+  auto lopt = hidden.options().dtype(at::kLong);
+  Tensor payload = at::empty({P, H}, hidden.options());
+  Tensor mask = at::zeros({P, q}, lopt);
+  Tensor gate_rows = at::zeros({P, q}, hidden.options());
+  Tensor u_src = at::zeros({P}, lopt);
+  Tensor node_counts = at::zeros({n_nodes}, lopt);
+  if (P == 0) return {payload, mask, gate_rows, u_src, node_counts};
+  Tensor scratch = at::empty(
+      {static_cast<int64_t>(tb200_k2_scratch_ints(T, k, groups_m, n_nodes))},
+      hidden.options().dtype(at::kInt));
+  check_rc(tb200_k2_pack(hidden.data_ptr(), i64(eidx), gates.data_ptr(),
+                         payload.data_ptr(), i64(mask), gate_rows.data_ptr(),
+                         i64(u_src), i64(node_counts),
+                         scratch.data_ptr<int>(), T, k, groups_m, slots, n_nodes,
+                         static_cast<int>(H * hidden.element_size()),
+                         static_cast<int>(hidden.element_size()), status_ptr(hidden), cur_stream()),
+           "k2_pack");
+  return {payload, mask, gate_rows, u_src, node_counts};
+}
+
+Tup5 k2_pack_meta(const Tensor& hidden, const Tensor& expert_idx, const Tensor& gates,
+                  int64_t world, int64_t n_experts, int64_t rpn, int64_t groups_m) {
+  const int64_t T = expert_idx.size(0), k = expert_idx.size(1);
+  const int64_t q = k / groups_m, P = T * groups_m;
+  auto lopt = hidden.options().dtype(at::kLong);
+  return {at::empty({P, hidden.size(1)}, hidden.options()), at::empty({P, q}, lopt),
+          at::empty({P, q}, hidden.options()), at::empty({P}, lopt),
+          at::empty({world / rpn}, lopt)};
+}
+
+// ---------------------------------------------------------------------------------------------
+std::tuple<Tensor, Tensor> rmsnorm_fwd(const Tensor& x, const Tensor& w, double eps) {
+  CHECK_CUDA_CONTIG(x);
+  CHECK_CUDA_CONTIG(w);
+  TORCH_CHECK(x.scalar_type() == w.scalar_type(), "rmsnorm: x and w dtypes differ");
+  TORCH_CHECK(x.scalar_type() == at::kBFloat16 || x.scalar_type() == at::kFloat,
+              "rmsnorm: bf16 or fp32");
+  c10::cuda::CUDAGuard guard(x.device());
+  const int64_t dim = x.size(-1), rows = x.numel() / dim;
+  TORCH_CHECK(w.numel() == dim, "rmsnorm: weight length");
+  Tensor y = at::empty_like(x);
+  Tensor rstd = at::empty({rows}, x.options().dtype(at::kFloat));
+  check_rc(tb200_rmsnorm_fwd(x.data_ptr(), w.data_ptr(), y.data_ptr(), rstd.data_ptr<float>(), rows,
+                             static_cast<int>(dim), static_cast<float>(eps),
+                             x.scalar_type() == at::kBFloat16, cur_stream()),
+           "rmsnorm_fwd");
+  return {y, rstd};
+}
+
+std::tuple<Tensor, Tensor> rmsnorm_bwd(const Tensor& x, const Tensor& w, const Tensor& dy,
+                                       const Tensor& rstd) {
+  CHECK_CUDA_CONTIG(x);
+  CHECK_CUDA_CONTIG(dy);
+  c10::cuda::CUDAGuard guard(x.device());
+  const int64_t dim = x.size(-1), rows = x.numel() / dim;
+  Tensor dx = at::empty_like(x);
+  const int n_partial = 148;
+  Tensor part = at::empty({n_partial, dim}, x.options().dtype(at::kFloat));
+  check_rc(tb200_rmsnorm_bwd(x.data_ptr(), w.data_ptr(), dy.data_ptr(), rstd.data_ptr<float>(),
+                             dx.data_ptr(), part.data_ptr<float>(), n_partial, rows,
+                             static_cast<int>(dim), x.scalar_type() == at::kBFloat16, cur_stream()),
+           "rmsnorm_bwd");
+  return {dx, part};
+}
+
+// ---------------------------------------------------------------------------------------------
+Tup5 route_select(const Tensor& logits, const Tensor& bias, int64_t n_groups, int64_t top_k,
+                  int64_t top_groups, int64_t pool) {
+  CHECK_CUDA_CONTIG(logits);
+  CHECK_CUDA_CONTIG(bias);
+  TORCH_CHECK(logits.scalar_type() == at::kFloat && bias.scalar_type() == at::kFloat,
+              "route_select: fp32 logits and bias");
+  c10::cuda::CUDAGuard guard(logits.device());
+  const int64_t T = logits.size(0), E = logits.size(1);
+  auto lopt = logits.options().dtype(at::kLong);
+  Tensor idx = at::empty({T, top_k}, lopt);
+  Tensor gates = at::empty({T, top_k}, logits.options());
+  Tensor aff = at::empty({T, top_k}, logits.options());
+  Tensor gidx = at::empty({T, top_groups}, lopt);
+  Tensor load = at::zeros({E}, logits.options());
+  check_rc(tb200_route_select(logits.data_ptr<float>(), bias.data_ptr<float>(),
+                              i64(idx), gates.data_ptr<float>(),
+                              i64(gidx), load.data_ptr<float>(),
+                              aff.data_ptr<float>(), T, E, n_groups, top_k, top_groups, pool,
+                              cur_stream()),
+           "route_select");
+  return {idx, gates, gidx, load, aff};
+}
+
+Tensor route_select_bwd(const Tensor& dgates, const Tensor& gates, const Tensor& aff,
+                        const Tensor& idx, int64_t E) {
+  CHECK_CUDA_CONTIG(dgates);
+  c10::cuda::CUDAGuard guard(dgates.device());
+  const int64_t T = idx.size(0), k = idx.size(1);
+  Tensor dlogits = at::zeros({T, E}, gates.options());
+  Tensor dg = dgates.to(at::kFloat).contiguous();
+  check_rc(tb200_route_select_bwd(dg.data_ptr<float>(), gates.data_ptr<float>(),
+                                  aff.data_ptr<float>(), i64(idx),
+                                  dlogits.data_ptr<float>(), T, E, k, cur_stream()),
+           "route_select_bwd");
+  return dlogits;
+}
+
+// ---------------------------------------------------------------------------------------------
+std::tuple<Tensor, Tensor, Tensor, Tensor, Tensor, Tensor> moe_plan(
+    const Tensor& expert_idx, const c10::optional<Tensor>& gates, int64_t E, int64_t seg_align) {
+  CHECK_CUDA_CONTIG(expert_idx);
+  TORCH_CHECK(expert_idx.scalar_type() == at::kLong && expert_idx.dim() == 2, "moe_plan: idx");
+  c10::cuda::CUDAGuard guard(expert_idx.device());
+  const int64_t T = expert_idx.size(0), k = expert_idx.size(1);
+  auto iopt = expert_idx.options().dtype(at::kInt);
+  auto fopt = expert_idx.options().dtype(at::kFloat);
+  Tensor es = at::empty({T, k}, iopt), cols = at::empty({T, k}, iopt), pos = at::empty({T, k}, iopt);
+  Tensor gs = at::empty({T, k}, fopt);
+  Tensor seg_start = at::empty({E}, iopt), seg_count = at::empty({E}, iopt);
+  Tensor scratch = at::empty({static_cast<int64_t>(tb200_plan_scratch_ints(T, k, E))}, iopt);
+  const float* gp = nullptr;
+  Tensor g32;
+  if (gates.has_value()) {
+    g32 = gates->to(at::kFloat).contiguous();
+    gp = g32.data_ptr<float>();
+  }
+  check_rc(tb200_moe_plan(i64(expert_idx), gp, es.data_ptr<int>(),
+                          gs.data_ptr<float>(), cols.data_ptr<int>(), pos.data_ptr<int>(),
+                          seg_start.data_ptr<int>(), seg_count.data_ptr<int>(),
+                          scratch.data_ptr<int>(), T, k, E, seg_align, cur_stream()),
+           "moe_plan");
+  return {es, gs, cols, pos, seg_start, seg_count};
+}
+
+Tensor moe_scatter_rows(const Tensor& x, const Tensor& pos, int64_t rows_out) {
+  CHECK_CUDA_CONTIG(x);
+  CHECK_CUDA_CONTIG(pos);
+  TORCH_CHECK(x.scalar_type() == at::kBFloat16 && x.dim() == 2, "moe_scatter_rows: bf16 [T, H]");
+  c10::cuda::CUDAGuard guard(x.device());
+  const int64_t T = pos.size(0), k = pos.size(1);
+  Tensor xs = at::empty({rows_out, x.size(1)}, x.options());
+  check_rc(tb200_moe_scatter_rows(x.data_ptr(), xs.data_ptr(), pos.data_ptr<int>(), T, k,
+                                  x.size(1), rows_out, status_ptr(x), cur_stream()),
+           "moe_scatter_rows");
+  return xs;
+}
+
+Tensor moe_combine(const Tensor& out, const Tensor& pos, const Tensor& es,
+                   const c10::optional<Tensor>& gs, int64_t group_size) {
+  CHECK_CUDA_CONTIG(out);
+  TORCH_CHECK(out.scalar_type() == at::kBFloat16, "moe_combine: bf16 rows");
+  c10::cuda::CUDAGuard guard(out.device());
+  const int64_t T = pos.size(0), k = pos.size(1);
+  Tensor y = at::empty({T, out.size(1)}, out.options());
+  check_rc(tb200_moe_combine(out.data_ptr(), pos.data_ptr<int>(), es.data_ptr<int>(),
+                             gs.has_value() ? gs->data_ptr<float>() : nullptr, y.data_ptr(), T, k,
+                             out.size(1), group_size, out.size(0), status_ptr(out), cur_stream()),
+           "moe_combine");
+  return y;
+}
+
+std::tuple<Tensor, Tensor> moe_combine_bwd(const Tensor& dy, const Tensor& out, const Tensor& pos,
+                                           const c10::optional<Tensor>& gs, bool need_dgs) {
+  CHECK_CUDA_CONTIG(dy);
+  CHECK_CUDA_CONTIG(out);
+  c10::cuda::CUDAGuard guard(dy.device());
+  const int64_t T = pos.size(0), k = pos.size(1);
+  Tensor dout = at::zeros_like(out);
+  Tensor dgs = need_dgs ? at::empty({T, k}, dy.options().dtype(at::kFloat)) : Tensor();
+  check_rc(tb200_moe_combine_bwd(dy.data_ptr(), out.data_ptr(), pos.data_ptr<int>(),
+                                 gs.has_value() ? gs->data_ptr<float>() : nullptr, dout.data_ptr(),
+                                 need_dgs ? dgs.data_ptr<float>() : nullptr, T, k, dy.size(1),
+                                 out.size(0), status_ptr(dy), cur_stream()),
+           "moe_combine_bwd");
+  return {dout, need_dgs ? dgs : at::empty({0}, dy.options().dtype(at::kFloat))};
+}
+
+Tensor swiglu_bwd(const Tensor& h13, const Tensor& dact) {
+  CHECK_CUDA_CONTIG(h13);
+  CHECK_CUDA_CONTIG(dact);
+  c10::cuda::CUDAGuard guard(h13.device());
+  Tensor dh = at::empty_like(h13);
+  check_rc(tb200_swiglu_bwd(h13.data_ptr(), dact.data_ptr(), dh.data_ptr(), dact.size(0),
+                            dact.size(1), cur_stream()),
+           "swiglu_bwd");
+  return dh;
+}
+
+// ---------------------------------------------------------------------------------------------
+// grouped GEMMs.  mode 0: B[g] is [K, N(*2 for SwiGLU)];  mode 1: B[g] is [N, K].
+std::tuple<Tensor, Tensor> grouped_gemm(const Tensor& A, const Tensor& B, const Tensor& seg_start,
+                                        const Tensor& seg_count, int64_t mode, int64_t epilogue,
+                                        bool save_pre, int64_t max_ctas) {
+  CHECK_CUDA_CONTIG(A);
+  CHECK_CUDA_CONTIG(B);
+  TORCH_CHECK(A.scalar_type() == at::kBFloat16 && B.scalar_type() == at::kBFloat16,
+              "grouped_gemm: bf16 operands");
+  TORCH_CHECK(A.dim() == 2 && B.dim() == 3, "grouped_gemm: A [rows, K], B [G, r, c]");
+  TORCH_CHECK(seg_start.scalar_type() == at::kInt && seg_count.scalar_type() == at::kInt,
+              "grouped_gemm: int32 segment tables");
+  c10::cuda::CUDAGuard guard(A.device());
+  const int64_t rows = A.size(0), K = A.size(1), G = B.size(0);
+  const int64_t b_rows = B.size(1), b_cols = B.size(2);
+  int64_t N;
+  if (mode == 0) {
+    TORCH_CHECK(b_rows == K, "grouped_gemm fwd: B rows must equal K");
+    N = epilogue == 1 ? b_cols / 2 : b_cols;
+  } else {
+    TORCH_CHECK(b_cols == K, "grouped_gemm dgrad: B cols must equal K");
+    N = epilogue == 1 ? b_rows / 2 : b_rows;
+  }
+  TORCH_CHECK(seg_start.numel() == G && seg_count.numel() == G, "grouped_gemm: segment tables");
+  Tensor C = at::empty({rows, N}, A.options());
+  Tensor C2 = (epilogue == 1 && save_pre) ? at::empty({rows, 2 * N}, A.options()) : Tensor();
+  if (rows > 0)
+    check_rc(tb200_grouped_gemm(A.data_ptr(), B.data_ptr(), C.data_ptr(),
+                                C2.defined() ? C2.data_ptr() : nullptr, seg_start.data_ptr<int>(),
+                                seg_count.data_ptr<int>(), G, rows, N, K, N, 2 * N, b_rows, b_cols,
+                                mode, epilogue, status_ptr(A), max_ctas, cur_stream()),
+             "grouped_gemm");
+  return {C, C2.defined() ? C2 : at::empty({0}, A.options())};
+}
+
+Tensor grouped_wgrad(const Tensor& X, const Tensor& dY, const Tensor& seg_start,
+                     const Tensor& seg_count, int64_t max_ctas) {
+  CHECK_CUDA_CONTIG(X);
+  CHECK_CUDA_CONTIG(dY);
+  TORCH_CHECK(X.scalar_type() == at::kBFloat16 && dY.scalar_type() == at::kBFloat16,
+              "grouped_wgrad: bf16 operands");
+  TORCH_CHECK(X.size(0) == dY.size(0), "grouped_wgrad: row mismatch");
+  c10::cuda::CUDAGuard guard(X.device());
+  const int64_t G = seg_start.numel();
+  Tensor dW = at::empty({G, X.size(1), dY.size(1)}, X.options());
+  check_rc(tb200_grouped_wgrad(X.data_ptr(), dY.data_ptr(), dW.data_ptr(),
+                               seg_start.data_ptr<int>(), seg_count.data_ptr<int>(), G, X.size(0),
+                               X.size(1), dY.size(1), status_ptr(X), max_ctas, cur_stream()),
+           "grouped_wgrad");
+  return dW;
+}
+
+}  // namespace
+
+TORCH_LIBRARY(terrace, m) {
+  m.def("passthrough(Tensor x) -> Tensor");
+  m.def("k1_arrival(Tensor rx, Tensor rslot, Tensor rgate, int quota, int epr, int rpn, "
+        "int my_local) -> (Tensor, Tensor, Tensor, Tensor, Tensor)");
+  m.def("k2_pack(Tensor hidden, Tensor expert_idx, Tensor gates, int world, int n_experts, "
+        "int rpn, int groups_m) -> (Tensor, Tensor, Tensor, Tensor, Tensor)");
+  m.def("take_status(int device) -> int", &take_status);
+  m.def("rmsnorm_fwd(Tensor x, Tensor w, float eps) -> (Tensor, Tensor)", &rmsnorm_fwd);
+  m.def("rmsnorm_bwd(Tensor x, Tensor w, Tensor dy, Tensor rstd) -> (Tensor, Tensor)",
+        &rmsnorm_bwd);
+  m.def("route_select(Tensor logits, Tensor bias, int n_groups, int top_k, int top_groups, "
+        "int pool) -> (Tensor, Tensor, Tensor, Tensor, Tensor)", &route_select);
+  m.def("route_select_bwd(Tensor dgates, Tensor gates, Tensor aff, Tensor idx, int E) -> Tensor",
+        &route_select_bwd);
+  m.def("moe_plan(Tensor expert_idx, Tensor? gates, int E, int seg_align) -> "
+        "(Tensor, Tensor, Tensor, Tensor, Tensor, Tensor)", &moe_plan);
+  m.def("moe_scatter_rows(Tensor x, Tensor pos, int rows_out) -> Tensor", &moe_scatter_rows);
+  m.def("moe_combine(Tensor out, Tensor pos, Tensor es, Tensor? gs, int group_size) -> Tensor",
+        &moe_combine);
+  m.def("moe_combine_bwd(Tensor dy, Tensor out, Tensor pos, Tensor? gs, bool need_dgs) -> "
+        "(Tensor, Tensor)", &moe_combine_bwd);
+  m.def("swiglu_bwd(Tensor h13, Tensor dact) -> Tensor", &swiglu_bwd);
+  m.def("grouped_gemm(Tensor A, Tensor B, Tensor seg_start, Tensor seg_count, int mode, "
+        "int epilogue, bool save_pre, int max_ctas) -> (Tensor, Tensor)", &grouped_gemm);
+  m.def("grouped_wgrad(Tensor X, Tensor dY, Tensor seg_start, Tensor seg_count, int max_ctas) "
+        "-> Tensor", &grouped_wgrad);
+  terrace_b200_register_symm(m);
+}
+
+TORCH_LIBRARY_IMPL(terrace, CUDA, m) {
+  m.impl("passthrough", &passthrough_cuda);
+  m.impl("k1_arrival", &k1_arrival_cuda);
+  m.impl("k2_pack", &k2_pack_cuda);
+}
+
+TORCH_LIBRARY_IMPL(terrace, Meta, m) {
+  m.impl("passthrough", &passthrough_meta);
+  m.impl("k1_arrival", &k1_arrival_meta);
+  m.impl("k2_pack", &k2_pack_meta);
+}

@@ -1,0 +1,584 @@
+// Grouped / dense bf16 GEMMs for sm_100a on the 5th-generation tensor cores.
+//
+//   tcgen05.mma (cta_group::1, kind::f16, 128 x 256 x 16 per instruction) issued by one elected
+//   thread, operands staged in shared memory by TMA (cp.async.bulk.tensor, 128-byte swizzle),
+//   fp32 accumulators in TMEM (two 256-column stages, so the epilogue of tile i overlaps the main
+//   loop of tile i+1), epilogue through tcgen05.ld.  Persistent CTAs (one per SM) walk a tile
+//   list that every CTA derives on the device from the per-expert row counts, so no host sync
+//   is needed between routing and the expert GEMMs.
+//
+// Three operand-layout variants cover every GEMM of the MoE layer and of the dense layers:
+//   * fwd   : C[rows, N]  = A[rows, K] * W[e][K, N]      (A K-major, B N-major)   x @ w13, h @ w2
+//   * dgrad : C[rows, N]  = A[rows, K] * W[e][N, K]^T    (A K-major, B K-major)   dy @ w^T, nn.Linear
+//   * wgrad : W'[e][M, N] = A[rows, M]^T * B[rows, N]    (A M-major, B N-major)   x^T @ dy
+// The fwd variant has an optional fused SwiGLU epilogue: the B tile holds 128 gate columns and
+// the matching 128 up columns, and the epilogue writes silu(gate) * up (and, for training, the
+// two pre-activations).
+//
+// Computes what the reference does with a Python loop of per-expert matmuls
+// (terrace/layer.py:30-68 `_grouped_mm_fwd` / `_GroupedMM`).
+#include "launch.h"
+#include "ptx_sm100.cuh"
+
+#include <cuda.h>
+#include <cuda_runtime.h>
+
+namespace tb200 {
+
+constexpr int BM = 128;
+constexpr int BN = 256;
+constexpr int BK = 64;                 // 64 bf16 = 128 bytes = one swizzle line
+constexpr int STAGES = 4;
+constexpr int A_BYTES = BM * BK * 2;   // 16 KiB
+constexpr int B_BYTES = BN * BK * 2;   // 32 KiB
+constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+constexpr int BOX_BYTES = 64 * BK * 2; // one 64 x 64 box = 8 KiB
+constexpr int GEMM_THREADS = 192;      // warp 0 TMA, warp 1 MMA, warps 2..5 epilogue
+constexpr int MAX_GROUPS = 1024;
+constexpr int TMEM_COLS = 512;
+
+struct GemmParams {
+  const int* seg_start;   // [E] first row of every group in A / C
+  const int* seg_count;   // [E] rows of every group
+  int n_groups;
+  int N;                  // output columns per group (for SwiGLU: the activation width d)
+  int K;                  // reduction length (wgrad: unused, rows come from seg_count)
+  int M;                  // wgrad only: rows of the weight gradient (input features)
+  int ldc;                // row stride of C in elements
+  int ldc2;               // row stride of C2 in elements
+  int up_offset;          // SwiGLU: column of the first up-projection weight (= d)
+  __nv_bfloat16* C;
+  __nv_bfloat16* C2;      // SwiGLU: optional [rows, 2d] pre-activations (may be null)
+  int* status;
+};
+
+struct __align__(8) PipeBarriers {
+  uint64_t full[STAGES];
+  uint64_t empty[STAGES];
+  uint64_t acc_full[2];
+  uint64_t acc_empty[2];
+};
+
+struct SharedCtl {
+  PipeBarriers bars;
+  uint32_t tmem_base;
+  volatile int abort_flag;
+  int total_tiles;
+  int tile_start[MAX_GROUPS + 1];
+};
+
+__device__ __forceinline__ void raise_abort(SharedCtl* ctl, int* status, int code) {
+  ctl->abort_flag = code;
+  if (status != nullptr) atomicCAS(status, 0, code);
+}
+
+// Whole-warp bounded wait with a warp-uniform verdict (lanes must not disagree, the callers
+// use warp-synchronous instructions afterwards).
+__device__ __forceinline__ bool warp_wait(uint64_t* bar, uint32_t parity,
+                                          volatile int* abort_flag) {
+  const bool got = mbar_wait(bar, parity, abort_flag);
+  return __all_sync(0xffffffffu, got);
+}
+
+__device__ __forceinline__ uint32_t pack_bf16(float a, float b) {
+  __nv_bfloat162 v = __floats2bfloat162_rn(a, b);
+  return *reinterpret_cast<uint32_t*>(&v);
+}
+
+__device__ __forceinline__ float silu_f(float x) { return x / (1.0f + __expf(-x)); }
+
+// Locate the group of global tile index t (tile_start is a prefix array); `e` is a cursor that
+// only moves forward because every role visits tiles in increasing order.
+__device__ __forceinline__ void locate_tile(const SharedCtl* ctl, int n_groups, int t, int& e) {
+  while (e + 1 < n_groups && t >= ctl->tile_start[e + 1]) ++e;
+}
+
+enum { MODE_FWD = 0, MODE_DGRAD = 1, MODE_WGRAD = 2 };
+enum { EPI_PLAIN = 0, EPI_SWIGLU = 1 };
+
+template <int MODE, int EPI>
+__global__ void __launch_bounds__(GEMM_THREADS, 1)
+gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+            const GemmParams p) {
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  // stage buffers need 1024-byte alignment for the 128-byte swizzle
+  uint8_t* stage_base = reinterpret_cast<uint8_t*>(
+      (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
+  SharedCtl* ctl = reinterpret_cast<SharedCtl*>(stage_base + STAGES * STAGE_BYTES);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int n_tiles_n = (MODE == MODE_WGRAD) ? (p.N + BN - 1) / BN
+                        : (EPI == EPI_SWIGLU) ? (p.N + 127) / 128
+                                              : (p.N + BN - 1) / BN;
+  const int n_tiles_m_w = (p.M + BM - 1) / BM;   // wgrad only
+
+  // ---- one-time setup ---------------------------------------------------------------------
+  if (threadIdx.x == 0) {
+    int acc = 0;
+    for (int e = 0; e < p.n_groups; ++e) {
+      ctl->tile_start[e] = acc;
+      if (MODE == MODE_WGRAD) {
+        acc += n_tiles_m_w * n_tiles_n;
+      } else {
+        int cnt = p.seg_count[e];
+        acc += ((cnt + BM - 1) / BM) * n_tiles_n;
+      }
+    }
+    ctl->tile_start[p.n_groups] = acc;
+    ctl->total_tiles = acc;
+    ctl->abort_flag = 0;
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(&ctl->bars.full[s], 1);
+      mbar_init(&ctl->bars.empty[s], 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(&ctl->bars.acc_full[a], 1);
+      mbar_init(&ctl->bars.acc_empty[a], 4);
+    }
+    fence_barrier_init();
+  }
+  if (warp == 1) {
+    tmem_alloc(&ctl->tmem_base, TMEM_COLS);
+    tmem_relinquish();
+  }
+  if (warp == 0 && lane == 0) {
+    prefetch_tmap(&tmap_a);
+    prefetch_tmap(&tmap_b);
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = ctl->tmem_base;
+  const int total_tiles = ctl->total_tiles;
+
+  if (warp == 0) {
+    // =========================== TMA producer =============================================
+    if (lane == 0) {
+      int e = 0;
+      uint32_t it = 0;
+      bool ok = true;
+      for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
+        locate_tile(ctl, p.n_groups, t, e);
+        const int local = t - ctl->tile_start[e];
+        const int mt = local / n_tiles_n;
+        const int nt = local - mt * n_tiles_n;
+        const int seg0 = p.seg_start[e];
+        const int cnt = p.seg_count[e];
+        const int kblocks = (MODE == MODE_WGRAD) ? (cnt + BK - 1) / BK : (p.K + BK - 1) / BK;
+        for (int kb = 0; kb < kblocks; ++kb, ++it) {
+          const int s = it % STAGES;
+          const uint32_t round = it / STAGES;
+          if (round > 0 && !mbar_wait(&ctl->bars.empty[s], (round - 1) & 1, &ctl->abort_flag)) {
+            raise_abort(ctl, p.status, ST_TIMEOUT_EMPTY);
+            ok = false;
+            break;
+          }
+          uint8_t* sa = stage_base + s * STAGE_BYTES;
+          uint8_t* sb = sa + A_BYTES;
+          uint64_t* bar = &ctl->bars.full[s];
+          mbar_expect_tx(bar, STAGE_BYTES);
+          if (MODE == MODE_WGRAD) {
+            const int row0 = seg0 + kb * BK;
+            for (int j = 0; j < 2; ++j)
+              tma_load_2d(sa + j * BOX_BYTES, &tmap_a, bar, mt * BM + j * 64, row0);
+            for (int j = 0; j < 4; ++j)
+              tma_load_2d(sb + j * BOX_BYTES, &tmap_b, bar, nt * BN + j * 64, row0);
+          } else {
+            tma_load_2d(sa, &tmap_a, bar, kb * BK, seg0 + mt * BM);
+            if (MODE == MODE_DGRAD && EPI == EPI_SWIGLU) {
+              // weight rows [gate | up]: 128 gate rows, then the matching 128 up rows
+              tma_load_3d(sb, &tmap_b, bar, kb * BK, nt * 128, e);
+              tma_load_3d(sb + B_BYTES / 2, &tmap_b, bar, kb * BK, p.up_offset + nt * 128, e);
+            } else if (MODE == MODE_DGRAD) {
+              tma_load_3d(sb, &tmap_b, bar, kb * BK, nt * BN, e);
+            } else if (EPI == EPI_SWIGLU) {
+              for (int j = 0; j < 2; ++j)
+                tma_load_3d(sb + j * BOX_BYTES, &tmap_b, bar, nt * 128 + j * 64, kb * BK, e);
+              for (int j = 0; j < 2; ++j)
+                tma_load_3d(sb + (2 + j) * BOX_BYTES, &tmap_b, bar,
+                            p.up_offset + nt * 128 + j * 64, kb * BK, e);
+            } else {
+              for (int j = 0; j < 4; ++j)
+                tma_load_3d(sb + j * BOX_BYTES, &tmap_b, bar, nt * BN + j * 64, kb * BK, e);
+            }
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // =========================== MMA issuer ===============================================
+    constexpr uint32_t idesc =
+        make_idesc_bf16(BM, BN, MODE == MODE_WGRAD, MODE != MODE_DGRAD);
+    int e = 0;
+    uint32_t it = 0;
+    uint32_t tile_iter = 0;
+    bool ok = true;
+    for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x, ++tile_iter) {
+      locate_tile(ctl, p.n_groups, t, e);
+      const int cnt = p.seg_count[e];
+      const int kblocks = (MODE == MODE_WGRAD) ? (cnt + BK - 1) / BK : (p.K + BK - 1) / BK;
+      const int a = tile_iter & 1;
+      const uint32_t around = tile_iter >> 1;
+      if (around > 0 &&
+          !warp_wait(&ctl->bars.acc_empty[a], (around - 1) & 1, &ctl->abort_flag)) {
+        if (lane == 0) raise_abort(ctl, p.status, ST_TIMEOUT_ACC);
+        ok = false;
+        break;
+      }
+      tc_fence_after();
+      const uint32_t d_tmem = tmem_base + a * BN;
+      for (int kb = 0; kb < kblocks; ++kb, ++it) {
+        const int s = it % STAGES;
+        const uint32_t round = it / STAGES;
+        if (!warp_wait(&ctl->bars.full[s], round & 1, &ctl->abort_flag)) {
+          if (lane == 0) raise_abort(ctl, p.status, ST_TIMEOUT_FULL);
+          ok = false;
+          break;
+        }
+        uint8_t* sa = stage_base + s * STAGE_BYTES;
+        uint8_t* sb = sa + A_BYTES;
+        if (MODE == MODE_WGRAD) {
+          // rows past the end of the group belong to the next group: zero their lines
+          const int valid = cnt - kb * BK;
+          if (valid < BK) {
+            const int lines = BK - valid;
+            for (int i = lane; i < lines * 8 * 6; i += 32) {
+              const int box = i / (lines * 8);
+              const int r = i - box * lines * 8;
+              const int line = valid + (r >> 3);
+              uint8_t* base = (box < 2 ? sa + box * BOX_BYTES : sb + (box - 2) * BOX_BYTES);
+              *reinterpret_cast<uint4*>(base + line * 128 + (r & 7) * 16) = make_uint4(0, 0, 0, 0);
+            }
+            fence_proxy_async_smem();
+          }
+          __syncwarp();
+        }
+        tc_fence_after();
+        if (lane == 0) {
+          const uint32_t a_addr = smem_u32(sa);
+          const uint32_t b_addr = smem_u32(sb);
+#pragma unroll
+          for (int k4 = 0; k4 < BK / 16; ++k4) {
+            uint64_t da, db;
+            if (MODE == MODE_WGRAD) {
+              da = make_smem_desc(a_addr + k4 * 2048, BOX_BYTES, 1024);
+            } else {
+              da = make_smem_desc(a_addr + k4 * 32, 16, 1024);
+            }
+            if (MODE == MODE_DGRAD) {
+              db = make_smem_desc(b_addr + k4 * 32, 16, 1024);
+            } else {
+              db = make_smem_desc(b_addr + k4 * 2048, BOX_BYTES, 1024);
+            }
+            umma_bf16(d_tmem, da, db, idesc, (kb | k4) != 0 ? 1u : 0u);
+          }
+          umma_commit(&ctl->bars.empty[s]);     // frees the stage when these MMAs retire
+        }
+        __syncwarp();
+      }
+      if (ok && lane == 0) umma_commit(&ctl->bars.acc_full[a]);
+      __syncwarp();
+    }
+  } else {
+    // =========================== epilogue (4 warps) =======================================
+    const int quad = warp & 3;                 // TMEM lane quadrant this warp may read
+    const int row_in_tile = quad * 32 + lane;
+    int e = 0;
+    uint32_t tile_iter = 0;
+    bool ok = true;
+    for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x, ++tile_iter) {
+      locate_tile(ctl, p.n_groups, t, e);
+      const int local = t - ctl->tile_start[e];
+      const int mt = local / n_tiles_n;
+      const int nt = local - mt * n_tiles_n;
+      const int cnt = p.seg_count[e];
+      const int seg0 = p.seg_start[e];
+      const int a = tile_iter & 1;
+      const uint32_t around = tile_iter >> 1;
+      if (!warp_wait(&ctl->bars.acc_full[a], around & 1, &ctl->abort_flag)) {
+        if (lane == 0) raise_abort(ctl, p.status, ST_TIMEOUT_ACC);
+        ok = false;
+        break;
+      }
+      tc_fence_after();
+      const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + a * BN;
+      if (MODE == MODE_WGRAD) {
+        const int m = mt * BM + row_in_tile;
+        const bool empty_group = cnt == 0;     // no MMA ran: the accumulator is undefined
+        __nv_bfloat16* crow = p.C + (static_cast<size_t>(e) * p.M + m) * p.ldc;
+#pragma unroll 1
+        for (int c = 0; c < BN / 32; ++c) {
+          uint32_t r[32];
+          tmem_ld_32x32(taddr + c * 32, r);
+          tmem_ld_wait();
+          const int n0 = nt * BN + c * 32;
+          if (m < p.M) {
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              if (n0 + j * 8 < p.N) {
+                uint4 v;
+                if (empty_group) {
+                  v = make_uint4(0, 0, 0, 0);
+                } else {
+                  v.x = pack_bf16(__uint_as_float(r[j * 8 + 0]), __uint_as_float(r[j * 8 + 1]));
+                  v.y = pack_bf16(__uint_as_float(r[j * 8 + 2]), __uint_as_float(r[j * 8 + 3]));
+                  v.z = pack_bf16(__uint_as_float(r[j * 8 + 4]), __uint_as_float(r[j * 8 + 5]));
+                  v.w = pack_bf16(__uint_as_float(r[j * 8 + 6]), __uint_as_float(r[j * 8 + 7]));
+                }
+                *reinterpret_cast<uint4*>(crow + n0 + j * 8) = v;
+              }
+            }
+          }
+        }
+      } else if (EPI == EPI_SWIGLU) {
+        const int row = mt * BM + row_in_tile;
+        const bool live = row < cnt;
+        __nv_bfloat16* crow = p.C + static_cast<size_t>(seg0 + row) * p.ldc;
+        __nv_bfloat16* c2row =
+            p.C2 ? p.C2 + static_cast<size_t>(seg0 + row) * p.ldc2 : nullptr;
+#pragma unroll 1
+        for (int c = 0; c < 4; ++c) {
+          uint32_t g[32], u[32];
+          tmem_ld_32x32(taddr + c * 32, g);
+          tmem_ld_32x32(taddr + 128 + c * 32, u);
+          tmem_ld_wait();
+          const int n0 = nt * 128 + c * 32;
+          if (live) {
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              if (n0 + j * 8 < p.N) {
+                uint4 v, vg, vu;
+                uint32_t* pv = reinterpret_cast<uint32_t*>(&v);
+                uint32_t* pg = reinterpret_cast<uint32_t*>(&vg);
+                uint32_t* pu = reinterpret_cast<uint32_t*>(&vu);
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                  const float g0 = __uint_as_float(g[j * 8 + 2 * i]);
+                  const float g1 = __uint_as_float(g[j * 8 + 2 * i + 1]);
+                  const float u0 = __uint_as_float(u[j * 8 + 2 * i]);
+                  const float u1 = __uint_as_float(u[j * 8 + 2 * i + 1]);
+                  pg[i] = pack_bf16(g0, g1);
+                  pu[i] = pack_bf16(u0, u1);
+                  // activation from the bf16-rounded pre-activations, so that a backward pass
+                  // that re-reads them sees exactly the forward's inputs
+                  __nv_bfloat162 gb = *reinterpret_cast<__nv_bfloat162*>(&pg[i]);
+                  __nv_bfloat162 ub = *reinterpret_cast<__nv_bfloat162*>(&pu[i]);
+                  const float2 gf = __bfloat1622float2(gb);
+                  const float2 uf = __bfloat1622float2(ub);
+                  pv[i] = pack_bf16(silu_f(gf.x) * uf.x, silu_f(gf.y) * uf.y);
+                }
+                *reinterpret_cast<uint4*>(crow + n0 + j * 8) = v;
+                if (c2row) {
+                  *reinterpret_cast<uint4*>(c2row + n0 + j * 8) = vg;
+                  *reinterpret_cast<uint4*>(c2row + p.up_offset + n0 + j * 8) = vu;
+                }
+              }
+            }
+          }
+        }
+      } else {
+        const int row = mt * BM + row_in_tile;
+        const bool live = row < cnt;
+        __nv_bfloat16* crow = p.C + static_cast<size_t>(seg0 + row) * p.ldc;
+#pragma unroll 1
+        for (int c = 0; c < BN / 32; ++c) {
+          uint32_t r[32];
+          tmem_ld_32x32(taddr + c * 32, r);
+          tmem_ld_wait();
+          const int n0 = nt * BN + c * 32;
+          if (live) {
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              if (n0 + j * 8 < p.N) {
+                uint4 v;
+                v.x = pack_bf16(__uint_as_float(r[j * 8 + 0]), __uint_as_float(r[j * 8 + 1]));
+                v.y = pack_bf16(__uint_as_float(r[j * 8 + 2]), __uint_as_float(r[j * 8 + 3]));
+                v.z = pack_bf16(__uint_as_float(r[j * 8 + 4]), __uint_as_float(r[j * 8 + 5]));
+                v.w = pack_bf16(__uint_as_float(r[j * 8 + 6]), __uint_as_float(r[j * 8 + 7]));
+                *reinterpret_cast<uint4*>(crow + n0 + j * 8) = v;
+              }
+            }
+          }
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&ctl->bars.acc_empty[a]);
+    }
+  }
+
+  // ---- teardown: everybody meets, then the allocating warp frees TMEM ------------------------
+  if (ctl->abort_flag != 0) {
+    // give copies that may still be in flight time to land before shared memory is released
+    const unsigned long long t0 = globaltimer_ns();
+    while (globaltimer_ns() - t0 < 1000000ull) __nanosleep(256);
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, TMEM_COLS);
+  }
+}
+
+// ---------------------------------------------------------------------------------------------
+// host side
+// ---------------------------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
+                                  const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                  const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  if (fn == nullptr) {
+    void* ptr = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &q) ==
+            cudaSuccess &&
+        q == cudaDriverEntryPointSuccess) {
+      fn = reinterpret_cast<EncodeTiledFn>(ptr);
+    }
+  }
+  return fn;
+}
+
+// bf16 tensor map with 128-byte swizzle; dims/strides innermost first, strides in bytes for
+// dims 1.. (rank - 1).
+static int make_tmap(CUtensorMap* out, const void* base, int rank, const uint64_t* dims,
+                     const uint64_t* strides_bytes, const uint32_t* box) {
+  EncodeTiledFn fn = encode_fn();
+  if (fn == nullptr) return TB200_ERR_DRIVER;
+  cuuint64_t gdim[3];
+  cuuint64_t gstr[2];
+  cuuint32_t bdim[3];
+  cuuint32_t estr[3] = {1, 1, 1};
+  for (int i = 0; i < rank; ++i) {
+    gdim[i] = dims[i];
+    bdim[i] = box[i];
+  }
+  for (int i = 0; i + 1 < rank; ++i) gstr[i] = strides_bytes[i];
+  CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, static_cast<cuuint32_t>(rank),
+                  const_cast<void*>(base), gdim, gstr, bdim, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                  CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? TB200_OK : TB200_ERR_TMAP;
+}
+
+static int sm_count_cached() {
+  static int sms[64] = {0};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev < 0 || dev >= 64) return 148;
+  if (sms[dev] == 0) cudaDeviceGetAttribute(&sms[dev], cudaDevAttrMultiProcessorCount, dev);
+  return sms[dev] > 0 ? sms[dev] : 148;
+}
+
+constexpr size_t GEMM_SMEM = STAGES * STAGE_BYTES + sizeof(SharedCtl) + 1024;
+
+template <int MODE, int EPI>
+static int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p,
+                       int max_ctas, cudaStream_t stream) {
+  static bool configured = false;
+  auto kern = gemm_kernel<MODE, EPI>;
+  if (!configured) {
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             static_cast<int>(GEMM_SMEM)) != cudaSuccess)
+      return TB200_ERR_LAUNCH;
+    configured = true;
+  }
+  int grid = sm_count_cached();
+  if (max_ctas > 0 && max_ctas < grid) grid = max_ctas;
+  kern<<<grid, GEMM_THREADS, GEMM_SMEM, stream>>>(ta, tb, p);
+  return cudaGetLastError() == cudaSuccess ? TB200_OK : TB200_ERR_LAUNCH;
+}
+
+}  // namespace tb200
+
+using namespace tb200;
+
+extern "C" int tb200_grouped_gemm(const void* A, const void* B, void* C, void* C2,
+                                  const int* seg_start, const int* seg_count, int n_groups,
+                                  long long a_rows, int N, int K, int ldc, int ldc2, int b_rows,
+                                  int b_cols, int mode, int epilogue, int* status, int max_ctas,
+                                  cudaStream_t stream) {
+  if (n_groups <= 0 || n_groups > MAX_GROUPS) return TB200_ERR_ARG;
+  if ((K % 8) || (N % 8) || (ldc % 8) || (b_cols % 8)) return TB200_ERR_ARG;
+  if (mode != MODE_FWD && mode != MODE_DGRAD) return TB200_ERR_ARG;
+  CUtensorMap ta, tb;
+  {
+    uint64_t dims[2] = {static_cast<uint64_t>(K), static_cast<uint64_t>(a_rows)};
+    uint64_t str[1] = {static_cast<uint64_t>(K) * 2};
+    uint32_t box[2] = {BK, BM};
+    int rc = make_tmap(&ta, A, 2, dims, str, box);
+    if (rc != TB200_OK) return rc;
+  }
+  {
+    // B is [n_groups, b_rows, b_cols] row-major.  fwd: b_rows = K, b_cols = N(+up half).
+    // dgrad: b_rows = N, b_cols = K.
+    uint64_t dims[3] = {static_cast<uint64_t>(b_cols), static_cast<uint64_t>(b_rows),
+                        static_cast<uint64_t>(n_groups)};
+    uint64_t str[2] = {static_cast<uint64_t>(b_cols) * 2,
+                       static_cast<uint64_t>(b_cols) * static_cast<uint64_t>(b_rows) * 2};
+    uint32_t box[3] = {64, static_cast<uint32_t>(mode == MODE_DGRAD
+                                                     ? (epilogue == EPI_SWIGLU ? 128 : BN)
+                                                     : BK), 1};
+    int rc = make_tmap(&tb, B, 3, dims, str, box);
+    if (rc != TB200_OK) return rc;
+  }
+  GemmParams p{};
+  p.seg_start = seg_start;
+  p.seg_count = seg_count;
+  p.n_groups = n_groups;
+  p.N = N;
+  p.K = K;
+  p.M = 0;
+  p.ldc = ldc;
+  p.ldc2 = ldc2;
+  p.up_offset = N;
+  p.C = static_cast<__nv_bfloat16*>(C);
+  p.C2 = static_cast<__nv_bfloat16*>(C2);
+  p.status = status;
+  if (mode == MODE_DGRAD && epilogue == EPI_SWIGLU)
+    return launch_gemm<MODE_DGRAD, EPI_SWIGLU>(ta, tb, p, max_ctas, stream);
+  if (mode == MODE_DGRAD) return launch_gemm<MODE_DGRAD, EPI_PLAIN>(ta, tb, p, max_ctas, stream);
+  if (epilogue == EPI_SWIGLU) return launch_gemm<MODE_FWD, EPI_SWIGLU>(ta, tb, p, max_ctas, stream);
+  return launch_gemm<MODE_FWD, EPI_PLAIN>(ta, tb, p, max_ctas, stream);
+}
+
+extern "C" int tb200_grouped_wgrad(const void* X, const void* dY, void* dW, const int* seg_start,
+                                   const int* seg_count, int n_groups, long long rows, int M,
+                                   int N, int* status, int max_ctas, cudaStream_t stream) {
+  if (n_groups <= 0 || n_groups > MAX_GROUPS) return TB200_ERR_ARG;
+  if ((M % 8) || (N % 8)) return TB200_ERR_ARG;
+  CUtensorMap ta, tb;
+  {
+    uint64_t dims[2] = {static_cast<uint64_t>(M), static_cast<uint64_t>(rows)};
+    uint64_t str[1] = {static_cast<uint64_t>(M) * 2};
+    uint32_t box[2] = {64, BK};
+    int rc = make_tmap(&ta, X, 2, dims, str, box);
+    if (rc != TB200_OK) return rc;
+  }
+  {
+    uint64_t dims[2] = {static_cast<uint64_t>(N), static_cast<uint64_t>(rows)};
+    uint64_t str[1] = {static_cast<uint64_t>(N) * 2};
+    uint32_t box[2] = {64, BK};
+    int rc = make_tmap(&tb, dY, 2, dims, str, box);
+    if (rc != TB200_OK) return rc;
+  }
+  GemmParams p{};
+  p.seg_start = seg_start;
+  p.seg_count = seg_count;
+  p.n_groups = n_groups;
+  p.N = N;
+  p.K = 0;
+  p.M = M;
+  p.ldc = N;
+  p.ldc2 = 0;
+  p.up_offset = 0;
+  p.C = static_cast<__nv_bfloat16*>(dW);
+  p.C2 = nullptr;
+  p.status = status;
+  return launch_gemm<MODE_WGRAD, EPI_PLAIN>(ta, tb, p, max_ctas, stream);
+}

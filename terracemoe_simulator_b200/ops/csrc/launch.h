@@ -1,0 +1,94 @@
+// C launch interface of the sm_100a kernels.  Plain pointers and a stream: no allocation, no
+// torch types, so the kernels can be driven from the torch bindings (bindings.cpp) or from any
+// other host runtime.  Every function returns TB200_OK or an error code and never throws.
+#pragma once
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+enum {
+  TB200_OK = 0,
+  TB200_ERR_ARG = 1,      // unsupported shape / alignment
+  TB200_ERR_DRIVER = 2,   // driver entry point unavailable
+  TB200_ERR_TMAP = 3,     // tensor-map encode failed
+  TB200_ERR_LAUNCH = 4,   // kernel launch failed
+  TB200_ERR_SIZE = 5,     // problem exceeds a stated maximum
+};
+
+// ---- gemm_sm100.cu ---------------------------------------------------------------------------
+// mode 0 (fwd):   C[rows, N] = A[rows, K] * B[g][K, N]   (B row-major [b_rows=K, b_cols])
+// mode 1 (dgrad): C[rows, N] = A[rows, K] * B[g][N, K]^T (B row-major [b_rows=N, b_cols=K])
+// epilogue 1: B holds [gate | up] halves (fwd: b_cols = 2N; dgrad: b_rows = 2N);
+// C = silu(gate) * up, and when C2 != null the bf16 pre-activations go to C2[rows, 2N].
+// Rows of group g are A[seg_start[g] .. seg_start[g] + seg_count[g]).
+int tb200_grouped_gemm(const void* A, const void* B, void* C, void* C2, const int* seg_start,
+                       const int* seg_count, int n_groups, long long a_rows, int N, int K, int ldc,
+                       int ldc2, int b_rows, int b_cols, int mode, int epilogue, int* status,
+                       int max_ctas, cudaStream_t stream);
+// dW[g][M, N] = X[rows of g, M]^T * dY[rows of g, N]; groups with no rows get zeros.
+int tb200_grouped_wgrad(const void* X, const void* dY, void* dW, const int* seg_start,
+                        const int* seg_count, int n_groups, long long rows, int M, int N,
+                        int* status, int max_ctas, cudaStream_t stream);
+
+// ---- moe_kernels.cu --------------------------------------------------------------------------
+int tb200_passthrough(const void* src, void* dst, size_t bytes, cudaStream_t stream);
+
+int tb200_rmsnorm_fwd(const void* x, const void* w, void* y, float* rstd, long long rows, int dim,
+                      float eps, int is_bf16, cudaStream_t stream);
+int tb200_rmsnorm_bwd(const void* x, const void* w, const void* dy, const float* rstd, void* dx,
+                      float* dw_partial, int n_partial, long long rows, int dim, int is_bf16,
+                      cudaStream_t stream);
+
+// Router select (mode "full"): logits[T, E] fp32 -> idx[T, k] int64, gates[T, k] fp32,
+// group_idx[T, M] int64, load[E] fp32 (accumulated; caller zeroes).
+int tb200_route_select(const float* logits, const float* bias, long long* idx, float* gates,
+                       long long* group_idx, float* load, float* affinity_sel, int T, int E,
+                       int n_groups, int top_k, int top_groups, int pool, cudaStream_t stream);
+// dlogits[T, E] (pre-zeroed) from dgates[T, k]: through the renormalisation and the sigmoid.
+int tb200_route_select_bwd(const float* dgates, const float* gates, const float* affinity_sel,
+                           const long long* idx, float* dlogits, int T, int E, int top_k,
+                           cudaStream_t stream);
+
+// Local permutation plan: counting sort of the T*k picks by expert, stable in (token, expert).
+//   es/gs/cols [T, k]: per-token ascending expert ids, their gates, their original columns
+//   pos [T, k]: row of every (sorted) pick in the expert-sorted buffer
+//   seg_start/seg_count [E]
+// `scratch` needs tb200_plan_scratch_ints(T, k, E) ints.
+size_t tb200_plan_scratch_ints(int T, int k, int E);
+int tb200_moe_plan(const long long* expert_idx, const float* gates, int* es, float* gs, int* cols,
+                   int* pos, int* seg_start, int* seg_count, int* scratch, int T, int k, int E,
+                   int seg_align, cudaStream_t stream);
+// xs[pos[t, j]] = x[t]   (bf16 rows of `dim` elements)
+int tb200_moe_scatter_rows(const void* x, void* xs, const int* pos, int T, int k, int dim,
+                           long long xs_rows, int* status, cudaStream_t stream);
+// y[t] = sum over groups asc ( sum over picks asc in group  gs * out[pos] ), fp32 accumulation,
+// group partial and total each rounded once to bf16.  gs == null means weight 1.
+int tb200_moe_combine(const void* out, const int* pos, const int* es, const float* gs, void* y,
+                      int T, int k, int dim, int group_size, long long out_rows, int* status,
+                      cudaStream_t stream);
+// dout[pos] = gs * dy[t];  dgs[t, j] = <out[pos], dy[t]>
+int tb200_moe_combine_bwd(const void* dy, const void* out, const int* pos, const float* gs,
+                          void* dout, float* dgs, int T, int k, int dim, long long out_rows,
+                          int* status, cudaStream_t stream);
+// SwiGLU backward: h13[rows, 2d] = [gate | up], dact[rows, d] -> dh13[rows, 2d]
+int tb200_swiglu_bwd(const void* h13, const void* dact, void* dh13, long long rows, int d,
+                     cudaStream_t stream);
+
+// K1 arrival chain and K2 send-side pack (element types moved as raw bytes).
+int tb200_k1_arrival(const void* rx, const long long* rslot, const void* rgate, void* send_buf,
+                     void* gate_pairs, long long* r_idx, long long* slot_idx, long long* i_send,
+                     int* scratch, int R, int quota, int epr, int rpn, int row_bytes,
+                     int gate_bytes, int* status, cudaStream_t stream);
+size_t tb200_k1_scratch_ints(int R, int quota, int rpn);
+int tb200_k2_pack(const void* hidden, const long long* expert_idx, const void* gates,
+                  void* payload, long long* mask, void* gate_rows, long long* u_src,
+                  long long* node_counts, int* scratch, int T, int k, int groups_m, int slots,
+                  int n_nodes, int row_bytes, int gate_bytes, int* status, cudaStream_t stream);
+size_t tb200_k2_scratch_ints(int T, int k, int groups_m, int n_nodes);
+
+#ifdef __cplusplus
+}
+#endif

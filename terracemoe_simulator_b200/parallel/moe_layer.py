@@ -1,0 +1,238 @@
+"""Expert-parallel MoE layer: T-Route router + routed experts over one of four transports.
+
+``mode``      ``fused``   transport
+``local``     --          all experts on this GPU (permute, grouped GEMMs, combine kernels)
+``one_hop``   False       ``torch.distributed`` all-to-all (``parallel/ep.py``; the baseline arm)
+``one_hop``   True        fused peer-memory dispatch / combine kernels (``parallel/fused.py``)
+``two_hop``   False       T-A2A over ``torch.distributed`` (``parallel/ta2a.py``)
+``two_hop``   True        fused T-A2A: Hop A push to the group representative, Hop B push into the
+                          owner's expert-sorted GEMM input, gate-weighted pull combine
+
+The reference has no EP-aware module: its ``TerracedMoE`` is single device and the EP paths are
+bare functions (``terrace/ep_dist.py:82``, ``terrace/ta2a_fwd.py:445``).  ``EPTerracedMoE`` keeps
+``TerracedMoE``'s parameters, stats dict and in-forward bias update (``terrace/layer.py:119-130``)
+and holds only this rank's expert shard ``w13[epr, h, 2d]`` / ``w2[epr, d, h]``; the router and
+the shared expert are replicated.  The router's expert load is summed over ranks before the
+bias update so every replica takes the same step.
+"""
+from __future__ import annotations
+
+import torch
+import torch.distributed as dist
+import torch.nn as nn
+
+from .. import ops
+from ..layer import SwiGLU, apply_capacity
+from ..routing import Router, TRouteConfig, expert_load, t_route, update_bias_
+from .ep import ep_moe_forward
+from .ta2a import init_ta2a_groups, ta2a_moe_forward
+
+EP_MODES = ("local", "one_hop", "two_hop")
+
+
+def _route(x, router_w, bias, cfg):
+    """Router logits + T-Route; native kernels when available."""
+    if x.is_cuda and ops.custom_ops_enabled() and ops.router_supported(cfg, x):
+        if ops.dense_supported(x, router_w):
+            logits = ops.linear(x, router_w)
+        else:
+            logits = x @ router_w.t().to(x.dtype)
+        idx, gates, gidx, load = ops.route_from_logits(logits, bias, cfg)
+        return idx, gates, gidx, load
+    aff = torch.sigmoid((x @ router_w.t().to(x.dtype)).float())
+    idx, gates, gidx = t_route(aff, bias.float(), cfg, "full")
+    return idx, gates, gidx, expert_load(idx, cfg.n_experts)
+
+
+def routed_experts(x, idx, gates, w13, w2, cfg: TRouteConfig, *, mode: str, world: int, rpn: int,
+                   fused: bool, ctx=None):
+    """Dispatch -> expert SwiGLU -> combine for this rank's tokens, on the chosen transport."""
+    if mode not in EP_MODES:
+        raise ValueError(f"unknown EP mode {mode!r}; expected one of {EP_MODES}")
+    E = cfg.n_experts
+    if mode == "local" or world == 1:
+        if x.is_cuda and ops.custom_ops_enabled() and ops.moe_local_supported(x, w13, w2):
+            return ops.moe_experts_local(x, idx, gates, w13, w2, cfg.group_size)
+        # PyTorch path: canonical tree through the one-hop code with a single rank is not
+        # available without a process group, so use the plain grouped formulation
+        from ..layer import grouped_mm
+        T, k = idx.shape
+        flat = idx.reshape(-1)
+        order = torch.argsort(flat, stable=True)
+        tok = torch.div(order, k, rounding_mode="floor")
+        counts = torch.zeros(E, dtype=torch.int64, device=x.device).scatter_add_(
+            0, flat, torch.ones_like(flat))
+        a, b = grouped_mm(x[tok], w13, counts).chunk(2, dim=-1)
+        out = grouped_mm(torch.nn.functional.silu(a) * b, w2, counts)
+        w = gates.reshape(-1)[order].unsqueeze(-1).to(out.dtype)
+        return torch.zeros_like(x).index_add(0, tok, w * out)
+    if fused:
+        from . import fused as fz
+        return fz.fused_moe_forward(ctx, x, idx, gates, w13, w2, mode=mode)
+    if mode == "one_hop":
+        return ep_moe_forward(x, idx, gates, w13, w2, world, E, rpn=rpn)
+    return ta2a_moe_forward(x, idx, gates, w13, w2, world, E, rpn=rpn, groups_m=cfg.top_groups)
+
+
+class MoELayerRunner:
+    """Functional MoE layer ``(x, router_w, w13_shard, w2_shard) -> y`` used by the benchmarks
+    and the tests; owns the per-layer communication context (process groups or the symmetric
+    arena of the fused transport)."""
+
+    def __init__(self, cfg: TRouteConfig, hidden: int, d_expert: int, tokens: int, *, world: int,
+                 rank: int, rpn: int, mode: str, fused: bool, device):
+        if mode not in EP_MODES:
+            raise ValueError(f"unknown EP mode {mode!r}; expected one of {EP_MODES}")
+        self.cfg, self.world, self.rank, self.rpn = cfg, world, rank, rpn
+        self.mode, self.fused = mode, fused and world > 1
+        self.hidden, self.d_expert, self.tokens = hidden, d_expert, tokens
+        self.device = device
+        self.bias = torch.zeros(cfg.n_experts, device=device)
+        self.ctx = None
+        if world > 1 and mode == "two_hop" and not self.fused:
+            init_ta2a_groups(world, rpn)
+        if self.fused:
+            from . import fused as fz
+            self.ctx = fz.FusedEPContext(cfg, hidden, d_expert, tokens, world=world, rank=rank,
+                                         rpn=rpn, device=device)
+
+    def __call__(self, x, router_w, w13, w2):
+        idx, gates, _gidx, _load = _route(x, router_w, self.bias, self.cfg)
+        return routed_experts(x, idx, gates, w13, w2, self.cfg, mode=self.mode, world=self.world,
+                              rpn=self.rpn, fused=self.fused, ctx=self.ctx)
+
+    @torch.no_grad()
+    def time_dispatch_combine(self, x, steps: int, warmup: int) -> float:
+        """Dispatch + combine only (no expert compute): rows go out and come straight back.
+        Device-timed, max over ranks, microseconds per call."""
+        cfg = self.cfg
+        g = torch.Generator(device="cpu").manual_seed(7 + self.rank)
+        aff = torch.rand(x.shape[0], cfg.n_experts, generator=g).to(x.device)
+        idx, gates, _ = t_route(aff, self.bias, cfg, "full")
+        fn = self._dispatch_combine_fn(x, idx, gates)
+        if fn is None:
+            return float("nan")
+        for _ in range(warmup):
+            fn()
+        torch.cuda.synchronize()
+        if self.world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+        t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        t0.record()
+        for _ in range(steps):
+            fn()
+        t1.record()
+        torch.cuda.synchronize()
+        us = torch.tensor([t0.elapsed_time(t1) * 1e3 / steps], device=x.device)
+        if self.world > 1:
+            dist.all_reduce(us, op=dist.ReduceOp.MAX)
+        return us.item()
+
+    def _dispatch_combine_fn(self, x, idx, gates):
+        lib = torch.ops.terrace
+        E, cfg = self.cfg.n_experts, self.cfg
+        T, k = idx.shape
+        if self.mode == "local" or self.world == 1:
+            if not (ops.custom_ops_enabled() and x.dtype == torch.bfloat16):
+                return None
+            g32 = gates.float().contiguous()
+
+            def fn():
+                es, gs, cols, pos, s0, c0 = lib.moe_plan(idx, g32, E, 1)
+                xs = lib.moe_scatter_rows(x, pos, T * k)
+                return lib.moe_combine(xs, pos, es, gs, cfg.group_size)
+            return fn
+        if self.fused:
+            from . import fused as fz
+            return lambda: fz.fused_dispatch_combine(self.ctx, x, idx, gates, mode=self.mode)
+        identity_w13 = identity_w2 = None  # NCCL arm: time the exchange with the GEMMs skipped
+        from . import ep as _ep
+        from . import ta2a as _ta
+
+        def fn():
+            saved = _ep.swiglu_experts
+            try:
+                _ep.swiglu_experts = lambda rows, *_: rows
+                _ta.swiglu_experts = _ep.swiglu_experts
+                if self.mode == "one_hop":
+                    return ep_moe_forward(x, idx, gates, identity_w13, identity_w2, self.world, E,
+                                          rpn=self.rpn)
+                return ta2a_moe_forward(x, idx, gates, identity_w13, identity_w2, self.world, E,
+                                        rpn=self.rpn, groups_m=cfg.top_groups)
+            finally:
+                _ep.swiglu_experts = saved
+                _ta.swiglu_experts = saved
+        return fn
+
+
+class EPTerracedMoE(nn.Module):
+    """``TerracedMoE`` whose routed experts are sharded over the default process group."""
+
+    def __init__(self, hidden: int, d_expert: int, d_shared: int, cfg: TRouteConfig,
+                 n_shared: int = 1, bias_gamma: float = 1e-3, *, mode: str = "one_hop",
+                 rpn: int = 1, fused: bool = False, capacity_factor: float | None = None,
+                 tokens_hint: int | None = None):
+        super().__init__()
+        if mode not in EP_MODES:
+            raise ValueError(f"unknown EP mode {mode!r}; expected one of {EP_MODES}")
+        self.cfg, self.bias_gamma, self.mode, self.rpn, self.fused = cfg, bias_gamma, mode, rpn, fused
+        self.capacity_factor = capacity_factor
+        self.routing_mode = "full"
+        self.expert_backend = "native"
+        self.world = dist.get_world_size() if dist.is_initialized() else 1
+        self.rank = dist.get_rank() if dist.is_initialized() else 0
+        if cfg.n_experts % self.world:
+            raise ValueError(f"n_experts={cfg.n_experts} not divisible by world={self.world}")
+        epr = cfg.n_experts // self.world
+        self.hidden, self.d_expert, self.tokens_hint = hidden, d_expert, tokens_hint
+        self.router = Router(hidden, cfg)
+        self.shared = SwiGLU(hidden, n_shared * d_shared) if n_shared * d_shared > 0 else None
+        self.w13 = nn.Parameter(torch.empty(epr, hidden, 2 * d_expert))
+        self.w2 = nn.Parameter(torch.empty(epr, d_expert, hidden))
+        nn.init.normal_(self.w13, std=hidden ** -0.5)
+        nn.init.normal_(self.w2, std=d_expert ** -0.5)
+        self._ctx = None
+        if self.world > 1 and mode == "two_hop" and not fused:
+            init_ta2a_groups(self.world, rpn)
+
+    def _context(self, tokens: int, device):
+        if not self.fused or self.world == 1:
+            return None
+        if self._ctx is None or self._ctx.tokens < tokens:
+            from . import fused as fz
+            self._ctx = fz.FusedEPContext(self.cfg, self.hidden, self.d_expert, tokens,
+                                          world=self.world, rank=self.rank, rpn=self.rpn,
+                                          device=device)
+        return self._ctx
+
+    def forward(self, x: torch.Tensor):
+        lead = x.shape[:-1]
+        x = x.reshape(-1, x.shape[-1])
+        if self.routing_mode != "full":
+            raise ValueError("the expert-parallel layer routes with mode 'full' only")
+        idx, gates, gidx, load = _route(x, self.router.weight, self.router.bias, self.cfg)
+        gates_used = gates
+        if self.capacity_factor is not None:
+            all_load = load.clone()
+            prior = torch.zeros_like(load)
+            if self.world > 1:
+                gathered = [torch.zeros_like(load) for _ in range(self.world)]
+                dist.all_gather(gathered, load)
+                prior = sum(gathered[: self.rank], torch.zeros_like(load))
+                all_load = sum(gathered)
+            gates_used, _keep, _cap = apply_capacity(
+                idx, gates, self.cfg.n_experts, self.capacity_factor,
+                n_tokens_global=x.shape[0] * self.world, prior_counts=prior.long())
+        y = routed_experts(x, idx, gates_used, self.w13, self.w2, self.cfg, mode=self.mode,
+                           world=self.world, rpn=self.rpn, fused=self.fused,
+                           ctx=self._context(x.shape[0], x.device))
+        if self.shared is not None:
+            y = y + self.shared(x)
+        if self.training:
+            total = load.detach().clone()
+            if self.world > 1:
+                dist.all_reduce(total)
+            update_bias_(self.router.bias, total, self.bias_gamma)
+        stats = {"expert_load": load, "group_idx": gidx, "gates": gates, "expert_idx": idx}
+        return y.reshape(*lead, -1), stats

@@ -1,0 +1,287 @@
+"""GPU numerics: every CUDA kernel against a plain PyTorch fp32 reference of the same op."""
+import pytest
+import torch
+import torch.nn.functional as F
+
+pytestmark = pytest.mark.gpu
+
+DEV = "cuda"
+
+
+def _close(a, b, rtol=2e-2, atol=None):
+    a, b = a.float(), b.float()
+    scale = b.abs().max().item() + 1e-6
+    atol = atol if atol is not None else 1e-2 * scale
+    torch.testing.assert_close(a, b, rtol=rtol, atol=atol)
+
+
+def test_passthrough_bitwise(native_ops):
+    for dt in (torch.float32, torch.bfloat16, torch.float16):
+        for shape in ((7,), (33, 65), (4, 128, 96)):
+            x = torch.randn(*shape, device=DEV).to(dt)
+            y = native_ops.passthrough(x)
+            assert y.data_ptr() != x.data_ptr() and torch.equal(x, y)
+    assert native_ops.OP_CALLS.get("passthrough", 0) > 0
+
+
+@pytest.mark.parametrize("dt", [torch.float32, torch.bfloat16])
+def test_rmsnorm_fwd_bwd(native_ops, dt):
+    torch.manual_seed(0)
+    x = torch.randn(37, 5, 512, device=DEV).to(dt).requires_grad_(True)
+    w = (1 + 0.1 * torch.randn(512, device=DEV)).to(dt).requires_grad_(True)
+    y = native_ops.rmsnorm(x, w, 1e-5)
+    gy = torch.randn_like(y)
+    y.backward(gy)
+    xr = x.detach().float().requires_grad_(True)
+    wr = w.detach().float().requires_grad_(True)
+    yr = xr * torch.rsqrt(xr.pow(2).mean(-1, keepdim=True) + 1e-5) * wr
+    yr.backward(gy.float())
+    tol = 1e-5 if dt == torch.float32 else 2e-2
+    torch.testing.assert_close(y.float(), yr, rtol=tol, atol=tol)
+    torch.testing.assert_close(x.grad.float(), xr.grad, rtol=tol, atol=tol)
+    torch.testing.assert_close(w.grad.float(), wr.grad, rtol=tol, atol=tol * 10)
+
+
+K1_GEOMS = [(16, 2, 2, 8, 64), (64, 1, 2, 8, 32), (33, 3, 2, 4, 48), (128, 4, 4, 8, 16),
+            (7, 2, 8, 4, 96), (1, 1, 1, 1, 24), (256, 2, 2, 16, 8), (40, 5, 3, 4, 40),
+            (48, 7, 9, 7, 8), (2000, 4, 32, 4, 256)]
+
+
+@pytest.mark.parametrize("geom", K1_GEOMS)
+@pytest.mark.parametrize("dt", [torch.float32, torch.bfloat16, torch.float16])
+def test_k1_arrival_bitwise(native_ops, geom, dt):
+    R, q, epr, rpn, H = geom
+    g = torch.Generator().manual_seed(R * 31 + q)
+    slots = epr * rpn
+    rslot = torch.stack([torch.randperm(slots, generator=g)[:q].sort().values for _ in range(R)])
+    rx = torch.randn(R, H, generator=g).to(dt)
+    rgate = torch.rand(R, q, generator=g).to(dt)
+    ref = native_ops.k1_arrival_ref(rx, rslot, rgate, q, epr, rpn, 0)
+    got = torch.ops.terrace.k1_arrival(rx.to(DEV), rslot.to(DEV), rgate.to(DEV), q, epr, rpn, 0)
+    for a, b in zip(got, ref):
+        assert torch.equal(a.cpu(), b)
+
+
+def test_k1_arrival_empty(native_ops):
+    rx = torch.zeros(0, 16, device=DEV)
+    out = torch.ops.terrace.k1_arrival(rx, torch.zeros(0, 2, dtype=torch.long, device=DEV),
+                                       torch.zeros(0, 2, device=DEV), 2, 2, 4, 0)
+    assert out[0].shape == (0, 16) and out[4].tolist() == [0, 0, 0, 0]
+
+
+K2_GEOMS = [(4, 2, 8, 8, 4, 2), (32, 8, 64, 48, 4, 2), (32, 8, 96, 32, 8, 4), (32, 8, 128, 32, 8, 2),
+            (16, 8, 32, 5, 2, 2), (16, 4, 16, 12, 4, 1), (8, 4, 8, 1, 2, 2), (64, 8, 128, 33, 6, 3),
+            (8, 4, 256, 777, 8, 2)]
+
+
+def _quota_routing(T, E, n_nodes, k, M, g, sort_rows):
+    per = E // n_nodes
+    q = k // M
+    rows = []
+    for _ in range(T):
+        groups = torch.randperm(n_nodes, generator=g)[:M]
+        picks = torch.cat([grp * per + torch.randperm(per, generator=g)[:q] for grp in groups])
+        picks = picks[torch.randperm(k, generator=g)]
+        rows.append(picks.sort().values if sort_rows else picks)
+    return torch.stack(rows)
+
+
+@pytest.mark.parametrize("geom", K2_GEOMS)
+@pytest.mark.parametrize("sort_rows", [True, False])
+@pytest.mark.parametrize("dt", [torch.float32, torch.bfloat16])
+def test_k2_pack_bitwise(native_ops, geom, sort_rows, dt):
+    world, rpn, E, T, k, M = geom
+    g = torch.Generator().manual_seed(T * 7 + k)
+    idx = _quota_routing(T, E, world // rpn, k, M, g, sort_rows)
+    hidden = torch.randn(T, 40, generator=g).to(dt)
+    gates = torch.rand(T, k, generator=g).to(dt)
+    ref = native_ops.k2_pack_ref(hidden, idx, gates, world, E, rpn, M)
+    got = torch.ops.terrace.k2_pack(hidden.to(DEV), idx.to(DEV), gates.to(DEV), world, E, rpn, M)
+    for a, b in zip(got, ref):
+        assert torch.equal(a.cpu(), b)
+
+
+def test_route_select_matches_t_route(native_ops):
+    from terracemoe_simulator_b200.routing import TRouteConfig, t_route
+    torch.manual_seed(1)
+    for (E, ng, k, M, T) in [(64, 4, 6, 2, 1000), (64, 16, 4, 2, 513), (256, 2, 8, 2, 300),
+                             (16, 2, 4, 1, 77)]:
+        cfg = TRouteConfig(E, ng, k, M)
+        logits = torch.randn(T, E, device=DEV)
+        bias = 0.01 * torch.randn(E, device=DEV)
+        idx, gates, gidx, load = native_ops.route_from_logits(logits, bias, cfg)
+        ridx, rgates, rgidx = t_route(torch.sigmoid(logits), bias, cfg, "full")
+        same = (idx == ridx).all(dim=1)
+        assert same.float().mean() > 0.995
+        torch.testing.assert_close(gates[same], rgates[same], rtol=1e-4, atol=1e-5)
+        assert torch.equal(gidx[same], rgidx[same])
+        assert load.sum().item() == T * k
+
+
+def test_route_select_backward(native_ops):
+    from terracemoe_simulator_b200.routing import TRouteConfig, t_route
+    torch.manual_seed(2)
+    cfg = TRouteConfig(64, 4, 6, 2)
+    logits = torch.randn(200, 64, device=DEV, requires_grad=True)
+    bias = torch.zeros(64, device=DEV)
+    idx, gates, _, _ = native_ops.route_from_logits(logits, bias, cfg)
+    w = torch.randn_like(gates)
+    (gates * w).sum().backward()
+    l2 = logits.detach().clone().requires_grad_(True)
+    ridx, rgates, _ = t_route(torch.sigmoid(l2), bias, cfg, "full")
+    assert torch.equal(idx, ridx)
+    (rgates * w).sum().backward()
+    torch.testing.assert_close(logits.grad, l2.grad, rtol=1e-3, atol=1e-6)
+
+
+def _segs(counts):
+    c = torch.tensor(counts, dtype=torch.int32, device=DEV)
+    return (torch.cumsum(c, 0, dtype=torch.int32) - c), c
+
+
+GEMM_CASES = [
+    # counts, K, N
+    ([128], 64, 256),
+    ([300, 0, 77, 129], 256, 512),
+    ([5, 1000, 3], 192, 264),
+    ([257] * 8, 4096, 1408),
+]
+
+
+@pytest.mark.parametrize("counts,K,N", GEMM_CASES)
+def test_grouped_gemm_fwd(native_ops, counts, K, N):
+    torch.manual_seed(0)
+    G, rows = len(counts), sum(counts)
+    A = torch.randn(rows, K, device=DEV, dtype=torch.bfloat16)
+    B = (torch.randn(G, K, N, device=DEV) * K ** -0.5).bfloat16()
+    s, c = _segs(counts)
+    C, _ = torch.ops.terrace.grouped_gemm(A, B, s, c, 0, 0, False, 0)
+    ref = torch.empty(rows, N, device=DEV)
+    off = 0
+    for g, n in enumerate(counts):
+        ref[off:off + n] = A[off:off + n].float() @ B[g].float()
+        off += n
+    _close(C, ref)
+    assert native_ops.take_status() == 0
+
+
+@pytest.mark.parametrize("counts,K,N", GEMM_CASES)
+def test_grouped_gemm_dgrad(native_ops, counts, K, N):
+    torch.manual_seed(0)
+    G, rows = len(counts), sum(counts)
+    A = torch.randn(rows, K, device=DEV, dtype=torch.bfloat16)
+    B = (torch.randn(G, N, K, device=DEV) * K ** -0.5).bfloat16()
+    s, c = _segs(counts)
+    C, _ = torch.ops.terrace.grouped_gemm(A, B, s, c, 1, 0, False, 0)
+    ref = torch.empty(rows, N, device=DEV)
+    off = 0
+    for g, n in enumerate(counts):
+        ref[off:off + n] = A[off:off + n].float() @ B[g].float().t()
+        off += n
+    _close(C, ref)
+    assert native_ops.take_status() == 0
+
+
+@pytest.mark.parametrize("counts,M,N", [([64], 128, 256), ([300, 0, 77, 129], 256, 512),
+                                          ([5, 1000, 3], 192, 264), ([700] * 4, 1024, 1408)])
+def test_grouped_wgrad(native_ops, counts, M, N):
+    torch.manual_seed(0)
+    G, rows = len(counts), sum(counts)
+    X = torch.randn(rows, M, device=DEV, dtype=torch.bfloat16)
+    dY = torch.randn(rows, N, device=DEV, dtype=torch.bfloat16)
+    s, c = _segs(counts)
+    dW = torch.ops.terrace.grouped_wgrad(X, dY, s, c, 0)
+    ref = torch.zeros(G, M, N, device=DEV)
+    off = 0
+    for g, n in enumerate(counts):
+        ref[g] = X[off:off + n].float().t() @ dY[off:off + n].float()
+        off += n
+    _close(dW, ref)
+    assert native_ops.take_status() == 0
+
+
+@pytest.mark.parametrize("mode", [0, 1])
+def test_grouped_gemm_swiglu_epilogue(native_ops, mode):
+    torch.manual_seed(0)
+    counts, K, d = [200, 31, 0, 400], 512, 384
+    G, rows = len(counts), sum(counts)
+    A = torch.randn(rows, K, device=DEV, dtype=torch.bfloat16)
+    W = (torch.randn(G, K, 2 * d, device=DEV) * K ** -0.5).bfloat16()
+    B = W if mode == 0 else W.transpose(1, 2).contiguous()
+    s, c = _segs(counts)
+    act, pre = torch.ops.terrace.grouped_gemm(A, B, s, c, mode, 1, True, 0)
+    ref = torch.empty(rows, 2 * d, device=DEV)
+    off = 0
+    for g, n in enumerate(counts):
+        ref[off:off + n] = A[off:off + n].float() @ W[g].float()
+        off += n
+    _close(pre, ref)
+    gate, up = pre.float().chunk(2, dim=-1)
+    _close(act, F.silu(gate) * up, rtol=1e-2)
+    assert native_ops.take_status() == 0
+
+
+def test_linear_and_ffn_autograd(native_ops):
+    torch.manual_seed(0)
+    x = torch.randn(3, 100, 256, device=DEV, dtype=torch.bfloat16, requires_grad=True)
+    w = (torch.randn(384, 256, device=DEV) * 256 ** -0.5).bfloat16().requires_grad_(True)
+    y = native_ops.linear(x, w)
+    gy = torch.randn_like(y)
+    y.backward(gy)
+    xr, wr = x.detach().float().requires_grad_(True), w.detach().float().requires_grad_(True)
+    yr = xr @ wr.t()
+    yr.backward(gy.float())
+    _close(y, yr)
+    _close(x.grad, xr.grad)
+    _close(w.grad, wr.grad)
+
+    w13 = (torch.randn(2 * 512, 256, device=DEV) * 256 ** -0.5).bfloat16().requires_grad_(True)
+    w2 = (torch.randn(256, 512, device=DEV) * 512 ** -0.5).bfloat16().requires_grad_(True)
+    x2 = x.detach().clone().requires_grad_(True)
+    y = native_ops.swiglu_ffn(x2, w13, w2)
+    y.backward(gy[..., :256].contiguous())
+    xr = x.detach().float().requires_grad_(True)
+    w13r, w2r = w13.detach().float().requires_grad_(True), w2.detach().float().requires_grad_(True)
+    a, b = (xr @ w13r.t()).chunk(2, -1)
+    yr = (F.silu(a) * b) @ w2r.t()
+    yr.backward(gy[..., :256].float())
+    _close(y, yr, rtol=5e-2)
+    _close(x2.grad, xr.grad, rtol=5e-2)
+    _close(w13.grad, w13r.grad, rtol=5e-2)
+    _close(w2.grad, w2r.grad, rtol=5e-2)
+    assert native_ops.take_status() == 0
+
+
+def test_moe_experts_local_fwd_bwd(native_ops):
+    from terracemoe_simulator_b200.routing import TRouteConfig, t_route
+    torch.manual_seed(0)
+    T, H, d, E, ng, k, M = 777, 256, 128, 16, 4, 4, 2
+    cfg = TRouteConfig(E, ng, k, M)
+    x = torch.randn(T, H, device=DEV, dtype=torch.bfloat16, requires_grad=True)
+    w13 = (torch.randn(E, H, 2 * d, device=DEV) * H ** -0.5).bfloat16().requires_grad_(True)
+    w2 = (torch.randn(E, d, H, device=DEV) * d ** -0.5).bfloat16().requires_grad_(True)
+    aff = torch.sigmoid(torch.randn(T, E, device=DEV))
+    idx, gates, _ = t_route(aff, torch.zeros(E, device=DEV), cfg)
+    gates = gates.detach().requires_grad_(True)
+    y = native_ops.moe_experts_local(x, idx, gates, w13, w2, cfg.group_size)
+    gy = torch.randn_like(y)
+    y.backward(gy)
+
+    xr = x.detach().float().requires_grad_(True)
+    w13r, w2r = w13.detach().float().requires_grad_(True), w2.detach().float().requires_grad_(True)
+    gr = gates.detach().clone().requires_grad_(True)
+    yr = torch.zeros(T, H, device=DEV)
+    for e in range(E):
+        tok, col = (idx == e).nonzero(as_tuple=True)
+        a, b = (xr[tok] @ w13r[e]).chunk(2, -1)
+        yr = yr.index_add(0, tok, gr[tok, col, None] * ((F.silu(a) * b) @ w2r[e]))
+    yr.backward(gy.float())
+    _close(y, yr, rtol=5e-2)
+    _close(x.grad, xr.grad, rtol=5e-2)
+    _close(gates.grad, gr.grad, rtol=5e-2)
+    _close(w13.grad, w13r.grad, rtol=5e-2)
+    _close(w2.grad, w2r.grad, rtol=5e-2)
+    assert native_ops.take_status() == 0
+    # determinism: same inputs, same bits
+    y2 = native_ops.moe_experts_local(x, idx, gates, w13, w2, cfg.group_size)
+    assert torch.equal(y, y2)
