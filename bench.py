@@ -206,7 +206,7 @@ def run_ours(args, rank, world, local):
         native.LAUNCHES[0] = 0
         ms, clk = timed(make_step(path, False), args.steps, args.warmup, world,
                         ClockSampler(local) if rank == 0 else None)
-        launches = native.LAUNCHES[0] * args.steps // (args.steps + args.warmup)
+        launches = native.LAUNCHES[0] // (args.steps + args.warmup)       # per step
         dc = runners[path].time_dispatch_combine(x_dev.detach(), args.steps, args.warmup)
         results[path] = {"ms_per_step": ms / args.steps, "launches": launches,
                          "dispatch_combine_us": dc, "status": native.take_status(local)}

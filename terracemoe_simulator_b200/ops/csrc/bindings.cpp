@@ -193,6 +193,12 @@ std::tuple<Tensor, Tensor> rmsnorm_bwd(const Tensor& x, const Tensor& w, const T
                                        const Tensor& rstd) {
   CHECK_CUDA_CONTIG(x);
   CHECK_CUDA_CONTIG(dy);
+  CHECK_CUDA_CONTIG(w);
+  CHECK_CUDA_CONTIG(rstd);
+  TORCH_CHECK(dy.sizes() == x.sizes() && dy.scalar_type() == x.scalar_type() &&
+                  w.scalar_type() == x.scalar_type() && w.numel() == x.size(-1) &&
+                  rstd.scalar_type() == at::kFloat && rstd.numel() * x.size(-1) == x.numel(),
+              "rmsnorm_bwd: inconsistent shapes or dtypes");
   c10::cuda::CUDAGuard guard(x.device());
   const int64_t dim = x.size(-1), rows = x.numel() / dim;
   Tensor dx = at::empty_like(x);
@@ -232,6 +238,13 @@ Tup5 route_select(const Tensor& logits, const Tensor& bias, int64_t n_groups, in
 Tensor route_select_bwd(const Tensor& dgates, const Tensor& gates, const Tensor& aff,
                         const Tensor& idx, int64_t E) {
   CHECK_CUDA_CONTIG(dgates);
+  CHECK_CUDA_CONTIG(gates);
+  CHECK_CUDA_CONTIG(aff);
+  CHECK_CUDA_CONTIG(idx);
+  TORCH_CHECK(idx.dim() == 2 && idx.scalar_type() == at::kLong && gates.sizes() == idx.sizes() &&
+                  aff.sizes() == idx.sizes() && dgates.sizes() == idx.sizes() &&
+                  gates.scalar_type() == at::kFloat && aff.scalar_type() == at::kFloat,
+              "route_select_bwd: inconsistent shapes or dtypes");
   c10::cuda::CUDAGuard guard(dgates.device());
   const int64_t T = idx.size(0), k = idx.size(1);
   Tensor dlogits = at::zeros({T, E}, gates.options());
@@ -274,6 +287,8 @@ Tensor moe_scatter_rows(const Tensor& x, const Tensor& pos, int64_t rows_out) {
   CHECK_CUDA_CONTIG(x);
   CHECK_CUDA_CONTIG(pos);
   TORCH_CHECK(x.scalar_type() == at::kBFloat16 && x.dim() == 2, "moe_scatter_rows: bf16 [T, H]");
+  TORCH_CHECK(pos.dim() == 2 && pos.scalar_type() == at::kInt && pos.size(0) == x.size(0),
+              "moe_scatter_rows: pos must be int32 [T, k]");
   c10::cuda::CUDAGuard guard(x.device());
   const int64_t T = pos.size(0), k = pos.size(1);
   Tensor xs = at::empty({rows_out, x.size(1)}, x.options());
@@ -286,7 +301,15 @@ Tensor moe_scatter_rows(const Tensor& x, const Tensor& pos, int64_t rows_out) {
 Tensor moe_combine(const Tensor& out, const Tensor& pos, const Tensor& es,
                    const c10::optional<Tensor>& gs, int64_t group_size) {
   CHECK_CUDA_CONTIG(out);
-  TORCH_CHECK(out.scalar_type() == at::kBFloat16, "moe_combine: bf16 rows");
+  CHECK_CUDA_CONTIG(pos);
+  CHECK_CUDA_CONTIG(es);
+  TORCH_CHECK(out.scalar_type() == at::kBFloat16 && out.dim() == 2, "moe_combine: bf16 rows");
+  TORCH_CHECK(pos.dim() == 2 && pos.scalar_type() == at::kInt && es.sizes() == pos.sizes() &&
+                  es.scalar_type() == at::kInt,
+              "moe_combine: pos and es must be int32 [T, k]");
+  TORCH_CHECK(!gs.has_value() || (gs->sizes() == pos.sizes() && gs->scalar_type() == at::kFloat &&
+                                  gs->is_contiguous()),
+              "moe_combine: gs must be fp32 [T, k]");
   c10::cuda::CUDAGuard guard(out.device());
   const int64_t T = pos.size(0), k = pos.size(1);
   Tensor y = at::empty({T, out.size(1)}, out.options());
@@ -301,6 +324,15 @@ std::tuple<Tensor, Tensor> moe_combine_bwd(const Tensor& dy, const Tensor& out, 
                                            const c10::optional<Tensor>& gs, bool need_dgs) {
   CHECK_CUDA_CONTIG(dy);
   CHECK_CUDA_CONTIG(out);
+  CHECK_CUDA_CONTIG(pos);
+  TORCH_CHECK(dy.scalar_type() == at::kBFloat16 && out.scalar_type() == at::kBFloat16 &&
+                  dy.dim() == 2 && out.dim() == 2 && dy.size(1) == out.size(1),
+              "moe_combine_bwd: bf16 dy [T, H] and out [rows, H]");
+  TORCH_CHECK(pos.dim() == 2 && pos.scalar_type() == at::kInt && pos.size(0) == dy.size(0),
+              "moe_combine_bwd: pos must be int32 [T, k]");
+  TORCH_CHECK(!gs.has_value() || (gs->sizes() == pos.sizes() && gs->scalar_type() == at::kFloat &&
+                                  gs->is_contiguous()),
+              "moe_combine_bwd: gs must be fp32 [T, k]");
   c10::cuda::CUDAGuard guard(dy.device());
   const int64_t T = pos.size(0), k = pos.size(1);
   Tensor dout = at::zeros_like(out);
@@ -316,6 +348,11 @@ std::tuple<Tensor, Tensor> moe_combine_bwd(const Tensor& dy, const Tensor& out, 
 Tensor swiglu_bwd(const Tensor& h13, const Tensor& dact) {
   CHECK_CUDA_CONTIG(h13);
   CHECK_CUDA_CONTIG(dact);
+  TORCH_CHECK(h13.dim() == 2 && dact.dim() == 2 && h13.size(0) == dact.size(0) &&
+                  h13.size(1) == 2 * dact.size(1),
+              "swiglu_bwd: h13 must be [rows, 2d] and dact [rows, d]");
+  TORCH_CHECK(h13.scalar_type() == at::kBFloat16 && dact.scalar_type() == at::kBFloat16,
+              "swiglu_bwd: bf16 tensors");
   c10::cuda::CUDAGuard guard(h13.device());
   Tensor dh = at::empty_like(h13);
   check_rc(tb200_swiglu_bwd(h13.data_ptr(), dact.data_ptr(), dh.data_ptr(), dact.size(0),
@@ -365,7 +402,11 @@ Tensor grouped_wgrad(const Tensor& X, const Tensor& dY, const Tensor& seg_start,
   CHECK_CUDA_CONTIG(dY);
   TORCH_CHECK(X.scalar_type() == at::kBFloat16 && dY.scalar_type() == at::kBFloat16,
               "grouped_wgrad: bf16 operands");
-  TORCH_CHECK(X.size(0) == dY.size(0), "grouped_wgrad: row mismatch");
+  TORCH_CHECK(X.dim() == 2 && dY.dim() == 2 && X.size(0) == dY.size(0), "grouped_wgrad: row mismatch");
+  TORCH_CHECK(seg_start.scalar_type() == at::kInt && seg_count.scalar_type() == at::kInt &&
+                  seg_start.numel() == seg_count.numel() && seg_start.is_cuda() &&
+                  seg_count.is_cuda(),
+              "grouped_wgrad: int32 CUDA segment tables");
   c10::cuda::CUDAGuard guard(X.device());
   const int64_t G = seg_start.numel();
   Tensor dW = at::empty({G, X.size(1), dY.size(1)}, X.options());

@@ -144,6 +144,23 @@ constexpr int ROUTE_MAX_E = 512;
 constexpr int ROUTE_MAX_G = 64;
 constexpr int ROUTE_WARPS = 4;
 
+// Advance (prev, prev_i) to the next element of v[0..n) in the order "value descending, index
+// ascending" and add its value to `sum`.  Call with prev = +inf, prev_i = -1 to start.
+__device__ __forceinline__ void next_best(const float* v, int n, float& prev, int& prev_i,
+                                          float& sum) {
+  float best = -INFINITY;
+  int bi = -1;
+  for (int j = 0; j < n; ++j) {
+    const float x = v[j];
+    const bool after_prev = x < prev || (x == prev && j > prev_i);
+    if (after_prev && (bi < 0 || x > best)) { best = x; bi = j; }
+  }
+  if (bi < 0) { bi = prev_i < 0 ? 0 : prev_i; best = v[bi]; }   // only with NaNs in v
+  prev = best;
+  prev_i = bi;
+  sum += best;
+}
+
 __global__ void route_select_kernel(const float* __restrict__ logits,
                                     const float* __restrict__ bias, long long* __restrict__ idx,
                                     float* __restrict__ gates, long long* __restrict__ group_idx,
@@ -171,31 +188,19 @@ __global__ void route_select_kernel(const float* __restrict__ logits,
   const int width = pool < g ? pool : g;
   for (int gi = lane; gi < n_groups; gi += 32) {
     const float* sg = sel + gi * g;
-    float sum = 0.f;
-    unsigned long long taken = 0ull;      // g <= 64 handled with a bitmask
-    for (int r = 0; r < width; ++r) {
-      float best = -INFINITY;
-      int bi = 0;
-      for (int j = 0; j < g; ++j) {
-        if (!((taken >> j) & 1ull) && sg[j] > best) { best = sg[j]; bi = j; }
-      }
-      taken |= 1ull << bi;
-      sum += best;
-    }
+    float sum = 0.f, prev = INFINITY;
+    int prev_i = -1;
+    for (int r = 0; r < width; ++r) next_best(sg, g, prev, prev_i, sum);
     s_gsc[warp][gi] = sum / width;
   }
   __syncwarp();
   // top-M groups, descending score, lowest index wins ties
   if (lane == 0) {
-    unsigned long long taken = 0ull;
+    float prev = INFINITY, dummy = 0.f;
+    int prev_i = -1;
     for (int m = 0; m < top_groups; ++m) {
-      float best = -INFINITY;
-      int bi = 0;
-      for (int gi = 0; gi < n_groups; ++gi) {
-        if (!((taken >> gi) & 1ull) && s_gsc[warp][gi] > best) { best = s_gsc[warp][gi]; bi = gi; }
-      }
-      taken |= 1ull << bi;
-      s_grp[warp][m] = bi;
+      next_best(s_gsc[warp], n_groups, prev, prev_i, dummy);
+      s_grp[warp][m] = prev_i;
     }
   }
   __syncwarp();
@@ -203,15 +208,11 @@ __global__ void route_select_kernel(const float* __restrict__ logits,
   for (int m = lane; m < top_groups; m += 32) {
     const int gi = s_grp[warp][m];
     const float* sg = sel + gi * g;
-    unsigned long long taken = 0ull;
+    float prev = INFINITY, dummy = 0.f;
+    int prev_i = -1;
     for (int r = 0; r < q; ++r) {
-      float best = -INFINITY;
-      int bi = 0;
-      for (int j = 0; j < g; ++j) {
-        if (!((taken >> j) & 1ull) && sg[j] > best) { best = sg[j]; bi = j; }
-      }
-      taken |= 1ull << bi;
-      s_pick[warp][m * q + r] = gi * g + bi;
+      next_best(sg, g, prev, prev_i, dummy);
+      s_pick[warp][m * q + r] = gi * g + prev_i;
     }
   }
   __syncwarp();
@@ -724,8 +725,8 @@ extern "C" int tb200_route_select(const float* logits, const float* bias, long l
                                   float* affinity_sel, int T, int E, int n_groups, int top_k,
                                   int top_groups, int pool, cudaStream_t stream) {
   if (T == 0) return TB200_OK;
-  if (E > ROUTE_MAX_E || n_groups > ROUTE_MAX_G || E % n_groups || E / n_groups > 64 ||
-      top_k > 32 || top_k % top_groups || top_groups > n_groups || top_k > 64)
+  if (E > ROUTE_MAX_E || n_groups > ROUTE_MAX_G || E % n_groups || top_k > 32 ||
+      top_k % top_groups || top_groups > n_groups || top_k / top_groups > E / n_groups)
     return TB200_ERR_SIZE;
   route_select_kernel<<<(T + ROUTE_WARPS - 1) / ROUTE_WARPS, ROUTE_WARPS * 32, 0, stream>>>(
       logits, bias, idx, gates, group_idx, load, affinity_sel, T, E, n_groups, top_k, top_groups,

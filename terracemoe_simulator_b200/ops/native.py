@@ -144,7 +144,7 @@ class _SwiGLUFFN(torch.autograd.Function):
     def forward(ctx, x, w13, w2):
         x2 = x.reshape(-1, x.shape[-1]).contiguous()
         s, c = _one_segment(x2.shape[0], x.device)
-        need = torch.is_grad_enabled()
+        need = any(ctx.needs_input_grad)
         act, h13 = _lib().grouped_gemm(x2, w13.contiguous().unsqueeze(0), s, c, 1, 1, need, 0)
         y, _ = _lib().grouped_gemm(act, w2.contiguous().unsqueeze(0), s, c, 1, 0, False, 0)
         ctx.save_for_backward(x2, w13, w2, h13, act, s, c)
@@ -212,7 +212,7 @@ def grouped_mm_native(x, w, counts):
 # ---------------------------------------------------------------------------------------------
 def router_supported(cfg, hidden) -> bool:
     g = cfg.group_size
-    return (hidden.is_cuda and cfg.n_experts <= 512 and cfg.n_groups <= 64 and g <= 64
+    return (hidden.is_cuda and cfg.n_experts <= 512 and cfg.n_groups <= 64 and g <= 512
             and cfg.top_k <= 32)
 
 
@@ -270,7 +270,7 @@ class _MoELocal(torch.autograd.Function):
         es, gs, cols, pos, seg_start, seg_count = lib.moe_plan(
             expert_idx.contiguous(), gates.detach().float().contiguous(), E, 1)
         xs = lib.moe_scatter_rows(xc, pos, T * k)
-        need = torch.is_grad_enabled()
+        need = any(ctx.needs_input_grad)
         act, h13 = lib.grouped_gemm(xs, w13.contiguous(), seg_start, seg_count, 0, 1, need, 0)
         out, _ = lib.grouped_gemm(act, w2.contiguous(), seg_start, seg_count, 0, 0, False, 0)
         y = lib.moe_combine(out, pos, es, gs, group_size)
