@@ -391,7 +391,8 @@ std::tuple<Tensor, Tensor> grouped_gemm(const Tensor& A, const Tensor& B, const 
     check_rc(tb200_grouped_gemm(A.data_ptr(), B.data_ptr(), C.data_ptr(),
                                 C2.defined() ? C2.data_ptr() : nullptr, seg_start.data_ptr<int>(),
                                 seg_count.data_ptr<int>(), G, rows, N, K, N, 2 * N, b_rows, b_cols,
-                                mode, epilogue, status_ptr(A), max_ctas, cur_stream()),
+                                mode, epilogue, status_ptr(A), max_ctas, nullptr, 0, 0,
+                                cur_stream()),
              "grouped_gemm");
   return {C, C2.defined() ? C2 : at::empty({0}, A.options())};
 }

@@ -50,6 +50,9 @@ struct GemmParams {
   __nv_bfloat16* C;
   __nv_bfloat16* C2;      // SwiGLU: optional [rows, 2d] pre-activations (may be null)
   int* status;
+  const int* wait_flags;  // optional: arrival flags that must reach wait_epoch before A is read
+  int wait_n;
+  int wait_epoch;
 };
 
 struct __align__(8) PipeBarriers {
@@ -158,6 +161,17 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
       int e = 0;
       uint32_t it = 0;
       bool ok = true;
+      if (p.wait_flags != nullptr) {
+        // rows of A are stored by peer GPUs: wait for their arrival flags, then order the
+        // generic-proxy writes before this thread's TMA (async-proxy) reads
+        for (int i = 0; i < p.wait_n && ok; ++i) {
+          if (!wait_flag_ge(p.wait_flags + i, p.wait_epoch)) {
+            raise_abort(ctl, p.status, ST_TIMEOUT_FLAG);
+            ok = false;
+          }
+        }
+        fence_proxy_async_all();
+      }
       for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
         locate_tile(ctl, p.n_groups, t, e);
         const int local = t - ctl->tile_start[e];
@@ -502,6 +516,7 @@ extern "C" int tb200_grouped_gemm(const void* A, const void* B, void* C, void* C
                                   const int* seg_start, const int* seg_count, int n_groups,
                                   long long a_rows, int N, int K, int ldc, int ldc2, int b_rows,
                                   int b_cols, int mode, int epilogue, int* status, int max_ctas,
+                                  const int* wait_flags, int wait_n, int wait_epoch,
                                   cudaStream_t stream) {
   if (n_groups <= 0 || n_groups > MAX_GROUPS) return TB200_ERR_ARG;
   if ((K % 8) || (N % 8) || (ldc % 8) || (b_cols % 8)) return TB200_ERR_ARG;
@@ -540,6 +555,9 @@ extern "C" int tb200_grouped_gemm(const void* A, const void* B, void* C, void* C
   p.C = static_cast<__nv_bfloat16*>(C);
   p.C2 = static_cast<__nv_bfloat16*>(C2);
   p.status = status;
+  p.wait_flags = wait_flags;
+  p.wait_n = wait_n;
+  p.wait_epoch = wait_epoch;
   if (mode == MODE_DGRAD && epilogue == EPI_SWIGLU)
     return launch_gemm<MODE_DGRAD, EPI_SWIGLU>(ta, tb, p, max_ctas, stream);
   if (mode == MODE_DGRAD) return launch_gemm<MODE_DGRAD, EPI_PLAIN>(ta, tb, p, max_ctas, stream);
@@ -580,5 +598,8 @@ extern "C" int tb200_grouped_wgrad(const void* X, const void* dY, void* dW, cons
   p.C = static_cast<__nv_bfloat16*>(dW);
   p.C2 = nullptr;
   p.status = status;
+  p.wait_flags = nullptr;
+  p.wait_n = 0;
+  p.wait_epoch = 0;
   return launch_gemm<MODE_WGRAD, EPI_PLAIN>(ta, tb, p, max_ctas, stream);
 }

@@ -27,7 +27,8 @@ enum {
 int tb200_grouped_gemm(const void* A, const void* B, void* C, void* C2, const int* seg_start,
                        const int* seg_count, int n_groups, long long a_rows, int N, int K, int ldc,
                        int ldc2, int b_rows, int b_cols, int mode, int epilogue, int* status,
-                       int max_ctas, cudaStream_t stream);
+                       int max_ctas, const int* wait_flags, int wait_n, int wait_epoch,
+                       cudaStream_t stream);
 // dW[g][M, N] = X[rows of g, M]^T * dY[rows of g, N]; groups with no rows get zeros.
 int tb200_grouped_wgrad(const void* X, const void* dY, void* dW, const int* seg_start,
                         const int* seg_count, int n_groups, long long rows, int M, int N,
@@ -58,6 +59,9 @@ int tb200_route_select_bwd(const float* dgates, const float* gates, const float*
 //   seg_start/seg_count [E]
 // `scratch` needs tb200_plan_scratch_ints(T, k, E) ints.
 size_t tb200_plan_scratch_ints(int T, int k, int E);
+// first pass only (sorted picks, local ranks, per-chunk histogram [TB200_PLAN_CHUNKS][E])
+int tb200_plan_pass1(const long long* expert_idx, const float* gates, int* es, float* gs, int* cols,
+                     int* rank_local, int* chunk_hist, int T, int k, int E, cudaStream_t stream);
 int tb200_moe_plan(const long long* expert_idx, const float* gates, int* es, float* gs, int* cols,
                    int* pos, int* seg_start, int* seg_count, int* scratch, int T, int k, int E,
                    int seg_align, cudaStream_t stream);
@@ -88,6 +92,41 @@ int tb200_k2_pack(const void* hidden, const long long* expert_idx, const void* g
                   long long* node_counts, int* scratch, int T, int k, int groups_m, int slots,
                   int n_nodes, int row_bytes, int gate_bytes, int* status, cudaStream_t stream);
 size_t tb200_k2_scratch_ints(int T, int k, int groups_m, int n_nodes);
+
+// ---- symm.cu -----------------------------------------------------------------------------------
+struct Tb200Arena;
+int tb200_ep_plan(const struct Tb200Arena* a, int* chunk_hist, int* chunka_hist, int* my_base,
+                  int* seg_start, int* seg_count, int* rows_a, int epoch, int* status,
+                  cudaStream_t stream);
+int tb200_ep_push(const struct Tb200Arena* a, const void* x, const int* es, const int* rank_local,
+                  const int* chunk_base, const int* my_base, int* pos_out, const float* gs,
+                  float* dgs, long long off_dst, long long off_dot, int T, int flag_kind, int epoch,
+                  int* done_counter, int* status, cudaStream_t stream);
+int tb200_signal(const struct Tb200Arena* a, int kind, int first, int n, int stride, int idx,
+                 int epoch, int wait_kind, int wait_first, int wait_n, int* status,
+                 cudaStream_t stream);
+int tb200_ep_pull_combine(const struct Tb200Arena* a, const int* pos, const int* es,
+                          const float* gs, void* y, long long off_src, int T, int group_size,
+                          int wait_kind, int epoch, int* status, cudaStream_t stream);
+int tb200_hopa_rank(const struct Tb200Arena* a, const int* es, int* ranka_local, int* chunka_hist,
+                    int T, cudaStream_t stream);
+int tb200_hopa_push(const struct Tb200Arena* a, const void* x, const int* es, const float* gs,
+                    const int* rank_local, const int* chunk_base, const int* my_base,
+                    const int* ranka_local, const int* chunka_base, int* pos_out, int* rowa,
+                    long long off_rows, int with_header, int T, int flag_kind, int epoch,
+                    int* done_counter, int* status, cudaStream_t stream);
+int tb200_arrival_push(const struct Tb200Arena* a, const int* rows_a, long long off_rows,
+                       long long off_dst, long long off_dot, int scale_gate, int want_dgate,
+                       int wait_kind, int data_kind, int dg_kind, int epoch, int* done_counter,
+                       int* status, cudaStream_t stream);
+int tb200_arrival_combine(const struct Tb200Arena* a, const int* rows_a, long long off_src,
+                          long long off_red, int use_gate, int wait_kind, int red_kind, int epoch,
+                          int* done_counter, int* status, cudaStream_t stream);
+int tb200_origin_combine(const struct Tb200Arena* a, const int* es, const int* rowa, void* y,
+                         long long off_red, int T, int wait_kind, int epoch, int* status,
+                         cudaStream_t stream);
+int tb200_origin_pull_dgate(const struct Tb200Arena* a, const int* es, const int* rowa, float* dgs,
+                            int T, int wait_kind, int epoch, int* status, cudaStream_t stream);
 
 #ifdef __cplusplus
 }

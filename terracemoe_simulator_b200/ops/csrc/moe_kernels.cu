@@ -11,6 +11,7 @@
 // terrace/ops/__init__.py:255-300 (K1), terrace/ops/k2_ref.py:70-134 (K2).
 #include "launch.h"
 #include "ptx_sm100.cuh"
+#include "symm_layout.h"
 
 #include <cuda_bf16.h>
 
@@ -262,7 +263,7 @@ __global__ void route_select_bwd_kernel(const float* __restrict__ dgates,
 //   pass 3: pos = base + local rank
 // ---------------------------------------------------------------------------------------------
 constexpr int PLAN_MAX_K = 32;
-constexpr int PLAN_CHUNKS = 128;
+constexpr int PLAN_CHUNKS = TB200_PLAN_CHUNKS;
 
 __global__ void plan_pass1_kernel(const long long* __restrict__ expert_idx,
                                   const float* __restrict__ gates, int* __restrict__ es,
@@ -746,6 +747,15 @@ extern "C" int tb200_route_select_bwd(const float* dgates, const float* gates,
 
 extern "C" size_t tb200_plan_scratch_ints(int T, int k, int E) {
   return static_cast<size_t>(T) * k + static_cast<size_t>(PLAN_CHUNKS) * E;
+}
+
+extern "C" int tb200_plan_pass1(const long long* expert_idx, const float* gates, int* es,
+                                float* gs, int* cols, int* rank_local, int* chunk_hist, int T,
+                                int k, int E, cudaStream_t stream) {
+  if (k > PLAN_MAX_K || E > 8192) return TB200_ERR_SIZE;
+  plan_pass1_kernel<<<PLAN_CHUNKS, 32, E * sizeof(int), stream>>>(expert_idx, gates, es, gs, cols,
+                                                                rank_local, chunk_hist, T, k, E);
+  return LAUNCH_OK();
 }
 
 extern "C" int tb200_moe_plan(const long long* expert_idx, const float* gates, int* es, float* gs,

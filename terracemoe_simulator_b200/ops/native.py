@@ -27,7 +27,10 @@ class _Counted:
     _PER_CALL = {"rmsnorm_fwd": 1, "rmsnorm_bwd": 1, "route_select": 1, "route_select_bwd": 1,
                  "moe_plan": 3, "moe_scatter_rows": 1, "moe_combine": 1, "moe_combine_bwd": 1,
                  "swiglu_bwd": 1, "grouped_gemm": 1, "grouped_wgrad": 1, "passthrough": 1,
-                 "k1_arrival": 3, "k2_pack": 3}
+                 "k1_arrival": 3, "k2_pack": 3, "ep_plan_pass1": 1, "ep_plan": 1, "ep_push": 1,
+                 "ep_signal": 1, "ep_pull_combine": 1, "hopa_rank": 1, "hopa_push": 1,
+                 "arrival_push": 1, "arrival_combine": 1, "origin_combine": 1,
+                 "origin_pull_dgate": 1, "grouped_gemm_ex": 1}
 
     def __getattr__(self, name):
         fn = getattr(torch.ops.terrace, name)
@@ -57,7 +60,8 @@ def take_status(device=None) -> int:
     problem: 1/2/3 pipeline wait timeouts, 4 flag timeout, 5 bad row index, 6 counts timeout."""
     if device is None:
         device = torch.cuda.current_device()
-    return int(_lib().take_status(int(device)))
+    code = int(_lib().take_status(int(device)))
+    return code or int(torch.ops.terrace.symm_take_status(int(device)))
 
 
 # ---------------------------------------------------------------------------------------------

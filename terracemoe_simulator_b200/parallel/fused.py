@@ -1,0 +1,270 @@
+"""Fused expert parallelism over peer memory: the product path for dispatch / combine.
+
+``FusedEPContext`` owns one symmetric arena per MoE layer (see ``ops/csrc/symm_layout.h``): every
+rank ``cudaMalloc``s the same layout, exports it with CUDA IPC, and maps all peers.  The kernels
+(``ops/csrc/symm.cu``) then move token rows with plain peer stores/loads and synchronise with
+epoch flags; NCCL is used only to exchange the IPC handles at start-up.
+
+One step of ``fused_moe_forward`` (no host synchronisation anywhere):
+
+  one-hop   plan -> push rows into the owners' expert-sorted input -> [GEMM1 waits on the
+            arrival flags of its A operand] SwiGLU GEMMs -> signal -> gate-weighted pull combine
+  two-hop   plan -> Hop A push (one row per (token, group) + header) to the representative ->
+            representative forwards every (row, pick) to the owner (Hop B) -> GEMMs -> the
+            representative pulls, applies the gates and reduces per row -> origin pulls and adds
+            its M group rows
+
+The backward pass runs the mirrored pipeline (combine-backward is dispatch shaped and also
+produces the gate gradients; dispatch-backward is combine shaped).  Both paths place rows at
+positions the ORIGIN computes from the all-gathered expert histogram, so the expert GEMMs see
+identical inputs and the two paths agree bit for bit.
+
+Reference counterparts: ``terrace/ep_dist.py:82-122`` and ``terrace/ta2a_fwd.py:445-670`` (which
+issue 4 and 9 collectives with 1-3 host syncs per forward).
+"""
+from __future__ import annotations
+
+import torch
+import torch.distributed as dist
+
+from ..routing import TRouteConfig
+
+# arena sections (must match section_offset() in symm_bindings.cpp)
+XIN, YOUT, DOUT, DXS, HA_ROWS, RED, HB_ROWS, DRED = range(8)
+# flag kinds (must match Tb200FlagKind)
+(FK_COUNTS, FK_HOPA, FK_DATA, FK_OUT, FK_RED, FK_B_HOPA, FK_B_DATA, FK_B_DG, FK_B_OUT,
+ FK_B_RED) = range(10)
+FK_NUM = 10
+MAX_WORLD = 16
+
+LIVE = {"one_hop_fwd": 0, "two_hop_fwd": 0, "one_hop_bwd": 0, "two_hop_bwd": 0, "echo": 0}
+
+
+def _lib():
+    from ..ops.native import _lib as counted
+    return counted()
+
+
+def _align(n: int, a: int = 256) -> int:
+    return (n + a - 1) // a * a
+
+
+class FusedEPContext:
+    def __init__(self, cfg: TRouteConfig, hidden: int, d_expert: int, tokens: int, *, world: int,
+                 rank: int, rpn: int, device, group=None, row_capacity_factor: float = 2.0):
+        if world > MAX_WORLD:
+            raise ValueError(f"world={world} exceeds the arena limit {MAX_WORLD}")
+        if cfg.n_experts % world or world % rpn:
+            raise ValueError("n_experts % world and world % rpn must be zero")
+        self.cfg, self.hidden, self.d_expert, self.tokens = cfg, hidden, d_expert, tokens
+        self.world, self.rank, self.rpn, self.device = world, rank, rpn, torch.device(device)
+        self.group = group
+        self.E = cfg.n_experts
+        self.epr = self.E // world
+        self.n_nodes = world // rpn
+        self.k, self.M, self.q = cfg.top_k, cfg.top_groups, cfg.per_group_k
+        self.two_hop_ok = (self.n_nodes >= 2 and cfg.n_groups == self.n_nodes)
+        self.cap_rows = _align(min(world * tokens * self.k,
+                                   int(row_capacity_factor * tokens * self.k)), 128)
+        self.epoch = 0
+        H = hidden
+        sizes = [
+            world * self.E * 4,                      # counts_all
+            FK_NUM * MAX_WORLD * 4,                  # flags
+            self.cap_rows * H * 2,                   # xin
+            self.cap_rows * H * 2,                   # yout
+            self.cap_rows * H * 2,                   # dout
+            self.cap_rows * H * 2,                   # dxs
+        ]
+        arows = self.n_nodes * tokens if self.two_hop_ok else 1
+        sizes += [arows * H * 2, arows * 3 * self.q * 4, arows * H * 2, arows * H * 2,
+                  arows * H * 2, arows * self.q * 4]
+        self.offsets, off = [], 0
+        for s in sizes:
+            self.offsets.append(off)
+            off += _align(s)
+        self.nbytes = off
+        lib = torch.ops.terrace
+        dev_index = self.device.index if self.device.index is not None else torch.cuda.current_device()
+        self.buf = lib.symm_alloc(self.nbytes, dev_index)
+        handle = lib.symm_ipc_handle(self.buf)
+        handles = [None] * world
+        dist.all_gather_object(handles, handle.numpy().tobytes(), group=group)
+        self.peer_ptrs = []
+        self._opened = []
+        for r in range(world):
+            if r == rank:
+                self.peer_ptrs.append(self.buf.data_ptr())
+            else:
+                h = torch.frombuffer(bytearray(handles[r]), dtype=torch.uint8)
+                p = lib.symm_ipc_open(h, dev_index)
+                self._opened.append(p)
+                self.peer_ptrs.append(p)
+        geom = [world, rank, self.E, self.epr, rpn, self.n_nodes, tokens, self.k, self.M, self.q,
+                H, self.cap_rows]
+        self.arena = lib.symm_make_arena(self.peer_ptrs, self.offsets, geom)
+        self.done = torch.zeros(8, dtype=torch.int32, device=self.device)
+        self._dev_index = dev_index
+        dist.barrier(group=group)
+
+    # views of this rank's own sections
+    def section(self, sel: int) -> torch.Tensor:
+        off = self.offsets[2 + sel] if sel < 4 else self.offsets[{4: 6, 5: 8, 6: 9, 7: 10}[sel]]
+        rows = self.cap_rows if sel < 4 else self.n_nodes * self.tokens
+        n = rows * self.hidden * 2
+        return self.buf[off: off + n].view(torch.bfloat16).view(rows, self.hidden)
+
+    def next_epoch(self) -> int:
+        self.epoch += 1
+        return self.epoch
+
+    def owner_wait_range(self, mode: str):
+        """Which arrival flags an expert owner waits for: every rank (one-hop) or the ranks of
+        its own group (two-hop, where the group's representatives forward the rows)."""
+        if mode == "one_hop":
+            return 0, self.world
+        return (self.rank // self.rpn) * self.rpn, self.rpn
+
+    def close(self):
+        lib = torch.ops.terrace
+        for p in self._opened:
+            lib.symm_ipc_close(p, self._dev_index)
+        self._opened = []
+
+    def take_status(self) -> int:
+        return int(torch.ops.terrace.symm_take_status(self._dev_index))
+
+
+def _plan(ctx: FusedEPContext, idx, gates, mode: str, ep: int):
+    lib = _lib()
+    es, gs, cols, rank_local, chunk_hist = lib.ep_plan_pass1(
+        idx.contiguous(), gates.detach().float().contiguous(), ctx.E)
+    ranka = chunka = None
+    if mode == "two_hop":
+        ranka, chunka = lib.hopa_rank(ctx.arena, es)
+    my_base, seg_start, seg_count, rows_a = lib.ep_plan(ctx.arena, chunk_hist, chunka, ep)
+    return dict(es=es, gs=gs, cols=cols, rank_local=rank_local, chunk_hist=chunk_hist,
+                ranka=ranka, chunka=chunka, my_base=my_base, seg_start=seg_start,
+                seg_count=seg_count, rows_a=rows_a)
+
+
+def _dispatch(ctx, p, x, mode: str, ep: int):
+    """Forward dispatch: rows of ``x`` land in the owners' ``xin`` sections."""
+    lib = _lib()
+    if mode == "one_hop":
+        pos, _ = lib.ep_push(ctx.arena, x, p["es"], p["rank_local"], p["chunk_hist"],
+                             p["my_base"], None, False, XIN, XIN, FK_DATA, ep, ctx.done[0:1])
+        p["pos"], p["rowa"] = pos, None
+    else:
+        pos, rowa = lib.hopa_push(ctx.arena, x, p["es"], p["gs"], p["rank_local"],
+                                  p["chunk_hist"], p["my_base"], p["ranka"], p["chunka"], None,
+                                  HA_ROWS, True, FK_HOPA, ep, ctx.done[0:1])
+        lib.arrival_push(ctx.arena, p["rows_a"], HA_ROWS, XIN, XIN, False, False, FK_HOPA,
+                         FK_DATA, -1, ep, ctx.done[1:2])
+        p["pos"], p["rowa"] = pos, rowa
+
+
+def _signal_out(ctx, mode: str, kind: int, ep: int, like, wait_kind: int = -1):
+    lib = _lib()
+    first, n = ctx.owner_wait_range(mode)
+    lib.ep_signal(ctx.arena, kind, first, n, 1, ctx.rank, ep, wait_kind, first, n, like)
+
+
+def _combine(ctx, p, mode: str, ep: int, *, src: int, use_gate: bool, backward: bool):
+    lib = _lib()
+    out_kind = FK_B_OUT if backward else FK_OUT
+    if mode == "one_hop":
+        return lib.ep_pull_combine(ctx.arena, p["pos"], p["es"], p["gs"] if use_gate else None,
+                                   src, ctx.cfg.group_size, out_kind, ep)
+    red_sel, red_kind = (DRED, FK_B_RED) if backward else (RED, FK_RED)
+    lib.arrival_combine(ctx.arena, p["rows_a"], src, red_sel, use_gate, out_kind, red_kind, ep,
+                        ctx.done[2:3])
+    return lib.origin_combine(ctx.arena, p["es"], p["rowa"], red_sel, red_kind, ep)
+
+
+class _FusedMoE(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, gates, w13, w2, idx, fctx: FusedEPContext, mode: str):
+        lib = _lib()
+        ep = fctx.next_epoch()
+        xc = x.contiguous()
+        p = _plan(fctx, idx, gates, mode, ep)
+        _dispatch(fctx, p, xc, mode, ep)
+        first, n = fctx.owner_wait_range(mode)
+        d = w2.shape[1]
+        xin, yout = fctx.section(XIN), fctx.section(YOUT)
+        act = torch.empty(fctx.cap_rows, d, dtype=torch.bfloat16, device=x.device)
+        need = any(ctx.needs_input_grad)
+        h13 = (torch.empty(fctx.cap_rows, 2 * d, dtype=torch.bfloat16, device=x.device)
+               if need else None)
+        lib.grouped_gemm_ex(xin, w13.contiguous(), act, h13, p["seg_start"], p["seg_count"], 0, 1,
+                            fctx.arena, FK_DATA, first, n, ep)
+        lib.grouped_gemm_ex(act, w2.contiguous(), yout, None, p["seg_start"], p["seg_count"], 0,
+                            0, None, 0, 0, 0, ep)
+        _signal_out(fctx, mode, FK_OUT, ep, xc)
+        y = _combine(fctx, p, mode, ep, src=YOUT, use_gate=True, backward=False)
+        ctx.fctx, ctx.mode, ctx.ep, ctx.plan = fctx, mode, ep, p
+        ctx.save_for_backward(w13, w2, act, h13 if h13 is not None else act)
+        ctx.gate_dtype = gates.dtype
+        LIVE[f"{mode}_fwd"] += 1
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        lib = _lib()
+        fctx, mode, ep, p = ctx.fctx, ctx.mode, ctx.ep, ctx.plan
+        w13, w2, act, h13 = ctx.saved_tensors
+        dyc = dy.contiguous()
+        first, n = fctx.owner_wait_range(mode)
+        if mode == "one_hop":
+            _, dgs = lib.ep_push(fctx.arena, dyc, p["es"], p["rank_local"], p["chunk_hist"],
+                                 p["my_base"], p["gs"], True, DOUT, YOUT, FK_B_DATA, ep,
+                                 fctx.done[0:1])
+        else:
+            lib.hopa_push(fctx.arena, dyc, p["es"], p["gs"], p["rank_local"], p["chunk_hist"],
+                          p["my_base"], p["ranka"], p["chunka"], p["rowa"], HB_ROWS, False,
+                          FK_B_HOPA, ep, fctx.done[0:1])
+            lib.arrival_push(fctx.arena, p["rows_a"], HB_ROWS, DOUT, YOUT, True, True, FK_B_HOPA,
+                             FK_B_DATA, FK_B_DG, ep, fctx.done[1:2])
+        xin, dout, dxs = fctx.section(XIN), fctx.section(DOUT), fctx.section(DXS)
+        d = w2.shape[1]
+        dact = torch.empty(fctx.cap_rows, d, dtype=torch.bfloat16, device=dy.device)
+        lib.grouped_gemm_ex(dout, w2.contiguous(), dact, None, p["seg_start"], p["seg_count"], 1,
+                            0, fctx.arena, FK_B_DATA, first, n, ep)
+        dw2 = lib.grouped_wgrad(act, dout, p["seg_start"], p["seg_count"], 0)
+        dh13 = lib.swiglu_bwd(h13, dact)
+        dw13 = lib.grouped_wgrad(xin, dh13, p["seg_start"], p["seg_count"], 0)
+        lib.grouped_gemm_ex(dh13, w13.contiguous(), dxs, None, p["seg_start"], p["seg_count"], 1,
+                            0, None, 0, 0, 0, ep)
+        _signal_out(fctx, mode, FK_B_OUT, ep, dyc)
+        dx = _combine(fctx, p, mode, ep, src=DXS, use_gate=False, backward=True)
+        if mode == "two_hop":
+            dgs = lib.origin_pull_dgate(fctx.arena, p["es"], p["rowa"], FK_B_DG, ep)
+        dgates = torch.zeros_like(dgs).scatter_(1, p["cols"].long(), dgs).to(ctx.gate_dtype)
+        LIVE[f"{mode}_bwd"] += 1
+        return dx, dgates, dw13, dw2, None, None, None
+
+
+def fused_moe_forward(fctx: FusedEPContext, x, idx, gates, w13, w2, *, mode: str):
+    """Routed-expert output for this rank's tokens over the fused transport."""
+    if mode == "two_hop" and not fctx.two_hop_ok:
+        mode = "one_hop"          # fewer than two groups (or groups != routing groups)
+    if x.shape[0] > fctx.tokens:
+        raise ValueError(f"{x.shape[0]} tokens exceed the context capacity {fctx.tokens}")
+    if x.dtype != torch.bfloat16 or w13.dtype != torch.bfloat16:
+        raise TypeError("the fused transport moves bf16 rows")
+    return _FusedMoE.apply(x, gates, w13, w2, idx, fctx, mode)
+
+
+@torch.no_grad()
+def fused_dispatch_combine(fctx: FusedEPContext, x, idx, gates, *, mode: str):
+    """Dispatch immediately followed by combine (rows echo back unchanged, gate-weighted): the
+    communication-only measurement."""
+    if mode == "two_hop" and not fctx.two_hop_ok:
+        mode = "one_hop"
+    ep = fctx.next_epoch()
+    p = _plan(fctx, idx, gates, mode, ep)
+    _dispatch(fctx, p, x.contiguous(), mode, ep)
+    _signal_out(fctx, mode, FK_OUT, ep, x, wait_kind=FK_DATA)
+    LIVE["echo"] += 1
+    return _combine(fctx, p, mode, ep, src=XIN, use_gate=True, backward=False)

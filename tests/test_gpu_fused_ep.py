@@ -1,0 +1,107 @@
+"""Fused peer-memory expert parallelism on real GPUs: world 1 against the local kernels
+(bitwise), world 2 one-hop against two-hop (bitwise) and against the NCCL arm (tolerance)."""
+import os
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def _worker(rank, world, port, queue, M):
+    import torch.distributed as dist
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    os.environ["NCCL_NVLS_ENABLE"] = "0"
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world,
+                            device_id=torch.device("cuda", rank))
+    try:
+        from terracemoe_simulator_b200 import ops
+        from terracemoe_simulator_b200.parallel import fused as fz
+        from terracemoe_simulator_b200.parallel.ep import ep_moe_forward
+        from terracemoe_simulator_b200.routing import TRouteConfig, t_route
+        assert ops.custom_ops_enabled()
+        dev = torch.device("cuda", rank)
+        E, k, H, d, T = 16, 4, 256, 128, 1000 + 37 * rank
+        n_groups = max(world, 2) if world > 1 else 2
+        cfg = TRouteConfig(E, n_groups, k, M)
+        g = torch.Generator().manual_seed(0)
+        w13_all = (torch.randn(E, H, 2 * d, generator=g) * H ** -0.5).bfloat16()
+        w2_all = (torch.randn(E, d, H, generator=g) * d ** -0.5).bfloat16()
+        epr = E // world
+        gx = torch.Generator().manual_seed(10 + rank)
+        x0 = torch.randn(T, H, generator=gx).bfloat16().to(dev)
+        aff = torch.rand(T, E, generator=gx).to(dev)
+        gy = torch.randn(T, H, generator=gx).bfloat16().to(dev)
+        idx, gates0, _ = t_route(aff, torch.zeros(E, device=dev), cfg)
+        fctx = fz.FusedEPContext(cfg, H, d, 1200, world=world, rank=rank, rpn=1, device=dev)
+        res = {}
+        modes = ["one_hop", "two_hop"] if world > 1 else ["one_hop"]
+        for mode in modes + ["ref"]:
+            x = x0.clone().requires_grad_(True)
+            gates = gates0.clone().requires_grad_(True)
+            a = w13_all[rank * epr:(rank + 1) * epr].to(dev).requires_grad_(True)
+            b = w2_all[rank * epr:(rank + 1) * epr].to(dev).requires_grad_(True)
+            if mode == "ref":
+                if world == 1:
+                    y = ops.moe_experts_local(x, idx, gates, a, b, cfg.group_size)
+                else:
+                    ops_state = ops._STATE
+                    y = ep_moe_forward(x, idx, gates, a, b, world, E, rpn=1)
+            else:
+                y = fz.fused_moe_forward(fctx, x, idx, gates, a, b, mode=mode)
+            y.backward(gy)
+            torch.cuda.synchronize()
+            res[mode] = [t.detach().float().cpu() for t in (y, x.grad, gates.grad, a.grad, b.grad)]
+        echo = fz.fused_dispatch_combine(fctx, x0, idx, gates0, mode=modes[-1])
+        torch.cuda.synchronize()
+        status = fctx.take_status() or ops.take_status(rank)
+        queue.put((rank, res, echo.float().cpu(), x0.float().cpu(), status,
+                   dict(fz.LIVE)))
+        dist.barrier()
+    finally:
+        dist.destroy_process_group()
+
+
+def _run(world, M, port):
+    import torch.multiprocessing as mp
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    procs = [ctx.Process(target=_worker, args=(r, world, port, q, M)) for r in range(world)]
+    for p in procs:
+        p.start()
+    out = [q.get(timeout=600) for _ in range(world)]
+    for p in procs:
+        p.join(timeout=120)
+    return sorted(out, key=lambda t: t[0])
+
+
+def _close(a, b, tol=5e-2):
+    scale = b.abs().max().item() + 1e-6
+    torch.testing.assert_close(a, b, rtol=tol, atol=tol * scale)
+
+
+def test_fused_world1_equals_local_kernels(native_ops):
+    (rank, res, echo, x0, status, live), = _run(1, 1, 29701)
+    assert status == 0
+    assert live["one_hop_fwd"] == 1 and live["one_hop_bwd"] == 1
+    for a, b in zip(res["one_hop"], res["ref"]):
+        assert torch.equal(a, b)
+    # echo: every token gets sum_j gate_j * x = x (gates sum to one) up to bf16 rounding
+    _close(echo, x0, 2e-2)
+
+
+@pytest.mark.parametrize("M", [2, 1])
+def test_fused_world2_one_hop_two_hop(native_ops, M):
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    out = _run(2, M, 29703 + M)
+    for rank, res, echo, x0, status, live in out:
+        assert status == 0
+        assert live["two_hop_fwd"] == 1 and live["two_hop_bwd"] == 1
+        for a, b in zip(res["one_hop"], res["two_hop"]):
+            assert torch.equal(a, b), "one-hop and two-hop fused paths must agree bit for bit"
+        for a, b in zip(res["one_hop"], res["ref"]):
+            _close(a, b)
+        _close(echo, x0, 2e-2)
