@@ -48,6 +48,7 @@ __device__ __forceinline__ bool block_done_is_last(int* counter) {
   __syncthreads();
   if (threadIdx.x == 0) {
     const int prev = atomicAdd(counter, 1);
+    __threadfence_system();           // acquire side: order the other blocks' stores before ours
     s_last = (prev == static_cast<int>(gridDim.x) - 1);
     if (s_last) *counter = 0;
   }

@@ -47,7 +47,6 @@ def _worker(rank, world, port, queue, M):
                 if world == 1:
                     y = ops.moe_experts_local(x, idx, gates, a, b, cfg.group_size)
                 else:
-                    ops_state = ops._STATE
                     y = ep_moe_forward(x, idx, gates, a, b, world, E, rpn=1)
             else:
                 y = fz.fused_moe_forward(fctx, x, idx, gates, a, b, mode=mode)
@@ -86,8 +85,11 @@ def test_fused_world1_equals_local_kernels(native_ops):
     (rank, res, echo, x0, status, live), = _run(1, 1, 29701)
     assert status == 0
     assert live["one_hop_fwd"] == 1 and live["one_hop_bwd"] == 1
-    for a, b in zip(res["one_hop"], res["ref"]):
-        assert torch.equal(a, b)
+    for i, (a, b) in enumerate(zip(res["one_hop"], res["ref"])):
+        if i == 2:      # gate gradients: same dot products, different lane partition
+            _close(a, b, 1e-2)
+        else:
+            assert torch.equal(a, b)
     # echo: every token gets sum_j gate_j * x = x (gates sum to one) up to bf16 rounding
     _close(echo, x0, 2e-2)
 
