@@ -116,14 +116,14 @@ def timed(fn, steps: int, warmup: int, world: int, sampler: ClockSampler | None)
     """W warm-up steps, then exactly K steps between CUDA events; returns max-over-ranks ms."""
     import torch
     import torch.distributed as dist
+    if sampler:
+        sampler.start()          # already polling while the warm-up loads the GPU
     for _ in range(warmup):
         fn()
     torch.cuda.synchronize()
     if world > 1:
         dist.barrier()
     torch.cuda.synchronize()
-    if sampler:
-        sampler.start()
     t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     t0.record()
     for _ in range(steps):

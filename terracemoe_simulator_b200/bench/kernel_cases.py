@@ -1,0 +1,124 @@
+"""Small single-kernel workloads for profiling (``ncu``) and for quick roofline numbers.
+
+    python -m terracemoe_simulator_b200.bench.kernel_cases <case> [--iters N] [--full]
+
+Every case allocates a few hundred MB at most (inputs larger than the 126 MB L2, so DRAM
+figures are meaningful), launches its kernel ``--iters`` times after one warm-up and prints the
+CUDA-event time with the achieved fraction of the measured peaks (``MEASURED_PEAKS.json`` at
+the repository root when present).  ``--full`` switches to the shapes of the single-MoE-layer
+benchmark (24576 rows, d_model 4096, 64 experts of hidden 1408).
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import sys
+
+import torch
+
+CASES = ("gemm_fwd", "gemm_swiglu", "gemm_dgrad", "gemm_wgrad", "rmsnorm", "route", "scatter",
+         "combine", "swiglu_bwd")
+
+
+def _peaks():
+    root = os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+    try:
+        with open(os.path.join(root, "MEASURED_PEAKS.json")) as f:
+            p = json.load(f)
+        return p["hbm_gbs"], p["bf16_tflops"], "of measured"
+    except (OSError, KeyError):
+        return 6650.0, 1590.0, "of fallback"
+
+
+def _time(fn, iters):
+    fn()
+    torch.cuda.synchronize()
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a.record()
+    for _ in range(iters):
+        fn()
+    b.record()
+    torch.cuda.synchronize()
+    return a.elapsed_time(b) / iters
+
+
+def main(argv=None) -> int:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("case", choices=CASES)
+    ap.add_argument("--iters", type=int, default=3)
+    ap.add_argument("--full", action="store_true")
+    args = ap.parse_args(argv)
+    from terracemoe_simulator_b200 import ops
+    if not ops.custom_ops_enabled():
+        raise SystemExit("native library not loaded")
+    lib = torch.ops.terrace
+    dev = "cuda"
+    torch.manual_seed(0)
+    if args.full:
+        E, rows, H, d, T, k = 64, 24576, 4096, 1408, 4096, 6
+    else:
+        E, rows, H, d, T, k = 8, 8192, 4096, 1408, 2048, 4
+    cnt = torch.full((E,), rows // E, dtype=torch.int32, device=dev)
+    st = torch.cumsum(cnt, 0, dtype=torch.int32) - cnt
+    bf = torch.bfloat16
+    hbm, tf, tag = _peaks()
+    flops = bytes_ = 0
+    if args.case in ("gemm_fwd", "gemm_swiglu"):
+        X = torch.randn(rows, H, device=dev, dtype=bf)
+        W = torch.randn(E, H, 2 * d, device=dev, dtype=bf) * H ** -0.5
+        epi = 1 if args.case == "gemm_swiglu" else 0
+        fn = lambda: lib.grouped_gemm(X, W, st, cnt, 0, epi, epi == 1, 0)
+        flops = 2 * rows * H * 2 * d
+    elif args.case == "gemm_dgrad":
+        dY = torch.randn(rows, 2 * d, device=dev, dtype=bf)
+        W = torch.randn(E, H, 2 * d, device=dev, dtype=bf) * H ** -0.5
+        fn = lambda: lib.grouped_gemm(dY, W, st, cnt, 1, 0, False, 0)
+        flops = 2 * rows * H * 2 * d
+    elif args.case == "gemm_wgrad":
+        X = torch.randn(rows, H, device=dev, dtype=bf)
+        dY = torch.randn(rows, 2 * d, device=dev, dtype=bf)
+        fn = lambda: lib.grouped_wgrad(X, dY, st, cnt, 0)
+        flops = 2 * rows * H * 2 * d
+    elif args.case == "rmsnorm":
+        x = torch.randn(rows * 2, H, device=dev, dtype=bf)
+        w = torch.ones(H, device=dev, dtype=bf)
+        fn = lambda: lib.rmsnorm_fwd(x, w, 1e-5)
+        bytes_ = 2 * x.numel() * 2
+    elif args.case == "route":
+        logits = torch.randn(T * 8, 64, device=dev)
+        bias = torch.zeros(64, device=dev)
+        fn = lambda: lib.route_select(logits, bias, 4, 6, 2, 2)
+        bytes_ = logits.numel() * 4
+    elif args.case in ("scatter", "combine"):
+        x = torch.randn(T, H, device=dev, dtype=bf)
+        idx = torch.stack([torch.randperm(E, device=dev)[:k] for _ in range(T)])
+        es, gs, cols, pos, s0, c0 = lib.moe_plan(idx, torch.rand(T, k, device=dev), E, 1)
+        xs = lib.moe_scatter_rows(x, pos, T * k)
+        if args.case == "scatter":
+            fn = lambda: lib.moe_scatter_rows(x, pos, T * k)
+            bytes_ = (T + T * k) * H * 2
+        else:
+            fn = lambda: lib.moe_combine(xs, pos, es, gs, E)
+            bytes_ = (T + T * k) * H * 2
+    else:
+        h13 = torch.randn(rows, 2 * d, device=dev, dtype=bf)
+        dact = torch.randn(rows, d, device=dev, dtype=bf)
+        fn = lambda: lib.swiglu_bwd(h13, dact)
+        bytes_ = rows * d * 2 * 5
+    ms = _time(fn, args.iters)
+    line = {"case": args.case, "full": args.full, "ms": round(ms, 4)}
+    if flops:
+        line["tflops"] = round(flops / ms / 1e9, 1)
+        line["frac_of_bf16_peak"] = round(flops / ms / 1e9 / tf, 3)
+    if bytes_:
+        line["gbs"] = round(bytes_ / ms / 1e6, 1)
+        line["frac_of_hbm_peak"] = round(bytes_ / ms / 1e6 / hbm, 3)
+    line["peaks"] = tag
+    line["status"] = ops.take_status()
+    print(json.dumps(line))
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -169,7 +169,7 @@ def _k1_grad_rgate(g_gate: torch.Tensor, rslot: torch.Tensor, epr: int, rpn: int
 
 
 def _k1_forward(rx, rslot, rgate, quota, epr, rpn, my_local):
-    if custom_ops_enabled() and rx.is_cuda:
+    if custom_ops_enabled() and rx.is_cuda and rgate.dtype == rx.dtype:
         _count("k1_arrival")
         return _ns().k1_arrival(rx, rslot, rgate, quota, epr, rpn, my_local)
     return k1_arrival_ref(rx, rslot, rgate, quota, epr, rpn, my_local)

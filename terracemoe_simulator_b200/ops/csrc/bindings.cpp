@@ -335,7 +335,7 @@ std::tuple<Tensor, Tensor> moe_combine_bwd(const Tensor& dy, const Tensor& out, 
               "moe_combine_bwd: gs must be fp32 [T, k]");
   c10::cuda::CUDAGuard guard(dy.device());
   const int64_t T = pos.size(0), k = pos.size(1);
-  Tensor dout = at::zeros_like(out);
+  Tensor dout = at::empty_like(out);      // every row of a valid pick is written
   Tensor dgs = need_dgs ? at::empty({T, k}, dy.options().dtype(at::kFloat)) : Tensor();
   check_rc(tb200_moe_combine_bwd(dy.data_ptr(), out.data_ptr(), pos.data_ptr<int>(),
                                  gs.has_value() ? gs->data_ptr<float>() : nullptr, dout.data_ptr(),

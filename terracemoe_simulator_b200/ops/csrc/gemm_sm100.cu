@@ -90,6 +90,26 @@ __device__ __forceinline__ uint32_t pack_bf16(float a, float b) {
 
 __device__ __forceinline__ float silu_f(float x) { return x / (1.0f + __expf(-x)); }
 
+// 32 fp32 accumulators of one row -> 32 bf16 at dst (16-byte stores), columns >= n_limit skipped
+__device__ __forceinline__ void store_row32(__nv_bfloat16* dst, const uint32_t (&r)[32], int n0,
+                                            int n_limit, bool zero) {
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    if (n0 + j * 8 < n_limit) {
+      uint4 v;
+      if (zero) {
+        v = make_uint4(0, 0, 0, 0);
+      } else {
+        v.x = pack_bf16(__uint_as_float(r[j * 8 + 0]), __uint_as_float(r[j * 8 + 1]));
+        v.y = pack_bf16(__uint_as_float(r[j * 8 + 2]), __uint_as_float(r[j * 8 + 3]));
+        v.z = pack_bf16(__uint_as_float(r[j * 8 + 4]), __uint_as_float(r[j * 8 + 5]));
+        v.w = pack_bf16(__uint_as_float(r[j * 8 + 6]), __uint_as_float(r[j * 8 + 7]));
+      }
+      *reinterpret_cast<uint4*>(dst + j * 8) = v;
+    }
+  }
+}
+
 // Locate the group of global tile index t (tile_start is a prefix array); `e` is a cursor that
 // only moves forward because every role visits tiles in increasing order.
 __device__ __forceinline__ void locate_tile(const SharedCtl* ctl, int n_groups, int t, int& e) {
@@ -322,27 +342,16 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
         const bool empty_group = cnt == 0;     // no MMA ran: the accumulator is undefined
         __nv_bfloat16* crow = p.C + (static_cast<size_t>(e) * p.M + m) * p.ldc;
 #pragma unroll 1
-        for (int c = 0; c < BN / 32; ++c) {
-          uint32_t r[32];
-          tmem_ld_32x32(taddr + c * 32, r);
+        for (int c = 0; c < BN / 32; c += 2) {
+          // two TMEM loads in flight before the wait: their latencies overlap
+          uint32_t r0[32], r1[32];
+          tmem_ld_32x32(taddr + c * 32, r0);
+          tmem_ld_32x32(taddr + (c + 1) * 32, r1);
           tmem_ld_wait();
           const int n0 = nt * BN + c * 32;
           if (m < p.M) {
-#pragma unroll
-            for (int j = 0; j < 4; ++j) {
-              if (n0 + j * 8 < p.N) {
-                uint4 v;
-                if (empty_group) {
-                  v = make_uint4(0, 0, 0, 0);
-                } else {
-                  v.x = pack_bf16(__uint_as_float(r[j * 8 + 0]), __uint_as_float(r[j * 8 + 1]));
-                  v.y = pack_bf16(__uint_as_float(r[j * 8 + 2]), __uint_as_float(r[j * 8 + 3]));
-                  v.z = pack_bf16(__uint_as_float(r[j * 8 + 4]), __uint_as_float(r[j * 8 + 5]));
-                  v.w = pack_bf16(__uint_as_float(r[j * 8 + 6]), __uint_as_float(r[j * 8 + 7]));
-                }
-                *reinterpret_cast<uint4*>(crow + n0 + j * 8) = v;
-              }
-            }
+            store_row32(crow + n0, r0, n0, p.N, empty_group);
+            store_row32(crow + n0 + 32, r1, n0 + 32, p.N, empty_group);
           }
         }
       } else if (EPI == EPI_SWIGLU) {
@@ -396,23 +405,15 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
         const bool live = row < cnt;
         __nv_bfloat16* crow = p.C + static_cast<size_t>(seg0 + row) * p.ldc;
 #pragma unroll 1
-        for (int c = 0; c < BN / 32; ++c) {
-          uint32_t r[32];
-          tmem_ld_32x32(taddr + c * 32, r);
+        for (int c = 0; c < BN / 32; c += 2) {
+          uint32_t r0[32], r1[32];
+          tmem_ld_32x32(taddr + c * 32, r0);
+          tmem_ld_32x32(taddr + (c + 1) * 32, r1);
           tmem_ld_wait();
           const int n0 = nt * BN + c * 32;
           if (live) {
-#pragma unroll
-            for (int j = 0; j < 4; ++j) {
-              if (n0 + j * 8 < p.N) {
-                uint4 v;
-                v.x = pack_bf16(__uint_as_float(r[j * 8 + 0]), __uint_as_float(r[j * 8 + 1]));
-                v.y = pack_bf16(__uint_as_float(r[j * 8 + 2]), __uint_as_float(r[j * 8 + 3]));
-                v.z = pack_bf16(__uint_as_float(r[j * 8 + 4]), __uint_as_float(r[j * 8 + 5]));
-                v.w = pack_bf16(__uint_as_float(r[j * 8 + 6]), __uint_as_float(r[j * 8 + 7]));
-                *reinterpret_cast<uint4*>(crow + n0 + j * 8) = v;
-              }
-            }
+            store_row32(crow + n0, r0, n0, p.N, false);
+            store_row32(crow + n0 + 32, r1, n0 + 32, p.N, false);
           }
         }
       }

@@ -82,7 +82,42 @@ __global__ void rmsnorm_fwd_kernel(const T* __restrict__ x, const T* __restrict_
   const long long row = static_cast<long long>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5);
   if (row >= rows) return;
   const T* xr = x + row * dim;
+  T* yr = y + row * dim;
   float ss = 0.f;
+  if (sizeof(T) == 2 && dim % 8 == 0) {
+    // 16-byte path: 8 bf16 per lane per step
+    const uint4* x4 = reinterpret_cast<const uint4*>(xr);
+    for (int i = lane; i < dim / 8; i += 32) {
+      const uint4 v = x4[i];
+      const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float2 f = __bfloat1622float2(h[j]);
+        ss += f.x * f.x + f.y * f.y;
+      }
+    }
+    ss = warp_sum(ss);
+    const float r = rsqrtf(ss / dim + eps);
+    if (lane == 0 && rstd != nullptr) rstd[row] = r;
+    const uint4* w4 = reinterpret_cast<const uint4*>(w);
+    uint4* y4 = reinterpret_cast<uint4*>(yr);
+    for (int i = lane; i < dim / 8; i += 32) {
+      const uint4 v = x4[i], g = w4[i];
+      const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v);
+      const __nv_bfloat162* gh = reinterpret_cast<const __nv_bfloat162*>(&g);
+      uint4 o;
+      __nv_bfloat162* oh = reinterpret_cast<__nv_bfloat162*>(&o);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float2 f = __bfloat1622float2(h[j]), gw = __bfloat1622float2(gh[j]);
+        // same rounding points as the eager expression x * rsqrt(.) * w in bf16
+        const float2 n = __bfloat1622float2(__floats2bfloat162_rn(f.x * r, f.y * r));
+        oh[j] = __floats2bfloat162_rn(n.x * gw.x, n.y * gw.y);
+      }
+      y4[i] = o;
+    }
+    return;
+  }
   for (int i = lane; i < dim; i += 32) {
     const float v = to_f(xr[i]);
     ss += v * v;
@@ -90,7 +125,6 @@ __global__ void rmsnorm_fwd_kernel(const T* __restrict__ x, const T* __restrict_
   ss = warp_sum(ss);
   const float r = rsqrtf(ss / dim + eps);
   if (lane == 0 && rstd != nullptr) rstd[row] = r;
-  T* yr = y + row * dim;
   for (int i = lane; i < dim; i += 32) {
     // same rounding points as the eager expression x * rsqrt(.) * w in the tensor dtype
     const T xn = from_f<T>(to_f(xr[i]) * r);
@@ -324,19 +358,42 @@ __global__ void plan_pass1_kernel(const long long* __restrict__ expert_idx,
 }
 
 // prior[E] (may be null): rows of lower-ranked sources that precede ours inside every expert
+// Exclusive prefix over the `n_chunks` (multiple of 32) rows of hist[chunk][stride] for column
+// `col`, done by one warp; returns the column total (valid in every lane).
+__device__ __forceinline__ int warp_chunk_prefix(int* hist, int n_chunks, int stride, int col,
+                                                 int lane) {
+  const int per = n_chunks / 32;
+  int local[8];
+  int sum = 0;
+  for (int i = 0; i < per; ++i) {
+    local[i] = hist[static_cast<size_t>(lane * per + i) * stride + col];
+    sum += local[i];
+  }
+  int incl = sum;
+#pragma unroll
+  for (int o = 1; o < 32; o <<= 1) {
+    const int v = __shfl_up_sync(0xffffffffu, incl, o);
+    if (lane >= o) incl += v;
+  }
+  int run = incl - sum;
+  for (int i = 0; i < per; ++i) {
+    hist[static_cast<size_t>(lane * per + i) * stride + col] = run;
+    run += local[i];
+  }
+  return __shfl_sync(0xffffffffu, incl, 31);
+}
+
 __global__ void plan_pass2_kernel(int* __restrict__ chunk_hist, int* __restrict__ seg_start,
                                   int* __restrict__ seg_count, int E, int seg_align) {
-  // single block; thread e owns expert e
+  // single block; one warp per expert column at a time
   extern __shared__ int s_tot[];
-  for (int e = threadIdx.x; e < E; e += blockDim.x) {
-    int acc = 0;
-    for (int c = 0; c < PLAN_CHUNKS; ++c) {
-      const int v = chunk_hist[static_cast<size_t>(c) * E + e];
-      chunk_hist[static_cast<size_t>(c) * E + e] = acc;      // exclusive prefix over chunks
-      acc += v;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
+  for (int e = warp; e < E; e += nwarps) {
+    const int total = warp_chunk_prefix(chunk_hist, PLAN_CHUNKS, E, e, lane);
+    if (lane == 0) {
+      s_tot[e] = total;
+      seg_count[e] = total;
     }
-    s_tot[e] = acc;
-    seg_count[e] = acc;
   }
   __syncthreads();
   if (threadIdx.x == 0) {
@@ -380,42 +437,63 @@ __global__ void scatter_rows_kernel(const uint8_t* __restrict__ x, uint8_t* __re
                   x + static_cast<size_t>(p / k) * row_bytes, row_bytes, lane);
 }
 
-// y[t] = sum_groups ( round_bf16( sum_picks gs * out[pos] ) ), one block per token
+// y[t] = sum_groups ( round_bf16( sum_picks gs * out[pos] ) ), one block per token; every thread
+// owns 8 consecutive columns (one 16-byte load per pick)
 __global__ void combine_kernel(const __nv_bfloat16* __restrict__ out, const int* __restrict__ pos,
                                const int* __restrict__ es, const float* __restrict__ gs,
                                __nv_bfloat16* __restrict__ y, int T, int k, int dim,
                                int group_size, long long out_rows, int* __restrict__ status) {
-  const int t = blockIdx.x;
-  if (t >= T) return;
-  for (int c = threadIdx.x * 2; c < dim; c += blockDim.x * 2) {
-    float tot0 = 0.f, tot1 = 0.f, par0 = 0.f, par1 = 0.f;
-    int prev_group = -1;
-    for (int j = 0; j < k; ++j) {
-      const int o = t * k + j;
-      const int row = pos[o];
-      const int grp = es[o] / group_size;
-      if (j > 0 && grp != prev_group) {
-        const __nv_bfloat162 r = __floats2bfloat162_rn(par0, par1);
-        tot0 += __low2float(r);
-        tot1 += __high2float(r);
-        par0 = par1 = 0.f;
-      }
-      prev_group = grp;
+  __shared__ int s_row[PLAN_MAX_K];
+  __shared__ int s_grp[PLAN_MAX_K];
+  __shared__ float s_w[PLAN_MAX_K];
+  for (int t = blockIdx.x; t < T; t += gridDim.x) {
+    __syncthreads();
+    if (static_cast<int>(threadIdx.x) < k) {
+      const int o = t * k + threadIdx.x;
+      int row = pos[o];
       if (row < 0 || row >= out_rows) {
-        if (c == 0 && status) atomicCAS(status, 0, ST_BAD_INDEX);
-        continue;
+        row = -1;
+        if (status) atomicCAS(status, 0, ST_BAD_INDEX);
       }
-      const float w = gs ? gs[o] : 1.0f;
-      const __nv_bfloat162 v =
-          *reinterpret_cast<const __nv_bfloat162*>(out + static_cast<size_t>(row) * dim + c);
-      par0 += w * __low2float(v);
-      par1 += w * __high2float(v);
+      s_row[threadIdx.x] = row;
+      s_grp[threadIdx.x] = es[o] / group_size;
+      s_w[threadIdx.x] = gs ? gs[o] : 1.0f;
     }
-    const __nv_bfloat162 r = __floats2bfloat162_rn(par0, par1);
-    tot0 += __low2float(r);
-    tot1 += __high2float(r);
-    *reinterpret_cast<__nv_bfloat162*>(y + static_cast<size_t>(t) * dim + c) =
-        __floats2bfloat162_rn(tot0, tot1);
+    __syncthreads();
+    for (int c = threadIdx.x; c < dim / 8; c += blockDim.x) {
+      float tot[8], par[8];
+#pragma unroll
+      for (int i = 0; i < 8; ++i) tot[i] = par[i] = 0.f;
+      for (int j = 0; j < k; ++j) {
+        if (j > 0 && s_grp[j] != s_grp[j - 1]) {
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            tot[i] += __bfloat162float(__float2bfloat16_rn(par[i]));
+            par[i] = 0.f;
+          }
+        }
+        const int row = s_row[j];
+        if (row < 0) continue;
+        const float w = s_w[j];
+        const uint4 v = *(reinterpret_cast<const uint4*>(out + static_cast<size_t>(row) * dim) + c);
+        const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const float2 f = __bfloat1622float2(h[i]);
+          par[2 * i] += w * f.x;
+          par[2 * i + 1] += w * f.y;
+        }
+      }
+      uint4 o4;
+      __nv_bfloat162* oh = reinterpret_cast<__nv_bfloat162*>(&o4);
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const float a0 = tot[2 * i] + __bfloat162float(__float2bfloat16_rn(par[2 * i]));
+        const float a1 = tot[2 * i + 1] + __bfloat162float(__float2bfloat16_rn(par[2 * i + 1]));
+        oh[i] = __floats2bfloat162_rn(a0, a1);
+      }
+      *(reinterpret_cast<uint4*>(y + static_cast<size_t>(t) * dim) + c) = o4;
+    }
   }
 }
 
@@ -517,15 +595,13 @@ __global__ void k1_pass1_kernel(const long long* __restrict__ rslot, int* __rest
 __global__ void sort_pass2_kernel(int* __restrict__ chunk_hist, long long* __restrict__ totals,
                                   int n_buckets) {
   __shared__ int s_tot[SORT_MAX_BUCKETS];
-  for (int b = threadIdx.x; b < n_buckets; b += blockDim.x) {
-    int acc = 0;
-    for (int c = 0; c < SORT_CHUNKS; ++c) {
-      const int v = chunk_hist[c * n_buckets + b];
-      chunk_hist[c * n_buckets + b] = acc;
-      acc += v;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
+  for (int b = warp; b < n_buckets; b += nwarps) {
+    const int total = warp_chunk_prefix(chunk_hist, SORT_CHUNKS, n_buckets, b, lane);
+    if (lane == 0) {
+      s_tot[b] = total;
+      totals[b] = total;
     }
-    s_tot[b] = acc;
-    totals[b] = acc;
   }
   __syncthreads();
   if (threadIdx.x == 0) {
@@ -789,8 +865,8 @@ extern "C" int tb200_moe_combine(const void* out, const int* pos, const int* es,
                                  void* y, int T, int k, int dim, int group_size,
                                  long long out_rows, int* status, cudaStream_t stream) {
   if (T == 0) return TB200_OK;
-  if (dim % 2 || group_size < 1) return TB200_ERR_ARG;
-  int threads = dim / 2 >= 256 ? 256 : 128;
+  if (dim % 8 || group_size < 1 || k > PLAN_MAX_K) return TB200_ERR_ARG;
+  int threads = dim / 8 >= 256 ? 256 : (dim / 8 >= 128 ? 128 : 64);
   combine_kernel<<<T, threads, 0, stream>>>(static_cast<const __nv_bfloat16*>(out), pos, es, gs,
                                             static_cast<__nv_bfloat16*>(y), T, k, dim, group_size,
                                             out_rows, status);

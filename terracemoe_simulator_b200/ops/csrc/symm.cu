@@ -72,6 +72,31 @@ __device__ __forceinline__ bool block_wait_flags(const Tb200Arena& a, int kind, 
   return s_ok != 0;
 }
 
+// Exclusive prefix over the `n_chunks` (multiple of 32) rows of hist[chunk][stride] for column
+// `col`, done by one warp; returns the column total (valid in every lane).
+__device__ __forceinline__ int warp_chunk_prefix(int* hist, int n_chunks, int stride, int col,
+                                                 int lane) {
+  const int per = n_chunks / 32;
+  int local[8];
+  int sum = 0;
+  for (int i = 0; i < per; ++i) {
+    local[i] = hist[static_cast<size_t>(lane * per + i) * stride + col];
+    sum += local[i];
+  }
+  int incl = sum;
+#pragma unroll
+  for (int o = 1; o < 32; o <<= 1) {
+    const int v = __shfl_up_sync(0xffffffffu, incl, o);
+    if (lane >= o) incl += v;
+  }
+  int run = incl - sum;
+  for (int i = 0; i < per; ++i) {
+    hist[static_cast<size_t>(lane * per + i) * stride + col] = run;
+    run += local[i];
+  }
+  return __shfl_sync(0xffffffffu, incl, 31);
+}
+
 // ---------------------------------------------------------------------------------------------
 // Plan: all-gather the expert histogram, derive every offset table.  One block.
 // ---------------------------------------------------------------------------------------------
@@ -91,23 +116,15 @@ __global__ void ep_plan_kernel(Tb200Arena a, PlanTables t, int epoch, int* statu
   int* tot_all = sm + E;          // [E]
   int* seg_g = sm + 2 * E;        // [E]
   int* src_prefix = sm + 3 * E;   // [E]
-  for (int e = threadIdx.x; e < E; e += blockDim.x) {
-    int acc = 0;
-    for (int c = 0; c < TB200_PLAN_CHUNKS; ++c) {
-      const int v = t.chunk_hist[c * E + e];
-      t.chunk_hist[c * E + e] = acc;
-      acc += v;
+  {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
+    for (int e = warp; e < E; e += nwarps) {
+      const int total = warp_chunk_prefix(t.chunk_hist, TB200_PLAN_CHUNKS, E, e, lane);
+      if (lane == 0) tot_mine[e] = total;
     }
-    tot_mine[e] = acc;
-  }
-  if (t.chunka_hist != nullptr) {
-    for (int g = threadIdx.x; g < a.n_nodes; g += blockDim.x) {
-      int acc = 0;
-      for (int c = 0; c < TB200_PLAN_CHUNKS; ++c) {
-        const int v = t.chunka_hist[c * a.n_nodes + g];
-        t.chunka_hist[c * a.n_nodes + g] = acc;
-        acc += v;
-      }
+    if (t.chunka_hist != nullptr) {
+      for (int g = warp; g < a.n_nodes; g += nwarps)
+        warp_chunk_prefix(t.chunka_hist, TB200_PLAN_CHUNKS, a.n_nodes, g, lane);
     }
   }
   __syncthreads();
