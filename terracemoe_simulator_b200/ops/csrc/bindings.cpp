@@ -361,11 +361,24 @@ Tensor swiglu_bwd(const Tensor& h13, const Tensor& dact) {
   return dh;
 }
 
+void zero_pad_rows(Tensor buf, const Tensor& seg_start, const Tensor& seg_count, int64_t align) {
+  TORCH_CHECK(buf.is_cuda() && buf.is_contiguous() && buf.dim() == 2, "zero_pad_rows: [rows, cols]");
+  TORCH_CHECK(seg_start.scalar_type() == at::kInt && seg_count.scalar_type() == at::kInt &&
+                  seg_start.numel() == seg_count.numel(),
+              "zero_pad_rows: int32 segment tables");
+  c10::cuda::CUDAGuard guard(buf.device());
+  check_rc(tb200_zero_pad_rows(buf.data_ptr(), seg_start.data_ptr<int>(),
+                               seg_count.data_ptr<int>(), seg_start.numel(), align,
+                               static_cast<int>(buf.size(1) * buf.element_size()), buf.size(0),
+                               cur_stream()),
+           "zero_pad_rows");
+}
+
 // ---------------------------------------------------------------------------------------------
 // grouped GEMMs.  mode 0: B[g] is [K, N(*2 for SwiGLU)];  mode 1: B[g] is [N, K].
 std::tuple<Tensor, Tensor> grouped_gemm(const Tensor& A, const Tensor& B, const Tensor& seg_start,
                                         const Tensor& seg_count, int64_t mode, int64_t epilogue,
-                                        bool save_pre, int64_t max_ctas) {
+                                        bool save_pre, int64_t max_ctas, int64_t pad_align) {
   CHECK_CUDA_CONTIG(A);
   CHECK_CUDA_CONTIG(B);
   TORCH_CHECK(A.scalar_type() == at::kBFloat16 && B.scalar_type() == at::kBFloat16,
@@ -392,13 +405,13 @@ std::tuple<Tensor, Tensor> grouped_gemm(const Tensor& A, const Tensor& B, const 
                                 C2.defined() ? C2.data_ptr() : nullptr, seg_start.data_ptr<int>(),
                                 seg_count.data_ptr<int>(), G, rows, N, K, N, 2 * N, b_rows, b_cols,
                                 mode, epilogue, status_ptr(A), max_ctas, nullptr, 0, 0,
-                                cur_stream()),
+                                static_cast<int>(pad_align), cur_stream()),
              "grouped_gemm");
   return {C, C2.defined() ? C2 : at::empty({0}, A.options())};
 }
 
 Tensor grouped_wgrad(const Tensor& X, const Tensor& dY, const Tensor& seg_start,
-                     const Tensor& seg_count, int64_t max_ctas) {
+                     const Tensor& seg_count, int64_t max_ctas, int64_t pad_align) {
   CHECK_CUDA_CONTIG(X);
   CHECK_CUDA_CONTIG(dY);
   TORCH_CHECK(X.scalar_type() == at::kBFloat16 && dY.scalar_type() == at::kBFloat16,
@@ -413,7 +426,8 @@ Tensor grouped_wgrad(const Tensor& X, const Tensor& dY, const Tensor& seg_start,
   Tensor dW = at::empty({G, X.size(1), dY.size(1)}, X.options());
   check_rc(tb200_grouped_wgrad(X.data_ptr(), dY.data_ptr(), dW.data_ptr(),
                                seg_start.data_ptr<int>(), seg_count.data_ptr<int>(), G, X.size(0),
-                               X.size(1), dY.size(1), status_ptr(X), max_ctas, cur_stream()),
+                               X.size(1), dY.size(1), status_ptr(X), max_ctas,
+                               static_cast<int>(pad_align), cur_stream()),
            "grouped_wgrad");
   return dW;
 }
@@ -443,9 +457,12 @@ TORCH_LIBRARY(terrace, m) {
         "(Tensor, Tensor)", &moe_combine_bwd);
   m.def("swiglu_bwd(Tensor h13, Tensor dact) -> Tensor", &swiglu_bwd);
   m.def("grouped_gemm(Tensor A, Tensor B, Tensor seg_start, Tensor seg_count, int mode, "
-        "int epilogue, bool save_pre, int max_ctas) -> (Tensor, Tensor)", &grouped_gemm);
-  m.def("grouped_wgrad(Tensor X, Tensor dY, Tensor seg_start, Tensor seg_count, int max_ctas) "
-        "-> Tensor", &grouped_wgrad);
+        "int epilogue, bool save_pre, int max_ctas, int pad_align=0) -> (Tensor, Tensor)",
+        &grouped_gemm);
+  m.def("grouped_wgrad(Tensor X, Tensor dY, Tensor seg_start, Tensor seg_count, int max_ctas, "
+        "int pad_align=0) -> Tensor", &grouped_wgrad);
+  m.def("zero_pad_rows(Tensor(a!) buf, Tensor seg_start, Tensor seg_count, int align) -> ()",
+        &zero_pad_rows);
   terrace_b200_register_symm(m);
 }
 

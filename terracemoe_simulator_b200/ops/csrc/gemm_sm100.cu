@@ -53,6 +53,8 @@ struct GemmParams {
   const int* wait_flags;  // optional: arrival flags that must reach wait_epoch before A is read
   int wait_n;
   int wait_epoch;
+  int pad_align;          // > 0: every group's rows are padded to this multiple; fwd / dgrad write
+                          // zeros into the padding rows, wgrad (multiple of BK) relies on them
 };
 
 struct __align__(8) PipeBarriers {
@@ -275,7 +277,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
         if (MODE == MODE_WGRAD) {
           // rows past the end of the group belong to the next group: zero their lines
           const int valid = cnt - kb * BK;
-          if (valid < BK) {
+          if (valid < BK && (p.pad_align <= 0 || p.pad_align % BK != 0)) {
             const int lines = BK - valid;
             for (int i = lane; i < lines * 8 * 6; i += 32) {
               const int box = i / (lines * 8);
@@ -356,7 +358,10 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
         }
       } else if (EPI == EPI_SWIGLU) {
         const int row = mt * BM + row_in_tile;
-        const bool live = row < cnt;
+        const int padded = p.pad_align > 0 ? (cnt + p.pad_align - 1) / p.pad_align * p.pad_align
+                                           : cnt;
+        const bool real = row < cnt;
+        const bool live = row < padded;            // padding rows are written as zeros
         __nv_bfloat16* crow = p.C + static_cast<size_t>(seg0 + row) * p.ldc;
         __nv_bfloat16* c2row =
             p.C2 ? p.C2 + static_cast<size_t>(seg0 + row) * p.ldc2 : nullptr;
@@ -391,6 +396,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
                   const float2 uf = __bfloat1622float2(ub);
                   pv[i] = pack_bf16(silu_f(gf.x) * uf.x, silu_f(gf.y) * uf.y);
                 }
+                if (!real) v = vg = vu = make_uint4(0, 0, 0, 0);
                 *reinterpret_cast<uint4*>(crow + n0 + j * 8) = v;
                 if (c2row) {
                   *reinterpret_cast<uint4*>(c2row + n0 + j * 8) = vg;
@@ -402,7 +408,10 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
         }
       } else {
         const int row = mt * BM + row_in_tile;
-        const bool live = row < cnt;
+        const int padded = p.pad_align > 0 ? (cnt + p.pad_align - 1) / p.pad_align * p.pad_align
+                                           : cnt;
+        const bool real = row < cnt;
+        const bool live = row < padded;            // padding rows are written as zeros
         __nv_bfloat16* crow = p.C + static_cast<size_t>(seg0 + row) * p.ldc;
 #pragma unroll 1
         for (int c = 0; c < BN / 32; c += 2) {
@@ -412,8 +421,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
           tmem_ld_wait();
           const int n0 = nt * BN + c * 32;
           if (live) {
-            store_row32(crow + n0, r0, n0, p.N, false);
-            store_row32(crow + n0 + 32, r1, n0 + 32, p.N, false);
+            store_row32(crow + n0, r0, n0, p.N, !real);
+            store_row32(crow + n0 + 32, r1, n0 + 32, p.N, !real);
           }
         }
       }
@@ -518,7 +527,7 @@ extern "C" int tb200_grouped_gemm(const void* A, const void* B, void* C, void* C
                                   long long a_rows, int N, int K, int ldc, int ldc2, int b_rows,
                                   int b_cols, int mode, int epilogue, int* status, int max_ctas,
                                   const int* wait_flags, int wait_n, int wait_epoch,
-                                  cudaStream_t stream) {
+                                  int pad_align, cudaStream_t stream) {
   if (n_groups <= 0 || n_groups > MAX_GROUPS) return TB200_ERR_ARG;
   if ((K % 8) || (N % 8) || (ldc % 8) || (b_cols % 8)) return TB200_ERR_ARG;
   if (mode != MODE_FWD && mode != MODE_DGRAD) return TB200_ERR_ARG;
@@ -559,6 +568,7 @@ extern "C" int tb200_grouped_gemm(const void* A, const void* B, void* C, void* C
   p.wait_flags = wait_flags;
   p.wait_n = wait_n;
   p.wait_epoch = wait_epoch;
+  p.pad_align = pad_align;
   if (mode == MODE_DGRAD && epilogue == EPI_SWIGLU)
     return launch_gemm<MODE_DGRAD, EPI_SWIGLU>(ta, tb, p, max_ctas, stream);
   if (mode == MODE_DGRAD) return launch_gemm<MODE_DGRAD, EPI_PLAIN>(ta, tb, p, max_ctas, stream);
@@ -568,7 +578,8 @@ extern "C" int tb200_grouped_gemm(const void* A, const void* B, void* C, void* C
 
 extern "C" int tb200_grouped_wgrad(const void* X, const void* dY, void* dW, const int* seg_start,
                                    const int* seg_count, int n_groups, long long rows, int M,
-                                   int N, int* status, int max_ctas, cudaStream_t stream) {
+                                   int N, int* status, int max_ctas, int pad_align,
+                                   cudaStream_t stream) {
   if (n_groups <= 0 || n_groups > MAX_GROUPS) return TB200_ERR_ARG;
   if ((M % 8) || (N % 8)) return TB200_ERR_ARG;
   CUtensorMap ta, tb;
@@ -602,5 +613,6 @@ extern "C" int tb200_grouped_wgrad(const void* X, const void* dY, void* dW, cons
   p.wait_flags = nullptr;
   p.wait_n = 0;
   p.wait_epoch = 0;
+  p.pad_align = pad_align;
   return launch_gemm<MODE_WGRAD, EPI_PLAIN>(ta, tb, p, max_ctas, stream);
 }

@@ -28,11 +28,17 @@ int tb200_grouped_gemm(const void* A, const void* B, void* C, void* C2, const in
                        const int* seg_count, int n_groups, long long a_rows, int N, int K, int ldc,
                        int ldc2, int b_rows, int b_cols, int mode, int epilogue, int* status,
                        int max_ctas, const int* wait_flags, int wait_n, int wait_epoch,
-                       cudaStream_t stream);
+                       int pad_align, cudaStream_t stream);
 // dW[g][M, N] = X[rows of g, M]^T * dY[rows of g, N]; groups with no rows get zeros.
 int tb200_grouped_wgrad(const void* X, const void* dY, void* dW, const int* seg_start,
                         const int* seg_count, int n_groups, long long rows, int M, int N,
-                        int* status, int max_ctas, cudaStream_t stream);
+                        int* status, int max_ctas, int pad_align, cudaStream_t stream);
+// pad_align > 0 declares that every group's rows are padded to that multiple: the fwd / dgrad
+// kernels then write zeros into the padding rows of C (and C2), and the wgrad kernel, when the
+// multiple is a multiple of 64, reads them as zero contributions instead of masking the K tail in
+// shared memory.  Zero the padding of buffers no GEMM writes with tb200_zero_pad_rows.
+int tb200_zero_pad_rows(void* buf, const int* seg_start, const int* seg_count, int n_groups,
+                        int align, int row_bytes, long long buf_rows, cudaStream_t stream);
 
 // ---- moe_kernels.cu --------------------------------------------------------------------------
 int tb200_passthrough(const void* src, void* dst, size_t bytes, cudaStream_t stream);
@@ -96,8 +102,8 @@ size_t tb200_k2_scratch_ints(int T, int k, int groups_m, int n_nodes);
 // ---- symm.cu -----------------------------------------------------------------------------------
 struct Tb200Arena;
 int tb200_ep_plan(const struct Tb200Arena* a, int* chunk_hist, int* chunka_hist, int* my_base,
-                  int* seg_start, int* seg_count, int* rows_a, int epoch, int* status,
-                  cudaStream_t stream);
+                  int* seg_start, int* seg_count, int* rows_a, int epoch, int seg_align,
+                  int* status, cudaStream_t stream);
 int tb200_ep_push(const struct Tb200Arena* a, const void* x, const int* es, const int* rank_local,
                   const int* chunk_base, const int* my_base, int* pos_out, const float* gs,
                   float* dgs, long long off_dst, long long off_dot, int T, int flag_kind, int epoch,

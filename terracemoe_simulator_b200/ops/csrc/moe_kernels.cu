@@ -535,6 +535,20 @@ __global__ void combine_bwd_kernel(const __nv_bfloat16* __restrict__ dy,
   }
 }
 
+// Zero the padding rows [count, align_up(count)) of every group of a row buffer.
+__global__ void zero_pad_rows_kernel(uint8_t* __restrict__ buf, const int* __restrict__ seg_start,
+                                     const int* __restrict__ seg_count, int align, int row_bytes,
+                                     long long buf_rows) {
+  const int e = blockIdx.x, j = blockIdx.y;
+  const int cnt = seg_count[e];
+  const int pad = (cnt + align - 1) / align * align - cnt;
+  if (j >= pad) return;
+  const long long row = static_cast<long long>(seg_start[e]) + cnt + j;
+  if (row < 0 || row >= buf_rows) return;
+  uint4* dst = reinterpret_cast<uint4*>(buf + static_cast<size_t>(row) * row_bytes);
+  for (int i = threadIdx.x; i < row_bytes / 16; i += blockDim.x) dst[i] = make_uint4(0, 0, 0, 0);
+}
+
 __global__ void swiglu_bwd_kernel(const __nv_bfloat16* __restrict__ h13,
                                   const __nv_bfloat16* __restrict__ dact,
                                   __nv_bfloat16* __restrict__ dh13, long long rows, int d) {
@@ -883,6 +897,17 @@ extern "C" int tb200_moe_combine_bwd(const void* dy, const void* out, const int*
   combine_bwd_kernel<<<(n + 7) / 8, 256, 0, stream>>>(
       static_cast<const __nv_bfloat16*>(dy), static_cast<const __nv_bfloat16*>(out), pos, gs,
       static_cast<__nv_bfloat16*>(dout), dgs, n, k, dim, out_rows, status);
+  return LAUNCH_OK();
+}
+
+extern "C" int tb200_zero_pad_rows(void* buf, const int* seg_start, const int* seg_count,
+                                   int n_groups, int align, int row_bytes, long long buf_rows,
+                                   cudaStream_t stream) {
+  if (align <= 1 || n_groups <= 0) return TB200_OK;
+  if (row_bytes % 16 || align > 1024) return TB200_ERR_ARG;
+  dim3 grid(n_groups, align - 1);
+  zero_pad_rows_kernel<<<grid, 128, 0, stream>>>(static_cast<uint8_t*>(buf), seg_start, seg_count,
+                                                 align, row_bytes, buf_rows);
   return LAUNCH_OK();
 }
 

@@ -109,7 +109,8 @@ struct PlanTables {
   int* rows_a;        // [W][N_g] Hop A rows rank s sends to group g
 };
 
-__global__ void ep_plan_kernel(Tb200Arena a, PlanTables t, int epoch, int* status) {
+__global__ void ep_plan_kernel(Tb200Arena a, PlanTables t, int epoch, int seg_align,
+                               int* status) {
   extern __shared__ int sm[];
   const int E = a.n_experts, W = a.world;
   int* tot_mine = sm;             // [E]
@@ -155,7 +156,7 @@ __global__ void ep_plan_kernel(Tb200Arena a, PlanTables t, int epoch, int* statu
     for (int le = 0; le < a.epr; ++le) {
       const int e = threadIdx.x * a.epr + le;
       seg_g[e] = off;
-      off += tot_all[e];
+      off += (tot_all[e] + seg_align - 1) / seg_align * seg_align;
     }
     if (off > a.cap_rows && status) atomicCAS(status, 0, ST_BAD_INDEX);
   }
@@ -609,11 +610,12 @@ static bool arena_ok(const Tb200Arena* a) {
 }
 
 extern "C" int tb200_ep_plan(const Tb200Arena* a, int* chunk_hist, int* chunka_hist, int* my_base,
-                             int* seg_start, int* seg_count, int* rows_a, int epoch, int* status,
-                             cudaStream_t stream) {
-  if (!arena_ok(a)) return TB200_ERR_ARG;
+                             int* seg_start, int* seg_count, int* rows_a, int epoch, int seg_align,
+                             int* status, cudaStream_t stream) {
+  if (!arena_ok(a) || seg_align < 1) return TB200_ERR_ARG;
   PlanTables t{chunk_hist, chunka_hist, my_base, seg_start, seg_count, rows_a};
-  ep_plan_kernel<<<1, 256, 4 * a->n_experts * sizeof(int), stream>>>(*a, t, epoch, status);
+  ep_plan_kernel<<<1, 256, 4 * a->n_experts * sizeof(int), stream>>>(*a, t, epoch, seg_align,
+                                                                     status);
   return LAUNCH_OK();
 }
 

@@ -164,7 +164,7 @@ std::tuple<Tensor, Tensor, Tensor, Tensor, Tensor> ep_plan_pass1(const Tensor& e
 
 std::tuple<Tensor, Tensor, Tensor, Tensor> ep_plan(const Tensor& arena, Tensor chunk_hist,
                                                    const c10::optional<Tensor>& chunka_hist,
-                                                   int64_t epoch) {
+                                                   int64_t epoch, int64_t seg_align) {
   const Tb200Arena* a = arena_of(arena);
   c10::cuda::CUDAGuard guard(chunk_hist.device());
   auto iopt = chunk_hist.options();
@@ -175,7 +175,7 @@ std::tuple<Tensor, Tensor, Tensor, Tensor> ep_plan(const Tensor& arena, Tensor c
                          chunka_hist.has_value() ? chunka_hist->data_ptr<int>() : nullptr,
                          my_base.data_ptr<int>(), seg_start.data_ptr<int>(),
                          seg_count.data_ptr<int>(), rows_a.data_ptr<int>(), epoch,
-                         st_ptr(chunk_hist), cur_stream()),
+                         static_cast<int>(seg_align), st_ptr(chunk_hist), cur_stream()),
            "ep_plan");
   return {my_base, seg_start, seg_count, rows_a};
 }
@@ -328,7 +328,7 @@ Tensor origin_pull_dgate(const Tensor& arena, const Tensor& es, const Tensor& ro
 void grouped_gemm_ex(const Tensor& A, const Tensor& B, Tensor C, const c10::optional<Tensor>& C2,
                      const Tensor& seg_start, const Tensor& seg_count, int64_t mode,
                      int64_t epilogue, const c10::optional<Tensor>& arena, int64_t wait_kind,
-                     int64_t wait_first, int64_t wait_n, int64_t epoch) {
+                     int64_t wait_first, int64_t wait_n, int64_t epoch, int64_t pad_align) {
   TORCH_CHECK(A.is_cuda() && A.is_contiguous() && B.is_cuda() && B.is_contiguous() &&
                   C.is_cuda() && C.is_contiguous(),
               "grouped_gemm_ex: contiguous CUDA tensors");
@@ -364,7 +364,7 @@ void grouped_gemm_ex(const Tensor& A, const Tensor& B, Tensor C, const c10::opti
                               C2.has_value() ? C2->data_ptr() : nullptr, seg_start.data_ptr<int>(),
                               seg_count.data_ptr<int>(), G, rows, N, K, N, 2 * N, b_rows, b_cols,
                               mode, epilogue, st_ptr(A), 0, wait_flags, wait_n, epoch,
-                              cur_stream()),
+                              static_cast<int>(pad_align), cur_stream()),
            "grouped_gemm_ex");
 }
 
@@ -379,8 +379,8 @@ void terrace_b200_register_symm(torch::Library& m) {
   m.def("symm_make_arena(int[] peers, int[] offsets, int[] geom) -> Tensor", &symm_make_arena);
   m.def("ep_plan_pass1(Tensor expert_idx, Tensor gates, int E) -> "
         "(Tensor, Tensor, Tensor, Tensor, Tensor)", &ep_plan_pass1);
-  m.def("ep_plan(Tensor arena, Tensor(a!) chunk_hist, Tensor(b!)? chunka_hist, int epoch) -> "
-        "(Tensor, Tensor, Tensor, Tensor)", &ep_plan);
+  m.def("ep_plan(Tensor arena, Tensor(a!) chunk_hist, Tensor(b!)? chunka_hist, int epoch, "
+        "int seg_align=1) -> (Tensor, Tensor, Tensor, Tensor)", &ep_plan);
   m.def("ep_push(Tensor arena, Tensor x, Tensor es, Tensor rank_local, Tensor chunk_base, "
         "Tensor my_base, Tensor? gs, bool want_dgs, int dst_sel, int dot_sel, int flag_kind, "
         "int epoch, Tensor(a!) done) -> (Tensor, Tensor)", &ep_push);
@@ -404,5 +404,5 @@ void terrace_b200_register_symm(torch::Library& m) {
         "Tensor", &origin_pull_dgate);
   m.def("grouped_gemm_ex(Tensor A, Tensor B, Tensor(a!) C, Tensor(b!)? C2, Tensor seg_start, "
         "Tensor seg_count, int mode, int epilogue, Tensor? arena, int wait_kind, int wait_first, "
-        "int wait_n, int epoch) -> ()", &grouped_gemm_ex);
+        "int wait_n, int epoch, int pad_align=0) -> ()", &grouped_gemm_ex);
 }

@@ -27,6 +27,7 @@ class _Counted:
     _PER_CALL = {"rmsnorm_fwd": 1, "rmsnorm_bwd": 1, "route_select": 1, "route_select_bwd": 1,
                  "moe_plan": 3, "moe_scatter_rows": 1, "moe_combine": 1, "moe_combine_bwd": 1,
                  "swiglu_bwd": 1, "grouped_gemm": 1, "grouped_wgrad": 1, "passthrough": 1,
+                 "zero_pad_rows": 1,
                  "k1_arrival": 3, "k2_pack": 3, "ep_plan_pass1": 1, "ep_plan": 1, "ep_push": 1,
                  "ep_signal": 1, "ep_pull_combine": 1, "hopa_rank": 1, "hopa_push": 1,
                  "arrival_push": 1, "arrival_combine": 1, "origin_combine": 1,
@@ -264,6 +265,9 @@ def moe_local_supported(x, w13, w2) -> bool:
             and min(w13.shape[1], w13.shape[2] // 2) >= 64 and w13.shape[0] <= 1024)
 
 
+SEG_ALIGN = 64      # expert segments start on multiples of 64 rows; padding rows hold zeros
+
+
 class _MoELocal(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x, expert_idx, gates, w13, w2, group_size):
@@ -271,12 +275,17 @@ class _MoELocal(torch.autograd.Function):
         E = w13.shape[0]
         T, k = expert_idx.shape
         xc = x.contiguous()
+        rows_cap = T * k + E * (SEG_ALIGN - 1)
         es, gs, cols, pos, seg_start, seg_count = lib.moe_plan(
-            expert_idx.contiguous(), gates.detach().float().contiguous(), E, 1)
-        xs = lib.moe_scatter_rows(xc, pos, T * k)
+            expert_idx.contiguous(), gates.detach().float().contiguous(), E, SEG_ALIGN)
+        xs = lib.moe_scatter_rows(xc, pos, rows_cap)
         need = any(ctx.needs_input_grad)
-        act, h13 = lib.grouped_gemm(xs, w13.contiguous(), seg_start, seg_count, 0, 1, need, 0)
-        out, _ = lib.grouped_gemm(act, w2.contiguous(), seg_start, seg_count, 0, 0, False, 0)
+        if need:
+            lib.zero_pad_rows(xs, seg_start, seg_count, SEG_ALIGN)   # wgrad reads the padding
+        act, h13 = lib.grouped_gemm(xs, w13.contiguous(), seg_start, seg_count, 0, 1, need, 0,
+                                    SEG_ALIGN)
+        out, _ = lib.grouped_gemm(act, w2.contiguous(), seg_start, seg_count, 0, 0, False, 0,
+                                  SEG_ALIGN)
         y = lib.moe_combine(out, pos, es, gs, group_size)
         ctx.save_for_backward(xs, h13, act, out, pos, es, gs, cols, seg_start, seg_count, w13, w2)
         ctx.group_size = group_size
@@ -288,12 +297,14 @@ class _MoELocal(torch.autograd.Function):
     def backward(ctx, dy):
         xs, h13, act, out, pos, es, gs, cols, seg_start, seg_count, w13, w2 = ctx.saved_tensors
         lib = _lib()
+        A = SEG_ALIGN
         dout, dgs = lib.moe_combine_bwd(dy.contiguous(), out, pos, gs, True)
-        dact, _ = lib.grouped_gemm(dout, w2.contiguous(), seg_start, seg_count, 1, 0, False, 0)
-        dw2 = lib.grouped_wgrad(act, dout, seg_start, seg_count, 0)
+        lib.zero_pad_rows(dout, seg_start, seg_count, A)
+        dact, _ = lib.grouped_gemm(dout, w2.contiguous(), seg_start, seg_count, 1, 0, False, 0, A)
+        dw2 = lib.grouped_wgrad(act, dout, seg_start, seg_count, 0, A)
         dh13 = lib.swiglu_bwd(h13, dact)
-        dxs, _ = lib.grouped_gemm(dh13, w13.contiguous(), seg_start, seg_count, 1, 0, False, 0)
-        dw13 = lib.grouped_wgrad(xs, dh13, seg_start, seg_count, 0)
+        dxs, _ = lib.grouped_gemm(dh13, w13.contiguous(), seg_start, seg_count, 1, 0, False, 0, A)
+        dw13 = lib.grouped_wgrad(xs, dh13, seg_start, seg_count, 0, A)
         dx = lib.moe_combine(dxs, pos, es, None, ctx.group_size)
         dgates = torch.zeros_like(dgs).scatter_(1, cols.long(), dgs).to(ctx.gate_dtype)
         return dx, None, dgates, dw13, dw2, None

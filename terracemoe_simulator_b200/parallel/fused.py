@@ -36,6 +36,7 @@ XIN, YOUT, DOUT, DXS, HA_ROWS, RED, HB_ROWS, DRED = range(8)
  FK_B_RED) = range(10)
 FK_NUM = 10
 MAX_WORLD = 16
+SEG_ALIGN = 64          # expert segments start on multiples of 64 rows (zero padding rows)
 
 LIVE = {"one_hop_fwd": 0, "two_hop_fwd": 0, "one_hop_bwd": 0, "two_hop_bwd": 0, "echo": 0}
 
@@ -65,7 +66,8 @@ class FusedEPContext:
         self.k, self.M, self.q = cfg.top_k, cfg.top_groups, cfg.per_group_k
         self.two_hop_ok = (self.n_nodes >= 2 and cfg.n_groups == self.n_nodes)
         self.cap_rows = _align(min(world * tokens * self.k,
-                                   int(row_capacity_factor * tokens * self.k)), 128)
+                                   int(row_capacity_factor * tokens * self.k))
+                               + self.epr * (SEG_ALIGN - 1), 128)
         self.epoch = 0
         H = hidden
         sizes = [
@@ -142,7 +144,8 @@ def _plan(ctx: FusedEPContext, idx, gates, mode: str, ep: int):
     ranka = chunka = None
     if mode == "two_hop":
         ranka, chunka = lib.hopa_rank(ctx.arena, es)
-    my_base, seg_start, seg_count, rows_a = lib.ep_plan(ctx.arena, chunk_hist, chunka, ep)
+    my_base, seg_start, seg_count, rows_a = lib.ep_plan(ctx.arena, chunk_hist, chunka, ep,
+                                                        SEG_ALIGN)
     return dict(es=es, gs=gs, cols=cols, rank_local=rank_local, chunk_hist=chunk_hist,
                 ranka=ranka, chunka=chunka, my_base=my_base, seg_start=seg_start,
                 seg_count=seg_count, rows_a=rows_a)
@@ -197,10 +200,12 @@ class _FusedMoE(torch.autograd.Function):
         need = any(ctx.needs_input_grad)
         h13 = (torch.empty(fctx.cap_rows, 2 * d, dtype=torch.bfloat16, device=x.device)
                if need else None)
+        if need:      # the weight gradient reads the padding rows of xin: keep them zero
+            lib.zero_pad_rows(xin, p["seg_start"], p["seg_count"], SEG_ALIGN)
         lib.grouped_gemm_ex(xin, w13.contiguous(), act, h13, p["seg_start"], p["seg_count"], 0, 1,
-                            fctx.arena, FK_DATA, first, n, ep)
+                            fctx.arena, FK_DATA, first, n, ep, SEG_ALIGN)
         lib.grouped_gemm_ex(act, w2.contiguous(), yout, None, p["seg_start"], p["seg_count"], 0,
-                            0, None, 0, 0, 0, ep)
+                            0, None, 0, 0, 0, ep, SEG_ALIGN)
         _signal_out(fctx, mode, FK_OUT, ep, xc)
         y = _combine(fctx, p, mode, ep, src=YOUT, use_gate=True, backward=False)
         ctx.fctx, ctx.mode, ctx.ep, ctx.plan = fctx, mode, ep, p
@@ -229,13 +234,14 @@ class _FusedMoE(torch.autograd.Function):
         xin, dout, dxs = fctx.section(XIN), fctx.section(DOUT), fctx.section(DXS)
         d = w2.shape[1]
         dact = torch.empty(fctx.cap_rows, d, dtype=torch.bfloat16, device=dy.device)
+        lib.zero_pad_rows(dout, p["seg_start"], p["seg_count"], SEG_ALIGN)
         lib.grouped_gemm_ex(dout, w2.contiguous(), dact, None, p["seg_start"], p["seg_count"], 1,
-                            0, fctx.arena, FK_B_DATA, first, n, ep)
-        dw2 = lib.grouped_wgrad(act, dout, p["seg_start"], p["seg_count"], 0)
+                            0, fctx.arena, FK_B_DATA, first, n, ep, SEG_ALIGN)
+        dw2 = lib.grouped_wgrad(act, dout, p["seg_start"], p["seg_count"], 0, SEG_ALIGN)
         dh13 = lib.swiglu_bwd(h13, dact)
-        dw13 = lib.grouped_wgrad(xin, dh13, p["seg_start"], p["seg_count"], 0)
+        dw13 = lib.grouped_wgrad(xin, dh13, p["seg_start"], p["seg_count"], 0, SEG_ALIGN)
         lib.grouped_gemm_ex(dh13, w13.contiguous(), dxs, None, p["seg_start"], p["seg_count"], 1,
-                            0, None, 0, 0, 0, ep)
+                            0, None, 0, 0, 0, ep, SEG_ALIGN)
         _signal_out(fctx, mode, FK_B_OUT, ep, dyc)
         dx = _combine(fctx, p, mode, ep, src=DXS, use_gate=False, backward=True)
         if mode == "two_hop":

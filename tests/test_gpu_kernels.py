@@ -285,3 +285,34 @@ def test_moe_experts_local_fwd_bwd(native_ops):
     # determinism: same inputs, same bits
     y2 = native_ops.moe_experts_local(x, idx, gates, w13, w2, cfg.group_size)
     assert torch.equal(y, y2)
+
+
+def test_padded_segments_gemm_and_wgrad(native_ops):
+    """Segments aligned to 64 rows: fwd/dgrad write zero padding rows, wgrad relies on them."""
+    torch.manual_seed(3)
+    lib = torch.ops.terrace
+    counts, K, N, A = [70, 0, 129, 64, 5], 256, 320, 64
+    G = len(counts)
+    c = torch.tensor(counts, dtype=torch.int32, device=DEV)
+    padded = (c + A - 1) // A * A
+    s = (torch.cumsum(padded, 0, dtype=torch.int32) - padded).to(torch.int32)
+    rows = int(padded.sum())
+    X = torch.full((rows, K), float("nan"), device=DEV, dtype=torch.bfloat16)   # poison padding
+    W = (torch.randn(G, K, N, device=DEV) * K ** -0.5).bfloat16()
+    for g, n in enumerate(counts):
+        X[int(s[g]):int(s[g]) + n] = torch.randn(n, K, device=DEV).bfloat16()
+    lib.zero_pad_rows(X, s, c, A)
+    Y, _ = lib.grouped_gemm(X, W, s, c, 0, 0, False, 0, A)
+    dY = torch.randn(rows, N, device=DEV, dtype=torch.bfloat16)
+    lib.zero_pad_rows(dY, s, c, A)
+    dW = lib.grouped_wgrad(X, dY, s, c, 0, A)
+    for g, n in enumerate(counts):
+        a, b = int(s[g]), int(s[g]) + n
+        if n == 0:
+            assert torch.all(dW[g] == 0)
+            continue
+        _close(Y[a:b], X[a:b].float() @ W[g].float())
+        assert torch.all(Y[b:int(s[g]) + int(padded[g])] == 0)
+        _close(dW[g], X[a:b].float().t() @ dY[a:b].float())
+    assert torch.isfinite(dW.float()).all()
+    assert native_ops.take_status() == 0
