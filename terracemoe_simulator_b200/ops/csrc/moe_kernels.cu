@@ -975,3 +975,69 @@ extern "C" int tb200_k2_pack(const void* hidden, const long long* expert_idx, co
         gate_bytes, status);
   return LAUNCH_OK();
 }
+
+// ---------------------------------------------------------------------------------------------
+// Allocation-free plan (see no_alloc.h): same three kernels as tb200_moe_plan, scratch in a
+// fixed device array owned by this library instead of a caller-provided buffer.
+// ---------------------------------------------------------------------------------------------
+#include "no_alloc.h"
+
+#include <cstdio>
+#include <mutex>
+
+static __device__ __align__(256) int g_plan_static_scratch[TB200_PLAN_STATIC_MAX_INTS];
+
+namespace {
+constexpr int kMaxDevices = 64;
+int* g_plan_static_ptr[kMaxDevices] = {nullptr};   // device address of the array, per device
+std::mutex g_plan_static_mu;
+
+// The array's name is only a host-side handle here; kernels need its device address, which has
+// to be asked for once per device with that device current.
+int* plan_static_scratch_ptr() {
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return nullptr;
+  std::lock_guard<std::mutex> lock(g_plan_static_mu);
+  if (g_plan_static_ptr[dev] == nullptr) {
+    void* p = nullptr;
+    const cudaError_t rc = cudaGetSymbolAddress(&p, g_plan_static_scratch);
+    if (rc != cudaSuccess || p == nullptr) {
+      std::fprintf(stderr, "tb200_moe_plan_static: cudaGetSymbolAddress failed on device %d: %s\n",
+                   dev, cudaGetErrorString(rc));
+      return nullptr;
+    }
+    g_plan_static_ptr[dev] = static_cast<int*>(p);
+  }
+  return g_plan_static_ptr[dev];
+}
+}  // namespace
+
+extern "C" int tb200_moe_plan_static(const long long* expert_idx, const float* gates, int* es,
+                                     float* gs, int* cols, int* pos, int* seg_start,
+                                     int* seg_count, int T, int k, int E, int seg_align,
+                                     cudaStream_t stream) {
+  if (T < 0 || k < 1 || E < 1 || seg_align < 1) return TB200_ERR_ARG;
+  if (static_cast<long long>(T) * k > TB200_PLAN_STATIC_MAX_PAIRS ||
+      E > TB200_PLAN_STATIC_MAX_EXPERTS || k > PLAN_MAX_K) {
+    std::fprintf(stderr,
+                 "tb200_moe_plan_static: T*k = %lld, E = %d, k = %d exceed the built-in scratch "
+                 "(T*k <= %d, E <= %d, k <= %d); use tb200_moe_plan with your own scratch\n",
+                 static_cast<long long>(T) * k, E, k, TB200_PLAN_STATIC_MAX_PAIRS,
+                 TB200_PLAN_STATIC_MAX_EXPERTS, PLAN_MAX_K);
+    return TB200_ERR_SIZE;
+  }
+  int* scratch = plan_static_scratch_ptr();
+  if (scratch == nullptr) return TB200_ERR_DRIVER;
+  // same layout as tb200_moe_plan: rank_local [T*k] | chunk_hist [PLAN_CHUNKS * E]; pass 1 writes
+  // every word pass 2 and pass 3 read, so stale contents of an earlier call are harmless
+  int* rank_local = scratch;
+  int* chunk_hist = scratch + static_cast<size_t>(T) * k;
+  plan_pass1_kernel<<<PLAN_CHUNKS, 32, E * sizeof(int), stream>>>(expert_idx, gates, es, gs, cols,
+                                                                rank_local, chunk_hist, T, k, E);
+  plan_pass2_kernel<<<1, 256, E * sizeof(int), stream>>>(chunk_hist, seg_start, seg_count, E,
+                                                         seg_align);
+  if (T * k > 0)
+    plan_pass3_kernel<<<(T * k + 255) / 256, 256, 0, stream>>>(es, rank_local, chunk_hist,
+                                                               seg_start, pos, T, k, E);
+  return LAUNCH_OK();
+}
