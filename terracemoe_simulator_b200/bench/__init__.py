@@ -1,0 +1,3 @@
+from .traffic import dispatch_traffic, traffic_bytes, uniformity_cv
+
+__all__ = ["dispatch_traffic", "traffic_bytes", "uniformity_cv"]

@@ -53,6 +53,10 @@ def _align(n: int, a: int = 256) -> int:
 class FusedEPContext:
     def __init__(self, cfg: TRouteConfig, hidden: int, d_expert: int, tokens: int, *, world: int,
                  rank: int, rpn: int, device, group=None, row_capacity_factor: float = 2.0):
+        from .. import ops
+        if not ops.custom_ops_enabled():
+            raise RuntimeError("the fused transport needs the native library: "
+                               + ops.status().reason)
         if world > MAX_WORLD:
             raise ValueError(f"world={world} exceeds the arena limit {MAX_WORLD}")
         if cfg.n_experts % world or world % rpn:

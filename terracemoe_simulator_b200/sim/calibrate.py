@@ -114,51 +114,90 @@ def synthetic(ratio: float, name: str = "", R: int = 8, base_beta_gbps: float = 
 
 
 # ---- platform B200 ----------------------------------------------------------------------------
-# Defaults measured on 2 x B200 with the fused transport (dispatch+combine of 24576 rows of 8 KiB,
-# half of them remote, took 0.36-0.38 ms).  ``b200_from_records`` replaces them with a fit.
-B200_ALPHA_US = {"fast": 12.0, "slow": 12.0, "flat": 14.0}     # kernel launch + flag round trip
-B200_BETA_GBPS = 650.0                                         # per direction, peer stores
-B200_X_HALF = 16 * 1024
-B200_CHAIN_US_PER_ROW = 0.0                                    # no arrival chain: rows are placed
-B200_SPLITS_SYNC_MS = 0.0                                      # no host read-back
+# Constants fitted (``b200_from_sweep``) on the 48-point dispatch+combine sweep measured on
+# 8 x B200 with the fused transport (``sim/data/b200_sweep_8gpu.json``; rows of 8 KiB, 256-16384
+# tokens per GPU, R in {1, 2, 4}, q in {1..4}; device-timed, max over ranks).  One exchange =
+# half of a measured dispatch+combine.
+B200_ALPHA_ONE_HOP_MS = 0.0387        # fixed cost of a one-hop exchange (plan + push/pull + flags)
+B200_ALPHA_TWO_HOP_MS = 0.0597        # both hops of a two-hop exchange together
+B200_BETA_GBPS = 640.0                # NVLink payload bandwidth per direction, peer stores/loads
+B200_SELF_COPY_GBPS = 2550.0          # rows that stay on the GPU: read + write through HBM
+B200_SELF_OVERLAP_P = 1.5             # wire and local traffic overlap partly inside one kernel
+B200_X_HALF = 0.0
+B200_CHAIN_US_PER_ROW = 0.0           # no arrival chain: rows are stored at their final place
+B200_SPLITS_SYNC_MS = 0.0             # no host read-back
+B200_ALPHA_US = {"fast": B200_ALPHA_TWO_HOP_MS * 500.0, "slow": B200_ALPHA_TWO_HOP_MS * 500.0,
+                 "flat": B200_ALPHA_ONE_HOP_MS * 1000.0}
 
 
-def b200_nvswitch(R: int = 2, alpha_us: dict | None = None, beta_gbps: float | None = None,
-                  x_half: float | None = None, hop_overlap: float = 0.0,
+def b200_nvswitch(R: int = 2, alpha_one_ms: float = B200_ALPHA_ONE_HOP_MS,
+                  alpha_two_ms: float = B200_ALPHA_TWO_HOP_MS, beta_gbps: float = B200_BETA_GBPS,
+                  self_copy_gbps: float = B200_SELF_COPY_GBPS,
+                  self_overlap_p: float = B200_SELF_OVERLAP_P, hop_overlap: float = 0.0,
                   chain_us_per_row: float = B200_CHAIN_US_PER_ROW) -> ClusterSpec:
-    """8 x B200 behind one NVSwitch: the three levels share one port, so their bandwidths are
-    equal and groups are logical; what differs is the per-exchange fixed cost."""
-    a = dict(B200_ALPHA_US)
-    a.update(alpha_us or {})
-    beta = saturating_beta(beta_gbps or B200_BETA_GBPS, B200_X_HALF if x_half is None else x_half)
+    """8 x B200 behind one NVSwitch: the three levels share one port per GPU, so their
+    bandwidths are equal and groups are logical; what differs is the per-exchange fixed cost.
+    Rows whose destination is the sending GPU are priced as a local copy."""
+    beta = [(1.0, beta_gbps), (1e12, beta_gbps)]
 
-    def pts(us):
-        return [(2, us / 1000.0), (16, us / 1000.0)]
+    def pts(ms):
+        return [(1, ms), (16, ms)]
     return ClusterSpec(
         name="b200_nvswitch", R=R,
-        fast=Level("intra-group", pts(a["fast"]), beta),
-        slow=Level("inter-group", pts(a["slow"]), beta),
-        flat=Level("all ranks", pts(a["flat"]), beta),
+        fast=Level("intra-group", pts(alpha_two_ms / 2), beta),
+        slow=Level("inter-group", pts(alpha_two_ms / 2), beta),
+        flat=Level("all ranks", pts(alpha_one_ms), beta),
         splits_sync_ms=B200_SPLITS_SYNC_MS, chain_us_per_row=chain_us_per_row,
-        hop_overlap=hop_overlap)
+        hop_overlap=hop_overlap, self_copy_gbps=self_copy_gbps, self_overlap_p=self_overlap_p)
+
+
+def load_b200_sweep(path: str | None = None) -> list:
+    """Rows of the committed 8-GPU sweep (or of another sweep JSON written by ``bench/sweep.py``)."""
+    import json
+    import os
+    if path is None:
+        path = os.path.join(os.path.dirname(os.path.abspath(__file__)), "data",
+                            "b200_sweep_8gpu.json")
+    with open(path, encoding="utf-8") as fh:
+        return json.load(fh)["rows"]
+
+
+def _sweep_geometry(row: dict):
+    from .core import MoEGeometry
+    T = row["tokens"]
+    return MoEGeometry(name="sweep", n_groups=row["n_groups"], R=row["R"], k=row["k"], M=row["M"],
+                       H=row["hidden"], seq=T, mbs=1, gbs=row["n_groups"] * row["R"] * T)
+
+
+def b200_from_sweep(rows, overlap_p: float = B200_SELF_OVERLAP_P) -> ClusterSpec:
+    """Least-squares fit (relative error) of (alpha one-hop, alpha two-hop, beta, self-copy
+    bandwidth) to sweep rows with measured ``one_hop_ms`` / ``two_hop_ms`` (dispatch + combine =
+    two exchanges each).  Needs scipy."""
+    import numpy as np
+    from scipy.optimize import least_squares
+    from .core import one_hop_call, two_hop_call
+    geoms = [_sweep_geometry(r) for r in rows]
+    target = np.array([v for r in rows for v in (r["one_hop_ms"] / 2, r["two_hop_ms"] / 2)])
+
+    def predict(p):
+        c = b200_nvswitch(alpha_one_ms=p[0], alpha_two_ms=p[1], beta_gbps=p[2],
+                          self_copy_gbps=p[3], self_overlap_p=overlap_p)
+        return np.array([v for g in geoms for v in (one_hop_call(c, g), two_hop_call(c, g))])
+
+    sol = least_squares(lambda p: (predict(p) - target) / target, [0.04, 0.06, 650.0, 2500.0],
+                        bounds=([0.0, 0.0, 50.0, 100.0], [1.0, 1.0, 2000.0, 20000.0]))
+    a1, a2, beta, loc = (float(v) for v in sol.x)
+    return b200_nvswitch(alpha_one_ms=a1, alpha_two_ms=a2, beta_gbps=beta, self_copy_gbps=loc,
+                         self_overlap_p=overlap_p)
 
 
 def b200_from_records(records, R: int = 2) -> ClusterSpec:
-    """Fit the B200 platform from sweep records ``{frame, world, bytes, ms}`` with frames
-    ``fast`` / ``slow`` / ``flat`` (see ``sim.fit``): alpha pinned from the smallest message of
-    every frame, (beta_inf, x_half) fitted on the rest."""
+    """Fit the flat level from ``{frame, world, bytes, ms}`` records (frame ``flat``) with alpha
+    pinned at the smallest message; the two-hop levels inherit the bandwidth."""
     from . import fit
-    alpha_us = {}
-    betas, halves = [], []
-    for frame in ("fast", "slow", "flat"):
-        recs = [r for r in records if r["frame"] == frame]
-        if not recs:
-            continue
-        small = min(recs, key=lambda r: r["bytes"])
-        alpha_us[frame] = small["ms"] * 1000.0
-        res = fit.fit_beta_pinned(recs, lambda w, a=small["ms"]: a)
-        betas.append(res["beta_inf"])
-        halves.append(res["x_half"])
-    beta = sum(betas) / len(betas) if betas else None
-    x_half = sum(halves) / len(halves) if halves else None
-    return b200_nvswitch(R=R, alpha_us=alpha_us, beta_gbps=beta, x_half=x_half)
+    recs = [r for r in records if (r["frame"] if isinstance(r, dict) else r[0]) == "flat"]
+    if not recs:
+        return b200_nvswitch(R=R)
+    small = min(recs, key=lambda r: r["bytes"])
+    res = fit.fit_beta_pinned(recs, lambda w, a=small["ms"]: a)
+    return b200_nvswitch(R=R, alpha_one_ms=small["ms"], beta_gbps=res["beta_inf"])

@@ -69,6 +69,8 @@ class ClusterSpec:
     combine_exponent: float = 1.0       # p of (alpha^p + T^p)^(1/p); 1 = additive
     per_peer_us: float = 0.0            # explicit cost per peer message (replaces the beta curve)
     hop_overlap: float = 0.0            # 0 = hops strictly serial, 1 = fully overlapped
+    self_copy_gbps: float = 0.0         # > 0: rows that stay on the rank cost a local copy
+    self_overlap_p: float = 1.0         # wire and local copy combine as (w^p + l^p)^(1/p)
 
     def ratio(self) -> float:
         p = OPERATING_POINT_BYTES
@@ -130,14 +132,21 @@ class MoEGeometry:
 
 
 def _a2a_ms(level: Level, world: int, total_rows: float, row_bytes: int, self_fraction: float,
-            combine_exponent: float = 1.0, per_peer_us: float = 0.0) -> float:
+            combine_exponent: float = 1.0, per_peer_us: float = 0.0, self_copy_gbps: float = 0.0,
+            self_overlap_p: float = 1.0) -> float:
     wire_bytes = total_rows * (1.0 - self_fraction) * row_bytes
     peers = max(world - 1, 1)
     alpha = level.alpha_ms(world)
-    if per_peer_us > 0.0:
+    if wire_bytes <= 0.0:
+        transfer = 0.0
+    elif per_peer_us > 0.0:
         transfer = wire_bytes / (level.beta_gbps(1e12) * 1e6) + (world - 1) * per_peer_us / 1000.0
     else:
         transfer = wire_bytes / (level.beta_gbps(wire_bytes / peers) * 1e6)
+    if self_copy_gbps > 0.0:
+        local = total_rows * self_fraction * row_bytes / (self_copy_gbps * 1e6)
+        p = self_overlap_p
+        transfer = (transfer ** p + local ** p) ** (1.0 / p)
     if combine_exponent == 1.0:
         return alpha + transfer
     p = combine_exponent
@@ -146,7 +155,7 @@ def _a2a_ms(level: Level, world: int, total_rows: float, row_bytes: int, self_fr
 
 def one_hop_call(c: ClusterSpec, g: MoEGeometry) -> float:
     return _a2a_ms(c.flat, g.ep, g.rows_one_hop(), g.row_bytes(), 1.0 / g.ep,
-                   c.combine_exponent, c.per_peer_us)
+                   c.combine_exponent, c.per_peer_us, c.self_copy_gbps, c.self_overlap_p)
 
 
 def hop_a_self_fraction(g: MoEGeometry) -> float:
@@ -156,9 +165,9 @@ def hop_a_self_fraction(g: MoEGeometry) -> float:
 
 def two_hop_parts(c: ClusterSpec, g: MoEGeometry) -> dict:
     hop_a = _a2a_ms(c.slow, g.n_groups, g.rows_hop_a(), g.row_bytes(), hop_a_self_fraction(g),
-                    c.combine_exponent, c.per_peer_us)
+                    c.combine_exponent, c.per_peer_us, c.self_copy_gbps, c.self_overlap_p)
     hop_b = _a2a_ms(c.fast, g.R, g.rows_hop_b(), g.row_bytes(), 1.0 / g.R,
-                    c.combine_exponent, c.per_peer_us)
+                    c.combine_exponent, c.per_peer_us, c.self_copy_gbps, c.self_overlap_p)
     chain = c.chain_us_per_row * g.rows_hop_b() / 1000.0
     return {"hop_a": hop_a, "hop_b": hop_b, "splits": c.splits_sync_ms, "chain": chain}
 

@@ -8,7 +8,7 @@ import torch
 pytestmark = pytest.mark.gpu
 
 
-def _worker(rank, world, port, queue, M):
+def _worker(rank, world, port, queue, M, rpn=1):
     import torch.distributed as dist
     os.environ["MASTER_ADDR"] = "127.0.0.1"
     os.environ["MASTER_PORT"] = str(port)
@@ -24,7 +24,7 @@ def _worker(rank, world, port, queue, M):
         assert ops.custom_ops_enabled()
         dev = torch.device("cuda", rank)
         E, k, H, d, T = 16, 4, 256, 128, 1000 + 37 * rank
-        n_groups = max(world, 2) if world > 1 else 2
+        n_groups = max(world // rpn, 2)
         cfg = TRouteConfig(E, n_groups, k, M)
         g = torch.Generator().manual_seed(0)
         w13_all = (torch.randn(E, H, 2 * d, generator=g) * H ** -0.5).bfloat16()
@@ -35,7 +35,7 @@ def _worker(rank, world, port, queue, M):
         aff = torch.rand(T, E, generator=gx).to(dev)
         gy = torch.randn(T, H, generator=gx).bfloat16().to(dev)
         idx, gates0, _ = t_route(aff, torch.zeros(E, device=dev), cfg)
-        fctx = fz.FusedEPContext(cfg, H, d, 1200, world=world, rank=rank, rpn=1, device=dev)
+        fctx = fz.FusedEPContext(cfg, H, d, 1200, world=world, rank=rank, rpn=rpn, device=dev)
         res = {}
         modes = ["one_hop", "two_hop"] if world > 1 else ["one_hop"]
         for mode in modes + ["ref"]:
@@ -47,7 +47,7 @@ def _worker(rank, world, port, queue, M):
                 if world == 1:
                     y = ops.moe_experts_local(x, idx, gates, a, b, cfg.group_size)
                 else:
-                    y = ep_moe_forward(x, idx, gates, a, b, world, E, rpn=1)
+                    y = ep_moe_forward(x, idx, gates, a, b, world, E, rpn=rpn)
             else:
                 y = fz.fused_moe_forward(fctx, x, idx, gates, a, b, mode=mode)
             y.backward(gy)
@@ -63,11 +63,11 @@ def _worker(rank, world, port, queue, M):
         dist.destroy_process_group()
 
 
-def _run(world, M, port):
+def _run(world, M, port, rpn=1):
     import torch.multiprocessing as mp
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
-    procs = [ctx.Process(target=_worker, args=(r, world, port, q, M)) for r in range(world)]
+    procs = [ctx.Process(target=_worker, args=(r, world, port, q, M, rpn)) for r in range(world)]
     for p in procs:
         p.start()
     out = [q.get(timeout=600) for _ in range(world)]
@@ -99,6 +99,22 @@ def test_fused_world2_one_hop_two_hop(native_ops, M):
     if torch.cuda.device_count() < 2:
         pytest.skip("needs two GPUs")
     out = _run(2, M, 29703 + M)
+    for rank, res, echo, x0, status, live in out:
+        assert status == 0
+        assert live["two_hop_fwd"] == 1 and live["two_hop_bwd"] == 1
+        for a, b in zip(res["one_hop"], res["two_hop"]):
+            assert torch.equal(a, b), "one-hop and two-hop fused paths must agree bit for bit"
+        for a, b in zip(res["one_hop"], res["ref"]):
+            _close(a, b)
+        _close(echo, x0, 2e-2)
+
+
+@pytest.mark.parametrize("world,rpn,M", [(4, 2, 2), (8, 2, 2), (8, 4, 2)])
+def test_fused_groups_of_several_gpus(native_ops, world, rpn, M):
+    """Logical groups of R > 1 GPUs: Hop B really crosses GPUs inside the group."""
+    if torch.cuda.device_count() < world:
+        pytest.skip(f"needs {world} GPUs")
+    out = _run(world, M, 29720 + world + rpn, rpn=rpn)
     for rank, res, echo, x0, status, live in out:
         assert status == 0
         assert live["two_hop_fwd"] == 1 and live["two_hop_bwd"] == 1
