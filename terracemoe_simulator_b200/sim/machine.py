@@ -149,3 +149,22 @@ def min_expert_parallelism(model: MoEModel, accel: Accelerator, reserve_frac: fl
 
 def spans_multiple_domains(ep: int, domain_size: int) -> bool:
     return ep > domain_size
+
+
+def report() -> str:
+    """Plain-ASCII table of the accelerator records and the arrival-chain tiers."""
+    out = ["accelerators:"]
+    for acc in (ASCEND_910C, B200):
+        out.append(f"  {acc.name:<18s} hbm {acc.hbm_gbps:8.1f} GB/s  capacity {acc.hbm_capacity_gb:6.1f} GB"
+                   f"  launch {acc.launch_ms * 1e3:5.1f} us")
+    out.append(f"arrival chain at the reference point ({CHAIN_REFERENCE_PAIRS} pairs):")
+    for H in sorted(CHAIN_H_SWEEP_MS):
+        cells = "  ".join(f"{t.name.split(' ')[0]:>8s} {t.ms(CHAIN_H_SWEEP_PAIRS, H, ASCEND_910C):6.3f} ms"
+                          for t in TIERS)
+        out.append(f"  H={H:<5d} measured {CHAIN_H_SWEEP_MS[H]:5.2f} ms   {cells}")
+    out.append(f"index cost {INDEX_NS_PER_ROW:.1f} ns/row, gather {GATHER_GBPS_MEASURED:.0f} GB/s")
+    return "\n".join(out)
+
+
+if __name__ == "__main__":
+    print(report())

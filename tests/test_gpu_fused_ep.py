@@ -17,50 +17,61 @@ def _worker(rank, world, port, queue, M, rpn=1):
     dist.init_process_group("nccl", rank=rank, world_size=world,
                             device_id=torch.device("cuda", rank))
     try:
-        from terracemoe_simulator_b200 import ops
-        from terracemoe_simulator_b200.parallel import fused as fz
-        from terracemoe_simulator_b200.parallel.ep import ep_moe_forward
-        from terracemoe_simulator_b200.routing import TRouteConfig, t_route
-        assert ops.custom_ops_enabled()
-        dev = torch.device("cuda", rank)
-        E, k, H, d, T = 16, 4, 256, 128, 1000 + 37 * rank
-        n_groups = max(world // rpn, 2)
-        cfg = TRouteConfig(E, n_groups, k, M)
-        g = torch.Generator().manual_seed(0)
-        w13_all = (torch.randn(E, H, 2 * d, generator=g) * H ** -0.5).bfloat16()
-        w2_all = (torch.randn(E, d, H, generator=g) * d ** -0.5).bfloat16()
-        epr = E // world
-        gx = torch.Generator().manual_seed(10 + rank)
-        x0 = torch.randn(T, H, generator=gx).bfloat16().to(dev)
-        aff = torch.rand(T, E, generator=gx).to(dev)
-        gy = torch.randn(T, H, generator=gx).bfloat16().to(dev)
-        idx, gates0, _ = t_route(aff, torch.zeros(E, device=dev), cfg)
-        fctx = fz.FusedEPContext(cfg, H, d, 1200, world=world, rank=rank, rpn=rpn, device=dev)
-        res = {}
-        modes = ["one_hop", "two_hop"] if world > 1 else ["one_hop"]
-        for mode in modes + ["ref"]:
-            x = x0.clone().requires_grad_(True)
-            gates = gates0.clone().requires_grad_(True)
-            a = w13_all[rank * epr:(rank + 1) * epr].to(dev).requires_grad_(True)
-            b = w2_all[rank * epr:(rank + 1) * epr].to(dev).requires_grad_(True)
-            if mode == "ref":
-                if world == 1:
-                    y = ops.moe_experts_local(x, idx, gates, a, b, cfg.group_size)
-                else:
-                    y = ep_moe_forward(x, idx, gates, a, b, world, E, rpn=rpn)
-            else:
-                y = fz.fused_moe_forward(fctx, x, idx, gates, a, b, mode=mode)
-            y.backward(gy)
-            torch.cuda.synchronize()
-            res[mode] = [t.detach().float().cpu() for t in (y, x.grad, gates.grad, a.grad, b.grad)]
-        echo = fz.fused_dispatch_combine(fctx, x0, idx, gates0, mode=modes[-1])
-        torch.cuda.synchronize()
-        status = fctx.take_status() or ops.take_status(rank)
-        queue.put((rank, res, echo.float().cpu(), x0.float().cpu(), status,
-                   dict(fz.LIVE)))
+        _body(rank, world, queue, M, rpn)
         dist.barrier()
+    except Exception as exc:  # noqa: BLE001  (the parent must hear of it instead of waiting)
+        import traceback
+        queue.put((rank, "error", f"{type(exc).__name__}: {exc}\n{traceback.format_exc()}"))
     finally:
         dist.destroy_process_group()
+
+
+CAPACITY = 1400          # rows per rank the arena is sized for; every rank's T stays below it
+
+
+def _body(rank, world, queue, M, rpn):
+    from terracemoe_simulator_b200 import ops
+    from terracemoe_simulator_b200.parallel import fused as fz
+    from terracemoe_simulator_b200.parallel.ep import ep_moe_forward
+    from terracemoe_simulator_b200.routing import TRouteConfig, t_route
+    assert ops.custom_ops_enabled()
+    dev = torch.device("cuda", rank)
+    E, k, H, d, T = 16, 4, 256, 128, 1000 + 37 * rank
+    n_groups = max(world // rpn, 2)
+    cfg = TRouteConfig(E, n_groups, k, M)
+    g = torch.Generator().manual_seed(0)
+    w13_all = (torch.randn(E, H, 2 * d, generator=g) * H ** -0.5).bfloat16()
+    w2_all = (torch.randn(E, d, H, generator=g) * d ** -0.5).bfloat16()
+    epr = E // world
+    gx = torch.Generator().manual_seed(10 + rank)
+    x0 = torch.randn(T, H, generator=gx).bfloat16().to(dev)
+    aff = torch.rand(T, E, generator=gx).to(dev)
+    gy = torch.randn(T, H, generator=gx).bfloat16().to(dev)
+    idx, gates0, _ = t_route(aff, torch.zeros(E, device=dev), cfg)
+    assert 1000 + 37 * (world - 1) <= CAPACITY
+    fctx = fz.FusedEPContext(cfg, H, d, CAPACITY, world=world, rank=rank, rpn=rpn, device=dev)
+    res = {}
+    modes = ["one_hop", "two_hop"] if world > 1 else ["one_hop"]
+    for mode in modes + ["ref"]:
+        x = x0.clone().requires_grad_(True)
+        gates = gates0.clone().requires_grad_(True)
+        a = w13_all[rank * epr:(rank + 1) * epr].to(dev).requires_grad_(True)
+        b = w2_all[rank * epr:(rank + 1) * epr].to(dev).requires_grad_(True)
+        if mode == "ref":
+            if world == 1:
+                y = ops.moe_experts_local(x, idx, gates, a, b, cfg.group_size)
+            else:
+                y = ep_moe_forward(x, idx, gates, a, b, world, E, rpn=rpn)
+        else:
+            y = fz.fused_moe_forward(fctx, x, idx, gates, a, b, mode=mode)
+        y.backward(gy)
+        torch.cuda.synchronize()
+        res[mode] = [t.detach().float().cpu() for t in (y, x.grad, gates.grad, a.grad, b.grad)]
+    echo = fz.fused_dispatch_combine(fctx, x0, idx, gates0, mode=modes[-1])
+    torch.cuda.synchronize()
+    status = fctx.take_status() or ops.take_status(rank)
+    queue.put((rank, res, echo.float().cpu(), x0.float().cpu(), status,
+               dict(fz.LIVE)))
 
 
 def _run(world, M, port, rpn=1):
@@ -70,9 +81,22 @@ def _run(world, M, port, rpn=1):
     procs = [ctx.Process(target=_worker, args=(r, world, port, q, M, rpn)) for r in range(world)]
     for p in procs:
         p.start()
-    out = [q.get(timeout=600) for _ in range(world)]
-    for p in procs:
-        p.join(timeout=120)
+    out, failed = [], None
+    try:
+        for _ in range(world):
+            item = q.get(timeout=300)
+            if item[1] == "error":
+                failed = item
+                break
+            out.append(item)
+    finally:
+        for p in procs:
+            p.join(timeout=30 if failed is None else 10)
+        for p in procs:
+            if p.is_alive():
+                p.terminate()
+    if failed is not None:
+        raise AssertionError(f"rank {failed[0]} failed: {failed[2]}")
     return sorted(out, key=lambda t: t[0])
 
 
