@@ -1,0 +1,117 @@
+"""Probe scripts run under gloo; figure generator is reproducible; one-sided verdict rules."""
+import json
+import os
+import subprocess
+import sys
+import xml.dom.minidom
+
+import pytest
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+PKG = "terracemoe_simulator_b200"
+
+
+def _torchrun(nproc, port, module, args):
+    env = dict(os.environ, PYTHONPATH=ROOT, OMP_NUM_THREADS="1")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={nproc}",
+           "--master-addr", "127.0.0.1", "--master-port", str(port), "-m", f"{PKG}.bench.{module}"]
+    proc = subprocess.run(cmd + args, capture_output=True, env=env, cwd=ROOT, timeout=600)
+    assert proc.returncode == 0, proc.stderr.decode(errors="replace")[-3000:]
+    return proc.stdout.decode()
+
+
+def test_a2a_form_probe_both_styles(tmp_path):
+    out = tmp_path / "form.json"
+    _torchrun(2, 29801, "a2a_form_probe", ["--cpu", "--sizes-mib", "0.0625", "0.25", "--repeats", "2",
+                                           "--burst-n", "3", "--percall-n", "3", "--out", str(out)])
+    data = json.loads(out.read_text())
+    assert data["world"] == 2 and len(data["rows"]) == 2
+    assert {r["frame"] for r in data["records"]} == {"burst", "percall"}
+    assert all(r["burst_ms"] > 0 and r["percall_ms"] > 0 for r in data["rows"])
+    assert set(data["records"][0]) == {"frame", "world", "bytes", "ms"}     # the fitting schema
+
+
+def test_twohop_verdict_phases(tmp_path):
+    out = tmp_path / "verdict.json"
+    text = _torchrun(4, 29802, "twohop_verdict", ["--cpu", "--rpn", "2", "--tokens", "64", "--hidden",
+                                                  "32", "--repeats", "1", "--calls", "2", "--out",
+                                                  str(out)])
+    rows = json.loads(out.read_text())["rows"]
+    assert [(r["M"], r["q"]) for r in rows] == [(1, 6), (2, 3)]
+    for r in rows:
+        parts = r["hop_a_ms"] + r["chain_ms"] + r["hop_b_ms"] + r["splits_ms"]
+        assert abs(parts - r["two_hop_ms"]) < 1e-9 and r["G"] > 0
+    assert "two-hop" in text
+
+
+def test_fabric_probes(tmp_path):
+    a, b = tmp_path / "c.json", tmp_path / "p.json"
+    _torchrun(4, 29803, "fabric_contention", ["--cpu", "--sizes-mib", "0.125", "--repeats", "1",
+                                              "--calls", "2", "--out", str(a)])
+    _torchrun(4, 29804, "fabric_peers", ["--cpu", "--sizes-mib", "0.125", "--repeats", "1",
+                                         "--calls", "2", "--out", str(b)])
+    cont = json.loads(a.read_text())
+    assert [r["active_pairs"] for r in cont["rows"] if r["phase"] == "pairs"] == [1, 2]
+    assert cont["rows"][-1]["phase"] == "global" and cont["worst_slowdown"] >= 1.0
+    peers = json.loads(b.read_text())
+    assert [r["peers"] for r in peers["rows"] if r["phase"] == "peers"] == [1, 2]
+
+
+def test_peer_splits_are_a_permutation():
+    from terracemoe_simulator_b200.bench.fabric_peers import peer_splits
+    world, n, chunk = 8, 3, 5
+    send = [peer_splits(r, world, n, chunk)[0] for r in range(world)]
+    recv = [peer_splits(r, world, n, chunk)[1] for r in range(world)]
+    for r in range(world):
+        assert sum(send[r]) == n * chunk == sum(recv[r])
+        assert all(send[r][p] == 0 for p in range(world) if (p < 4) == (r < 4))   # only across
+        for p in range(world):
+            assert send[r][p] == recv[p][r]
+
+
+def test_chain_probes_on_cpu(tmp_path):
+    from terracemoe_simulator_b200.bench import chain_live_vs_ref, chain_sweep
+    assert chain_live_vs_ref.main(["--tokens", "64", "--hidden", "32", "--calls", "2", "--cpu"]) == 0
+    out = tmp_path / "chain.json"
+    assert chain_sweep.main(["--out", str(out), "--pairs", "600", "1200", "2400", "--hidden", "32",
+                             "--calls", "2", "--cpu"]) == 0
+    data = json.loads(out.read_text())
+    assert len(data["rows"]) == 3 and "32" in data["fit_ref"]
+    fixed, per = chain_sweep.line_fit([1, 2, 3], [3.0, 5.0, 7.0])
+    assert abs(fixed - 1.0) < 1e-9 and abs(per - 2.0) < 1e-9
+
+
+def test_onesided_verdict_rules():
+    from terracemoe_simulator_b200.bench.onesided_vs_collective import verdict
+    rows = [{"collective_ms": 0.05, "one_sided_ms": 0.01},      # launch floor: not counted
+            {"collective_ms": 0.20, "one_sided_ms": 0.16},
+            {"collective_ms": 0.40, "one_sided_ms": 0.30}]
+    v = verdict(rows)
+    assert v["counted"] == 2 and v["adopt_one_sided"] and 1.25 <= v["median_speedup"] <= 1.34
+    assert not verdict(rows, criterion=1.5)["adopt_one_sided"]
+    assert verdict(rows[:1])["counted"] == 0 and not verdict([])["adopt_one_sided"]
+
+
+def test_figures_reproducible_and_wellformed(tmp_path):
+    from terracemoe_simulator_b200.tools import gen_figures
+    first = gen_figures.generate(str(tmp_path / "a"))
+    second = gen_figures.generate(str(tmp_path / "b"))
+    assert len(first) == len(gen_figures.FIGURES) >= 13
+    for pa, pb in zip(first, second):
+        ta, tb = open(pa).read(), open(pb).read()
+        assert ta == tb and "nan" not in ta
+        xml.dom.minidom.parseString(ta)
+    only = gen_figures.generate(str(tmp_path / "c"), only=["f8", "f17"])
+    assert [os.path.basename(p) for p in only] == ["f8-breakeven-map.svg", "f17-b200-ratio.svg"]
+
+
+def test_traffic_helpers():
+    import torch
+    from terracemoe_simulator_b200.bench import traffic
+    from terracemoe_simulator_b200.routing import TRouteConfig
+    cfg = TRouteConfig(16, 4, 4, 2)
+    group_idx = torch.tensor([[0, 1], [1, 2], [0, 3]])
+    src = torch.tensor([0, 2, 5])
+    m = traffic.dispatch_traffic(group_idx, src, cfg, cards_per_group=2)
+    assert m.shape == (4, 4) and int(m.sum()) == 6
+    assert traffic.uniformity_cv(torch.ones(4, 4)) == pytest.approx(0.0)
