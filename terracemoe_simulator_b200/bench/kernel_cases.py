@@ -48,6 +48,9 @@ def main(argv=None) -> int:
     ap.add_argument("case", choices=CASES)
     ap.add_argument("--iters", type=int, default=3)
     ap.add_argument("--full", action="store_true")
+    ap.add_argument("--pad", type=int, default=0,
+                    help="declare the groups padded to this multiple (64 lets the weight-gradient "
+                         "GEMM use CTA pairs)")
     args = ap.parse_args(argv)
     from terracemoe_simulator_b200 import ops
     if not ops.custom_ops_enabled():
@@ -68,17 +71,17 @@ def main(argv=None) -> int:
         X = torch.randn(rows, H, device=dev, dtype=bf)
         W = torch.randn(E, H, 2 * d, device=dev, dtype=bf) * H ** -0.5
         epi = 1 if args.case == "gemm_swiglu" else 0
-        fn = lambda: lib.grouped_gemm(X, W, st, cnt, 0, epi, epi == 1, 0)
+        fn = lambda: lib.grouped_gemm(X, W, st, cnt, 0, epi, epi == 1, 0, args.pad)
         flops = 2 * rows * H * 2 * d
     elif args.case == "gemm_dgrad":
         dY = torch.randn(rows, 2 * d, device=dev, dtype=bf)
         W = torch.randn(E, H, 2 * d, device=dev, dtype=bf) * H ** -0.5
-        fn = lambda: lib.grouped_gemm(dY, W, st, cnt, 1, 0, False, 0)
+        fn = lambda: lib.grouped_gemm(dY, W, st, cnt, 1, 0, False, 0, args.pad)
         flops = 2 * rows * H * 2 * d
     elif args.case == "gemm_wgrad":
         X = torch.randn(rows, H, device=dev, dtype=bf)
         dY = torch.randn(rows, 2 * d, device=dev, dtype=bf)
-        fn = lambda: lib.grouped_wgrad(X, dY, st, cnt, 0)
+        fn = lambda: lib.grouped_wgrad(X, dY, st, cnt, 0, args.pad)
         flops = 2 * rows * H * 2 * d
     elif args.case == "rmsnorm":
         x = torch.randn(rows * 2, H, device=dev, dtype=bf)
@@ -107,7 +110,8 @@ def main(argv=None) -> int:
         fn = lambda: lib.swiglu_bwd(h13, dact)
         bytes_ = rows * d * 2 * 5
     ms = _time(fn, args.iters)
-    line = {"case": args.case, "full": args.full, "ms": round(ms, 4)}
+    line = {"case": args.case, "full": args.full, "pad": args.pad,
+            "pair_policy": os.environ.get("TERRACE_GEMM_PAIR", "auto"), "ms": round(ms, 4)}
     if flops:
         line["tflops"] = round(flops / ms / 1e9, 1)
         line["frac_of_bf16_peak"] = round(flops / ms / 1e9 / tf, 3)

@@ -1,0 +1,163 @@
+"""End-to-end decoder training step: tokens/s through the public model API.
+
+    python -m terracemoe_simulator_b200.bench.train_step [--steps 5 --warmup 3]
+    python -m torch.distributed.run --nproc-per-node 8 \
+        -m terracemoe_simulator_b200.bench.train_step --ep two_hop --rpn 2
+
+Default shape: 16-layer decoder, d_model 2048, 16 heads, 64 SwiGLU experts of hidden 1024 per MoE
+layer (every layer between a dense first and a dense last layer), top-4 in 2 of 4 routing groups,
+one shared expert, 8 sequences of 4096 tokens per GPU, bf16 parameters, AdamW.  One step =
+pinned host -> device copy of the token batch, forward, loss, backward, gradient average of the
+replicated parameters over the ranks, optimizer step, device -> host read of the loss.  With N
+ranks the routed experts are sharded N ways (``--ep one_hop | two_hop``, fused peer-memory
+kernels unless ``--nccl``) and every rank trains on its own sequences (weak scaling).
+
+Timing: W warm-up steps, K timed steps between CUDA events bracketed by barrier + synchronize,
+max over ranks.  Prints one JSON line on rank 0.  The reference has no such loop on GPUs; its
+only training step is the CPU toy in ``tests/test_checkpoint.py:16-23``.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import sys
+import time
+
+import torch
+import torch.distributed as dist
+
+
+def build_args(ns, world: int):
+    from ..models import ModelArgs
+    return ModelArgs(vocab=ns.vocab, dim=ns.dim, n_layers=ns.layers, n_heads=ns.heads,
+                     seq_len=ns.seq, n_experts=ns.experts, n_groups=ns.groups, top_k=ns.top_k,
+                     top_groups=ns.top_groups, d_expert=ns.d_expert, d_shared=ns.d_shared,
+                     n_shared=1, dense_first=1, expert_backend=ns.backend,
+                     ep_mode=ns.ep if world > 1 else "local", ep_rpn=ns.rpn,
+                     ep_fused=not ns.nccl)
+
+
+def main(argv=None) -> int:
+    ap = argparse.ArgumentParser(description=__doc__.split("\n")[0])
+    ap.add_argument("--steps", type=int, default=5)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--layers", type=int, default=16)
+    ap.add_argument("--dim", type=int, default=2048)
+    ap.add_argument("--heads", type=int, default=16)
+    ap.add_argument("--experts", type=int, default=64)
+    ap.add_argument("--d-expert", type=int, default=1024)
+    ap.add_argument("--d-shared", type=int, default=1024)
+    ap.add_argument("--groups", type=int, default=4)
+    ap.add_argument("--top-k", type=int, default=4)
+    ap.add_argument("--top-groups", type=int, default=2)
+    ap.add_argument("--seq", type=int, default=4096)
+    ap.add_argument("--batch", type=int, default=8, help="sequences per GPU")
+    ap.add_argument("--vocab", type=int, default=32000)
+    ap.add_argument("--ep", default="two_hop", choices=["one_hop", "two_hop"])
+    ap.add_argument("--rpn", type=int, default=1)
+    ap.add_argument("--nccl", action="store_true", help="all_to_all arm instead of fused kernels")
+    ap.add_argument("--backend", default="native", choices=["native", "grouped", "loop"])
+    ap.add_argument("--dtype", default="bf16", choices=["bf16", "fp32"])
+    ap.add_argument("--cpu", action="store_true")
+    ap.add_argument("--lr", type=float, default=3e-4)
+    ns = ap.parse_args(argv)
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    cuda = torch.cuda.is_available() and not ns.cpu
+    os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+    os.environ.setdefault("MASTER_PORT", "29541")
+    if cuda:
+        torch.cuda.set_device(local)
+        device = torch.device("cuda", local)
+    else:
+        device = torch.device("cpu")
+    if world > 1:
+        if cuda:
+            dist.init_process_group("nccl", rank=rank, world_size=world, device_id=device)
+        else:
+            dist.init_process_group("gloo", rank=rank, world_size=world)
+    from ..models import TerraceLM
+    from ..parallel.dp import DPGradSync
+    dtype = torch.bfloat16 if ns.dtype == "bf16" else torch.float32
+    torch.manual_seed(1234)                      # replicated parameters start identical
+    model = TerraceLM(build_args(ns, world)).to(device=device, dtype=dtype)
+    if world > 1:                                # expert shards differ per rank
+        g = torch.Generator(device="cpu").manual_seed(99 + rank)
+        for name, p in model.named_parameters():
+            if name.endswith((".w13", ".w2")) and "ffn" in name and p.dim() == 3:
+                with torch.no_grad():
+                    p.copy_((torch.randn(p.shape, generator=g) * p.shape[1] ** -0.5).to(p))
+    sync = DPGradSync(model)
+    opt = torch.optim.AdamW(model.parameters(), lr=ns.lr, weight_decay=0.1,
+                            fused=True if cuda else None)
+    gtok = torch.Generator(device="cpu").manual_seed(7 + rank)
+    n_host = 4
+    host = [torch.randint(0, ns.vocab, (ns.batch, ns.seq + 1), generator=gtok) for _ in range(n_host)]
+    if cuda:
+        host = [h.pin_memory() for h in host]
+    model.train()
+    state = {"i": 0, "loss": 0.0}
+
+    def step():
+        tok = host[state["i"] % n_host].to(device, non_blocking=True)
+        state["i"] += 1
+        opt.zero_grad(set_to_none=True)
+        loss, _ = model(tok[:, :-1], tok[:, 1:])
+        loss.backward()
+        sync.sync()
+        opt.step()
+        state["loss"] = loss.item()              # device -> host read of the result
+
+    def barrier():
+        if cuda:
+            torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        if cuda:
+            torch.cuda.synchronize()
+
+    for _ in range(ns.warmup):
+        step()
+    barrier()
+    if cuda:
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+    t0 = time.perf_counter()
+    for _ in range(ns.steps):
+        step()
+    if cuda:
+        b.record()
+    barrier()
+    ms = a.elapsed_time(b) if cuda else (time.perf_counter() - t0) * 1e3
+    t = torch.tensor([ms], device=device)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms = t.item() / ns.steps
+    tokens = ns.batch * ns.seq * world
+    status = 0
+    if cuda:
+        from .. import ops
+        status = ops.take_status(local) if ops.custom_ops_enabled() else -1
+    out = {"metric": "train_tokens_per_s", "value": tokens / (ms * 1e-3), "unit": "tokens/s",
+           "n_gpus": world, "steps": ns.steps, "warmup": ns.warmup, "ms_per_step": ms,
+           "loss": state["loss"], "dtype": ns.dtype, "data": "synthetic", "scaling": "weak",
+           "n_params": model.n_params(), "dp_allreduce_calls": sync.calls, "status": status,
+           "config": {"model": f"decoder L{ns.layers} d{ns.dim} h{ns.heads} E{ns.experts}x{ns.d_expert} "
+                               f"top{ns.top_k} M{ns.top_groups}", "global_batch": ns.batch * world,
+                      "seq_len": ns.seq, "parallelism": f"ep{world}+dp{world}" if world > 1 else "single",
+                      "ep_mode": ns.ep if world > 1 else "local", "rpn": ns.rpn,
+                      "transport": "nccl" if ns.nccl else "fused", "optimizer": "AdamW",
+                      "h2d_bytes_per_step": ns.batch * (ns.seq + 1) * 8, "d2h_bytes_per_step": 4}}
+    if rank == 0:
+        print(json.dumps(out), flush=True)
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -316,3 +316,37 @@ def test_padded_segments_gemm_and_wgrad(native_ops):
         _close(dW[g], X[a:b].float().t() @ dY[a:b].float())
     assert torch.isfinite(dW.float()).all()
     assert native_ops.take_status() == 0
+
+
+def test_gemm_cta_pair_variant_in_subprocess(native_ops):
+    """The pair policy is read once per process, so the cta_group::2 variants of every GEMM test
+    run in a child process with TERRACE_GEMM_PAIR=1 (the default policy only pairs long groups)."""
+    import os
+    import subprocess
+    import sys
+    if os.environ.get("TERRACE_GEMM_PAIR") == "1":
+        pytest.skip("already inside the pair run")
+    env = dict(os.environ, TERRACE_GEMM_PAIR="1")
+    proc = subprocess.run([sys.executable, "-m", "pytest", os.path.abspath(__file__), "-q", "-x", "-k",
+                           "grouped or swiglu or padded or linear or moe_experts or long_groups"],
+                          env=env, capture_output=True, timeout=900)
+    assert proc.returncode == 0, proc.stdout.decode()[-3000:] + proc.stderr.decode()[-2000:]
+
+
+def test_long_groups_use_pairs_by_default(native_ops):
+    """Groups of 1024+ rows take the 256-row pair tiles under the default policy."""
+    torch.manual_seed(1)
+    counts, K, N = [1100, 1300, 1024, 2048], 512, 640
+    G, rows = len(counts), sum(counts)
+    A = torch.randn(rows, K, device=DEV, dtype=torch.bfloat16)
+    B = (torch.randn(G, K, N, device=DEV) * K ** -0.5).bfloat16()
+    s, c = _segs(counts)
+    C, _ = torch.ops.terrace.grouped_gemm(A, B, s, c, 0, 0, False, 0)
+    Ct, _ = torch.ops.terrace.grouped_gemm(A, B.transpose(1, 2).contiguous(), s, c, 1, 0, False, 0)
+    off = 0
+    for g, n in enumerate(counts):
+        ref = A[off:off + n].float() @ B[g].float()
+        _close(C[off:off + n], ref)
+        _close(Ct[off:off + n], ref)
+        off += n
+    assert native_ops.take_status() == 0
