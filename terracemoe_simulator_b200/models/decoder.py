@@ -82,10 +82,6 @@ class Attention(nn.Module):
         from .. import ops
         B, T, D = x.shape
         native = x.is_cuda and ops.custom_ops_enabled()
-        if native and ops.attention_supported(x, self.nh):
-            qkv = ops.linear(x.reshape(B * T, D), self.wqkv.weight)
-            o = ops.causal_attention_rope(qkv.view(B, T, 3, self.nh, self.hd), cos, sin)
-            return ops.linear(o.reshape(B * T, D), self.wo.weight).view(B, T, D)
         proj = native and ops.dense_supported(x, self.wqkv.weight)
         qkv = ops.linear(x, self.wqkv.weight) if proj else self.wqkv(x)
         q, k, v = qkv.chunk(3, dim=-1)
@@ -94,7 +90,10 @@ class Attention(nn.Module):
         v = v.view(B, T, self.nh, self.hd).transpose(1, 2)
         q = _rope(q, cos, sin).to(v.dtype)
         k = _rope(k, cos, sin).to(v.dtype)
-        o = F.scaled_dot_product_attention(q, k, v, is_causal=True)
+        if native and ops.attention_supported(x, self.nh):
+            o = ops.attention(q, k, v, causal=True)      # tcgen05 flash attention, fwd and bwd
+        else:
+            o = F.scaled_dot_product_attention(q, k, v, is_causal=True)
         o = o.transpose(1, 2).reshape(B, T, D)
         return ops.linear(o, self.wo.weight) if proj else self.wo(o)
 

@@ -298,7 +298,7 @@ def k2_pack(hidden, expert_idx, gates, world: int, n_experts: int, rpn: int, gro
 # compute kernels (wrappers live in native.py; they import lazily so CPU-only use stays light)
 # ---------------------------------------------------------------------------------------------
 from .native import (  # noqa: E402
-    attention_supported, causal_attention_rope, dense_supported, fused_route, grouped_mm_native,
+    attention, attention_shape_supported, attention_supported, dense_supported, fused_route, grouped_mm_native,
     grouped_supported, linear, moe_experts_local, moe_local_supported, rmsnorm, rmsnorm_supported,
     route_from_logits, router_supported, segments_from_counts, swiglu_ffn, take_status)
 
@@ -307,5 +307,5 @@ __all__ = [
     "TerracePassthroughFn", "k1_arrival", "k1_arrival_ref", "k1_arrival_segment",
     "TerraceK1ArrivalFn", "k2_pack", "k2_pack_ref", "fixed_hist", "stable_bucket_order",
     "rmsnorm", "fused_route", "linear", "swiglu_ffn", "grouped_mm_native", "moe_experts_local",
-    "causal_attention_rope", "OP_CALLS",
+    "attention", "OP_CALLS",
 ]

@@ -434,6 +434,61 @@ Tensor grouped_wgrad(const Tensor& X, const Tensor& dY, const Tensor& seg_start,
 
 }  // namespace
 
+// ---------------------------------------------------------------------------------------------
+// attention: q, k, v [B, H, S, D] (or [BH, S, D]) bf16 contiguous
+std::tuple<Tensor, Tensor> attn_fwd(const Tensor& q, const Tensor& k, const Tensor& v, bool causal,
+                                    double scale) {
+  CHECK_CUDA_CONTIG(q);
+  CHECK_CUDA_CONTIG(k);
+  CHECK_CUDA_CONTIG(v);
+  TORCH_CHECK(q.scalar_type() == at::kBFloat16 && k.scalar_type() == at::kBFloat16 &&
+                  v.scalar_type() == at::kBFloat16, "attn_fwd: bf16 operands");
+  TORCH_CHECK(q.dim() >= 3 && q.sizes() == k.sizes() && q.sizes() == v.sizes(),
+              "attn_fwd: q, k, v of one shape [..., S, D]");
+  c10::cuda::CUDAGuard guard(q.device());
+  const int64_t D = q.size(-1), S = q.size(-2), BH = q.numel() / (S * D);
+  TORCH_CHECK(S % 128 == 0 && (D == 64 || D == 128), "attn_fwd: S % 128 == 0 and D in {64, 128}");
+  Tensor o = at::empty_like(q);
+  auto lse_shape = q.sizes().vec();
+  lse_shape.pop_back();
+  Tensor lse = at::empty(lse_shape, q.options().dtype(at::kFloat));
+  check_rc(tb200_attn_fwd(q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(),
+                          lse.data_ptr<float>(), static_cast<int>(BH), static_cast<int>(S),
+                          static_cast<int>(D), causal ? 1 : 0, static_cast<float>(scale),
+                          status_ptr(q), cur_stream()),
+           "attn_fwd");
+  return {o, lse};
+}
+
+std::tuple<Tensor, Tensor, Tensor> attn_bwd(const Tensor& q, const Tensor& k, const Tensor& v,
+                                            const Tensor& o, const Tensor& d_o, const Tensor& lse,
+                                            bool causal, double scale) {
+  CHECK_CUDA_CONTIG(q);
+  CHECK_CUDA_CONTIG(k);
+  CHECK_CUDA_CONTIG(v);
+  CHECK_CUDA_CONTIG(o);
+  CHECK_CUDA_CONTIG(d_o);
+  CHECK_CUDA_CONTIG(lse);
+  TORCH_CHECK(q.scalar_type() == at::kBFloat16 && d_o.scalar_type() == at::kBFloat16 &&
+                  o.scalar_type() == at::kBFloat16 && lse.scalar_type() == at::kFloat,
+              "attn_bwd: bf16 tensors and an fp32 lse");
+  TORCH_CHECK(q.sizes() == k.sizes() && q.sizes() == v.sizes() && q.sizes() == o.sizes() &&
+                  q.sizes() == d_o.sizes(), "attn_bwd: shape mismatch");
+  c10::cuda::CUDAGuard guard(q.device());
+  const int64_t D = q.size(-1), S = q.size(-2), BH = q.numel() / (S * D);
+  TORCH_CHECK(lse.numel() == BH * S, "attn_bwd: lse must be [..., S]");
+  TORCH_CHECK(S % 128 == 0 && (D == 64 || D == 128), "attn_bwd: S % 128 == 0 and D in {64, 128}");
+  Tensor dq = at::empty_like(q), dk = at::empty_like(q), dv = at::empty_like(q);
+  Tensor delta = at::empty_like(lse);
+  check_rc(tb200_attn_bwd(q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), d_o.data_ptr(),
+                          lse.data_ptr<float>(), delta.data_ptr<float>(), dq.data_ptr(),
+                          dk.data_ptr(), dv.data_ptr(), static_cast<int>(BH), static_cast<int>(S),
+                          static_cast<int>(D), causal ? 1 : 0, static_cast<float>(scale),
+                          status_ptr(q), cur_stream()),
+           "attn_bwd");
+  return {dq, dk, dv};
+}
+
 TORCH_LIBRARY(terrace, m) {
   m.def("passthrough(Tensor x) -> Tensor");
   m.def("k1_arrival(Tensor rx, Tensor rslot, Tensor rgate, int quota, int epr, int rpn, "
@@ -463,6 +518,10 @@ TORCH_LIBRARY(terrace, m) {
         "int pad_align=0) -> Tensor", &grouped_wgrad);
   m.def("zero_pad_rows(Tensor(a!) buf, Tensor seg_start, Tensor seg_count, int align) -> ()",
         &zero_pad_rows);
+  m.def("attn_fwd(Tensor q, Tensor k, Tensor v, bool causal, float scale) -> (Tensor, Tensor)",
+        &attn_fwd);
+  m.def("attn_bwd(Tensor q, Tensor k, Tensor v, Tensor o, Tensor d_o, Tensor lse, bool causal, "
+        "float scale) -> (Tensor, Tensor, Tensor)", &attn_bwd);
   terrace_b200_register_symm(m);
 }
 

@@ -40,6 +40,16 @@ int tb200_grouped_wgrad(const void* X, const void* dY, void* dW, const int* seg_
 int tb200_zero_pad_rows(void* buf, const int* seg_start, const int* seg_count, int n_groups,
                         int align, int row_bytes, long long buf_rows, cudaStream_t stream);
 
+// ---- attention_sm100.cu ----------------------------------------------------------------------
+// Self-attention over q, k, v [BH, S, D] bf16 contiguous (S a multiple of 128, D 64 or 128):
+// o = softmax(scale * q k^T (+ causal mask)) v, lse[BH, S] = log-sum-exp of the scaled scores.
+int tb200_attn_fwd(const void* q, const void* k, const void* v, void* o, float* lse, int BH,
+                   int S, int D, int causal, float scale, int* status, cudaStream_t stream);
+// Gradients dq, dk, dv [BH, S, D] from d_o; `delta` is [BH, S] fp32 scratch (rowsum(d_o * o)).
+int tb200_attn_bwd(const void* q, const void* k, const void* v, const void* o, const void* d_o,
+                   const float* lse, float* delta, void* dq, void* dk, void* dv, int BH, int S,
+                   int D, int causal, float scale, int* status, cudaStream_t stream);
+
 // ---- moe_kernels.cu --------------------------------------------------------------------------
 int tb200_passthrough(const void* src, void* dst, size_t bytes, cudaStream_t stream);
 

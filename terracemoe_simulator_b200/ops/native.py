@@ -15,7 +15,7 @@ from __future__ import annotations
 import torch
 
 LIVE = {"rmsnorm": 0, "route": 0, "linear": 0, "swiglu_ffn": 0, "grouped_mm": 0,
-        "moe_experts_local": 0}
+        "moe_experts_local": 0, "attention": 0}
 
 
 # Kernel launches issued through this module since the last reset (bench.py reports it).
@@ -31,7 +31,7 @@ class _Counted:
                  "k1_arrival": 3, "k2_pack": 3, "ep_plan_pass1": 1, "ep_plan": 1, "ep_push": 1,
                  "ep_signal": 1, "ep_pull_combine": 1, "hopa_rank": 1, "hopa_push": 1,
                  "arrival_push": 1, "arrival_combine": 1, "origin_combine": 1,
-                 "origin_pull_dgate": 1, "grouped_gemm_ex": 1}
+                 "origin_pull_dgate": 1, "grouped_gemm_ex": 1, "attn_fwd": 1, "attn_bwd": 3}
 
     def __getattr__(self, name):
         fn = getattr(torch.ops.terrace, name)
@@ -318,11 +318,43 @@ def moe_experts_local(x, expert_idx, gates, w13, w2, group_size: int | None = No
 
 
 # ---------------------------------------------------------------------------------------------
-# attention (kernel pending; predicate keeps callers on the PyTorch path)
+# attention
 # ---------------------------------------------------------------------------------------------
+class _Attention(torch.autograd.Function):
+    """softmax(scale * q k^T (+ causal mask)) v on q, k, v [B, H, S, D] through the tcgen05
+    attention kernels (forward saves the log-sum-exp; backward recomputes the probabilities)."""
+
+    @staticmethod
+    def forward(ctx, q, k, v, causal, scale):
+        q, k, v = q.contiguous(), k.contiguous(), v.contiguous()
+        o, lse = _lib().attn_fwd(q, k, v, bool(causal), float(scale))
+        ctx.save_for_backward(q, k, v, o, lse)
+        ctx.causal, ctx.scale = bool(causal), float(scale)
+        LIVE["attention"] += 1
+        return o
+
+    @staticmethod
+    def backward(ctx, d_o):
+        q, k, v, o, lse = ctx.saved_tensors
+        dq, dk, dv = _lib().attn_bwd(q, k, v, o, d_o.contiguous(), lse, ctx.causal, ctx.scale)
+        return dq, dk, dv, None, None
+
+
+def attention_shape_supported(q) -> bool:
+    return (q.is_cuda and q.dtype == torch.bfloat16 and q.dim() == 4 and q.shape[-2] % 128 == 0
+            and q.shape[-1] in (64, 128))
+
+
+def attention(q, k, v, causal: bool = True, scale: float | None = None):
+    """Self-attention on [B, H, S, D] bf16 tensors (S a multiple of 128, D 64 or 128)."""
+    if scale is None:
+        scale = q.shape[-1] ** -0.5
+    return _Attention.apply(q, k, v, causal, scale)
+
+
 def attention_supported(x, n_heads) -> bool:
-    return False
-
-
-def causal_attention_rope(qkv, cos, sin):
-    raise NotImplementedError("native attention kernel is not available")
+    """Can the attention of a [B, T, dim] bf16 activation with n_heads heads run natively?"""
+    if not (x.is_cuda and x.dtype == torch.bfloat16 and x.dim() == 3):
+        return False
+    hd = x.shape[-1] // n_heads
+    return x.shape[1] % 128 == 0 and hd in (64, 128)
