@@ -18,7 +18,7 @@ import sys
 import torch
 
 CASES = ("gemm_fwd", "gemm_swiglu", "gemm_dgrad", "gemm_wgrad", "rmsnorm", "route", "scatter",
-         "combine", "swiglu_bwd")
+         "combine", "swiglu_bwd", "attn_fwd", "attn_bwd")
 
 
 def _peaks():
@@ -48,6 +48,8 @@ def main(argv=None) -> int:
     ap.add_argument("case", choices=CASES)
     ap.add_argument("--iters", type=int, default=3)
     ap.add_argument("--full", action="store_true")
+    ap.add_argument("--library", action="store_true",
+                    help="attention cases: time torch's scaled_dot_product_attention instead")
     ap.add_argument("--pad", type=int, default=0,
                     help="declare the groups padded to this multiple (64 lets the weight-gradient "
                          "GEMM use CTA pairs)")
@@ -83,6 +85,27 @@ def main(argv=None) -> int:
         dY = torch.randn(rows, 2 * d, device=dev, dtype=bf)
         fn = lambda: lib.grouped_wgrad(X, dY, st, cnt, 0, args.pad)
         flops = 2 * rows * H * 2 * d
+    elif args.case in ("attn_fwd", "attn_bwd"):
+        # small: 2 x 16 heads x 2048 x 128; --full: the decoder benchmark's 8 x 16 x 4096 x 128
+        B_, H_, S_, D_ = (8, 16, 4096, 128) if args.full else (2, 16, 2048, 128)
+        q, k_, v = (torch.randn(B_, H_, S_, D_, device=dev, dtype=bf) for _ in range(3))
+        causal_flops = 4 * B_ * H_ * S_ * S_ * D_ / 2
+        if args.case == "attn_fwd":
+            fn = lambda: lib.attn_fwd(q, k_, v, True, D_ ** -0.5)
+            flops = causal_flops
+        else:
+            o, lse = lib.attn_fwd(q, k_, v, True, D_ ** -0.5)
+            go = torch.randn_like(o)
+            fn = lambda: lib.attn_bwd(q, k_, v, o, go, lse, True, D_ ** -0.5)
+            flops = 2.5 * causal_flops
+        if args.library:
+            import torch.nn.functional as F
+            if args.case == "attn_fwd":
+                fn = lambda: F.scaled_dot_product_attention(q, k_, v, is_causal=True)
+            else:
+                qq, kk, vv = (t.clone().requires_grad_(True) for t in (q, k_, v))
+                oo = F.scaled_dot_product_attention(qq, kk, vv, is_causal=True)
+                fn = lambda: torch.autograd.grad(oo, (qq, kk, vv), go, retain_graph=True)
     elif args.case == "rmsnorm":
         x = torch.randn(rows * 2, H, device=dev, dtype=bf)
         w = torch.ones(H, device=dev, dtype=bf)
@@ -110,7 +133,7 @@ def main(argv=None) -> int:
         fn = lambda: lib.swiglu_bwd(h13, dact)
         bytes_ = rows * d * 2 * 5
     ms = _time(fn, args.iters)
-    line = {"case": args.case, "full": args.full, "pad": args.pad,
+    line = {"case": args.case, "full": args.full, "pad": args.pad, "library": args.library,
             "pair_policy": os.environ.get("TERRACE_GEMM_PAIR", "auto"), "ms": round(ms, 4)}
     if flops:
         line["tflops"] = round(flops / ms / 1e9, 1)

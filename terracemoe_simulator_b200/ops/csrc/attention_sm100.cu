@@ -29,7 +29,10 @@
 namespace tb200 {
 
 constexpr int AT_ROWS = 128;          // rows per block (queries or keys)
-constexpr int AT_THREADS = 192;       // warp 0 TMA, warp 1 MMA, warps 2..5 one thread per row
+constexpr int AT_THREADS = 320;       // warp 0 TMA, warp 1 MMA, warps 2..9: two threads per row
+                                      // (columns 0-63 and 64-127 of a 128-wide block), i.e. two
+                                      // row warps per scheduler so that their latencies overlap
+constexpr int AT_ROW_THREADS = 256;    // (10 warps = 3 on the fullest scheduler: 168 registers each)
 constexpr int AT_BOX = AT_ROWS * 128; // one TMA box: 128 rows x 64 bf16 = 16 KiB
 constexpr int AT_TMEM_COLS = 512;
 
@@ -52,7 +55,13 @@ struct __align__(8) AttnCtl {
   uint64_t bar[16];
   uint32_t tmem_base;
   volatile int abort_flag;
+  float xch[2][2][AT_ROWS];   // [block parity][column half][row]: row maxima / sums exchanged
 };
+
+// barrier among the 256 row threads only (the TMA and MMA warps never join it)
+__device__ __forceinline__ void at_row_sync() {
+  asm volatile("bar.sync 1, %0;" ::"n"(AT_ROW_THREADS) : "memory");
+}
 
 __device__ __forceinline__ void at_abort(AttnCtl* ctl, int* status, int code) {
   ctl->abort_flag = code;
@@ -127,6 +136,70 @@ __device__ __forceinline__ void at_teardown(AttnCtl* ctl, int warp, uint32_t tme
   }
 }
 
+// Row maximum of 64 scores held in registers; with MASK only columns [0, n_valid) count.
+// Four independent chains, so consecutive instructions do not wait on one another.
+template <bool MASK>
+__device__ __forceinline__ float at_row_max64(const uint32_t (&sv)[2][32], int n_valid) {
+  float m0 = -INFINITY, m1 = -INFINITY, m2 = -INFINITY, m3 = -INFINITY;
+#pragma unroll
+  for (int c = 0; c < 2; ++c) {
+#pragma unroll
+    for (int i = 0; i < 32; i += 4) {
+      float x0 = __uint_as_float(sv[c][i]), x1 = __uint_as_float(sv[c][i + 1]);
+      float x2 = __uint_as_float(sv[c][i + 2]), x3 = __uint_as_float(sv[c][i + 3]);
+      if (MASK) {
+        if (c * 32 + i >= n_valid) x0 = -INFINITY;
+        if (c * 32 + i + 1 >= n_valid) x1 = -INFINITY;
+        if (c * 32 + i + 2 >= n_valid) x2 = -INFINITY;
+        if (c * 32 + i + 3 >= n_valid) x3 = -INFINITY;
+      }
+      m0 = fmaxf(m0, x0);
+      m1 = fmaxf(m1, x1);
+      m2 = fmaxf(m2, x2);
+      m3 = fmaxf(m3, x3);
+    }
+  }
+  return fmaxf(fmaxf(m0, m1), fmaxf(m2, m3));
+}
+
+// exp2(s * scale_log2 - mxs) of 32 scores -> bf16 into columns [c0, c0 + 32) of row `row` of the
+// swizzled P tile (one 16-byte store per 8 values); returns their sum.
+template <bool MASK>
+__device__ __forceinline__ float at_exp_store32(const uint32_t (&sv)[32], uint8_t* tile, int row,
+                                                int c0, int col0, int n_valid, float scale_log2,
+                                                float mxs) {
+  float s0 = 0.f, s1 = 0.f, s2 = 0.f, s3 = 0.f;
+  uint8_t* base = tile + (c0 >> 6) * AT_BOX + row * 128;
+  const int chunk0 = (c0 & 63) >> 3;
+#pragma unroll
+  for (int q = 0; q < 4; ++q) {
+    uint32_t w[4];
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      const int i = q * 8 + h * 4;
+      float a = exp2f(__uint_as_float(sv[i]) * scale_log2 - mxs);
+      float b = exp2f(__uint_as_float(sv[i + 1]) * scale_log2 - mxs);
+      float c = exp2f(__uint_as_float(sv[i + 2]) * scale_log2 - mxs);
+      float d = exp2f(__uint_as_float(sv[i + 3]) * scale_log2 - mxs);
+      if (MASK) {
+        if (col0 + i >= n_valid) a = 0.f;
+        if (col0 + i + 1 >= n_valid) b = 0.f;
+        if (col0 + i + 2 >= n_valid) c = 0.f;
+        if (col0 + i + 3 >= n_valid) d = 0.f;
+      }
+      s0 += a;
+      s1 += b;
+      s2 += c;
+      s3 += d;
+      w[h * 2] = at_pack(a, b);
+      w[h * 2 + 1] = at_pack(c, d);
+    }
+    *reinterpret_cast<uint4*>(base + (((chunk0 + q) ^ (row & 7)) << 4)) =
+        make_uint4(w[0], w[1], w[2], w[3]);
+  }
+  return (s0 + s1) + (s2 + s3);
+}
+
 // =============================================================================================
 // forward
 // =============================================================================================
@@ -155,7 +228,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
   const int row_base = bh * p.S;
 
   {
-    const int counts[FB_N] = {1, 1, 1, 1, 1, 1, 1, 1, 1, 1, 1, 4, 4, 4, 1};
+    const int counts[FB_N] = {1, 1, 1, 1, 1, 1, 1, 1, 1, 1, 1, 8, 8, 8, 1};
     at_setup(ctl, FB_N, counts, warp, lane);
   }
   const uint32_t tmem = ctl->tmem_base;
@@ -230,78 +303,73 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     if (!ok && lane == 0) at_abort(ctl, p.status, ST_TIMEOUT_ACC);
   } else {
     const int quad = warp & 3;
+    const int half = (warp - 2) >> 2;          // which 64 columns of a block this thread owns
     const int row = quad * 32 + lane;
     const uint32_t lane_addr = tmem + (static_cast<uint32_t>(quad * 32) << 16);
     const int q_glob = qb * AT_ROWS + row;
+    constexpr int DH = D / 2;                  // output columns per thread
     float m = -INFINITY, l = 0.f, alpha_pending = 0.f;
-    float o[D];
+    float o[DH];
 #pragma unroll
-    for (int i = 0; i < D; ++i) o[i] = 0.f;
+    for (int i = 0; i < DH; ++i) o[i] = 0.f;
     bool ok = true;
-    for (int j = 0; j < n_kv && ok; ++j) {
+    for (int j = 0; j < n_kv; ++j) {
       const int s = j & 1, r = j >> 1;
-      if (!at_wait(ctl, FB_SF + s, r & 1)) {
-        ok = false;
-        break;
-      }
+      ok = ok && at_wait(ctl, FB_SF + s, r & 1);
       tc_fence_after();
+      // on the diagonal block of a causal mask this thread sees columns [0, n_valid) of its half
       const bool diag = p.causal && j == qb;
-      const int kv0 = j * AT_ROWS;
-      // pass 1: row maximum
-      float mx = m;
-#pragma unroll 1
-      for (int c = 0; c < 4; ++c) {
-        uint32_t v[32];
-        tmem_ld_32x32(lane_addr + s * 128 + c * 32, v);
+      const int n_valid = min(max(row - half * 64 + 1, 0), 64);
+      // pass 1: row maximum over this thread's 64 columns (both loads in flight), then over both
+      // halves of the row.  The scores are read again in pass 2: keeping them in registers next
+      // to the 64 output accumulators spilled and ran slower.
+      float mx = -INFINITY;
+      if (ok) {
+        uint32_t sv[2][32];
+        tmem_ld_32x32(lane_addr + s * 128 + half * 64, sv[0]);
+        tmem_ld_32x32(lane_addr + s * 128 + half * 64 + 32, sv[1]);
         tmem_ld_wait();
-#pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          const float x = __uint_as_float(v[i]);
-          if (!diag || kv0 + c * 32 + i <= q_glob) mx = fmaxf(mx, x);
-        }
+        mx = diag ? at_row_max64<true>(sv, n_valid) : at_row_max64<false>(sv, 64);
       }
+      ctl->xch[s][half][row] = mx;
+      at_row_sync();                          // every row thread reaches this, also after a timeout
+      mx = fmaxf(fmaxf(mx, ctl->xch[s][half ^ 1][row]), m);
+      if (!ok) continue;
       const float alpha = (m == -INFINITY) ? 0.f : exp2f((m - mx) * p.scale_log2);
-      // fold the previous block's P V into O (it was computed against the previous maximum)
       if (j > 0) {
         if (!at_wait(ctl, FB_PV, (j - 1) & 1)) {
           ok = false;
-          break;
+          continue;
         }
         tc_fence_after();
+      }
+      // pass 2: probabilities to shared memory; the previous block's P V (computed against the
+      // previous maximum) is loaded alongside each score chunk and folded into O
+      const float mxs = mx * p.scale_log2;
+      float rowsum = 0.f;
+      static_assert(DH / 32 <= 2, "one P V chunk per score chunk");
 #pragma unroll
-        for (int c = 0; c < D / 32; ++c) {
-          uint32_t v[32];
-          tmem_ld_32x32(lane_addr + 256 + c * 32, v);
-          tmem_ld_wait();
+      for (int c = 0; c < 2; ++c) {
+        uint32_t sv[32], pv[32];
+        const bool fold = j > 0 && c < DH / 32;
+        tmem_ld_32x32(lane_addr + s * 128 + half * 64 + c * 32, sv);
+        if (fold) tmem_ld_32x32(lane_addr + 256 + half * DH + c * 32, pv);
+        tmem_ld_wait();
+        rowsum += diag ? at_exp_store32<true>(sv, sP, row, half * 64 + c * 32, c * 32, n_valid,
+                                              p.scale_log2, mxs)
+                       : at_exp_store32<false>(sv, sP, row, half * 64 + c * 32, c * 32, 64,
+                                               p.scale_log2, mxs);
+        if (c < DH / 32) {
+          if (fold) {
 #pragma unroll
-          for (int i = 0; i < 32; ++i)
-            o[c * 32 + i] = o[c * 32 + i] * alpha_pending + __uint_as_float(v[i]);
+            for (int i = 0; i < 32; ++i)
+              o[(c < DH / 32 ? c : 0) * 32 + i] =
+                  o[(c < DH / 32 ? c : 0) * 32 + i] * alpha_pending + __uint_as_float(pv[i]);
+          }
         }
       }
       alpha_pending = alpha;
-      // pass 2: probabilities to shared memory
-      const float mxs = mx * p.scale_log2;
-      float rowsum = 0.f;
-#pragma unroll 1
-      for (int c = 0; c < 4; ++c) {
-        uint32_t v[32];
-        tmem_ld_32x32(lane_addr + s * 128 + c * 32, v);
-        tmem_ld_wait();
-        uint32_t w[16];
-#pragma unroll
-        for (int i = 0; i < 16; ++i) {
-          float a = exp2f(__uint_as_float(v[2 * i]) * p.scale_log2 - mxs);
-          float b = exp2f(__uint_as_float(v[2 * i + 1]) * p.scale_log2 - mxs);
-          if (diag) {
-            if (kv0 + c * 32 + 2 * i > q_glob) a = 0.f;
-            if (kv0 + c * 32 + 2 * i + 1 > q_glob) b = 0.f;
-          }
-          rowsum += a + b;
-          w[i] = at_pack(a, b);
-        }
-        at_store_chunk32(sP, row, c * 32, w);
-      }
-      l = l * alpha + rowsum;
+      l = l * alpha + rowsum;                 // this half's share of the row sum
       m = mx;
       fence_proxy_async_smem();
       tc_fence_before();
@@ -312,14 +380,18 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       }
     }
     if (ok && !at_wait(ctl, FB_PV, (n_kv - 1) & 1)) ok = false;
+    // both halves of a row add their sums (buffer of the parity the last block did not use)
+    ctl->xch[n_kv & 1][half][row] = l;
+    at_row_sync();
+    l += ctl->xch[n_kv & 1][half ^ 1][row];
     if (ok) {
       tc_fence_after();
       const float inv = 1.f / l;
-      __nv_bfloat16* orow = p.O + (static_cast<size_t>(row_base) + q_glob) * D;
+      __nv_bfloat16* orow = p.O + (static_cast<size_t>(row_base) + q_glob) * D + half * DH;
 #pragma unroll
-      for (int c = 0; c < D / 32; ++c) {
+      for (int c = 0; c < DH / 32; ++c) {
         uint32_t v[32];
-        tmem_ld_32x32(lane_addr + 256 + c * 32, v);
+        tmem_ld_32x32(lane_addr + 256 + half * DH + c * 32, v);
         tmem_ld_wait();
 #pragma unroll
         for (int q = 0; q < 4; ++q) {
@@ -335,7 +407,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
           *reinterpret_cast<uint4*>(orow + c * 32 + q * 8) = out;
         }
       }
-      p.LSE[static_cast<size_t>(row_base) + q_glob] = m * p.scale + logf(l);
+      if (half == 0) p.LSE[static_cast<size_t>(row_base) + q_glob] = m * p.scale + logf(l);
     } else if (lane == 0) {
       at_abort(ctl, p.status, ST_TIMEOUT_ACC);
     }
@@ -368,34 +440,62 @@ __global__ void attn_delta_kernel(const __nv_bfloat16* __restrict__ O,
   if (lane == 0) delta[row] = acc;
 }
 
-// One thread's row of S and dP (TMEM) -> P and dS chunks in shared memory.
+template <bool WRITE_P, bool MASK>
+__device__ __forceinline__ void at_p_ds_cols(uint32_t lane_addr, uint8_t* sP, uint8_t* sdS,
+                                             int row, int half, float lse_l2, float delta,
+                                             float scale, float scale_log2, int limit) {
+  // this thread's 64 columns of S and of dP: four TMEM loads in flight, one wait
+  uint32_t sv[2][32], dv[2][32];
+#pragma unroll
+  for (int c = 0; c < 2; ++c) {
+    tmem_ld_32x32(lane_addr + half * 64 + c * 32, sv[c]);
+    tmem_ld_32x32(lane_addr + 128 + half * 64 + c * 32, dv[c]);
+  }
+  tmem_ld_wait();
+  const float dsc = delta * scale;
+#pragma unroll
+  for (int c = 0; c < 2; ++c) {
+    const int col0 = half * 64 + c * 32;
+    const int off = (col0 >> 6) * AT_BOX + row * 128;
+    const int chunk0 = (col0 & 63) >> 3;
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+      uint32_t wp[4], wd[4];
+#pragma unroll
+      for (int h = 0; h < 4; ++h) {
+        const int i = q * 8 + h * 2;
+        float p0 = exp2f(__uint_as_float(sv[c][i]) * scale_log2 - lse_l2);
+        float p1 = exp2f(__uint_as_float(sv[c][i + 1]) * scale_log2 - lse_l2);
+        if (MASK) {
+          if (col0 + i > limit) p0 = 0.f;
+          if (col0 + i + 1 > limit) p1 = 0.f;
+        }
+        const float d0 = p0 * (__uint_as_float(dv[c][i]) * scale - dsc);
+        const float d1 = p1 * (__uint_as_float(dv[c][i + 1]) * scale - dsc);
+        wp[h] = at_pack(p0, p1);
+        wd[h] = at_pack(d0, d1);
+      }
+      const int sw = ((chunk0 + q) ^ (row & 7)) << 4;
+      if (WRITE_P)
+        *reinterpret_cast<uint4*>(sP + off + sw) = make_uint4(wp[0], wp[1], wp[2], wp[3]);
+      *reinterpret_cast<uint4*>(sdS + off + sw) = make_uint4(wd[0], wd[1], wd[2], wd[3]);
+    }
+  }
+}
+
+// One thread's 64 columns of S and dP (TMEM) -> P and dS in shared memory.
 //   p  = exp2(s * scale_log2 - lse * log2e),  ds = p * (dp - delta) * scale
-// `limit`: columns (keys) > limit are masked (pass a large value for no mask).
+// Columns (keys) > limit are masked; limit >= 127 means no mask.
 template <bool WRITE_P>
 __device__ __forceinline__ void at_p_ds_row(uint32_t lane_addr, uint8_t* sP, uint8_t* sdS, int row,
-                                            float lse_l2, float delta, float scale,
-                                            float scale_log2, int limit) {
-#pragma unroll 1
-  for (int c = 0; c < 4; ++c) {
-    uint32_t sv[32], dv[32];
-    tmem_ld_32x32(lane_addr + c * 32, sv);
-    tmem_ld_32x32(lane_addr + 128 + c * 32, dv);
-    tmem_ld_wait();
-    uint32_t wp[16], wd[16];
-#pragma unroll
-    for (int i = 0; i < 16; ++i) {
-      float p0 = exp2f(__uint_as_float(sv[2 * i]) * scale_log2 - lse_l2);
-      float p1 = exp2f(__uint_as_float(sv[2 * i + 1]) * scale_log2 - lse_l2);
-      if (c * 32 + 2 * i > limit) p0 = 0.f;
-      if (c * 32 + 2 * i + 1 > limit) p1 = 0.f;
-      const float d0 = p0 * (__uint_as_float(dv[2 * i]) - delta) * scale;
-      const float d1 = p1 * (__uint_as_float(dv[2 * i + 1]) - delta) * scale;
-      wp[i] = at_pack(p0, p1);
-      wd[i] = at_pack(d0, d1);
-    }
-    if (WRITE_P) at_store_chunk32(sP, row, c * 32, wp);
-    at_store_chunk32(sdS, row, c * 32, wd);
-  }
+                                            int half, float lse_l2, float delta, float scale,
+                                            float scale_log2, int limit, bool masked) {
+  if (masked)
+    at_p_ds_cols<WRITE_P, true>(lane_addr, sP, sdS, row, half, lse_l2, delta, scale, scale_log2,
+                                limit);
+  else
+    at_p_ds_cols<WRITE_P, false>(lane_addr, sP, sdS, row, half, lse_l2, delta, scale, scale_log2,
+                                 limit);
 }
 
 // =============================================================================================
@@ -429,7 +529,7 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tm_q,
   const int n_it = nb - i0;
   const int row_base = bh * p.S;
   {
-    const int counts[KB_N] = {1, 1, 1, 1, 4, 1};
+    const int counts[KB_N] = {1, 1, 1, 1, 8, 1};
     at_setup(ctl, KB_N, counts, warp, lane);
   }
   const uint32_t tmem = ctl->tmem_base;
@@ -496,6 +596,7 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tm_q,
     if (!ok && lane == 0) at_abort(ctl, p.status, ST_TIMEOUT_ACC);
   } else {
     const int quad = warp & 3;
+    const int half = (warp - 2) >> 2;
     const int row = quad * 32 + lane;
     const uint32_t lane_addr = tmem + (static_cast<uint32_t>(quad * 32) << 16);
     bool ok = true;
@@ -515,7 +616,8 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tm_q,
       tc_fence_after();
       // keys of this block visible to query `row` of the diagonal block: key <= query
       const int limit = (p.causal && ib == jb) ? row : 1 << 30;
-      at_p_ds_row<true>(lane_addr, sP, sdS, row, lse_l2, delta, p.scale, p.scale_log2, limit);
+      at_p_ds_row<true>(lane_addr, sP, sdS, row, half, lse_l2, delta, p.scale, p.scale_log2, limit,
+                        p.causal && ib == jb);
       fence_proxy_async_smem();
       tc_fence_before();
       __syncwarp();
@@ -525,8 +627,9 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tm_q,
     if (ok) {
       tc_fence_after();
       const size_t g = (static_cast<size_t>(row_base) + jb * AT_ROWS + row) * D;   // this key row
-#pragma unroll 1
-      for (int which = 0; which < 2; ++which) {
+      // half 0 writes dV, half 1 writes dK
+      {
+        const int which = half;
         __nv_bfloat16* dst = (which == 0 ? p.dV : p.dK) + g;
 #pragma unroll
         for (int c = 0; c < D / 32; ++c) {
@@ -580,7 +683,7 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_q,
   const int n_it = p.causal ? ib + 1 : nb;
   const int row_base = bh * p.S;
   {
-    const int counts[QB_N] = {1, 1, 1, 1, 4, 1};
+    const int counts[QB_N] = {1, 1, 1, 1, 8, 1};
     at_setup(ctl, QB_N, counts, warp, lane);
   }
   const uint32_t tmem = ctl->tmem_base;
@@ -643,6 +746,7 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_q,
     if (!ok && lane == 0) at_abort(ctl, p.status, ST_TIMEOUT_ACC);
   } else {
     const int quad = warp & 3;
+    const int half = (warp - 2) >> 2;
     const int row = quad * 32 + lane;
     const uint32_t lane_addr = tmem + (static_cast<uint32_t>(quad * 32) << 16);
     const size_t g = static_cast<size_t>(row_base) + ib * AT_ROWS + row;
@@ -660,7 +764,8 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_q,
       }
       tc_fence_after();
       const int limit = (p.causal && j == ib) ? row : 1 << 30;
-      at_p_ds_row<false>(lane_addr, nullptr, sdS, row, lse_l2, delta, p.scale, p.scale_log2, limit);
+      at_p_ds_row<false>(lane_addr, nullptr, sdS, row, half, lse_l2, delta, p.scale, p.scale_log2, limit,
+                         p.causal && j == ib);
       fence_proxy_async_smem();
       tc_fence_before();
       __syncwarp();
@@ -671,7 +776,7 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_q,
       tc_fence_after();
       __nv_bfloat16* dst = p.dQ + g * D;
 #pragma unroll
-      for (int c = 0; c < D / 32; ++c) {
+      for (int c = half * (D / 64); c < (half + 1) * (D / 64); ++c) {
         uint32_t v[32];
         tmem_ld_32x32(lane_addr + 256 + c * 32, v);
         tmem_ld_wait();
