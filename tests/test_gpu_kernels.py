@@ -333,6 +333,19 @@ def test_gemm_cta_pair_variant_in_subprocess(native_ops):
     assert proc.returncode == 0, proc.stdout.decode()[-3000:] + proc.stderr.decode()[-2000:]
 
 
+def test_gemm_swapped_operand_variant_in_subprocess(native_ops):
+    """TERRACE_GEMM_SWAP=1 routes padded short groups through the swapped-operand kernel."""
+    import os
+    import subprocess
+    import sys
+    if os.environ.get("TERRACE_GEMM_SWAP") == "1":
+        pytest.skip("already inside the swap run")
+    env = dict(os.environ, TERRACE_GEMM_SWAP="1")
+    proc = subprocess.run([sys.executable, "-m", "pytest", os.path.abspath(__file__), "-q", "-x", "-k",
+                           "padded or moe_experts"], env=env, capture_output=True, timeout=900)
+    assert proc.returncode == 0, proc.stdout.decode()[-3000:] + proc.stderr.decode()[-2000:]
+
+
 def test_long_groups_use_pairs_by_default(native_ops):
     """Groups of 1024+ rows take the 256-row pair tiles under the default policy."""
     torch.manual_seed(1)
