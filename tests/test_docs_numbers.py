@@ -93,7 +93,7 @@ def _b200_grouping_ratios():
 
 def _phase_spans():
     from terracemoe_simulator_b200.sim import calibrate, core, phase
-    g = core.MoEGeometry("flag", 16, 8, 6, 2)
+    g = core.MoEGeometry(name="n4", n_groups=4, R=8, k=6, M=2, seq=4096, mbs=1, gbs=4 * 8 * 4096)
     r = phase.report(calibrate.flat_supernode(), g, {"n_experts": 128, "d_expert": 2048})
     s = r["spans"]
     return [s.splits_sync, s.hop_a, s.arrival_chain, s.hop_b, s.combine]
