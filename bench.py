@@ -16,7 +16,8 @@ headline value is the faster of the two and ``config.path`` names it.
 Timing: CUDA events on the launching stream, max over ranks, barrier + synchronize on both
 sides; the 2.2 GB of expert weights per step exceed the 126 MB L2, so no L2 flush is needed.
 The ``e2e`` entry repeats the measurement through the public API with a pinned-host -> device
-copy of the step's tokens and a device -> host read of the loss inside every timed step.
+copy of the step's tokens (issued one step ahead on a side stream by the package's
+``DevicePrefetcher``) and a device -> host read of the loss inside every timed step.
 ``--impl reference`` runs the unmodified reference (``baseline/_ref``: a plain copy of its
 ``terrace`` package, it has no build system to install) through ``ep_moe_forward`` /
 ``ta2a_moe_forward`` on NCCL for the same configuration.
@@ -179,6 +180,12 @@ def run_ours(args, rank, world, local):
                                        rpn=RPN[world], mode=path, fused=not args.nccl_arm,
                                        device=device)
     x_dev = x_host.to(device).requires_grad_(True)
+    # end-to-end path: every step's tokens come from pinned host memory through the package's
+    # input prefetcher (the copy of step i+1 runs on a side stream during step i)
+    import itertools
+    from terracemoe_simulator_b200.utils.prefetch import DevicePrefetcher
+    host_batches = [x_host] + [x_host.clone().pin_memory() for _ in range(2)]
+    feed = DevicePrefetcher(itertools.cycle(host_batches), device)
 
     def make_step(path, e2e: bool):
         runner = runners[path]
@@ -187,7 +194,7 @@ def run_ours(args, rank, world, local):
             for p in params:
                 p.grad = None
             if e2e:
-                x = x_host.to(device, non_blocking=True).requires_grad_(True)
+                x = next(feed).requires_grad_(True)
             else:
                 x = x_dev
                 x.grad = None

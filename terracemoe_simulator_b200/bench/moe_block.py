@@ -74,10 +74,14 @@ def main(argv=None) -> int:
         x_host = x_host.pin_memory()
     last = {"loss": 0.0}
 
+    import itertools
+    from ..utils.prefetch import DevicePrefetcher
+    feed = DevicePrefetcher(itertools.cycle([x_host]), device)
+
     def step():
         for p in layer.parameters():
             p.grad = None
-        x = x_host.to(device, non_blocking=True).requires_grad_(True)
+        x = next(feed).requires_grad_(True)
         y, _ = layer(x)
         loss = (y.float() * gy.float()).mean()
         loss.backward()

@@ -1,7 +1,7 @@
 """Dispatch/combine sweep for cost-model calibration (run under ``torch.distributed.run``).
 
     python -m torch.distributed.run --nproc-per-node N -m terracemoe_simulator_b200.bench.sweep \
-        --out gpurun_out/sweep_N.json [--tokens 256 1024 4096 16384] [--hidden 4096]
+        --out sweep_N.json [--tokens 256 1024 4096 16384] [--hidden 4096]
 
 For every tokens-per-GPU value, group size R in {2, 4} (where N allows at least two groups) and
 quota q in {1, 2, 3, 4} (64 experts, M = 2, k = q*M) it times the fused one-hop and two-hop
@@ -45,7 +45,7 @@ def _timed(fn, iters, warmup, world):
 
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser()
-    ap.add_argument("--out", default="gpurun_out/sweep.json")
+    ap.add_argument("--out", default="sweep.json")
     ap.add_argument("--tokens", type=int, nargs="+", default=[256, 1024, 4096, 16384])
     ap.add_argument("--hidden", type=int, default=4096)
     ap.add_argument("--experts", type=int, default=64)

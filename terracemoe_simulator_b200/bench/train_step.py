@@ -101,8 +101,12 @@ def main(argv=None) -> int:
     model.train()
     state = {"i": 0, "loss": 0.0}
 
+    import itertools
+    from ..utils.prefetch import DevicePrefetcher
+    feed = DevicePrefetcher(itertools.cycle(host), device)
+
     def step():
-        tok = host[state["i"] % n_host].to(device, non_blocking=True)
+        tok = next(feed)
         state["i"] += 1
         opt.zero_grad(set_to_none=True)
         loss, _ = model(tok[:, :-1], tok[:, 1:])

@@ -1,0 +1,67 @@
+"""Host-to-device input prefetch: the copy of step i+1's batch overlaps step i's compute.
+
+``DevicePrefetcher`` takes an iterable of pinned host tensors (or tuples of them), keeps two
+device buffers, and issues every host-to-device copy on a side stream one step ahead of its use;
+``next()`` makes the compute stream wait on that copy's event and immediately starts the
+following copy.  On a CPU device it degenerates to passing the batches through.
+
+The reference has no input pipeline (its only training loop builds tensors on the device,
+``tests/test_checkpoint.py:16-23``); this exists so that the end-to-end numbers of the benchmarks
+include the copy of every step's input without serialising it in front of the step.
+"""
+from __future__ import annotations
+
+import torch
+
+
+class DevicePrefetcher:
+    def __init__(self, batches, device, depth: int = 2):
+        self.it = iter(batches)
+        self.device = torch.device(device)
+        self.cuda = self.device.type == "cuda"
+        self.depth = max(1, depth)
+        self.stream = torch.cuda.Stream(self.device) if self.cuda else None
+        self.queue = []                 # (device batch, event) in issue order
+        self.copied_bytes = 0
+        for _ in range(self.depth):
+            self._issue()
+
+    @staticmethod
+    def _map(batch, fn):
+        if isinstance(batch, (tuple, list)):
+            return type(batch)(fn(t) for t in batch)
+        return fn(batch)
+
+    def _issue(self) -> None:
+        try:
+            host = next(self.it)
+        except StopIteration:
+            return
+        if not self.cuda:
+            self.queue.append((host, None))
+            return
+        with torch.cuda.stream(self.stream):
+            dev = self._map(host, lambda t: t.to(self.device, non_blocking=True))
+            event = torch.cuda.Event()
+            event.record(self.stream)
+        self._map(host, lambda t: self._count(t))
+        self.queue.append((dev, event))
+
+    def _count(self, t):
+        self.copied_bytes += t.numel() * t.element_size()
+        return t
+
+    def __iter__(self):
+        return self
+
+    def __next__(self):
+        if not self.queue:
+            raise StopIteration
+        dev, event = self.queue.pop(0)
+        if event is not None:
+            torch.cuda.current_stream(self.device).wait_event(event)
+            # the buffer is consumed on the compute stream: keep the allocator from handing its
+            # memory to the side stream's next copy before that work has run
+            self._map(dev, lambda t: t.record_stream(torch.cuda.current_stream(self.device)) or t)
+        self._issue()
+        return dev

@@ -115,3 +115,16 @@ def test_traffic_helpers():
     m = traffic.dispatch_traffic(group_idx, src, cfg, cards_per_group=2)
     assert m.shape == (4, 4) and int(m.sum()) == 6
     assert traffic.uniformity_cv(torch.ones(4, 4)) == pytest.approx(0.0)
+
+
+def test_device_prefetcher_passthrough_and_order():
+    import itertools
+    import torch
+    from terracemoe_simulator_b200.utils.prefetch import DevicePrefetcher
+    batches = [torch.full((2, 3), float(i)) for i in range(5)]
+    out = list(DevicePrefetcher(batches, "cpu"))
+    assert len(out) == 5 and all(torch.equal(a, b) for a, b in zip(out, batches))
+    pairs = list(DevicePrefetcher([(torch.ones(1), torch.zeros(2))] * 3, "cpu", depth=1))
+    assert len(pairs) == 3 and isinstance(pairs[0], tuple)
+    feed = DevicePrefetcher(itertools.cycle(batches), "cpu")
+    assert [int(next(feed)[0, 0]) for _ in range(7)] == [0, 1, 2, 3, 4, 0, 1]

@@ -363,3 +363,19 @@ def test_long_groups_use_pairs_by_default(native_ops):
         _close(Ct[off:off + n], ref)
         off += n
     assert native_ops.take_status() == 0
+
+
+def test_device_prefetcher_on_gpu(native_ops):
+    import itertools
+    from terracemoe_simulator_b200.utils.prefetch import DevicePrefetcher
+    host = [torch.full((1024, 1024), float(i)).pin_memory() for i in range(3)]
+    feed = DevicePrefetcher(itertools.cycle(host), DEV)
+    acc = torch.zeros(1024, 1024, device=DEV)
+    for step in range(9):
+        x = next(feed)
+        assert x.is_cuda
+        acc += x @ torch.eye(1024, device=DEV)          # compute that overlaps the next copy
+        assert float(x[0, 0]) == float(step % 3)
+    torch.cuda.synchronize()
+    assert float(acc[0, 0]) == 3 * (0 + 1 + 2)
+    assert feed.copied_bytes >= 9 * 4 * 1024 * 1024
