@@ -17,7 +17,9 @@ Timing: CUDA events on the launching stream, max over ranks, barrier + synchroni
 sides; the 2.2 GB of expert weights per step exceed the 126 MB L2, so no L2 flush is needed.
 The ``e2e`` entry repeats the measurement through the public API with a pinned-host -> device
 copy of the step's tokens (issued one step ahead on a side stream by the package's
-``DevicePrefetcher``) and a device -> host read of the loss inside every timed step.
+``DevicePrefetcher``) and a device -> host read of every step's loss inside the timed region
+(``DeferredScalar``: a non-blocking copy to pinned memory, consumed one step later, so the host
+keeps launching ahead of the device; the last value is read before the closing synchronize).
 ``--impl reference`` runs the unmodified reference (``baseline/_ref``: a plain copy of its
 ``terrace`` package, it has no build system to install) through ``ep_moe_forward`` /
 ``ta2a_moe_forward`` on NCCL for the same configuration.
@@ -113,8 +115,10 @@ def setup_dist(n_gpus: int, force: bool):
     return rank, world, local
 
 
-def timed(fn, steps: int, warmup: int, world: int, sampler: ClockSampler | None):
-    """W warm-up steps, then exactly K steps between CUDA events; returns max-over-ranks ms."""
+def timed(fn, steps: int, warmup: int, world: int, sampler: ClockSampler | None, drain=None):
+    """W warm-up steps, then exactly K steps between CUDA events; returns max-over-ranks ms.
+    ``drain`` (optional) runs after the last step and before the closing event: deferred
+    device-to-host reads are completed inside the timed region."""
     import torch
     import torch.distributed as dist
     if sampler:
@@ -129,6 +133,8 @@ def timed(fn, steps: int, warmup: int, world: int, sampler: ClockSampler | None)
     t0.record()
     for _ in range(steps):
         fn()
+    if drain is not None:
+        drain()
     t1.record()
     torch.cuda.synchronize()
     if world > 1:
@@ -184,9 +190,10 @@ def run_ours(args, rank, world, local):
     # end-to-end path: every step's tokens come from pinned host memory through the package's
     # input prefetcher (the copy of step i+1 runs on a side stream during step i)
     import itertools
-    from terracemoe_simulator_b200.utils.prefetch import DevicePrefetcher
+    from terracemoe_simulator_b200.utils.prefetch import DeferredScalar, DevicePrefetcher
     host_batches = [x_host] + [x_host.clone().pin_memory() for _ in range(2)]
     feed = DevicePrefetcher(itertools.cycle(host_batches), device)
+    losses = DeferredScalar(device)      # every step's loss is read on the host, one step late
 
     def make_step(path, e2e: bool):
         runner = runners[path]
@@ -203,7 +210,7 @@ def run_ours(args, rank, world, local):
             if e2e:
                 loss = torch.dot(y.reshape(-1), gy_flat) * inv_n      # one reduction, fp32 accumulate
                 loss.backward()
-                return loss.item()                      # device -> host read of the result
+                return losses.push(loss)     # device -> host read of the result, one step deferred
             y.backward(gy)
             return None
         return step
@@ -220,7 +227,10 @@ def run_ours(args, rank, world, local):
                          "dispatch_combine_us": dc, "status": native.take_status(local)}
         clocks = clocks or clk
     best = min(paths, key=lambda p: results[p]["ms_per_step"])
-    e2e_ms, _ = timed(make_step(best, True), args.steps, args.warmup, world, None)
+    final = {}
+    e2e_ms, _ = timed(make_step(best, True), args.steps, args.warmup, world, None,
+                      drain=lambda: final.update(loss=losses.flush()))
+    last_loss = final.get("loss")
     tokens = TOKENS * world
     value = tokens / (results[best]["ms_per_step"] * 1e-3)
     peaks = {}
@@ -247,7 +257,8 @@ def run_ours(args, rank, world, local):
         "gemm_frac_of_measured_sustained": flops / (results[best]["ms_per_step"] * 1e-3) / (peak_tf * 1e12),
         "clocks": clocks,
         "e2e": {"value": tokens / (e2e_ms / args.steps * 1e-3), "unit": "tokens/s",
-                "h2d_bytes_per_step": x_host.numel() * 2, "d2h_bytes_per_step": 2},
+                "h2d_bytes_per_step": x_host.numel() * 2,
+                "d2h_bytes_per_step": losses.bytes_per_read, "last_loss": last_loss},
         "gpu_launches": results[best]["launches"] * args.steps,
     }
     return out

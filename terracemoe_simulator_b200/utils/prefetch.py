@@ -65,3 +65,37 @@ class DevicePrefetcher:
             self._map(dev, lambda t: t.record_stream(torch.cuda.current_stream(self.device)) or t)
         self._issue()
         return dev
+
+
+class DeferredScalar:
+    """Device-to-host read of a per-step scalar (loss, metric) that does not stall the launch queue.
+
+    ``push(t)`` starts a non-blocking copy of the 0-d tensor ``t`` into pinned host memory and
+    returns the value pushed one call earlier (``None`` the first time), waiting only for that
+    older copy; ``flush()`` waits for and returns the last one.  Every step's value reaches the host,
+    one step late, while the host keeps launching ahead of the device."""
+
+    def __init__(self, device, dtype=torch.float32):
+        self.cuda = torch.device(device).type == "cuda"
+        self.slots = [torch.zeros((), dtype=dtype, pin_memory=self.cuda) for _ in range(2)]
+        self.events = [None, None]
+        self.n = 0
+        self.bytes_per_read = self.slots[0].element_size()
+
+    def _take(self, i):
+        if self.events[i] is not None:
+            self.events[i].synchronize()
+        return float(self.slots[i])
+
+    def push(self, t):
+        i = self.n & 1
+        prev = self._take(i ^ 1) if self.n > 0 else None
+        self.slots[i].copy_(t.detach().to(self.slots[i].dtype), non_blocking=True)
+        if self.cuda:
+            self.events[i] = torch.cuda.Event()
+            self.events[i].record()
+        self.n += 1
+        return prev
+
+    def flush(self):
+        return self._take((self.n - 1) & 1) if self.n > 0 else None

@@ -128,3 +128,12 @@ def test_device_prefetcher_passthrough_and_order():
     assert len(pairs) == 3 and isinstance(pairs[0], tuple)
     feed = DevicePrefetcher(itertools.cycle(batches), "cpu")
     assert [int(next(feed)[0, 0]) for _ in range(7)] == [0, 1, 2, 3, 4, 0, 1]
+
+
+def test_deferred_scalar_reads_every_value_one_step_late():
+    import torch
+    from terracemoe_simulator_b200.utils.prefetch import DeferredScalar
+    d = DeferredScalar("cpu")
+    out = [d.push(torch.tensor(float(i))) for i in range(5)]
+    assert out == [None, 0.0, 1.0, 2.0, 3.0] and d.flush() == 4.0 and d.bytes_per_read == 4
+    assert DeferredScalar("cpu").flush() is None
