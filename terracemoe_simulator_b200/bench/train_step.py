@@ -8,7 +8,8 @@ Default shape: 16-layer decoder, d_model 2048, 16 heads, 64 SwiGLU experts of hi
 layer (every layer between a dense first and a dense last layer), top-4 in 2 of 4 routing groups,
 one shared expert, 8 sequences of 4096 tokens per GPU, bf16 parameters, AdamW.  One step =
 pinned host -> device copy of the token batch, forward, loss, backward, gradient average of the
-replicated parameters over the ranks, optimizer step, device -> host read of the loss.  With N
+replicated parameters over the ranks, optimizer step, device -> host read of the loss (consumed one step later so that the host keeps
+launching ahead).  With N
 ranks the routed experts are sharded N ways (``--ep one_hop | two_hop``, fused peer-memory
 kernels unless ``--nccl``) and every rank trains on its own sequences (weak scaling).
 
@@ -102,8 +103,9 @@ def main(argv=None) -> int:
     state = {"i": 0, "loss": 0.0}
 
     import itertools
-    from ..utils.prefetch import DevicePrefetcher
+    from ..utils.prefetch import DeferredScalar, DevicePrefetcher
     feed = DevicePrefetcher(itertools.cycle(host), device)
+    losses = DeferredScalar(device)          # every step's loss reaches the host, one step late
 
     def step():
         tok = next(feed)
@@ -113,7 +115,9 @@ def main(argv=None) -> int:
         loss.backward()
         sync.sync()
         opt.step()
-        state["loss"] = loss.item()              # device -> host read of the result
+        prev = losses.push(loss)                 # device -> host read of the result (deferred)
+        if prev is not None:
+            state["loss"] = prev
 
     def barrier():
         if cuda:
@@ -132,6 +136,7 @@ def main(argv=None) -> int:
     t0 = time.perf_counter()
     for _ in range(ns.steps):
         step()
+    state["loss"] = losses.flush()               # the last step's loss, inside the timed region
     if cuda:
         b.record()
     barrier()
