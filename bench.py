@@ -18,7 +18,7 @@ sides; the 2.2 GB of expert weights per step exceed the 126 MB L2, so no L2 flus
 The ``e2e`` entry repeats the measurement through the public API with a pinned-host -> device
 copy of the step's tokens (issued one step ahead on a side stream by the package's
 ``DevicePrefetcher``) and a device -> host read of every step's loss inside the timed region
-(``DeferredScalar``: a non-blocking copy to pinned memory, consumed one step later, so the host
+(``DeferredScalar``: a non-blocking copy to pinned memory, consumed three steps later, so the host
 keeps launching ahead of the device; the last value is read before the closing synchronize).
 ``--impl reference`` runs the unmodified reference (``baseline/_ref``: a plain copy of its
 ``terrace`` package, it has no build system to install) through ``ep_moe_forward`` /
@@ -193,7 +193,7 @@ def run_ours(args, rank, world, local):
     from terracemoe_simulator_b200.utils.prefetch import DeferredScalar, DevicePrefetcher
     host_batches = [x_host] + [x_host.clone().pin_memory() for _ in range(2)]
     feed = DevicePrefetcher(itertools.cycle(host_batches), device)
-    losses = DeferredScalar(device)      # every step's loss is read on the host, one step late
+    losses = DeferredScalar(device, lag=3)   # every step's loss is read on the host, 3 steps late
 
     def make_step(path, e2e: bool):
         runner = runners[path]

@@ -71,14 +71,18 @@ class DeferredScalar:
     """Device-to-host read of a per-step scalar (loss, metric) that does not stall the launch queue.
 
     ``push(t)`` starts a non-blocking copy of the 0-d tensor ``t`` into pinned host memory and
-    returns the value pushed one call earlier (``None`` the first time), waiting only for that
-    older copy; ``flush()`` waits for and returns the last one.  Every step's value reaches the host,
-    one step late, while the host keeps launching ahead of the device."""
+    returns the value pushed ``lag`` calls earlier (``None`` until then), waiting only for that
+    older copy; ``flush()`` waits for the copies still in flight and returns the newest value.
+    Every step's value reaches the host, ``lag`` steps late, while the host keeps launching ahead
+    of the device (a lag of one bounds the run-ahead to a single step, which leaves no slack for
+    host jitter when several ranks wait on one another)."""
 
-    def __init__(self, device, dtype=torch.float32):
+    def __init__(self, device, dtype=torch.float32, lag: int = 1):
         self.cuda = torch.device(device).type == "cuda"
-        self.slots = [torch.zeros((), dtype=dtype, pin_memory=self.cuda) for _ in range(2)]
-        self.events = [None, None]
+        self.lag = max(1, lag)
+        n = self.lag + 1
+        self.slots = [torch.zeros((), dtype=dtype, pin_memory=self.cuda) for _ in range(n)]
+        self.events = [None] * n
         self.n = 0
         self.bytes_per_read = self.slots[0].element_size()
 
@@ -88,8 +92,9 @@ class DeferredScalar:
         return float(self.slots[i])
 
     def push(self, t):
-        i = self.n & 1
-        prev = self._take(i ^ 1) if self.n > 0 else None
+        n_slots = len(self.slots)
+        i = self.n % n_slots
+        prev = self._take((self.n - self.lag) % n_slots) if self.n >= self.lag else None
         self.slots[i].copy_(t.detach().to(self.slots[i].dtype), non_blocking=True)
         if self.cuda:
             self.events[i] = torch.cuda.Event()
@@ -98,4 +103,9 @@ class DeferredScalar:
         return prev
 
     def flush(self):
-        return self._take((self.n - 1) & 1) if self.n > 0 else None
+        if self.n == 0:
+            return None
+        last = None
+        for j in range(max(0, self.n - self.lag), self.n):
+            last = self._take(j % len(self.slots))
+        return last

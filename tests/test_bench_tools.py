@@ -137,3 +137,6 @@ def test_deferred_scalar_reads_every_value_one_step_late():
     out = [d.push(torch.tensor(float(i))) for i in range(5)]
     assert out == [None, 0.0, 1.0, 2.0, 3.0] and d.flush() == 4.0 and d.bytes_per_read == 4
     assert DeferredScalar("cpu").flush() is None
+    d3 = DeferredScalar("cpu", lag=3)
+    out = [d3.push(torch.tensor(float(i))) for i in range(6)]
+    assert out == [None, None, None, 0.0, 1.0, 2.0] and d3.flush() == 5.0
