@@ -340,16 +340,27 @@ class _Attention(torch.autograd.Function):
         return dq, dk, dv, None, None
 
 
-def attention_shape_supported(q) -> bool:
-    return (q.is_cuda and q.dtype == torch.bfloat16 and q.dim() == 4 and q.shape[-2] % 128 == 0
-            and q.shape[-1] in (64, 128))
+def attention_shape_supported(q, causal: bool = True) -> bool:
+    return (q.is_cuda and q.dtype == torch.bfloat16 and q.dim() == 4
+            and (causal or q.shape[-2] % 128 == 0) and q.shape[-1] in (64, 128))
 
 
 def attention(q, k, v, causal: bool = True, scale: float | None = None):
-    """Self-attention on [B, H, S, D] bf16 tensors (S a multiple of 128, D 64 or 128)."""
+    """Self-attention on [B, H, S, D] bf16 tensors, D 64 or 128.  The kernels work on blocks of
+    128 positions; a causal sequence of any other length is padded with zero rows at the end,
+    which the mask hides from every real query (the padded queries' outputs are dropped and
+    receive zero gradient), so the result is exact.  Without a mask S must be a multiple of 128."""
     if scale is None:
         scale = q.shape[-1] ** -0.5
-    return _Attention.apply(q, k, v, causal, scale)
+    S = q.shape[-2]
+    pad = (-S) % 128
+    if pad == 0:
+        return _Attention.apply(q, k, v, causal, scale)
+    if not causal:
+        raise ValueError("attention without a causal mask needs a sequence length that is a "
+                         "multiple of 128")
+    qp, kp, vp = (torch.nn.functional.pad(t, (0, 0, 0, pad)) for t in (q, k, v))
+    return _Attention.apply(qp, kp, vp, True, scale)[..., :S, :]
 
 
 def attention_supported(x, n_heads) -> bool:
@@ -362,4 +373,4 @@ def attention_supported(x, n_heads) -> bool:
     if not (x.is_cuda and x.dtype == torch.bfloat16 and x.dim() == 3):
         return False
     hd = x.shape[-1] // n_heads
-    return x.shape[1] % 128 == 0 and hd in (64, 128)
+    return hd in (64, 128)           # any length: the causal wrapper pads to blocks of 128

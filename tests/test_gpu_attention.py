@@ -68,3 +68,23 @@ def test_decoder_attention_uses_native_kernel(native_ops):
     loss.backward()
     assert native.LIVE["attention"] == before + 2 and torch.isfinite(loss)
     assert native_ops.take_status() == 0
+
+
+@pytest.mark.parametrize("S", [77, 200, 129])
+def test_causal_attention_of_any_length(native_ops, S):
+    """Lengths that are not a multiple of 128 are padded behind the causal mask: exact result."""
+    torch.manual_seed(2)
+    q, k, v = (torch.randn(2, 2, S, 64, device=DEV).bfloat16().requires_grad_(True) for _ in range(3))
+    o = native_ops.attention(q, k, v, causal=True)
+    assert o.shape == q.shape
+    go = torch.randn_like(o)
+    o.backward(go)
+    ro, (qf, kf, vf), _ = _ref(q, k, v, True)
+    ro.backward(go.float())
+    _close(o, ro)
+    _close(q.grad, qf.grad)
+    _close(k.grad, kf.grad)
+    _close(v.grad, vf.grad)
+    with pytest.raises(ValueError):
+        native_ops.attention(q, k, v, causal=False)
+    assert native_ops.take_status() == 0
