@@ -1,0 +1,12 @@
+"""Forwarder to ``terracemoe_simulator_b200.sim.platforms``; ``python -m sim.platforms`` runs that module's entry point."""
+from terracemoe_simulator_b200.sim.platforms import *  # noqa: F401,F403
+from terracemoe_simulator_b200.sim import platforms as _impl
+
+
+def __getattr__(name):
+    return getattr(_impl, name)
+
+
+if __name__ == "__main__":
+    import runpy
+    runpy.run_module("terracemoe_simulator_b200.sim.platforms", run_name="__main__")

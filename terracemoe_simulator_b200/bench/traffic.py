@@ -13,13 +13,13 @@ import torch
 def dispatch_traffic(group_idx: torch.Tensor, src_card: torch.Tensor, cfg,
                      cards_per_group: int) -> torch.Tensor:
     """``group_idx[T, M]`` destination groups per token, ``src_card[T]`` the card holding each
-    token -> ``[N_g, N_g]`` int64 message counts (token-level dedup: one per (token, group))."""
+    token -> ``[N_g, N_g]`` message counts as float32 (token-level dedup: one per (token, group))."""
     n = cfg.n_groups
     src_group = torch.div(src_card, cards_per_group, rounding_mode="floor").long()
     T, M = group_idx.shape
     flat = (src_group.unsqueeze(1).expand(T, M) * n + group_idx.long()).reshape(-1)
-    out = torch.zeros(n * n, dtype=torch.int64, device=group_idx.device)
-    out.scatter_add_(0, flat, torch.ones_like(flat))
+    out = torch.zeros(n * n, dtype=torch.float32, device=group_idx.device)
+    out.scatter_add_(0, flat, torch.ones_like(flat, dtype=torch.float32))
     return out.view(n, n)
 
 

@@ -126,11 +126,21 @@ class HopALayout(HopASmallLayout):
                 f"id_1d={self.id_1d}, dtype={self.dtype}, words={self.words})")
 
 
+class PackMismatch(RuntimeError, TypeError, ValueError):
+    """A plane handed to a packer has the wrong dtype, shape or row count.  It is a RuntimeError
+    (what the reference raises here), and also a TypeError / ValueError for callers that tell
+    the two kinds of mistake apart."""
+
+
+class PackAliasError(RuntimeError, AssertionError):
+    """An unpacked plane still shares storage with its container."""
+
+
 def _check_ids(ids: torch.Tensor, n: int):
     if ids.dtype != torch.int64:
-        raise TypeError(f"id plane must be int64, got {ids.dtype}")
+        raise PackMismatch(f"id plane must be int64, got {ids.dtype}")
     if ids.shape[0] != n:
-        raise ValueError(f"id plane has {ids.shape[0]} rows, expected {n}")
+        raise PackMismatch(f"id plane has {ids.shape[0]} rows, expected {n}")
     return ids.dim() == 1
 
 
@@ -142,10 +152,10 @@ def hopa_small_layout(gate_rows: torch.Tensor, ids: torch.Tensor) -> HopASmallLa
 
 def hopa_layout(payload: torch.Tensor, gate_rows: torch.Tensor, ids: torch.Tensor) -> HopALayout:
     if payload.dtype != gate_rows.dtype:
-        raise TypeError(f"payload dtype {payload.dtype} != gate dtype {gate_rows.dtype}: the full "
+        raise PackMismatch(f"payload dtype {payload.dtype} != gate dtype {gate_rows.dtype}: the full "
                         f"container holds both planes in one dtype")
     if payload.shape[0] != gate_rows.shape[0]:
-        raise ValueError("payload and gate planes disagree on the row count")
+        raise PackMismatch("payload and gate planes disagree on the row count")
     id_1d = _check_ids(ids, payload.shape[0])
     return HopALayout(payload.shape[1], gate_rows.shape[1], 1 if id_1d else ids.shape[1], id_1d,
                       payload.dtype)
@@ -224,12 +234,14 @@ def hopb_meta_words() -> int:
 
 def hopb_pack_meta(slot_idx: torch.Tensor, gate_pairs: torch.Tensor) -> torch.Tensor:
     if slot_idx.dtype != torch.int64:
-        raise TypeError(f"slot plane must be int64, got {slot_idx.dtype}")
+        raise PackMismatch(f"slot plane must be int64, got {slot_idx.dtype}")
     if slot_idx.shape != gate_pairs.shape or slot_idx.dim() != 1:
-        raise ValueError("slot and gate planes must be 1-D and of equal length")
+        raise PackMismatch("slot and gate planes must be 1-D and of equal length")
+    if not gate_pairs.is_floating_point():
+        raise PackMismatch(f"gate plane must be floating point, got {gate_pairs.dtype}")
     esz = gate_pairs.element_size()
     if esz > 8:
-        raise TypeError(f"gate dtype {gate_pairs.dtype} does not fit one word")
+        raise PackMismatch(f"gate dtype {gate_pairs.dtype} does not fit one word")
     n = slot_idx.shape[0]
     buf = torch.zeros(n, 2, dtype=torch.int64, device=slot_idx.device)
     buf[:, 0] = slot_idx
@@ -255,5 +267,5 @@ def assert_not_aliased(buf: torch.Tensor, *planes: torch.Tensor) -> None:
     base = buf.untyped_storage().data_ptr()
     for i, p in enumerate(planes):
         if p.numel() and p.untyped_storage().data_ptr() == base:
-            raise AssertionError(f"unpacked plane #{i} aliases its container; freeing the "
-                                 f"container would invalidate it")
+            raise PackAliasError(f"unpacked plane #{i} aliases its container (shared storage); "
+                                 f"freeing the container would invalidate it")

@@ -146,7 +146,11 @@ def _exchange_counts(send, group, want_async: bool):
 
 
 def _permute_core(hidden_states, probs, routing_map, *, world, rank, rpn, n_experts, intra_group,
-                  inter_group, groups_m, overlap_cb=None):
+                  inter_group, groups_m, overlap_cb=None, staged=False):
+    """Shared body of the two permute seams.  ``staged`` (the overlap seam) cuts the autograd graph
+    at Hop A: the payload and gate planes cross detached, outside autograd, and come back as the
+    leaves ``rx_d`` / ``rgate_d`` of a second graph; the caller replays the backward segment by
+    segment and moves the gradients across Hop A itself."""
     n_nodes = world // rpn
     if n_nodes < 2:
         raise ValueError("ta2a_permute needs at least two groups (world // rpn >= 2)")
@@ -156,6 +160,9 @@ def _permute_core(hidden_states, probs, routing_map, *, world, rank, rpn, n_expe
     x = hidden_states.reshape(-1, hidden_states.shape[-1])
     T, H = x.shape
     expert_idx, gates = routing_map_to_topk(routing_map, probs)
+    # the gate plane travels in the payload dtype (router-precision probabilities are rounded
+    # once, here, in both seams)
+    gates = gates.to(x.dtype)
     k = expert_idx.shape[1]
     u_src, u_node, counts, inverse = plan_ta2a(expert_idx, world, n_experts, rpn, groups_m)
     n_rows = u_src.shape[0]
@@ -188,8 +195,32 @@ def _permute_core(hidden_states, probs, routing_map, *, world, rank, rpn, n_expe
     send_l, recv_l = send.tolist(), recv.tolist()
 
     shared_out = None
-    mode = _pack.pack_mode()
-    if overlap_cb is not None and shared_overlap_enabled():
+    # the public switch first (callers and tests may override it), then the container form
+    mode = _pack.pack_mode() if _pack.pack_enabled() else "off"
+    stage1 = None
+    if staged:
+        # Hop A outside autograd, the payload in flight while the shared experts compute
+        if shared_overlap_enabled():
+            rx_buf, rx_work = _pack.hopa_exchange_async(payload.detach(), send_l, recv_l, hop_group)
+            if overlap_cb is not None:
+                shared_out = overlap_cb()
+            rx_work.wait()
+        else:
+            if overlap_cb is not None:
+                shared_out = overlap_cb()      # serial control arm
+            rx_buf = _a2a_raw(payload.detach(), send_l, recv_l, hop_group)
+        if mode in ("small", "full"):
+            buf, lay = _pack.hopa_pack_small(gate_tab.detach(), ids)
+            rbuf = _pack.hopa_exchange_raw(buf, send_l, recv_l, hop_group)
+            rgate_raw, rids = _pack.hopa_unpack_small(rbuf, lay)
+        else:
+            rids = _a2a_raw(ids, send_l, recv_l, hop_group)
+            rgate_raw = _a2a_raw(gate_tab.detach(), send_l, recv_l, hop_group)
+        rx = rx_buf.detach().requires_grad_(True)
+        rgate = rgate_raw.detach().requires_grad_(True)
+        stage1 = (payload, gate_tab, rx, rgate)
+        mode_payload_done = True
+    elif overlap_cb is not None and shared_overlap_enabled():
         # Hop A payload in flight while the shared experts compute
         rx_buf, rx_work = _pack.hopa_exchange_async(payload.detach(), send_l, recv_l, hop_group)
         shared_out = overlap_cb()
@@ -202,7 +233,9 @@ def _permute_core(hidden_states, probs, routing_map, *, world, rank, rpn, n_expe
         mode_payload_done = False
         rx = None
 
-    if mode == "full" and not mode_payload_done and gate_tab.dtype == payload.dtype:
+    if staged:
+        pass
+    elif mode == "full" and not mode_payload_done and gate_tab.dtype == payload.dtype:
         buf, lay = _pack.hopa_pack(payload, gate_tab, ids)
         rbuf = _pack.hopa_exchange_raw(buf, send_l, recv_l, hop_group)
         rx_raw, rgate_raw, rids = _pack.hopa_unpack(rbuf, lay)
@@ -226,7 +259,14 @@ def _permute_core(hidden_states, probs, routing_map, *, world, rank, rpn, n_expe
 
     # ---- arrival chain
     R = rx.shape[0]
-    if q is not None:
+    if q is not None and staged:
+        # the row path and the gate path must be separate graphs: the layer calls backward on
+        # each of them in turn.  Same values as the fused step: the gates are a pure gather.
+        send_buf, _gp, r_idx, slot_idx, i_send = ops.k1_arrival(
+            rx, rids.view(R, q), rgate.detach(), q, epr, rpn, my_local)
+        owner = torch.div(rids.view(R, q).reshape(-1), epr, rounding_mode="floor")
+        gate_pairs = rgate.reshape(-1)[stable_bucket_order(owner, rpn)]
+    elif q is not None:
         send_buf, gate_pairs, r_idx, slot_idx, i_send = ops.k1_arrival(
             rx, rids.view(R, q), rgate, q, epr, rpn, my_local)
     else:
@@ -269,6 +309,8 @@ def _permute_core(hidden_states, probs, routing_map, *, world, rank, rpn, n_expe
     st = TA2AState(u_src=u_src, r_idx=r_idx, order=order, R=R, T=T, hidden=H, send_l=send_l,
                    recv_l=recv_l, is_l=is_l, ir_l=ir_l, intra=intra_group, inter=hop_group,
                    dtype=x.dtype)
+    if staged:
+        return permuted, tokens_per_expert, pprobs, shared_out, st, stage1
     return permuted, tokens_per_expert, pprobs, shared_out, st
 
 
@@ -308,25 +350,62 @@ def ta2a_unpermute(expert_out, st: TA2AState, out_like):
 def ta2a_permute_overlap(hidden_states, probs, routing_map, *, world, rank, rpn, n_experts,
                          intra_group, inter_group=None, groups_m=None, save_tensors,
                          run_shared_experts=None):
-    """Like :func:`ta2a_permute`, with the Hop A payload exchange started asynchronously so that
-    ``run_shared_experts()`` computes while it is in flight.  Appends seven tensors to
-    ``save_tensors`` (hidden, probs, permuted, permuted_probs, tokens_per_expert, shared output
-    or an empty tensor, u_src) and returns ``(permuted, tpe, pprobs, shared_out, state)``."""
+    """Overlap seam, forward half, for a layer that replays its backward by hand.
+
+    Hop A runs outside autograd (asynchronously, with ``run_shared_experts()`` computing while
+    the payload is in flight) and the graph is cut there.  Seven entries are appended to
+    ``save_tensors`` at fixed positions (``ta2a_dispatch.py:750-751, 951-955`` in the reference):
+
+    0. the Hop A payload ``hidden[u_src]`` with its graph (stage 1),
+    1. the gate plane as shipped, with its graph (stage 1),
+    2. ``None`` (the seat of a host-side count tensor this implementation does not need),
+    3. ``rx_d``: the received rows as a detached leaf (input of stage 2),
+    4. ``permuted`` with the stage-2 graph (arrival step, Hop B, expert sort),
+    5. ``rgate_d``: the received gates as a detached leaf,
+    6. ``permuted_probs`` with the stage-2 graph.
+
+    The backward of the layer calls ``permuted.backward(d_permuted)`` and
+    ``permuted_probs.backward(d_probs)``, sends ``rx_d.grad`` / ``rgate_d.grad`` back over Hop A with
+    ``_a2a_raw(grad, st.recv_l, st.send_l)`` and finishes with
+    ``torch.autograd.backward([payload, gates], [d_payload, d_gates])``.
+    Returns ``(permuted, tokens_per_expert, permuted_probs, shared_out, state)``."""
     SEAM_CALLS["permute_overlap"] += 1
     _dp.tick_dispatch()
-    permuted, tpe, pprobs, shared_out, st = _permute_core(
-        hidden_states, probs, routing_map, world=world, rank=rank, rpn=rpn, n_experts=n_experts,
-        intra_group=intra_group, inter_group=inter_group, groups_m=groups_m,
-        overlap_cb=run_shared_experts)
-    empty = hidden_states.new_zeros(0)
-    save_tensors.extend([hidden_states, probs, permuted, pprobs, tpe,
-                         shared_out if shared_out is not None else empty, st.u_src])
+    with torch.enable_grad():
+        permuted, tpe, pprobs, shared_out, st, stage1 = _permute_core(
+            hidden_states, probs, routing_map, world=world, rank=rank, rpn=rpn,
+            n_experts=n_experts, intra_group=intra_group, inter_group=inter_group,
+            groups_m=groups_m, overlap_cb=run_shared_experts, staged=True)
+    payload, gate_tab, rx_d, rgate_d = stage1
+    save_tensors.extend([payload, gate_tab, None, rx_d, permuted, rgate_d, pprobs])
     return permuted, tpe, pprobs, shared_out, st
 
 
 def ta2a_unpermute_overlap(expert_out, st: TA2AState, save_tensors, out_shape=None):
-    """Return leg of the overlap seam; appends three tensors (expert_out, r_idx, order)."""
+    """Overlap seam, return half.  Appends three entries (``ta2a_dispatch.py:995-996, 1011``):
+
+    7. ``eo_d``: the expert output as a detached leaf,
+    8. ``red``: per-(token, group) sums at the representative, with the graph from ``eo_d``
+       (un-sort, Hop B reverse, reduction over the arrival pairs),
+    9. ``back_d``: the rows returned over Hop A (outside autograd) as a detached leaf, from which
+       the result ``y`` is built.
+
+    Backward by hand: ``y.backward(dy)``; ``d_red = _a2a_raw(back_d.grad, st.send_l, st.recv_l)``;
+    ``red.backward(d_red)``; ``eo_d.grad`` is the gradient of the expert output."""
     SEAM_CALLS["unpermute_overlap"] += 1
-    y = _unpermute_core(expert_out, st)
-    save_tensors.extend([expert_out, st.r_idx, st.order])
+    with torch.enable_grad():
+        eo_d = expert_out.detach().requires_grad_(True)
+        _dp.note("seam.eout", eo_d)
+        unsort = torch.empty_like(st.order)
+        unsort[st.order] = torch.arange(st.order.numel(), device=st.order.device)
+        ret = _a2a(eo_d[unsort], st.ir_l, st.is_l, st.intra)
+        red = torch.zeros(st.R, st.hidden, dtype=torch.float32, device=ret.device).index_add(
+            0, st.r_idx, ret.float()).to(ret.dtype)
+        _dp.note("seam.red", red)
+        back = _a2a_raw(red.detach(), st.recv_l, st.send_l, st.inter)
+        back_d = back.detach().requires_grad_(True)
+        y = torch.zeros(st.T, st.hidden, dtype=torch.float32, device=back.device).index_add(
+            0, st.u_src, back_d.float()).to(back.dtype)
+        _dp.note("seam.y", y)
+    save_tensors.extend([eo_d, red, back_d])
     return y.view(out_shape) if out_shape is not None else y

@@ -226,7 +226,8 @@ def profile(arch: MoEArch, machine: Machine, mem: MemoryProfile = UNMEASURED,
             "caveat": "step-level composition is behind a failing gate; the terms above are "
                       "per-call and per-layer and do not add to a step time",
             "memory_caveat": None if mep["measured"] else
-            "the residency verdict rests on an unmeasured memory profile"}
+            "the residency verdict rests on an unmeasured memory profile (docs/11-residency.md lists "
+            "what has to be measured)"}
 
 
 def sweep(base: MoEArch, machine: Machine, knob: str, values, mem: MemoryProfile = UNMEASURED):

@@ -200,13 +200,28 @@ def _seam_worker(rank, port, queue):
                 assert len(saved) == 7 and torch.equal(shared, x.detach() * 2)
             else:
                 permuted, tpe, pprobs, st = seams.ta2a_permute(x, probs, rmap, **kw)
-            eo = swiglu_experts(permuted, a, b, tpe) * pprobs.unsqueeze(-1)
             if overlap:
+                # the layer owns the backward: every segment is replayed by hand and the
+                # gradients cross Hop A through raw exchanges, outside autograd
+                from terracemoe_simulator_b200.parallel.ep import _a2a_raw
+                d_in = permuted.detach().requires_grad_(True)
+                p_in = pprobs.detach().requires_grad_(True)
+                eo = swiglu_experts(d_in, a, b, tpe) * p_in.unsqueeze(-1)
                 y = seams.ta2a_unpermute_overlap(eo, st, saved, out_shape=x.shape)
-                assert len(saved) == 10
+                assert len(saved) == 10 and saved[2] is None
+                p1g, p1p, _, p2in, p2g, p2pd, p2pg, u1in, u1g, u2in = saved
+                (y * gy).sum().backward()                                   # y <- back_d
+                u1g.backward(_a2a_raw(u2in.grad, st.send_l, st.recv_l))     # red <- eo_d
+                eo.backward(u1in.grad)                                      # experts
+                p2pg.backward(p_in.grad)                                    # gates of stage 2
+                d_gate = _a2a_raw(p2pd.grad, st.recv_l, st.send_l)
+                p2g.backward(d_in.grad)                                     # rows of stage 2
+                d_rows = _a2a_raw(p2in.grad, st.recv_l, st.send_l)
+                torch.autograd.backward([p1g, p1p], grad_tensors=[d_rows, d_gate])
             else:
+                eo = swiglu_experts(permuted, a, b, tpe) * pprobs.unsqueeze(-1)
                 y = seams.ta2a_unpermute(eo, st, x)
-            (y * gy).sum().backward()
+                (y * gy).sum().backward()
             return [t.detach().clone() for t in (y, x.grad, w.grad, a.grad, b.grad, tpe)]
 
         out = {v: run(v) for v in ("small", "off", "full", "sync")}
