@@ -40,8 +40,7 @@ def install_aliases(force: bool = False) -> None:
     for name, mod in pairs.items():
         sys.modules[f"terrace.{name}"] = mod
         setattr(terrace, name, mod)
-    sys.modules["terrace.ta2a"] = _module(
-        "terrace.ta2a", plan_ta2a=plan.plan_ta2a, dispatch_stats=plan.dispatch_stats)
+    sys.modules["terrace.ta2a"] = plan
     fwd = {k: getattr(ta2a, k) for k in ("init_ta2a_groups", "ta2a_moe_forward",
                                          "build_expansion", "fixed_hist")}
     fwd["_stable_argsort_small"] = refs.stable_bucket_order

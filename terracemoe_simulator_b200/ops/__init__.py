@@ -96,7 +96,10 @@ def _try_load() -> tuple[bool, str | None, str]:
 def _initialize() -> OpsState:
     switch = _normalized_switch()
     if switch == "0":
-        return OpsState("0", False, None, "native ops switched off")
+        raw = os.environ.get("TERRACE_CUSTOM_OPS")
+        why = "explicit off (TERRACE_CUSTOM_OPS=0)" if raw not in (None, "") else \
+            "native ops off by default on a host without CUDA"
+        return OpsState("0", False, None, why)
     ok, lib, reason = _try_load()
     if ok:
         log.info("terrace native ops loaded from %s", lib)
