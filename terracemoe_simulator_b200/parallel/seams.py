@@ -261,11 +261,9 @@ def _permute_core(hidden_states, probs, routing_map, *, world, rank, rpn, n_expe
     R = rx.shape[0]
     if q is not None and staged:
         # the row path and the gate path must be separate graphs: the layer calls backward on
-        # each of them in turn.  Same values as the fused step: the gates are a pure gather.
-        send_buf, _gp, r_idx, slot_idx, i_send = ops.k1_arrival(
-            rx, rids.view(R, q), rgate.detach(), q, epr, rpn, my_local)
-        owner = torch.div(rids.view(R, q).reshape(-1), epr, rounding_mode="floor")
-        gate_pairs = rgate.reshape(-1)[stable_bucket_order(owner, rpn)]
+        # each of them in turn (the segment variant hangs them on two disjoint autograd edges)
+        send_buf, gate_pairs, r_idx, slot_idx, i_send = ops.k1_arrival_segment(
+            rx, rids.view(R, q), rgate, q, epr, rpn, my_local)
     elif q is not None:
         send_buf, gate_pairs, r_idx, slot_idx, i_send = ops.k1_arrival(
             rx, rids.view(R, q), rgate, q, epr, rpn, my_local)
