@@ -208,7 +208,7 @@ def run_ours(args, rank, world, local):
                 x.grad = None
             y = runner(x, *params)
             if e2e:
-                loss = torch.dot(y.reshape(-1), gy_flat) * inv_n      # one reduction, fp32 accumulate
+                loss = torch.dot(y.reshape(-1).to(gy_flat.dtype), gy_flat) * inv_n   # one reduction
                 loss.backward()
                 return losses.push(loss)     # device -> host read of the result, one step deferred
             y.backward(gy)
@@ -305,7 +305,7 @@ def run_reference(args, rank, world, local):
                 y = ta2a_moe_forward(x, idx, gates.to(x.dtype), w13, w2, world, N_EXPERTS,
                                      rpn=rpn, groups_m=TOP_GROUPS)
             if e2e:
-                loss = torch.dot(y.reshape(-1), gy_flat) * inv_n      # one reduction, fp32 accumulate
+                loss = torch.dot(y.reshape(-1).to(gy_flat.dtype), gy_flat) * inv_n   # one reduction
                 loss.backward()
                 return loss.item()
             y.backward(gy)
