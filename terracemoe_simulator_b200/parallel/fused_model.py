@@ -1,0 +1,145 @@
+"""Host-side model of the fused expert-parallel step: placement arithmetic and the flag protocol.
+
+The CUDA kernels of ``ops/csrc/symm.cu`` derive, on every source rank and without any exchange
+beyond the per-expert histograms, the row of the OWNER's expert-sorted GEMM input that each
+(token, pick) lands in.  This module restates that arithmetic in plain PyTorch for all ranks in
+one process, so that it can be checked on a CPU: the positions of all sources must tile every
+owner's segments exactly (no gap, no overlap), in (expert, source rank, token) order, with
+segments aligned to ``seg_align`` rows.  It also restates the epoch-flag protocol (flags only grow;
+a wait is bounded and returns a status instead of blocking) so that a withheld flag can be tested
+without a GPU.
+
+    position(s, t, e) = segment_start(e)                       # owner-local, aligned
+                      + sum over sources s' < s of count[s'][e]
+                      + number of earlier tokens of source s that picked e
+
+There is no counterpart in the reference (its dispatch is a variable-length collective whose
+placement is implied by the split sizes, ``terrace/ep_dist.py:104-122``).
+"""
+from __future__ import annotations
+
+import torch
+
+ST_OK, ST_TIMEOUT_FLAG, ST_BAD_INDEX, ST_TIMEOUT_COUNTS = 0, 4, 5, 6
+
+
+def plan_positions(idx_per_rank, world: int, n_experts: int, seg_align: int = 64):
+    """``idx_per_rank[s]``: ``[T_s, k]`` expert ids of source rank s.  Returns a dict with
+    ``pos[s]`` / ``owner[s]`` (``[T_s, k]``), and per owner ``seg_start[o]``, ``seg_count[o]``
+    (``[epr]``) and ``rows[o]`` (rows of the owner's buffer in use, padding included)."""
+    if len(idx_per_rank) != world or n_experts % world:
+        raise ValueError("one index tensor per rank, and world must divide n_experts")
+    epr = n_experts // world
+    counts = torch.stack([torch.bincount(i.reshape(-1), minlength=n_experts) for i in idx_per_rank])
+    total = counts.sum(0)                                            # [E]
+    before = torch.cumsum(counts, 0) - counts                        # rows of lower sources, [W, E]
+    padded = (total + seg_align - 1) // seg_align * seg_align
+    seg = torch.zeros(n_experts, dtype=torch.int64)
+    for o in range(world):                                           # owner-local running offset
+        block = padded[o * epr:(o + 1) * epr]
+        seg[o * epr:(o + 1) * epr] = torch.cumsum(block, 0) - block
+    pos, owner = [], []
+    for s, idx in enumerate(idx_per_rank):
+        T, k = idx.shape
+        onehot = torch.zeros(T, n_experts, dtype=torch.int64).scatter_add_(
+            1, idx, torch.ones_like(idx))
+        if int(onehot.max()) > 1:
+            raise ValueError("a token may pick an expert at most once")
+        earlier = torch.cumsum(onehot, 0) - onehot                   # earlier tokens picking e
+        local = earlier.gather(1, idx)
+        pos.append(seg[idx] + before[s][idx] + local)
+        owner.append(torch.div(idx, epr, rounding_mode="floor"))
+    return {"pos": pos, "owner": owner,
+            "seg_start": [seg[o * epr:(o + 1) * epr].clone() for o in range(world)],
+            "seg_count": [total[o * epr:(o + 1) * epr].clone() for o in range(world)],
+            "rows": [int(padded[o * epr:(o + 1) * epr].sum()) for o in range(world)]}
+
+
+def check_tiling(plan, idx_per_rank, world: int, n_experts: int) -> None:
+    """Every owner's segment of expert e is covered exactly once, in (source, token) order."""
+    epr = n_experts // world
+    for o in range(world):
+        taken = torch.zeros(max(plan["rows"][o], 1), dtype=torch.int64)
+        keys = []                                                    # (row, expert, source, token)
+        for s, idx in enumerate(idx_per_rank):
+            mine = plan["owner"][s] == o
+            rows = plan["pos"][s][mine]
+            taken.scatter_add_(0, rows, torch.ones_like(rows))
+            tok = torch.arange(idx.shape[0]).unsqueeze(1).expand_as(idx)[mine]
+            keys += list(zip(rows.tolist(), idx[mine].tolist(), [s] * rows.numel(), tok.tolist()))
+        if int(taken.max()) > 1:
+            raise AssertionError(f"owner {o}: two picks share a row")
+        for le in range(epr):
+            a, n = int(plan["seg_start"][o][le]), int(plan["seg_count"][o][le])
+            if n and not bool((taken[a:a + n] == 1).all()):
+                raise AssertionError(f"owner {o} expert {o * epr + le}: segment has a gap")
+        keys.sort()
+        order = [(e, s, t) for _, e, s, t in keys]
+        if order != sorted(order):
+            raise AssertionError(f"owner {o}: rows are not in (expert, source, token) order")
+
+
+def one_hop_model(x_per_rank, idx_per_rank, gates_per_rank, w13, w2, group_size: int,
+                  seg_align: int = 64):
+    """The whole one-hop step on the host: push rows to their positions, grouped SwiGLU per
+    segment, pull back and reduce with the canonical tree (per group ascending, one rounding per
+    level).  ``w13[E, H, 2d]``, ``w2[E, d, H]`` hold all experts.  Returns ``y`` per rank."""
+    world, E = len(x_per_rank), w13.shape[0]
+    epr = E // world
+    plan = plan_positions(idx_per_rank, world, E, seg_align)
+    H, dt = x_per_rank[0].shape[1], x_per_rank[0].dtype
+    xin = [torch.zeros(max(plan["rows"][o], 1), H, dtype=dt) for o in range(world)]
+    for s, x in enumerate(x_per_rank):
+        for o in range(world):
+            mine = plan["owner"][s] == o
+            tok = torch.arange(x.shape[0]).unsqueeze(1).expand_as(mine)[mine]
+            xin[o][plan["pos"][s][mine]] = x[tok]
+    yout = []
+    for o in range(world):
+        out = torch.zeros_like(xin[o])
+        for le in range(epr):
+            a, n = int(plan["seg_start"][o][le]), int(plan["seg_count"][o][le])
+            if n:
+                gate, up = (xin[o][a:a + n] @ w13[o * epr + le]).chunk(2, dim=-1)
+                out[a:a + n] = (torch.nn.functional.silu(gate) * up) @ w2[o * epr + le]
+        yout.append(out)
+    ys = []
+    for s, x in enumerate(x_per_rank):
+        idx, gates = idx_per_rank[s], gates_per_rank[s]
+        order = torch.argsort(idx, dim=1, stable=True)               # experts ascending per token
+        e_sorted, g_sorted = idx.gather(1, order), gates.gather(1, order)
+        p_sorted, o_sorted = plan["pos"][s].gather(1, order), plan["owner"][s].gather(1, order)
+        y = torch.zeros(x.shape[0], H, dtype=torch.float32)
+        group = torch.div(e_sorted, group_size, rounding_mode="floor")
+        for g in torch.unique(group).tolist():                       # groups ascending
+            part = torch.zeros_like(y)
+            for j in range(idx.shape[1]):                            # experts ascending inside
+                sel = group[:, j] == g
+                rows = torch.stack([yout[int(o)][int(p)] for o, p in
+                                    zip(o_sorted[sel, j], p_sorted[sel, j])]) if sel.any() else None
+                if rows is not None:
+                    part[sel] += g_sorted[sel, j].float().unsqueeze(1) * rows.float()
+            y += part.to(dt).float()                                 # one rounding per level
+        ys.append(y.to(dt))
+    return ys
+
+
+class EpochFlags:
+    """Flags of one arena: ``flag[kind][src]`` holds the last epoch that source signalled.
+    ``signal`` never lowers a flag; ``wait`` polls a bounded number of times and returns a status
+    code (``ST_OK`` or the timeout code) instead of blocking."""
+
+    def __init__(self, kinds: int, world: int):
+        self.flags = [[0] * world for _ in range(kinds)]
+
+    def signal(self, kind: int, src: int, epoch: int) -> None:
+        self.flags[kind][src] = max(self.flags[kind][src], epoch)
+
+    def wait(self, kind: int, sources, epoch: int, max_polls: int = 1000,
+             timeout_code: int = ST_TIMEOUT_FLAG, on_poll=None) -> int:
+        for _ in range(max_polls):
+            if all(self.flags[kind][s] >= epoch for s in sources):
+                return ST_OK
+            if on_poll is not None:
+                on_poll()
+        return timeout_code

@@ -1,0 +1,101 @@
+"""Host model of the fused expert-parallel step: placement tiling, numerics, flag protocol."""
+import pytest
+import torch
+
+from terracemoe_simulator_b200.parallel import fused_model as fm
+from terracemoe_simulator_b200.routing import TRouteConfig, t_route
+
+
+def _routing(world, T, E, n_groups, k, M, seed):
+    cfg = TRouteConfig(E, n_groups, k, M)
+    out = []
+    for r in range(world):
+        g = torch.Generator().manual_seed(seed + r)
+        idx, gates, _ = t_route(torch.rand(T + 7 * r, E, generator=g), torch.zeros(E), cfg)
+        out.append((idx, gates))
+    return cfg, out
+
+
+@pytest.mark.parametrize("world,E,n_groups,k,M,align", [(4, 16, 4, 4, 2, 64), (8, 64, 4, 6, 2, 64),
+                                                      (2, 8, 2, 2, 2, 1), (1, 8, 4, 4, 2, 64)])
+def test_positions_tile_every_owner_segment(world, E, n_groups, k, M, align):
+    _, routed = _routing(world, 50, E, n_groups, k, M, seed=3)
+    idx = [i for i, _ in routed]
+    plan = fm.plan_positions(idx, world, E, align)
+    fm.check_tiling(plan, idx, world, E)
+    epr = E // world
+    for o in range(world):
+        assert all(int(s) % align == 0 for s in plan["seg_start"][o])
+        assert plan["rows"][o] % align == 0
+        total = sum(int((i // epr == o).sum()) for i in idx)
+        assert int(plan["seg_count"][o].sum()) == total
+
+
+def test_check_tiling_catches_a_wrong_plan():
+    _, routed = _routing(2, 20, 8, 2, 2, 2, seed=1)
+    idx = [i for i, _ in routed]
+    plan = fm.plan_positions(idx, 2, 8, 64)
+    plan["pos"][1][0, 0] = plan["pos"][0][0, 0] if int(plan["owner"][0][0, 0]) == int(
+        plan["owner"][1][0, 0]) else plan["pos"][1][0, 0] + 1
+    with pytest.raises(AssertionError):
+        fm.check_tiling(plan, idx, 2, 8)
+    with pytest.raises(ValueError):
+        fm.plan_positions([torch.tensor([[1, 1]])], 1, 4)            # an expert picked twice
+
+
+def test_one_hop_model_matches_the_dense_definition():
+    torch.manual_seed(0)
+    world, E, H, d = 4, 16, 32, 16
+    cfg, routed = _routing(world, 24, E, 4, 4, 2, seed=9)
+    w13 = torch.randn(E, H, 2 * d) * H ** -0.5
+    w2 = torch.randn(E, d, H) * d ** -0.5
+    xs = [torch.randn(i.shape[0], H) for i, _ in routed]
+    ys = fm.one_hop_model(xs, [i for i, _ in routed], [g for _, g in routed], w13, w2,
+                          cfg.group_size)
+    for x, (idx, gates), y in zip(xs, routed, ys):
+        ref = torch.zeros_like(x)
+        for t in range(x.shape[0]):
+            for j in range(idx.shape[1]):
+                e = int(idx[t, j])
+                a, b = (x[t] @ w13[e]).chunk(2)
+                ref[t] += gates[t, j] * ((torch.nn.functional.silu(a) * b) @ w2[e])
+        torch.testing.assert_close(y, ref, rtol=1e-4, atol=1e-5)
+
+
+def test_model_does_not_depend_on_how_tokens_are_split_over_ranks():
+    """The same tokens on 1 rank or spread over 4 give the same output rows, bit for bit:
+    placement only decides where a row is computed, never what is added to what."""
+    torch.manual_seed(1)
+    E, H, d = 16, 32, 16
+    cfg = TRouteConfig(E, 4, 4, 2)
+    x = torch.randn(40, H).bfloat16()
+    idx, gates, _ = t_route(torch.rand(40, E), torch.zeros(E), cfg)
+    w13 = (torch.randn(E, H, 2 * d) * H ** -0.5).bfloat16()
+    w2 = (torch.randn(E, d, H) * d ** -0.5).bfloat16()
+    gates = gates.bfloat16()
+    whole = fm.one_hop_model([x], [idx], [gates], w13, w2, cfg.group_size)[0]
+    parts = fm.one_hop_model(list(x.chunk(4)), list(idx.chunk(4)), list(gates.chunk(4)),
+                             w13, w2, cfg.group_size)
+    assert torch.equal(torch.cat(parts), whole)
+
+
+def test_epoch_flags_bounded_wait_and_monotone_epochs():
+    flags = fm.EpochFlags(kinds=3, world=4)
+    for s in range(4):
+        flags.signal(1, s, epoch=5)
+    assert flags.wait(1, range(4), epoch=5) == fm.ST_OK
+    assert flags.wait(1, range(4), epoch=4) == fm.ST_OK               # older epochs stay satisfied
+    flags.signal(1, 2, epoch=3)                                       # a stale signal never lowers
+    assert flags.wait(1, range(4), epoch=5) == fm.ST_OK
+    # a rank that never signals: the wait gives up with a status instead of blocking
+    polls = []
+    status = flags.wait(1, range(4), epoch=6, max_polls=50, on_poll=lambda: polls.append(1))
+    assert status == fm.ST_TIMEOUT_FLAG and len(polls) == 50
+    assert flags.wait(2, [0], epoch=1, max_polls=3, timeout_code=fm.ST_TIMEOUT_COUNTS) \
+        == fm.ST_TIMEOUT_COUNTS
+    # the late rank arrives during the wait
+    late = iter(range(10))
+    status = flags.wait(1, range(4), epoch=6, max_polls=50,
+                        on_poll=lambda: [flags.signal(1, s, 6) for s in range(4)]
+                        if next(late) == 3 else None)
+    assert status == fm.ST_OK
