@@ -99,7 +99,13 @@ def _phase_spans():
     return [s.splits_sync, s.hop_a, s.arrival_chain, s.hop_b, s.combine]
 
 
+def _b200_step_worst():
+    from terracemoe_simulator_b200.sim import b200_step
+    return [100 * b200_step.validate(verbose=False)[1]["worst"]]
+
+
 CLAIMS = [
+    ("docs/05-simulator.md", "the worst error is {n} %", _b200_step_worst, 0.06),
     ("docs/03-applicability.md", "2.49 with the PyTorch arrival chain, 1.49 with the fused-kernel "
      "target and 1.10 with zero implementation overhead".replace("2.49", "{n}", 1)
      .replace("1.49", "{n}", 1).replace("1.10", "{n}", 1), _breakevens, 0.015),

@@ -287,3 +287,18 @@ def test_b200_platform_and_gate():
     g2 = core.MoEGeometry("r2", 4, 2, 6, 2, H=4096, seq=4096, gbs=8 * 4096)
     assert core.two_hop_call(c, g1) < core.one_hop_call(c, g1)
     assert core.two_hop_call(c, g2) > 0.9 * core.one_hop_call(c, g2)
+
+
+def test_b200_step_model_within_gate():
+    from terracemoe_simulator_b200.sim import b200_step
+    ok, d = b200_step.validate(verbose=False)
+    assert ok and d["worst"] <= b200_step.GATE and len(d["rows"]) == 5
+    g1, g8 = b200_step.gemm_ms(1), b200_step.gemm_ms(8)
+    assert g1["tile_efficiency"] < 0.9 < g8["tile_efficiency"] <= 1.0
+    assert g1["wgrad_tflops"] == pytest.approx(b200_step.TFLOPS_WGRAD_SHORT, rel=1e-6)
+    assert g8["ms"] < g1["ms"]
+    # the two-hop path is predicted (and measured) faster than one-hop at 2 and at 8 GPUs
+    for n, rpn in ((2, 1), (8, 2)):
+        assert b200_step.predict_ms(n, rpn, "two_hop")["total_ms"] \
+            < b200_step.predict_ms(n, rpn, "one_hop")["total_ms"]
+        assert b200_step.MEASURED_MS[(n, rpn, "two_hop")] < b200_step.MEASURED_MS[(n, rpn, "one_hop")]
