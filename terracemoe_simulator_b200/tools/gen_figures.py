@@ -5,7 +5,8 @@
 Figures are SVG text written by ``tools/svgplot.py`` (no plotting library is needed), byte-for-byte
 reproducible: running twice gives identical files.  The set follows the reference's three
 generators (``tools/gen_figures.py``, ``tools/gen_route_figures.py``, ``tools/gen_sim_figures.py``):
-published routing results (f1, f5), cost-model figures computed live (f7-f11, f13, f16), routing
+published routing results (f1-f6, data in `tools/route_results.py`), cost-model figures computed
+live (f7-f11, f13, f16), the one-sided comparison from the B200 sweep (f12), routing
 figures computed live from ``routing.t_route`` (f14, f15), plus two figures of this package's own
 measurements on 8 x B200 (f17 measured against modelled two-hop/one-hop ratio, f18 dispatch +
 combine time against tokens per GPU).
@@ -18,29 +19,83 @@ import sys
 
 from .svgplot import Chart, heatmap
 
-# Published routing-quality results of the reference (13.14B total / 1.33B active parameters,
-# 4 seeds x 62.9B tokens): loss cost in nats against unconstrained top-k, with 95 % intervals,
-# and the step-time effect G of constrained routing (README.md:122-126, docs/06-troute-results.md:62-66).
-ROUTE_LOSS_COST = [("full", 0.00339, 0.00224, 0.00455), ("group_limited", 0.00276, None, None),
-                   ("quota_only", 0.00895, None, None)]
-ROUTE_STEP_G = [0.9882, 1.0070]
+from . import route_results as rr
 
 
 def f1_loss_axis():
-    c = Chart("f1  Loss cost of constrained routing against unconstrained top-k",
-              "routing mode", "extra loss (nats)", xcats=[r[0] for r in ROUTE_LOSS_COST])
-    c.bars([r[1] for r in ROUTE_LOSS_COST], color="#1f77b4")
-    lo, hi = ROUTE_LOSS_COST[0][2], ROUTE_LOSS_COST[0][3]
-    c.note("full: +%.5f nats, 95%% interval [%+.5f, %+.5f]" % (ROUTE_LOSS_COST[0][1], lo, hi))
+    c = Chart("f1  Loss cost of constrained routing against unconstrained top-k (90 % intervals)",
+              "routing mode", "extra loss (nats)", xcats=list(rr.MODES), width=700)
+    for i, (readout, color) in enumerate((("20k", "#9ecae1"), ("30k", "#1f77b4"))):
+        c.bars([rr.LOSS_COST[readout][m][0] for m in rr.MODES], label="read out at " + readout,
+               color=color, group=i, n_groups=2)
+    lo, hi = rr.LOSS_COST["20k"]["full"][1:]
+    c.note("full at 20k: +%.5f nats [%+.5f, %+.5f]; %.0f %% of what the quota alone costs"
+           % (rr.LOSS_COST["20k"]["full"][0], lo, hi, 100 * rr.conjunction_cost_share()))
+    return c.render()
+
+
+def f2_per_seed():
+    c = Chart("f2  The same loss differences per seed", "seed", "extra loss (nats)",
+              xcats=["seed 1", "seed 2", "seed 3", "seed 4"], width=700)
+    for m, color in zip(rr.MODES, ("#2ca02c", "#d62728", "#1f77b4")):
+        c.line(range(4), rr.PER_SEED["20k"][m], label=m + " @20k", color=color)
+        c.line(range(4), rr.PER_SEED["30k"][m], label=m + " @30k", color=color, dash="4,3")
+    c.hline(0.0, None)
+    return c.render()
+
+
+def f3_downstream():
+    names = list(rr.DOWNSTREAM_PP)
+    c = Chart("f3  Downstream accuracy of T-Route against top-k (percentage points)", "task",
+              "difference (pp)", xcats=names)
+    c.bars([rr.DOWNSTREAM_PP[n][0] for n in names], color="#1f77b4", label="mean difference")
+    c.hline(rr.EQUIVALENCE_PP, "equivalence bounds +-%.1f pp" % rr.EQUIVALENCE_PP, "#d62728")
+    c.hline(-rr.EQUIVALENCE_PP, None, "#d62728")
+    c.note("90 % intervals: " + "; ".join("%s [%+.3f, %+.3f]" % (n, *rr.DOWNSTREAM_PP[n][1:])
+                                          for n in names))
+    return c.render()
+
+
+def f4_load_axis():
+    c = Chart("f4  Load balance against top-k: entropy and coefficient of variation", "routing mode",
+              "difference", xcats=list(rr.MODES), width=700)
+    c.bars([rr.LOAD_ENTROPY[m][0] for m in rr.MODES], label="load entropy", color="#2ca02c",
+           group=0, n_groups=2)
+    c.bars([rr.LOAD_CV[m][0] for m in rr.MODES], label="load CV", color="#ff7f0e", group=1,
+           n_groups=2)
+    c.hline(0.0, None)
     return c.render()
 
 
 def f5_step_neutral():
     c = Chart("f5  Step-time effect of T-Route alone (two runs)", "run", "G = t(top-k) / t(T-Route)",
               xcats=["run 1", "run 2", "mean"])
-    mean = sum(ROUTE_STEP_G) / len(ROUTE_STEP_G)
-    c.bars(ROUTE_STEP_G + [mean], color="#2ca02c").hline(1.0, "neutral")
+    mean = sum(rr.STEP_G) / len(rr.STEP_G)
+    c.bars(list(rr.STEP_G) + [mean], color="#2ca02c").hline(1.0, "neutral")
     c.ylim = (0.95, 1.03)
+    return c.render()
+
+
+def f6_forerunner():
+    names = [m[0] for m in rr.FORERUNNER]
+    c = Chart("f6  Small-scale forerunner: hold-out loss of the four modes", "routing mode",
+              "hold-out loss", xcats=names, width=700)
+    c.bars([m[1] for m in rr.FORERUNNER], color="#1f77b4")
+    c.ylim = (6.024, 6.036)
+    c.note("load entropy: " + ", ".join("%s %.3f" % (m[0], m[3]) for m in rr.FORERUNNER))
+    return c.render()
+
+
+def f12_onesided():
+    from ..sim import calibrate
+    rows = sorted((r["tokens"], r["one_hop_ms"], r["nccl_a2a_x2_ms"])
+                  for r in calibrate.load_b200_sweep() if r["q"] == 3 and r["R"] == 2)
+    c = Chart("f12  One-sided peer-memory stores against the collective, 8 x B200 (there + back)",
+              "tokens per GPU", "collective time / one-sided time", xlog=True)
+    c.line([r[0] for r in rows], [r[2] / r[1] for r in rows], label="NCCL all-to-all x2 / fused one-hop")
+    c.hline(1.15, "criterion 1.15", "#d62728")
+    c.hline(1.0, "parity")
+    c.note("reference machine: 0.68 (collective wins)")
     return c.render()
 
 
@@ -201,10 +256,13 @@ def f18_b200_dispatch():
 
 
 FIGURES = {
-    "f1-loss-axis": f1_loss_axis, "f5-step-neutral": f5_step_neutral,
+    "f1-loss-axis": f1_loss_axis, "f2-per-seed": f2_per_seed, "f3-downstream": f3_downstream,
+    "f4-load-axis": f4_load_axis, "f5-step-neutral": f5_step_neutral,
+    "f6-forerunner": f6_forerunner,
     "f7-overlap-families": f7_overlap_families, "f8-breakeven-map": f8_breakeven_map,
     "f9-uncertainty": f9_uncertainty, "f10-scale-alpha": f10_scale_alpha,
-    "f11-verdict-bed": f11_verdict_bed, "f13-platform-map": f13_platform_map,
+    "f11-verdict-bed": f11_verdict_bed, "f12-onesided": f12_onesided,
+    "f13-platform-map": f13_platform_map,
     "f14-routing-modes": f14_routing_modes, "f15-routing-costs": f15_routing_costs,
     "f16-launch-cost": f16_launch_cost, "f17-b200-ratio": f17_b200_ratio,
     "f18-b200-dispatch": f18_b200_dispatch,

@@ -96,7 +96,7 @@ def test_figures_reproducible_and_wellformed(tmp_path):
     from terracemoe_simulator_b200.tools import gen_figures
     first = gen_figures.generate(str(tmp_path / "a"))
     second = gen_figures.generate(str(tmp_path / "b"))
-    assert len(first) == len(gen_figures.FIGURES) >= 13
+    assert len(first) == len(gen_figures.FIGURES) >= 18
     for pa, pb in zip(first, second):
         ta, tb = open(pa).read(), open(pb).read()
         assert ta == tb and "nan" not in ta
@@ -140,3 +140,18 @@ def test_deferred_scalar_reads_every_value_one_step_late():
     d3 = DeferredScalar("cpu", lag=3)
     out = [d3.push(torch.tensor(float(i))) for i in range(6)]
     assert out == [None, None, None, 0.0, 1.0, 2.0] and d3.flush() == 5.0
+
+
+def test_route_results_record_is_consistent():
+    from terracemoe_simulator_b200.tools import route_results as rr
+    assert abs(rr.conjunction_cost_share() - 0.38) < 0.005           # "38 % of the quota alone"
+    for readout in ("20k", "30k"):
+        for mode in rr.MODES:
+            mean, lo, hi = rr.LOSS_COST[readout][mode]
+            assert lo < mean < hi
+            seeds = rr.PER_SEED[readout][mode]
+            assert len(seeds) == 4 and abs(sum(seeds) / 4 - mean) < 2e-4
+    assert all(abs(v[0]) < rr.EQUIVALENCE_PP and -rr.EQUIVALENCE_PP < v[1] and v[2] < rr.EQUIVALENCE_PP
+               for v in rr.DOWNSTREAM_PP.values())
+    assert abs(sum(rr.STEP_G) / 2 - 0.9976) < 1e-4
+    assert max(m[3] for m in rr.FORERUNNER) == dict((m[0], m[3]) for m in rr.FORERUNNER)["full"]
