@@ -147,3 +147,78 @@ def test_fused_groups_of_several_gpus(native_ops, world, rpn, M):
         for a, b in zip(res["one_hop"], res["ref"]):
             _close(a, b)
         _close(echo, x0, 2e-2)
+
+
+def _model_worker(rank, world, port, queue):
+    import torch.distributed as dist
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    os.environ["NCCL_NVLS_ENABLE"] = "0"
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world,
+                            device_id=torch.device("cuda", rank))
+    try:
+        from terracemoe_simulator_b200.parallel import fused as fz
+        from terracemoe_simulator_b200.parallel import fused_model as fm
+        from terracemoe_simulator_b200.routing import TRouteConfig, t_route
+        dev = torch.device("cuda", rank)
+        E, k, H, T = 16, 4, 256, 300 + 11 * rank
+        cfg = TRouteConfig(E, max(world, 2), k, 2)
+        g = torch.Generator().manual_seed(40 + rank)
+        x = torch.randn(T, H, generator=g).bfloat16().to(dev)
+        idx, gates, _ = t_route(torch.rand(T, E, generator=g).to(dev), torch.zeros(E, device=dev), cfg)
+        fctx = fz.FusedEPContext(cfg, H, 128, 400, world=world, rank=rank, rpn=1, device=dev)
+        ep = fctx.next_epoch()
+        p = fz._plan(fctx, idx, gates, "one_hop", ep)
+        fz._dispatch(fctx, p, x, "one_hop", ep)
+        torch.cuda.synchronize()
+        gathered = [None] * world
+        dist.all_gather_object(gathered, idx.cpu())
+        plan = fm.plan_positions(gathered, world, E, fz.SEG_ALIGN)
+        fm.check_tiling(plan, gathered, world, E)
+        order = torch.argsort(idx.cpu(), dim=1, stable=True)           # the kernel walks sorted picks
+        want = plan["pos"][rank].gather(1, order)
+        got = p["pos"].cpu().long().view(T, k)
+        res = {"pos_equal": bool(torch.equal(got, want)),
+               "seg_start_equal": bool(torch.equal(p["seg_start"].cpu().long(), plan["seg_start"][rank])),
+               "seg_count_equal": bool(torch.equal(p["seg_count"].cpu().long(), plan["seg_count"][rank])),
+               "status": fctx.take_status()}
+        dist.barrier()
+        if world == 1:       # every row of this rank's buffer holds the token the model put there
+            xin = fctx.section(fz.XIN)
+            tok = torch.arange(T).unsqueeze(1).expand(T, k)
+            res["rows_equal"] = bool(torch.equal(xin[plan["pos"][0].reshape(-1).to(dev)],
+                                                 x[tok.reshape(-1).to(dev)]))
+        queue.put((rank, res))
+        dist.barrier()
+    except Exception as exc:  # noqa: BLE001
+        import traceback
+        queue.put((rank, "error", f"{type(exc).__name__}: {exc}\n{traceback.format_exc()}"))
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("world", [1, 2])
+def test_fused_positions_match_host_model(native_ops, world):
+    """The placement computed by the plan and push kernels equals the host model's arithmetic."""
+    if torch.cuda.device_count() < world:
+        pytest.skip(f"needs {world} GPUs")
+    import torch.multiprocessing as mp
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    procs = [ctx.Process(target=_model_worker, args=(r, world, 29760 + world, q)) for r in range(world)]
+    for p in procs:
+        p.start()
+    out = []
+    try:
+        for _ in range(world):
+            out.append(q.get(timeout=300))
+    finally:
+        for p in procs:
+            p.join(timeout=30)
+        for p in procs:
+            if p.is_alive():
+                p.terminate()
+    for item in out:
+        assert item[1] != "error", item[2]
+        assert all(v is True or v == 0 for v in item[1].values()), item
