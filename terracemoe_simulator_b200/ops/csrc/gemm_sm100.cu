@@ -78,6 +78,12 @@ struct GemmParams {
   int wait_epoch;
   int pad_align;          // > 0: every group's rows are padded to this multiple; fwd / dgrad write
                           // zeros into the padding rows, wgrad (multiple of BK) relies on them
+  // EPI_SCATTER only: output row r goes to scatter_base[m / scatter_slots] + (m % scatter_slots)
+  // rows of ldc elements, m = row_map[r]; the bases may be peer GPUs' buffers (plain peer stores)
+  const int* row_map;
+  const unsigned long long* scatter_base;
+  int scatter_slots;
+  int scatter_world;
 };
 
 struct __align__(8) PipeBarriers {
@@ -158,6 +164,43 @@ __device__ __forceinline__ void stage_and_store64(uint8_t* stg, int lane, const 
   __syncwarp();
 }
 
+// Same staging as stage_and_store64, but every row goes to its own destination: lane r holds the
+// address of row r (0 = skip the row); the store loop fetches it with two shuffles.  The
+// destinations may live in peer GPUs' memory.
+__device__ __forceinline__ void stage_and_scatter64(uint8_t* stg, int lane, const uint32_t (&r0)[32],
+                                                    const uint32_t (&r1)[32],
+                                                    unsigned long long row_addr, int n0,
+                                                    int n_limit) {
+#pragma unroll
+  for (int j = 0; j < 8; ++j) {
+    uint4 v;
+    if (j < 4) {
+      v.x = pack_bf16(__uint_as_float(r0[j * 8 + 0]), __uint_as_float(r0[j * 8 + 1]));
+      v.y = pack_bf16(__uint_as_float(r0[j * 8 + 2]), __uint_as_float(r0[j * 8 + 3]));
+      v.z = pack_bf16(__uint_as_float(r0[j * 8 + 4]), __uint_as_float(r0[j * 8 + 5]));
+      v.w = pack_bf16(__uint_as_float(r0[j * 8 + 6]), __uint_as_float(r0[j * 8 + 7]));
+    } else {
+      v.x = pack_bf16(__uint_as_float(r1[j * 8 - 32]), __uint_as_float(r1[j * 8 - 31]));
+      v.y = pack_bf16(__uint_as_float(r1[j * 8 - 30]), __uint_as_float(r1[j * 8 - 29]));
+      v.z = pack_bf16(__uint_as_float(r1[j * 8 - 28]), __uint_as_float(r1[j * 8 - 27]));
+      v.w = pack_bf16(__uint_as_float(r1[j * 8 - 26]), __uint_as_float(r1[j * 8 - 25]));
+    }
+    *reinterpret_cast<uint4*>(stg + lane * 128 + ((j ^ (lane & 7)) << 4)) = v;
+  }
+  __syncwarp();
+  const int ch = lane & 7;
+  const bool col_ok = n0 + ch * 8 < n_limit;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    const int rr = i * 4 + (lane >> 3);
+    const uint4 v = *reinterpret_cast<const uint4*>(stg + rr * 128 + ((ch ^ (rr & 7)) << 4));
+    const unsigned long long dst = __shfl_sync(0xffffffffu, row_addr, rr);
+    if (col_ok && dst != 0ull)
+      *reinterpret_cast<uint4*>(dst + static_cast<unsigned long long>(n0 + ch * 8) * 2ull) = v;
+  }
+  __syncwarp();
+}
+
 // Locate the group of global tile index t (tile_start is a prefix array); `e` is a cursor that
 // only moves forward because every role visits tiles in increasing order.
 __device__ __forceinline__ void locate_tile(const SharedCtl* ctl, int n_groups, int t, int& e) {
@@ -167,7 +210,9 @@ __device__ __forceinline__ void locate_tile(const SharedCtl* ctl, int n_groups, 
 __device__ __forceinline__ int clamp32(int v) { return v < 0 ? 0 : (v > 32 ? 32 : v); }
 
 enum { MODE_FWD = 0, MODE_DGRAD = 1, MODE_WGRAD = 2 };
-enum { EPI_PLAIN = 0, EPI_SWIGLU = 1 };
+// EPI_SCATTER: plain epilogue whose rows go to per-row destinations (the combine leg of expert
+// parallelism folded into the GEMM: the tile is stored straight into the token owner's buffer)
+enum { EPI_PLAIN = 0, EPI_SWIGLU = 1, EPI_SCATTER = 2 };
 
 template <int MODE, int EPI, int CTAS>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
@@ -530,6 +575,29 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
             }
           }
         }
+      } else if (EPI == EPI_SCATTER) {
+        const int row = m_off + row_in_tile;       // this lane's row inside the group
+        unsigned long long row_addr = 0ull;
+        if (row < cnt) {
+          const int m = __ldcg(p.row_map + seg0 + row);
+          const int src = m >= 0 ? m / p.scatter_slots : -1;
+          if (src >= 0 && src < p.scatter_world) {
+            const int slot = m - src * p.scatter_slots;
+            row_addr = __ldg(p.scatter_base + src) +
+                       static_cast<unsigned long long>(slot) *
+                           static_cast<unsigned long long>(p.ldc) * 2ull;
+          } else if (p.status != nullptr) {
+            atomicCAS(p.status, 0, ST_BAD_INDEX);  // recorded, the row is skipped
+          }
+        }
+#pragma unroll 1
+        for (int c = 0; c < BN / 32; c += 2) {
+          uint32_t r0[32], r1[32];
+          tmem_ld_32x32(taddr + c * 32, r0);
+          tmem_ld_32x32(taddr + (c + 1) * 32, r1);
+          tmem_ld_wait();
+          stage_and_scatter64(stg, lane, r0, r1, row_addr, nt * BN + c * 32, p.N);
+        }
       } else {
         const int padded = p.pad_align > 0 ? (cnt + p.pad_align - 1) / p.pad_align * p.pad_align
                                            : cnt;
@@ -555,6 +623,9 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
         else mbar_arrive_cluster(mapa_u32(smem_u32(&ctl->bars.acc_empty[a]), 0));
       }
     }
+    // rows stored into other GPUs' memory: publish them before the kernel (and the flag that a
+    // later launch raises) can complete
+    if (EPI == EPI_SCATTER) __threadfence_system();
   }
 
   // ---- teardown: everybody meets, then the allocating warp frees TMEM ------------------------
@@ -1051,13 +1122,18 @@ static int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, const GemmP
 
 using namespace tb200;
 
-extern "C" int tb200_grouped_gemm(const void* A, const void* B, void* C, void* C2,
-                                  const int* seg_start, const int* seg_count, int n_groups,
-                                  long long a_rows, int N, int K, int ldc, int ldc2, int b_rows,
-                                  int b_cols, int mode, int epilogue, int* status, int max_ctas,
-                                  const int* wait_flags, int wait_n, int wait_epoch,
-                                  int pad_align, cudaStream_t stream) {
+static int grouped_gemm_impl(const void* A, const void* B, void* C, void* C2,
+                             const int* seg_start, const int* seg_count, int n_groups,
+                             long long a_rows, int N, int K, int ldc, int ldc2, int b_rows,
+                             int b_cols, int mode, int epilogue, int* status, int max_ctas,
+                             const int* wait_flags, int wait_n, int wait_epoch, int pad_align,
+                             const int* row_map, const unsigned long long* scatter_base,
+                             int scatter_slots, int scatter_world, cudaStream_t stream) {
   if (n_groups <= 0 || n_groups > MAX_GROUPS) return TB200_ERR_ARG;
+  const bool scatter = epilogue == EPI_SCATTER;
+  if (scatter && (row_map == nullptr || scatter_base == nullptr || scatter_slots < 1 ||
+                  scatter_world < 1))
+    return TB200_ERR_ARG;
   if ((K % 8) || (N % 8) || (ldc % 8) || (b_cols % 8)) return TB200_ERR_ARG;
   if (mode != MODE_FWD && mode != MODE_DGRAD) return TB200_ERR_ARG;
   // 256-row tiles of a CTA pair pay off when groups are long: with short groups the second
@@ -1066,8 +1142,8 @@ extern "C" int tb200_grouped_gemm(const void* A, const void* B, void* C, void* C
   const bool pair = policy == 1 || (policy == -1 && a_rows / n_groups >= 1024);
   // short groups padded to 64 rows: features on the accumulator rows, rows on the MMA's N
   const int spol = swap_policy();
-  const bool swap = !pair && pad_align > 0 && pad_align % 64 == 0 && a_rows < (1ll << 31) &&
-                    spol == 1;
+  const bool swap = !scatter && !pair && pad_align > 0 && pad_align % 64 == 0 &&
+                    a_rows < (1ll << 31) && spol == 1;
   CUtensorMap ta, tb;
   {
     uint64_t dims[2] = {static_cast<uint64_t>(K), static_cast<uint64_t>(a_rows)};
@@ -1106,6 +1182,20 @@ extern "C" int tb200_grouped_gemm(const void* A, const void* B, void* C, void* C
   p.wait_n = wait_n;
   p.wait_epoch = wait_epoch;
   p.pad_align = pad_align;
+  p.row_map = row_map;
+  p.scatter_base = scatter_base;
+  p.scatter_slots = scatter_slots;
+  p.scatter_world = scatter_world;
+  if (scatter) {
+    if (pair) {
+      if (mode == MODE_DGRAD)
+        return launch_gemm<MODE_DGRAD, EPI_SCATTER, 2>(ta, tb, p, max_ctas, stream);
+      return launch_gemm<MODE_FWD, EPI_SCATTER, 2>(ta, tb, p, max_ctas, stream);
+    }
+    if (mode == MODE_DGRAD)
+      return launch_gemm<MODE_DGRAD, EPI_SCATTER, 1>(ta, tb, p, max_ctas, stream);
+    return launch_gemm<MODE_FWD, EPI_SCATTER, 1>(ta, tb, p, max_ctas, stream);
+  }
   if (swap) {
     if (mode == MODE_DGRAD && epilogue == EPI_SWIGLU)
       return launch_swap<MODE_DGRAD, EPI_SWIGLU>(tb, ta, p, max_ctas, stream);
@@ -1130,6 +1220,30 @@ extern "C" int tb200_grouped_gemm(const void* A, const void* B, void* C, void* C
   if (epilogue == EPI_SWIGLU)
     return launch_gemm<MODE_FWD, EPI_SWIGLU, 1>(ta, tb, p, max_ctas, stream);
   return launch_gemm<MODE_FWD, EPI_PLAIN, 1>(ta, tb, p, max_ctas, stream);
+}
+
+extern "C" int tb200_grouped_gemm(const void* A, const void* B, void* C, void* C2,
+                                  const int* seg_start, const int* seg_count, int n_groups,
+                                  long long a_rows, int N, int K, int ldc, int ldc2, int b_rows,
+                                  int b_cols, int mode, int epilogue, int* status, int max_ctas,
+                                  const int* wait_flags, int wait_n, int wait_epoch,
+                                  int pad_align, cudaStream_t stream) {
+  if (epilogue != EPI_PLAIN && epilogue != EPI_SWIGLU) return TB200_ERR_ARG;
+  return grouped_gemm_impl(A, B, C, C2, seg_start, seg_count, n_groups, a_rows, N, K, ldc, ldc2,
+                           b_rows, b_cols, mode, epilogue, status, max_ctas, wait_flags, wait_n,
+                           wait_epoch, pad_align, nullptr, nullptr, 0, 0, stream);
+}
+
+extern "C" int tb200_grouped_gemm_scatter(const void* A, const void* B, const int* seg_start,
+                                          const int* seg_count, int n_groups, long long a_rows,
+                                          int N, int K, int ld_dst, int b_rows, int b_cols,
+                                          int mode, const int* row_map,
+                                          const unsigned long long* scatter_base,
+                                          int scatter_slots, int scatter_world, int* status,
+                                          int max_ctas, cudaStream_t stream) {
+  return grouped_gemm_impl(A, B, nullptr, nullptr, seg_start, seg_count, n_groups, a_rows, N, K,
+                           ld_dst, 0, b_rows, b_cols, mode, EPI_SCATTER, status, max_ctas, nullptr,
+                           0, 0, 0, row_map, scatter_base, scatter_slots, scatter_world, stream);
 }
 
 extern "C" int tb200_grouped_wgrad(const void* X, const void* dY, void* dW, const int* seg_start,

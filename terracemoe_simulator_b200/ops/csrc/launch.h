@@ -29,6 +29,16 @@ int tb200_grouped_gemm(const void* A, const void* B, void* C, void* C2, const in
                        int ldc2, int b_rows, int b_cols, int mode, int epilogue, int* status,
                        int max_ctas, const int* wait_flags, int wait_n, int wait_epoch,
                        int pad_align, cudaStream_t stream);
+// Plain fwd / dgrad GEMM whose output rows are scattered: row r (inside the segments) goes to
+// scatter_base[m / scatter_slots] + (m % scatter_slots) * ld_dst elements with m = row_map[r];
+// scatter_base[] are device addresses that may belong to peer GPUs (plain stores, published
+// system-wide before the kernel ends).  Rows with a map value outside [0, world * slots) are
+// skipped and ST_BAD_INDEX is recorded.  Padding rows are not written anywhere.
+int tb200_grouped_gemm_scatter(const void* A, const void* B, const int* seg_start,
+                               const int* seg_count, int n_groups, long long a_rows, int N, int K,
+                               int ld_dst, int b_rows, int b_cols, int mode, const int* row_map,
+                               const unsigned long long* scatter_base, int scatter_slots,
+                               int scatter_world, int* status, int max_ctas, cudaStream_t stream);
 // dW[g][M, N] = X[rows of g, M]^T * dY[rows of g, N]; groups with no rows get zeros.
 int tb200_grouped_wgrad(const void* X, const void* dY, void* dW, const int* seg_start,
                         const int* seg_count, int n_groups, long long rows, int M, int N,
@@ -117,13 +127,15 @@ int tb200_ep_plan(const struct Tb200Arena* a, int* chunk_hist, int* chunka_hist,
 int tb200_ep_push(const struct Tb200Arena* a, const void* x, const int* es, const int* rank_local,
                   const int* chunk_base, const int* my_base, int* pos_out, const float* gs,
                   float* dgs, long long off_dst, long long off_dot, int T, int flag_kind, int epoch,
-                  int* done_counter, int* status, cudaStream_t stream);
+                  int* done_counter, int* status, long long off_rowmap, int ret_slots,
+                  int dot_local, cudaStream_t stream);
 int tb200_signal(const struct Tb200Arena* a, int kind, int first, int n, int stride, int idx,
                  int epoch, int wait_kind, int wait_first, int wait_n, int* status,
                  cudaStream_t stream);
 int tb200_ep_pull_combine(const struct Tb200Arena* a, const int* pos, const int* es,
                           const float* gs, void* y, long long off_src, int T, int group_size,
-                          int wait_kind, int epoch, int* status, cudaStream_t stream);
+                          int wait_kind, int epoch, int* status, int local_slots,
+                          cudaStream_t stream);
 int tb200_hopa_rank(const struct Tb200Arena* a, const int* es, int* ranka_local, int* chunka_hist,
                     int T, cudaStream_t stream);
 int tb200_hopa_push(const struct Tb200Arena* a, const void* x, const int* es, const float* gs,

@@ -190,7 +190,8 @@ __global__ void ep_push_kernel(Tb200Arena a, const __nv_bfloat16* __restrict__ x
                                const int* __restrict__ chunk_base, const int* __restrict__ my_base,
                                int* __restrict__ pos_out, const float* __restrict__ gs,
                                float* __restrict__ dgs, long long off_dst, long long off_dot,
-                               int T, int flag_kind, int epoch, int* done_counter, int* status) {
+                               int T, int flag_kind, int epoch, int* done_counter, int* status,
+                               long long off_rowmap, int ret_slots, int dot_local) {
   const int lane = threadIdx.x & 31;
   const int k = a.top_k, H = a.hidden;
   const int n_pairs = T * k;
@@ -215,14 +216,21 @@ __global__ void ep_push_kernel(Tb200Arena a, const __nv_bfloat16* __restrict__ x
     const uint4* src = reinterpret_cast<const uint4*>(x + static_cast<size_t>(t) * H);
     uint4* dst = reinterpret_cast<uint4*>(sect<__nv_bfloat16>(a, owner, off_dst) +
                                           static_cast<size_t>(pos) * H);
+    // return address of this row for a GEMM epilogue that scatters its output: (me, slot p)
+    if (off_rowmap >= 0 && lane == 0) sect<int>(a, owner, off_rowmap)[pos] = a.rank * ret_slots + p;
     if (gs == nullptr && dgs == nullptr) {
       for (int i = lane; i < H / 8; i += 32) dst[i] = src[i];
     } else {
       const float w = gs ? gs[p] : 1.0f;
-      const uint4* oth = dgs ? reinterpret_cast<const uint4*>(
-                                   sect<__nv_bfloat16>(a, owner, off_dot) +
-                                   static_cast<size_t>(pos) * H)
-                             : nullptr;
+      // the saved expert output of this pick: at the owner's row, or (when the forward GEMM
+      // scattered its rows to the origins) in my own return slot p
+      const uint4* oth = !dgs ? nullptr
+                         : dot_local ? reinterpret_cast<const uint4*>(
+                                           sect<__nv_bfloat16>(a, a.rank, off_dot) +
+                                           static_cast<size_t>(p) * H)
+                                     : reinterpret_cast<const uint4*>(
+                                           sect<__nv_bfloat16>(a, owner, off_dot) +
+                                           static_cast<size_t>(pos) * H);
       float dot = 0.f;
       for (int i = lane; i < H / 8; i += 32) {
         uint4 v = src[i];
@@ -274,7 +282,10 @@ __global__ void signal_kernel(Tb200Arena a, int kind, int first, int n, int stri
 __global__ void ep_pull_combine_kernel(Tb200Arena a, const int* __restrict__ pos,
                                        const int* __restrict__ es, const float* __restrict__ gs,
                                        __nv_bfloat16* __restrict__ y, long long off_src, int T,
-                                       int group_size, int wait_kind, int epoch, int* status) {
+                                       int group_size, int wait_kind, int epoch, int* status,
+                                       int local_slots) {
+  // local_slots > 0: the rows already sit in MY section at slot t * k + j (the owners' GEMM
+  // epilogues stored them there); otherwise they are read from the owners' sections at pos
   block_wait_flags(a, wait_kind, 0, a.world, epoch, status, ST_TIMEOUT_FLAG);
   const int k = a.top_k, H = a.hidden;
   for (int t = blockIdx.x; t < T; t += gridDim.x) {
@@ -295,11 +306,14 @@ __global__ void ep_pull_combine_kernel(Tb200Arena a, const int* __restrict__ pos
           }
         }
         prev_group = grp;
-        const int row = pos[o];
-        if (row < 0 || row >= a.cap_rows || e < 0 || e >= a.n_experts) continue;
+        const int row = local_slots > 0 ? o : pos[o];
+        const int row_cap = local_slots > 0 ? local_slots : a.cap_rows;
+        if (row < 0 || row >= row_cap || e < 0 || e >= a.n_experts) continue;
+        if (local_slots > 0 && pos[o] < 0) continue;     // the push skipped this pick
         const float w = gs ? gs[o] : 1.0f;
         const uint4 v = __ldcg(reinterpret_cast<const uint4*>(
-                                   sect<__nv_bfloat16>(a, e / a.epr, off_src) +
+                                   sect<__nv_bfloat16>(a, local_slots > 0 ? a.rank : e / a.epr,
+                                                       off_src) +
                                    static_cast<size_t>(row) * H) + c);
         const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v);
 #pragma unroll
@@ -623,15 +637,17 @@ extern "C" int tb200_ep_push(const Tb200Arena* a, const void* x, const int* es,
                              const int* rank_local, const int* chunk_base, const int* my_base,
                              int* pos_out, const float* gs, float* dgs, long long off_dst,
                              long long off_dot, int T, int flag_kind, int epoch, int* done_counter,
-                             int* status, cudaStream_t stream) {
+                             int* status, long long off_rowmap, int ret_slots, int dot_local,
+                             cudaStream_t stream) {
   if (!arena_ok(a)) return TB200_ERR_ARG;
+  if ((off_rowmap >= 0 || dot_local) && ret_slots < T * a->top_k) return TB200_ERR_ARG;
   int blocks = (T * a->top_k + 7) / 8;
   if (blocks < 1) blocks = 1;
   if (blocks > 148 * 8) blocks = 148 * 8;
   ep_push_kernel<<<blocks, 256, 0, stream>>>(*a, static_cast<const __nv_bfloat16*>(x), es,
                                              rank_local, chunk_base, my_base, pos_out, gs, dgs,
                                              off_dst, off_dot, T, flag_kind, epoch, done_counter,
-                                             status);
+                                             status, off_rowmap, ret_slots, dot_local);
   return LAUNCH_OK();
 }
 
@@ -647,12 +663,14 @@ extern "C" int tb200_signal(const Tb200Arena* a, int kind, int first, int n, int
 extern "C" int tb200_ep_pull_combine(const Tb200Arena* a, const int* pos, const int* es,
                                      const float* gs, void* y, long long off_src, int T,
                                      int group_size, int wait_kind, int epoch, int* status,
-                                     cudaStream_t stream) {
+                                     int local_slots, cudaStream_t stream) {
   if (!arena_ok(a) || group_size < 1) return TB200_ERR_ARG;
+  if (local_slots > 0 && local_slots < T * a->top_k) return TB200_ERR_ARG;
   int blocks = T < 1 ? 1 : (T > 148 * 8 ? 148 * 8 : T);
   ep_pull_combine_kernel<<<blocks, 256, 0, stream>>>(*a, pos, es, gs,
                                                      static_cast<__nv_bfloat16*>(y), off_src, T,
-                                                     group_size, wait_kind, epoch, status);
+                                                     group_size, wait_kind, epoch, status,
+                                                     local_slots);
   return LAUNCH_OK();
 }
 

@@ -180,12 +180,15 @@ std::tuple<Tensor, Tensor, Tensor, Tensor> ep_plan(const Tensor& arena, Tensor c
   return {my_base, seg_start, seg_count, rows_a};
 }
 
-std::tuple<Tensor, Tensor> ep_push(const Tensor& arena, const Tensor& x, const Tensor& es,
-                                   const Tensor& rank_local, const Tensor& chunk_base,
-                                   const Tensor& my_base, const c10::optional<Tensor>& gs,
-                                   bool want_dgs, int64_t dst_sel, int64_t dot_sel,
-                                   int64_t flag_kind, int64_t epoch, Tensor done) {
+std::tuple<Tensor, Tensor> ep_push_impl(const Tensor& arena, const Tensor& x, const Tensor& es,
+                                        const Tensor& rank_local, const Tensor& chunk_base,
+                                        const Tensor& my_base, const c10::optional<Tensor>& gs,
+                                        bool want_dgs, int64_t dst_sel, int64_t dot_off,
+                                        int64_t flag_kind, int64_t epoch, Tensor done,
+                                        int64_t rowmap_off, int64_t ret_slots, bool dot_local) {
   const Tb200Arena* a = arena_of(arena);
+  TORCH_CHECK(rowmap_off < 0 || rowmap_off % 16 == 0, "ep_push: row map offset alignment");
+  TORCH_CHECK(dot_off % 16 == 0, "ep_push: dot section alignment");
   TORCH_CHECK(x.is_cuda() && x.is_contiguous() && x.scalar_type() == at::kBFloat16 &&
                   x.dim() == 2 && x.size(1) == a->hidden,
               "ep_push: bf16 [T, H] rows");
@@ -201,10 +204,37 @@ std::tuple<Tensor, Tensor> ep_push(const Tensor& arena, const Tensor& x, const T
                          chunk_base.data_ptr<int>(), my_base.data_ptr<int>(), pos.data_ptr<int>(),
                          gs.has_value() ? gs->data_ptr<float>() : nullptr,
                          want_dgs ? dgs.data_ptr<float>() : nullptr, section_offset(a, dst_sel),
-                         want_dgs ? section_offset(a, dot_sel) : 0, T, flag_kind, epoch,
-                         done.data_ptr<int>(), st_ptr(x), cur_stream()),
+                         want_dgs ? dot_off : 0, T, flag_kind, epoch, done.data_ptr<int>(),
+                         st_ptr(x), rowmap_off, static_cast<int>(ret_slots), dot_local ? 1 : 0,
+                         cur_stream()),
            "ep_push");
   return {pos, dgs};
+}
+
+std::tuple<Tensor, Tensor> ep_push(const Tensor& arena, const Tensor& x, const Tensor& es,
+                                   const Tensor& rank_local, const Tensor& chunk_base,
+                                   const Tensor& my_base, const c10::optional<Tensor>& gs,
+                                   bool want_dgs, int64_t dst_sel, int64_t dot_sel,
+                                   int64_t flag_kind, int64_t epoch, Tensor done) {
+  const Tb200Arena* a = arena_of(arena);
+  return ep_push_impl(arena, x, es, rank_local, chunk_base, my_base, gs, want_dgs, dst_sel,
+                      want_dgs ? section_offset(a, dot_sel) : 0, flag_kind, epoch, done, -1, 0,
+                      false);
+}
+
+// Push that also leaves, beside every row, its return address (source rank, slot) in the owner's
+// row map at byte offset `rowmap_off` of the arena, for a GEMM whose epilogue scatters its rows
+// back (grouped_gemm_scatter).  With `dot_local` the gate gradient reads the saved expert output
+// from MY return section (`dot_off`) at slot p instead of the owner's row.
+std::tuple<Tensor, Tensor> ep_push_ret(const Tensor& arena, const Tensor& x, const Tensor& es,
+                                       const Tensor& rank_local, const Tensor& chunk_base,
+                                       const Tensor& my_base, const c10::optional<Tensor>& gs,
+                                       bool want_dgs, int64_t dst_sel, int64_t dot_off,
+                                       bool dot_local, int64_t flag_kind, int64_t epoch,
+                                       Tensor done, int64_t rowmap_off, int64_t ret_slots) {
+  TORCH_CHECK(rowmap_off >= 0 && ret_slots > 0, "ep_push_ret: row map offset and slot count");
+  return ep_push_impl(arena, x, es, rank_local, chunk_base, my_base, gs, want_dgs, dst_sel,
+                      dot_off, flag_kind, epoch, done, rowmap_off, ret_slots, dot_local);
 }
 
 void ep_signal(const Tensor& arena, int64_t kind, int64_t first, int64_t n, int64_t stride,
@@ -217,10 +247,11 @@ void ep_signal(const Tensor& arena, int64_t kind, int64_t first, int64_t n, int6
            "ep_signal");
 }
 
-Tensor ep_pull_combine(const Tensor& arena, const Tensor& pos, const Tensor& es,
-                       const c10::optional<Tensor>& gs, int64_t src_sel, int64_t group_size,
-                       int64_t wait_kind, int64_t epoch) {
+Tensor ep_pull_combine_impl(const Tensor& arena, const Tensor& pos, const Tensor& es,
+                            const c10::optional<Tensor>& gs, int64_t src_off, int64_t group_size,
+                            int64_t wait_kind, int64_t epoch, int64_t local_slots) {
   const Tb200Arena* a = arena_of(arena);
+  TORCH_CHECK(src_off >= 0 && src_off % 16 == 0, "ep_pull_combine: section offset");
   TORCH_CHECK(pos.is_cuda() && pos.is_contiguous() && pos.sizes() == es.sizes() &&
                   pos.size(1) == a->top_k,
               "ep_pull_combine: [T, k] index planes");
@@ -229,10 +260,26 @@ Tensor ep_pull_combine(const Tensor& arena, const Tensor& pos, const Tensor& es,
   Tensor y = at::empty({T, a->hidden}, pos.options().dtype(at::kBFloat16));
   check_rc(tb200_ep_pull_combine(a, pos.data_ptr<int>(), es.data_ptr<int>(),
                                  gs.has_value() ? gs->data_ptr<float>() : nullptr, y.data_ptr(),
-                                 section_offset(a, src_sel), T, group_size, wait_kind, epoch,
-                                 st_ptr(pos), cur_stream()),
+                                 src_off, T, group_size, wait_kind, epoch, st_ptr(pos),
+                                 static_cast<int>(local_slots), cur_stream()),
            "ep_pull_combine");
   return y;
+}
+
+Tensor ep_pull_combine(const Tensor& arena, const Tensor& pos, const Tensor& es,
+                       const c10::optional<Tensor>& gs, int64_t src_sel, int64_t group_size,
+                       int64_t wait_kind, int64_t epoch) {
+  return ep_pull_combine_impl(arena, pos, es, gs, section_offset(arena_of(arena), src_sel),
+                              group_size, wait_kind, epoch, 0);
+}
+
+// Combine from MY return section (byte offset `src_off`, `slots` rows): the owners' GEMM
+// epilogues stored row (t, j) at slot t * k + j; same canonical reduction as ep_pull_combine.
+Tensor ep_combine_local(const Tensor& arena, const Tensor& pos, const Tensor& es,
+                        const c10::optional<Tensor>& gs, int64_t src_off, int64_t slots,
+                        int64_t group_size, int64_t wait_kind, int64_t epoch) {
+  TORCH_CHECK(slots > 0, "ep_combine_local: slot count");
+  return ep_pull_combine_impl(arena, pos, es, gs, src_off, group_size, wait_kind, epoch, slots);
 }
 
 std::tuple<Tensor, Tensor> hopa_rank(const Tensor& arena, const Tensor& es) {
@@ -368,6 +415,45 @@ void grouped_gemm_ex(const Tensor& A, const Tensor& B, Tensor C, const c10::opti
            "grouped_gemm_ex");
 }
 
+// Grouped fwd / dgrad GEMM whose output rows go straight to their return slots, possibly in
+// peer GPUs' arenas: row r -> scatter_base[m / slots] + (m % slots) * N elements, m = row_map[r].
+void grouped_gemm_scatter(const Tensor& A, const Tensor& B, const Tensor& seg_start,
+                          const Tensor& seg_count, int64_t mode, const Tensor& row_map,
+                          const Tensor& scatter_base, int64_t slots) {
+  TORCH_CHECK(A.is_cuda() && A.is_contiguous() && B.is_cuda() && B.is_contiguous() &&
+                  A.scalar_type() == at::kBFloat16 && B.scalar_type() == at::kBFloat16 &&
+                  A.dim() == 2 && B.dim() == 3,
+              "grouped_gemm_scatter: bf16 A [rows, K], B [G, r, c]");
+  TORCH_CHECK(seg_start.scalar_type() == at::kInt && seg_count.scalar_type() == at::kInt &&
+                  seg_start.numel() == B.size(0) && seg_count.numel() == B.size(0),
+              "grouped_gemm_scatter: int32 segment tables of length G");
+  TORCH_CHECK(row_map.is_cuda() && row_map.scalar_type() == at::kInt && row_map.is_contiguous() &&
+                  row_map.numel() >= A.size(0),
+              "grouped_gemm_scatter: int32 row map covering the rows of A");
+  TORCH_CHECK(scatter_base.is_cuda() && scatter_base.scalar_type() == at::kLong &&
+                  scatter_base.is_contiguous() && scatter_base.numel() >= 1 &&
+                  scatter_base.numel() <= TB200_MAX_WORLD && slots > 0,
+              "grouped_gemm_scatter: int64 base address per rank");
+  c10::cuda::CUDAGuard guard(A.device());
+  const int64_t rows = A.size(0), K = A.size(1), G = B.size(0);
+  const int64_t b_rows = B.size(1), b_cols = B.size(2);
+  int64_t N;
+  if (mode == 0) {
+    TORCH_CHECK(b_rows == K, "grouped_gemm_scatter fwd: B rows must equal K");
+    N = b_cols;
+  } else {
+    TORCH_CHECK(mode == 1 && b_cols == K, "grouped_gemm_scatter dgrad: B cols must equal K");
+    N = b_rows;
+  }
+  check_rc(tb200_grouped_gemm_scatter(
+               A.data_ptr(), B.data_ptr(), seg_start.data_ptr<int>(), seg_count.data_ptr<int>(),
+               G, rows, N, K, N, b_rows, b_cols, mode, row_map.data_ptr<int>(),
+               reinterpret_cast<const unsigned long long*>(scatter_base.data_ptr<int64_t>()),
+               static_cast<int>(slots), static_cast<int>(scatter_base.numel()), st_ptr(A), 0,
+               cur_stream()),
+           "grouped_gemm_scatter");
+}
+
 }  // namespace
 
 void terrace_b200_register_symm(torch::Library& m) {
@@ -388,6 +474,14 @@ void terrace_b200_register_symm(torch::Library& m) {
         "int wait_kind, int wait_first, int wait_n, Tensor like) -> ()", &ep_signal);
   m.def("ep_pull_combine(Tensor arena, Tensor pos, Tensor es, Tensor? gs, int src_sel, "
         "int group_size, int wait_kind, int epoch) -> Tensor", &ep_pull_combine);
+  m.def("ep_push_ret(Tensor arena, Tensor x, Tensor es, Tensor rank_local, Tensor chunk_base, "
+        "Tensor my_base, Tensor? gs, bool want_dgs, int dst_sel, int dot_off, bool dot_local, "
+        "int flag_kind, int epoch, Tensor(a!) done, int rowmap_off, int ret_slots) "
+        "-> (Tensor, Tensor)", &ep_push_ret);
+  m.def("ep_combine_local(Tensor arena, Tensor pos, Tensor es, Tensor? gs, int src_off, "
+        "int slots, int group_size, int wait_kind, int epoch) -> Tensor", &ep_combine_local);
+  m.def("grouped_gemm_scatter(Tensor A, Tensor B, Tensor seg_start, Tensor seg_count, int mode, "
+        "Tensor row_map, Tensor scatter_base, int slots) -> ()", &grouped_gemm_scatter);
   m.def("hopa_rank(Tensor arena, Tensor es) -> (Tensor, Tensor)", &hopa_rank);
   m.def("hopa_push(Tensor arena, Tensor x, Tensor es, Tensor gs, Tensor rank_local, "
         "Tensor chunk_base, Tensor my_base, Tensor ranka_local, Tensor chunka_base, "

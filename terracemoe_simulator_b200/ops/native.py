@@ -31,7 +31,8 @@ class _Counted:
                  "k1_arrival": 3, "k2_pack": 3, "ep_plan_pass1": 1, "ep_plan": 1, "ep_push": 1,
                  "ep_signal": 1, "ep_pull_combine": 1, "hopa_rank": 1, "hopa_push": 1,
                  "arrival_push": 1, "arrival_combine": 1, "origin_combine": 1,
-                 "origin_pull_dgate": 1, "grouped_gemm_ex": 1, "attn_fwd": 1, "attn_bwd": 3}
+                 "origin_pull_dgate": 1, "grouped_gemm_ex": 1, "attn_fwd": 1, "attn_bwd": 3,
+                 "ep_push_ret": 1, "ep_combine_local": 1, "grouped_gemm_scatter": 1}
 
     def __getattr__(self, name):
         fn = getattr(torch.ops.terrace, name)

@@ -14,6 +14,12 @@ One step of ``fused_moe_forward`` (no host synchronisation anywhere):
             representative pulls, applies the gates and reduces per row -> origin pulls and adds
             its M group rows
 
+One-hop with ``epilogue_push`` (``TERRACE_EP_EPILOGUE_PUSH=1``; off by default): the push also
+leaves every row's return address in the owner's row map, the second expert GEMM stores each
+output row from its epilogue straight into the ORIGIN's return slot over NVLink (one kernel does
+the GEMM and the combine transfer, tile by tile), and the combine reads local memory only.  The
+reduction order is unchanged, so the result equals the pull path bit for bit.
+
 The backward pass runs the mirrored pipeline (combine-backward is dispatch shaped and also
 produces the gate gradients; dispatch-backward is combine shaped).  Both paths place rows at
 positions the ORIGIN computes from the all-gathered expert histogram, so the expert GEMMs see
@@ -23,6 +29,8 @@ Reference counterparts: ``terrace/ep_dist.py:82-122`` and ``terrace/ta2a_fwd.py:
 issue 4 and 9 collectives with 1-3 host syncs per forward).
 """
 from __future__ import annotations
+
+import os
 
 import torch
 import torch.distributed as dist
@@ -38,7 +46,8 @@ FK_NUM = 10
 MAX_WORLD = 16
 SEG_ALIGN = 64          # expert segments start on multiples of 64 rows (zero padding rows)
 
-LIVE = {"one_hop_fwd": 0, "two_hop_fwd": 0, "one_hop_bwd": 0, "two_hop_bwd": 0, "echo": 0}
+LIVE = {"one_hop_fwd": 0, "two_hop_fwd": 0, "one_hop_bwd": 0, "two_hop_bwd": 0, "echo": 0,
+        "epilogue_push_fwd": 0, "epilogue_push_bwd": 0}
 
 
 def _lib():
@@ -52,7 +61,8 @@ def _align(n: int, a: int = 256) -> int:
 
 class FusedEPContext:
     def __init__(self, cfg: TRouteConfig, hidden: int, d_expert: int, tokens: int, *, world: int,
-                 rank: int, rpn: int, device, group=None, row_capacity_factor: float = 2.0):
+                 rank: int, rpn: int, device, group=None, row_capacity_factor: float = 2.0,
+                 epilogue_push=None):
         from .. import ops
         if not ops.custom_ops_enabled():
             raise RuntimeError("the fused transport needs the native library: "
@@ -73,6 +83,10 @@ class FusedEPContext:
                                    int(row_capacity_factor * tokens * self.k))
                                + self.epr * (SEG_ALIGN - 1), 128)
         self.epoch = 0
+        if epilogue_push is None:
+            epilogue_push = os.environ.get("TERRACE_EP_EPILOGUE_PUSH", "0") == "1"
+        self.epilogue_push = bool(epilogue_push)
+        self.ret_slots = tokens * self.k
         H = hidden
         sizes = [
             world * self.E * 4,                      # counts_all
@@ -85,6 +99,8 @@ class FusedEPContext:
         arows = self.n_nodes * tokens if self.two_hop_ok else 1
         sizes += [arows * H * 2, arows * 3 * self.q * 4, arows * H * 2, arows * H * 2,
                   arows * H * 2, arows * self.q * 4]
+        if self.epilogue_push:      # return slots (forward, backward) and the owners' row map
+            sizes += [self.ret_slots * H * 2, self.ret_slots * H * 2, self.cap_rows * 4]
         self.offsets, off = [], 0
         for s in sizes:
             self.offsets.append(off)
@@ -108,7 +124,15 @@ class FusedEPContext:
                 self.peer_ptrs.append(p)
         geom = [world, rank, self.E, self.epr, rpn, self.n_nodes, tokens, self.k, self.M, self.q,
                 H, self.cap_rows]
-        self.arena = lib.symm_make_arena(self.peer_ptrs, self.offsets, geom)
+        self.arena = lib.symm_make_arena(self.peer_ptrs, self.offsets[:12], geom)
+        if self.epilogue_push:
+            self.off_ret, self.off_dret, self.off_rowmap = self.offsets[12:15]
+            self.ret_base = torch.tensor([p + self.off_ret for p in self.peer_ptrs],
+                                         dtype=torch.int64, device=self.device)
+            self.dret_base = torch.tensor([p + self.off_dret for p in self.peer_ptrs],
+                                          dtype=torch.int64, device=self.device)
+            self.row_map = self.buf[self.off_rowmap: self.off_rowmap + self.cap_rows * 4].view(
+                torch.int32)
         self.done = torch.zeros(8, dtype=torch.int32, device=self.device)
         self._dev_index = dev_index
         dist.barrier(group=group)
@@ -158,7 +182,12 @@ def _plan(ctx: FusedEPContext, idx, gates, mode: str, ep: int):
 def _dispatch(ctx, p, x, mode: str, ep: int):
     """Forward dispatch: rows of ``x`` land in the owners' ``xin`` sections."""
     lib = _lib()
-    if mode == "one_hop":
+    if mode == "one_hop" and ctx.epilogue_push:
+        pos, _ = lib.ep_push_ret(ctx.arena, x, p["es"], p["rank_local"], p["chunk_hist"],
+                                 p["my_base"], None, False, XIN, 0, False, FK_DATA, ep,
+                                 ctx.done[0:1], ctx.off_rowmap, ctx.ret_slots)
+        p["pos"], p["rowa"] = pos, None
+    elif mode == "one_hop":
         pos, _ = lib.ep_push(ctx.arena, x, p["es"], p["rank_local"], p["chunk_hist"],
                              p["my_base"], None, False, XIN, XIN, FK_DATA, ep, ctx.done[0:1])
         p["pos"], p["rowa"] = pos, None
@@ -177,9 +206,16 @@ def _signal_out(ctx, mode: str, kind: int, ep: int, like, wait_kind: int = -1):
     lib.ep_signal(ctx.arena, kind, first, n, 1, ctx.rank, ep, wait_kind, first, n, like)
 
 
-def _combine(ctx, p, mode: str, ep: int, *, src: int, use_gate: bool, backward: bool):
+def _combine(ctx, p, mode: str, ep: int, *, src: int, use_gate: bool, backward: bool,
+             pull: bool = False):
+    """``pull`` forces the remote-read combine even on a context with ``epilogue_push`` (the
+    echo measurement has no GEMM whose epilogue could have delivered the rows)."""
     lib = _lib()
     out_kind = FK_B_OUT if backward else FK_OUT
+    if mode == "one_hop" and ctx.epilogue_push and not pull:
+        return lib.ep_combine_local(ctx.arena, p["pos"], p["es"], p["gs"] if use_gate else None,
+                                    ctx.off_dret if backward else ctx.off_ret, ctx.ret_slots,
+                                    ctx.cfg.group_size, out_kind, ep)
     if mode == "one_hop":
         return lib.ep_pull_combine(ctx.arena, p["pos"], p["es"], p["gs"] if use_gate else None,
                                    src, ctx.cfg.group_size, out_kind, ep)
@@ -208,8 +244,14 @@ class _FusedMoE(torch.autograd.Function):
             lib.zero_pad_rows(xin, p["seg_start"], p["seg_count"], SEG_ALIGN)
         lib.grouped_gemm_ex(xin, w13.contiguous(), act, h13, p["seg_start"], p["seg_count"], 0, 1,
                             fctx.arena, FK_DATA, first, n, ep, SEG_ALIGN)
-        lib.grouped_gemm_ex(act, w2.contiguous(), yout, None, p["seg_start"], p["seg_count"], 0,
-                            0, None, 0, 0, 0, ep, SEG_ALIGN)
+        scatter = mode == "one_hop" and fctx.epilogue_push
+        if scatter:     # GEMM 2 stores every output row into its origin's return slot
+            lib.grouped_gemm_scatter(act, w2.contiguous(), p["seg_start"], p["seg_count"], 0,
+                                     fctx.row_map, fctx.ret_base, fctx.ret_slots)
+            LIVE["epilogue_push_fwd"] += 1
+        else:
+            lib.grouped_gemm_ex(act, w2.contiguous(), yout, None, p["seg_start"], p["seg_count"],
+                                0, 0, None, 0, 0, 0, ep, SEG_ALIGN)
         _signal_out(fctx, mode, FK_OUT, ep, xc)
         y = _combine(fctx, p, mode, ep, src=YOUT, use_gate=True, backward=False)
         ctx.fctx, ctx.mode, ctx.ep, ctx.plan = fctx, mode, ep, p
@@ -225,7 +267,13 @@ class _FusedMoE(torch.autograd.Function):
         w13, w2, act, h13 = ctx.saved_tensors
         dyc = dy.contiguous()
         first, n = fctx.owner_wait_range(mode)
-        if mode == "one_hop":
+        scatter = mode == "one_hop" and fctx.epilogue_push
+        if scatter:     # the saved expert outputs sit in my own return slots
+            _, dgs = lib.ep_push_ret(fctx.arena, dyc, p["es"], p["rank_local"], p["chunk_hist"],
+                                     p["my_base"], p["gs"], True, DOUT, fctx.off_ret, True,
+                                     FK_B_DATA, ep, fctx.done[0:1], fctx.off_rowmap,
+                                     fctx.ret_slots)
+        elif mode == "one_hop":
             _, dgs = lib.ep_push(fctx.arena, dyc, p["es"], p["rank_local"], p["chunk_hist"],
                                  p["my_base"], p["gs"], True, DOUT, YOUT, FK_B_DATA, ep,
                                  fctx.done[0:1])
@@ -244,8 +292,13 @@ class _FusedMoE(torch.autograd.Function):
         dw2 = lib.grouped_wgrad(act, dout, p["seg_start"], p["seg_count"], 0, SEG_ALIGN)
         dh13 = lib.swiglu_bwd(h13, dact)
         dw13 = lib.grouped_wgrad(xin, dh13, p["seg_start"], p["seg_count"], 0, SEG_ALIGN)
-        lib.grouped_gemm_ex(dh13, w13.contiguous(), dxs, None, p["seg_start"], p["seg_count"], 1,
-                            0, None, 0, 0, 0, ep, SEG_ALIGN)
+        if scatter:
+            lib.grouped_gemm_scatter(dh13, w13.contiguous(), p["seg_start"], p["seg_count"], 1,
+                                     fctx.row_map, fctx.dret_base, fctx.ret_slots)
+            LIVE["epilogue_push_bwd"] += 1
+        else:
+            lib.grouped_gemm_ex(dh13, w13.contiguous(), dxs, None, p["seg_start"],
+                                p["seg_count"], 1, 0, None, 0, 0, 0, ep, SEG_ALIGN)
         _signal_out(fctx, mode, FK_B_OUT, ep, dyc)
         dx = _combine(fctx, p, mode, ep, src=DXS, use_gate=False, backward=True)
         if mode == "two_hop":
@@ -277,4 +330,4 @@ def fused_dispatch_combine(fctx: FusedEPContext, x, idx, gates, *, mode: str):
     _dispatch(fctx, p, x.contiguous(), mode, ep)
     _signal_out(fctx, mode, FK_OUT, ep, x, wait_kind=FK_DATA)
     LIVE["echo"] += 1
-    return _combine(fctx, p, mode, ep, src=XIN, use_gate=True, backward=False)
+    return _combine(fctx, p, mode, ep, src=XIN, use_gate=True, backward=False, pull=True)

@@ -79,11 +79,50 @@ def check_tiling(plan, idx_per_rank, world: int, n_experts: int) -> None:
             raise AssertionError(f"owner {o}: rows are not in (expert, source, token) order")
 
 
+def return_maps(plan, idx_per_rank, world: int, slots: int):
+    """The owners' row maps of the epilogue-push variant: ``map[o][row] = s * slots + t * k + j``
+    for the row that source ``s`` pushed for token ``t``'s j-th pick in expert order, ``-1`` for
+    padding rows.  The GEMM epilogue stores row ``row`` into rank ``s``'s return slot
+    ``t * k + j``."""
+    maps = [torch.full((max(plan["rows"][o], 1),), -1, dtype=torch.int64) for o in range(world)]
+    for s, idx in enumerate(idx_per_rank):
+        T, k = idx.shape
+        if T * k > slots:
+            raise ValueError("more picks than return slots")
+        order = torch.argsort(idx, dim=1, stable=True)
+        p_sorted = plan["pos"][s].gather(1, order)
+        o_sorted = plan["owner"][s].gather(1, order)
+        slot = torch.arange(T * k).view(T, k)
+        for o in range(world):
+            mine = o_sorted == o
+            maps[o][p_sorted[mine]] = s * slots + slot[mine]
+    return maps
+
+
+def scatter_rows(yout, maps, world: int, slots: int, hidden: int, dtype):
+    """What the scattering epilogues do, for all owners: every mapped row lands in its origin's
+    return section; a map value outside ``[0, world * slots)`` is skipped and counted."""
+    ret = [torch.zeros(slots, hidden, dtype=dtype) for _ in range(world)]
+    skipped = 0
+    for o in range(world):
+        m = maps[o]
+        rows = torch.nonzero(m != -1).flatten()
+        for r in rows.tolist():
+            v = int(m[r])
+            if v < 0 or v >= world * slots:
+                skipped += 1
+                continue
+            ret[v // slots][v % slots] = yout[o][r]
+    return ret, skipped
+
+
 def one_hop_model(x_per_rank, idx_per_rank, gates_per_rank, w13, w2, group_size: int,
-                  seg_align: int = 64):
+                  seg_align: int = 64, epilogue_push: bool = False):
     """The whole one-hop step on the host: push rows to their positions, grouped SwiGLU per
     segment, pull back and reduce with the canonical tree (per group ascending, one rounding per
-    level).  ``w13[E, H, 2d]``, ``w2[E, d, H]`` hold all experts.  Returns ``y`` per rank."""
+    level).  ``w13[E, H, 2d]``, ``w2[E, d, H]`` hold all experts.  Returns ``y`` per rank.
+    With ``epilogue_push`` the expert output rows travel through the row maps into the origins'
+    return slots and the combine reads those; the reduction order is the same."""
     world, E = len(x_per_rank), w13.shape[0]
     epr = E // world
     plan = plan_positions(idx_per_rank, world, E, seg_align)
@@ -103,6 +142,13 @@ def one_hop_model(x_per_rank, idx_per_rank, gates_per_rank, w13, w2, group_size:
                 gate, up = (xin[o][a:a + n] @ w13[o * epr + le]).chunk(2, dim=-1)
                 out[a:a + n] = (torch.nn.functional.silu(gate) * up) @ w2[o * epr + le]
         yout.append(out)
+    ret = None
+    if epilogue_push:
+        slots = max(i.numel() for i in idx_per_rank)
+        maps = return_maps(plan, idx_per_rank, world, slots)
+        ret, skipped = scatter_rows(yout, maps, world, slots, H, dt)
+        if skipped:
+            raise AssertionError("a row map entry fell outside the return sections")
     ys = []
     for s, x in enumerate(x_per_rank):
         idx, gates = idx_per_rank[s], gates_per_rank[s]
@@ -115,8 +161,14 @@ def one_hop_model(x_per_rank, idx_per_rank, gates_per_rank, w13, w2, group_size:
             part = torch.zeros_like(y)
             for j in range(idx.shape[1]):                            # experts ascending inside
                 sel = group[:, j] == g
-                rows = torch.stack([yout[int(o)][int(p)] for o, p in
-                                    zip(o_sorted[sel, j], p_sorted[sel, j])]) if sel.any() else None
+                if not sel.any():
+                    rows = None
+                elif ret is not None:
+                    tok = torch.nonzero(sel).flatten()
+                    rows = ret[s][tok * idx.shape[1] + j]
+                else:
+                    rows = torch.stack([yout[int(o)][int(p)] for o, p in
+                                        zip(o_sorted[sel, j], p_sorted[sel, j])])
                 if rows is not None:
                     part[sel] += g_sorted[sel, j].float().unsqueeze(1) * rows.float()
             y += part.to(dt).float()                                 # one rounding per level

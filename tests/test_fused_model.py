@@ -99,3 +99,47 @@ def test_epoch_flags_bounded_wait_and_monotone_epochs():
                         on_poll=lambda: [flags.signal(1, s, 6) for s in range(4)]
                         if next(late) == 3 else None)
     assert status == fm.ST_OK
+
+
+@pytest.mark.parametrize("world,E,n_groups,k,M", [(4, 16, 4, 4, 2), (2, 8, 2, 2, 2), (1, 8, 4, 4, 2)])
+def test_return_maps_cover_real_rows_once(world, E, n_groups, k, M):
+    """Epilogue-push variant: every real row of every owner has exactly one return address,
+    padding rows have none, and every (source, slot) is addressed exactly once."""
+    _, routed = _routing(world, 40, E, n_groups, k, M, seed=5)
+    idx = [i for i, _ in routed]
+    plan = fm.plan_positions(idx, world, E, 64)
+    slots = max(i.numel() for i in idx)
+    maps = fm.return_maps(plan, idx, world, slots)
+    seen = set()
+    for o in range(world):
+        real = torch.zeros_like(maps[o], dtype=torch.bool)
+        for a, n in zip(plan["seg_start"][o].tolist(), plan["seg_count"][o].tolist()):
+            real[a:a + n] = True
+        assert bool(((maps[o] >= 0) == real).all())
+        vals = maps[o][real].tolist()
+        assert not seen.intersection(vals)
+        seen.update(vals)
+    want = {s * slots + p for s, i in enumerate(idx) for p in range(i.numel())}
+    assert seen == want
+
+
+def test_epilogue_push_model_equals_pull_model_bitwise():
+    torch.manual_seed(1)
+    world, E, H, d = 4, 16, 32, 16
+    cfg, routed = _routing(world, 24, E, 4, 4, 2, seed=11)
+    w13 = (torch.randn(E, H, 2 * d) * H ** -0.5).bfloat16()
+    w2 = (torch.randn(E, d, H) * d ** -0.5).bfloat16()
+    xs = [torch.randn(i.shape[0], H).bfloat16() for i, _ in routed]
+    args = (xs, [i for i, _ in routed], [g for _, g in routed], w13, w2, cfg.group_size)
+    pull = fm.one_hop_model(*args)
+    push = fm.one_hop_model(*args, epilogue_push=True)
+    for a, b in zip(pull, push):
+        assert torch.equal(a, b)
+
+
+def test_scatter_rows_skips_and_counts_bad_addresses():
+    yout = [torch.ones(4, 8)]
+    maps = [torch.tensor([0, 5, -1, 99])]            # 99 is outside 1 rank x 8 slots
+    ret, skipped = fm.scatter_rows(yout, maps, 1, 8, 8, torch.float32)
+    assert skipped == 1
+    assert ret[0][0].sum() == 8 and ret[0][5].sum() == 8 and ret[0].sum() == 16

@@ -222,3 +222,39 @@ def test_fused_positions_match_host_model(native_ops, world):
     for item in out:
         assert item[1] != "error", item[2]
         assert all(v is True or v == 0 for v in item[1].values()), item
+
+
+# The epilogue-push variant (GEMM 2 and the last dgrad GEMM store their rows into the origins'
+# return slots) has been checked against the host model on a CPU only; it runs here on request.
+_PUSH = pytest.mark.skipif(os.environ.get("TERRACE_TEST_EPILOGUE_PUSH", "0") != "1",
+                           reason="opt-in: TERRACE_TEST_EPILOGUE_PUSH=1")
+
+
+@_PUSH
+def test_epilogue_push_world1_equals_local_kernels(native_ops, monkeypatch):
+    monkeypatch.setenv("TERRACE_EP_EPILOGUE_PUSH", "1")
+    (rank, res, echo, x0, status, live), = _run(1, 1, 29781)
+    assert status == 0
+    assert live["epilogue_push_fwd"] == 1 and live["epilogue_push_bwd"] == 1
+    for i, (a, b) in enumerate(zip(res["one_hop"], res["ref"])):
+        if i == 2:
+            _close(a, b, 1e-2)
+        else:
+            assert torch.equal(a, b)
+    _close(echo, x0, 2e-2)
+
+
+@_PUSH
+def test_epilogue_push_world2_equals_two_hop_pull(native_ops, monkeypatch):
+    """One-hop with scattering epilogues against the two-hop pull path: bit for bit."""
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    monkeypatch.setenv("TERRACE_EP_EPILOGUE_PUSH", "1")
+    for rank, res, echo, x0, status, live in _run(2, 2, 29783):
+        assert status == 0
+        assert live["epilogue_push_fwd"] == 1 and live["epilogue_push_bwd"] == 1
+        for a, b in zip(res["one_hop"], res["two_hop"]):
+            assert torch.equal(a, b)
+        for a, b in zip(res["one_hop"], res["ref"]):
+            _close(a, b)
+        _close(echo, x0, 2e-2)
