@@ -154,3 +154,27 @@ def test_every_doc_names_only_existing_files():
             if not any(os.path.exists(os.path.join(ROOT, c)) for c in cands):
                 missing.append((name, path))
     assert not missing, missing
+
+
+def test_troute_explainer_example_is_what_the_code_routes():
+    """The one-token table of docs/10-troute.md, recomputed by ``t_route``."""
+    import torch
+    from terracemoe_simulator_b200.routing import TRouteConfig, t_route
+    text = _read("docs/10-troute.md")
+    aff = torch.tensor([[0.90, 0.85, 0.80, 0.78, 0.30, 0.20, 0.75, 0.72, 0.10, 0.60, 0.15, 0.05]])
+    cfg = TRouteConfig(12, 4, 4, 2)
+    for mode in ("global_topk", "group_limited", "quota_only", "full"):
+        idx, gates, _ = t_route(aff, torch.zeros(12), cfg, mode=mode)
+        order = torch.argsort(idx[0])
+        experts = " ".join(str(int(e)) for e in idx[0][order])
+        groups = ", ".join(str(g) for g in sorted(set((idx[0] // 3).tolist())))
+        g = " ".join("%.3f" % v for v in gates[0][order].tolist())
+        row = f"| `{mode}` | {experts} | {groups} | {g} |"
+        assert row in text, row
+
+
+def test_troute_explainer_conjunction_share():
+    from terracemoe_simulator_b200.tools import route_results as rr
+    text = _read("docs/10-troute.md")
+    assert "cost %d %% of what the quota alone costs" % round(100 * rr.conjunction_cost_share("20k")) in text
+    assert "%d %% at 30 k" % round(100 * rr.conjunction_cost_share("30k")) in text
