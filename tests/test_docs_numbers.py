@@ -99,6 +99,14 @@ def _phase_spans():
     return [s.splits_sync, s.hop_a, s.arrival_chain, s.hop_b, s.combine]
 
 
+def _launch_row(tier):
+    from terracemoe_simulator_b200.sim import core, profile, sweep
+    g = core.MoEGeometry("launch", 16, 8, 6, 2)
+    rows = profile.launch_sensitivity(g, sweep.CHAIN_SCENARIOS[tier][1],
+                                      deltas_ms=(0.0, 0.04, 0.08, 0.111, 0.16, 0.25))
+    return [r["breakeven"] for r in rows]
+
+
 def _b200_step_worst():
     from terracemoe_simulator_b200.sim import b200_step
     return [100 * b200_step.validate(verbose=False)[1]["worst"]]
@@ -129,6 +137,12 @@ CLAIMS = [
     ("docs/03-applicability.md", "| {n} | | groups of 2 GPUs | {n} | | groups of 4 GPUs | {n} |",
      _b200_grouping_ratios, 0.006),
     ("docs/09-phase-model.md", "the spans are {n} / {n} / {n} / {n} / {n} ms", _phase_spans, 0.0006),
+    ("docs/09-phase-model.md", "| breakeven, PyTorch chain | {n} | {n} | {n} | {n} | {n} | {n} |",
+     lambda: _launch_row(0), 0.006),
+    ("docs/09-phase-model.md", "| breakeven, fused target | {n} | {n} | {n} | {n} | {n} | {n} |",
+     lambda: _launch_row(1), 0.006),
+    ("docs/09-phase-model.md", "| breakeven, zero overhead | {n} | {n} | {n} | {n} | {n} | {n} |",
+     lambda: _launch_row(2), 0.006),
 ]
 
 
