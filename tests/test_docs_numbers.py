@@ -107,6 +107,11 @@ def _launch_row(tier):
     return [r["breakeven"] for r in rows]
 
 
+def _byte_criterion(q):
+    from terracemoe_simulator_b200.tools.breakeven import breakeven
+    return [breakeven(q, 8), breakeven(q, 8, True, 4), breakeven(q, 2), breakeven(q, 128)]
+
+
 def _b200_step_worst():
     from terracemoe_simulator_b200.sim import b200_step
     return [100 * b200_step.validate(verbose=False)[1]["worst"]]
@@ -137,6 +142,10 @@ CLAIMS = [
     ("docs/03-applicability.md", "| {n} | | groups of 2 GPUs | {n} | | groups of 4 GPUs | {n} |",
      _b200_grouping_ratios, 0.006),
     ("docs/09-phase-model.md", "the spans are {n} / {n} / {n} / {n} / {n} ms", _phase_spans, 0.0006),
+    ("docs/03-applicability.md", "| 2 | {n} | {n} | {n} | {n} |", lambda: _byte_criterion(2), 0.0006),
+    ("docs/03-applicability.md", "| 3 | {n} | {n} | {n} | {n} |", lambda: _byte_criterion(3), 0.0006),
+    ("docs/03-applicability.md", "| 4 | {n} | {n} | {n} | {n} |", lambda: _byte_criterion(4), 0.0006),
+    ("docs/03-applicability.md", "| 6 | {n} | {n} | {n} | {n} |", lambda: _byte_criterion(6), 0.0006),
     ("docs/09-phase-model.md", "| breakeven, PyTorch chain | {n} | {n} | {n} | {n} | {n} | {n} |",
      lambda: _launch_row(0), 0.006),
     ("docs/09-phase-model.md", "| breakeven, fused target | {n} | {n} | {n} | {n} | {n} | {n} |",
