@@ -155,3 +155,39 @@ def test_route_results_record_is_consistent():
                for v in rr.DOWNSTREAM_PP.values())
     assert abs(sum(rr.STEP_G) / 2 - 0.9976) < 1e-4
     assert max(m[3] for m in rr.FORERUNNER) == dict((m[0], m[3]) for m in rr.FORERUNNER)["full"]
+
+
+def test_residency_fit_recovers_a_known_profile():
+    from terracemoe_simulator_b200.bench import residency as rs
+    a, b, c, static, cap = 3.5e4, 2.0e5, 7.0e8, 4.0e10, 180e9
+    samples = []
+    for L in (4, 8, 16):
+        for tok in (4096, 8192):
+            peak = static + a * tok * L + b * tok + c
+            samples.append(rs.Sample(L, tok, static, peak, peak * 1.05, peak + 9e9))
+    prof, d = rs.fit_profile(samples, cap)
+    assert prof.measured and abs(prof.activation_bytes_per_token_layer - a) / a < 1e-6
+    assert abs(d["per_token"] - b) / b < 1e-6 and d["worst_residual"] < 1e-9
+    assert abs(prof.overhead_frac - 9e9 / cap) < 1e-12
+    with pytest.raises(ValueError):
+        rs.fit_profile(samples[:2], cap)
+    with pytest.raises(ValueError):                       # layers never vary
+        rs.fit_profile([s for s in samples if s.layers == 4] * 2, cap)
+    # a measured profile removes the ASSUMED tag from the memory verdict
+    from terracemoe_simulator_b200.sim import codesign
+    arch, machine = codesign.REFERENCE_ARCH, codesign.hgx_b200()
+    got = codesign.residency(arch, machine, 8, prof)
+    assert got["measured"] and got["provenance"]["activation_bytes"].startswith("measured")
+    assert codesign.residency(arch, machine, 8)["provenance"]["activation_bytes"].startswith("ASSUMED")
+
+
+def test_residency_measure_point_with_an_injected_probe():
+    from terracemoe_simulator_b200.bench import residency as rs
+    calls = []
+    probe = (lambda: calls.append("reset"),
+             lambda: {"peak_allocated": 5e6, "peak_reserved": 6e6, "device_used": 7e6})
+    s = rs.measure_point(2, 1, 16, device="cpu", dim=32, heads=2, experts=4, d_expert=16,
+                         d_shared=16, groups=2, top_k=2, top_groups=1, vocab=64, backend="grouped",
+                         steps=2, probe=probe)
+    assert calls == ["reset"] and s.layers == 2 and s.tokens == 16
+    assert s.peak_allocated == 5e6 and s.static_bytes > 0
