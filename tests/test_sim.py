@@ -302,3 +302,14 @@ def test_b200_step_model_within_gate():
         assert b200_step.predict_ms(n, rpn, "two_hop")["total_ms"] \
             < b200_step.predict_ms(n, rpn, "one_hop")["total_ms"]
         assert b200_step.MEASURED_MS[(n, rpn, "two_hop")] < b200_step.MEASURED_MS[(n, rpn, "one_hop")]
+
+
+def test_b200_epilogue_push_forecast_is_a_gain_bounded_by_the_combine():
+    from terracemoe_simulator_b200.sim import b200_step
+    for n, rpn, measured, now, then, scaled in b200_step.forecast_epilogue_push(verbose=False):
+        one_way = 0.5 * b200_step.comm_ms(n, rpn, "one_hop")
+        assert then < now and now - then <= 2.0 * one_way          # at most the two combines
+        assert abs((now - then) - 2.0 * (one_way - b200_step.local_reduce_ms())) < 1e-9
+        assert scaled < measured
+    with pytest.raises(ValueError):
+        b200_step.predict_ms(8, 2, "two_hop", epilogue_push=True)
