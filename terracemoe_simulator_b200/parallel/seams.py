@@ -30,7 +30,7 @@ from .. import ops
 from ..ops.refs import fixed_hist, stable_bucket_order
 from ..utils import drift_probe as _dp
 from . import pack as _pack
-from .ep import CALLS, _a2a, _a2a_raw, _as_list
+from .ep import CALLS, _a2a, _a2a_raw
 from .plan import plan_ta2a
 from .ta2a import _RowGather, build_expansion, expand_arrival_mask, pack_quota_wire
 
