@@ -1,4 +1,6 @@
 """Host model of the fused expert-parallel step: placement tiling, numerics, flag protocol."""
+import os
+
 import pytest
 import torch
 
@@ -143,3 +145,114 @@ def test_scatter_rows_skips_and_counts_bad_addresses():
     ret, skipped = fm.scatter_rows(yout, maps, 1, 8, 8, torch.float32)
     assert skipped == 1
     assert ret[0][0].sum() == 8 and ret[0][5].sum() == 8 and ret[0].sum() == 16
+
+
+class _RecorderLib:
+    """Stands in for the native op namespace: records op names, returns tensors of the right
+    shapes so that the Python orchestration of ``parallel/fused.py`` can run on a CPU."""
+
+    def __init__(self, T, k, H, epr, cap_rows):
+        self.calls, self.T, self.k, self.H, self.epr, self.cap = [], T, k, H, epr, cap_rows
+        self.check_schema = False
+
+    @staticmethod
+    def _check_schema(name, args):
+        """Arguments must fit the registered schema of the real op (count and basic types)."""
+        schema = getattr(torch.ops.terrace, name).default._schema
+        formal = schema.arguments
+        assert len(args) <= len(formal), (name, len(args), len(formal))
+        for i, f in enumerate(formal):
+            if i >= len(args):
+                assert f.has_default_value(), f"{name}: argument {f.name} missing"
+                continue
+            v, t = args[i], str(f.type)
+            if t == "Tensor":
+                ok = torch.is_tensor(v)
+            elif t == "Optional[Tensor]":
+                ok = v is None or torch.is_tensor(v)
+            elif t == "int":
+                ok = isinstance(v, int) and not isinstance(v, bool)
+            elif t == "bool":
+                ok = isinstance(v, bool)
+            elif t == "float":
+                ok = isinstance(v, (int, float)) and not isinstance(v, bool)
+            else:
+                ok = True
+            assert ok, f"{name}: argument {i} ({f.name}: {t}) got {type(v).__name__}"
+
+    def __getattr__(self, name):
+        def op(*a, **kw):
+            self.calls.append(name)
+            assert not kw
+            if self.check_schema:
+                self._check_schema(name, a)
+            T, k, H = self.T, self.k, self.H
+            i32 = dict(dtype=torch.int32)
+            if name == "ep_plan_pass1":
+                return (torch.zeros(T, k, **i32), torch.zeros(T, k), torch.zeros(T, k, **i32),
+                        torch.zeros(T, k, **i32), torch.zeros(128, 16, **i32))
+            if name == "ep_plan":
+                return (torch.zeros(16, **i32), torch.zeros(self.epr, **i32),
+                        torch.zeros(self.epr, **i32), torch.zeros(1, **i32))
+            if name in ("ep_push", "ep_push_ret"):
+                return torch.zeros(T, k, **i32), torch.zeros(T, k)
+            if name in ("ep_pull_combine", "ep_combine_local"):
+                return torch.zeros(T, H, dtype=torch.bfloat16)
+            if name == "grouped_wgrad":
+                return torch.zeros(self.epr, a[0].shape[1], a[1].shape[1], dtype=torch.bfloat16)
+            if name == "swiglu_bwd":
+                return torch.zeros_like(a[0])
+            return None
+        return op
+
+
+@pytest.mark.parametrize("push", [False, True])
+def test_fused_orchestration_launch_sequence(monkeypatch, push):
+    """Which ops one fused one-hop step issues, with and without the scattering epilogue."""
+    from terracemoe_simulator_b200.parallel import fused as fz
+    T, k, H, d, epr, cap = 8, 4, 32, 16, 16, 128
+    rec = _RecorderLib(T, k, H, epr, cap)
+    monkeypatch.setenv("TERRACE_CUSTOM_OPS", "1")
+    from terracemoe_simulator_b200 import ops
+    ops.reset()
+    rec.check_schema = ops.status().loaded       # the real schemas, when the library is built
+    assert rec.check_schema or not os.path.isfile(ops.status().lib or "")
+    monkeypatch.setattr(fz, "_lib", lambda: rec)
+    fctx = object.__new__(fz.FusedEPContext)
+    fctx.cfg = TRouteConfig(16, 2, 4, 2)
+    fctx.world, fctx.rank, fctx.rpn, fctx.tokens, fctx.cap_rows, fctx.epoch = 1, 0, 1, T, cap, 0
+    fctx.arena, fctx.done = torch.zeros(1, dtype=torch.uint8), torch.zeros(8, dtype=torch.int32)
+    fctx.two_hop_ok, fctx.epilogue_push, fctx.ret_slots = False, push, T * k
+    fctx.E, fctx.epr, fctx.k, fctx.M, fctx.q, fctx.hidden, fctx.d_expert = 16, epr, k, 2, 2, H, d
+    fctx.n_nodes, fctx.device = 1, torch.device("cpu")
+    fctx.off_ret, fctx.off_dret, fctx.off_rowmap = 0, 256, 512
+    fctx.ret_base = fctx.dret_base = torch.zeros(1, dtype=torch.int64)
+    fctx.row_map = torch.zeros(cap, dtype=torch.int32)
+    monkeypatch.setattr(fz.FusedEPContext, "section",
+                        lambda self, sel: torch.zeros(cap, H, dtype=torch.bfloat16))
+    x = torch.zeros(T, H, dtype=torch.bfloat16, requires_grad=True)
+    gates = torch.full((T, k), 0.25, requires_grad=True)
+    w13 = torch.zeros(epr, H, 2 * d, dtype=torch.bfloat16, requires_grad=True)
+    w2 = torch.zeros(epr, d, H, dtype=torch.bfloat16, requires_grad=True)
+    idx = torch.zeros(T, k, dtype=torch.int64)
+    y = fz.fused_moe_forward(fctx, x, idx, gates, w13, w2, mode="one_hop")
+    fwd = list(rec.calls)
+    rec.calls.clear()
+    y.backward(torch.zeros_like(y))
+    bwd = list(rec.calls)
+    if push:
+        assert fwd == ["ep_plan_pass1", "ep_plan", "ep_push_ret", "zero_pad_rows", "grouped_gemm_ex",
+                       "grouped_gemm_scatter", "ep_signal", "ep_combine_local"]
+        assert bwd == ["ep_push_ret", "zero_pad_rows", "grouped_gemm_ex", "grouped_wgrad",
+                       "swiglu_bwd", "grouped_wgrad", "grouped_gemm_scatter", "ep_signal",
+                       "ep_combine_local"]
+    else:
+        assert fwd == ["ep_plan_pass1", "ep_plan", "ep_push", "zero_pad_rows", "grouped_gemm_ex",
+                       "grouped_gemm_ex", "ep_signal", "ep_pull_combine"]
+        assert bwd == ["ep_push", "zero_pad_rows", "grouped_gemm_ex", "grouped_wgrad",
+                       "swiglu_bwd", "grouped_wgrad", "grouped_gemm_ex", "ep_signal",
+                       "ep_pull_combine"]
+    assert x.grad.shape == x.shape and gates.grad.shape == gates.shape
+    assert w13.grad.shape == w13.shape and w2.grad.shape == w2.shape
+    monkeypatch.undo()
+    ops.reset()
