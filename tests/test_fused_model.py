@@ -196,7 +196,13 @@ class _RecorderLib:
                         torch.zeros(self.epr, **i32), torch.zeros(1, **i32))
             if name in ("ep_push", "ep_push_ret"):
                 return torch.zeros(T, k, **i32), torch.zeros(T, k)
-            if name in ("ep_pull_combine", "ep_combine_local"):
+            if name == "hopa_rank":
+                return torch.zeros(T, 2, **i32), torch.zeros(128, 2, **i32)
+            if name == "hopa_push":
+                return torch.zeros(T, k, **i32), torch.zeros(T, 2, **i32)
+            if name == "origin_pull_dgate":
+                return torch.zeros(T, k)
+            if name in ("ep_pull_combine", "ep_combine_local", "origin_combine"):
                 return torch.zeros(T, H, dtype=torch.bfloat16)
             if name == "grouped_wgrad":
                 return torch.zeros(self.epr, a[0].shape[1], a[1].shape[1], dtype=torch.bfloat16)
@@ -254,5 +260,43 @@ def test_fused_orchestration_launch_sequence(monkeypatch, push):
                        "ep_pull_combine"]
     assert x.grad.shape == x.shape and gates.grad.shape == gates.shape
     assert w13.grad.shape == w13.shape and w2.grad.shape == w2.shape
+    monkeypatch.undo()
+    ops.reset()
+
+
+def test_fused_two_hop_orchestration_launch_sequence(monkeypatch):
+    from terracemoe_simulator_b200 import ops
+    from terracemoe_simulator_b200.parallel import fused as fz
+    T, k, H, d, epr, cap = 8, 4, 32, 16, 8, 128
+    rec = _RecorderLib(T, k, H, epr, cap)
+    monkeypatch.setenv("TERRACE_CUSTOM_OPS", "1")
+    ops.reset()
+    rec.check_schema = ops.status().loaded
+    monkeypatch.setattr(fz, "_lib", lambda: rec)
+    fctx = object.__new__(fz.FusedEPContext)
+    fctx.cfg = TRouteConfig(16, 2, 4, 2)
+    fctx.world, fctx.rank, fctx.rpn, fctx.tokens, fctx.cap_rows, fctx.epoch = 2, 0, 1, T, cap, 0
+    fctx.arena, fctx.done = torch.zeros(1, dtype=torch.uint8), torch.zeros(8, dtype=torch.int32)
+    fctx.two_hop_ok, fctx.epilogue_push = True, False
+    fctx.E, fctx.epr, fctx.k, fctx.M, fctx.q, fctx.hidden, fctx.d_expert = 16, epr, k, 2, 2, H, d
+    fctx.n_nodes, fctx.device = 2, torch.device("cpu")
+    monkeypatch.setattr(fz.FusedEPContext, "section",
+                        lambda self, sel: torch.zeros(cap, H, dtype=torch.bfloat16))
+    x = torch.zeros(T, H, dtype=torch.bfloat16, requires_grad=True)
+    gates = torch.full((T, k), 0.25, requires_grad=True)
+    w13 = torch.zeros(epr, H, 2 * d, dtype=torch.bfloat16, requires_grad=True)
+    w2 = torch.zeros(epr, d, H, dtype=torch.bfloat16, requires_grad=True)
+    y = fz.fused_moe_forward(fctx, x, torch.zeros(T, k, dtype=torch.int64), gates, w13, w2,
+                             mode="two_hop")
+    fwd = list(rec.calls)
+    rec.calls.clear()
+    y.backward(torch.zeros_like(y))
+    assert fwd == ["ep_plan_pass1", "hopa_rank", "ep_plan", "hopa_push", "arrival_push",
+                   "zero_pad_rows", "grouped_gemm_ex", "grouped_gemm_ex", "ep_signal",
+                   "arrival_combine", "origin_combine"]
+    assert rec.calls == ["hopa_push", "arrival_push", "zero_pad_rows", "grouped_gemm_ex",
+                         "grouped_wgrad", "swiglu_bwd", "grouped_wgrad", "grouped_gemm_ex",
+                         "ep_signal", "arrival_combine", "origin_combine", "origin_pull_dgate"]
+    assert gates.grad.shape == gates.shape
     monkeypatch.undo()
     ops.reset()
