@@ -260,6 +260,11 @@ def run_ours(args, rank, world, local):
                 "d2h_bytes_per_step": losses.bytes_per_read, "last_loss": last_loss},
         "gpu_launches": results[best]["launches"] * args.steps,
     }
+    from terracemoe_simulator_b200.utils import trace
+    if trace.enabled():          # TERRACE_TRACE=events: per-phase device spans, max over ranks
+        rep = trace.report(group=True if world > 1 else None)
+        if rank == 0:
+            print(trace.format_report(rep), file=sys.stderr)
     return out
 
 

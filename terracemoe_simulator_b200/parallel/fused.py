@@ -36,6 +36,7 @@ import torch
 import torch.distributed as dist
 
 from ..routing import TRouteConfig
+from ..utils import trace
 
 # arena sections (must match section_offset() in symm_bindings.cpp)
 XIN, YOUT, DOUT, DXS, HA_ROWS, RED, HB_ROWS, DRED = range(8)
@@ -231,8 +232,10 @@ class _FusedMoE(torch.autograd.Function):
         lib = _lib()
         ep = fctx.next_epoch()
         xc = x.contiguous()
-        p = _plan(fctx, idx, gates, mode, ep)
-        _dispatch(fctx, p, xc, mode, ep)
+        with trace.phase("ep.fwd.plan"):
+            p = _plan(fctx, idx, gates, mode, ep)
+        with trace.phase("ep.fwd.dispatch"):
+            _dispatch(fctx, p, xc, mode, ep)
         first, n = fctx.owner_wait_range(mode)
         d = w2.shape[1]
         xin, yout = fctx.section(XIN), fctx.section(YOUT)
@@ -240,20 +243,22 @@ class _FusedMoE(torch.autograd.Function):
         need = any(ctx.needs_input_grad)
         h13 = (torch.empty(fctx.cap_rows, 2 * d, dtype=torch.bfloat16, device=x.device)
                if need else None)
-        if need:      # the weight gradient reads the padding rows of xin: keep them zero
-            lib.zero_pad_rows(xin, p["seg_start"], p["seg_count"], SEG_ALIGN)
-        lib.grouped_gemm_ex(xin, w13.contiguous(), act, h13, p["seg_start"], p["seg_count"], 0, 1,
-                            fctx.arena, FK_DATA, first, n, ep, SEG_ALIGN)
         scatter = mode == "one_hop" and fctx.epilogue_push
-        if scatter:     # GEMM 2 stores every output row into its origin's return slot
-            lib.grouped_gemm_scatter(act, w2.contiguous(), p["seg_start"], p["seg_count"], 0,
-                                     fctx.row_map, fctx.ret_base, fctx.ret_slots)
-            LIVE["epilogue_push_fwd"] += 1
-        else:
-            lib.grouped_gemm_ex(act, w2.contiguous(), yout, None, p["seg_start"], p["seg_count"],
-                                0, 0, None, 0, 0, 0, ep, SEG_ALIGN)
-        _signal_out(fctx, mode, FK_OUT, ep, xc)
-        y = _combine(fctx, p, mode, ep, src=YOUT, use_gate=True, backward=False)
+        with trace.phase("ep.fwd.experts"):
+            if need:      # the weight gradient reads the padding rows of xin: keep them zero
+                lib.zero_pad_rows(xin, p["seg_start"], p["seg_count"], SEG_ALIGN)
+            lib.grouped_gemm_ex(xin, w13.contiguous(), act, h13, p["seg_start"], p["seg_count"],
+                                0, 1, fctx.arena, FK_DATA, first, n, ep, SEG_ALIGN)
+            if scatter:     # GEMM 2 stores every output row into its origin's return slot
+                lib.grouped_gemm_scatter(act, w2.contiguous(), p["seg_start"], p["seg_count"], 0,
+                                         fctx.row_map, fctx.ret_base, fctx.ret_slots)
+                LIVE["epilogue_push_fwd"] += 1
+            else:
+                lib.grouped_gemm_ex(act, w2.contiguous(), yout, None, p["seg_start"],
+                                    p["seg_count"], 0, 0, None, 0, 0, 0, ep, SEG_ALIGN)
+        with trace.phase("ep.fwd.combine"):
+            _signal_out(fctx, mode, FK_OUT, ep, xc)
+            y = _combine(fctx, p, mode, ep, src=YOUT, use_gate=True, backward=False)
         ctx.fctx, ctx.mode, ctx.ep, ctx.plan = fctx, mode, ep, p
         ctx.save_for_backward(w13, w2, act, h13 if h13 is not None else act)
         ctx.gate_dtype = gates.dtype
@@ -268,6 +273,8 @@ class _FusedMoE(torch.autograd.Function):
         dyc = dy.contiguous()
         first, n = fctx.owner_wait_range(mode)
         scatter = mode == "one_hop" and fctx.epilogue_push
+        tr_dispatch = trace.phase("ep.bwd.dispatch")
+        tr_dispatch.__enter__()
         if scatter:     # the saved expert outputs sit in my own return slots
             _, dgs = lib.ep_push_ret(fctx.arena, dyc, p["es"], p["rank_local"], p["chunk_hist"],
                                      p["my_base"], p["gs"], True, DOUT, fctx.off_ret, True,
@@ -283,9 +290,12 @@ class _FusedMoE(torch.autograd.Function):
                           FK_B_HOPA, ep, fctx.done[0:1])
             lib.arrival_push(fctx.arena, p["rows_a"], HB_ROWS, DOUT, YOUT, True, True, FK_B_HOPA,
                              FK_B_DATA, FK_B_DG, ep, fctx.done[1:2])
+        tr_dispatch.__exit__(None, None, None)
         xin, dout, dxs = fctx.section(XIN), fctx.section(DOUT), fctx.section(DXS)
         d = w2.shape[1]
         dact = torch.empty(fctx.cap_rows, d, dtype=torch.bfloat16, device=dy.device)
+        tr_experts = trace.phase("ep.bwd.experts")
+        tr_experts.__enter__()
         lib.zero_pad_rows(dout, p["seg_start"], p["seg_count"], SEG_ALIGN)
         lib.grouped_gemm_ex(dout, w2.contiguous(), dact, None, p["seg_start"], p["seg_count"], 1,
                             0, fctx.arena, FK_B_DATA, first, n, ep, SEG_ALIGN)
@@ -299,10 +309,12 @@ class _FusedMoE(torch.autograd.Function):
         else:
             lib.grouped_gemm_ex(dh13, w13.contiguous(), dxs, None, p["seg_start"],
                                 p["seg_count"], 1, 0, None, 0, 0, 0, ep, SEG_ALIGN)
-        _signal_out(fctx, mode, FK_B_OUT, ep, dyc)
-        dx = _combine(fctx, p, mode, ep, src=DXS, use_gate=False, backward=True)
-        if mode == "two_hop":
-            dgs = lib.origin_pull_dgate(fctx.arena, p["es"], p["rowa"], FK_B_DG, ep)
+        tr_experts.__exit__(None, None, None)
+        with trace.phase("ep.bwd.combine"):
+            _signal_out(fctx, mode, FK_B_OUT, ep, dyc)
+            dx = _combine(fctx, p, mode, ep, src=DXS, use_gate=False, backward=True)
+            if mode == "two_hop":
+                dgs = lib.origin_pull_dgate(fctx.arena, p["es"], p["rowa"], FK_B_DG, ep)
         dgates = torch.zeros_like(dgs).scatter_(1, p["cols"].long(), dgs).to(ctx.gate_dtype)
         LIVE[f"{mode}_bwd"] += 1
         return dx, dgates, dw13, dw2, None, None, None

@@ -191,3 +191,46 @@ def test_residency_measure_point_with_an_injected_probe():
                          steps=2, probe=probe)
     assert calls == ["reset"] and s.layers == 2 and s.tokens == 16
     assert s.peak_allocated == 5e6 and s.static_bytes > 0
+
+
+def test_trace_is_a_noop_unless_enabled_and_accumulates_per_phase(monkeypatch):
+    import time
+    from terracemoe_simulator_b200.utils import trace
+    monkeypatch.delenv("TERRACE_TRACE", raising=False)
+    trace.reset()
+    assert not trace.enabled()
+    assert trace.phase("a") is trace.phase("b")                 # one shared no-op object
+    with trace.phase("a"):
+        pass
+    assert trace.report() == {}
+    monkeypatch.setenv("TERRACE_TRACE", "events")
+    trace.reset()
+    assert trace.enabled()
+    for _ in range(3):
+        with trace.phase("slow", cuda=False):
+            time.sleep(0.01)
+        with trace.phase("fast", cuda=False):
+            pass
+    rep = trace.report()
+    assert list(rep) == ["slow", "fast"] and rep["slow"]["calls"] == 3
+    assert rep["slow"]["ms"] >= 25.0 > rep["fast"]["ms"]
+    assert abs(rep["slow"]["ms_per_call"] - rep["slow"]["ms"] / 3) < 1e-9
+    assert "slow" in trace.format_report(rep)
+    assert trace.report() == {}                                  # the report reset the totals
+    monkeypatch.setenv("TERRACE_TRACE", "0")
+    trace.reset()
+    assert not trace.enabled()
+
+
+def test_trace_folds_old_spans_instead_of_growing_without_bound(monkeypatch):
+    from terracemoe_simulator_b200.utils import trace
+    monkeypatch.setenv("TERRACE_TRACE", "events")
+    trace.reset()
+    monkeypatch.setattr(trace, "_MAX_PENDING", 8)
+    for _ in range(50):
+        with trace.phase("p", cuda=False):
+            pass
+    assert len(trace._SPANS["p"]) <= 8
+    assert trace.report()["p"]["calls"] == 50
+    monkeypatch.setenv("TERRACE_TRACE", "0")
+    trace.reset()
