@@ -60,6 +60,22 @@ def _align(n: int, a: int = 256) -> int:
     return (n + a - 1) // a * a
 
 
+GUARD_BYTES = 256       # canary words after every arena section
+GUARD_VALUE = 0xA5
+
+
+def arena_layout(sizes, guard: int = GUARD_BYTES):
+    """Offsets of the arena's sections, each followed by ``guard`` canary bytes that no kernel
+    may touch: ``(offsets, guard_offsets, total_bytes)``.  Sections start 256-byte aligned."""
+    offsets, guards, off = [], [], 0
+    for s in sizes:
+        offsets.append(off)
+        off += _align(s)
+        guards.append(off)
+        off += _align(guard) if guard > 0 else 0
+    return offsets, guards, off
+
+
 class FusedEPContext:
     def __init__(self, cfg: TRouteConfig, hidden: int, d_expert: int, tokens: int, *, world: int,
                  rank: int, rpn: int, device, group=None, row_capacity_factor: float = 2.0,
@@ -102,14 +118,13 @@ class FusedEPContext:
                   arows * H * 2, arows * self.q * 4]
         if self.epilogue_push:      # return slots (forward, backward) and the owners' row map
             sizes += [self.ret_slots * H * 2, self.ret_slots * H * 2, self.cap_rows * 4]
-        self.offsets, off = [], 0
-        for s in sizes:
-            self.offsets.append(off)
-            off += _align(s)
-        self.nbytes = off
+        self.offsets, self.guards, self.nbytes = arena_layout(sizes)
         lib = torch.ops.terrace
         dev_index = self.device.index if self.device.index is not None else torch.cuda.current_device()
         self.buf = lib.symm_alloc(self.nbytes, dev_index)
+        self._guard_index = (torch.tensor(self.guards, dtype=torch.int64, device=self.device)
+                             .unsqueeze(1) + torch.arange(GUARD_BYTES, device=self.device))
+        self.buf[self._guard_index.reshape(-1)] = GUARD_VALUE
         handle = lib.symm_ipc_handle(self.buf)
         handles = [None] * world
         dist.all_gather_object(handles, handle.numpy().tobytes(), group=group)
@@ -164,6 +179,14 @@ class FusedEPContext:
 
     def take_status(self) -> int:
         return int(torch.ops.terrace.symm_take_status(self._dev_index))
+
+    def check_canaries(self) -> list:
+        """Indices of the arena sections whose trailing canary bytes were overwritten (by this
+        rank's kernels or by a peer's stores).  One host synchronisation; for tests and for
+        debugging, not for the step."""
+        bad = (self.buf[self._guard_index.reshape(-1)].view(len(self.guards), GUARD_BYTES)
+               != GUARD_VALUE).any(dim=1)
+        return torch.nonzero(bad).flatten().tolist()
 
 
 def _plan(ctx: FusedEPContext, idx, gates, mode: str, ep: int):

@@ -300,3 +300,15 @@ def test_fused_two_hop_orchestration_launch_sequence(monkeypatch):
     assert gates.grad.shape == gates.shape
     monkeypatch.undo()
     ops.reset()
+
+
+def test_arena_layout_puts_a_guard_after_every_section():
+    from terracemoe_simulator_b200.parallel.fused import GUARD_BYTES, arena_layout
+    sizes = [100, 4096, 1, 256 * 7 + 3]
+    offs, guards, total = arena_layout(sizes)
+    assert offs[0] == 0 and all(o % 256 == 0 for o in offs + guards)
+    for i, s in enumerate(sizes):
+        assert offs[i] + s <= guards[i]                          # the section ends before its guard
+        end = offs[i + 1] if i + 1 < len(sizes) else total
+        assert guards[i] + GUARD_BYTES <= end                    # and the guard before the next
+    assert arena_layout(sizes, guard=0)[2] == sum((s + 255) // 256 * 256 for s in sizes)

@@ -70,6 +70,8 @@ def _body(rank, world, queue, M, rpn):
     echo = fz.fused_dispatch_combine(fctx, x0, idx, gates0, mode=modes[-1])
     torch.cuda.synchronize()
     status = fctx.take_status() or ops.take_status(rank)
+    if not status and fctx.check_canaries():      # a store went past the end of an arena section
+        status = 7700 + fctx.check_canaries()[0]
     queue.put((rank, res, echo.float().cpu(), x0.float().cpu(), status,
                dict(fz.LIVE)))
 
