@@ -84,6 +84,10 @@ class FusedEPContext:
         if not ops.custom_ops_enabled():
             raise RuntimeError("the fused transport needs the native library: "
                                + ops.status().reason)
+        self._init_args = dict(cfg=cfg, hidden=hidden, d_expert=d_expert, tokens=tokens,
+                               world=world, rank=rank, rpn=rpn, device=device, group=group,
+                               row_capacity_factor=row_capacity_factor,
+                               epilogue_push=epilogue_push)
         if world > MAX_WORLD:
             raise ValueError(f"world={world} exceeds the arena limit {MAX_WORLD}")
         if cfg.n_experts % world or world % rpn:
@@ -176,6 +180,27 @@ class FusedEPContext:
         for p in self._opened:
             lib.symm_ipc_close(p, self._dev_index)
         self._opened = []
+
+    def rebuild(self) -> None:
+        """Recovery after a reported failure (a wait that ran out, a bad index): every rank of
+        the group calls this between steps.  The peers' mappings are closed, then (after a
+        barrier, so that nobody frees memory a peer still maps) the arena is freed and a fresh one
+        with the same geometry is allocated, exchanged and mapped; epochs restart at zero."""
+        args = self._init_args
+        torch.cuda.synchronize(self.device)
+        self.close()
+        if self.world > 1:
+            dist.barrier(group=self.group)
+        self.buf = self.arena = self.peer_ptrs = self.row_map = None   # views keep the storage alive
+        torch.cuda.synchronize(self.device)
+        if self.world > 1:
+            dist.barrier(group=self.group)
+        self.take_status()
+        self.__init__(args["cfg"], args["hidden"], args["d_expert"], args["tokens"],
+                      world=args["world"], rank=args["rank"], rpn=args["rpn"],
+                      device=args["device"], group=args["group"],
+                      row_capacity_factor=args["row_capacity_factor"],
+                      epilogue_push=args["epilogue_push"])
 
     def take_status(self) -> int:
         return int(torch.ops.terrace.symm_take_status(self._dev_index))

@@ -285,16 +285,17 @@ def _timeout_worker(rank, world, port, queue):
         torch.cuda.synchronize()
         waited = time.perf_counter() - t0
         status = fctx.take_status()
-        # the context is still usable: a regular dispatch + combine on a fresh arena runs clean
+        # the context is still usable: after recovery a regular dispatch + combine runs clean
         g = torch.Generator().manual_seed(0)
         x = torch.randn(200, 256, generator=g).bfloat16().to(dev)
         idx, gates, _ = t_route(torch.rand(200, 16, generator=g).to(dev), torch.zeros(16, device=dev), cfg)
-        fresh = fz.FusedEPContext(cfg, 256, 128, 256, world=1, rank=0, rpn=1, device=dev)
-        echo = fz.fused_dispatch_combine(fresh, x, idx, gates, mode="one_hop")
+        fctx.rebuild()                      # recovery: tear the arena down, build a fresh one
+        echo = fz.fused_dispatch_combine(fctx, x, idx, gates, mode="one_hop")
         torch.cuda.synchronize()
         err = (echo.float() - x.float()).abs().max().item()
-        queue.put((rank, {"status": status, "waited": waited, "after": fresh.take_status(),
-                          "echo_err": err}))
+        queue.put((rank, {"status": status, "waited": waited, "after": fctx.take_status(),
+                          "echo_err": err, "epoch": fctx.epoch,
+                          "canaries": len(fctx.check_canaries())}))
     except Exception as exc:  # noqa: BLE001
         import traceback
         queue.put((rank, "error", f"{type(exc).__name__}: {exc}\n{traceback.format_exc()}"))
@@ -321,3 +322,4 @@ def test_flag_wait_runs_out_with_a_status_and_a_usable_context(native_ops):
     assert res["status"] == 4, res                   # ST_TIMEOUT_FLAG
     assert 1.0 < res["waited"] < 30.0, res           # the 2 s limit, not an endless spin
     assert res["after"] == 0 and res["echo_err"] < 0.2, res
+    assert res["epoch"] == 1 and res["canaries"] == 0, res      # rebuilt arena, epochs restarted
