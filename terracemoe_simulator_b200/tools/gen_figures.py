@@ -269,16 +269,28 @@ FIGURES = {
 }
 
 
-def generate(out_dir: str, only=None) -> list:
+def also_pdf() -> bool:
+    """``TERRACE_FIG_PDF=1``: write a vector PDF beside every SVG (off by default)."""
+    return os.environ.get("TERRACE_FIG_PDF", "0").strip().lower() in ("1", "on", "true", "yes")
+
+
+def generate(out_dir: str, only=None, pdf=None) -> list:
     os.makedirs(out_dir, exist_ok=True)
+    pdf = also_pdf() if pdf is None else pdf
     written = []
     for name, fn in FIGURES.items():
         if only and not any(name.startswith(o) for o in only):
             continue
+        svg = fn()
         path = os.path.join(out_dir, name + ".svg")
         with open(path, "w", encoding="utf-8") as fh:
-            fh.write(fn())
+            fh.write(svg)
         written.append(path)
+        if pdf:
+            from .svg2pdf import convert
+            with open(os.path.join(out_dir, name + ".pdf"), "wb") as fh:
+                fh.write(convert(svg))
+            written.append(os.path.join(out_dir, name + ".pdf"))
     return written
 
 

@@ -234,3 +234,46 @@ def test_trace_folds_old_spans_instead_of_growing_without_bound(monkeypatch):
     assert trace.report()["p"]["calls"] == 50
     monkeypatch.setenv("TERRACE_TRACE", "0")
     trace.reset()
+
+
+def _check_pdf(blob: bytes):
+    """Structural check of a PDF: header, trailer, and every xref offset lands on its object."""
+    import re
+    assert blob.startswith(b"%PDF-1.4") and blob.rstrip().endswith(b"%%EOF")
+    start = int(re.search(rb"startxref\s+(\d+)", blob).group(1))
+    assert blob[start:start + 4] == b"xref"
+    lines = blob[start:].split(b"\n")
+    n = int(lines[1].split()[1])
+    for i in range(1, n):
+        off = int(lines[2 + i].split()[0])
+        assert blob[off:].startswith(b"%d 0 obj" % i), (i, blob[off:off + 12])
+    length = int(re.search(rb"/Length (\d+)", blob).group(1))
+    body = blob.split(b"stream\n", 1)[1]
+    assert body[length:length + 10] == b"\nendstream"
+    return body[:length].decode("latin-1")
+
+
+def test_svg2pdf_converts_every_figure(tmp_path, monkeypatch):
+    from terracemoe_simulator_b200.tools import gen_figures, svg2pdf
+    from terracemoe_simulator_b200.tools.svgplot import Chart, heatmap
+    c = Chart("a (title) with \\ specials", "x", "y")
+    c.line([1, 2, 3], [1.0, 4.0, 9.0], label="squares", dash="4,2")
+    c.band([1, 2, 3], [0.5, 3.0, 8.0], [1.5, 5.0, 10.0], label="band")
+    c.hline(2.0, label="limit")
+    stream = _check_pdf(svg2pdf.convert(c.render()))
+    assert "(squares) Tj" in stream and "\\(title\\)" in stream and "\\\\ specials" in stream
+    assert "/GS1 gs" in stream and "[4 2] 0 d" in stream and " c " in stream     # alpha, dash, circles
+    assert "0 -1 -1 0" in stream                                  # the rotated axis label
+    _check_pdf(svg2pdf.convert(heatmap([[0.5, 1.5], [1.0, 2.0]], ["a", "b"], ["c", "d"])))
+    # anchors use the Helvetica advance widths
+    assert abs(svg2pdf.text_width("0123456789", 10.0) - 55.6) < 1e-9
+    assert svg2pdf.text_width("iii", 10.0) < svg2pdf.text_width("WWW", 10.0)
+    # the switch: off by default, a .pdf beside every .svg when on
+    monkeypatch.delenv("TERRACE_FIG_PDF", raising=False)
+    assert [os.path.splitext(p)[1] for p in gen_figures.generate(str(tmp_path), ["f8"])] == [".svg"]
+    monkeypatch.setenv("TERRACE_FIG_PDF", "1")
+    out = gen_figures.generate(str(tmp_path), ["f8", "f14"])
+    assert sorted(os.path.splitext(p)[1] for p in out) == [".pdf", ".pdf", ".svg", ".svg"]
+    for p in out:
+        if p.endswith(".pdf"):
+            _check_pdf(open(p, "rb").read())
