@@ -86,7 +86,7 @@ def _cuda_probe(device):
 
 def measure_point(layers: int, batch: int, seq: int, *, device, dim=2048, heads=16, experts=64,
                   d_expert=1024, d_shared=1024, groups=4, top_k=4, top_groups=2, vocab=32000,
-                  backend="native", steps=3, probe=None) -> Sample:
+                  backend="native", steps=3, probe=None, ce_chunk=0) -> Sample:
     """One (layers, tokens) point: build the decoder, run ``steps`` optimizer steps, read the peaks
     of the last one.  ``probe = (reset, read)`` replaces the CUDA counters (tests)."""
     import torch
@@ -96,7 +96,7 @@ def measure_point(layers: int, batch: int, seq: int, *, device, dim=2048, heads=
     args = ModelArgs(vocab=vocab, dim=dim, n_layers=layers, n_heads=heads, seq_len=seq,
                      n_experts=experts, n_groups=groups, top_k=top_k, top_groups=top_groups,
                      d_expert=d_expert, d_shared=d_shared, n_shared=1, dense_first=1,
-                     expert_backend=backend)
+                     expert_backend=backend, ce_chunk=ce_chunk)
     torch.manual_seed(0)
     model = TerraceLM(args).to(device=dev, dtype=dtype)
     opt = torch.optim.AdamW(model.parameters(), lr=1e-4, fused=True if dev.type == "cuda" else None)

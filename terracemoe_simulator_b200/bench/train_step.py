@@ -36,7 +36,7 @@ def build_args(ns, world: int):
                      top_groups=ns.top_groups, d_expert=ns.d_expert, d_shared=ns.d_shared,
                      n_shared=1, dense_first=1, expert_backend=ns.backend,
                      ep_mode=ns.ep if world > 1 else "local", ep_rpn=ns.rpn,
-                     ep_fused=not ns.nccl)
+                     ep_fused=not ns.nccl, ce_chunk=ns.ce_chunk)
 
 
 def main(argv=None) -> int:
@@ -62,6 +62,9 @@ def main(argv=None) -> int:
     ap.add_argument("--dtype", default="bf16", choices=["bf16", "fp32"])
     ap.add_argument("--cpu", action="store_true")
     ap.add_argument("--lr", type=float, default=3e-4)
+    ap.add_argument("--ce-chunk", type=int, default=0,
+                    help="> 0: LM head + cross-entropy in chunks of that many tokens (saves the "
+                         "[tokens, vocab] logits)")
     ns = ap.parse_args(argv)
 
     rank = int(os.environ.get("RANK", "0"))

@@ -55,6 +55,51 @@ class ModelArgs:
     ep_mode: str = "local"               # local | one_hop | two_hop (expert-parallel layer)
     ep_rpn: int = 1                      # ranks per logical group for two_hop
     ep_fused: bool = False               # fused peer-memory kernels instead of NCCL all_to_all
+    ce_chunk: int = 0                    # > 0: LM head + cross-entropy in chunks of that many tokens
+
+
+class _ChunkedLMLoss(torch.autograd.Function):
+    """Mean cross-entropy of ``h @ w.T`` against ``targets`` without ever holding the
+    ``[tokens, vocab]`` logits: the head GEMM, the loss and their gradients are computed one token
+    chunk at a time in the forward pass (weight gradient accumulated in fp32), the backward pass
+    only scales.  Every chunk rounds its logits to the dtype of ``h`` exactly as the unchunked
+    ``head`` + ``F.cross_entropy(logits.float())`` does, so the loss differs from it only by the
+    order of the final sum.  At vocabulary 32000 and 32768 tokens the logits, their fp32 copy and
+    the gradient are 10 GB that this path never allocates.  The reference computes the loss in
+    one piece (``terrace/model.py:135-138``)."""
+
+    @staticmethod
+    def forward(ctx, h, w, targets, chunk):
+        n = h.shape[0]
+        dh = torch.empty_like(h)
+        dw = torch.zeros(w.shape, dtype=torch.float32, device=w.device)
+        total = torch.zeros((), dtype=torch.float32, device=h.device)
+        for s in range(0, n, chunk):
+            hc = h[s:s + chunk].detach().requires_grad_(True)
+            wc = w.detach().requires_grad_(True)
+            with torch.enable_grad():
+                part = F.cross_entropy(F.linear(hc, wc).float(), targets[s:s + chunk],
+                                       reduction="sum")
+            gh, gw = torch.autograd.grad(part, (hc, wc))
+            dh[s:s + chunk] = gh
+            dw += gw
+            total += part.detach()
+        ctx.save_for_backward(dh, dw)
+        ctx.n, ctx.w_dtype = n, w.dtype
+        return total / n
+
+    @staticmethod
+    def backward(ctx, g):
+        dh, dw = ctx.saved_tensors
+        scale = g / ctx.n
+        return dh * scale.to(dh.dtype), (dw * scale).to(ctx.w_dtype), None, None
+
+
+def chunked_lm_loss(h: torch.Tensor, w: torch.Tensor, targets: torch.Tensor, chunk: int):
+    """``F.cross_entropy(F.linear(h, w).float(), targets)`` computed in token chunks."""
+    if chunk <= 0:
+        raise ValueError("chunk must be positive")
+    return _ChunkedLMLoss.apply(h.reshape(-1, h.shape[-1]), w, targets.reshape(-1), int(chunk))
 
 
 def rmsnorm(x: torch.Tensor, w: torch.Tensor, eps: float = 1e-5) -> torch.Tensor:
@@ -171,10 +216,14 @@ class TerraceLM(nn.Module):
             idx_l.append(stats["expert_idx"])
             if getattr(self, "collect_routes", False):
                 routes.append(stats["expert_idx"])
-        logits = self.head(rmsnorm(x, self.nf))
-        if targets is None:
-            return logits, {}
-        lm = F.cross_entropy(logits.view(-1, logits.size(-1)).float(), targets.reshape(-1))
+        h = rmsnorm(x, self.nf)
+        if targets is not None and self.args.ce_chunk > 0 and torch.is_grad_enabled():
+            lm = chunked_lm_loss(h, self.head.weight, targets, self.args.ce_chunk)
+        else:
+            logits = self.head(h)
+            if targets is None:
+                return logits, {}
+            lm = F.cross_entropy(logits.view(-1, logits.size(-1)).float(), targets.reshape(-1))
         if self.args.balance_aux and loads:
             aux = _balance_aux(loads, gate_l, idx_l, self.args)
         else:

@@ -200,3 +200,45 @@ def test_expert_shard_round_trip():
         merge_state_dicts(shards)
     with pytest.raises(ValueError):
         shard_state_dict(full, 0, 3)
+
+
+@pytest.mark.parametrize("chunk", [5, 16, 64])
+def test_chunked_lm_loss_equals_the_unchunked_loss_and_gradients(chunk):
+    import torch.nn.functional as F
+    from terracemoe_simulator_b200.models.decoder import chunked_lm_loss
+    torch.manual_seed(0)
+    n, d, v = 37, 24, 50                                   # 37 tokens: the last chunk is ragged
+    h0, w0 = torch.randn(n, d), torch.randn(v, d) * d ** -0.5
+    tgt = torch.randint(0, v, (n,))
+    h1, w1 = h0.clone().requires_grad_(True), w0.clone().requires_grad_(True)
+    ref = F.cross_entropy(F.linear(h1, w1).float(), tgt)
+    (3.0 * ref).backward()
+    h2, w2 = h0.clone().requires_grad_(True), w0.clone().requires_grad_(True)
+    got = chunked_lm_loss(h2, w2, tgt, chunk)
+    (3.0 * got).backward()
+    torch.testing.assert_close(got, ref, rtol=1e-6, atol=1e-6)
+    torch.testing.assert_close(h2.grad, h1.grad, rtol=1e-5, atol=1e-6)
+    torch.testing.assert_close(w2.grad, w1.grad, rtol=1e-5, atol=1e-6)
+    with pytest.raises(ValueError):
+        chunked_lm_loss(h2, w2, tgt, 0)
+
+
+def test_model_with_chunked_loss_trains_like_the_unchunked_model():
+    from terracemoe_simulator_b200.models import ModelArgs, TerraceLM
+    kw = dict(vocab=64, dim=32, n_layers=3, n_heads=2, seq_len=16, n_experts=8, n_groups=4, top_k=2,
+              top_groups=1, d_expert=16, d_shared=16, expert_backend="grouped")
+    torch.manual_seed(1)
+    a = TerraceLM(ModelArgs(**kw))
+    torch.manual_seed(1)
+    b = TerraceLM(ModelArgs(ce_chunk=10, **kw))
+    idx = torch.randint(0, 64, (3, 17))
+    la, _ = a(idx[:, :-1], idx[:, 1:])
+    lb, _ = b(idx[:, :-1], idx[:, 1:])
+    la.backward()
+    lb.backward()
+    torch.testing.assert_close(la, lb, rtol=1e-6, atol=1e-6)
+    for (n1, p1), (_, p2) in zip(a.named_parameters(), b.named_parameters()):
+        if p1.grad is not None:
+            torch.testing.assert_close(p1.grad, p2.grad, rtol=2e-5, atol=1e-6, msg=n1)
+    with torch.no_grad():                                   # evaluation takes the plain path
+        assert torch.isfinite(b(idx[:, :-1], idx[:, 1:])[0])
