@@ -5,7 +5,10 @@ beyond the per-expert histograms, the row of the OWNER's expert-sorted GEMM inpu
 (token, pick) lands in.  This module restates that arithmetic in plain PyTorch for all ranks in
 one process, so that it can be checked on a CPU: the positions of all sources must tile every
 owner's segments exactly (no gap, no overlap), in (expert, source rank, token) order, with
-segments aligned to ``seg_align`` rows.  It also restates the epoch-flag protocol (flags only grow;
+segments aligned to ``seg_align`` rows.  ``hop_a_rows`` and ``two_hop_model`` do the same for the two-hop path (arrival rows at the
+group representatives, forwarding, reduction at the representative and at the origin), and
+``return_maps`` / ``scatter_rows`` for the variant in which the GEMM epilogue delivers the output
+rows.  It also restates the epoch-flag protocol (flags only grow;
 a wait is bounded and returns a status instead of blocking) so that a withheld flag can be tested
 without a GPU.
 
@@ -172,6 +175,101 @@ def one_hop_model(x_per_rank, idx_per_rank, gates_per_rank, w13, w2, group_size:
                 if rows is not None:
                     part[sel] += g_sorted[sel, j].float().unsqueeze(1) * rows.float()
             y += part.to(dt).float()                                 # one rounding per level
+        ys.append(y.to(dt))
+    return ys
+
+
+def hop_a_rows(idx_per_rank, world: int, n_experts: int, rpn: int, groups_m: int,
+               tokens_cap: int):
+    """Two-hop, Hop A placement.  Source ``s`` (group ``s // rpn``, local index ``s % rpn``) sends
+    one row per (token, run of ``q`` picks in one group ``g``) to the representative
+    ``g * rpn + s % rpn``, into row ``(s // rpn) * tokens_cap + rank`` of its arrival section,
+    ``rank`` counting the source's earlier items for the same group in (token, run) order.
+    Returns per source ``rep[T, M]`` and ``row[T, M]`` (picks sorted by expert first)."""
+    epr = n_experts // world
+    slots = epr * rpn
+    reps, rows = [], []
+    for s, idx in enumerate(idx_per_rank):
+        T, k = idx.shape
+        q = k // groups_m
+        es = torch.sort(idx, dim=1).values
+        first = es[:, ::q]                                           # first pick of every run
+        if not bool((torch.div(es, slots, rounding_mode="floor").view(T, groups_m, q)
+                     == torch.div(first, slots, rounding_mode="floor").unsqueeze(2)).all()):
+            raise ValueError("a run of q picks spans two groups: routing is not quota-shaped")
+        g = torch.div(first, slots, rounding_mode="floor")           # [T, M]
+        n_groups = world // rpn
+        onehot = torch.nn.functional.one_hot(g.reshape(-1), n_groups)
+        rank = (torch.cumsum(onehot, 0) - onehot).gather(1, g.reshape(-1, 1)).view(T, groups_m)
+        if int(rank.max()) >= tokens_cap:
+            raise ValueError("more Hop A rows for one group than the arrival section holds")
+        reps.append(g * rpn + s % rpn)
+        rows.append((s // rpn) * tokens_cap + rank)
+    return reps, rows
+
+
+def two_hop_model(x_per_rank, idx_per_rank, gates_per_rank, w13, w2, rpn: int, groups_m: int,
+                  seg_align: int = 64):
+    """The two-hop step on the host: Hop A row per (token, group) to the representative, Hop B of
+    every pick to its owner at the ORIGIN-computed position (the same positions as one-hop, so
+    the expert GEMMs see identical inputs), gate-weighted reduction of the ``q`` picks at the
+    representative (fp32, one rounding), sum of the ``M`` group rows at the origin in group order
+    (fp32, one rounding).  Returns ``y`` per rank; equals ``one_hop_model`` bit for bit when the
+    routing groups are the ``world // rpn`` rank groups."""
+    world, E = len(x_per_rank), w13.shape[0]
+    epr = E // world
+    plan = plan_positions(idx_per_rank, world, E, seg_align)
+    H, dt = x_per_rank[0].shape[1], x_per_rank[0].dtype
+    cap = max(i.shape[0] for i in idx_per_rank)
+    reps, rows = hop_a_rows(idx_per_rank, world, E, rpn, groups_m, cap)
+    n_groups = world // rpn
+    arrive = [torch.zeros(n_groups * cap, H, dtype=dt) for _ in range(world)]
+    used = [torch.zeros(n_groups * cap, dtype=torch.int64) for _ in range(world)]
+    for s, x in enumerate(x_per_rank):                               # Hop A
+        for m in range(groups_m):
+            for t in range(x.shape[0]):
+                r, a = int(reps[s][t, m]), int(rows[s][t, m])
+                arrive[r][a] = x[t]
+                used[r][a] += 1
+    if any(int(u.max()) > 1 for u in used):
+        raise AssertionError("two Hop A rows share an arrival slot")
+    xin = [torch.zeros(max(plan["rows"][o], 1), H, dtype=dt) for o in range(world)]
+    order = [torch.argsort(i, dim=1, stable=True) for i in idx_per_rank]
+    for s, idx in enumerate(idx_per_rank):                           # Hop B, from the arrival rows
+        k = idx.shape[1]
+        q = k // groups_m
+        p_sorted = plan["pos"][s].gather(1, order[s])
+        o_sorted = plan["owner"][s].gather(1, order[s])
+        for t in range(idx.shape[0]):
+            for j in range(k):
+                m = j // q
+                src = arrive[int(reps[s][t, m])][int(rows[s][t, m])]
+                xin[int(o_sorted[t, j])][int(p_sorted[t, j])] = src
+    yout = []
+    for o in range(world):
+        out = torch.zeros_like(xin[o])
+        for le in range(epr):
+            a, n = int(plan["seg_start"][o][le]), int(plan["seg_count"][o][le])
+            if n:
+                gate, up = (xin[o][a:a + n] @ w13[o * epr + le]).chunk(2, dim=-1)
+                out[a:a + n] = (torch.nn.functional.silu(gate) * up) @ w2[o * epr + le]
+        yout.append(out)
+    ys = []
+    for s, x in enumerate(x_per_rank):
+        idx, gates = idx_per_rank[s], gates_per_rank[s]
+        k = idx.shape[1]
+        q = k // groups_m
+        g_sorted = gates.gather(1, order[s])
+        p_sorted = plan["pos"][s].gather(1, order[s])
+        o_sorted = plan["owner"][s].gather(1, order[s])
+        y = torch.zeros(x.shape[0], H, dtype=torch.float32)
+        for m in range(groups_m):                                    # groups ascending
+            red = torch.zeros(x.shape[0], H, dtype=torch.float32)
+            for j in range(m * q, (m + 1) * q):                      # at the representative
+                rows_j = torch.stack([yout[int(o)][int(p)] for o, p in
+                                      zip(o_sorted[:, j], p_sorted[:, j])])
+                red += g_sorted[:, j].float().unsqueeze(1) * rows_j.float()
+            y += red.to(dt).float()                                  # the reduced row travels as bf16
         ys.append(y.to(dt))
     return ys
 

@@ -312,3 +312,40 @@ def test_arena_layout_puts_a_guard_after_every_section():
         end = offs[i + 1] if i + 1 < len(sizes) else total
         assert guards[i] + GUARD_BYTES <= end                    # and the guard before the next
     assert arena_layout(sizes, guard=0)[2] == sum((s + 255) // 256 * 256 for s in sizes)
+
+
+@pytest.mark.parametrize("world,rpn,E,k,M", [(4, 1, 16, 4, 2), (8, 2, 32, 6, 2), (4, 2, 16, 4, 2)])
+def test_two_hop_model_equals_one_hop_model_bitwise(world, rpn, E, k, M):
+    """The claim the GPU tests check on hardware, restated on the host: with origin-computed
+    positions and the canonical reduction tree the two paths give the same bits."""
+    torch.manual_seed(2)
+    n_groups = world // rpn
+    cfg, routed = _routing(world, 12, E, n_groups, k, M, seed=21)
+    H, d = 32, 16
+    w13 = (torch.randn(E, H, 2 * d) * H ** -0.5).bfloat16()
+    w2 = (torch.randn(E, d, H) * d ** -0.5).bfloat16()
+    xs = [torch.randn(i.shape[0], H).bfloat16() for i, _ in routed]
+    idx, gates = [i for i, _ in routed], [g for _, g in routed]
+    one = fm.one_hop_model(xs, idx, gates, w13, w2, cfg.group_size)
+    two = fm.two_hop_model(xs, idx, gates, w13, w2, rpn, M)
+    for a, b in zip(one, two):
+        assert torch.equal(a, b)
+
+
+def test_hop_a_rows_fill_each_source_block_from_zero_without_gaps():
+    world, rpn, E, k, M = 8, 2, 32, 6, 2
+    _, routed = _routing(world, 20, E, world // rpn, k, M, seed=4)
+    idx = [i for i, _ in routed]
+    cap = max(i.shape[0] for i in idx)
+    reps, rows = fm.hop_a_rows(idx, world, E, rpn, M, cap)
+    for s in range(world):
+        assert bool((reps[s] % rpn == s % rpn).all())                # same local index as the source
+        block = rows[s] // cap
+        assert bool((block == s // rpn).all())                       # the source group's block
+        for g in range(world // rpn):
+            mine = (reps[s] // rpn == g)
+            got = sorted((rows[s][mine] % cap).tolist())
+            assert got == list(range(len(got)))                      # ranks 0 .. n-1, each once
+    with pytest.raises(ValueError):                                  # global top-k is not quota-shaped
+        bad = [torch.tensor([[0, 1, 2, 9, 17, 25]])] * world
+        fm.hop_a_rows(bad, world, E, rpn, M, cap)
