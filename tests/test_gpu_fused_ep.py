@@ -186,6 +186,16 @@ def _model_worker(rank, world, port, queue):
                "seg_count_equal": bool(torch.equal(p["seg_count"].cpu().long(), plan["seg_count"][rank])),
                "status": fctx.take_status()}
         dist.barrier()
+        if world >= 2:       # two-hop: arrival rows at the representatives against the host model
+            ep2 = fctx.next_epoch()
+            p2 = fz._plan(fctx, idx, gates, "two_hop", ep2)
+            fz._dispatch(fctx, p2, x, "two_hop", ep2)
+            torch.cuda.synchronize()
+            reps, rows = fm.hop_a_rows(gathered, world, E, 1, 2, fctx.tokens)
+            res["rowa_equal"] = bool(torch.equal(p2["rowa"].cpu().long().view(T, 2), rows[rank]))
+            res["two_hop_pos_equal"] = bool(torch.equal(p2["pos"].cpu().long().view(T, k), want))
+            res["status2"] = fctx.take_status()
+            dist.barrier()
         if world == 1:       # every row of this rank's buffer holds the token the model put there
             xin = fctx.section(fz.XIN)
             tok = torch.arange(T).unsqueeze(1).expand(T, k)
