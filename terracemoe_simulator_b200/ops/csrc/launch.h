@@ -149,10 +149,10 @@ int tb200_arrival_push(const struct Tb200Arena* a, const int* rows_a, long long 
                        int* status, cudaStream_t stream);
 int tb200_arrival_combine(const struct Tb200Arena* a, const int* rows_a, long long off_src,
                           long long off_red, int use_gate, int wait_kind, int red_kind, int epoch,
-                          int* done_counter, int* status, cudaStream_t stream);
+                          int* done_counter, int* status, int push_back, cudaStream_t stream);
 int tb200_origin_combine(const struct Tb200Arena* a, const int* es, const int* rowa, void* y,
                          long long off_red, int T, int wait_kind, int epoch, int* status,
-                         cudaStream_t stream);
+                         int local_rows, cudaStream_t stream);
 int tb200_origin_pull_dgate(const struct Tb200Arena* a, const int* es, const int* rowa, float* dgs,
                             int T, int wait_kind, int epoch, int* status, cudaStream_t stream);
 

@@ -507,17 +507,23 @@ __global__ void arrival_push_kernel(Tb200Arena a, const int* __restrict__ rows_a
 __global__ void arrival_combine_kernel(Tb200Arena a, const int* __restrict__ rows_a,
                                        long long off_src, long long off_red, int use_gate,
                                        int wait_kind, int red_kind, int epoch, int* done_counter,
-                                       int* status) {
+                                       int* status, int push_back) {
+  // push_back: the reduced row goes straight into the ORIGIN's section (block of my group, row
+  // i) instead of my own (block of the source group); the origin then combines from local memory
   const int H = a.hidden, q = a.q, Tc = a.tokens_cap;
   const int my_local = a.rank % a.rpn, my_group = a.rank / a.rpn;
   block_wait_flags(a, wait_kind, my_group * a.rpn, a.rpn, epoch, status, ST_TIMEOUT_FLAG);
   const int* hdrs = sect<int>(a, a.rank, a.off_ha_hdr);
-  __nv_bfloat16* red = sect<__nv_bfloat16>(a, a.rank, off_red);
+  __nv_bfloat16* red_local = sect<__nv_bfloat16>(a, a.rank, off_red);
   for (int row = blockIdx.x; row < a.n_nodes * Tc; row += gridDim.x) {
     const int sg = row / Tc, i = row - sg * Tc;
     const int n_rows = rows_a[(sg * a.rpn + my_local) * a.n_nodes + my_group];
     if (i >= n_rows) continue;
     const int* hdr = hdrs + static_cast<size_t>(row) * 3 * q;
+    __nv_bfloat16* red_row =
+        push_back ? sect<__nv_bfloat16>(a, sg * a.rpn + my_local, off_red) +
+                        (static_cast<size_t>(my_group) * Tc + i) * H
+                  : red_local + static_cast<size_t>(row) * H;
     for (int cix = threadIdx.x; cix < H / 8; cix += blockDim.x) {
       float acc[8];
 #pragma unroll
@@ -542,7 +548,7 @@ __global__ void arrival_combine_kernel(Tb200Arena a, const int* __restrict__ row
       __nv_bfloat162* oh = reinterpret_cast<__nv_bfloat162*>(&out);
 #pragma unroll
       for (int u = 0; u < 4; ++u) oh[u] = __floats2bfloat162_rn(acc[2 * u], acc[2 * u + 1]);
-      *(reinterpret_cast<uint4*>(red + static_cast<size_t>(row) * H) + cix) = out;
+      *(reinterpret_cast<uint4*>(red_row) + cix) = out;
     }
   }
   if (block_done_is_last(done_counter)) {
@@ -555,10 +561,12 @@ __global__ void arrival_combine_kernel(Tb200Arena a, const int* __restrict__ row
 __global__ void origin_combine_kernel(Tb200Arena a, const int* __restrict__ es,
                                       const int* __restrict__ rowa, __nv_bfloat16* __restrict__ y,
                                       long long off_red, int T, int wait_kind, int epoch,
-                                      int* status) {
+                                      int* status, int local_rows) {
+  // local_rows: the representatives pushed the reduced rows into MY section (block of their
+  // group, same row inside the block); otherwise they are read from the representatives
   block_wait_flags(a, wait_kind, 0, a.n_nodes, epoch, status, ST_TIMEOUT_FLAG);
   const int H = a.hidden, M = a.groups_m, q = a.q, k = a.top_k;
-  const int slots = a.epr * a.rpn, my_local = a.rank % a.rpn;
+  const int slots = a.epr * a.rpn, my_local = a.rank % a.rpn, my_group = a.rank / a.rpn;
   for (int t = blockIdx.x; t < T; t += gridDim.x) {
     for (int cix = threadIdx.x; cix < H / 8; cix += blockDim.x) {
       float acc[8];
@@ -568,10 +576,17 @@ __global__ void origin_combine_kernel(Tb200Arena a, const int* __restrict__ es,
         const int e0 = es[t * k + m * q];
         const int row = rowa[t * M + m];
         if (e0 < 0 || e0 >= a.n_experts || row < 0 || row >= a.n_nodes * a.tokens_cap) continue;
-        const int rep = (e0 / slots) * a.rpn + my_local;
+        const int g = e0 / slots;
+        int rep = g * a.rpn + my_local, src_row = row;
+        if (local_rows) {
+          const int i = row - my_group * a.tokens_cap;      // my rank among the rows sent to g
+          if (i < 0 || i >= a.tokens_cap || g >= a.n_nodes) continue;
+          rep = a.rank;
+          src_row = g * a.tokens_cap + i;
+        }
         const uint4 v = __ldcg(reinterpret_cast<const uint4*>(
                                    sect<__nv_bfloat16>(a, rep, off_red) +
-                                   static_cast<size_t>(row) * H) + cix);
+                                   static_cast<size_t>(src_row) * H) + cix);
         const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v);
 #pragma unroll
         for (int u = 0; u < 4; ++u) {
@@ -713,22 +728,23 @@ extern "C" int tb200_arrival_push(const Tb200Arena* a, const int* rows_a, long l
 
 extern "C" int tb200_arrival_combine(const Tb200Arena* a, const int* rows_a, long long off_src,
                                      long long off_red, int use_gate, int wait_kind, int red_kind,
-                                     int epoch, int* done_counter, int* status,
+                                     int epoch, int* done_counter, int* status, int push_back,
                                      cudaStream_t stream) {
   if (!arena_ok(a)) return TB200_ERR_ARG;
   arrival_combine_kernel<<<148 * 8, 256, 0, stream>>>(*a, rows_a, off_src, off_red, use_gate,
                                                       wait_kind, red_kind, epoch, done_counter,
-                                                      status);
+                                                      status, push_back);
   return LAUNCH_OK();
 }
 
 extern "C" int tb200_origin_combine(const Tb200Arena* a, const int* es, const int* rowa, void* y,
                                     long long off_red, int T, int wait_kind, int epoch, int* status,
-                                    cudaStream_t stream) {
+                                    int local_rows, cudaStream_t stream) {
   if (!arena_ok(a)) return TB200_ERR_ARG;
   int blocks = T < 1 ? 1 : (T > 148 * 8 ? 148 * 8 : T);
   origin_combine_kernel<<<blocks, 256, 0, stream>>>(*a, es, rowa, static_cast<__nv_bfloat16*>(y),
-                                                    off_red, T, wait_kind, epoch, status);
+                                                    off_red, T, wait_kind, epoch, status,
+                                                    local_rows);
   return LAUNCH_OK();
 }
 

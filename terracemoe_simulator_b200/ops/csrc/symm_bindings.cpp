@@ -335,24 +335,25 @@ void arrival_push(const Tensor& arena, const Tensor& rows_a, int64_t rows_sel, i
 
 void arrival_combine(const Tensor& arena, const Tensor& rows_a, int64_t src_sel, int64_t red_sel,
                      bool use_gate, int64_t wait_kind, int64_t red_kind, int64_t epoch,
-                     Tensor done) {
+                     Tensor done, bool push_back) {
   const Tb200Arena* a = arena_of(arena);
   c10::cuda::CUDAGuard guard(rows_a.device());
   check_rc(tb200_arrival_combine(a, rows_a.data_ptr<int>(), section_offset(a, src_sel),
                                  section_offset(a, red_sel), use_gate, wait_kind, red_kind, epoch,
-                                 done.data_ptr<int>(), st_ptr(rows_a), cur_stream()),
+                                 done.data_ptr<int>(), st_ptr(rows_a), push_back ? 1 : 0,
+                                 cur_stream()),
            "arrival_combine");
 }
 
 Tensor origin_combine(const Tensor& arena, const Tensor& es, const Tensor& rowa, int64_t red_sel,
-                      int64_t wait_kind, int64_t epoch) {
+                      int64_t wait_kind, int64_t epoch, bool local_rows) {
   const Tb200Arena* a = arena_of(arena);
   c10::cuda::CUDAGuard guard(es.device());
   const int64_t T = es.size(0);
   Tensor y = at::empty({T, a->hidden}, es.options().dtype(at::kBFloat16));
   check_rc(tb200_origin_combine(a, es.data_ptr<int>(), rowa.data_ptr<int>(), y.data_ptr(),
                                 section_offset(a, red_sel), T, wait_kind, epoch, st_ptr(es),
-                                cur_stream()),
+                                local_rows ? 1 : 0, cur_stream()),
            "origin_combine");
   return y;
 }
@@ -491,9 +492,10 @@ void terrace_b200_register_symm(torch::Library& m) {
         "bool scale_gate, bool want_dgate, int wait_kind, int data_kind, int dg_kind, int epoch, "
         "Tensor(a!) done) -> ()", &arrival_push);
   m.def("arrival_combine(Tensor arena, Tensor rows_a, int src_sel, int red_sel, bool use_gate, "
-        "int wait_kind, int red_kind, int epoch, Tensor(a!) done) -> ()", &arrival_combine);
+        "int wait_kind, int red_kind, int epoch, Tensor(a!) done, bool push_back=False) -> ()",
+        &arrival_combine);
   m.def("origin_combine(Tensor arena, Tensor es, Tensor rowa, int red_sel, int wait_kind, "
-        "int epoch) -> Tensor", &origin_combine);
+        "int epoch, bool local_rows=False) -> Tensor", &origin_combine);
   m.def("origin_pull_dgate(Tensor arena, Tensor es, Tensor rowa, int wait_kind, int epoch) -> "
         "Tensor", &origin_pull_dgate);
   m.def("grouped_gemm_ex(Tensor A, Tensor B, Tensor(a!) C, Tensor(b!)? C2, Tensor seg_start, "
