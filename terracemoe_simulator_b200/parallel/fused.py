@@ -14,6 +14,11 @@ One step of ``fused_moe_forward`` (no host synchronisation anywhere):
             representative pulls, applies the gates and reduces per row -> origin pulls and adds
             its M group rows
 
+Two-hop with ``TERRACE_EP_PUSH_BACK=1`` (off by default): the representative stores each reduced
+(token, group) row into the ORIGIN's section (block of the representative's group, same row
+inside the block) instead of keeping it for the origin to read remotely; the origin's final sum
+then reads local memory.  Values and order are unchanged.
+
 One-hop with ``epilogue_push`` (``TERRACE_EP_EPILOGUE_PUSH=1``; off by default): the push also
 leaves every row's return address in the owner's row map, the second expert GEMM stores each
 output row from its epilogue straight into the ORIGIN's return slot over NVLink (one kernel does
@@ -48,7 +53,7 @@ MAX_WORLD = 16
 SEG_ALIGN = 64          # expert segments start on multiples of 64 rows (zero padding rows)
 
 LIVE = {"one_hop_fwd": 0, "two_hop_fwd": 0, "one_hop_bwd": 0, "two_hop_bwd": 0, "echo": 0,
-        "epilogue_push_fwd": 0, "epilogue_push_bwd": 0}
+        "epilogue_push_fwd": 0, "epilogue_push_bwd": 0, "push_back": 0}
 
 
 def _lib():
@@ -107,6 +112,9 @@ class FusedEPContext:
         if epilogue_push is None:
             epilogue_push = os.environ.get("TERRACE_EP_EPILOGUE_PUSH", "0") == "1"
         self.epilogue_push = bool(epilogue_push)
+        # two-hop return leg: the representative stores its reduced rows into the origin's section
+        # instead of the origin reading them remotely (off by default; not yet run on a GPU)
+        self.push_back = os.environ.get("TERRACE_EP_PUSH_BACK", "0") == "1"
         self.ret_slots = tokens * self.k
         H = hidden
         sizes = [
@@ -269,9 +277,12 @@ def _combine(ctx, p, mode: str, ep: int, *, src: int, use_gate: bool, backward: 
         return lib.ep_pull_combine(ctx.arena, p["pos"], p["es"], p["gs"] if use_gate else None,
                                    src, ctx.cfg.group_size, out_kind, ep)
     red_sel, red_kind = (DRED, FK_B_RED) if backward else (RED, FK_RED)
+    push = bool(getattr(ctx, "push_back", False))
     lib.arrival_combine(ctx.arena, p["rows_a"], src, red_sel, use_gate, out_kind, red_kind, ep,
-                        ctx.done[2:3])
-    return lib.origin_combine(ctx.arena, p["es"], p["rowa"], red_sel, red_kind, ep)
+                        ctx.done[2:3], push)
+    if push:
+        LIVE["push_back"] += 1
+    return lib.origin_combine(ctx.arena, p["es"], p["rowa"], red_sel, red_kind, ep, push)
 
 
 class _FusedMoE(torch.autograd.Function):

@@ -208,6 +208,14 @@ def hop_a_rows(idx_per_rank, world: int, n_experts: int, rpn: int, groups_m: int
     return reps, rows
 
 
+def push_back_rows(rows, reps, rpn: int, tokens_cap: int):
+    """Where the reduced (token, group) rows land when the representatives push them back: in
+    the origin's own section at ``group * tokens_cap + (arrival row - origin group * tokens_cap)``.
+    ``rows`` / ``reps`` as returned by ``hop_a_rows`` for one source; returns ``[T, M]``."""
+    origin_group = torch.div(rows, tokens_cap, rounding_mode="floor")
+    return torch.div(reps, rpn, rounding_mode="floor") * tokens_cap + (rows - origin_group * tokens_cap)
+
+
 def two_hop_model(x_per_rank, idx_per_rank, gates_per_rank, w13, w2, rpn: int, groups_m: int,
                   seg_align: int = 64):
     """The two-hop step on the host: Hop A row per (token, group) to the representative, Hop B of

@@ -349,3 +349,16 @@ def test_hop_a_rows_fill_each_source_block_from_zero_without_gaps():
     with pytest.raises(ValueError):                                  # global top-k is not quota-shaped
         bad = [torch.tensor([[0, 1, 2, 9, 17, 25]])] * world
         fm.hop_a_rows(bad, world, E, rpn, M, cap)
+
+
+def test_push_back_rows_are_distinct_slots_of_the_origin_section():
+    world, rpn, E, k, M = 8, 2, 32, 6, 2
+    _, routed = _routing(world, 20, E, world // rpn, k, M, seed=6)
+    idx = [i for i, _ in routed]
+    cap = max(i.shape[0] for i in idx)
+    reps, rows = fm.hop_a_rows(idx, world, E, rpn, M, cap)
+    for s in range(world):
+        local = fm.push_back_rows(rows[s], reps[s], rpn, cap)
+        assert int(local.min()) >= 0 and int(local.max()) < (world // rpn) * cap
+        assert local.unique().numel() == local.numel()               # one slot per (token, group)
+        assert bool((local // cap == reps[s] // rpn).all())          # block of the sending group

@@ -333,3 +333,21 @@ def test_flag_wait_runs_out_with_a_status_and_a_usable_context(native_ops):
     assert 1.0 < res["waited"] < 30.0, res           # the 2 s limit, not an endless spin
     assert res["after"] == 0 and res["echo_err"] < 0.2, res
     assert res["epoch"] == 1 and res["canaries"] == 0, res      # rebuilt arena, epochs restarted
+
+
+@pytest.mark.skipif(os.environ.get("TERRACE_TEST_PUSH_BACK", "0") != "1",
+                    reason="opt-in: TERRACE_TEST_PUSH_BACK=1 (two-hop return leg by push; not yet "
+                           "run on a GPU)")
+@pytest.mark.parametrize("world,rpn", [(2, 1), (4, 2)])
+def test_two_hop_push_back_equals_one_hop(native_ops, monkeypatch, world, rpn):
+    """The representatives push their reduced rows into the origins' sections: same bits as the
+    one-hop path (which the switch does not touch)."""
+    if torch.cuda.device_count() < world:
+        pytest.skip(f"needs {world} GPUs")
+    monkeypatch.setenv("TERRACE_EP_PUSH_BACK", "1")
+    for rank, res, echo, x0, status, live in _run(world, 2, 29795 + world, rpn=rpn):
+        assert status == 0
+        assert live["push_back"] >= 2                      # forward and backward combine
+        for a, b in zip(res["one_hop"], res["two_hop"]):
+            assert torch.equal(a, b)
+        _close(echo, x0, 2e-2)
