@@ -97,3 +97,20 @@ def test_train_step_bench_runs_on_cpu(nproc, extra):
     assert out["config"]["parallelism"] == ("single" if nproc == 1 else "ep2+dp2")
     if nproc == 2:
         assert out["dp_allreduce_calls"] >= 3
+
+
+@pytest.mark.parametrize("nproc,extra", [(1, []), (2, ["--nccl", "--ep", "two_hop"])])
+def test_moe_block_bench_runs_on_cpu(nproc, extra):
+    """The V3-shaped block benchmark (capacity factor, shared expert) at toy size, 1 and 2 ranks."""
+    env = dict(os.environ, PYTHONPATH=ROOT, OMP_NUM_THREADS="1")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={nproc}",
+           "--master-addr", "127.0.0.1", "--master-port", str(29895 + nproc),
+           "-m", "terracemoe_simulator_b200.bench.moe_block", "--cpu", "--dtype", "fp32",
+           "--dim", "64", "--experts", "8", "--d-expert", "32", "--d-shared", "32", "--groups", "2",
+           "--top-k", "4", "--top-groups", "2", "--tokens", "64", "--capacity", "1.25",
+           "--steps", "2", "--warmup", "1"] + extra
+    proc = subprocess.run(cmd, capture_output=True, env=env, cwd=ROOT, timeout=600)
+    assert proc.returncode == 0, proc.stderr.decode(errors="replace")[-3000:]
+    line = [l for l in proc.stdout.decode().splitlines() if l.startswith("{")][-1]
+    out = json.loads(line)
+    assert out["n_gpus"] == nproc and out["value"] > 0 and out["ms_per_step"] > 0
