@@ -390,10 +390,105 @@ def fused_moe_forward(fctx: FusedEPContext, x, idx, gates, w13, w2, *, mode: str
     return _FusedMoE.apply(x, gates, w13, w2, idx, fctx, mode)
 
 
+def pipeline_depth() -> int:
+    """``TERRACE_EP_PIPELINE=n`` (default 1 = off): run the fused layer on ``n`` token slices."""
+    v = os.environ.get("TERRACE_EP_PIPELINE", "1").strip()
+    n = int(v) if v.isdigit() else 1
+    if n < 1 or n > 8:
+        raise ValueError(f"TERRACE_EP_PIPELINE={v!r}: expected 1..8")
+    return n
+
+
+class PipelinedFusedEP:
+    """Token-sliced software pipeline over the fused transport: ``n`` independent arenas, each
+    slice of the tokens runs plan -> push -> GEMMs -> combine on its own CUDA stream, so that the
+    dispatch and combine of one slice overlap the expert GEMMs of another.  The kernels are the
+    unchanged ones of the unsliced path.
+
+    Why this cannot deadlock although the GEMM kernels spin on flags: a slice's kernels wait only
+    for the SAME slice's pushes of OTHER GPUs; its own push precedes them in stream order; pushes
+    never wait; and slices never wait for each other.  Every chain of waits therefore ends in a
+    push kernel, which needs no shared memory and is always schedulable beside a resident GEMM.
+    If the hardware does not co-schedule the streams, the slices simply run one after another.
+
+    Numerics: every token's output and input gradient equal the unsliced path bit for bit (a
+    row's products do not depend on which tile it sits in); weight gradients are the sum of the
+    slices' partial gradients, so they differ from the unsliced ones by rounding.  One-hop and
+    two-hop still agree bit for bit under the same slicing."""
+
+    def __init__(self, cfg: TRouteConfig, hidden: int, d_expert: int, tokens: int, *, n: int,
+                 world: int, rank: int, rpn: int, device, group=None, **kw):
+        if n < 2:
+            raise ValueError("a pipeline needs at least two slices")
+        self.n, self.tokens = n, tokens
+        self.slice_tokens = (tokens + n - 1) // n
+        self.ctxs = [FusedEPContext(cfg, hidden, d_expert, self.slice_tokens, world=world,
+                                    rank=rank, rpn=rpn, device=device, group=group, **kw)
+                     for _ in range(n)]
+        self.device = torch.device(device)
+        self.streams = ([torch.cuda.Stream(device=self.device) for _ in range(n)]
+                        if self.device.type == "cuda" else [None] * n)
+        self.two_hop_ok = self.ctxs[0].two_hop_ok
+        self.cfg = cfg
+
+    def bounds(self, T: int):
+        step = (T + self.n - 1) // self.n
+        return [(lo, min(T, lo + step)) for lo in range(0, T, step)]
+
+    def forward(self, x, idx, gates, w13, w2, *, mode: str):
+        if x.shape[0] > self.tokens:
+            raise ValueError(f"{x.shape[0]} tokens exceed the context capacity {self.tokens}")
+        outs = []
+        cur = torch.cuda.current_stream(self.device) if self.streams[0] is not None else None
+        for (lo, hi), ctx, st in zip(self.bounds(x.shape[0]), self.ctxs, self.streams):
+            if st is None:
+                outs.append(fused_moe_forward(ctx, x[lo:hi], idx[lo:hi], gates[lo:hi], w13, w2,
+                                              mode=mode))
+                continue
+            st.wait_stream(cur)
+            with torch.cuda.stream(st):
+                y = fused_moe_forward(ctx, x[lo:hi], idx[lo:hi], gates[lo:hi], w13, w2, mode=mode)
+            for t in (x, idx, gates, w13, w2):      # allocated on the caller's stream, read on st
+                t.record_stream(st)
+            y.record_stream(cur)                    # allocated on st, read on the caller's stream
+            outs.append(y)
+        if cur is not None:
+            for st in self.streams[:len(outs)]:
+                cur.wait_stream(st)
+        return torch.cat(outs, dim=0)
+
+    def take_status(self) -> int:
+        return max(c.take_status() for c in self.ctxs)
+
+    def check_canaries(self) -> list:
+        return [(i, sec) for i, c in enumerate(self.ctxs) for sec in c.check_canaries()]
+
+    def close(self) -> None:
+        for c in self.ctxs:
+            c.close()
+
+
+def make_context(cfg: TRouteConfig, hidden: int, d_expert: int, tokens: int, **kw):
+    """A ``FusedEPContext``, or a ``PipelinedFusedEP`` when ``TERRACE_EP_PIPELINE`` asks for one."""
+    n = pipeline_depth()
+    if n > 1 and kw.get("world", 1) > 1:
+        return PipelinedFusedEP(cfg, hidden, d_expert, tokens, n=n, **kw)
+    return FusedEPContext(cfg, hidden, d_expert, tokens, **kw)
+
+
+def run_fused(ctx, x, idx, gates, w13, w2, *, mode: str):
+    if isinstance(ctx, PipelinedFusedEP):
+        return ctx.forward(x, idx, gates, w13, w2, mode=mode)
+    return fused_moe_forward(ctx, x, idx, gates, w13, w2, mode=mode)
+
+
 @torch.no_grad()
 def fused_dispatch_combine(fctx: FusedEPContext, x, idx, gates, *, mode: str):
     """Dispatch immediately followed by combine (rows echo back unchanged, gate-weighted): the
     communication-only measurement."""
+    if isinstance(fctx, PipelinedFusedEP):      # slice after slice on the caller's stream
+        return torch.cat([fused_dispatch_combine(c, x[lo:hi], idx[lo:hi], gates[lo:hi], mode=mode)
+                          for (lo, hi), c in zip(fctx.bounds(x.shape[0]), fctx.ctxs)], dim=0)
     if mode == "two_hop" and not fctx.two_hop_ok:
         mode = "one_hop"
     ep = fctx.next_epoch()

@@ -68,7 +68,7 @@ def routed_experts(x, idx, gates, w13, w2, cfg: TRouteConfig, *, mode: str, worl
         return torch.zeros_like(x).index_add(0, tok, w * out)
     if fused:
         from . import fused as fz
-        return fz.fused_moe_forward(ctx, x, idx, gates, w13, w2, mode=mode)
+        return fz.run_fused(ctx, x, idx, gates, w13, w2, mode=mode)
     if mode == "one_hop":
         return ep_moe_forward(x, idx, gates, w13, w2, world, E, rpn=rpn)
     return ta2a_moe_forward(x, idx, gates, w13, w2, world, E, rpn=rpn, groups_m=cfg.top_groups)
@@ -93,8 +93,8 @@ class MoELayerRunner:
             init_ta2a_groups(world, rpn)
         if self.fused:
             from . import fused as fz
-            self.ctx = fz.FusedEPContext(cfg, hidden, d_expert, tokens, world=world, rank=rank,
-                                         rpn=rpn, device=device)
+            self.ctx = fz.make_context(cfg, hidden, d_expert, tokens, world=world, rank=rank,
+                                       rpn=rpn, device=device)
 
     def __call__(self, x, router_w, w13, w2):
         idx, gates, _gidx, _load = _route(x, router_w, self.bias, self.cfg)
@@ -201,9 +201,9 @@ class EPTerracedMoE(nn.Module):
             return None
         if self._ctx is None or self._ctx.tokens < tokens:
             from . import fused as fz
-            self._ctx = fz.FusedEPContext(self.cfg, self.hidden, self.d_expert, tokens,
-                                          world=self.world, rank=self.rank, rpn=self.rpn,
-                                          device=device)
+            self._ctx = fz.make_context(self.cfg, self.hidden, self.d_expert, tokens,
+                                        world=self.world, rank=self.rank, rpn=self.rpn,
+                                        device=device)
         return self._ctx
 
     def forward(self, x: torch.Tensor):

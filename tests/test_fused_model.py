@@ -187,6 +187,11 @@ class _RecorderLib:
             if self.check_schema:
                 self._check_schema(name, a)
             T, k, H = self.T, self.k, self.H
+            if name in ("ep_plan_pass1",):
+                T = a[0].shape[0]
+            elif name in ("ep_push", "ep_push_ret", "hopa_push", "hopa_rank", "ep_pull_combine",
+                          "ep_combine_local", "origin_combine", "origin_pull_dgate"):
+                T = a[1].shape[0]                      # x, es or pos: one row per token
             i32 = dict(dtype=torch.int32)
             if name == "ep_plan_pass1":
                 return (torch.zeros(T, k, **i32), torch.zeros(T, k), torch.zeros(T, k, **i32),
@@ -362,3 +367,56 @@ def test_push_back_rows_are_distinct_slots_of_the_origin_section():
         assert int(local.min()) >= 0 and int(local.max()) < (world // rpn) * cap
         assert local.unique().numel() == local.numel()               # one slot per (token, group)
         assert bool((local // cap == reps[s] // rpn).all())          # block of the sending group
+
+
+def test_pipelined_context_slices_tokens_and_runs_every_slice(monkeypatch):
+    """The token-sliced pipeline: each slice runs the unsliced op sequence on its own context;
+    outputs come back in token order (CPU: no streams, the recorder stands in for the kernels)."""
+    from terracemoe_simulator_b200 import ops
+    from terracemoe_simulator_b200.parallel import fused as fz
+    T, k, H, d, epr, cap = 10, 4, 32, 16, 16, 128
+
+    rec = _RecorderLib(T, k, H, epr, cap)
+    monkeypatch.setenv("TERRACE_CUSTOM_OPS", "1")
+    ops.reset()
+    rec.check_schema = ops.status().loaded
+    monkeypatch.setattr(fz, "_lib", lambda: rec)
+
+    def fake_ctx(tokens):
+        c = object.__new__(fz.FusedEPContext)
+        c.cfg = TRouteConfig(16, 2, 4, 2)
+        c.world, c.rank, c.rpn, c.tokens, c.cap_rows, c.epoch = 1, 0, 1, tokens, cap, 0
+        c.arena, c.done = torch.zeros(1, dtype=torch.uint8), torch.zeros(8, dtype=torch.int32)
+        c.two_hop_ok, c.epilogue_push, c.push_back, c.ret_slots = False, False, False, tokens * k
+        c.E, c.epr, c.k, c.M, c.q, c.hidden, c.d_expert = 16, epr, k, 2, 2, H, d
+        c.n_nodes, c.device = 1, torch.device("cpu")
+        return c
+
+    monkeypatch.setattr(fz.FusedEPContext, "section",
+                        lambda self, sel: torch.zeros(cap, H, dtype=torch.bfloat16))
+    pipe = object.__new__(fz.PipelinedFusedEP)
+    pipe.n, pipe.tokens, pipe.slice_tokens = 3, T, 4
+    pipe.ctxs, pipe.streams = [fake_ctx(4) for _ in range(3)], [None] * 3
+    pipe.device, pipe.two_hop_ok = torch.device("cpu"), False
+    assert pipe.bounds(10) == [(0, 4), (4, 8), (8, 10)] and pipe.bounds(3) == [(0, 1), (1, 2), (2, 3)]
+    x = torch.zeros(T, H, dtype=torch.bfloat16, requires_grad=True)
+    gates = torch.full((T, k), 0.25, requires_grad=True)
+    w13 = torch.zeros(epr, H, 2 * d, dtype=torch.bfloat16, requires_grad=True)
+    w2 = torch.zeros(epr, d, H, dtype=torch.bfloat16, requires_grad=True)
+    y = fz.run_fused(pipe, x, torch.zeros(T, k, dtype=torch.int64), gates, w13, w2, mode="one_hop")
+    assert y.shape == (T, H)
+    assert rec.calls.count("ep_push") == 3 and rec.calls.count("ep_pull_combine") == 3
+    assert [c.epoch for c in pipe.ctxs] == [1, 1, 1]
+    y.backward(torch.zeros_like(y))
+    assert x.grad.shape == x.shape and w13.grad.shape == w13.shape
+    with pytest.raises(ValueError):
+        fz.run_fused(pipe, torch.zeros(T + 1, H, dtype=torch.bfloat16),
+                     torch.zeros(T + 1, k, dtype=torch.int64), torch.zeros(T + 1, k), w13, w2,
+                     mode="one_hop")
+    monkeypatch.setenv("TERRACE_EP_PIPELINE", "2")
+    assert fz.pipeline_depth() == 2
+    monkeypatch.setenv("TERRACE_EP_PIPELINE", "9")
+    with pytest.raises(ValueError):
+        fz.pipeline_depth()
+    monkeypatch.undo()
+    ops.reset()
