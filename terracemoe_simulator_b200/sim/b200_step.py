@@ -125,6 +125,26 @@ def predict_ms(n_gpus: int, rpn: int, path: str, epilogue_push: bool = False) ->
     return {"gemm_ms": g["ms"], "comm_ms": c, "total_ms": total, "gemm": g}
 
 
+PIPELINE_GEMM_TAIL = 0.03      # extra tail of the shorter per-slice GEMM launches (n = 2, 8 GPUs)
+
+
+def predict_pipelined_ms(n_gpus: int, rpn: int, path: str, slices: int = 2) -> dict:
+    """Token-sliced pipeline: while one slice computes, another dispatches or combines, so as long
+    as a slice's GEMMs outlast its communication only the first dispatch and the last combine
+    stay exposed, 1 / slices of the total; the GEMMs pay a small tail for their shorter launches.
+    A forecast written down before the first run of that path."""
+    if n_gpus == 1 or slices < 2:
+        return predict_ms(n_gpus, rpn, path)
+    g = gemm_ms(n_gpus)
+    c = comm_ms(n_gpus, rpn, path)
+    gemm = g["ms"] * (1.0 + PIPELINE_GEMM_TAIL)
+    per_slice_comm, per_slice_gemm = 2.0 * c / slices, gemm / slices
+    hidden_ok = per_slice_gemm >= per_slice_comm
+    exposed = 2.0 * c / slices if hidden_ok else 2.0 * c - (slices - 1) * per_slice_gemm
+    return {"gemm_ms": gemm, "comm_ms": c, "total_ms": gemm + ELEMENTWISE_FUSED_MS + exposed,
+            "hidden": hidden_ok}
+
+
 def forecast_epilogue_push(verbose: bool = True) -> list:
     """Expected one-hop step with the combine folded into the GEMM, next to today's model and
     measurement.  The additive model reads 2-8 % low, so the forecast is scaled by the measured /
@@ -165,10 +185,29 @@ def validate(verbose: bool = True):
     return ok, {"worst": worst, "rows": rows}
 
 
+def forecast_pipeline(verbose: bool = True, slices: int = 2) -> list:
+    rows = []
+    for (n, rpn, path), measured in sorted(MEASURED_MS.items()):
+        if n == 1:
+            continue
+        now = predict_ms(n, rpn, path)["total_ms"]
+        then = predict_pipelined_ms(n, rpn, path, slices)["total_ms"]
+        rows.append((n, rpn, path, measured, now, then, then * measured / now))
+    if verbose:
+        print("step with %d token slices on %d streams: forecast" % (slices, slices))
+        print("%4s %4s %-8s %9s %9s %9s %12s" % ("GPUs", "rpn", "path", "measured", "model",
+                                                 "forecast", "scaled (ms)"))
+        for n, rpn, path, m, now, then, scaled in rows:
+            print("%4d %4d %-8s %9.2f %9.2f %9.2f %12.2f" % (n, rpn, path, m, now, then, scaled))
+    return rows
+
+
 def main() -> None:
     validate()
     print()
     forecast_epilogue_push()
+    print()
+    forecast_pipeline()
 
 
 if __name__ == "__main__":

@@ -313,3 +313,15 @@ def test_b200_epilogue_push_forecast_is_a_gain_bounded_by_the_combine():
         assert scaled < measured
     with pytest.raises(ValueError):
         b200_step.predict_ms(8, 2, "two_hop", epilogue_push=True)
+
+
+def test_b200_pipeline_forecast_hides_all_but_one_slice_of_communication():
+    from terracemoe_simulator_b200.sim import b200_step
+    for n, rpn, path, measured, now, then, scaled in b200_step.forecast_pipeline(verbose=False):
+        p = b200_step.predict_pipelined_ms(n, rpn, path, 2)
+        assert p["hidden"] and then < now and scaled < measured
+        comm = 2.0 * b200_step.comm_ms(n, rpn, path)
+        gain = now - then
+        assert abs(gain - (comm / 2 - b200_step.PIPELINE_GEMM_TAIL * b200_step.gemm_ms(n)["ms"])) < 1e-9
+    assert b200_step.predict_pipelined_ms(1, 1, "local")["total_ms"] == \
+        b200_step.predict_ms(1, 1, "local")["total_ms"]
