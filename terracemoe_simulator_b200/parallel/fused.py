@@ -467,6 +467,10 @@ class PipelinedFusedEP:
         for c in self.ctxs:
             c.close()
 
+    def rebuild(self) -> None:
+        for c in self.ctxs:
+            c.rebuild()
+
 
 def make_context(cfg: TRouteConfig, hidden: int, d_expert: int, tokens: int, **kw):
     """A ``FusedEPContext``, or a ``PipelinedFusedEP`` when ``TERRACE_EP_PIPELINE`` asks for one."""
