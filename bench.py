@@ -251,7 +251,10 @@ def run_ours(args, rank, world, local):
                    "routing_groups": ROUTING_GROUPS[world], "rpn": RPN[world],
                    "step": "router+dispatch+experts+combine fwd+bwd",
                    "l2": "inputs larger than L2 (expert weights 2.2 GB per step)",
-                   "transport": "nccl all_to_all" if args.nccl_arm else "fused peer-memory kernels"},
+                   "transport": "nccl all_to_all" if args.nccl_arm else "fused peer-memory kernels",
+                   "variants": {"ep_pipeline": int(os.environ.get("TERRACE_EP_PIPELINE", "1") or 1),
+                                "epilogue_push": os.environ.get("TERRACE_EP_EPILOGUE_PUSH", "0") == "1",
+                                "push_back": os.environ.get("TERRACE_EP_PUSH_BACK", "0") == "1"}},
         "paths": results,
         "gemm_frac_of_measured_sustained": flops / (results[best]["ms_per_step"] * 1e-3) / (peak_tf * 1e12),
         "clocks": clocks,
