@@ -201,3 +201,14 @@ def test_troute_explainer_conjunction_share():
     text = _read("docs/10-troute.md")
     assert "cost %d %% of what the quota alone costs" % round(100 * rr.conjunction_cost_share("20k")) in text
     assert "%d %% at 30 k" % round(100 * rr.conjunction_cost_share("30k")) in text
+
+
+def test_onesided_doc_quotes_the_sweep():
+    import statistics
+    from terracemoe_simulator_b200.sim import calibrate
+    r = [x["nccl_a2a_x2_ms"] / x["one_hop_ms"] for x in calibrate.load_b200_sweep()
+         if x["tokens"] >= 4096]
+    lo, med, hi = min(r), statistics.median(r), max(r)
+    text = _read("docs/08-onesided.md")
+    assert "win by %d-%d %% (median %d %%)" % (round(100 * (lo - 1)), round(100 * (hi - 1)),
+                                               round(100 * (med - 1))) in text
