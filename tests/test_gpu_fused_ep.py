@@ -243,20 +243,6 @@ _PUSH = pytest.mark.skipif(os.environ.get("TERRACE_TEST_EPILOGUE_PUSH", "0") != 
 
 
 @_PUSH
-def test_epilogue_push_world1_equals_local_kernels(native_ops, monkeypatch):
-    monkeypatch.setenv("TERRACE_EP_EPILOGUE_PUSH", "1")
-    (rank, res, echo, x0, status, live), = _run(1, 1, 29781)
-    assert status == 0
-    assert live["epilogue_push_fwd"] == 1 and live["epilogue_push_bwd"] == 1
-    for i, (a, b) in enumerate(zip(res["one_hop"], res["ref"])):
-        if i == 2:
-            _close(a, b, 1e-2)
-        else:
-            assert torch.equal(a, b)
-    _close(echo, x0, 2e-2)
-
-
-@_PUSH
 def test_epilogue_push_world2_equals_two_hop_pull(native_ops, monkeypatch):
     """One-hop with scattering epilogues against the two-hop pull path: bit for bit."""
     if torch.cuda.device_count() < 2:
