@@ -104,3 +104,33 @@ def test_processes_learn_of_a_leaving_rank_before_their_next_step():
     assert out[1] == (1, "left")
     for r in (0, 2):
         assert out[r][:3] == (r, "lost", [1]) and out[r][4] > 0, out
+
+
+def _trace_proc(rank, world, port, queue):
+    import os as _os
+    import torch.distributed as _dist
+    _os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), TERRACE_TRACE="events")
+    _dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        from terracemoe_simulator_b200.utils import trace
+        trace.reset()
+        with trace.phase("work", cuda=False):
+            time.sleep(0.05 * (rank + 1))                # rank 1 is the slow one
+        rep = trace.report(group=True)
+        queue.put((rank, rep["work"]["ms"], rep["work"]["calls"]))
+    finally:
+        _dist.destroy_process_group()
+
+
+def test_trace_report_is_the_max_over_ranks():
+    import torch.multiprocessing as mp
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    procs = [ctx.Process(target=_trace_proc, args=(r, 2, 29433, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    out = sorted(q.get(timeout=120) for _ in range(2))
+    for p in procs:
+        p.join(timeout=30)
+    assert out[0][1] == out[1][1] >= 95.0                # both report the slow rank's 100 ms
+    assert out[0][2] == out[1][2] == 1
