@@ -62,6 +62,9 @@ def main(argv=None) -> int:
     ap.add_argument("--dtype", default="bf16", choices=["bf16", "fp32"])
     ap.add_argument("--cpu", action="store_true")
     ap.add_argument("--lr", type=float, default=3e-4)
+    ap.add_argument("--heartbeat", action="store_true",
+                    help="ranks watch each other over a TCP store and stop before the next step "
+                         "when a peer left or went quiet (utils/health.py)")
     ap.add_argument("--ce-chunk", type=int, default=0,
                     help="> 0: LM head + cross-entropy in chunks of that many tokens (saves the "
                          "[tokens, vocab] logits)")
@@ -110,7 +113,17 @@ def main(argv=None) -> int:
     feed = DevicePrefetcher(itertools.cycle(host), device)
     losses = DeferredScalar(device)          # every step's loss reaches the host, one step late
 
+    hb = None
+    if ns.heartbeat and world > 1:
+        from datetime import timedelta
+        from ..utils.health import Heartbeat
+        store = dist.TCPStore(os.environ["MASTER_ADDR"], int(os.environ["MASTER_PORT"]) + 7, world,
+                              rank == 0, timeout=timedelta(seconds=60))
+        hb = Heartbeat(store, rank, world, interval_s=0.5, timeout_s=30.0)
+
     def step():
+        if hb is not None:
+            hb.guard()                           # PeerLost before any launch of this step
         tok = next(feed)
         state["i"] += 1
         opt.zero_grad(set_to_none=True)
@@ -143,6 +156,8 @@ def main(argv=None) -> int:
     if cuda:
         b.record()
     barrier()
+    if hb is not None:
+        hb.stop()
     ms = a.elapsed_time(b) if cuda else (time.perf_counter() - t0) * 1e3
     t = torch.tensor([ms], device=device)
     if world > 1:

@@ -80,7 +80,9 @@ def test_is_expert_sharded_only_for_ep_layers():
     assert sync.calls == 0
 
 
-@pytest.mark.parametrize("nproc,extra", [(1, ["--backend", "grouped"]), (2, ["--nccl", "--ep", "two_hop"])])
+@pytest.mark.parametrize("nproc,extra", [(1, ["--backend", "grouped"]),
+                                         (2, ["--nccl", "--ep", "two_hop", "--heartbeat",
+                                              "--ce-chunk", "24"])])
 def test_train_step_bench_runs_on_cpu(nproc, extra):
     env = dict(os.environ, PYTHONPATH=ROOT, OMP_NUM_THREADS="1")
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={nproc}",
