@@ -56,10 +56,11 @@ def test_background_thread_beats_and_stops():
         watcher.check()
         time.sleep(0.15)
         first = watcher._counter(0, "beat")
-        assert first >= 3                            # the daemon thread has been beating
+        assert first >= 2                            # the daemon thread has been beating
         assert watcher.check() == ([], [])
     time.sleep(0.1)
     assert watcher._counter(0, "beat") <= first + 1  # stopped with the context
+    watcher.check()                                  # takes note of a last beat, if there was one
     time.sleep(0.4)
     assert watcher.check() == ([], [0])              # and is reported quiet after the timeout
 
