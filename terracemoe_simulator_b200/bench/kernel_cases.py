@@ -17,8 +17,8 @@ import sys
 
 import torch
 
-CASES = ("gemm_fwd", "gemm_swiglu", "gemm_dgrad", "gemm_wgrad", "rmsnorm", "route", "scatter",
-         "combine", "swiglu_bwd", "attn_fwd", "attn_bwd")
+CASES = ("gemm_fwd", "gemm_swiglu", "gemm_dgrad", "gemm_wgrad", "gemm_scatter", "rmsnorm", "route",
+         "scatter", "combine", "swiglu_bwd", "attn_fwd", "attn_bwd")
 
 
 def _peaks():
@@ -80,6 +80,26 @@ def main(argv=None) -> int:
         W = torch.randn(E, H, 2 * d, device=dev, dtype=bf) * H ** -0.5
         fn = lambda: lib.grouped_gemm(dY, W, st, cnt, 1, 0, False, 0, args.pad)
         flops = 2 * rows * H * 2 * d
+    elif args.case == "gemm_scatter":
+        # the scattering epilogue on one GPU: rows leave through a random permutation into a local
+        # buffer; checked once against the plain kernel followed by the same permutation
+        A = torch.randn(rows, d, device=dev, dtype=bf)
+        W = torch.randn(E, d, H, device=dev, dtype=bf) * d ** -0.5
+        perm = torch.randperm(rows, device=dev)
+        row_map = perm.to(torch.int32)                       # source 0, slot perm[r]
+        ret = torch.zeros(rows, H, device=dev, dtype=bf)
+        base = torch.tensor([ret.data_ptr()], dtype=torch.int64, device=dev)
+        fn = lambda: lib.grouped_gemm_scatter(A, W, st, cnt, 0, row_map, base, rows)
+        fn()
+        plain = lib.grouped_gemm(A, W, st, cnt, 0, 0, False, 0, args.pad)
+        plain = plain[0] if isinstance(plain, (tuple, list)) else plain
+        want = torch.zeros_like(ret)
+        want[perm] = plain[:rows]
+        torch.cuda.synchronize()
+        if not torch.equal(ret, want):
+            raise SystemExit("gemm_scatter: rows differ from the plain kernel's, max |diff| %g"
+                             % (ret.float() - want.float()).abs().max().item())
+        flops = 2 * rows * d * H
     elif args.case == "gemm_wgrad":
         X = torch.randn(rows, H, device=dev, dtype=bf)
         dY = torch.randn(rows, 2 * d, device=dev, dtype=bf)
