@@ -279,6 +279,11 @@ def test_b200_platform_and_gate():
     assert abs(fitted.flat.beta_gbps(1e6) - calibrate.B200_BETA_GBPS) < 30
     assert abs(fitted.self_copy_gbps - calibrate.B200_SELF_COPY_GBPS) < 200
     assert platforms.get("B200").hierarchy_ratio == 1.0 and platforms.coverage()["n_platforms"] == 3
+    # the registry's B200 line is the live gate: same target count, same median error
+    from terracemoe_simulator_b200.sim import calibrate as _cal, validate_b200 as _vb
+    _, d = _vb.validate_b200(verbose=False)
+    b = platforms.get("B200")
+    assert b.n_targets == len(_cal.load_b200_sweep()) and abs(b.fit_median_err - d["median"]) < 5e-4
     with pytest.raises(KeyError):
         platforms.get("Z")
     # token-level dedup (groups of one GPU) is where two-hop pays on a flat NVSwitch
