@@ -82,6 +82,8 @@ def _try_load() -> tuple[bool, str | None, str]:
         return False, None, (f"no native library found (TERRACE_OPS_LIB unset or missing, "
                              f"nothing under {_LIB_DIR}); build it with "
                              f"`python -m terracemoe_simulator_b200.ops.build`")
+    from ..utils.flags import check_native_flags
+    check_native_flags()      # the GEMM policy switches are read by C++: unknown values raise here
     try:
         torch.ops.load_library(lib)
     except Exception as exc:  # noqa: BLE001 - any loader failure is reported the same way

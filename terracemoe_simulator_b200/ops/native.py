@@ -368,8 +368,8 @@ def attention_supported(x, n_heads) -> bool:
     """Can the attention of a [B, T, dim] bf16 activation with n_heads heads run natively?
     ``TERRACE_ATTENTION=sdpa`` keeps the model on torch's scaled_dot_product_attention (the
     library kernel is about twice as fast as the kernels of this package at head width 128)."""
-    import os
-    if os.environ.get("TERRACE_ATTENTION", "native").strip().lower() == "sdpa":
+    from ..utils.flags import flag_choice
+    if flag_choice("TERRACE_ATTENTION", ("native", "sdpa"), "native") == "sdpa":
         return False
     if not (x.is_cuda and x.dtype == torch.bfloat16 and x.dim() == 3):
         return False

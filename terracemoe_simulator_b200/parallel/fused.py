@@ -35,13 +35,12 @@ issue 4 and 9 collectives with 1-3 host syncs per forward).
 """
 from __future__ import annotations
 
-import os
-
 import torch
 import torch.distributed as dist
 
 from ..routing import TRouteConfig
 from ..utils import trace
+from ..utils.flags import flag_bool, flag_int
 
 # arena sections (must match section_offset() in symm_bindings.cpp)
 XIN, YOUT, DOUT, DXS, HA_ROWS, RED, HB_ROWS, DRED = range(8)
@@ -110,11 +109,11 @@ class FusedEPContext:
                                + self.epr * (SEG_ALIGN - 1), 128)
         self.epoch = 0
         if epilogue_push is None:
-            epilogue_push = os.environ.get("TERRACE_EP_EPILOGUE_PUSH", "0") == "1"
+            epilogue_push = flag_bool("TERRACE_EP_EPILOGUE_PUSH")
         self.epilogue_push = bool(epilogue_push)
         # two-hop return leg: the representative stores its reduced rows into the origin's section
         # instead of the origin reading them remotely (off by default; not yet run on a GPU)
-        self.push_back = os.environ.get("TERRACE_EP_PUSH_BACK", "0") == "1"
+        self.push_back = flag_bool("TERRACE_EP_PUSH_BACK")
         self.ret_slots = tokens * self.k
         H = hidden
         sizes = [
@@ -392,11 +391,7 @@ def fused_moe_forward(fctx: FusedEPContext, x, idx, gates, w13, w2, *, mode: str
 
 def pipeline_depth() -> int:
     """``TERRACE_EP_PIPELINE=n`` (default 1 = off): run the fused layer on ``n`` token slices."""
-    v = os.environ.get("TERRACE_EP_PIPELINE", "1").strip()
-    n = int(v) if v.isdigit() else 1
-    if n < 1 or n > 8:
-        raise ValueError(f"TERRACE_EP_PIPELINE={v!r}: expected 1..8")
-    return n
+    return flag_int("TERRACE_EP_PIPELINE", 1, 1, 8)
 
 
 class PipelinedFusedEP:

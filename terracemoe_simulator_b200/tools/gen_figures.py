@@ -271,7 +271,8 @@ FIGURES = {
 
 def also_pdf() -> bool:
     """``TERRACE_FIG_PDF=1``: write a vector PDF beside every SVG (off by default)."""
-    return os.environ.get("TERRACE_FIG_PDF", "0").strip().lower() in ("1", "on", "true", "yes")
+    from ..utils.flags import flag_bool
+    return flag_bool("TERRACE_FIG_PDF")
 
 
 def generate(out_dir: str, only=None, pdf=None) -> list:

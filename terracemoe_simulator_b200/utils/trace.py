@@ -37,7 +37,12 @@ def _mode():
         elif v in ("1", "on", "true", "all"):
             _MODE = frozenset(("nvtx", "events"))
         else:
-            _MODE = frozenset(p for p in v.replace("+", ",").split(",") if p in ("nvtx", "events"))
+            parts = [p.strip() for p in v.replace("+", ",").split(",") if p.strip()]
+            bad = [p for p in parts if p not in ("nvtx", "events")]
+            if bad:
+                _MODE = frozenset()
+                raise ValueError("TERRACE_TRACE=%r: expected 0, 1, nvtx, events or nvtx,events" % v)
+            _MODE = frozenset(parts)
     return _MODE
 
 

@@ -102,3 +102,36 @@ def test_drift_probe_notes_contracts_and_compare(monkeypatch, tmp_path):
     assert len(problems) == 1 and problems[0].startswith("FIRST-DIVERGENCE pt=p2")
     assert dp.main(["compare", str(log_a), str(log_a)]) == 0
     assert dp.main(["compare", str(log_a), str(log_b)]) == 1
+
+
+def test_environment_switches_are_strict(monkeypatch):
+    """Unknown values raise; unset means the documented default."""
+    from terracemoe_simulator_b200.utils import flags, trace
+    monkeypatch.delenv("TERRACE_EP_PUSH_BACK", raising=False)
+    assert flags.flag_bool("TERRACE_EP_PUSH_BACK") is False
+    for v, want in (("1", True), ("on", True), ("0", False), ("", False), ("No", False)):
+        monkeypatch.setenv("TERRACE_EP_PUSH_BACK", v)
+        assert flags.flag_bool("TERRACE_EP_PUSH_BACK") is want
+    monkeypatch.setenv("TERRACE_EP_PUSH_BACK", "maybe")
+    with pytest.raises(ValueError):
+        flags.flag_bool("TERRACE_EP_PUSH_BACK")
+    monkeypatch.setenv("TERRACE_ATTENTION", "flash")
+    with pytest.raises(ValueError):
+        flags.flag_choice("TERRACE_ATTENTION", ("native", "sdpa"), "native")
+    monkeypatch.setenv("TERRACE_EP_PIPELINE", "two")
+    with pytest.raises(ValueError):
+        flags.flag_int("TERRACE_EP_PIPELINE", 1, 1, 8)
+    monkeypatch.setenv("TERRACE_EP_PIPELINE", "3")
+    assert flags.flag_int("TERRACE_EP_PIPELINE", 1, 1, 8) == 3
+    monkeypatch.setenv("TERRACE_GEMM_PAIR", "sometimes")
+    with pytest.raises(ValueError):
+        flags.check_native_flags()
+    monkeypatch.setenv("TERRACE_GEMM_PAIR", "auto")
+    flags.check_native_flags()
+    monkeypatch.setenv("TERRACE_TRACE", "everything")
+    trace.reset()
+    with pytest.raises(ValueError):
+        trace.enabled()
+    monkeypatch.setenv("TERRACE_TRACE", "0")
+    trace.reset()
+    assert not trace.enabled()
