@@ -148,3 +148,26 @@ def test_token_pipeline_on_one_gpu_equals_the_unsliced_layer(native_ops):
     _close(res["pipe"][2], res["plain"][2], 1e-2)        # gate gradients: lane partition differs
     for i in (3, 4):
         _close(res["pipe"][i], res["plain"][i], 2e-2)
+
+
+def test_residency_protocol_runs_and_returns_a_measured_profile(native_ops):
+    """The memory protocol at toy size: four (layers, tokens) points, a fitted activation slope
+    and an overhead share that make physical sense."""
+    import json
+    import os
+    import subprocess
+    import sys
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    env = dict(os.environ, TERRACE_CUSTOM_OPS="1", PYTHONPATH=root)
+    proc = subprocess.run([sys.executable, "-m", "terracemoe_simulator_b200.bench.residency",
+                           "--layers", "3", "5", "--batch", "1", "2", "--seq", "256", "--dim", "256",
+                           "--experts", "8", "--d-expert", "128"],
+                          env=env, capture_output=True, timeout=900, cwd=root)
+    assert proc.returncode == 0, proc.stderr.decode(errors="replace")[-3000:]
+    out = json.loads([l for l in proc.stdout.decode().splitlines() if l.startswith("{")][-1])
+    prof = out["profile"]
+    assert prof["measured"] is True and len(out["samples"]) == 4
+    assert prof["activation_bytes_per_token_layer"] > 0          # deeper and longer costs memory
+    assert 0.0 <= prof["overhead_frac"] < 0.5
+    peaks = [s["peak_allocated"] for s in out["samples"]]
+    assert max(peaks) > min(peaks)
