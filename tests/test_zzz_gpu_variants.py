@@ -171,3 +171,24 @@ def test_residency_protocol_runs_and_returns_a_measured_profile(native_ops):
     assert 0.0 <= prof["overhead_frac"] < 0.5
     peaks = [s["peak_allocated"] for s in out["samples"]]
     assert max(peaks) > min(peaks)
+
+
+def test_chunked_lm_loss_on_gpu_matches_the_unchunked_loss(native_ops):
+    import torch.nn.functional as F
+    from terracemoe_simulator_b200.models.decoder import chunked_lm_loss
+    torch.manual_seed(0)
+    dev = torch.device("cuda", 0)
+    n, d, v = 1000, 256, 2048
+    h0 = torch.randn(n, d, device=dev).bfloat16()
+    w0 = (torch.randn(v, d, device=dev) * d ** -0.5).bfloat16()
+    tgt = torch.randint(0, v, (n,), device=dev)
+    h1, w1 = h0.clone().requires_grad_(True), w0.clone().requires_grad_(True)
+    ref = F.cross_entropy(F.linear(h1, w1).float(), tgt)
+    ref.backward()
+    h2, w2 = h0.clone().requires_grad_(True), w0.clone().requires_grad_(True)
+    got = chunked_lm_loss(h2, w2, tgt, 384)                  # 1000 tokens: ragged last chunk
+    got.backward()
+    torch.cuda.synchronize()
+    torch.testing.assert_close(got, ref, rtol=1e-4, atol=1e-4)
+    _close(h2.grad.float(), h1.grad.float(), 2e-2)
+    _close(w2.grad.float(), w1.grad.float(), 2e-2)
