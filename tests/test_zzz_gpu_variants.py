@@ -6,6 +6,8 @@ through a per-row destination into the return slots, and the combine reduces fro
 The destinations are this GPU's own memory here; with more GPUs only the base addresses change
 (``tests/test_gpu_fused_ep.py::test_epilogue_push_world2_equals_two_hop_pull``, opt-in).
 """
+import os
+
 import pytest
 import torch
 
@@ -14,18 +16,88 @@ from test_gpu_fused_ep import _close, _run
 pytestmark = pytest.mark.gpu
 
 
-def test_epilogue_push_world1_equals_local_kernels(native_ops, monkeypatch):
-    """Bit-equal to the local kernels: same GEMM tiles, same reduction order, different route."""
-    monkeypatch.setenv("TERRACE_EP_EPILOGUE_PUSH", "1")
-    (rank, res, echo, x0, status, live), = _run(1, 1, 29781)
-    assert status == 0
-    assert live["epilogue_push_fwd"] == 1 and live["epilogue_push_bwd"] == 1
-    for i, (a, b) in enumerate(zip(res["one_hop"], res["ref"])):
-        if i == 2:      # gate gradients: same dot products, different lane partition
-            _close(a, b, 1e-2)
-        else:
-            assert torch.equal(a, b)
-    _close(echo, x0, 2e-2)
+def test_chunked_lm_loss_on_gpu_matches_the_unchunked_loss(native_ops):
+    import torch.nn.functional as F
+    from terracemoe_simulator_b200.models.decoder import chunked_lm_loss
+    torch.manual_seed(0)
+    dev = torch.device("cuda", 0)
+    n, d, v = 1000, 256, 2048
+    h0 = torch.randn(n, d, device=dev).bfloat16()
+    w0 = (torch.randn(v, d, device=dev) * d ** -0.5).bfloat16()
+    tgt = torch.randint(0, v, (n,), device=dev)
+    h1, w1 = h0.clone().requires_grad_(True), w0.clone().requires_grad_(True)
+    ref = F.cross_entropy(F.linear(h1, w1).float(), tgt)
+    ref.backward()
+    h2, w2 = h0.clone().requires_grad_(True), w0.clone().requires_grad_(True)
+    got = chunked_lm_loss(h2, w2, tgt, 384)                  # 1000 tokens: ragged last chunk
+    got.backward()
+    torch.cuda.synchronize()
+    torch.testing.assert_close(got, ref, rtol=1e-4, atol=1e-4)
+    _close(h2.grad.float(), h1.grad.float(), 2e-2)
+    _close(w2.grad.float(), w1.grad.float(), 2e-2)
+
+
+def _timeout_worker(rank, world, port, queue):
+    import torch.distributed as dist
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    os.environ["NCCL_NVLS_ENABLE"] = "0"
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world,
+                            device_id=torch.device("cuda", rank))
+    try:
+        import time
+        from terracemoe_simulator_b200.parallel import fused as fz
+        from terracemoe_simulator_b200.routing import TRouteConfig, t_route
+        dev = torch.device("cuda", rank)
+        cfg = TRouteConfig(16, 2, 4, 2)
+        fctx = fz.FusedEPContext(cfg, 256, 128, 256, world=1, rank=0, rpn=1, device=dev)
+        like = torch.zeros(8, device=dev)
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        # wait for an arrival flag of an epoch that nothing will ever signal
+        torch.ops.terrace.ep_signal(fctx.arena, fz.FK_OUT, 0, 1, 1, 0, 1 << 20, fz.FK_DATA, 0, 1, like)
+        torch.cuda.synchronize()
+        waited = time.perf_counter() - t0
+        status = fctx.take_status()
+        # the context is still usable: after recovery a regular dispatch + combine runs clean
+        g = torch.Generator().manual_seed(0)
+        x = torch.randn(200, 256, generator=g).bfloat16().to(dev)
+        idx, gates, _ = t_route(torch.rand(200, 16, generator=g).to(dev), torch.zeros(16, device=dev), cfg)
+        fctx.rebuild()                      # recovery: tear the arena down, build a fresh one
+        echo = fz.fused_dispatch_combine(fctx, x, idx, gates, mode="one_hop")
+        torch.cuda.synchronize()
+        err = (echo.float() - x.float()).abs().max().item()
+        queue.put((rank, {"status": status, "waited": waited, "after": fctx.take_status(),
+                          "echo_err": err, "epoch": fctx.epoch,
+                          "canaries": len(fctx.check_canaries())}))
+    except Exception as exc:  # noqa: BLE001
+        import traceback
+        queue.put((rank, "error", f"{type(exc).__name__}: {exc}\n{traceback.format_exc()}"))
+    finally:
+        dist.destroy_process_group()
+
+
+def test_flag_wait_runs_out_with_a_status_and_a_usable_context(native_ops):
+    """Failure detection without a fault: a wait on a flag that nothing sets gives up after its
+    limit, reports the flag-timeout code to the host, and later launches run normally."""
+    import torch.multiprocessing as mp
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    p = ctx.Process(target=_timeout_worker, args=(0, 1, 29791, q))
+    p.start()
+    try:
+        item = q.get(timeout=300)
+    finally:
+        p.join(timeout=30)
+        if p.is_alive():
+            p.terminate()
+    assert item[1] != "error", item[2]
+    res = item[1]
+    assert res["status"] == 4, res                   # ST_TIMEOUT_FLAG
+    assert 1.0 < res["waited"] < 30.0, res           # the 2 s limit, not an endless spin
+    assert res["after"] == 0 and res["echo_err"] < 0.2, res
+    assert res["epoch"] == 1 and res["canaries"] == 0, res      # rebuilt arena, epochs restarted
 
 
 @pytest.mark.parametrize("mode,pair", [(0, "0"), (1, "0"), (0, "1")])
@@ -80,6 +152,20 @@ print("ok")
     env["PYTHONPATH"] = root + os.pathsep + env.get("PYTHONPATH", "")
     proc = subprocess.run([sys.executable, "-c", code], env=env, capture_output=True, timeout=600)
     assert proc.returncode == 0 and b"ok" in proc.stdout, proc.stderr.decode(errors="replace")[-3000:]
+
+
+def test_epilogue_push_world1_equals_local_kernels(native_ops, monkeypatch):
+    """Bit-equal to the local kernels: same GEMM tiles, same reduction order, different route."""
+    monkeypatch.setenv("TERRACE_EP_EPILOGUE_PUSH", "1")
+    (rank, res, echo, x0, status, live), = _run(1, 1, 29781)
+    assert status == 0
+    assert live["epilogue_push_fwd"] == 1 and live["epilogue_push_bwd"] == 1
+    for i, (a, b) in enumerate(zip(res["one_hop"], res["ref"])):
+        if i == 2:      # gate gradients: same dot products, different lane partition
+            _close(a, b, 1e-2)
+        else:
+            assert torch.equal(a, b)
+    _close(echo, x0, 2e-2)
 
 
 def _pipeline_worker(rank, world, port, queue):
@@ -171,24 +257,3 @@ def test_residency_protocol_runs_and_returns_a_measured_profile(native_ops):
     assert 0.0 <= prof["overhead_frac"] < 0.5
     peaks = [s["peak_allocated"] for s in out["samples"]]
     assert max(peaks) > min(peaks)
-
-
-def test_chunked_lm_loss_on_gpu_matches_the_unchunked_loss(native_ops):
-    import torch.nn.functional as F
-    from terracemoe_simulator_b200.models.decoder import chunked_lm_loss
-    torch.manual_seed(0)
-    dev = torch.device("cuda", 0)
-    n, d, v = 1000, 256, 2048
-    h0 = torch.randn(n, d, device=dev).bfloat16()
-    w0 = (torch.randn(v, d, device=dev) * d ** -0.5).bfloat16()
-    tgt = torch.randint(0, v, (n,), device=dev)
-    h1, w1 = h0.clone().requires_grad_(True), w0.clone().requires_grad_(True)
-    ref = F.cross_entropy(F.linear(h1, w1).float(), tgt)
-    ref.backward()
-    h2, w2 = h0.clone().requires_grad_(True), w0.clone().requires_grad_(True)
-    got = chunked_lm_loss(h2, w2, tgt, 384)                  # 1000 tokens: ragged last chunk
-    got.backward()
-    torch.cuda.synchronize()
-    torch.testing.assert_close(got, ref, rtol=1e-4, atol=1e-4)
-    _close(h2.grad.float(), h1.grad.float(), 2e-2)
-    _close(w2.grad.float(), w1.grad.float(), 2e-2)
