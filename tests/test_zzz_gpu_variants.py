@@ -1,10 +1,15 @@
-"""Opt-in transport variants on one GPU; collected last so that the established suites run first.
+"""The newest paths on one GPU, collected last and ordered from the most to the least established,
+so that with ``-x`` a failure here cannot hide the suites before it.
 
-World 1 exercises the whole mechanism of the scattering GEMM epilogue on a single device: the
-push writes the row map, the second expert GEMM (and the last dgrad GEMM) store every output row
-through a per-row destination into the return slots, and the combine reduces from those slots.
-The destinations are this GPU's own memory here; with more GPUs only the base addresses change
-(``tests/test_gpu_fused_ep.py::test_epilogue_push_world2_equals_two_hop_pull``, opt-in).
+* chunked LM head + loss in bf16 against the unchunked loss
+* a flag wait that nothing satisfies: status code, then ``FusedEPContext.rebuild()``
+* the scattering GEMM op alone (forward, dgrad, CTA pair; a map entry out of range)
+* the world-1 fused layer through the scattering epilogue: the push writes the row map, the second
+  expert GEMM and the last dgrad GEMM store every row through a per-row destination into the
+  return slots, the combine reduces from those slots (with more GPUs only the base addresses
+  change: ``tests/test_gpu_fused_ep.py::test_epilogue_push_world2_equals_two_hop_pull``, opt-in)
+* three token slices on three streams and arenas against the unsliced layer
+* the residency protocol at toy size
 """
 import os
 
