@@ -420,3 +420,19 @@ def test_pipelined_context_slices_tokens_and_runs_every_slice(monkeypatch):
         fz.pipeline_depth()
     monkeypatch.undo()
     ops.reset()
+
+
+def test_canary_check_flags_the_section_whose_guard_was_overwritten():
+    from terracemoe_simulator_b200.parallel.fused import (GUARD_BYTES, GUARD_VALUE, FusedEPContext,
+                                                          arena_layout)
+    sizes = [100, 4096, 1, 256 * 7 + 3]
+    offs, guards, total = arena_layout(sizes)
+    c = object.__new__(FusedEPContext)
+    c.buf, c.guards = torch.zeros(total, dtype=torch.uint8), guards
+    c._guard_index = torch.tensor(guards, dtype=torch.int64).unsqueeze(1) + torch.arange(GUARD_BYTES)
+    c.buf[c._guard_index.reshape(-1)] = GUARD_VALUE
+    assert c.check_canaries() == []
+    c.buf[offs[1]:offs[1] + 4096] = 7                  # filling a whole section touches no guard
+    assert c.check_canaries() == []
+    c.buf[offs[2] + 256 + 5] = 0                       # one byte past the padded end of section 2
+    assert c.check_canaries() == [2]
