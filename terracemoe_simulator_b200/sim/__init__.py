@@ -12,7 +12,8 @@ import importlib
 MODULES = ("core", "calibrate", "fit", "validate_micro", "validate_sweep", "validate", "sweep",
            "uncertainty", "profile", "platforms", "compute", "imbalance", "machine", "codesign",
            "envelope", "archsearch", "overlap", "phase", "record", "hostregime", "hierarchy",
-           "tiers", "twohop_measured", "chain_remeasured", "records", "validate_b200", "b200_step")
+           "tiers", "twohop_measured", "chain_remeasured", "records", "validate_b200", "b200_step",
+           "b200_roofline")
 
 _LAZY = {"ClusterSpec": "core", "MoEGeometry": "core", "Level": "core", "one_hop_call": "core",
          "two_hop_call": "core", "step_delta": "core", "HOLDOUTS": "validate",

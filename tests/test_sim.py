@@ -330,3 +330,27 @@ def test_b200_pipeline_forecast_hides_all_but_one_slice_of_communication():
         assert abs(gain - (comm / 2 - b200_step.PIPELINE_GEMM_TAIL * b200_step.gemm_ms(n)["ms"])) < 1e-9
     assert b200_step.predict_pipelined_ms(1, 1, "local")["total_ms"] == \
         b200_step.predict_ms(1, 1, "local")["total_ms"]
+
+
+def test_b200_roofline_ledger_and_fractions():
+    from terracemoe_simulator_b200.sim import b200_roofline as br
+    # the byte ledger of the headline configuration (per GPU and direction)
+    one = br.egress_bytes("one_hop", 4096, 6, 2, 4096, 8, 2)
+    two = br.egress_bytes("two_hop", 4096, 6, 2, 4096, 8, 2)
+    assert one["total"] == pytest.approx(176.2e6, rel=1e-3)
+    assert two["hop_a"] == pytest.approx(50.3e6, rel=1e-3) and two["hop_b"] == pytest.approx(100.7e6, rel=1e-3)
+    assert br.egress_bytes("two_hop", 4096, 6, 2, 4096, 8, 2, dedup=True)["hop_b"] < two["hop_b"]
+    assert br.egress_bytes("two_hop", 4096, 6, 2, 4096, 8, 1)["hop_b"] == 0.0      # groups of one GPU
+    with pytest.raises(ValueError):
+        br.egress_bytes("three_hop", 1, 2, 1, 8, 8, 2)
+    # direction agrees with the closed-form byte criterion at ratio 1: fewer bytes iff q > R
+    for R, q, fewer in ((2, 3, True), (8, 3, False), (4, 6, True)):
+        a = br.egress_bytes("one_hop", 4096, 2 * q, 2, 2048, 128, R)["total"]
+        b = br.egress_bytes("two_hop", 4096, 2 * q, 2, 2048, 128, R)["total"]
+        assert (b < a) is fewer
+    rows = br.table()
+    assert len(rows) == 48
+    big = [t for t in rows if t["tokens"] == 16384]
+    assert all(0.70 <= t["one_hop_frac"] <= 0.85 for t in big)          # of the measured 770 GB/s
+    assert all(t["nccl_frac"] <= t["one_hop_frac"] + 1e-9 for t in big)  # the stores beat NCCL
+    assert all(t["one_hop_frac"] < 1.0 and t["two_hop_frac"] < 1.0 for t in rows)
