@@ -212,3 +212,13 @@ def test_onesided_doc_quotes_the_sweep():
     text = _read("docs/08-onesided.md")
     assert "win by %d-%d %% (median %d %%)" % (round(100 * (lo - 1)), round(100 * (hi - 1)),
                                                round(100 * (med - 1))) in text
+
+
+def test_profile_summary_quotes_the_roofline_module():
+    from terracemoe_simulator_b200.sim import b200_roofline as br
+    big = [t for t in br.table() if t["tokens"] == 16384]
+    text = _read("profiles/fused_dispatch_combine_8gpu.md")
+    want = "reaches %.2f-%.2f of the 770 GB/s roofline and NCCL %.2f-%.2f" % (
+        min(t["one_hop_frac"] for t in big), max(t["one_hop_frac"] for t in big),
+        min(t["nccl_frac"] for t in big), max(t["nccl_frac"] for t in big))
+    assert want in text, want
