@@ -224,6 +224,12 @@ def run_ours(args, rank, world, local):
         dc = runners[path].time_dispatch_combine(x_dev.detach(), args.steps, args.warmup)
         results[path] = {"ms_per_step": ms / args.steps, "launches": launches,
                          "dispatch_combine_us": dc, "status": native.take_status(local)}
+        if world > 1 and dc == dc and dc > 0:      # NVLink roofline of the communication alone
+            from terracemoe_simulator_b200.sim import b200_roofline as br
+            led = br.egress_bytes(path, TOKENS, TOP_K, TOP_GROUPS, D_MODEL, world, RPN[world])
+            results[path]["nvlink_mb_per_direction"] = led["total"] / 1e6
+            results[path]["dispatch_combine_frac_of_measured_link"] = \
+                2.0 * br.roofline_ms(led["total"]) * 1e3 / dc
         clocks = clocks or clk
     best = min(paths, key=lambda p: results[p]["ms_per_step"])
     final = {}
