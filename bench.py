@@ -15,6 +15,13 @@ headline value is the faster of the two and ``config.path`` names it.
 
 Timing: CUDA events on the launching stream, max over ranks, barrier + synchronize on both
 sides; the 2.2 GB of expert weights per step exceed the 126 MB L2, so no L2 flush is needed.
+The block of K steps is repeated ``--repeats`` times (default 5) and the median block is the
+reported one (minimum and maximum beside it); SM clocks are sampled over all timed blocks.
+Before any timing, one step on a 512-token slice checks every path (``parity``): one-hop against
+two-hop bit for bit, and outputs and all gradients against a dense fp32 PyTorch oracle.  A path
+that fails the check is reported and not used for the headline.  With more than one GPU the
+remote-read schedule (``TERRACE_EP_OVERLAP=0``) is timed beside the default overlap schedule as
+the A/B arm (``paths.*_pull``).
 The ``e2e`` entry repeats the measurement through the public API with a pinned-host -> device
 copy of the step's tokens (issued one step ahead on a side stream by the package's
 ``DevicePrefetcher``) and a device -> host read of every step's loss inside the timed region
@@ -114,36 +121,43 @@ def setup_dist(n_gpus: int, force: bool):
     return rank, world, local
 
 
-def timed(fn, steps: int, warmup: int, world: int, sampler: ClockSampler | None, drain=None):
-    """W warm-up steps, then exactly K steps between CUDA events; returns max-over-ranks ms.
-    ``drain`` (optional) runs after the last step and before the closing event: deferred
-    device-to-host reads are completed inside the timed region."""
+def timed(fn, steps: int, warmup: int, world: int, repeats: int = 1, drain=None):
+    """W warm-up steps, then ``repeats`` blocks of exactly K steps, each between CUDA events with
+    a barrier + synchronize on both sides; returns the max-over-ranks ms of every block.
+    ``drain`` (optional) runs after the last step of a block and before its closing event:
+    deferred device-to-host reads are completed inside the timed region."""
     import torch
     import torch.distributed as dist
-    if sampler:
-        sampler.start()          # already polling while the warm-up loads the GPU
     for _ in range(warmup):
         fn()
-    torch.cuda.synchronize()
-    if world > 1:
-        dist.barrier()
-    torch.cuda.synchronize()
-    t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    t0.record()
-    for _ in range(steps):
-        fn()
-    if drain is not None:
-        drain()
-    t1.record()
-    torch.cuda.synchronize()
-    if world > 1:
-        dist.barrier()
-    torch.cuda.synchronize()
-    clocks = sampler.stop() if sampler else None
-    ms = torch.tensor([t0.elapsed_time(t1)], device="cuda")
-    if world > 1:
-        dist.all_reduce(ms, op=dist.ReduceOp.MAX)
-    return ms.item(), clocks
+    blocks = []
+    for _ in range(repeats):
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+        t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        t0.record()
+        for _ in range(steps):
+            fn()
+        if drain is not None:
+            drain()
+        t1.record()
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+        ms = torch.tensor([t0.elapsed_time(t1)], device="cuda")
+        if world > 1:
+            dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+        blocks.append(ms.item())
+    return blocks
+
+
+def block_stats(blocks, steps):
+    per = sorted(b / steps for b in blocks)
+    return {"ms_per_step": statistics.median(per), "ms_min": per[0], "ms_max": per[-1],
+            "blocks": len(per)}
 
 
 def make_problem(rank: int, world: int, device):
@@ -165,11 +179,103 @@ def make_problem(rank: int, world: int, device):
             w2_shard.bfloat16().to(device), x_host, gy)
 
 
+PARITY_TOKENS = 512
+PARITY_TOL = 5e-2        # relative to the largest magnitude of the oracle tensor (bf16 pipeline)
+
+
+def fp32_oracle(rank, world, x, idx, gates, gy, w13, w2):
+    """Dense fp32 PyTorch restatement of the routed experts over all ranks' tokens and all
+    experts; returns this rank's (y, dx, dgates, dw13, dw2)."""
+    import torch
+    import torch.distributed as dist
+    import torch.nn.functional as F
+
+    def gather(t):
+        if world == 1:
+            return t
+        out = [torch.empty_like(t) for _ in range(world)]
+        dist.all_gather(out, t.contiguous())
+        return torch.cat(out)
+    T = x.shape[0]
+    xa = gather(x).float().requires_grad_(True)
+    ga = gather(gates.float()).requires_grad_(True)
+    ia, gya = gather(idx), gather(gy).float()
+    w13a, w2a = gather(w13.detach()), gather(w2.detach())        # bf16, all experts
+    epr = w13.shape[0]
+    y = torch.zeros_like(xa)
+    dw13 = torch.zeros(epr, *w13.shape[1:], device=x.device)
+    dw2 = torch.zeros(epr, *w2.shape[1:], device=x.device)
+    own = []
+    for e in range(w13a.shape[0]):
+        tok, col = (ia == e).nonzero(as_tuple=True)
+        if tok.numel() == 0:
+            continue
+        mine = e // epr == rank
+        a = w13a[e].float().requires_grad_(mine)
+        b = w2a[e].float().requires_grad_(mine)
+        g, u = (xa[tok] @ a).chunk(2, dim=-1)
+        y = y.index_add(0, tok, ga[tok, col].unsqueeze(1) * ((F.silu(g) * u) @ b))
+        if mine:
+            own.append((e - rank * epr, a, b))
+    y.backward(gya)
+    for le, a, b in own:
+        dw13[le], dw2[le] = a.grad, b.grad
+    lo = rank * T
+    return [y.detach()[lo:lo + T], xa.grad[lo:lo + T], ga.grad[lo:lo + T], dw13, dw2]
+
+
+def parity_check(runners, cfg, rank, world, x_dev, gy, router_w, w13, w2):
+    """One forward + backward of every path on a 512-token slice, outside any timed region."""
+    import torch
+    import torch.distributed as dist
+    from terracemoe_simulator_b200.ops import native
+    from terracemoe_simulator_b200.parallel.moe_layer import _route, routed_experts
+    n = PARITY_TOKENS
+    x0, g0 = x_dev.detach()[:n].contiguous(), gy[:n].contiguous()
+    with torch.no_grad():
+        idx, gates0, _, _ = _route(x0, router_w.detach(), next(iter(runners.values())).bias, cfg)
+    got = {}
+    for name, r in runners.items():
+        x = x0.clone().requires_grad_(True)
+        gates = gates0.clone().float().requires_grad_(True)
+        a, b = w13.detach().clone().requires_grad_(True), w2.detach().clone().requires_grad_(True)
+        y = routed_experts(x, idx, gates, a, b, cfg, mode=r.mode, world=world, rpn=r.rpn,
+                           fused=r.fused, ctx=r.ctx)
+        y.backward(g0)
+        got[name] = [t.detach().float() for t in (y, x.grad, gates.grad, a.grad, b.grad)]
+    torch.cuda.synchronize()
+    status = native.take_status(torch.cuda.current_device())
+    oracle = fp32_oracle(rank, world, x0, idx, gates0, g0, w13, w2)
+    report = {"tokens": n, "status": status, "paths": {}}
+    names = list(got)
+    flags = torch.zeros(len(names) + 1, device=x0.device)
+    for i, name in enumerate(names):
+        err = max(((a - b.float()).abs().max() / (b.float().abs().max() + 1e-12)).item()
+                  for a, b in zip(got[name], oracle))
+        flags[i] = err
+    hops = [n_ for n_ in names if n_ in ("one_hop", "two_hop", "one_hop_pull", "two_hop_pull")]
+    same = all(torch.equal(a, b) for n_ in hops[1:] for a, b in zip(got[hops[0]], got[n_]))
+    flags[-1] = 0.0 if same else 1.0
+    if world > 1:
+        dist.all_reduce(flags, op=dist.ReduceOp.MAX)
+    for i, name in enumerate(names):
+        report["paths"][name] = {"max_rel_err_vs_fp32": flags[i].item(),
+                                 "ok": bool(flags[i].item() < PARITY_TOL)}
+    report["max_rel_err_vs_fp32"] = max(flags[:-1]).item()
+    report["one_hop_eq_two_hop"] = bool(flags[-1].item() == 0.0) if len(hops) > 1 else None
+    if world > 1:
+        st = torch.tensor([float(status)], device=x0.device)
+        dist.all_reduce(st, op=dist.ReduceOp.MAX)
+        report["status"] = int(st.item())
+    return report
+
+
 def run_ours(args, rank, world, local):
     import torch
     sys.path.insert(0, ROOT)
     from terracemoe_simulator_b200 import ops
     from terracemoe_simulator_b200.ops import native
+    from terracemoe_simulator_b200.parallel import fused as fz
     from terracemoe_simulator_b200.parallel.moe_layer import MoELayerRunner
     from terracemoe_simulator_b200.routing import TRouteConfig
 
@@ -179,13 +285,19 @@ def run_ours(args, rank, world, local):
     cfg = TRouteConfig(N_EXPERTS, ROUTING_GROUPS[world], TOP_K, TOP_GROUPS)
     params = [t.requires_grad_(True) for t in (router_w, w13, w2)]
     runners = {}
-    paths = ["local"] if world == 1 else ["one_hop", "two_hop"]
-    for path in paths:
-        runners[path] = MoELayerRunner(cfg, D_MODEL, D_EXPERT, TOKENS, world=world, rank=rank,
-                                       rpn=RPN[world], mode=path, fused=not args.nccl_arm,
-                                       device=device)
+    if world == 1:
+        variants = [("local", "local", None)]
+    else:
+        variants = [("one_hop", "one_hop", None), ("two_hop", "two_hop", None)]
+        if not args.nccl_arm and not args.no_ab and fz.flag_bool("TERRACE_EP_OVERLAP", True):
+            variants += [("one_hop_pull", "one_hop", False), ("two_hop_pull", "two_hop", False)]
+    for name, mode, overlap in variants:
+        runners[name] = MoELayerRunner(cfg, D_MODEL, D_EXPERT, TOKENS, world=world, rank=rank,
+                                       rpn=RPN[world], mode=mode, fused=not args.nccl_arm,
+                                       device=device, overlap=overlap)
     x_dev = x_host.to(device).requires_grad_(True)
     gy_flat, inv_n = gy.reshape(-1), 1.0 / gy.numel()
+    parity = parity_check(runners, cfg, rank, world, x_dev, gy, router_w, w13, w2)
     # end-to-end path: every step's tokens come from pinned host memory through the package's
     # input prefetcher (the copy of step i+1 runs on a side stream during step i)
     import itertools
@@ -215,26 +327,34 @@ def run_ours(args, rank, world, local):
         return step
 
     results = {}
-    clocks = None
-    for path in paths:
+    sampler = ClockSampler(local) if rank == 0 else None
+    if sampler:
+        sampler.start()          # polls through the warm-ups and every timed block of every path
+    for path in runners:
         native.LAUNCHES[0] = 0
-        ms, clk = timed(make_step(path, False), args.steps, args.warmup, world,
-                        ClockSampler(local) if rank == 0 else None)
-        launches = native.LAUNCHES[0] // (args.steps + args.warmup)       # per step
+        blocks = timed(make_step(path, False), args.steps, args.warmup, world, args.repeats)
+        launches = native.LAUNCHES[0] // (args.steps * args.repeats + args.warmup)    # per step
+        results[path] = dict(block_stats(blocks, args.steps), launches=launches,
+                             parity_ok=parity["paths"][path]["ok"])
+    clocks = sampler.stop() if sampler else None
+    for path in runners:
+        if path.endswith("_pull"):
+            continue
         dc = runners[path].time_dispatch_combine(x_dev.detach(), args.steps, args.warmup)
-        results[path] = {"ms_per_step": ms / args.steps, "launches": launches,
-                         "dispatch_combine_us": dc, "status": native.take_status(local)}
+        results[path]["dispatch_combine_us"] = dc
         if world > 1 and dc == dc and dc > 0:      # NVLink roofline of the communication alone
             from terracemoe_simulator_b200.sim import b200_roofline as br
             led = br.egress_bytes(path, TOKENS, TOP_K, TOP_GROUPS, D_MODEL, world, RPN[world])
             results[path]["nvlink_mb_per_direction"] = led["total"] / 1e6
             results[path]["dispatch_combine_frac_of_measured_link"] = \
                 2.0 * br.roofline_ms(led["total"]) * 1e3 / dc
-        clocks = clocks or clk
-    best = min(paths, key=lambda p: results[p]["ms_per_step"])
+    status = native.take_status(local)
+    usable = [p for p in runners if results[p]["parity_ok"]] or list(runners)
+    best = min(usable, key=lambda p: results[p]["ms_per_step"])
     final = {}
-    e2e_ms, _ = timed(make_step(best, True), args.steps, args.warmup, world, None,
-                      drain=lambda: final.update(loss=losses.flush()))
+    e2e_blocks = timed(make_step(best, True), args.steps, args.warmup, world, args.repeats,
+                       drain=lambda: final.update(loss=losses.flush()))
+    e2e = block_stats(e2e_blocks, args.steps)
     last_loss = final.get("loss")
     tokens = TOKENS * world
     value = tokens / (results[best]["ms_per_step"] * 1e-3)
@@ -246,25 +366,34 @@ def run_ours(args, rank, world, local):
         pass
     flops = 3 * 2 * 3 * TOKENS * TOP_K * D_MODEL * D_EXPERT          # fwd + 2x bwd, 3 matrices
     peak_tf = peaks.get("bf16_tflops_sustained", 1400.0)
+    ctx0 = runners[best].ctx
+    if world == 1:
+        transport = "local kernels (no communication)"
+    elif args.nccl_arm:
+        transport = "nccl all_to_all"
+    else:
+        transport = "fused peer-memory kernels"
     out = {
         "metric": "moe_layer_tokens_per_s", "value": value, "unit": "tokens/s", "n_gpus": world,
         "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": results[best]["ms_per_step"], "higher_is_better": True,
         "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
         "impl": "ours",
-        "config": {"model": "single MoE layer d4096 E64x1408 top6 M2", "global_batch": tokens,
-                   "seq_len": TOKENS, "parallelism": f"ep{world}", "path": best,
-                   "routing_groups": ROUTING_GROUPS[world], "rpn": RPN[world],
-                   "step": "router+dispatch+experts+combine fwd+bwd",
-                   "l2": "inputs larger than L2 (expert weights 2.2 GB per step)",
-                   "transport": "nccl all_to_all" if args.nccl_arm else "fused peer-memory kernels",
-                   "variants": {"ep_pipeline": int(os.environ.get("TERRACE_EP_PIPELINE", "1") or 1),
-                                "epilogue_push": os.environ.get("TERRACE_EP_EPILOGUE_PUSH", "0") == "1",
-                                "push_back": os.environ.get("TERRACE_EP_PUSH_BACK", "0") == "1"}},
+        "config": bench_config(world),
+        "impl_detail": {"path": best, "transport": transport,
+                        "schedule": ("overlap" if getattr(ctx0, "overlap", False) else
+                                     "remote-read" if ctx0 is not None else "local"),
+                        "chunks": len(getattr(ctx0, "chunks", [])) or None,
+                        "ep_pipeline": int(os.environ.get("TERRACE_EP_PIPELINE", "1") or 1),
+                        "timed_blocks": args.repeats,
+                        "value_is": "median block of K steps"},
         "paths": results,
+        "parity": parity,
+        "status": status,
         "gemm_frac_of_measured_sustained": flops / (results[best]["ms_per_step"] * 1e-3) / (peak_tf * 1e12),
         "clocks": clocks,
-        "e2e": {"value": tokens / (e2e_ms / args.steps * 1e-3), "unit": "tokens/s",
+        "e2e": {"value": tokens / (e2e["ms_per_step"] * 1e-3), "unit": "tokens/s",
+                "ms_per_step": e2e["ms_per_step"], "ms_min": e2e["ms_min"], "ms_max": e2e["ms_max"],
                 "h2d_bytes_per_step": x_host.numel() * 2,
                 "d2h_bytes_per_step": losses.bytes_per_read, "last_loss": last_loss},
         "gpu_launches": results[best]["launches"] * args.steps,
@@ -275,6 +404,15 @@ def run_ours(args, rank, world, local):
         if rank == 0:
             print(trace.format_report(rep), file=sys.stderr)
     return out
+
+
+def bench_config(world: int) -> dict:
+    """The benchmark configuration, identical for both implementations."""
+    return {"model": "single MoE layer d4096 E64x1408 top6 M2", "global_batch": TOKENS * world,
+            "seq_len": TOKENS, "parallelism": f"ep{world}",
+            "routing_groups": ROUTING_GROUPS[world], "rpn": RPN[world],
+            "step": "router+dispatch+experts+combine fwd+bwd",
+            "l2": "inputs larger than L2 (expert weights 2.2 GB per step)"}
 
 
 def run_reference(args, rank, world, local):
@@ -326,14 +464,16 @@ def run_reference(args, rank, world, local):
         return step
 
     results = {}
-    clocks = None
+    sampler = ClockSampler(local) if rank == 0 else None
+    if sampler:
+        sampler.start()
     for path in paths:
-        ms, clk = timed(make_step(path, False), args.steps, args.warmup, world,
-                        ClockSampler(local) if rank == 0 else None)
-        results[path] = {"ms_per_step": ms / args.steps}
-        clocks = clocks or clk
+        blocks = timed(make_step(path, False), args.steps, args.warmup, world, args.repeats)
+        results[path] = block_stats(blocks, args.steps)
+    clocks = sampler.stop() if sampler else None
     best = min(paths, key=lambda p: results[p]["ms_per_step"])
-    e2e_ms, _ = timed(make_step(best, True), args.steps, args.warmup, world, None)
+    e2e = block_stats(timed(make_step(best, True), args.steps, args.warmup, world, args.repeats),
+                      args.steps)
     tokens = TOKENS * world
     return {
         "metric": "moe_layer_tokens_per_s",
@@ -341,14 +481,13 @@ def run_reference(args, rank, world, local):
         "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": results[best]["ms_per_step"], "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "bf16", "data": "synthetic", "impl": "reference",
-        "config": {"model": "single MoE layer d4096 E64x1408 top6 M2", "global_batch": tokens,
-                   "seq_len": TOKENS, "parallelism": f"ep{world}", "path": best,
-                   "routing_groups": ROUTING_GROUPS[world], "rpn": rpn,
-                   "step": "router+dispatch+experts+combine fwd+bwd",
-                   "l2": "inputs larger than L2 (expert weights 2.2 GB per step)",
-                   "transport": "reference torch ops over NCCL all_to_all_single + cuBLAS"},
+        "config": bench_config(world),
+        "impl_detail": {"path": best,
+                        "transport": "reference torch ops over NCCL all_to_all_single + cuBLAS",
+                        "timed_blocks": args.repeats, "value_is": "median block of K steps"},
         "paths": results, "clocks": clocks,
-        "e2e": {"value": tokens / (e2e_ms / args.steps * 1e-3), "unit": "tokens/s",
+        "e2e": {"value": tokens / (e2e["ms_per_step"] * 1e-3), "unit": "tokens/s",
+                "ms_per_step": e2e["ms_per_step"],
                 "h2d_bytes_per_step": x_host.numel() * 2, "d2h_bytes_per_step": 2},
         "gpu_launches": 0,
     }
@@ -360,6 +499,10 @@ def main():
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--repeats", type=int, default=5,
+                    help="timed blocks of K steps each; the median block is reported")
+    ap.add_argument("--no-ab", action="store_true",
+                    help="skip the remote-read schedule that is timed beside the default one")
     ap.add_argument("--nccl-arm", action="store_true",
                     help="ours, but dispatch/combine over NCCL all_to_all instead of fused kernels")
     args = ap.parse_args()

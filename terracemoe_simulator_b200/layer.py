@@ -27,12 +27,21 @@ EXPERT_BACKENDS = ("loop", "grouped", "native")
 
 
 class SwiGLU(nn.Module):
+    """``inter = 0`` is allowed and contributes zero: the module then still owns its two
+    (zero-element) weights, so that a layer without a shared expert carries the same state-dict
+    keys as the reference's (``terrace/layer.py:88`` always builds the shared SwiGLU)."""
+
     def __init__(self, hidden: int, inter: int):
         super().__init__()
-        self.w13 = nn.Linear(hidden, 2 * inter, bias=False)
-        self.w2 = nn.Linear(inter, hidden, bias=False)
+        import warnings
+        with warnings.catch_warnings():
+            warnings.simplefilter("ignore")      # "initializing zero-element tensors is a no-op"
+            self.w13 = nn.Linear(hidden, 2 * inter, bias=False)
+            self.w2 = nn.Linear(inter, hidden, bias=False)
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
+        if self.w2.in_features == 0:
+            return torch.zeros_like(x)
         from . import ops
         if x.is_cuda and ops.custom_ops_enabled() and ops.dense_supported(x, self.w13.weight):
             return ops.swiglu_ffn(x, self.w13.weight, self.w2.weight)
@@ -134,7 +143,7 @@ class TerracedMoE(nn.Module):
         self.expert_backend = "loop"
         self.capacity_factor = capacity_factor
         self.router = Router(hidden, cfg)
-        self.shared = SwiGLU(hidden, n_shared * d_shared) if n_shared * d_shared > 0 else None
+        self.shared = SwiGLU(hidden, n_shared * d_shared)
         e = cfg.n_experts
         self.w13 = nn.Parameter(torch.empty(e, hidden, 2 * d_expert))
         self.w2 = nn.Parameter(torch.empty(e, d_expert, hidden))
@@ -184,7 +193,7 @@ class TerracedMoE(nn.Module):
         expert_idx, gates, group_idx = self.router(x, self.routing_mode)
         gates_used, keep, cap = apply_capacity(expert_idx, gates, self.cfg.n_experts,
                                                self.capacity_factor)
-        base = self.shared(x) if self.shared is not None else torch.zeros_like(x)
+        base = self.shared(x)
         y = self._experts(x, expert_idx, gates_used, base)
         load = expert_load(expert_idx, self.cfg.n_experts)
         if self.training:

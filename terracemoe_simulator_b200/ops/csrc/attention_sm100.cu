@@ -18,6 +18,7 @@
 //
 // The reference computes attention with torch's scaled_dot_product_attention
 // (terrace/model.py:55-71); this file replaces that library call on B200.
+#include "host_util.h"
 #include "launch.h"
 #include "ptx_sm100.cuh"
 
@@ -847,10 +848,10 @@ template <int D>
 static int at_fwd(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv,
                   const AttnParams& p, cudaStream_t stream) {
   constexpr size_t smem = 5 * AT_ROWS * D * 2 + 2 * AT_BOX + sizeof(AttnCtl) + 1024;
-  static bool done = false;
-  if (!done) {
+  static OncePerDevice done;
+  if (done.need()) {
     if (at_configure(attn_fwd_kernel<D>, smem) != TB200_OK) return TB200_ERR_LAUNCH;
-    done = true;
+    done.done();
   }
   attn_fwd_kernel<D><<<p.BH * (p.S / AT_ROWS), AT_THREADS, smem, stream>>>(tq, tk, tv, p);
   return cudaGetLastError() == cudaSuccess ? TB200_OK : TB200_ERR_LAUNCH;
@@ -861,11 +862,11 @@ static int at_bwd(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMa
                   const CUtensorMap& tdo, const AttnParams& p, cudaStream_t stream) {
   constexpr size_t smem_kv = 4 * AT_ROWS * D * 2 + 4 * AT_BOX + sizeof(AttnCtl) + 1024;
   constexpr size_t smem_q = 4 * AT_ROWS * D * 2 + 2 * AT_BOX + sizeof(AttnCtl) + 1024;
-  static bool done = false;
-  if (!done) {
+  static OncePerDevice done;
+  if (done.need()) {
     if (at_configure(attn_bwd_dkdv_kernel<D>, smem_kv) != TB200_OK) return TB200_ERR_LAUNCH;
     if (at_configure(attn_bwd_dq_kernel<D>, smem_q) != TB200_OK) return TB200_ERR_LAUNCH;
-    done = true;
+    done.done();
   }
   const int grid = p.BH * (p.S / AT_ROWS);
   attn_bwd_dkdv_kernel<D><<<grid, AT_THREADS, smem_kv, stream>>>(tq, tk, tv, tdo, p);

@@ -432,6 +432,34 @@ Tensor grouped_wgrad(const Tensor& X, const Tensor& dY, const Tensor& seg_start,
   return dW;
 }
 
+// Weight gradient of the groups [g0, g0 + G) written into dW[g0 : g0 + G] of a gradient tensor
+// that covers all groups (G = seg_start.numel()): one launch per chunk of experts.
+void grouped_wgrad_out(const Tensor& X, const Tensor& dY, Tensor dW, int64_t g0,
+                       const Tensor& seg_start, const Tensor& seg_count, int64_t max_ctas,
+                       int64_t pad_align) {
+  CHECK_CUDA_CONTIG(X);
+  CHECK_CUDA_CONTIG(dY);
+  CHECK_CUDA_CONTIG(dW);
+  TORCH_CHECK(X.scalar_type() == at::kBFloat16 && dY.scalar_type() == at::kBFloat16 &&
+                  dW.scalar_type() == at::kBFloat16,
+              "grouped_wgrad_out: bf16 operands");
+  TORCH_CHECK(X.dim() == 2 && dY.dim() == 2 && X.size(0) == dY.size(0) && dW.dim() == 3 &&
+                  dW.size(1) == X.size(1) && dW.size(2) == dY.size(1),
+              "grouped_wgrad_out: X [rows, M], dY [rows, N], dW [groups, M, N]");
+  const int64_t G = seg_start.numel();
+  TORCH_CHECK(seg_start.scalar_type() == at::kInt && seg_count.scalar_type() == at::kInt &&
+                  seg_count.numel() == G && seg_start.is_cuda() && seg_count.is_cuda() &&
+                  seg_start.is_contiguous() && seg_count.is_contiguous(),
+              "grouped_wgrad_out: int32 CUDA segment tables");
+  TORCH_CHECK(g0 >= 0 && G >= 1 && g0 + G <= dW.size(0), "grouped_wgrad_out: group range");
+  c10::cuda::CUDAGuard guard(X.device());
+  auto* out = static_cast<char*>(dW.data_ptr()) + g0 * dW.size(1) * dW.size(2) * 2;
+  check_rc(tb200_grouped_wgrad(X.data_ptr(), dY.data_ptr(), out, seg_start.data_ptr<int>(),
+                               seg_count.data_ptr<int>(), G, X.size(0), X.size(1), dY.size(1),
+                               status_ptr(X), max_ctas, static_cast<int>(pad_align), cur_stream()),
+           "grouped_wgrad_out");
+}
+
 }  // namespace
 
 // ---------------------------------------------------------------------------------------------
@@ -516,6 +544,8 @@ TORCH_LIBRARY(terrace, m) {
         &grouped_gemm);
   m.def("grouped_wgrad(Tensor X, Tensor dY, Tensor seg_start, Tensor seg_count, int max_ctas, "
         "int pad_align=0) -> Tensor", &grouped_wgrad);
+  m.def("grouped_wgrad_out(Tensor X, Tensor dY, Tensor(a!) dW, int g0, Tensor seg_start, "
+        "Tensor seg_count, int max_ctas, int pad_align=0) -> ()", &grouped_wgrad_out);
   m.def("zero_pad_rows(Tensor(a!) buf, Tensor seg_start, Tensor seg_count, int align) -> ()",
         &zero_pad_rows);
   m.def("attn_fwd(Tensor q, Tensor k, Tensor v, bool causal, float scale) -> (Tensor, Tensor)",

@@ -24,6 +24,7 @@
 //
 // Computes what the reference does with a Python loop of per-expert matmuls
 // (terrace/layer.py:30-68 `_grouped_mm_fwd` / `_GroupedMM`).
+#include "host_util.h"
 #include "launch.h"
 #include "ptx_sm100.cuh"
 
@@ -31,6 +32,9 @@
 #include <cuda_runtime.h>
 #include <stdio.h>
 #include <stdlib.h>
+#include <string.h>
+
+#include <mutex>
 
 namespace tb200 {
 
@@ -97,7 +101,6 @@ struct SharedCtl {
   PipeBarriers bars;
   uint32_t tmem_base;
   volatile int abort_flag;
-  volatile int epi_abort;   // swapped SwiGLU epilogue: verdict shared by the four epilogue warps
   int total_tiles;
   int tile_start[MAX_GROUPS + 1];
 };
@@ -644,328 +647,6 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
   }
 }
 
-// =============================================================================================
-// Swapped-operand variant for short groups.
-//
-// With ~400 rows per expert the 128-row tiles above waste one tile in seven (a 64-row remainder
-// still pays for 128 rows of MMA).  Here the OUTPUT FEATURES take the 128 accumulator rows (M) and
-// the group's rows take the MMA's N, which may be any multiple of 16 up to 256: D^T[feature, row]
-// = W^T[feature, k] X^T[k, row].  A 384-row group is one 256-wide and one 128-wide tile, nothing
-// is wasted.  The weights are the A operand (fwd: M-major, as stored [K, N]; dgrad: K-major, as
-// stored [N, K]), the activation rows the K-major B operand.  The accumulator comes out
-// transposed (lane = feature, column = row), so the epilogue turns 32 x 32 blocks through shared
-// memory before writing rows.  SwiGLU: a tile holds 64 gate and the matching 64 up features;
-// the four epilogue warps meet in a shared staging tile where gate meets up.
-// Requires groups padded to 64 rows with zeroed padding (the padding rows then compute to zero).
-//
-// Measured result: correct, and SLOWER (64 experts x 384 rows: 918 against 1127 TFLOPS; the
-// single-layer step 3.50 against 3.38 ms).  The loop is bound by bytes staged per flop, not by
-// MMA slots, and a 128-feature x 128-row tile stages 32 KiB per K slice for half the flops of a
-// 48 KiB 128 x 256 tile.  It stays as an option (TERRACE_GEMM_SWAP=1) and off by default.
-// =============================================================================================
-constexpr int SW_ROWS = 256;                 // rows (MMA N) per tile at most
-constexpr int SW_B_BYTES = SW_ROWS * BK * 2; // 32 KiB
-constexpr int SW_STAGE_BYTES = A_BYTES + SW_B_BYTES;
-constexpr int SW_STAGES = 4;
-
-__device__ __forceinline__ void epi_sync() {   // the four epilogue warps only
-  asm volatile("bar.sync 2, 128;" ::: "memory");
-}
-
-template <int MODE, int EPI>
-__global__ void __launch_bounds__(GEMM_THREADS, 1)
-gemm_swap_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ CUtensorMap tmap_x,
-                 const GemmParams p) {
-  extern __shared__ __align__(1024) uint8_t smem_raw[];
-  uint8_t* stage_base = reinterpret_cast<uint8_t*>(
-      (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
-  uint8_t* out_stage = stage_base + SW_STAGES * SW_STAGE_BYTES;
-  SharedCtl* ctl = reinterpret_cast<SharedCtl*>(out_stage + OUT_STAGE_BYTES);
-
-  const int warp = threadIdx.x >> 5;
-  const int lane = threadIdx.x & 31;
-  constexpr int FEAT = EPI == EPI_SWIGLU ? 64 : 128;     // output features per tile
-  const int n_ft = (p.N + FEAT - 1) / FEAT;
-  const int kblocks = (p.K + BK - 1) / BK;
-
-  if (warp == 0) {
-    int carry = 0;
-    for (int base = 0; base < p.n_groups; base += 32) {
-      const int e = base + lane;
-      int tiles = 0;
-      if (e < p.n_groups) {
-        const int padded = (p.seg_count[e] + p.pad_align - 1) / p.pad_align * p.pad_align;
-        tiles = ((padded + SW_ROWS - 1) / SW_ROWS) * n_ft;
-      }
-      int incl = tiles;
-#pragma unroll
-      for (int d = 1; d < 32; d <<= 1) {
-        const int v = __shfl_up_sync(0xffffffffu, incl, d);
-        if (lane >= d) incl += v;
-      }
-      if (e < p.n_groups) ctl->tile_start[e] = carry + incl - tiles;
-      carry += __shfl_sync(0xffffffffu, incl, 31);
-    }
-    if (lane == 0) {
-      ctl->tile_start[p.n_groups] = carry;
-      ctl->total_tiles = carry;
-      ctl->abort_flag = 0;
-      ctl->epi_abort = 0;
-      for (int s = 0; s < SW_STAGES; ++s) {
-        mbar_init(&ctl->bars.full[s], 1);
-        mbar_init(&ctl->bars.empty[s], 1);
-      }
-      for (int a = 0; a < 2; ++a) {
-        mbar_init(&ctl->bars.acc_full[a], 1);
-        mbar_init(&ctl->bars.acc_empty[a], 4);
-      }
-      fence_barrier_init();
-    }
-  }
-  if (warp == 1) {
-    tmem_alloc(&ctl->tmem_base, TMEM_COLS);
-    tmem_relinquish();
-  }
-  if (warp == 0 && lane == 0) {
-    prefetch_tmap(&tmap_w);
-    prefetch_tmap(&tmap_x);
-  }
-  tc_fence_before();
-  __syncthreads();
-  tc_fence_after();
-  const uint32_t tmem_base = ctl->tmem_base;
-  const int total_tiles = ctl->total_tiles;
-
-  // tile t of group e: feature tile ft = local / n_rt ... row tile rt fastest, so that the two or
-  // three row tiles of one weight tile run on neighbouring CTAs at the same time
-  auto decode = [&](int t, int& e, int& ft, int& rt, int& rows_here, int& seg0, int& cnt) {
-    locate_tile(ctl, p.n_groups, t, e);
-    cnt = p.seg_count[e];
-    seg0 = p.seg_start[e];
-    const int padded = (cnt + p.pad_align - 1) / p.pad_align * p.pad_align;
-    const int n_rt = (padded + SW_ROWS - 1) / SW_ROWS;
-    const int local = t - ctl->tile_start[e];
-    ft = local / n_rt;
-    rt = local - ft * n_rt;
-    rows_here = min(SW_ROWS, padded - rt * SW_ROWS);
-  };
-
-  if (warp == 0) {
-    if (lane == 0) {
-      int e = 0;
-      uint32_t it = 0;
-      bool ok = true;
-      if (p.wait_flags != nullptr) {
-        for (int i = 0; i < p.wait_n && ok; ++i) {
-          if (!wait_flag_ge(p.wait_flags + i, p.wait_epoch)) {
-            raise_abort(ctl, p.status, ST_TIMEOUT_FLAG);
-            ok = false;
-          }
-        }
-        fence_proxy_async_all();
-      }
-      for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
-        int ft, rt, rows_here, seg0, cnt;
-        decode(t, e, ft, rt, rows_here, seg0, cnt);
-        for (int kb = 0; kb < kblocks; ++kb, ++it) {
-          const int s = it % SW_STAGES;
-          const uint32_t round = it / SW_STAGES;
-          if (round > 0 && !mbar_wait(&ctl->bars.empty[s], (round - 1) & 1, &ctl->abort_flag)) {
-            raise_abort(ctl, p.status, ST_TIMEOUT_EMPTY);
-            ok = false;
-            break;
-          }
-          uint8_t* sa = stage_base + s * SW_STAGE_BYTES;
-          uint8_t* sb = sa + A_BYTES;
-          uint64_t* bar = &ctl->bars.full[s];
-          const int x_boxes = (rows_here + 127) / 128;          // 128-row boxes of activations
-          mbar_expect_tx(bar, A_BYTES + x_boxes * 128 * BK * 2);
-          if (MODE == MODE_FWD) {
-            // weights stored [K, N(+up half)]: two boxes of 64 features x 64 K
-            if (EPI == EPI_SWIGLU) {
-              tma_load_3d(sa, &tmap_w, bar, ft * 64, kb * BK, e);
-              tma_load_3d(sa + BOX_BYTES, &tmap_w, bar, p.up_offset + ft * 64, kb * BK, e);
-            } else {
-              tma_load_3d(sa, &tmap_w, bar, ft * 128, kb * BK, e);
-              tma_load_3d(sa + BOX_BYTES, &tmap_w, bar, ft * 128 + 64, kb * BK, e);
-            }
-          } else {
-            // weights stored [N(+up half), K]: two boxes of 64 K x 64 features
-            if (EPI == EPI_SWIGLU) {
-              tma_load_3d(sa, &tmap_w, bar, kb * BK, ft * 64, e);
-              tma_load_3d(sa + BOX_BYTES, &tmap_w, bar, kb * BK, p.up_offset + ft * 64, e);
-            } else {
-              tma_load_3d(sa, &tmap_w, bar, kb * BK, ft * 128, e);
-              tma_load_3d(sa + BOX_BYTES, &tmap_w, bar, kb * BK, ft * 128 + 64, e);
-            }
-          }
-          for (int j = 0; j < x_boxes; ++j)
-            tma_load_2d(sb + j * (128 * BK * 2), &tmap_x, bar, kb * BK,
-                        seg0 + rt * SW_ROWS + j * 128);
-        }
-      }
-    }
-  } else if (warp == 1) {
-    constexpr int A_KSTEP = MODE == MODE_FWD ? 2048 : 32;
-    const uint64_t a_desc0 = MODE == MODE_FWD
-                                 ? make_smem_desc(smem_u32(stage_base), BOX_BYTES, 1024)
-                                 : make_smem_desc(smem_u32(stage_base), 16, 1024);
-    const uint64_t b_desc0 = make_smem_desc(smem_u32(stage_base) + A_BYTES, 16, 1024);
-    int e = 0;
-    uint32_t it = 0, tile_iter = 0;
-    bool ok = true;
-    for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x, ++tile_iter) {
-      int ft, rt, rows_here, seg0, cnt;
-      decode(t, e, ft, rt, rows_here, seg0, cnt);
-      const uint32_t idesc = make_idesc_bf16(128, rows_here, MODE == MODE_FWD, false);
-      const int a = tile_iter & 1;
-      const uint32_t around = tile_iter >> 1;
-      if (around > 0 && !warp_wait<1>(&ctl->bars.acc_empty[a], (around - 1) & 1, &ctl->abort_flag)) {
-        if (lane == 0) raise_abort(ctl, p.status, ST_TIMEOUT_ACC);
-        ok = false;
-        break;
-      }
-      tc_fence_after();
-      const uint32_t d_tmem = tmem_base + a * SW_ROWS;
-      for (int kb = 0; kb < kblocks; ++kb, ++it) {
-        const int s = it % SW_STAGES;
-        const uint32_t round = it / SW_STAGES;
-        if (!warp_wait<1>(&ctl->bars.full[s], round & 1, &ctl->abort_flag)) {
-          if (lane == 0) raise_abort(ctl, p.status, ST_TIMEOUT_FULL);
-          ok = false;
-          break;
-        }
-        tc_fence_after();
-        if (lane == 0) {
-          const uint64_t stage_off = static_cast<uint64_t>((s * SW_STAGE_BYTES) >> 4);
-#pragma unroll
-          for (int k4 = 0; k4 < BK / 16; ++k4) {
-            const uint64_t da = a_desc0 + stage_off + ((k4 * A_KSTEP) >> 4);
-            const uint64_t db = b_desc0 + stage_off + ((k4 * 32) >> 4);
-            umma_bf16(d_tmem, da, db, idesc, (kb | k4) != 0 ? 1u : 0u);
-          }
-          umma_commit(&ctl->bars.empty[s]);
-        }
-        __syncwarp();
-      }
-      if (ok && lane == 0) umma_commit(&ctl->bars.acc_full[a]);
-      __syncwarp();
-    }
-  } else {
-    const int quad = warp & 3;
-    const int et = (quad * 32) + lane;             // index among the 128 epilogue threads
-    int e = 0;
-    uint32_t tile_iter = 0, chunk_iter = 0;
-    bool ok = true;
-    for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x, ++tile_iter) {
-      int ft, rt, rows_here, seg0, cnt;
-      decode(t, e, ft, rt, rows_here, seg0, cnt);
-      const int a = tile_iter & 1;
-      const uint32_t around = tile_iter >> 1;
-      const bool got = warp_wait<1>(&ctl->bars.acc_full[a], around & 1, &ctl->abort_flag);
-      if (!got && lane == 0) {
-        ctl->epi_abort = 1;
-        raise_abort(ctl, p.status, ST_TIMEOUT_ACC);
-      }
-      if (EPI == EPI_SWIGLU) {
-        // the four warps meet below once per 32 rows, so they must agree on giving up: every
-        // warp passes this barrier, then all read the same verdict
-        epi_sync();
-        if (ctl->epi_abort != 0) {
-          ok = false;
-          break;
-        }
-      } else if (!got) {
-        ok = false;
-        break;
-      }
-      tc_fence_after();
-      const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + a * SW_ROWS;
-      const int row0 = seg0 + rt * SW_ROWS;          // first row of C covered by this tile
-      const int real_rows = cnt - rt * SW_ROWS;      // rows below this bound carry data
-      for (int c = 0; c < rows_here / 32; ++c, ++chunk_iter) {
-        uint32_t v[32];
-        tmem_ld_32x32(taddr + c * 32, v);
-        tmem_ld_wait();
-        if (EPI == EPI_SWIGLU) {
-          // staging tile [32 rows][64 gate | 64 up] bf16, two buffers alternate per chunk
-          uint8_t* T = out_stage + (chunk_iter & 1) * 8192;
-          const int col = quad * 32 + lane;          // 0..63 gate, 64..127 up
-#pragma unroll
-          for (int r = 0; r < 32; ++r)
-            *reinterpret_cast<__nv_bfloat16*>(T + r * 256 + col * 2) =
-                __float2bfloat16_rn(__uint_as_float(v[r]));
-          epi_sync();
-          const int r = et >> 2, seg = et & 3;       // 16 features of one row per thread
-          const int f0 = ft * 64 + seg * 16;
-          const int grow = c * 32 + r;
-          if (f0 < p.N) {
-            const uint4* gp = reinterpret_cast<const uint4*>(T + r * 256 + seg * 32);
-            const uint4* up = reinterpret_cast<const uint4*>(T + r * 256 + 128 + seg * 32);
-            const bool real = grow < real_rows;
-            __nv_bfloat16* crow = p.C + static_cast<size_t>(row0 + grow) * p.ldc + f0;
-            __nv_bfloat16* c2row = p.C2 ? p.C2 + static_cast<size_t>(row0 + grow) * p.ldc2 + f0
-                                        : nullptr;
-#pragma unroll
-            for (int h = 0; h < 2; ++h) {
-              if (f0 + h * 8 < p.N) {
-                uint4 g4 = gp[h], u4 = up[h], o4;
-                const __nv_bfloat162* gb = reinterpret_cast<const __nv_bfloat162*>(&g4);
-                const __nv_bfloat162* ub = reinterpret_cast<const __nv_bfloat162*>(&u4);
-                uint32_t* po = reinterpret_cast<uint32_t*>(&o4);
-#pragma unroll
-                for (int i = 0; i < 4; ++i) {
-                  const float2 gf = __bfloat1622float2(gb[i]);
-                  const float2 uf = __bfloat1622float2(ub[i]);
-                  po[i] = pack_bf16(silu_f(gf.x) * uf.x, silu_f(gf.y) * uf.y);
-                }
-                if (!real) g4 = u4 = o4 = make_uint4(0, 0, 0, 0);
-                *reinterpret_cast<uint4*>(crow + h * 8) = o4;
-                if (c2row) {
-                  *reinterpret_cast<uint4*>(c2row + h * 8) = g4;
-                  *reinterpret_cast<uint4*>(c2row + p.up_offset + h * 8) = u4;
-                }
-              }
-            }
-          }
-        } else {
-          // per-warp staging [32 rows][32 features] bf16 (64 bytes per row)
-          uint8_t* T = out_stage + quad * 4096 + (chunk_iter & 1) * 2048;
-#pragma unroll
-          for (int r = 0; r < 32; ++r)
-            *reinterpret_cast<__nv_bfloat16*>(T + r * 64 + lane * 2) =
-                __float2bfloat16_rn(__uint_as_float(v[r]));
-          __syncwarp();
-          const int f0 = ft * 128 + quad * 32 + (lane & 3) * 8;
-#pragma unroll
-          for (int i = 0; i < 4; ++i) {
-            const int r = i * 8 + (lane >> 2);
-            const int grow = c * 32 + r;
-            uint4 o4 = *reinterpret_cast<const uint4*>(T + r * 64 + (lane & 3) * 16);
-            if (grow >= real_rows) o4 = make_uint4(0, 0, 0, 0);
-            if (f0 < p.N)
-              *reinterpret_cast<uint4*>(p.C + static_cast<size_t>(row0 + grow) * p.ldc + f0) = o4;
-          }
-        }
-      }
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&ctl->bars.acc_empty[a]);
-    }
-  }
-
-  if (ctl->abort_flag != 0) {
-    const unsigned long long t0 = globaltimer_ns();
-    while (globaltimer_ns() - t0 < 1000000ull) __nanosleep(256);
-  }
-  tc_fence_before();
-  __syncthreads();
-  if (warp == 1) {
-    tc_fence_after();
-    tmem_dealloc(tmem_base, TMEM_COLS);
-  }
-}
-
 // ---------------------------------------------------------------------------------------------
 // host side
 // ---------------------------------------------------------------------------------------------
@@ -990,8 +671,8 @@ static EncodeTiledFn encode_fn() {
 
 // bf16 tensor map with 128-byte swizzle; dims/strides innermost first, strides in bytes for
 // dims 1.. (rank - 1).
-static int make_tmap(CUtensorMap* out, const void* base, int rank, const uint64_t* dims,
-                     const uint64_t* strides_bytes, const uint32_t* box) {
+static int encode_tmap(CUtensorMap* out, const void* base, int rank, const uint64_t* dims,
+                       const uint64_t* strides_bytes, const uint32_t* box) {
   EncodeTiledFn fn = encode_fn();
   if (fn == nullptr) return TB200_ERR_DRIVER;
   // the encode is a driver call and needs a current context; a thread that has only switched
@@ -1026,13 +707,53 @@ static int make_tmap(CUtensorMap* out, const void* base, int rank, const uint64_
   return TB200_OK;
 }
 
-static int sm_count_cached() {
-  static int sms[64] = {0};
-  int dev = 0;
-  cudaGetDevice(&dev);
-  if (dev < 0 || dev >= 64) return 148;
-  if (sms[dev] == 0) cudaDeviceGetAttribute(&sms[dev], cudaDevAttrMultiProcessorCount, dev);
-  return sms[dev] > 0 ? sms[dev] : 148;
+// The descriptor depends only on (base, dims, strides, box), and a training loop presents the
+// same few operands every step (weights, arena sections, cached activations), so encoded maps are
+// kept in a small table and the driver call leaves the launch path after the first step.
+struct TmapKey {
+  const void* base;
+  int rank;
+  uint64_t dims[3];
+  uint64_t strides[2];
+  uint32_t box[3];
+  bool operator==(const TmapKey& o) const { return memcmp(this, &o, sizeof(TmapKey)) == 0; }
+};
+struct TmapSlot {
+  TmapKey key;
+  CUtensorMap map;
+  bool used;
+};
+constexpr int TMAP_SLOTS = 512;          // direct-mapped; a collision just re-encodes
+
+static int make_tmap(CUtensorMap* out, const void* base, int rank, const uint64_t* dims,
+                     const uint64_t* strides_bytes, const uint32_t* box) {
+  static TmapSlot table[TMAP_SLOTS];
+  static std::mutex mu;
+  TmapKey key;
+  memset(&key, 0, sizeof(key));
+  key.base = base;
+  key.rank = rank;
+  for (int i = 0; i < rank; ++i) {
+    key.dims[i] = dims[i];
+    key.box[i] = box[i];
+  }
+  for (int i = 0; i + 1 < rank; ++i) key.strides[i] = strides_bytes[i];
+  uint64_t h = 1469598103934665603ull;
+  const unsigned char* kb = reinterpret_cast<const unsigned char*>(&key);
+  for (size_t i = 0; i < sizeof(key); ++i) h = (h ^ kb[i]) * 1099511628211ull;
+  TmapSlot& slot = table[h % TMAP_SLOTS];
+  std::lock_guard<std::mutex> lock(mu);
+  if (slot.used && slot.key == key) {
+    *out = slot.map;
+    return TB200_OK;
+  }
+  const int rc = encode_tmap(out, base, rank, dims, strides_bytes, box);
+  if (rc == TB200_OK) {
+    slot.key = key;
+    slot.map = *out;
+    slot.used = true;
+  }
+  return rc;
 }
 
 template <int CTAS>
@@ -1052,46 +773,20 @@ static int pair_policy() {
   return policy;
 }
 
-static int swap_policy() {
-  static int policy = -2;      // TERRACE_GEMM_SWAP = 1: whenever allowed; default: never
-  if (policy == -2) {
-    const char* v = getenv("TERRACE_GEMM_SWAP");
-    policy = (v != nullptr && v[0] == '1') ? 1 : 0;
-  }
-  return policy;
-}
-
-template <int MODE, int EPI>
-static int launch_swap(const CUtensorMap& tw, const CUtensorMap& tx, const GemmParams& p,
-                       int max_ctas, cudaStream_t stream) {
-  static bool configured = false;
-  auto kern = gemm_swap_kernel<MODE, EPI>;
-  constexpr size_t smem = SW_STAGES * SW_STAGE_BYTES + OUT_STAGE_BYTES + sizeof(SharedCtl) + 1024;
-  if (!configured) {
-    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                             static_cast<int>(smem)) != cudaSuccess)
-      return TB200_ERR_LAUNCH;
-    configured = true;
-  }
-  int grid = sm_count_cached();
-  if (max_ctas > 0 && max_ctas < grid) grid = max_ctas;
-  kern<<<grid, GEMM_THREADS, smem, stream>>>(tw, tx, p);
-  return cudaGetLastError() == cudaSuccess ? TB200_OK : TB200_ERR_LAUNCH;
-}
-
 template <int MODE, int EPI, int CTAS>
 static int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p,
                        int max_ctas, cudaStream_t stream) {
-  static bool configured = false;
+  // the shared-memory opt-in is an attribute of the function ON ONE DEVICE
+  static OncePerDevice configured;
   auto kern = gemm_kernel<MODE, EPI, CTAS>;
   constexpr size_t smem = gemm_smem<CTAS>();
-  if (!configured) {
+  if (configured.need()) {
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
                              static_cast<int>(smem)) != cudaSuccess)
       return TB200_ERR_LAUNCH;
-    configured = true;
+    configured.done();
   }
-  int grid = sm_count_cached();
+  int grid = sm_count();
   if (max_ctas > 0 && max_ctas < grid) grid = max_ctas;
   grid -= grid % CTAS;
   if (grid < CTAS) grid = CTAS;
@@ -1140,10 +835,6 @@ static int grouped_gemm_impl(const void* A, const void* B, void* C, void* C2,
   // CTA of the last pair of a group often has no rows
   const int policy = pair_policy();
   const bool pair = policy == 1 || (policy == -1 && a_rows / n_groups >= 1024);
-  // short groups padded to 64 rows: features on the accumulator rows, rows on the MMA's N
-  const int spol = swap_policy();
-  const bool swap = !scatter && !pair && pad_align > 0 && pad_align % 64 == 0 &&
-                    a_rows < (1ll << 31) && spol == 1;
   CUtensorMap ta, tb;
   {
     uint64_t dims[2] = {static_cast<uint64_t>(K), static_cast<uint64_t>(a_rows)};
@@ -1160,7 +851,7 @@ static int grouped_gemm_impl(const void* A, const void* B, void* C, void* C2,
     uint64_t str[2] = {static_cast<uint64_t>(b_cols) * 2,
                        static_cast<uint64_t>(b_cols) * static_cast<uint64_t>(b_rows) * 2};
     uint32_t box[3] = {64, static_cast<uint32_t>(mode == MODE_DGRAD
-                                                     ? (swap ? 64 : (epilogue == EPI_SWIGLU || pair) ? 128 : BN)
+                                                     ? ((epilogue == EPI_SWIGLU || pair) ? 128 : BN)
                                                      : BK), 1};
     int rc = make_tmap(&tb, B, 3, dims, str, box);
     if (rc != TB200_OK) return rc;
@@ -1195,14 +886,6 @@ static int grouped_gemm_impl(const void* A, const void* B, void* C, void* C2,
     if (mode == MODE_DGRAD)
       return launch_gemm<MODE_DGRAD, EPI_SCATTER, 1>(ta, tb, p, max_ctas, stream);
     return launch_gemm<MODE_FWD, EPI_SCATTER, 1>(ta, tb, p, max_ctas, stream);
-  }
-  if (swap) {
-    if (mode == MODE_DGRAD && epilogue == EPI_SWIGLU)
-      return launch_swap<MODE_DGRAD, EPI_SWIGLU>(tb, ta, p, max_ctas, stream);
-    if (mode == MODE_DGRAD) return launch_swap<MODE_DGRAD, EPI_PLAIN>(tb, ta, p, max_ctas, stream);
-    if (epilogue == EPI_SWIGLU)
-      return launch_swap<MODE_FWD, EPI_SWIGLU>(tb, ta, p, max_ctas, stream);
-    return launch_swap<MODE_FWD, EPI_PLAIN>(tb, ta, p, max_ctas, stream);
   }
   if (pair) {
     if (mode == MODE_DGRAD && epilogue == EPI_SWIGLU)

@@ -40,6 +40,7 @@ int tb200_grouped_gemm_scatter(const void* A, const void* B, const int* seg_star
                                const unsigned long long* scatter_base, int scatter_slots,
                                int scatter_world, int* status, int max_ctas, cudaStream_t stream);
 // dW[g][M, N] = X[rows of g, M]^T * dY[rows of g, N]; groups with no rows get zeros.
+// (dW may be a slice of a larger gradient tensor: a chunk of the groups at a time)
 int tb200_grouped_wgrad(const void* X, const void* dY, void* dW, const int* seg_start,
                         const int* seg_count, int n_groups, long long rows, int M, int N,
                         int* status, int max_ctas, int pad_align, cudaStream_t stream);
@@ -124,13 +125,16 @@ struct Tb200Arena;
 int tb200_ep_plan(const struct Tb200Arena* a, int* chunk_hist, int* chunka_hist, int* my_base,
                   int* seg_start, int* seg_count, int* rows_a, int epoch, int seg_align,
                   int* status, cudaStream_t stream);
+// The push kernels cover the picks of LOCAL experts [le_lo, le_hi) (0 .. epr = all) and raise the
+// owners' arrival flags to `flag_value` when their rows have landed; a step that sends in several
+// launches passes growing values, and each owner GEMM waits for the value of its expert range.
 int tb200_ep_push(const struct Tb200Arena* a, const void* x, const int* es, const int* rank_local,
                   const int* chunk_base, const int* my_base, int* pos_out, const float* gs,
-                  float* dgs, long long off_dst, long long off_dot, int T, int flag_kind, int epoch,
-                  int* done_counter, int* status, long long off_rowmap, int ret_slots,
-                  int dot_local, cudaStream_t stream);
+                  float* dgs, long long off_dst, long long off_dot, int T, int flag_kind,
+                  int flag_value, int le_lo, int le_hi, int* done_counter, int* status,
+                  long long off_rowmap, int ret_slots, int dot_local, cudaStream_t stream);
 int tb200_signal(const struct Tb200Arena* a, int kind, int first, int n, int stride, int idx,
-                 int epoch, int wait_kind, int wait_first, int wait_n, int* status,
+                 int epoch, int wait_kind, int wait_first, int wait_n, int wait_value, int* status,
                  cudaStream_t stream);
 int tb200_ep_pull_combine(const struct Tb200Arena* a, const int* pos, const int* es,
                           const float* gs, void* y, long long off_src, int T, int group_size,
@@ -145,11 +149,13 @@ int tb200_hopa_push(const struct Tb200Arena* a, const void* x, const int* es, co
                     int* done_counter, int* status, cudaStream_t stream);
 int tb200_arrival_push(const struct Tb200Arena* a, const int* rows_a, long long off_rows,
                        long long off_dst, long long off_dot, int scale_gate, int want_dgate,
-                       int wait_kind, int data_kind, int dg_kind, int epoch, int* done_counter,
-                       int* status, cudaStream_t stream);
+                       int wait_kind, int data_kind, int dg_kind, int epoch, int flag_value,
+                       int le_lo, int le_hi, int* done_counter, int* status, long long off_rowmap,
+                       int dot_local, cudaStream_t stream);
 int tb200_arrival_combine(const struct Tb200Arena* a, const int* rows_a, long long off_src,
                           long long off_red, int use_gate, int wait_kind, int red_kind, int epoch,
-                          int* done_counter, int* status, int push_back, cudaStream_t stream);
+                          int* done_counter, int* status, int push_back, int local_slots,
+                          cudaStream_t stream);
 int tb200_origin_combine(const struct Tb200Arena* a, const int* es, const int* rowa, void* y,
                          long long off_red, int T, int wait_kind, int epoch, int* status,
                          int local_rows, cudaStream_t stream);

@@ -9,6 +9,7 @@
 // Reference behaviour: terrace/model.py:46-47 (rmsnorm), terrace/routing.py:45-96 (t_route
 // mode "full"), terrace/layer.py:101-112 (permute / un-permute around the grouped matmul),
 // terrace/ops/__init__.py:255-300 (K1), terrace/ops/k2_ref.py:70-134 (K2).
+#include "host_util.h"
 #include "launch.h"
 #include "ptx_sm100.cuh"
 #include "symm_layout.h"
@@ -761,7 +762,7 @@ extern "C" int tb200_passthrough(const void* src, void* dst, size_t bytes, cudaS
   const int threads = 256;
   size_t blocks = (bytes / 16 + threads - 1) / threads;
   if (blocks < 1) blocks = 1;
-  if (blocks > 148 * 8) blocks = 148 * 8;
+  if (blocks > sm_count() * 8) blocks = sm_count() * 8;
   passthrough_kernel<<<static_cast<unsigned>(blocks), threads, 0, stream>>>(
       static_cast<const uint8_t*>(src), static_cast<uint8_t*>(dst), bytes);
   return LAUNCH_OK();
@@ -915,7 +916,7 @@ extern "C" int tb200_swiglu_bwd(const void* h13, const void* dact, void* dh13, l
                                 int d, cudaStream_t stream) {
   if (rows == 0) return TB200_OK;
   if (d % 2) return TB200_ERR_ARG;
-  swiglu_bwd_kernel<<<148 * 8, 256, 0, stream>>>(static_cast<const __nv_bfloat16*>(h13),
+  swiglu_bwd_kernel<<<sm_count() * 8, 256, 0, stream>>>(static_cast<const __nv_bfloat16*>(h13),
                                                  static_cast<const __nv_bfloat16*>(dact),
                                                  static_cast<__nv_bfloat16*>(dh13), rows, d);
   return LAUNCH_OK();

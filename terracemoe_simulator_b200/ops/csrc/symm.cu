@@ -19,6 +19,7 @@
 // Replaces the all_to_all_single sequences of terrace/ep_dist.py:98-122 (one-hop) and
 // terrace/ta2a_fwd.py:522-670 (two-hop), the arrival chain (terrace/ops/__init__.py:255-300)
 // and the pack chain (terrace/ops/k2_ref.py) of the reference.
+#include "host_util.h"
 #include "launch.h"
 #include "ptx_sm100.cuh"
 #include "symm_layout.h"
@@ -38,6 +39,30 @@ __device__ __forceinline__ float warp_sum_f(float v) {
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
   return v;
+}
+
+// One warp copies a row of n 16-byte chunks; four loads are issued before the four stores so that
+// every lane keeps 64 bytes in flight (a peer store retires only after its NVLink round trip).
+__device__ __forceinline__ void warp_copy_row(uint4* __restrict__ dst, const uint4* __restrict__ src,
+                                              int n, int lane) {
+  int i = lane;
+  for (; i + 96 < n; i += 128) {
+    const uint4 v0 = __ldcg(src + i), v1 = __ldcg(src + i + 32), v2 = __ldcg(src + i + 64),
+                v3 = __ldcg(src + i + 96);
+    dst[i] = v0;
+    dst[i + 32] = v1;
+    dst[i + 64] = v2;
+    dst[i + 96] = v3;
+  }
+  for (; i < n; i += 32) dst[i] = __ldcg(src + i);
+}
+
+// Does local expert `le` (or an invalid pick, which the first chunk reports) belong to the
+// launch that covers local experts [le_lo, le_hi)?
+__device__ __forceinline__ bool in_chunk(int e, int n_experts, int epr, int le_lo, int le_hi) {
+  if (e < 0 || e >= n_experts) return le_lo == 0;
+  const int le = e % epr;
+  return le >= le_lo && le < le_hi;
 }
 
 // Last-block-done: after this block's peer stores, publish them system-wide and count the block;
@@ -184,14 +209,18 @@ __global__ void ep_plan_kernel(Tb200Arena a, PlanTables t, int epoch, int seg_al
 //   dst[owner][pos] = scale * x[t]      (scale = gate when `gs` != null, the backward push)
 //   dgs[p] = <src2[owner][pos], x[t]>   (when `dgs` != null: gate gradient, reads the owner's
 //                                        saved expert output)
+// A launch covers the picks whose LOCAL expert index lies in [le_lo, le_hi) and then raises the
+// arrival flags to `flag_value`: the owners' GEMMs over that expert range can start while the
+// next launch is still sending (the flag values of one step grow from launch to launch).
 // ---------------------------------------------------------------------------------------------
 __global__ void ep_push_kernel(Tb200Arena a, const __nv_bfloat16* __restrict__ x,
                                const int* __restrict__ es, const int* __restrict__ rank_local,
                                const int* __restrict__ chunk_base, const int* __restrict__ my_base,
                                int* __restrict__ pos_out, const float* __restrict__ gs,
                                float* __restrict__ dgs, long long off_dst, long long off_dot,
-                               int T, int flag_kind, int epoch, int* done_counter, int* status,
-                               long long off_rowmap, int ret_slots, int dot_local) {
+                               int T, int flag_kind, int flag_value, int le_lo, int le_hi,
+                               int* done_counter, int* status, long long off_rowmap, int ret_slots,
+                               int dot_local) {
   const int lane = threadIdx.x & 31;
   const int k = a.top_k, H = a.hidden;
   const int n_pairs = T * k;
@@ -200,6 +229,7 @@ __global__ void ep_push_kernel(Tb200Arena a, const __nv_bfloat16* __restrict__ x
        p += gridDim.x * (blockDim.x >> 5)) {
     const int t = p / k;
     const int e = es[p];
+    if (!in_chunk(e, a.n_experts, a.epr, le_lo, le_hi)) continue;
     const int r = rank_local[p];
     int pos = -1;
     if (r >= 0 && e >= 0 && e < a.n_experts)
@@ -219,7 +249,7 @@ __global__ void ep_push_kernel(Tb200Arena a, const __nv_bfloat16* __restrict__ x
     // return address of this row for a GEMM epilogue that scatters its output: (me, slot p)
     if (off_rowmap >= 0 && lane == 0) sect<int>(a, owner, off_rowmap)[pos] = a.rank * ret_slots + p;
     if (gs == nullptr && dgs == nullptr) {
-      for (int i = lane; i < H / 8; i += 32) dst[i] = src[i];
+      warp_copy_row(dst, src, H / 8, lane);
     } else {
       const float w = gs ? gs[p] : 1.0f;
       // the saved expert output of this pick: at the owner's row, or (when the forward GEMM
@@ -232,8 +262,9 @@ __global__ void ep_push_kernel(Tb200Arena a, const __nv_bfloat16* __restrict__ x
                                            sect<__nv_bfloat16>(a, owner, off_dot) +
                                            static_cast<size_t>(pos) * H);
       float dot = 0.f;
+#pragma unroll 2
       for (int i = lane; i < H / 8; i += 32) {
-        uint4 v = src[i];
+        uint4 v = __ldcg(src + i);
         __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&v);
         if (oth) {
           uint4 o = __ldcg(oth + i);
@@ -259,16 +290,17 @@ __global__ void ep_push_kernel(Tb200Arena a, const __nv_bfloat16* __restrict__ x
   }
   if (block_done_is_last(done_counter)) {
     if (static_cast<int>(threadIdx.x) < a.world)
-      st_release_sys(flag_ptr(a, threadIdx.x, flag_kind, a.rank), epoch);
+      st_release_sys(flag_ptr(a, threadIdx.x, flag_kind, a.rank), flag_value);
   }
 }
 
 // Raise flag[kind][me] = epoch on the ranks [first, first + n), optionally after waiting for local
-// flags (the echo path of the dispatch/combine microbenchmark).
+// flags to reach `wait_value` (the echo path of the dispatch/combine microbenchmark).
 __global__ void signal_kernel(Tb200Arena a, int kind, int first, int n, int stride, int epoch,
-                              int wait_kind, int wait_first, int wait_n, int idx, int* status) {
+                              int wait_kind, int wait_first, int wait_n, int wait_value, int idx,
+                              int* status) {
   if (wait_kind >= 0)
-    block_wait_flags(a, wait_kind, wait_first, wait_n, epoch, status, ST_TIMEOUT_FLAG);
+    block_wait_flags(a, wait_kind, wait_first, wait_n, wait_value, status, ST_TIMEOUT_FLAG);
   __threadfence_system();
   __syncthreads();
   if (static_cast<int>(threadIdx.x) < n)
@@ -420,7 +452,7 @@ __global__ void hopa_push_kernel(Tb200Arena a, const __nv_bfloat16* __restrict__
     const uint4* src = reinterpret_cast<const uint4*>(x + static_cast<size_t>(t) * H);
     uint4* dst = reinterpret_cast<uint4*>(sect<__nv_bfloat16>(a, rep, off_rows) +
                                           static_cast<size_t>(dst_row) * H);
-    for (int i = lane; i < H / 8; i += 32) dst[i] = src[i];
+    warp_copy_row(dst, src, H / 8, lane);
   }
   if (block_done_is_last(done_counter)) {
     if (static_cast<int>(threadIdx.x) < a.n_nodes)
@@ -432,12 +464,19 @@ __global__ void hopa_push_kernel(Tb200Arena a, const __nv_bfloat16* __restrict__
 // Two-hop, representative (arrival) side.
 // ---------------------------------------------------------------------------------------------
 // Hop B push: one warp per (arrived row, pick): forward the row to the pick's owner at its final
-// position.  scale_gate: multiply by the pick's gate (backward); dgate_src >= 0: also write
-// dgate[row][c] = <src[owner][pos], row>.
+// position.  scale_gate: multiply by the pick's gate (backward); want_dgate: also write
+// dgate[row][c] = <saved expert output of the pick, row>.  Like the one-hop push, a launch covers
+// the picks of local experts [le_lo, le_hi) and raises the owners' data flags to `flag_value`.
+// off_rowmap >= 0: the return address of every forwarded row (me, slot row * q + c) is left in
+// the owner's row map for a GEMM epilogue that scatters its output back to this representative;
+// dot_local: the saved expert output is read from MY return section (off_dot) at that slot
+// instead of the owner's row.
 __global__ void arrival_push_kernel(Tb200Arena a, const int* __restrict__ rows_a,
                                     long long off_rows, long long off_dst, long long off_dot,
                                     int scale_gate, int want_dgate, int wait_kind, int data_kind,
-                                    int dg_kind, int epoch, int* done_counter, int* status) {
+                                    int dg_kind, int epoch, int flag_value, int le_lo, int le_hi,
+                                    int* done_counter, int* status, long long off_rowmap,
+                                    int dot_local) {
   const int lane = threadIdx.x & 31;
   const int H = a.hidden, q = a.q, Tc = a.tokens_cap;
   const int my_local = a.rank % a.rpn, my_group = a.rank / a.rpn;
@@ -455,6 +494,7 @@ __global__ void arrival_push_kernel(Tb200Arena a, const int* __restrict__ rows_a
     const int* hdr = hdrs + static_cast<size_t>(row) * 3 * q;
     const int pos = __ldcg(hdr + c);
     const int e = __ldcg(hdr + q + c);
+    if (!in_chunk(e, a.n_experts, a.epr, le_lo, le_hi)) continue;
     if (pos < 0 || pos >= a.cap_rows || e < 0 || e >= a.n_experts ||
         e / (a.epr * a.rpn) != my_group) {
       if (lane == 0) {
@@ -468,24 +508,32 @@ __global__ void arrival_push_kernel(Tb200Arena a, const int* __restrict__ rows_a
     const uint4* src = reinterpret_cast<const uint4*>(rows + static_cast<size_t>(row) * H);
     uint4* dst = reinterpret_cast<uint4*>(sect<__nv_bfloat16>(a, owner, off_dst) +
                                           static_cast<size_t>(pos) * H);
-    const uint4* oth = want_dgate ? reinterpret_cast<const uint4*>(
-                                        sect<__nv_bfloat16>(a, owner, off_dot) +
-                                        static_cast<size_t>(pos) * H)
-                                  : nullptr;
+    if (off_rowmap >= 0 && lane == 0)
+      sect<int>(a, owner, off_rowmap)[pos] = a.rank * (a.n_nodes * Tc * q) + item;
+    if (!scale_gate && !want_dgate) {
+      warp_copy_row(dst, src, H / 8, lane);
+      continue;
+    }
+    const uint4* oth = !want_dgate ? nullptr
+                       : dot_local ? reinterpret_cast<const uint4*>(
+                                         sect<__nv_bfloat16>(a, a.rank, off_dot) +
+                                         static_cast<size_t>(item) * H)
+                                   : reinterpret_cast<const uint4*>(
+                                         sect<__nv_bfloat16>(a, owner, off_dot) +
+                                         static_cast<size_t>(pos) * H);
     float dot = 0.f;
+#pragma unroll 2
     for (int j = lane; j < H / 8; j += 32) {
       uint4 v = __ldcg(src + j);
-      if (scale_gate || want_dgate) {
-        __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&v);
-        uint4 o = make_uint4(0, 0, 0, 0);
-        if (oth) o = __ldcg(oth + j);
-        const __nv_bfloat162* oh = reinterpret_cast<const __nv_bfloat162*>(&o);
+      __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&v);
+      uint4 o = make_uint4(0, 0, 0, 0);
+      if (oth) o = __ldcg(oth + j);
+      const __nv_bfloat162* oh = reinterpret_cast<const __nv_bfloat162*>(&o);
 #pragma unroll
-        for (int u = 0; u < 4; ++u) {
-          const float2 g2 = __bfloat1622float2(h[u]), o2 = __bfloat1622float2(oh[u]);
-          dot += g2.x * o2.x + g2.y * o2.y;
-          h[u] = __floats2bfloat162_rn(w * g2.x, w * g2.y);
-        }
+      for (int u = 0; u < 4; ++u) {
+        const float2 g2 = __bfloat1622float2(h[u]), o2 = __bfloat1622float2(oh[u]);
+        dot += g2.x * o2.x + g2.y * o2.y;
+        h[u] = __floats2bfloat162_rn(w * g2.x, w * g2.y);
       }
       dst[j] = v;
     }
@@ -496,7 +544,7 @@ __global__ void arrival_push_kernel(Tb200Arena a, const int* __restrict__ rows_a
   }
   if (block_done_is_last(done_counter)) {
     if (static_cast<int>(threadIdx.x) < a.rpn)
-      st_release_sys(flag_ptr(a, my_group * a.rpn + threadIdx.x, data_kind, a.rank), epoch);
+      st_release_sys(flag_ptr(a, my_group * a.rpn + threadIdx.x, data_kind, a.rank), flag_value);
     if (dg_kind >= 0 && static_cast<int>(threadIdx.x) < a.n_nodes)
       st_release_sys(flag_ptr(a, threadIdx.x * a.rpn + my_local, dg_kind, my_group), epoch);
   }
@@ -507,9 +555,11 @@ __global__ void arrival_push_kernel(Tb200Arena a, const int* __restrict__ rows_a
 __global__ void arrival_combine_kernel(Tb200Arena a, const int* __restrict__ rows_a,
                                        long long off_src, long long off_red, int use_gate,
                                        int wait_kind, int red_kind, int epoch, int* done_counter,
-                                       int* status, int push_back) {
+                                       int* status, int push_back, int local_slots) {
   // push_back: the reduced row goes straight into the ORIGIN's section (block of my group, row
   // i) instead of my own (block of the source group); the origin then combines from local memory
+  // local_slots: the owners' GEMM epilogues stored the expert output of (row, c) into MY section
+  // off_src at slot row * q + c; otherwise it is read from the owner's section at pos
   const int H = a.hidden, q = a.q, Tc = a.tokens_cap;
   const int my_local = a.rank % a.rpn, my_group = a.rank / a.rpn;
   block_wait_flags(a, wait_kind, my_group * a.rpn, a.rpn, epoch, status, ST_TIMEOUT_FLAG);
@@ -533,9 +583,11 @@ __global__ void arrival_combine_kernel(Tb200Arena a, const int* __restrict__ row
         const int e = __ldcg(hdr + q + c);
         if (pos < 0 || pos >= a.cap_rows || e < 0 || e >= a.n_experts) continue;
         const float w = use_gate ? __int_as_float(__ldcg(hdr + 2 * q + c)) : 1.0f;
-        const uint4 v = __ldcg(reinterpret_cast<const uint4*>(
-                                   sect<__nv_bfloat16>(a, e / a.epr, off_src) +
-                                   static_cast<size_t>(pos) * H) + cix);
+        const __nv_bfloat16* srow =
+            local_slots ? sect<__nv_bfloat16>(a, a.rank, off_src) +
+                              (static_cast<size_t>(row) * q + c) * H
+                        : sect<__nv_bfloat16>(a, e / a.epr, off_src) + static_cast<size_t>(pos) * H;
+        const uint4 v = __ldcg(reinterpret_cast<const uint4*>(srow) + cix);
         const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v);
 #pragma unroll
         for (int u = 0; u < 4; ++u) {
@@ -648,30 +700,40 @@ extern "C" int tb200_ep_plan(const Tb200Arena* a, int* chunk_hist, int* chunka_h
   return LAUNCH_OK();
 }
 
+// Grid of a warp-per-item kernel: enough blocks of 8 warps for `items`, at most 8 per SM.
+static int warp_item_grid(long long items) {
+  long long blocks = (items + 7) / 8;
+  const long long cap = static_cast<long long>(sm_count()) * 8;
+  if (blocks < 1) blocks = 1;
+  return static_cast<int>(blocks > cap ? cap : blocks);
+}
+
 extern "C" int tb200_ep_push(const Tb200Arena* a, const void* x, const int* es,
                              const int* rank_local, const int* chunk_base, const int* my_base,
                              int* pos_out, const float* gs, float* dgs, long long off_dst,
-                             long long off_dot, int T, int flag_kind, int epoch, int* done_counter,
-                             int* status, long long off_rowmap, int ret_slots, int dot_local,
-                             cudaStream_t stream) {
-  if (!arena_ok(a)) return TB200_ERR_ARG;
+                             long long off_dot, int T, int flag_kind, int flag_value, int le_lo,
+                             int le_hi, int* done_counter, int* status, long long off_rowmap,
+                             int ret_slots, int dot_local, cudaStream_t stream) {
+  if (!arena_ok(a) || le_lo < 0 || le_hi > a->epr || le_lo >= le_hi) return TB200_ERR_ARG;
   if ((off_rowmap >= 0 || dot_local) && ret_slots < T * a->top_k) return TB200_ERR_ARG;
-  int blocks = (T * a->top_k + 7) / 8;
-  if (blocks < 1) blocks = 1;
-  if (blocks > 148 * 8) blocks = 148 * 8;
+  // a launch that covers a part of the experts touches about that share of the picks
+  const long long items = static_cast<long long>(T) * a->top_k;
+  const int blocks = warp_item_grid(le_hi - le_lo == a->epr ? items
+                                                            : items * (le_hi - le_lo) / a->epr * 2);
   ep_push_kernel<<<blocks, 256, 0, stream>>>(*a, static_cast<const __nv_bfloat16*>(x), es,
                                              rank_local, chunk_base, my_base, pos_out, gs, dgs,
-                                             off_dst, off_dot, T, flag_kind, epoch, done_counter,
-                                             status, off_rowmap, ret_slots, dot_local);
+                                             off_dst, off_dot, T, flag_kind, flag_value, le_lo,
+                                             le_hi, done_counter, status, off_rowmap, ret_slots,
+                                             dot_local);
   return LAUNCH_OK();
 }
 
 extern "C" int tb200_signal(const Tb200Arena* a, int kind, int first, int n, int stride, int idx,
-                            int epoch, int wait_kind, int wait_first, int wait_n, int* status,
-                            cudaStream_t stream) {
+                            int epoch, int wait_kind, int wait_first, int wait_n, int wait_value,
+                            int* status, cudaStream_t stream) {
   if (!arena_ok(a) || n > 32 || wait_n > 32) return TB200_ERR_ARG;
   signal_kernel<<<1, 32, 0, stream>>>(*a, kind, first, n, stride, epoch, wait_kind, wait_first,
-                                      wait_n, idx, status);
+                                      wait_n, wait_value, idx, status);
   return LAUNCH_OK();
 }
 
@@ -681,7 +743,8 @@ extern "C" int tb200_ep_pull_combine(const Tb200Arena* a, const int* pos, const 
                                      int local_slots, cudaStream_t stream) {
   if (!arena_ok(a) || group_size < 1) return TB200_ERR_ARG;
   if (local_slots > 0 && local_slots < T * a->top_k) return TB200_ERR_ARG;
-  int blocks = T < 1 ? 1 : (T > 148 * 8 ? 148 * 8 : T);
+  const int cap = sm_count() * 8;
+  const int blocks = T < 1 ? 1 : (T > cap ? cap : T);
   ep_pull_combine_kernel<<<blocks, 256, 0, stream>>>(*a, pos, es, gs,
                                                      static_cast<__nv_bfloat16*>(y), off_src, T,
                                                      group_size, wait_kind, epoch, status,
@@ -705,9 +768,7 @@ extern "C" int tb200_hopa_push(const Tb200Arena* a, const void* x, const int* es
                                int flag_kind, int epoch, int* done_counter, int* status,
                                cudaStream_t stream) {
   if (!arena_ok(a) || T > a->tokens_cap) return TB200_ERR_ARG;
-  int blocks = (T * a->groups_m + 7) / 8;
-  if (blocks < 1) blocks = 1;
-  if (blocks > 148 * 8) blocks = 148 * 8;
+  const int blocks = warp_item_grid(static_cast<long long>(T) * a->groups_m);
   hopa_push_kernel<<<blocks, 256, 0, stream>>>(
       *a, static_cast<const __nv_bfloat16*>(x), es, gs, rank_local, chunk_base, my_base,
       ranka_local, chunka_base, pos_out, rowa, off_rows, with_header, T, flag_kind, epoch,
@@ -718,22 +779,25 @@ extern "C" int tb200_hopa_push(const Tb200Arena* a, const void* x, const int* es
 extern "C" int tb200_arrival_push(const Tb200Arena* a, const int* rows_a, long long off_rows,
                                   long long off_dst, long long off_dot, int scale_gate,
                                   int want_dgate, int wait_kind, int data_kind, int dg_kind,
-                                  int epoch, int* done_counter, int* status, cudaStream_t stream) {
-  if (!arena_ok(a)) return TB200_ERR_ARG;
-  arrival_push_kernel<<<148 * 8, 256, 0, stream>>>(*a, rows_a, off_rows, off_dst, off_dot,
-                                                   scale_gate, want_dgate, wait_kind, data_kind,
-                                                   dg_kind, epoch, done_counter, status);
+                                  int epoch, int flag_value, int le_lo, int le_hi,
+                                  int* done_counter, int* status, long long off_rowmap,
+                                  int dot_local, cudaStream_t stream) {
+  if (!arena_ok(a) || le_lo < 0 || le_hi > a->epr || le_lo >= le_hi) return TB200_ERR_ARG;
+  arrival_push_kernel<<<sm_count() * 8, 256, 0, stream>>>(
+      *a, rows_a, off_rows, off_dst, off_dot, scale_gate, want_dgate, wait_kind, data_kind,
+      dg_kind, epoch, flag_value, le_lo, le_hi, done_counter, status, off_rowmap, dot_local);
   return LAUNCH_OK();
 }
 
 extern "C" int tb200_arrival_combine(const Tb200Arena* a, const int* rows_a, long long off_src,
                                      long long off_red, int use_gate, int wait_kind, int red_kind,
                                      int epoch, int* done_counter, int* status, int push_back,
-                                     cudaStream_t stream) {
+                                     int local_slots, cudaStream_t stream) {
   if (!arena_ok(a)) return TB200_ERR_ARG;
-  arrival_combine_kernel<<<148 * 8, 256, 0, stream>>>(*a, rows_a, off_src, off_red, use_gate,
-                                                      wait_kind, red_kind, epoch, done_counter,
-                                                      status, push_back);
+  arrival_combine_kernel<<<sm_count() * 8, 256, 0, stream>>>(*a, rows_a, off_src, off_red,
+                                                             use_gate, wait_kind, red_kind, epoch,
+                                                             done_counter, status, push_back,
+                                                             local_slots);
   return LAUNCH_OK();
 }
 
@@ -741,7 +805,8 @@ extern "C" int tb200_origin_combine(const Tb200Arena* a, const int* es, const in
                                     long long off_red, int T, int wait_kind, int epoch, int* status,
                                     int local_rows, cudaStream_t stream) {
   if (!arena_ok(a)) return TB200_ERR_ARG;
-  int blocks = T < 1 ? 1 : (T > 148 * 8 ? 148 * 8 : T);
+  const int cap = sm_count() * 8;
+  const int blocks = T < 1 ? 1 : (T > cap ? cap : T);
   origin_combine_kernel<<<blocks, 256, 0, stream>>>(*a, es, rowa, static_cast<__nv_bfloat16*>(y),
                                                     off_red, T, wait_kind, epoch, status,
                                                     local_rows);

@@ -63,6 +63,10 @@ Tensor& symm_status(int device) {
 }
 int* st_ptr(const Tensor& like) { return symm_status(like.get_device()).data_ptr<int>(); }
 
+// The device status word itself (no copy, no synchronisation): a training loop can read it a few
+// steps late through a deferred device-to-host copy instead of stalling on take_status.
+Tensor symm_status_tensor(int64_t device) { return symm_status(static_cast<int>(device)); }
+
 int64_t symm_take_status(int64_t device) {
   Tensor& w = symm_status(static_cast<int>(device));
   const int v = w.item<int>();
@@ -180,76 +184,64 @@ std::tuple<Tensor, Tensor, Tensor, Tensor> ep_plan(const Tensor& arena, Tensor c
   return {my_base, seg_start, seg_count, rows_a};
 }
 
-std::tuple<Tensor, Tensor> ep_push_impl(const Tensor& arena, const Tensor& x, const Tensor& es,
-                                        const Tensor& rank_local, const Tensor& chunk_base,
-                                        const Tensor& my_base, const c10::optional<Tensor>& gs,
-                                        bool want_dgs, int64_t dst_sel, int64_t dot_off,
-                                        int64_t flag_kind, int64_t epoch, Tensor done,
-                                        int64_t rowmap_off, int64_t ret_slots, bool dot_local) {
+// One-hop push of the picks whose local expert index lies in [le_lo, le_hi) into the owners'
+// sections at byte offset `dst_off`; `pos` ([T, k], written for the covered picks) and `dgs`
+// (gate gradients, optional) are shared by the launches of one step.  rowmap_off >= 0: the
+// return address (source rank, slot) of every row is left in the owner's row map for a GEMM
+// whose epilogue scatters its rows back (grouped_gemm_scatter).  dot_local: the gate gradient
+// reads the saved expert output from MY return section (`dot_off`) at slot p instead of the
+// owner's row at `dot_off`.
+void ep_push(const Tensor& arena, const Tensor& x, const Tensor& es, const Tensor& rank_local,
+             const Tensor& chunk_base, const Tensor& my_base, const c10::optional<Tensor>& gs,
+             Tensor pos, const c10::optional<Tensor>& dgs, int64_t dst_off, int64_t dot_off,
+             bool dot_local, int64_t flag_kind, int64_t flag_value, int64_t le_lo, int64_t le_hi,
+             Tensor done, int64_t rowmap_off, int64_t ret_slots) {
   const Tb200Arena* a = arena_of(arena);
   TORCH_CHECK(rowmap_off < 0 || rowmap_off % 16 == 0, "ep_push: row map offset alignment");
-  TORCH_CHECK(dot_off % 16 == 0, "ep_push: dot section alignment");
+  TORCH_CHECK(dst_off >= 0 && dst_off % 16 == 0 && dot_off % 16 == 0,
+              "ep_push: section offsets must be 16-byte aligned");
   TORCH_CHECK(x.is_cuda() && x.is_contiguous() && x.scalar_type() == at::kBFloat16 &&
                   x.dim() == 2 && x.size(1) == a->hidden,
               "ep_push: bf16 [T, H] rows");
   TORCH_CHECK(es.sizes() == rank_local.sizes() && es.size(0) == x.size(0) &&
-                  es.size(1) == a->top_k,
-              "ep_push: index planes must be [T, k]");
+                  es.size(1) == a->top_k && es.scalar_type() == at::kInt,
+              "ep_push: index planes must be int32 [T, k]");
+  TORCH_CHECK(pos.is_cuda() && pos.is_contiguous() && pos.scalar_type() == at::kInt &&
+                  pos.sizes() == es.sizes(),
+              "ep_push: pos must be int32 [T, k]");
+  const bool want_dgs = dgs.has_value();
+  if (want_dgs)
+    TORCH_CHECK(dgs->is_cuda() && dgs->is_contiguous() && dgs->scalar_type() == at::kFloat &&
+                    dgs->sizes() == es.sizes(),
+                "ep_push: dgs must be fp32 [T, k]");
   c10::cuda::CUDAGuard guard(x.device());
   const int64_t T = x.size(0);
-  Tensor pos = at::empty({T, a->top_k}, es.options());
-  Tensor dgs = want_dgs ? at::empty({T, a->top_k}, x.options().dtype(at::kFloat))
-                        : at::empty({0}, x.options().dtype(at::kFloat));
   check_rc(tb200_ep_push(a, x.data_ptr(), es.data_ptr<int>(), rank_local.data_ptr<int>(),
                          chunk_base.data_ptr<int>(), my_base.data_ptr<int>(), pos.data_ptr<int>(),
                          gs.has_value() ? gs->data_ptr<float>() : nullptr,
-                         want_dgs ? dgs.data_ptr<float>() : nullptr, section_offset(a, dst_sel),
-                         want_dgs ? dot_off : 0, T, flag_kind, epoch, done.data_ptr<int>(),
-                         st_ptr(x), rowmap_off, static_cast<int>(ret_slots), dot_local ? 1 : 0,
-                         cur_stream()),
+                         want_dgs ? dgs->data_ptr<float>() : nullptr, dst_off,
+                         want_dgs ? dot_off : 0, T, flag_kind, flag_value, le_lo, le_hi,
+                         done.data_ptr<int>(), st_ptr(x), rowmap_off, static_cast<int>(ret_slots),
+                         dot_local ? 1 : 0, cur_stream()),
            "ep_push");
-  return {pos, dgs};
-}
-
-std::tuple<Tensor, Tensor> ep_push(const Tensor& arena, const Tensor& x, const Tensor& es,
-                                   const Tensor& rank_local, const Tensor& chunk_base,
-                                   const Tensor& my_base, const c10::optional<Tensor>& gs,
-                                   bool want_dgs, int64_t dst_sel, int64_t dot_sel,
-                                   int64_t flag_kind, int64_t epoch, Tensor done) {
-  const Tb200Arena* a = arena_of(arena);
-  return ep_push_impl(arena, x, es, rank_local, chunk_base, my_base, gs, want_dgs, dst_sel,
-                      want_dgs ? section_offset(a, dot_sel) : 0, flag_kind, epoch, done, -1, 0,
-                      false);
-}
-
-// Push that also leaves, beside every row, its return address (source rank, slot) in the owner's
-// row map at byte offset `rowmap_off` of the arena, for a GEMM whose epilogue scatters its rows
-// back (grouped_gemm_scatter).  With `dot_local` the gate gradient reads the saved expert output
-// from MY return section (`dot_off`) at slot p instead of the owner's row.
-std::tuple<Tensor, Tensor> ep_push_ret(const Tensor& arena, const Tensor& x, const Tensor& es,
-                                       const Tensor& rank_local, const Tensor& chunk_base,
-                                       const Tensor& my_base, const c10::optional<Tensor>& gs,
-                                       bool want_dgs, int64_t dst_sel, int64_t dot_off,
-                                       bool dot_local, int64_t flag_kind, int64_t epoch,
-                                       Tensor done, int64_t rowmap_off, int64_t ret_slots) {
-  TORCH_CHECK(rowmap_off >= 0 && ret_slots > 0, "ep_push_ret: row map offset and slot count");
-  return ep_push_impl(arena, x, es, rank_local, chunk_base, my_base, gs, want_dgs, dst_sel,
-                      dot_off, flag_kind, epoch, done, rowmap_off, ret_slots, dot_local);
 }
 
 void ep_signal(const Tensor& arena, int64_t kind, int64_t first, int64_t n, int64_t stride,
                int64_t idx, int64_t epoch, int64_t wait_kind, int64_t wait_first, int64_t wait_n,
-               const Tensor& like) {
+               int64_t wait_value, const Tensor& like) {
   const Tb200Arena* a = arena_of(arena);
   c10::cuda::CUDAGuard guard(like.device());
   check_rc(tb200_signal(a, kind, first, n, stride, idx, epoch, wait_kind, wait_first, wait_n,
-                        st_ptr(like), cur_stream()),
+                        wait_value, st_ptr(like), cur_stream()),
            "ep_signal");
 }
 
-Tensor ep_pull_combine_impl(const Tensor& arena, const Tensor& pos, const Tensor& es,
-                            const c10::optional<Tensor>& gs, int64_t src_off, int64_t group_size,
-                            int64_t wait_kind, int64_t epoch, int64_t local_slots) {
+// y[t] = canonical gate-weighted reduction of the token's k expert-output rows, read from the
+// owners' sections at byte offset `src_off` (row pos) or, with local_slots > 0, from MY section
+// at `src_off`, slot t * k + j (the owners' GEMM epilogues stored them there).
+Tensor ep_pull_combine(const Tensor& arena, const Tensor& pos, const Tensor& es,
+                       const c10::optional<Tensor>& gs, int64_t src_off, int64_t group_size,
+                       int64_t wait_kind, int64_t epoch, int64_t local_slots) {
   const Tb200Arena* a = arena_of(arena);
   TORCH_CHECK(src_off >= 0 && src_off % 16 == 0, "ep_pull_combine: section offset");
   TORCH_CHECK(pos.is_cuda() && pos.is_contiguous() && pos.sizes() == es.sizes() &&
@@ -264,22 +256,6 @@ Tensor ep_pull_combine_impl(const Tensor& arena, const Tensor& pos, const Tensor
                                  static_cast<int>(local_slots), cur_stream()),
            "ep_pull_combine");
   return y;
-}
-
-Tensor ep_pull_combine(const Tensor& arena, const Tensor& pos, const Tensor& es,
-                       const c10::optional<Tensor>& gs, int64_t src_sel, int64_t group_size,
-                       int64_t wait_kind, int64_t epoch) {
-  return ep_pull_combine_impl(arena, pos, es, gs, section_offset(arena_of(arena), src_sel),
-                              group_size, wait_kind, epoch, 0);
-}
-
-// Combine from MY return section (byte offset `src_off`, `slots` rows): the owners' GEMM
-// epilogues stored row (t, j) at slot t * k + j; same canonical reduction as ep_pull_combine.
-Tensor ep_combine_local(const Tensor& arena, const Tensor& pos, const Tensor& es,
-                        const c10::optional<Tensor>& gs, int64_t src_off, int64_t slots,
-                        int64_t group_size, int64_t wait_kind, int64_t epoch) {
-  TORCH_CHECK(slots > 0, "ep_combine_local: slot count");
-  return ep_pull_combine_impl(arena, pos, es, gs, src_off, group_size, wait_kind, epoch, slots);
 }
 
 std::tuple<Tensor, Tensor> hopa_rank(const Tensor& arena, const Tensor& es) {
@@ -320,27 +296,33 @@ std::tuple<Tensor, Tensor> hopa_push(const Tensor& arena, const Tensor& x, const
   return {pos, rowa};
 }
 
-void arrival_push(const Tensor& arena, const Tensor& rows_a, int64_t rows_sel, int64_t dst_sel,
-                  int64_t dot_sel, bool scale_gate, bool want_dgate, int64_t wait_kind,
-                  int64_t data_kind, int64_t dg_kind, int64_t epoch, Tensor done) {
+void arrival_push(const Tensor& arena, const Tensor& rows_a, int64_t rows_sel, int64_t dst_off,
+                  int64_t dot_off, bool dot_local, bool scale_gate, bool want_dgate,
+                  int64_t wait_kind, int64_t data_kind, int64_t dg_kind, int64_t epoch,
+                  int64_t flag_value, int64_t le_lo, int64_t le_hi, Tensor done,
+                  int64_t rowmap_off) {
   const Tb200Arena* a = arena_of(arena);
+  TORCH_CHECK(dst_off >= 0 && dst_off % 16 == 0 && dot_off % 16 == 0 &&
+                  (rowmap_off < 0 || rowmap_off % 16 == 0),
+              "arrival_push: section offsets must be 16-byte aligned");
   c10::cuda::CUDAGuard guard(rows_a.device());
-  check_rc(tb200_arrival_push(a, rows_a.data_ptr<int>(), section_offset(a, rows_sel),
-                              section_offset(a, dst_sel),
-                              want_dgate ? section_offset(a, dot_sel) : 0, scale_gate, want_dgate,
-                              wait_kind, data_kind, dg_kind, epoch, done.data_ptr<int>(),
-                              st_ptr(rows_a), cur_stream()),
+  check_rc(tb200_arrival_push(a, rows_a.data_ptr<int>(), section_offset(a, rows_sel), dst_off,
+                              want_dgate ? dot_off : 0, scale_gate, want_dgate, wait_kind,
+                              data_kind, dg_kind, epoch, flag_value, le_lo, le_hi,
+                              done.data_ptr<int>(), st_ptr(rows_a), rowmap_off, dot_local ? 1 : 0,
+                              cur_stream()),
            "arrival_push");
 }
 
-void arrival_combine(const Tensor& arena, const Tensor& rows_a, int64_t src_sel, int64_t red_sel,
+void arrival_combine(const Tensor& arena, const Tensor& rows_a, int64_t src_off, int64_t red_sel,
                      bool use_gate, int64_t wait_kind, int64_t red_kind, int64_t epoch,
-                     Tensor done, bool push_back) {
+                     Tensor done, bool push_back, bool local_slots) {
   const Tb200Arena* a = arena_of(arena);
+  TORCH_CHECK(src_off >= 0 && src_off % 16 == 0, "arrival_combine: section offset");
   c10::cuda::CUDAGuard guard(rows_a.device());
-  check_rc(tb200_arrival_combine(a, rows_a.data_ptr<int>(), section_offset(a, src_sel),
-                                 section_offset(a, red_sel), use_gate, wait_kind, red_kind, epoch,
-                                 done.data_ptr<int>(), st_ptr(rows_a), push_back ? 1 : 0,
+  check_rc(tb200_arrival_combine(a, rows_a.data_ptr<int>(), src_off, section_offset(a, red_sel),
+                                 use_gate, wait_kind, red_kind, epoch, done.data_ptr<int>(),
+                                 st_ptr(rows_a), push_back ? 1 : 0, local_slots ? 1 : 0,
                                  cur_stream()),
            "arrival_combine");
 }
@@ -459,6 +441,7 @@ void grouped_gemm_scatter(const Tensor& A, const Tensor& B, const Tensor& seg_st
 
 void terrace_b200_register_symm(torch::Library& m) {
   m.def("symm_take_status(int device) -> int", &symm_take_status);
+  m.def("symm_status_tensor(int device) -> Tensor", &symm_status_tensor);
   m.def("symm_alloc(int nbytes, int device) -> Tensor", &symm_alloc);
   m.def("symm_ipc_handle(Tensor buf) -> Tensor", &symm_ipc_handle);
   m.def("symm_ipc_open(Tensor handle, int device) -> int", &symm_ipc_open);
@@ -469,18 +452,15 @@ void terrace_b200_register_symm(torch::Library& m) {
   m.def("ep_plan(Tensor arena, Tensor(a!) chunk_hist, Tensor(b!)? chunka_hist, int epoch, "
         "int seg_align=1) -> (Tensor, Tensor, Tensor, Tensor)", &ep_plan);
   m.def("ep_push(Tensor arena, Tensor x, Tensor es, Tensor rank_local, Tensor chunk_base, "
-        "Tensor my_base, Tensor? gs, bool want_dgs, int dst_sel, int dot_sel, int flag_kind, "
-        "int epoch, Tensor(a!) done) -> (Tensor, Tensor)", &ep_push);
+        "Tensor my_base, Tensor? gs, Tensor(a!) pos, Tensor(b!)? dgs, int dst_off, int dot_off, "
+        "bool dot_local, int flag_kind, int flag_value, int le_lo, int le_hi, Tensor(c!) done, "
+        "int rowmap_off, int ret_slots) -> ()", &ep_push);
   m.def("ep_signal(Tensor arena, int kind, int first, int n, int stride, int idx, int epoch, "
-        "int wait_kind, int wait_first, int wait_n, Tensor like) -> ()", &ep_signal);
-  m.def("ep_pull_combine(Tensor arena, Tensor pos, Tensor es, Tensor? gs, int src_sel, "
-        "int group_size, int wait_kind, int epoch) -> Tensor", &ep_pull_combine);
-  m.def("ep_push_ret(Tensor arena, Tensor x, Tensor es, Tensor rank_local, Tensor chunk_base, "
-        "Tensor my_base, Tensor? gs, bool want_dgs, int dst_sel, int dot_off, bool dot_local, "
-        "int flag_kind, int epoch, Tensor(a!) done, int rowmap_off, int ret_slots) "
-        "-> (Tensor, Tensor)", &ep_push_ret);
-  m.def("ep_combine_local(Tensor arena, Tensor pos, Tensor es, Tensor? gs, int src_off, "
-        "int slots, int group_size, int wait_kind, int epoch) -> Tensor", &ep_combine_local);
+        "int wait_kind, int wait_first, int wait_n, int wait_value, Tensor like) -> ()",
+        &ep_signal);
+  m.def("ep_pull_combine(Tensor arena, Tensor pos, Tensor es, Tensor? gs, int src_off, "
+        "int group_size, int wait_kind, int epoch, int local_slots=0) -> Tensor",
+        &ep_pull_combine);
   m.def("grouped_gemm_scatter(Tensor A, Tensor B, Tensor seg_start, Tensor seg_count, int mode, "
         "Tensor row_map, Tensor scatter_base, int slots) -> ()", &grouped_gemm_scatter);
   m.def("hopa_rank(Tensor arena, Tensor es) -> (Tensor, Tensor)", &hopa_rank);
@@ -488,12 +468,13 @@ void terrace_b200_register_symm(torch::Library& m) {
         "Tensor chunk_base, Tensor my_base, Tensor ranka_local, Tensor chunka_base, "
         "Tensor? rowa_in, int rows_sel, bool with_header, int flag_kind, int epoch, "
         "Tensor(a!) done) -> (Tensor, Tensor)", &hopa_push);
-  m.def("arrival_push(Tensor arena, Tensor rows_a, int rows_sel, int dst_sel, int dot_sel, "
-        "bool scale_gate, bool want_dgate, int wait_kind, int data_kind, int dg_kind, int epoch, "
-        "Tensor(a!) done) -> ()", &arrival_push);
-  m.def("arrival_combine(Tensor arena, Tensor rows_a, int src_sel, int red_sel, bool use_gate, "
-        "int wait_kind, int red_kind, int epoch, Tensor(a!) done, bool push_back=False) -> ()",
-        &arrival_combine);
+  m.def("arrival_push(Tensor arena, Tensor rows_a, int rows_sel, int dst_off, int dot_off, "
+        "bool dot_local, bool scale_gate, bool want_dgate, int wait_kind, int data_kind, "
+        "int dg_kind, int epoch, int flag_value, int le_lo, int le_hi, Tensor(a!) done, "
+        "int rowmap_off) -> ()", &arrival_push);
+  m.def("arrival_combine(Tensor arena, Tensor rows_a, int src_off, int red_sel, bool use_gate, "
+        "int wait_kind, int red_kind, int epoch, Tensor(a!) done, bool push_back=False, "
+        "bool local_slots=False) -> ()", &arrival_combine);
   m.def("origin_combine(Tensor arena, Tensor es, Tensor rowa, int red_sel, int wait_kind, "
         "int epoch, bool local_rows=False) -> Tensor", &origin_combine);
   m.def("origin_pull_dgate(Tensor arena, Tensor es, Tensor rowa, int wait_kind, int epoch) -> "

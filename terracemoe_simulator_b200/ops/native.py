@@ -32,7 +32,7 @@ class _Counted:
                  "ep_signal": 1, "ep_pull_combine": 1, "hopa_rank": 1, "hopa_push": 1,
                  "arrival_push": 1, "arrival_combine": 1, "origin_combine": 1,
                  "origin_pull_dgate": 1, "grouped_gemm_ex": 1, "attn_fwd": 1, "attn_bwd": 3,
-                 "ep_push_ret": 1, "ep_combine_local": 1, "grouped_gemm_scatter": 1}
+                 "grouped_wgrad_out": 1, "grouped_gemm_scatter": 1}
 
     def __getattr__(self, name):
         fn = getattr(torch.ops.terrace, name)

@@ -131,11 +131,14 @@ def swiglu_experts(rows: torch.Tensor, w13: torch.Tensor, w2: torch.Tensor, coun
 
 def ep_moe_forward(x_local: torch.Tensor, expert_idx: torch.Tensor, gates: torch.Tensor,
                    w13_shard: torch.Tensor, w2_shard: torch.Tensor, world: int, n_experts: int,
-                   *, group=None, rpn: int | None = None, canonical: bool = True) -> torch.Tensor:
+                   *, group=None, rpn: int | None = None, canonical: bool = True,
+                   experts_fn=None) -> torch.Tensor:
     """Routed-expert output for this rank's tokens under one-hop EP (4 collectives forward).
 
     Rank r owns experts ``[r*epr, (r+1)*epr)``.  ``rpn`` (ranks per logical group) only
     selects the grouping of the canonical reduction tree; ``None`` means a single group.
+    ``experts_fn(rows, w13, w2, counts)`` replaces the expert compute (default: the SwiGLU
+    experts); a benchmark passes the identity to time the exchange alone.
     """
     CALLS["one_hop"] += 1
     if n_experts % world:
@@ -165,7 +168,7 @@ def ep_moe_forward(x_local: torch.Tensor, expert_idx: torch.Tensor, gates: torch
 
     order = torch.argsort(reid, stable=True)            # (expert, source rank, token)
     counts = hist(reid, epr)
-    ye = swiglu_experts(rx[order], w13_shard, w2_shard, counts)
+    ye = (experts_fn or swiglu_experts)(rx[order], w13_shard, w2_shard, counts)
     unsort = torch.empty_like(order)
     unsort[order] = torch.arange(order.numel(), device=dev)
     back = _a2a(ye[unsort], recv_l, send_l, group)

@@ -5,35 +5,48 @@ rank ``cudaMalloc``s the same layout, exports it with CUDA IPC, and maps all pee
 (``ops/csrc/symm.cu``) then move token rows with plain peer stores/loads and synchronise with
 epoch flags; NCCL is used only to exchange the IPC handles at start-up.
 
-One step of ``fused_moe_forward`` (no host synchronisation anywhere):
+Default schedule (``overlap``; no host synchronisation anywhere, nothing is read remotely):
 
-  one-hop   plan -> push rows into the owners' expert-sorted input -> [GEMM1 waits on the
-            arrival flags of its A operand] SwiGLU GEMMs -> signal -> gate-weighted pull combine
+  one-hop   plan -> the push of the rows runs on a side stream in ``chunks`` launches, one per
+            range of local experts, each raising the owners' arrival flags a little further ->
+            per chunk: [GEMM 1 waits for the flag value of its expert range] SwiGLU GEMM, then
+            GEMM 2 whose epilogue stores every output row straight into the ORIGIN's return slot
+            over NVLink -> signal -> the origin reduces its k slots from local memory
   two-hop   plan -> Hop A push (one row per (token, group) + header) to the representative ->
-            representative forwards every (row, pick) to the owner (Hop B) -> GEMMs -> the
-            representative pulls, applies the gates and reduces per row -> origin pulls and adds
-            its M group rows
+            the representative forwards every (row, pick) to the owner (Hop B), again chunk by
+            chunk on the side stream -> per chunk: gated SwiGLU GEMM, GEMM 2 storing each row
+            into the REPRESENTATIVE's return slot -> the representative applies the gates and
+            reduces the q picks of a row from local memory and stores the result into the
+            origin's section -> the origin adds its M group rows from local memory
 
-Two-hop with ``TERRACE_EP_PUSH_BACK=1`` (off by default): the representative stores each reduced
-(token, group) row into the ORIGIN's section (block of the representative's group, same row
-inside the block) instead of keeping it for the origin to read remotely; the origin's final sum
-then reads local memory.  Values and order are unchanged.
+  so the transfer of chunk c + 1 runs under the GEMMs of chunk c, the return transfer is part of
+  the second GEMM, and the only exposed communication is the first chunk's push and the final
+  local reduction.  The backward pass mirrors it (combine-backward is dispatch shaped and also
+  produces the gate gradients; dispatch-backward is combine shaped).
 
-One-hop with ``epilogue_push`` (``TERRACE_EP_EPILOGUE_PUSH=1``; off by default): the push also
-leaves every row's return address in the owner's row map, the second expert GEMM stores each
-output row from its epilogue straight into the ORIGIN's return slot over NVLink (one kernel does
-the GEMM and the combine transfer, tile by tile), and the combine reads local memory only.  The
-reduction order is unchanged, so the result equals the pull path bit for bit.
+Why the side stream cannot deadlock although GEMM kernels spin on flags: a GEMM only waits for
+pushes of OTHER GPUs (its own GPU's push of the same chunk precedes it through an event); pushes
+wait for nothing but, in the two-hop case, other GPUs' Hop A pushes, which wait for nothing; and
+a push kernel needs no shared memory, so it is always schedulable beside a resident GEMM.
 
-The backward pass runs the mirrored pipeline (combine-backward is dispatch shaped and also
-produces the gate gradients; dispatch-backward is combine shaped).  Both paths place rows at
-positions the ORIGIN computes from the all-gathered expert histogram, so the expert GEMMs see
-identical inputs and the two paths agree bit for bit.
+``TERRACE_EP_OVERLAP=0`` keeps the earlier schedule as the A/B arm: one push launch, plain GEMMs
+into the owner's output section, and a combine that reads the owners' rows remotely.
+
+Both schedules and both hops place rows at positions the ORIGIN computes from the all-gathered
+expert histogram and reduce in the same canonical order, so one-hop and two-hop agree bit for
+bit with each other and across schedules.
+
+One forward may be outstanding per context: the backward reads the forward's rows from the
+arena, so a second forward before the backward of the first would overwrite them.  The context
+refuses that with an error instead of returning wrong gradients.
 
 Reference counterparts: ``terrace/ep_dist.py:82-122`` and ``terrace/ta2a_fwd.py:445-670`` (which
-issue 4 and 9 collectives with 1-3 host syncs per forward).
+issue 4 and 9 collectives with 1-3 host syncs per forward); the overlap window of the seam,
+``terrace/ta2a_dispatch.py:765-778``.
 """
 from __future__ import annotations
+
+import weakref
 
 import torch
 import torch.distributed as dist
@@ -42,7 +55,8 @@ from ..routing import TRouteConfig
 from ..utils import trace
 from ..utils.flags import flag_bool, flag_int
 
-# arena sections (must match section_offset() in symm_bindings.cpp)
+# arena sections with a selector in the native ops (must match section_offset() in
+# symm_bindings.cpp)
 XIN, YOUT, DOUT, DXS, HA_ROWS, RED, HB_ROWS, DRED = range(8)
 # flag kinds (must match Tb200FlagKind)
 (FK_COUNTS, FK_HOPA, FK_DATA, FK_OUT, FK_RED, FK_B_HOPA, FK_B_DATA, FK_B_DG, FK_B_OUT,
@@ -50,9 +64,17 @@ XIN, YOUT, DOUT, DXS, HA_ROWS, RED, HB_ROWS, DRED = range(8)
 FK_NUM = 10
 MAX_WORLD = 16
 SEG_ALIGN = 64          # expert segments start on multiples of 64 rows (zero padding rows)
+MAX_CHUNKS = 8
+FLAG_STRIDE = 16        # data flags take the values epoch * 16 + (chunks landed), 15 = all
 
 LIVE = {"one_hop_fwd": 0, "two_hop_fwd": 0, "one_hop_bwd": 0, "two_hop_bwd": 0, "echo": 0,
-        "epilogue_push_fwd": 0, "epilogue_push_bwd": 0, "push_back": 0}
+        "overlap_fwd": 0, "overlap_bwd": 0, "chunk_pushes": 0}
+
+# names of the arena sections in layout order; the first twelve fill the native descriptor
+_BASE_SECTIONS = ("counts_all", "flags", "xin", "yout", "dout", "dxs", "ha_rows", "ha_hdr", "red",
+                  "hb_rows", "dred", "dgate")
+_SEL_NAME = {XIN: "xin", YOUT: "yout", DOUT: "dout", DXS: "dxs", HA_ROWS: "ha_rows", RED: "red",
+             HB_ROWS: "hb_rows", DRED: "dred"}
 
 
 def _lib():
@@ -80,18 +102,40 @@ def arena_layout(sizes, guard: int = GUARD_BYTES):
     return offsets, guards, off
 
 
+def chunk_ranges(epr: int, chunks: int):
+    """Split the local experts ``0 .. epr`` into at most ``chunks`` contiguous ranges of (almost)
+    equal length: ``[(lo, hi), ...]``."""
+    n = max(1, min(int(chunks), epr, MAX_CHUNKS))
+    base, extra = divmod(epr, n)
+    out, lo = [], 0
+    for i in range(n):
+        hi = lo + base + (1 if i < extra else 0)
+        out.append((lo, hi))
+        lo = hi
+    return out
+
+
+def flag_value(epoch: int, i: int, n: int) -> int:
+    """Value of the data flags once chunk ``i`` of ``n`` has landed (the last one writes 15)."""
+    return epoch * FLAG_STRIDE + (FLAG_STRIDE - 1 if i == n - 1 else i + 1)
+
+
 class FusedEPContext:
     def __init__(self, cfg: TRouteConfig, hidden: int, d_expert: int, tokens: int, *, world: int,
                  rank: int, rpn: int, device, group=None, row_capacity_factor: float = 2.0,
-                 epilogue_push=None):
+                 overlap=None, chunks=None):
         from .. import ops
         if not ops.custom_ops_enabled():
             raise RuntimeError("the fused transport needs the native library: "
                                + ops.status().reason)
+        if overlap is None:
+            overlap = flag_bool("TERRACE_EP_OVERLAP", True)
+        if chunks is None:
+            chunks = flag_int("TERRACE_EP_CHUNKS", 2, 1, MAX_CHUNKS)
         self._init_args = dict(cfg=cfg, hidden=hidden, d_expert=d_expert, tokens=tokens,
                                world=world, rank=rank, rpn=rpn, device=device, group=group,
-                               row_capacity_factor=row_capacity_factor,
-                               epilogue_push=epilogue_push)
+                               row_capacity_factor=row_capacity_factor, overlap=overlap,
+                               chunks=chunks)
         if world > MAX_WORLD:
             raise ValueError(f"world={world} exceeds the arena limit {MAX_WORLD}")
         if cfg.n_experts % world or world % rpn:
@@ -108,28 +152,37 @@ class FusedEPContext:
                                    int(row_capacity_factor * tokens * self.k))
                                + self.epr * (SEG_ALIGN - 1), 128)
         self.epoch = 0
-        if epilogue_push is None:
-            epilogue_push = flag_bool("TERRACE_EP_EPILOGUE_PUSH")
-        self.epilogue_push = bool(epilogue_push)
-        # two-hop return leg: the representative stores its reduced rows into the origin's section
-        # instead of the origin reading them remotely (off by default; not yet run on a GPU)
-        self.push_back = flag_bool("TERRACE_EP_PUSH_BACK")
+        self.overlap = bool(overlap)
+        self.chunks = chunk_ranges(self.epr, chunks if self.overlap else 1)
         self.ret_slots = tokens * self.k
         H = hidden
-        sizes = [
-            world * self.E * 4,                      # counts_all
-            FK_NUM * MAX_WORLD * 4,                  # flags
-            self.cap_rows * H * 2,                   # xin
-            self.cap_rows * H * 2,                   # yout
-            self.cap_rows * H * 2,                   # dout
-            self.cap_rows * H * 2,                   # dxs
-        ]
+        row = H * 2
         arows = self.n_nodes * tokens if self.two_hop_ok else 1
-        sizes += [arows * H * 2, arows * 3 * self.q * 4, arows * H * 2, arows * H * 2,
-                  arows * H * 2, arows * self.q * 4]
-        if self.epilogue_push:      # return slots (forward, backward) and the owners' row map
-            sizes += [self.ret_slots * H * 2, self.ret_slots * H * 2, self.cap_rows * 4]
-        self.offsets, self.guards, self.nbytes = arena_layout(sizes)
+        self.arows = arows
+        self.ret2_slots = arows * self.q
+        # with the overlap schedule the second GEMM stores into return slots, so the owner-side
+        # output sections are never touched
+        out_rows = 1 if self.overlap else self.cap_rows
+        sizes = {
+            "counts_all": world * self.E * 4, "flags": FK_NUM * MAX_WORLD * 4,
+            "xin": self.cap_rows * row, "yout": out_rows * row, "dout": self.cap_rows * row,
+            "dxs": out_rows * row, "ha_rows": arows * row, "ha_hdr": arows * 3 * self.q * 4,
+            "red": arows * row, "hb_rows": arows * row, "dred": arows * row,
+            "dgate": arows * self.q * 4,
+        }
+        if self.overlap:
+            sizes.update({"ret": self.ret_slots * row, "dret": self.ret_slots * row,
+                          "rowmap": self.cap_rows * 4,
+                          "ret2": (self.ret2_slots if self.two_hop_ok else 1) * row,
+                          "dret2": (self.ret2_slots if self.two_hop_ok else 1) * row})
+        names = list(sizes)
+        assert tuple(names[:12]) == _BASE_SECTIONS
+        offsets, self.guards, self.nbytes = arena_layout([sizes[n] for n in names])
+        self.off = dict(zip(names, offsets))
+        self.offsets = offsets
+        self._rows = {"xin": self.cap_rows, "yout": out_rows, "dout": self.cap_rows,
+                      "dxs": out_rows, "ha_rows": arows, "red": arows, "hb_rows": arows,
+                      "dred": arows}
         lib = torch.ops.terrace
         dev_index = self.device.index if self.device.index is not None else torch.cuda.current_device()
         self.buf = lib.symm_alloc(self.nbytes, dev_index)
@@ -151,23 +204,29 @@ class FusedEPContext:
                 self.peer_ptrs.append(p)
         geom = [world, rank, self.E, self.epr, rpn, self.n_nodes, tokens, self.k, self.M, self.q,
                 H, self.cap_rows]
-        self.arena = lib.symm_make_arena(self.peer_ptrs, self.offsets[:12], geom)
-        if self.epilogue_push:
-            self.off_ret, self.off_dret, self.off_rowmap = self.offsets[12:15]
-            self.ret_base = torch.tensor([p + self.off_ret for p in self.peer_ptrs],
-                                         dtype=torch.int64, device=self.device)
-            self.dret_base = torch.tensor([p + self.off_dret for p in self.peer_ptrs],
-                                          dtype=torch.int64, device=self.device)
-            self.row_map = self.buf[self.off_rowmap: self.off_rowmap + self.cap_rows * 4].view(
-                torch.int32)
+        self.arena = lib.symm_make_arena(self.peer_ptrs, offsets[:12], geom)
+        self.row_map = None
+        if self.overlap:
+            def bases(name):
+                return torch.tensor([p + self.off[name] for p in self.peer_ptrs],
+                                    dtype=torch.int64, device=self.device)
+            self.ret_base, self.dret_base = bases("ret"), bases("dret")
+            self.ret2_base, self.dret2_base = bases("ret2"), bases("dret2")
+            o = self.off["rowmap"]
+            self.row_map = self.buf[o: o + self.cap_rows * 4].view(torch.int32)
         self.done = torch.zeros(8, dtype=torch.int32, device=self.device)
         self._dev_index = dev_index
+        self.side = torch.cuda.Stream(device=self.device) if self.overlap else None
+        self._events = [torch.cuda.Event() for _ in range(MAX_CHUNKS)] if self.overlap else []
+        self._inflight = None       # weak reference to the autograd context of a forward whose
+        #                             backward has not run yet
         dist.barrier(group=group)
 
     # views of this rank's own sections
     def section(self, sel: int) -> torch.Tensor:
-        off = self.offsets[2 + sel] if sel < 4 else self.offsets[{4: 6, 5: 8, 6: 9, 7: 10}[sel]]
-        rows = self.cap_rows if sel < 4 else self.n_nodes * self.tokens
+        name = _SEL_NAME[sel]
+        rows = self._rows[name]
+        off = self.off[name]
         n = rows * self.hidden * 2
         return self.buf[off: off + n].view(torch.bfloat16).view(rows, self.hidden)
 
@@ -181,6 +240,27 @@ class FusedEPContext:
         if mode == "one_hop":
             return 0, self.world
         return (self.rank // self.rpn) * self.rpn, self.rpn
+
+    # ---- one outstanding forward -----------------------------------------------------------
+    def claim(self, actx) -> None:
+        """Called by a forward that will be backwarded: refuses when an earlier forward of this
+        context still waits for its backward (its rows in the arena would be overwritten)."""
+        self.check_free()
+        self._inflight = weakref.ref(actx)
+
+    def check_free(self) -> None:
+        held = self._inflight() if self._inflight is not None else None
+        if held is not None and not getattr(held, "_terrace_done", False):
+            raise RuntimeError(
+                "this FusedEPContext still holds the rows of a forward whose backward has not "
+                "run: one forward may be outstanding per context (use one context per call "
+                "site, or run the earlier backward first)")
+        self._inflight = None
+
+    def release(self, actx) -> None:
+        actx._terrace_done = True
+        if self._inflight is not None and self._inflight() is actx:
+            self._inflight = None
 
     def close(self):
         lib = torch.ops.terrace
@@ -207,10 +287,15 @@ class FusedEPContext:
                       world=args["world"], rank=args["rank"], rpn=args["rpn"],
                       device=args["device"], group=args["group"],
                       row_capacity_factor=args["row_capacity_factor"],
-                      epilogue_push=args["epilogue_push"])
+                      overlap=args["overlap"], chunks=len(self.chunks))
 
     def take_status(self) -> int:
         return int(torch.ops.terrace.symm_take_status(self._dev_index))
+
+    def status_tensor(self) -> torch.Tensor:
+        """The device status word (int32 [1]) without a synchronisation: non-zero once a kernel of
+        this device skipped a row (arena overflow), gave up a wait, ...  For a deferred read."""
+        return torch.ops.terrace.symm_status_tensor(self._dev_index)
 
     def check_canaries(self) -> list:
         """Indices of the arena sections whose trailing canary bytes were overwritten (by this
@@ -235,85 +320,168 @@ def _plan(ctx: FusedEPContext, idx, gates, mode: str, ep: int):
                 seg_count=seg_count, rows_a=rows_a)
 
 
-def _dispatch(ctx, p, x, mode: str, ep: int):
-    """Forward dispatch: rows of ``x`` land in the owners' ``xin`` sections."""
+def _push_launches(ctx, chunked: bool):
+    """``[(i, n, lo, hi)]``: the push launches of one dispatch."""
+    ranges = ctx.chunks if chunked else [(0, ctx.epr)]
+    return [(i, len(ranges), lo, hi) for i, (lo, hi) in enumerate(ranges)]
+
+
+def _dispatch(ctx, p, x, mode: str, ep: int, *, backward: bool = False, chunked: bool = False,
+              events=None):
+    """Dispatch of ``x`` (forward: token rows into the owners' ``xin``; backward: gate-scaled
+    gradient rows into the owners' ``dout`` plus the gate gradients) on the current stream.
+    With ``chunked`` it is issued as one launch per range of local experts, and ``events[i]`` is
+    recorded after launch ``i``.  Returns the gate gradients (backward, one-hop) or None."""
     lib = _lib()
-    if mode == "one_hop" and ctx.epilogue_push:
-        pos, _ = lib.ep_push_ret(ctx.arena, x, p["es"], p["rank_local"], p["chunk_hist"],
-                                 p["my_base"], None, False, XIN, 0, False, FK_DATA, ep,
-                                 ctx.done[0:1], ctx.off_rowmap, ctx.ret_slots)
-        p["pos"], p["rowa"] = pos, None
-    elif mode == "one_hop":
-        pos, _ = lib.ep_push(ctx.arena, x, p["es"], p["rank_local"], p["chunk_hist"],
-                             p["my_base"], None, False, XIN, XIN, FK_DATA, ep, ctx.done[0:1])
-        p["pos"], p["rowa"] = pos, None
+    ov = ctx.overlap
+    T = x.shape[0]
+    data_kind = FK_B_DATA if backward else FK_DATA
+    dst_off = ctx.off["dout" if backward else "xin"]
+    launches = _push_launches(ctx, chunked)
+    dgs = None
+
+    def mark(i):
+        if events:
+            events[i].record(torch.cuda.current_stream(ctx.device))
+        LIVE["chunk_pushes"] += 1
+
+    if mode == "one_hop":
+        if backward:
+            pos = p["pos"]
+            dgs = torch.empty(T, ctx.k, dtype=torch.float32, device=x.device)
+            dot_off = ctx.off["ret"] if ov else ctx.off["yout"]
+        else:
+            pos = torch.empty(T, ctx.k, dtype=torch.int32, device=x.device)
+            dot_off = 0
+        for i, n, lo, hi in launches:
+            lib.ep_push(ctx.arena, x, p["es"], p["rank_local"], p["chunk_hist"], p["my_base"],
+                        p["gs"] if backward else None, pos, dgs, dst_off, dot_off, ov and backward,
+                        data_kind, flag_value(ep, i, n), lo, hi, ctx.done[0:1],
+                        ctx.off["rowmap"] if (ov and not backward) else -1, ctx.ret_slots)
+            mark(i)
+        if not backward:
+            p["pos"], p["rowa"] = pos, None
+        return dgs
+    # two-hop: Hop A in one launch, Hop B forwarded by the representative chunk by chunk
+    if backward:
+        lib.hopa_push(ctx.arena, x, p["es"], p["gs"], p["rank_local"], p["chunk_hist"],
+                      p["my_base"], p["ranka"], p["chunka"], p["rowa"], HB_ROWS, False,
+                      FK_B_HOPA, ep, ctx.done[0:1])
     else:
         pos, rowa = lib.hopa_push(ctx.arena, x, p["es"], p["gs"], p["rank_local"],
                                   p["chunk_hist"], p["my_base"], p["ranka"], p["chunka"], None,
                                   HA_ROWS, True, FK_HOPA, ep, ctx.done[0:1])
-        lib.arrival_push(ctx.arena, p["rows_a"], HA_ROWS, XIN, XIN, False, False, FK_HOPA,
-                         FK_DATA, -1, ep, ctx.done[1:2])
         p["pos"], p["rowa"] = pos, rowa
+    for i, n, lo, hi in launches:
+        last = i == n - 1
+        if backward:
+            lib.arrival_push(ctx.arena, p["rows_a"], HB_ROWS, dst_off,
+                             ctx.off["ret2"] if ov else ctx.off["yout"], ov, True, True,
+                             FK_B_HOPA, data_kind, FK_B_DG if last else -1, ep,
+                             flag_value(ep, i, n), lo, hi, ctx.done[1:2], -1)
+        else:
+            lib.arrival_push(ctx.arena, p["rows_a"], HA_ROWS, dst_off, 0, False, False, False,
+                             FK_HOPA, data_kind, -1, ep, flag_value(ep, i, n), lo, hi,
+                             ctx.done[1:2], ctx.off["rowmap"] if ov else -1)
+        mark(i)
+    return None
+
+
+def _dispatch_side(ctx, p, x, mode: str, ep: int, *, backward: bool):
+    """The chunked dispatch on the context's side stream; returns ``(dgs, events)``.  The caller
+    makes the current stream wait for ``events[i]`` before it launches the GEMM of chunk ``i``.
+    A context without a side stream issues the same launches in line (``events`` is None)."""
+    if ctx.side is None:
+        return _dispatch(ctx, p, x, mode, ep, backward=backward, chunked=True), None
+    cur = torch.cuda.current_stream(ctx.device)
+    ctx.side.wait_stream(cur)
+    with torch.cuda.stream(ctx.side):
+        dgs = _dispatch(ctx, p, x, mode, ep, backward=backward, chunked=True, events=ctx._events)
+    # tensors allocated while the side stream was current are consumed on the caller's stream
+    for t in (dgs, p.get("pos"), p.get("rowa")):
+        if t is not None:
+            t.record_stream(cur)
+    return dgs, ctx._events
 
 
 def _signal_out(ctx, mode: str, kind: int, ep: int, like, wait_kind: int = -1):
     lib = _lib()
     first, n = ctx.owner_wait_range(mode)
-    lib.ep_signal(ctx.arena, kind, first, n, 1, ctx.rank, ep, wait_kind, first, n, like)
+    lib.ep_signal(ctx.arena, kind, first, n, 1, ctx.rank, ep, wait_kind, first, n,
+                  flag_value(ep, 0, 1), like)
 
 
 def _combine(ctx, p, mode: str, ep: int, *, src: int, use_gate: bool, backward: bool,
              pull: bool = False):
-    """``pull`` forces the remote-read combine even on a context with ``epilogue_push`` (the
-    echo measurement has no GEMM whose epilogue could have delivered the rows)."""
+    """``pull`` forces the remote-read combine even on an overlap context (the echo measurement
+    has no GEMM whose epilogue could have delivered the rows)."""
     lib = _lib()
     out_kind = FK_B_OUT if backward else FK_OUT
-    if mode == "one_hop" and ctx.epilogue_push and not pull:
-        return lib.ep_combine_local(ctx.arena, p["pos"], p["es"], p["gs"] if use_gate else None,
-                                    ctx.off_dret if backward else ctx.off_ret, ctx.ret_slots,
-                                    ctx.cfg.group_size, out_kind, ep)
+    local = ctx.overlap and not pull
     if mode == "one_hop":
+        if local:
+            return lib.ep_pull_combine(ctx.arena, p["pos"], p["es"], p["gs"] if use_gate else None,
+                                       ctx.off["dret" if backward else "ret"], ctx.cfg.group_size,
+                                       out_kind, ep, ctx.ret_slots)
         return lib.ep_pull_combine(ctx.arena, p["pos"], p["es"], p["gs"] if use_gate else None,
-                                   src, ctx.cfg.group_size, out_kind, ep)
+                                   ctx.off[_SEL_NAME[src]], ctx.cfg.group_size, out_kind, ep, 0)
     red_sel, red_kind = (DRED, FK_B_RED) if backward else (RED, FK_RED)
-    push = bool(getattr(ctx, "push_back", False))
-    lib.arrival_combine(ctx.arena, p["rows_a"], src, red_sel, use_gate, out_kind, red_kind, ep,
-                        ctx.done[2:3], push)
-    if push:
-        LIVE["push_back"] += 1
-    return lib.origin_combine(ctx.arena, p["es"], p["rowa"], red_sel, red_kind, ep, push)
+    src_off = ctx.off["dret2" if backward else "ret2"] if local else ctx.off[_SEL_NAME[src]]
+    lib.arrival_combine(ctx.arena, p["rows_a"], src_off, red_sel, use_gate, out_kind, red_kind, ep,
+                        ctx.done[2:3], local, local)
+    return lib.origin_combine(ctx.arena, p["es"], p["rowa"], red_sel, red_kind, ep, local)
 
 
 class _FusedMoE(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x, gates, w13, w2, idx, fctx: FusedEPContext, mode: str):
         lib = _lib()
+        need = any(ctx.needs_input_grad)
+        if need:
+            fctx.claim(ctx)
+        else:
+            fctx.check_free()
         ep = fctx.next_epoch()
         xc = x.contiguous()
+        ov = fctx.overlap
         with trace.phase("ep.fwd.plan"):
             p = _plan(fctx, idx, gates, mode, ep)
         with trace.phase("ep.fwd.dispatch"):
-            _dispatch(fctx, p, xc, mode, ep)
+            if ov:
+                _, events = _dispatch_side(fctx, p, xc, mode, ep, backward=False)
+            else:
+                _dispatch(fctx, p, xc, mode, ep)
         first, n = fctx.owner_wait_range(mode)
         d = w2.shape[1]
-        xin, yout = fctx.section(XIN), fctx.section(YOUT)
+        xin = fctx.section(XIN)
         act = torch.empty(fctx.cap_rows, d, dtype=torch.bfloat16, device=x.device)
-        need = any(ctx.needs_input_grad)
         h13 = (torch.empty(fctx.cap_rows, 2 * d, dtype=torch.bfloat16, device=x.device)
                if need else None)
-        scatter = mode == "one_hop" and fctx.epilogue_push
+        w13c, w2c = w13.contiguous(), w2.contiguous()
+        ss, sc = p["seg_start"], p["seg_count"]
         with trace.phase("ep.fwd.experts"):
             if need:      # the weight gradient reads the padding rows of xin: keep them zero
-                lib.zero_pad_rows(xin, p["seg_start"], p["seg_count"], SEG_ALIGN)
-            lib.grouped_gemm_ex(xin, w13.contiguous(), act, h13, p["seg_start"], p["seg_count"],
-                                0, 1, fctx.arena, FK_DATA, first, n, ep, SEG_ALIGN)
-            if scatter:     # GEMM 2 stores every output row into its origin's return slot
-                lib.grouped_gemm_scatter(act, w2.contiguous(), p["seg_start"], p["seg_count"], 0,
-                                         fctx.row_map, fctx.ret_base, fctx.ret_slots)
-                LIVE["epilogue_push_fwd"] += 1
+                lib.zero_pad_rows(xin, ss, sc, SEG_ALIGN)
+            if ov:
+                cur = torch.cuda.current_stream(fctx.device) if events else None
+                base, slots = ((fctx.ret_base, fctx.ret_slots) if mode == "one_hop"
+                               else (fctx.ret2_base, fctx.ret2_slots))
+                nch = len(fctx.chunks)
+                for i, (lo, hi) in enumerate(fctx.chunks):
+                    if cur is not None:
+                        cur.wait_event(events[i])
+                    lib.grouped_gemm_ex(xin, w13c[lo:hi], act, h13, ss[lo:hi], sc[lo:hi], 0, 1,
+                                        fctx.arena, FK_DATA, first, n, flag_value(ep, i, nch),
+                                        SEG_ALIGN)
+                    # GEMM 2 stores every output row into its return slot (origin / representative)
+                    lib.grouped_gemm_scatter(act, w2c[lo:hi], ss[lo:hi], sc[lo:hi], 0,
+                                             fctx.row_map, base, slots)
+                LIVE["overlap_fwd"] += 1
             else:
-                lib.grouped_gemm_ex(act, w2.contiguous(), yout, None, p["seg_start"],
-                                    p["seg_count"], 0, 0, None, 0, 0, 0, ep, SEG_ALIGN)
+                lib.grouped_gemm_ex(xin, w13c, act, h13, ss, sc, 0, 1, fctx.arena, FK_DATA, first,
+                                    n, flag_value(ep, 0, 1), SEG_ALIGN)
+                lib.grouped_gemm_ex(act, w2c, fctx.section(YOUT), None, ss, sc, 0, 0, None, 0, 0,
+                                    0, ep, SEG_ALIGN)
         with trace.phase("ep.fwd.combine"):
             _signal_out(fctx, mode, FK_OUT, ep, xc)
             y = _combine(fctx, p, mode, ep, src=YOUT, use_gate=True, backward=False)
@@ -327,47 +495,50 @@ class _FusedMoE(torch.autograd.Function):
     def backward(ctx, dy):
         lib = _lib()
         fctx, mode, ep, p = ctx.fctx, ctx.mode, ctx.ep, ctx.plan
+        if fctx.epoch != ep:
+            raise RuntimeError("the arena of this FusedEPContext was reused by a later forward: "
+                               "the rows this backward needs are gone")
         w13, w2, act, h13 = ctx.saved_tensors
         dyc = dy.contiguous()
         first, n = fctx.owner_wait_range(mode)
-        scatter = mode == "one_hop" and fctx.epilogue_push
-        tr_dispatch = trace.phase("ep.bwd.dispatch")
-        tr_dispatch.__enter__()
-        if scatter:     # the saved expert outputs sit in my own return slots
-            _, dgs = lib.ep_push_ret(fctx.arena, dyc, p["es"], p["rank_local"], p["chunk_hist"],
-                                     p["my_base"], p["gs"], True, DOUT, fctx.off_ret, True,
-                                     FK_B_DATA, ep, fctx.done[0:1], fctx.off_rowmap,
-                                     fctx.ret_slots)
-        elif mode == "one_hop":
-            _, dgs = lib.ep_push(fctx.arena, dyc, p["es"], p["rank_local"], p["chunk_hist"],
-                                 p["my_base"], p["gs"], True, DOUT, YOUT, FK_B_DATA, ep,
-                                 fctx.done[0:1])
-        else:
-            lib.hopa_push(fctx.arena, dyc, p["es"], p["gs"], p["rank_local"], p["chunk_hist"],
-                          p["my_base"], p["ranka"], p["chunka"], p["rowa"], HB_ROWS, False,
-                          FK_B_HOPA, ep, fctx.done[0:1])
-            lib.arrival_push(fctx.arena, p["rows_a"], HB_ROWS, DOUT, YOUT, True, True, FK_B_HOPA,
-                             FK_B_DATA, FK_B_DG, ep, fctx.done[1:2])
-        tr_dispatch.__exit__(None, None, None)
-        xin, dout, dxs = fctx.section(XIN), fctx.section(DOUT), fctx.section(DXS)
+        ov = fctx.overlap
+        w13c, w2c = w13.contiguous(), w2.contiguous()
+        ss, sc = p["seg_start"], p["seg_count"]
+        with trace.phase("ep.bwd.dispatch"):
+            if ov:
+                dgs, events = _dispatch_side(fctx, p, dyc, mode, ep, backward=True)
+            else:
+                dgs = _dispatch(fctx, p, dyc, mode, ep, backward=True)
+        xin, dout = fctx.section(XIN), fctx.section(DOUT)
         d = w2.shape[1]
         dact = torch.empty(fctx.cap_rows, d, dtype=torch.bfloat16, device=dy.device)
-        tr_experts = trace.phase("ep.bwd.experts")
-        tr_experts.__enter__()
-        lib.zero_pad_rows(dout, p["seg_start"], p["seg_count"], SEG_ALIGN)
-        lib.grouped_gemm_ex(dout, w2.contiguous(), dact, None, p["seg_start"], p["seg_count"], 1,
-                            0, fctx.arena, FK_B_DATA, first, n, ep, SEG_ALIGN)
-        dw2 = lib.grouped_wgrad(act, dout, p["seg_start"], p["seg_count"], 0, SEG_ALIGN)
-        dh13 = lib.swiglu_bwd(h13, dact)
-        dw13 = lib.grouped_wgrad(xin, dh13, p["seg_start"], p["seg_count"], 0, SEG_ALIGN)
-        if scatter:
-            lib.grouped_gemm_scatter(dh13, w13.contiguous(), p["seg_start"], p["seg_count"], 1,
-                                     fctx.row_map, fctx.dret_base, fctx.ret_slots)
-            LIVE["epilogue_push_bwd"] += 1
-        else:
-            lib.grouped_gemm_ex(dh13, w13.contiguous(), dxs, None, p["seg_start"],
-                                p["seg_count"], 1, 0, None, 0, 0, 0, ep, SEG_ALIGN)
-        tr_experts.__exit__(None, None, None)
+        with trace.phase("ep.bwd.experts"):
+            lib.zero_pad_rows(dout, ss, sc, SEG_ALIGN)
+            if ov:
+                cur = torch.cuda.current_stream(fctx.device) if events else None
+                dw2 = torch.empty_like(w2c)
+                nch = len(fctx.chunks)
+                for i, (lo, hi) in enumerate(fctx.chunks):
+                    if cur is not None:
+                        cur.wait_event(events[i])
+                    lib.grouped_gemm_ex(dout, w2c[lo:hi], dact, None, ss[lo:hi], sc[lo:hi], 1, 0,
+                                        fctx.arena, FK_B_DATA, first, n, flag_value(ep, i, nch),
+                                        SEG_ALIGN)
+                    lib.grouped_wgrad_out(act, dout, dw2, lo, ss[lo:hi], sc[lo:hi], 0, SEG_ALIGN)
+                dh13 = lib.swiglu_bwd(h13, dact)
+                dw13 = lib.grouped_wgrad(xin, dh13, ss, sc, 0, SEG_ALIGN)
+                base, slots = ((fctx.dret_base, fctx.ret_slots) if mode == "one_hop"
+                               else (fctx.dret2_base, fctx.ret2_slots))
+                lib.grouped_gemm_scatter(dh13, w13c, ss, sc, 1, fctx.row_map, base, slots)
+                LIVE["overlap_bwd"] += 1
+            else:
+                lib.grouped_gemm_ex(dout, w2c, dact, None, ss, sc, 1, 0, fctx.arena, FK_B_DATA,
+                                    first, n, flag_value(ep, 0, 1), SEG_ALIGN)
+                dw2 = lib.grouped_wgrad(act, dout, ss, sc, 0, SEG_ALIGN)
+                dh13 = lib.swiglu_bwd(h13, dact)
+                dw13 = lib.grouped_wgrad(xin, dh13, ss, sc, 0, SEG_ALIGN)
+                lib.grouped_gemm_ex(dh13, w13c, fctx.section(DXS), None, ss, sc, 1, 0, None, 0, 0,
+                                    0, ep, SEG_ALIGN)
         with trace.phase("ep.bwd.combine"):
             _signal_out(fctx, mode, FK_B_OUT, ep, dyc)
             dx = _combine(fctx, p, mode, ep, src=DXS, use_gate=False, backward=True)
@@ -375,6 +546,7 @@ class _FusedMoE(torch.autograd.Function):
                 dgs = lib.origin_pull_dgate(fctx.arena, p["es"], p["rowa"], FK_B_DG, ep)
         dgates = torch.zeros_like(dgs).scatter_(1, p["cols"].long(), dgs).to(ctx.gate_dtype)
         LIVE[f"{mode}_bwd"] += 1
+        fctx.release(ctx)
         return dx, dgates, dw13, dw2, None, None, None
 
 
@@ -398,7 +570,8 @@ class PipelinedFusedEP:
     """Token-sliced software pipeline over the fused transport: ``n`` independent arenas, each
     slice of the tokens runs plan -> push -> GEMMs -> combine on its own CUDA stream, so that the
     dispatch and combine of one slice overlap the expert GEMMs of another.  The kernels are the
-    unchanged ones of the unsliced path.
+    unchanged ones of the unsliced path.  (The default schedule already overlaps chunk by chunk
+    inside one arena; slicing by tokens is the alternative that needs no scattering epilogue.)
 
     Why this cannot deadlock although the GEMM kernels spin on flags: a slice's kernels wait only
     for the SAME slice's pushes of OTHER GPUs; its own push precedes them in stream order; pushes
@@ -455,6 +628,9 @@ class PipelinedFusedEP:
     def take_status(self) -> int:
         return max(c.take_status() for c in self.ctxs)
 
+    def status_tensor(self) -> torch.Tensor:
+        return self.ctxs[0].status_tensor()
+
     def check_canaries(self) -> list:
         return [(i, sec) for i, c in enumerate(self.ctxs) for sec in c.check_canaries()]
 
@@ -484,12 +660,14 @@ def run_fused(ctx, x, idx, gates, w13, w2, *, mode: str):
 @torch.no_grad()
 def fused_dispatch_combine(fctx: FusedEPContext, x, idx, gates, *, mode: str):
     """Dispatch immediately followed by combine (rows echo back unchanged, gate-weighted): the
-    communication-only measurement."""
+    communication-only measurement.  The rows come back by remote reads of the owners' input
+    sections, whatever the context's schedule (no GEMM runs whose epilogue could return them)."""
     if isinstance(fctx, PipelinedFusedEP):      # slice after slice on the caller's stream
         return torch.cat([fused_dispatch_combine(c, x[lo:hi], idx[lo:hi], gates[lo:hi], mode=mode)
                           for (lo, hi), c in zip(fctx.bounds(x.shape[0]), fctx.ctxs)], dim=0)
     if mode == "two_hop" and not fctx.two_hop_ok:
         mode = "one_hop"
+    fctx.check_free()
     ep = fctx.next_epoch()
     p = _plan(fctx, idx, gates, mode, ep)
     _dispatch(fctx, p, x.contiguous(), mode, ep)

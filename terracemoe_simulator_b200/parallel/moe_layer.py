@@ -80,7 +80,9 @@ class MoELayerRunner:
     arena of the fused transport)."""
 
     def __init__(self, cfg: TRouteConfig, hidden: int, d_expert: int, tokens: int, *, world: int,
-                 rank: int, rpn: int, mode: str, fused: bool, device):
+                 rank: int, rpn: int, mode: str, fused: bool, device, overlap=None):
+        """``overlap``: schedule of the fused transport (None = ``TERRACE_EP_OVERLAP``, default
+        on; False = the remote-read schedule, the A/B arm)."""
         if mode not in EP_MODES:
             raise ValueError(f"unknown EP mode {mode!r}; expected one of {EP_MODES}")
         self.cfg, self.world, self.rank, self.rpn = cfg, world, rank, rpn
@@ -94,7 +96,7 @@ class MoELayerRunner:
         if self.fused:
             from . import fused as fz
             self.ctx = fz.make_context(cfg, hidden, d_expert, tokens, world=world, rank=rank,
-                                       rpn=rpn, device=device)
+                                       rpn=rpn, device=device, overlap=overlap)
 
     def __call__(self, x, router_w, w13, w2):
         idx, gates, _gidx, _load = _route(x, router_w, self.bias, self.cfg)
@@ -146,23 +148,17 @@ class MoELayerRunner:
         if self.fused:
             from . import fused as fz
             return lambda: fz.fused_dispatch_combine(self.ctx, x, idx, gates, mode=self.mode)
-        identity_w13 = identity_w2 = None  # NCCL arm: time the exchange with the GEMMs skipped
-        from . import ep as _ep
-        from . import ta2a as _ta
+        # torch.distributed arm: the same exchange with the expert compute replaced by identity
+
+        def echo(rows, *_):
+            return rows
 
         def fn():
-            saved = _ep.swiglu_experts
-            try:
-                _ep.swiglu_experts = lambda rows, *_: rows
-                _ta.swiglu_experts = _ep.swiglu_experts
-                if self.mode == "one_hop":
-                    return ep_moe_forward(x, idx, gates, identity_w13, identity_w2, self.world, E,
-                                          rpn=self.rpn)
-                return ta2a_moe_forward(x, idx, gates, identity_w13, identity_w2, self.world, E,
-                                        rpn=self.rpn, groups_m=cfg.top_groups)
-            finally:
-                _ep.swiglu_experts = saved
-                _ta.swiglu_experts = saved
+            if self.mode == "one_hop":
+                return ep_moe_forward(x, idx, gates, None, None, self.world, E, rpn=self.rpn,
+                                      experts_fn=echo)
+            return ta2a_moe_forward(x, idx, gates, None, None, self.world, E, rpn=self.rpn,
+                                    groups_m=cfg.top_groups, experts_fn=echo)
         return fn
 
 
@@ -172,7 +168,7 @@ class EPTerracedMoE(nn.Module):
     def __init__(self, hidden: int, d_expert: int, d_shared: int, cfg: TRouteConfig,
                  n_shared: int = 1, bias_gamma: float = 1e-3, *, mode: str = "one_hop",
                  rpn: int = 1, fused: bool = False, capacity_factor: float | None = None,
-                 tokens_hint: int | None = None):
+                 tokens_hint: int | None = None, row_capacity_factor: float = 2.0):
         super().__init__()
         if mode not in EP_MODES:
             raise ValueError(f"unknown EP mode {mode!r}; expected one of {EP_MODES}")
@@ -186,8 +182,12 @@ class EPTerracedMoE(nn.Module):
             raise ValueError(f"n_experts={cfg.n_experts} not divisible by world={self.world}")
         epr = cfg.n_experts // self.world
         self.hidden, self.d_expert, self.tokens_hint = hidden, d_expert, tokens_hint
+        # rows an expert owner's arena holds, as a multiple of tokens * top_k: 1.0 is perfectly
+        # balanced routing, `world` the worst case.  A step that exceeds it skips the overflowing
+        # rows and raises the device status word (stats["ep_status"], `check_status`).
+        self.row_capacity_factor = row_capacity_factor
         self.router = Router(hidden, cfg)
-        self.shared = SwiGLU(hidden, n_shared * d_shared) if n_shared * d_shared > 0 else None
+        self.shared = SwiGLU(hidden, n_shared * d_shared)
         self.w13 = nn.Parameter(torch.empty(epr, hidden, 2 * d_expert))
         self.w2 = nn.Parameter(torch.empty(epr, d_expert, hidden))
         nn.init.normal_(self.w13, std=hidden ** -0.5)
@@ -197,14 +197,51 @@ class EPTerracedMoE(nn.Module):
             init_ta2a_groups(self.world, rpn)
 
     def _context(self, tokens: int, device):
+        """The fused transport's arena, created at the first call for the largest token count
+        of any rank (one host synchronisation, once).  Growing it later is a collective decision:
+        every rank calls :meth:`reserve` between steps."""
         if not self.fused or self.world == 1:
             return None
-        if self._ctx is None or self._ctx.tokens < tokens:
-            from . import fused as fz
-            self._ctx = fz.make_context(self.cfg, self.hidden, self.d_expert, tokens,
-                                        world=self.world, rank=self.rank, rpn=self.rpn,
-                                        device=device)
+        if self._ctx is None:
+            want = torch.tensor([max(tokens, self.tokens_hint or 0)], device=device)
+            dist.all_reduce(want, op=dist.ReduceOp.MAX)
+            self._build_context(int(want.item()), device)
+        elif self._ctx.tokens < tokens:
+            raise RuntimeError(
+                f"{tokens} tokens exceed the arena sized for {self._ctx.tokens}: call "
+                "reserve(tokens) on every rank between steps (or pass tokens_hint)")
         return self._ctx
+
+    def _build_context(self, tokens: int, device):
+        from . import fused as fz
+        self._ctx = fz.make_context(self.cfg, self.hidden, self.d_expert, tokens,
+                                    world=self.world, rank=self.rank, rpn=self.rpn, device=device,
+                                    row_capacity_factor=self.row_capacity_factor)
+
+    def reserve(self, tokens: int, device=None) -> None:
+        """Collective: size the arena for ``tokens`` tokens per rank.  The old arena's peer
+        mappings are closed and, after a barrier (no rank frees memory a peer still maps), a new
+        one is allocated and exchanged."""
+        if not self.fused or self.world == 1:
+            return
+        device = device or self.w13.device
+        if self._ctx is not None:
+            if self._ctx.tokens >= tokens:
+                return
+            torch.cuda.synchronize(device)
+            self._ctx.close()
+            dist.barrier()
+            self._ctx = None
+        self._build_context(tokens, device)
+
+    def check_status(self) -> int:
+        """Read and clear the device status word (one host synchronisation); raises when a kernel
+        reported a problem, e.g. routed rows beyond ``row_capacity_factor``."""
+        code = ops.take_status(self.w13.device.index) if self.w13.is_cuda else 0
+        if code:
+            raise RuntimeError(f"expert-parallel kernels reported status {code} "
+                               "(5 = a row fell outside its buffer: raise row_capacity_factor)")
+        return code
 
     def forward(self, x: torch.Tensor):
         lead = x.shape[:-1]
@@ -227,7 +264,7 @@ class EPTerracedMoE(nn.Module):
         y = routed_experts(x, idx, gates_used, self.w13, self.w2, self.cfg, mode=self.mode,
                            world=self.world, rpn=self.rpn, fused=self.fused,
                            ctx=self._context(x.shape[0], x.device))
-        if self.shared is not None:
+        if self.shared.w2.in_features > 0:
             y = y + self.shared(x)
         if self.training:
             total = load.detach().clone()
@@ -235,4 +272,6 @@ class EPTerracedMoE(nn.Module):
                 dist.all_reduce(total)
             update_bias_(self.router.bias, total, self.bias_gamma)
         stats = {"expert_load": load, "group_idx": gidx, "gates": gates, "expert_idx": idx}
+        if self._ctx is not None:       # device word, no synchronisation: read it a few steps late
+            stats["ep_status"] = self._ctx.status_tensor()
         return y.reshape(*lead, -1), stats

@@ -125,7 +125,8 @@ class _RowGather(torch.autograd.Function):
 
 
 def ta2a_moe_forward(x_local, expert_idx, gates, w13_shard, w2_shard, world: int, n_experts: int,
-                     rpn: int = 8, groups_m: int | None = None, *, canonical: bool = True):
+                     rpn: int = 8, groups_m: int | None = None, *, canonical: bool = True,
+                     experts_fn=None):
     """Routed-expert output for this rank's tokens under two-hop EP.
 
     ``groups_m=M`` declares equal-quota routing (exactly ``k/M`` picks in each of M groups per
@@ -135,7 +136,7 @@ def ta2a_moe_forward(x_local, expert_idx, gates, w13_shard, w2_shard, world: int
     n_nodes = world // rpn
     if n_nodes < 2:
         return ep_moe_forward(x_local, expert_idx, gates, w13_shard, w2_shard, world, n_experts,
-                              rpn=rpn, canonical=canonical)
+                              rpn=rpn, canonical=canonical, experts_fn=experts_fn)
     CALLS["two_hop"] += 1
     intra, _inter = get_ta2a_groups(world, rpn)
     rank = dist.get_rank()
@@ -204,7 +205,7 @@ def ta2a_moe_forward(x_local, expert_idx, gates, w13_shard, w2_shard, world: int
     else:
         order = torch.argsort(exp_j, stable=True)
     tokens_per_expert = fixed_hist(exp_j, epr)
-    ye = swiglu_experts(node_rx[order], w13_shard, w2_shard, tokens_per_expert)
+    ye = (experts_fn or swiglu_experts)(node_rx[order], w13_shard, w2_shard, tokens_per_expert)
     unsort = torch.empty_like(order)
     unsort[order] = torch.arange(order.numel(), device=dev)
 

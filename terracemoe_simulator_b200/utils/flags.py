@@ -2,7 +2,7 @@
 "off" (the rule of the reference's flag system: new capability defaults off, unknown values
 raise; ``terrace/ta2a_pack.py:114-143``).
 
-    flag_bool("TERRACE_EP_PUSH_BACK")             -> False unless set to 1 / on / true / yes
+    flag_bool("TERRACE_EP_OVERLAP", True)         -> True unless set to 0 / off / false / no
     flag_choice("TERRACE_ATTENTION", ("native", "sdpa"), "native")
     check_native_flags()                           -> validates the switches the C++ side reads
 """
@@ -53,4 +53,3 @@ def check_native_flags() -> None:
     """The switches that the native library reads with ``getenv``; validated here, once, when the
     library is loaded, because C++ has nobody to raise to."""
     flag_choice("TERRACE_GEMM_PAIR", ("0", "1", "auto"), "auto")
-    flag_choice("TERRACE_GEMM_SWAP", ("0", "1"), "0")

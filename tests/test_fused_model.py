@@ -189,8 +189,8 @@ class _RecorderLib:
             T, k, H = self.T, self.k, self.H
             if name in ("ep_plan_pass1",):
                 T = a[0].shape[0]
-            elif name in ("ep_push", "ep_push_ret", "hopa_push", "hopa_rank", "ep_pull_combine",
-                          "ep_combine_local", "origin_combine", "origin_pull_dgate"):
+            elif name in ("hopa_push", "hopa_rank", "ep_pull_combine", "origin_combine",
+                          "origin_pull_dgate"):
                 T = a[1].shape[0]                      # x, es or pos: one row per token
             i32 = dict(dtype=torch.int32)
             if name == "ep_plan_pass1":
@@ -199,15 +199,13 @@ class _RecorderLib:
             if name == "ep_plan":
                 return (torch.zeros(16, **i32), torch.zeros(self.epr, **i32),
                         torch.zeros(self.epr, **i32), torch.zeros(1, **i32))
-            if name in ("ep_push", "ep_push_ret"):
-                return torch.zeros(T, k, **i32), torch.zeros(T, k)
             if name == "hopa_rank":
                 return torch.zeros(T, 2, **i32), torch.zeros(128, 2, **i32)
             if name == "hopa_push":
                 return torch.zeros(T, k, **i32), torch.zeros(T, 2, **i32)
             if name == "origin_pull_dgate":
                 return torch.zeros(T, k)
-            if name in ("ep_pull_combine", "ep_combine_local", "origin_combine"):
+            if name in ("ep_pull_combine", "origin_combine"):
                 return torch.zeros(T, H, dtype=torch.bfloat16)
             if name == "grouped_wgrad":
                 return torch.zeros(self.epr, a[0].shape[1], a[1].shape[1], dtype=torch.bfloat16)
@@ -217,9 +215,28 @@ class _RecorderLib:
         return op
 
 
-@pytest.mark.parametrize("push", [False, True])
-def test_fused_orchestration_launch_sequence(monkeypatch, push):
-    """Which ops one fused one-hop step issues, with and without the scattering epilogue."""
+def _fake_context(fz, *, T, k, H, d, epr, cap, world, n_nodes, two_hop, overlap, chunks=2):
+    """A FusedEPContext with every attribute the orchestration reads and no arena behind it."""
+    c = object.__new__(fz.FusedEPContext)
+    c.cfg = TRouteConfig(16, 2, 4, 2)
+    c.world, c.rank, c.rpn, c.tokens, c.cap_rows, c.epoch = world, 0, 1, T, cap, 0
+    c.arena, c.done = torch.zeros(1, dtype=torch.uint8), torch.zeros(8, dtype=torch.int32)
+    c.two_hop_ok, c.overlap, c.ret_slots, c.ret2_slots = two_hop, overlap, T * k, n_nodes * T * 2
+    c.E, c.epr, c.k, c.M, c.q, c.hidden, c.d_expert = 16, epr, k, 2, 2, H, d
+    c.n_nodes, c.device = n_nodes, torch.device("cpu")
+    c.chunks = fz.chunk_ranges(epr, chunks if overlap else 1)
+    names = list(fz._BASE_SECTIONS) + ["ret", "dret", "rowmap", "ret2", "dret2"]
+    c.off = {n: 256 * i for i, n in enumerate(names)}
+    c.ret_base = c.dret_base = c.ret2_base = c.dret2_base = torch.zeros(world, dtype=torch.int64)
+    c.row_map = torch.zeros(cap, dtype=torch.int32)
+    c.side, c._events, c._inflight = None, [], None
+    return c
+
+
+@pytest.mark.parametrize("overlap", [False, True])
+def test_fused_orchestration_launch_sequence(monkeypatch, overlap):
+    """Which ops one fused one-hop step issues: the remote-read schedule, and the overlap
+    schedule (two chunks of experts, scattering epilogues, local combine)."""
     from terracemoe_simulator_b200.parallel import fused as fz
     T, k, H, d, epr, cap = 8, 4, 32, 16, 16, 128
     rec = _RecorderLib(T, k, H, epr, cap)
@@ -229,16 +246,8 @@ def test_fused_orchestration_launch_sequence(monkeypatch, push):
     rec.check_schema = ops.status().loaded       # the real schemas, when the library is built
     assert rec.check_schema or not os.path.isfile(ops.status().lib or "")
     monkeypatch.setattr(fz, "_lib", lambda: rec)
-    fctx = object.__new__(fz.FusedEPContext)
-    fctx.cfg = TRouteConfig(16, 2, 4, 2)
-    fctx.world, fctx.rank, fctx.rpn, fctx.tokens, fctx.cap_rows, fctx.epoch = 1, 0, 1, T, cap, 0
-    fctx.arena, fctx.done = torch.zeros(1, dtype=torch.uint8), torch.zeros(8, dtype=torch.int32)
-    fctx.two_hop_ok, fctx.epilogue_push, fctx.ret_slots = False, push, T * k
-    fctx.E, fctx.epr, fctx.k, fctx.M, fctx.q, fctx.hidden, fctx.d_expert = 16, epr, k, 2, 2, H, d
-    fctx.n_nodes, fctx.device = 1, torch.device("cpu")
-    fctx.off_ret, fctx.off_dret, fctx.off_rowmap = 0, 256, 512
-    fctx.ret_base = fctx.dret_base = torch.zeros(1, dtype=torch.int64)
-    fctx.row_map = torch.zeros(cap, dtype=torch.int32)
+    fctx = _fake_context(fz, T=T, k=k, H=H, d=d, epr=epr, cap=cap, world=1, n_nodes=1,
+                         two_hop=False, overlap=overlap)
     monkeypatch.setattr(fz.FusedEPContext, "section",
                         lambda self, sel: torch.zeros(cap, H, dtype=torch.bfloat16))
     x = torch.zeros(T, H, dtype=torch.bfloat16, requires_grad=True)
@@ -249,14 +258,21 @@ def test_fused_orchestration_launch_sequence(monkeypatch, push):
     y = fz.fused_moe_forward(fctx, x, idx, gates, w13, w2, mode="one_hop")
     fwd = list(rec.calls)
     rec.calls.clear()
+    # a second forward while the first waits for its backward would overwrite the arena rows
+    with pytest.raises(RuntimeError, match="one forward may be outstanding"):
+        fz.fused_moe_forward(fctx, x, idx, gates, w13, w2, mode="one_hop")
+    with pytest.raises(RuntimeError, match="one forward may be outstanding"):
+        fz.fused_dispatch_combine(fctx, x.detach(), idx, gates.detach(), mode="one_hop")
+    assert rec.calls == []
     y.backward(torch.zeros_like(y))
     bwd = list(rec.calls)
-    if push:
-        assert fwd == ["ep_plan_pass1", "ep_plan", "ep_push_ret", "zero_pad_rows", "grouped_gemm_ex",
-                       "grouped_gemm_scatter", "ep_signal", "ep_combine_local"]
-        assert bwd == ["ep_push_ret", "zero_pad_rows", "grouped_gemm_ex", "grouped_wgrad",
-                       "swiglu_bwd", "grouped_wgrad", "grouped_gemm_scatter", "ep_signal",
-                       "ep_combine_local"]
+    if overlap:
+        assert fwd == ["ep_plan_pass1", "ep_plan", "ep_push", "ep_push", "zero_pad_rows",
+                       "grouped_gemm_ex", "grouped_gemm_scatter", "grouped_gemm_ex",
+                       "grouped_gemm_scatter", "ep_signal", "ep_pull_combine"]
+        assert bwd == ["ep_push", "ep_push", "zero_pad_rows", "grouped_gemm_ex",
+                       "grouped_wgrad_out", "grouped_gemm_ex", "grouped_wgrad_out", "swiglu_bwd",
+                       "grouped_wgrad", "grouped_gemm_scatter", "ep_signal", "ep_pull_combine"]
     else:
         assert fwd == ["ep_plan_pass1", "ep_plan", "ep_push", "zero_pad_rows", "grouped_gemm_ex",
                        "grouped_gemm_ex", "ep_signal", "ep_pull_combine"]
@@ -265,11 +281,29 @@ def test_fused_orchestration_launch_sequence(monkeypatch, push):
                        "ep_pull_combine"]
     assert x.grad.shape == x.shape and gates.grad.shape == gates.shape
     assert w13.grad.shape == w13.shape and w2.grad.shape == w2.shape
+    # the backward released the context: the next forward goes through, and a forward whose
+    # graph is dropped without a backward releases it too
+    y2 = fz.fused_moe_forward(fctx, x, idx, gates, w13, w2, mode="one_hop")
+    del y2
+    fz.fused_moe_forward(fctx, x, idx, gates, w13, w2, mode="one_hop")
     monkeypatch.undo()
     ops.reset()
 
 
-def test_fused_two_hop_orchestration_launch_sequence(monkeypatch):
+def test_chunk_ranges_and_flag_values():
+    from terracemoe_simulator_b200.parallel import fused as fz
+    assert fz.chunk_ranges(8, 2) == [(0, 4), (4, 8)]
+    assert fz.chunk_ranges(8, 3) == [(0, 3), (3, 6), (6, 8)]
+    assert fz.chunk_ranges(2, 4) == [(0, 1), (1, 2)] and fz.chunk_ranges(5, 1) == [(0, 5)]
+    # values grow inside a step and from step to step; the last chunk always writes "all"
+    vals = [fz.flag_value(ep, i, 3) for ep in (1, 2) for i in range(3)]
+    assert vals == sorted(vals) and len(set(vals)) == len(vals)
+    assert fz.flag_value(3, 0, 1) == fz.flag_value(3, 7, 8) == 3 * fz.FLAG_STRIDE + 15
+    assert fz.flag_value(3, fz.MAX_CHUNKS - 2, fz.MAX_CHUNKS) < fz.flag_value(3, 0, 1)
+
+
+@pytest.mark.parametrize("overlap", [False, True])
+def test_fused_two_hop_orchestration_launch_sequence(monkeypatch, overlap):
     from terracemoe_simulator_b200 import ops
     from terracemoe_simulator_b200.parallel import fused as fz
     T, k, H, d, epr, cap = 8, 4, 32, 16, 8, 128
@@ -278,13 +312,8 @@ def test_fused_two_hop_orchestration_launch_sequence(monkeypatch):
     ops.reset()
     rec.check_schema = ops.status().loaded
     monkeypatch.setattr(fz, "_lib", lambda: rec)
-    fctx = object.__new__(fz.FusedEPContext)
-    fctx.cfg = TRouteConfig(16, 2, 4, 2)
-    fctx.world, fctx.rank, fctx.rpn, fctx.tokens, fctx.cap_rows, fctx.epoch = 2, 0, 1, T, cap, 0
-    fctx.arena, fctx.done = torch.zeros(1, dtype=torch.uint8), torch.zeros(8, dtype=torch.int32)
-    fctx.two_hop_ok, fctx.epilogue_push = True, False
-    fctx.E, fctx.epr, fctx.k, fctx.M, fctx.q, fctx.hidden, fctx.d_expert = 16, epr, k, 2, 2, H, d
-    fctx.n_nodes, fctx.device = 2, torch.device("cpu")
+    fctx = _fake_context(fz, T=T, k=k, H=H, d=d, epr=epr, cap=cap, world=2, n_nodes=2,
+                         two_hop=True, overlap=overlap)
     monkeypatch.setattr(fz.FusedEPContext, "section",
                         lambda self, sel: torch.zeros(cap, H, dtype=torch.bfloat16))
     x = torch.zeros(T, H, dtype=torch.bfloat16, requires_grad=True)
@@ -296,12 +325,24 @@ def test_fused_two_hop_orchestration_launch_sequence(monkeypatch):
     fwd = list(rec.calls)
     rec.calls.clear()
     y.backward(torch.zeros_like(y))
-    assert fwd == ["ep_plan_pass1", "hopa_rank", "ep_plan", "hopa_push", "arrival_push",
-                   "zero_pad_rows", "grouped_gemm_ex", "grouped_gemm_ex", "ep_signal",
-                   "arrival_combine", "origin_combine"]
-    assert rec.calls == ["hopa_push", "arrival_push", "zero_pad_rows", "grouped_gemm_ex",
-                         "grouped_wgrad", "swiglu_bwd", "grouped_wgrad", "grouped_gemm_ex",
-                         "ep_signal", "arrival_combine", "origin_combine", "origin_pull_dgate"]
+    if overlap:
+        assert fwd == ["ep_plan_pass1", "hopa_rank", "ep_plan", "hopa_push", "arrival_push",
+                       "arrival_push", "zero_pad_rows", "grouped_gemm_ex", "grouped_gemm_scatter",
+                       "grouped_gemm_ex", "grouped_gemm_scatter", "ep_signal", "arrival_combine",
+                       "origin_combine"]
+        assert rec.calls == ["hopa_push", "arrival_push", "arrival_push", "zero_pad_rows",
+                             "grouped_gemm_ex", "grouped_wgrad_out", "grouped_gemm_ex",
+                             "grouped_wgrad_out", "swiglu_bwd", "grouped_wgrad",
+                             "grouped_gemm_scatter", "ep_signal", "arrival_combine",
+                             "origin_combine", "origin_pull_dgate"]
+    else:
+        assert fwd == ["ep_plan_pass1", "hopa_rank", "ep_plan", "hopa_push", "arrival_push",
+                       "zero_pad_rows", "grouped_gemm_ex", "grouped_gemm_ex", "ep_signal",
+                       "arrival_combine", "origin_combine"]
+        assert rec.calls == ["hopa_push", "arrival_push", "zero_pad_rows", "grouped_gemm_ex",
+                             "grouped_wgrad", "swiglu_bwd", "grouped_wgrad", "grouped_gemm_ex",
+                             "ep_signal", "arrival_combine", "origin_combine",
+                             "origin_pull_dgate"]
     assert gates.grad.shape == gates.shape
     monkeypatch.undo()
     ops.reset()
@@ -383,14 +424,8 @@ def test_pipelined_context_slices_tokens_and_runs_every_slice(monkeypatch):
     monkeypatch.setattr(fz, "_lib", lambda: rec)
 
     def fake_ctx(tokens):
-        c = object.__new__(fz.FusedEPContext)
-        c.cfg = TRouteConfig(16, 2, 4, 2)
-        c.world, c.rank, c.rpn, c.tokens, c.cap_rows, c.epoch = 1, 0, 1, tokens, cap, 0
-        c.arena, c.done = torch.zeros(1, dtype=torch.uint8), torch.zeros(8, dtype=torch.int32)
-        c.two_hop_ok, c.epilogue_push, c.push_back, c.ret_slots = False, False, False, tokens * k
-        c.E, c.epr, c.k, c.M, c.q, c.hidden, c.d_expert = 16, epr, k, 2, 2, H, d
-        c.n_nodes, c.device = 1, torch.device("cpu")
-        return c
+        return _fake_context(fz, T=tokens, k=k, H=H, d=d, epr=epr, cap=cap, world=1, n_nodes=1,
+                             two_hop=False, overlap=False)
 
     monkeypatch.setattr(fz.FusedEPContext, "section",
                         lambda self, sel: torch.zeros(cap, H, dtype=torch.bfloat16))

@@ -1,5 +1,7 @@
-"""Fused peer-memory expert parallelism on real GPUs: world 1 against the local kernels
-(bitwise), world 2 one-hop against two-hop (bitwise) and against the NCCL arm (tolerance)."""
+"""Fused peer-memory expert parallelism on real GPUs.  Every multi-rank run computes the layer
+six ways and compares them: one-hop and two-hop under the overlap schedule and under the
+remote-read schedule (all four bit for bit), the ``torch.distributed`` arm, and a dense fp32
+PyTorch oracle of the same layer (forward, input, gate and weight gradients, within tolerance)."""
 import os
 
 import pytest
@@ -29,6 +31,36 @@ def _worker(rank, world, port, queue, M, rpn=1):
 CAPACITY = 1400          # rows per rank the arena is sized for; every rank's T stays below it
 
 
+def _fp32_oracle(rank, world, x0, idx, gates0, gy, w13_all, w2_all, dev):
+    """The layer as plain fp32 PyTorch over ALL ranks' tokens and ALL experts:
+    ``y[t] = sum_j gate[t, j] * (silu(x W13a) * (x W13b)) W2`` of expert ``idx[t, j]``; autograd gives
+    every gradient.  Returns this rank's slices, in the order of the fused results."""
+    import torch.distributed as dist
+    import torch.nn.functional as F
+    parts = [None] * world
+    dist.all_gather_object(parts, (x0.cpu(), idx.cpu(), gates0.cpu(), gy.cpu()))
+    lo = sum(p[0].shape[0] for p in parts[:rank])
+    hi = lo + parts[rank][0].shape[0]
+    x = torch.cat([p[0] for p in parts]).float().to(dev).requires_grad_(True)
+    ids = torch.cat([p[1] for p in parts]).to(dev)
+    gates = torch.cat([p[2] for p in parts]).float().to(dev).requires_grad_(True)
+    g_out = torch.cat([p[3] for p in parts]).float().to(dev)
+    w13 = w13_all.float().to(dev).requires_grad_(True)
+    w2 = w2_all.float().to(dev).requires_grad_(True)
+    y = torch.zeros_like(x)
+    for e in range(w13.shape[0]):
+        tok, col = (ids == e).nonzero(as_tuple=True)
+        if tok.numel() == 0:
+            continue
+        a, b = (x[tok] @ w13[e]).chunk(2, dim=-1)
+        y = y.index_add(0, tok, gates[tok, col].unsqueeze(1) * ((F.silu(a) * b) @ w2[e]))
+    y.backward(g_out)
+    epr = w13.shape[0] // world
+    own = slice(rank * epr, (rank + 1) * epr)
+    return [t.detach().float().cpu() for t in
+            (y[lo:hi], x.grad[lo:hi], gates.grad[lo:hi], w13.grad[own], w2.grad[own])]
+
+
 def _body(rank, world, queue, M, rpn):
     from terracemoe_simulator_b200 import ops
     from terracemoe_simulator_b200.parallel import fused as fz
@@ -49,29 +81,39 @@ def _body(rank, world, queue, M, rpn):
     gy = torch.randn(T, H, generator=gx).bfloat16().to(dev)
     idx, gates0, _ = t_route(aff, torch.zeros(E, device=dev), cfg)
     assert 1000 + 37 * (world - 1) <= CAPACITY
+    # the context the environment asks for (default: the overlap schedule; a token pipeline when
+    # TERRACE_EP_PIPELINE is set) and the remote-read schedule as the second arm
     fctx = fz.make_context(cfg, H, d, CAPACITY, world=world, rank=rank, rpn=rpn, device=dev)
+    pull = fz.FusedEPContext(cfg, H, d, CAPACITY, world=world, rank=rank, rpn=rpn, device=dev,
+                             overlap=False)
     res = {}
-    modes = ["one_hop", "two_hop"] if world > 1 else ["one_hop"]
-    for mode in modes + ["ref"]:
+    hops = ["one_hop", "two_hop"] if world > 1 else ["one_hop"]
+    arms = [(m, fctx, m) for m in hops] + [("pull_" + m, pull, m) for m in hops]
+    for name, ctx, mode in arms + [("ref", None, None)]:
         x = x0.clone().requires_grad_(True)
         gates = gates0.clone().requires_grad_(True)
         a = w13_all[rank * epr:(rank + 1) * epr].to(dev).requires_grad_(True)
         b = w2_all[rank * epr:(rank + 1) * epr].to(dev).requires_grad_(True)
-        if mode == "ref":
-            if world == 1:
-                y = ops.moe_experts_local(x, idx, gates, a, b, cfg.group_size)
+        for _ in range(2):              # twice: arena, flags and streams are reused
+            for t in (x, gates, a, b):
+                t.grad = None
+            if name == "ref":
+                if world == 1:
+                    y = ops.moe_experts_local(x, idx, gates, a, b, cfg.group_size)
+                else:
+                    y = ep_moe_forward(x, idx, gates, a, b, world, E, rpn=rpn)
             else:
-                y = ep_moe_forward(x, idx, gates, a, b, world, E, rpn=rpn)
-        else:
-            y = fz.run_fused(fctx, x, idx, gates, a, b, mode=mode)
-        y.backward(gy)
+                y = fz.run_fused(ctx, x, idx, gates, a, b, mode=mode)
+            y.backward(gy)
         torch.cuda.synchronize()
-        res[mode] = [t.detach().float().cpu() for t in (y, x.grad, gates.grad, a.grad, b.grad)]
-    echo = fz.fused_dispatch_combine(fctx, x0, idx, gates0, mode=modes[-1])
+        res[name] = [t.detach().float().cpu() for t in (y, x.grad, gates.grad, a.grad, b.grad)]
+    res["oracle"] = _fp32_oracle(rank, world, x0, idx, gates0, gy, w13_all, w2_all, dev)
+    echo = fz.fused_dispatch_combine(fctx, x0, idx, gates0, mode=hops[-1])
     torch.cuda.synchronize()
     status = fctx.take_status() or ops.take_status(rank)
-    if not status and fctx.check_canaries():      # a store went past the end of an arena section
-        status = 7700 + fctx.check_canaries()[0]
+    bad = fctx.check_canaries() or pull.check_canaries()
+    if not status and bad:            # a store went past the end of an arena section
+        status = 7700 + (bad[0] if isinstance(bad[0], int) else bad[0][1])
     queue.put((rank, res, echo.float().cpu(), x0.float().cpu(), status,
                dict(fz.LIVE)))
 
@@ -107,32 +149,49 @@ def _close(a, b, tol=5e-2):
     torch.testing.assert_close(a, b, rtol=tol, atol=tol * scale)
 
 
+def _check_ranks(out, world, *, pipeline: int = 1):
+    """Every rank: status 0; all fused arms bit-identical (weight gradients within rounding when
+    token slices sum partial results); fused against the NCCL arm and the fp32 oracle."""
+    hops = ["one_hop", "two_hop"] if world > 1 else ["one_hop"]
+    for rank, res, echo, x0, status, live in out:
+        assert status == 0, (rank, status)
+        for m in hops:
+            assert live[m + "_fwd"] >= 2 and live[m + "_bwd"] >= 2
+        if pipeline == 1:
+            assert live["overlap_fwd"] >= 2 * len(hops) and live["overlap_bwd"] >= 2 * len(hops)
+            assert live["chunk_pushes"] > 0
+        base = res["one_hop"]
+        for name in ["two_hop"] * (world > 1):
+            for a, b in zip(base, res[name]):
+                assert torch.equal(a, b), "one-hop and two-hop fused paths must agree bit for bit"
+        for name in ["pull_" + m for m in hops]:
+            for i, (a, b) in enumerate(zip(base, res[name])):
+                if pipeline > 1 and i >= 2:      # sums of per-slice partial results
+                    _close(a, b, 2e-2)
+                elif i == 2 and world == 1:
+                    _close(a, b, 1e-2)
+                else:
+                    assert torch.equal(a, b), f"schedules disagree on tensor {i} ({name})"
+        for i, (a, b) in enumerate(zip(base, res["ref"])):
+            if world == 1 and i != 2:
+                assert torch.equal(a, b)
+            else:
+                _close(a, b, 1e-2 if world == 1 else 5e-2)
+        for a, b in zip(base, res["oracle"]):
+            _close(a, b)
+        # echo: every token gets sum_j gate_j * x = x (gates sum to one) up to bf16 rounding
+        _close(echo, x0, 2e-2)
+
+
 def test_fused_world1_equals_local_kernels(native_ops):
-    (rank, res, echo, x0, status, live), = _run(1, 1, 29701)
-    assert status == 0
-    assert live["one_hop_fwd"] == 1 and live["one_hop_bwd"] == 1
-    for i, (a, b) in enumerate(zip(res["one_hop"], res["ref"])):
-        if i == 2:      # gate gradients: same dot products, different lane partition
-            _close(a, b, 1e-2)
-        else:
-            assert torch.equal(a, b)
-    # echo: every token gets sum_j gate_j * x = x (gates sum to one) up to bf16 rounding
-    _close(echo, x0, 2e-2)
+    _check_ranks(_run(1, 1, 29701), 1)
 
 
 @pytest.mark.parametrize("M", [2, 1])
 def test_fused_world2_one_hop_two_hop(native_ops, M):
     if torch.cuda.device_count() < 2:
         pytest.skip("needs two GPUs")
-    out = _run(2, M, 29703 + M)
-    for rank, res, echo, x0, status, live in out:
-        assert status == 0
-        assert live["two_hop_fwd"] == 1 and live["two_hop_bwd"] == 1
-        for a, b in zip(res["one_hop"], res["two_hop"]):
-            assert torch.equal(a, b), "one-hop and two-hop fused paths must agree bit for bit"
-        for a, b in zip(res["one_hop"], res["ref"]):
-            _close(a, b)
-        _close(echo, x0, 2e-2)
+    _check_ranks(_run(2, M, 29703 + M), 2)
 
 
 @pytest.mark.parametrize("world,rpn,M", [(4, 2, 2), (8, 2, 2), (8, 4, 2)])
@@ -140,15 +199,16 @@ def test_fused_groups_of_several_gpus(native_ops, world, rpn, M):
     """Logical groups of R > 1 GPUs: Hop B really crosses GPUs inside the group."""
     if torch.cuda.device_count() < world:
         pytest.skip(f"needs {world} GPUs")
-    out = _run(world, M, 29720 + world + rpn, rpn=rpn)
-    for rank, res, echo, x0, status, live in out:
-        assert status == 0
-        assert live["two_hop_fwd"] == 1 and live["two_hop_bwd"] == 1
-        for a, b in zip(res["one_hop"], res["two_hop"]):
-            assert torch.equal(a, b), "one-hop and two-hop fused paths must agree bit for bit"
-        for a, b in zip(res["one_hop"], res["ref"]):
-            _close(a, b)
-        _close(echo, x0, 2e-2)
+    _check_ranks(_run(world, M, 29720 + world + rpn, rpn=rpn), world)
+
+
+@pytest.mark.parametrize("chunks", ["1", "4"])
+def test_fused_world2_other_chunk_counts(native_ops, monkeypatch, chunks):
+    """One push launch (no overlap window) and four: same bits as two."""
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    monkeypatch.setenv("TERRACE_EP_CHUNKS", chunks)
+    _check_ranks(_run(2, 2, 29740 + int(chunks)), 2)
 
 
 def _model_worker(rank, world, port, queue):
@@ -236,61 +296,12 @@ def test_fused_positions_match_host_model(native_ops, world):
         assert all(v is True or v == 0 for v in item[1].values()), item
 
 
-# The epilogue-push variant (GEMM 2 and the last dgrad GEMM store their rows into the origins'
-# return slots) has been checked against the host model on a CPU only; it runs here on request.
-_PUSH = pytest.mark.skipif(os.environ.get("TERRACE_TEST_EPILOGUE_PUSH", "0") != "1",
-                           reason="opt-in: TERRACE_TEST_EPILOGUE_PUSH=1")
-
-
-@_PUSH
-def test_epilogue_push_world2_equals_two_hop_pull(native_ops, monkeypatch):
-    """One-hop with scattering epilogues against the two-hop pull path: bit for bit."""
-    if torch.cuda.device_count() < 2:
-        pytest.skip("needs two GPUs")
-    monkeypatch.setenv("TERRACE_EP_EPILOGUE_PUSH", "1")
-    for rank, res, echo, x0, status, live in _run(2, 2, 29783):
-        assert status == 0
-        assert live["epilogue_push_fwd"] == 1 and live["epilogue_push_bwd"] == 1
-        for a, b in zip(res["one_hop"], res["two_hop"]):
-            assert torch.equal(a, b)
-        for a, b in zip(res["one_hop"], res["ref"]):
-            _close(a, b)
-        _close(echo, x0, 2e-2)
-
-
-@pytest.mark.skipif(os.environ.get("TERRACE_TEST_PUSH_BACK", "0") != "1",
-                    reason="opt-in: TERRACE_TEST_PUSH_BACK=1 (two-hop return leg by push; not yet "
-                           "run on a GPU)")
-@pytest.mark.parametrize("world,rpn", [(2, 1), (4, 2)])
-def test_two_hop_push_back_equals_one_hop(native_ops, monkeypatch, world, rpn):
-    """The representatives push their reduced rows into the origins' sections: same bits as the
-    one-hop path (which the switch does not touch)."""
-    if torch.cuda.device_count() < world:
-        pytest.skip(f"needs {world} GPUs")
-    monkeypatch.setenv("TERRACE_EP_PUSH_BACK", "1")
-    for rank, res, echo, x0, status, live in _run(world, 2, 29795 + world, rpn=rpn):
-        assert status == 0
-        assert live["push_back"] >= 2                      # forward and backward combine
-        for a, b in zip(res["one_hop"], res["two_hop"]):
-            assert torch.equal(a, b)
-        _close(echo, x0, 2e-2)
-
-
-@pytest.mark.skipif(os.environ.get("TERRACE_TEST_PIPELINE", "0") != "1",
-                    reason="opt-in: TERRACE_TEST_PIPELINE=1 (token-sliced pipeline; not yet run on "
-                           "a GPU)")
 @pytest.mark.parametrize("world,rpn,n", [(2, 1, 2), (4, 2, 3)])
 def test_token_pipeline_keeps_one_hop_two_hop_identity(native_ops, monkeypatch, world, rpn, n):
-    """n token slices on n streams and n arenas: the two paths still agree bit for bit, outputs
-    and input gradients match the NCCL arm within tolerance."""
+    """n token slices on n streams and n arenas: the two hops still agree bit for bit; outputs and
+    input gradients equal the unsliced remote-read schedule bit for bit, weight gradients within
+    rounding."""
     if torch.cuda.device_count() < world:
         pytest.skip(f"needs {world} GPUs")
     monkeypatch.setenv("TERRACE_EP_PIPELINE", str(n))
-    for rank, res, echo, x0, status, live in _run(world, 2, 29805 + world, rpn=rpn):
-        assert status == 0
-        assert live["two_hop_fwd"] == n and live["one_hop_fwd"] == n
-        for a, b in zip(res["one_hop"], res["two_hop"]):
-            assert torch.equal(a, b)
-        for a, b in zip(res["one_hop"], res["ref"]):
-            _close(a, b)
-        _close(echo, x0, 2e-2)
+    _check_ranks(_run(world, 2, 29805 + world, rpn=rpn), world, pipeline=n)

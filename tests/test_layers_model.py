@@ -88,11 +88,50 @@ def test_hierarchical_moe_runs_and_reports_hard_tokens():
     cfg = TRouteConfig(8, 2, 2, 1)
     h = HierarchicalMoE(16, 8, 32, 0.25, cfg)
     h.expert_backend = "grouped"
-    assert h.tier1.shared is None
     y, stats = h(torch.randn(40, 16))
     assert y.shape == (40, 16) and stats["n_hard"] == 10
-    keys = set(h.state_dict())
-    assert "tier0.shared.w13.weight" in keys and not any(k.startswith("tier1.shared") for k in keys)
+    # tier 1 has no shared expert, yet it keeps the two (zero-element) keys the reference's
+    # HierarchicalMoE carries, so state dicts interchange with strict loading
+    sd = h.state_dict()
+    assert "tier0.shared.w13.weight" in sd
+    assert sd["tier1.shared.w13.weight"].numel() == 0 and sd["tier1.shared.w2.weight"].numel() == 0
+    assert tuple(sd["tier1.shared.w2.weight"].shape) == (16, 0)
+    # n_shared = 0 on tier 0 as well: the layer runs and the shared branch contributes zero
+    h0 = HierarchicalMoE(16, 8, 32, 0.25, cfg, n_shared=0)
+    assert h0(torch.randn(8, 16))[0].shape == (8, 16)
+
+
+def test_hierarchical_state_dict_round_trips_with_the_reference_model():
+    """Strict loading in both directions against the reference's own TerraceLM (arch "hier")."""
+    import importlib.util
+    import os
+    import sys
+    ref_root = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))),
+                            "baseline", "_ref")
+    if not os.path.isfile(os.path.join(ref_root, "terrace", "model.py")):
+        pytest.skip("no copy of the reference package beside the repository")
+    saved = {k: v for k, v in sys.modules.items() if k == "terrace" or k.startswith("terrace.")}
+    for k in saved:
+        del sys.modules[k]
+    sys.path.insert(0, ref_root)
+    try:
+        ref_model = importlib.import_module("terrace.model")
+        kw = dict(vocab=64, dim=32, n_layers=2, n_heads=2, seq_len=16, n_experts=8, n_groups=2,
+                  top_k=2, top_groups=1, arch="hier", d0=16, d1=32, dense_first=1)
+        torch.manual_seed(0)
+        theirs = ref_model.TerraceLM(ref_model.ModelArgs(**kw))
+        ours = TerraceLM(ModelArgs(**kw))
+        assert set(theirs.state_dict()) == set(ours.state_dict())
+        ours.load_state_dict(theirs.state_dict(), strict=True)
+        theirs.load_state_dict(ours.state_dict(), strict=True)
+        ids = torch.randint(0, 64, (2, 16))
+        theirs.eval(), ours.eval()
+        torch.testing.assert_close(ours(ids)[0], theirs(ids)[0], rtol=1e-5, atol=1e-5)
+    finally:
+        sys.path.remove(ref_root)
+        for k in [k for k in sys.modules if k == "terrace" or k.startswith("terrace.")]:
+            del sys.modules[k]
+        sys.modules.update(saved)
 
 
 def test_rmsnorm_and_swiglu_formulas():
