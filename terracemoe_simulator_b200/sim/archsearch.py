@@ -1,17 +1,30 @@
-"""Architecture search at fixed capacity: the granularity family (E x g, d_expert / g, k x g keeps
-total and active parameters) crossed with every group cap M that divides k.  Candidates are
-ranked by dispatch + expert time with nothing overlapped -- an upper bound, not a step time.
+"""Architecture search at fixed capacity, priced on one machine.
+
+The search space is a lattice: the granularity axis (experts x g, expert width / g, top-k x g:
+total and active parameters stay put), crossed with every group cap M that divides k and fits
+the fabric's group count, plus an optional hidden-width axis (which moves capacity and is to be
+read separately).  Each lattice point becomes a ``Candidate`` carrying its dispatch time (the
+better of one-hop and two-hop, when two-hop applies at all), its expert time and the smallest
+expert-parallel degree its weights fit in.  The sort key is dispatch + expert with nothing
+overlapped: an upper bound that is loose in the same direction everywhere, not a step time.
 Quality is not priced.
 
-Parity with the reference ``sim/archsearch.py`` (``Candidate`` :46-63, ``granularity_family``
-:70-87, ``evaluate`` :90-115, ``search`` / ``rank`` / ``table`` :118-165).
+Public surface of the reference's ``sim/archsearch.py`` (``Candidate`` :46-63,
+``granularity_family`` :70-87, ``evaluate`` :90-115, ``search`` / ``rank`` / ``table``
+:118-165).
 """
 from __future__ import annotations
 
+import itertools
+import operator
 from dataclasses import dataclass, replace
 
-from .codesign import (UNMEASURED, Machine, MemoryProfile, MoEArch, dispatch_breakdown,
-                       expert_matmul, min_ep_for_memory)
+from . import codesign as cd
+from ._text import Column, render_table
+from .codesign import UNMEASURED, Machine, MemoryProfile, MoEArch
+
+DEFAULT_FACTORS = (0.5, 1, 2, 4, 8)
+CAPACITY_TOLERANCE = 0.01       # rounding may move either capacity product by at most 1 %
 
 
 @dataclass(frozen=True)
@@ -34,88 +47,110 @@ class Candidate:
 
 
 def _divisors(n: int):
-    return [d for d in range(1, n + 1) if n % d == 0]
+    small = [d for d in range(1, int(n ** 0.5) + 1) if n % d == 0]
+    return sorted(set(small) | {n // d for d in small})
 
 
-def granularity_family(base: MoEArch, factors=(0.5, 1, 2, 4, 8)):
-    cap_total, cap_active = base.n_experts * base.d_expert, base.k * base.d_expert
-    out = []
-    for g in factors:
-        E, d, k = (int(round(base.n_experts * g)), int(round(base.d_expert / g)),
-                   int(round(base.k * g)))
-        if min(E, d, k) < 1 or k > E:
-            continue
-        if abs(E * d - cap_total) > 0.01 * cap_total or abs(k * d - cap_active) > 0.01 * cap_active:
-            continue
-        out.append((g, replace(base, name="%s-g%g" % (base.name, g), n_experts=E, d_expert=d,
-                               k=k)))
-    return out
+def _scaled(base: MoEArch, g: float):
+    """``base`` moved by granularity ``g``, or None when the point is illegal or rounding broke
+    one of the two capacity invariants."""
+    shape = {"n_experts": round(base.n_experts * g), "d_expert": round(base.d_expert / g),
+             "k": round(base.k * g)}
+    if min(shape.values()) < 1 or shape["k"] > shape["n_experts"]:
+        return None
+    for width_of in ("n_experts", "k"):               # total, then active parameters
+        kept, want = shape[width_of] * shape["d_expert"], getattr(base, width_of) * base.d_expert
+        if abs(kept - want) > CAPACITY_TOLERANCE * want:
+            return None
+    return replace(base, name="%s-g%g" % (base.name, g), **{k: int(v) for k, v in shape.items()})
+
+
+def granularity_family(base: MoEArch, factors=DEFAULT_FACTORS):
+    scaled = ((g, _scaled(base, g)) for g in factors)
+    return [(g, arch) for g, arch in scaled if arch is not None]
+
+
+def _why_not_two_hop(d: dict) -> str:
+    if not d["domain_condition"]:
+        return "two-hop does not apply: expert parallelism fits one fast domain"
+    return "two-hop does not apply: q = k/M is 1, nothing to deduplicate"
 
 
 def evaluate(arch: MoEArch, machine: Machine, mem: MemoryProfile = UNMEASURED) -> Candidate:
-    floor = min_ep_for_memory(arch, machine, mem)["min_ep"]
-    feasible = 0 < floor <= machine.fabric.ep
-    reason = "" if feasible else "experts need EP %d, fabric has %d" % (floor, machine.fabric.ep)
-    mm = expert_matmul(arch, machine, machine.fabric.ep)
-    d = dispatch_breakdown(arch, machine)
-    applies = d["domain_condition"] and d["fanout_condition"]
-    if applies and d["two_hop_ms"] < d["one_hop_ms"]:
-        best, strategy = d["two_hop_ms"], "two-hop"
-    else:
-        best, strategy = d["one_hop_ms"], "one-hop"
-        if not applies:
-            why = "expert parallelism fits one fast domain" if not d["domain_condition"] else \
-                "q = k/M is 1, nothing to deduplicate"
-            reason = (reason + "; " if reason else "") + "two-hop does not apply: " + why
-    return Candidate(arch=arch, granularity=0.0, one_hop_ms=d["one_hop_ms"],
-                     two_hop_ms=d["two_hop_ms"], best_dispatch_ms=best, strategy=strategy,
-                     expert_ms=mm["ms"], expert_bound_by=mm["bound_by"], min_ep=floor,
-                     feasible=feasible, reason=reason)
+    ep = machine.fabric.ep
+    need = cd.min_ep_for_memory(arch, machine, mem)["min_ep"]
+    experts = cd.expert_matmul(arch, machine, ep)
+    hops = cd.dispatch_breakdown(arch, machine)
+    notes = []
+    fits = 0 < need <= ep
+    if not fits:
+        notes.append("experts need EP %d, fabric has %d" % (need, ep))
+    eligible = hops["domain_condition"] and hops["fanout_condition"]
+    use_two = eligible and hops["two_hop_ms"] < hops["one_hop_ms"]
+    if not eligible:
+        notes.append(_why_not_two_hop(hops))
+    chosen = "two_hop_ms" if use_two else "one_hop_ms"
+    priced = {name: hops[name] for name in ("one_hop_ms", "two_hop_ms")}
+    priced.update(best_dispatch_ms=hops[chosen], strategy=chosen[:3] + "-hop",
+                  expert_ms=experts["ms"], expert_bound_by=experts["bound_by"])
+    return Candidate(arch, 0.0, min_ep=need, feasible=fits, reason="; ".join(notes), **priced)
 
 
-def search(base: MoEArch, machine: Machine, granularities=(0.5, 1, 2, 4, 8), hiddens=None,
-           mem: MemoryProfile = UNMEASURED) -> list:
-    out = []
+def _lattice(base: MoEArch, machine: Machine, granularities, hiddens):
+    """``(granularity, architecture)`` for every point of the search lattice."""
+    groups = machine.fabric.nodes
     for g, arch in granularity_family(base, granularities):
         for M in _divisors(arch.k):
-            if M <= machine.fabric.nodes:
-                cand = evaluate(replace(arch, name="%s-M%d" % (arch.name, M), M=M), machine, mem)
-                out.append(replace(cand, granularity=g))
-    for H in hiddens or ():
-        for M in _divisors(base.k):
-            if M <= machine.fabric.nodes:
-                cand = evaluate(replace(base, name="%s-H%d-M%d" % (base.name, H, M), hidden=H,
-                                        M=M), machine, mem)
-                out.append(replace(cand, granularity=1.0))
-    return out
+            if M <= groups:
+                yield g, replace(arch, name="%s-M%d" % (arch.name, M), M=M)
+    for H, M in itertools.product(hiddens or (), _divisors(base.k)):
+        if M <= groups:
+            yield 1.0, replace(base, name="%s-H%d-M%d" % (base.name, H, M), hidden=H, M=M)
+
+
+def search(base: MoEArch, machine: Machine, granularities=DEFAULT_FACTORS, hiddens=None,
+           mem: MemoryProfile = UNMEASURED) -> list:
+    return [replace(evaluate(arch, machine, mem), granularity=g)
+            for g, arch in _lattice(base, machine, granularities, hiddens)]
 
 
 def rank(cands, key="no_overlap_ms", feasible_only: bool = True) -> list:
-    pool = [c for c in cands if c.feasible] if feasible_only else list(cands)
-    return sorted(pool, key=lambda c: getattr(c, key))
+    keep = filter(operator.attrgetter("feasible"), cands) if feasible_only else cands
+    return sorted(keep, key=operator.attrgetter(key))
+
+
+_COLUMNS = (
+    Column("gran", "%-6g", lambda c: c.granularity),
+    Column("experts", "%-7d", lambda c: c.arch.n_experts),
+    Column("d_exp", "%-7d", lambda c: c.arch.d_expert),
+    Column("k", "%-4d", lambda c: c.arch.k),
+    Column("M", "%-4d", lambda c: c.arch.M),
+    Column("q", "%-4d", lambda c: c.arch.q),
+    Column("dispatch", "%10.3f", lambda c: c.best_dispatch_ms),
+    Column("expert", "%10.3f", lambda c: c.expert_ms),
+    Column("sum(UB)", "%10.3f", lambda c: c.no_overlap_ms),
+    Column("strategy", "%-9s", lambda c: c.strategy),
+)
+_FOOTNOTE = ("sum(UB) is dispatch plus expert with nothing overlapped, an upper bound and not a "
+             "step time: the step-level gate fails.")
 
 
 def table(cands, top: int = 12) -> str:
-    lines = ["%-6s %-7s %-7s %-4s %-4s %-4s %10s %10s %10s %-9s"
-             % ("gran", "experts", "d_exp", "k", "M", "q", "dispatch", "expert", "sum(UB)",
-                "strategy"), "-" * 88]
-    for c in rank(cands)[:top]:
-        a = c.arch
-        lines.append("%-6g %-7d %-7d %-4d %-4d %-4d %10.3f %10.3f %10.3f %-9s"
-                     % (c.granularity, a.n_experts, a.d_expert, a.k, a.M, a.q, c.best_dispatch_ms,
-                        c.expert_ms, c.no_overlap_ms, c.strategy))
-    lines += ["", "sum(UB) is dispatch plus expert with nothing overlapped, an upper bound and "
-                  "not a step time: the step-level gate fails."]
-    return "\n".join(lines)
+    return "\n".join(render_table(_COLUMNS, rank(cands)[:top], rule=88) + ["", _FOOTNOTE])
 
 
 def main() -> None:
-    from .codesign import REFERENCE_ARCH, synthetic_dgx_h100
-    m = synthetic_dgx_h100()
+    m = cd.synthetic_dgx_h100()
     print("Granularity x group-cap search at the reference capacity on the %s" % m.fabric.name)
     print("(synthetic sensitivity; quality of each point is NOT priced)")
     print()
-    print(table(search(REFERENCE_ARCH, m)))
+    print(table(search(cd.REFERENCE_ARCH, m)))
+    b = cd.hgx_b200()
+    print()
+    print("Same search on the %s (measured fabric: one NVSwitch domain, logical groups)"
+          % b.fabric.name)
+    print()
+    print(table(search(cd.REFERENCE_ARCH, b)))
 
 
 if __name__ == "__main__":

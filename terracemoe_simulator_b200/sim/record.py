@@ -1,34 +1,53 @@
-"""Directional check against published MFU: Mixtral 8x22B against its fine-grained G8T8 variant on
-128-1024 H100s.  The model prices MoE layers only, so it does not predict MFU; it is asked two
-directional questions -- is the fine-grained model's ceiling lower at every cluster size, and do
-the ceilings not rise from the smallest to the largest cluster -- and both hold.
+"""Directional check against a published MFU record: Mixtral 8x22B and its fine-grained G8T8
+variant on clusters of 128 to 1024 H100s at one global batch.
 
-Parity with the reference ``sim/record.py`` (:69-154).
+The model prices MoE layers only, so it cannot predict an MFU.  It is asked two directional
+questions instead -- is the fine-grained model's utilisation ceiling the lower one at every
+cluster size, and does no model's ceiling rise from the smallest cluster to the largest -- and
+both hold.  For every (model, cluster) the expert-parallel degree is the one that maximises the
+ceiling, as a tuned run would choose it.
+
+Public surface of the reference's ``sim/record.py`` (:69-154).
 """
 from __future__ import annotations
 
 from dataclasses import replace
 
-from .codesign import Machine, MoEArch, synthetic_dgx_h100
+from . import codesign as cd
+from ._text import Column, Ledger, render_table
+from .codesign import Machine, MoEArch
 from .envelope import evaluate
 
 MPF_SEQ = 4096
 MPF_GLOBAL_BATCH_SEQS = 1024
 MPF_CLUSTERS = (128, 256, 512, 1024)
-MIXTRAL_8X22B = MoEArch(name="Mixtral 8x22B", hidden=6144, d_expert=16384, n_experts=8, k=2, M=2,
-                        n_moe_layers=56, seq=MPF_SEQ, mbs=1, gbs=MPF_GLOBAL_BATCH_SEQS)
-MIXTRAL_G8T8 = MoEArch(name="Mixtral-8x22B-G8T8", hidden=6144, d_expert=2048, n_experts=64, k=8,
-                       M=8, n_moe_layers=56, seq=MPF_SEQ, mbs=1, gbs=MPF_GLOBAL_BATCH_SEQS)
-MPF_MFU = {"Mixtral 8x22B": {128: 52.2, 256: 50.7, 512: 48.9, 1024: 44.9},
-           "Mixtral-8x22B-G8T8": {128: 30.0, 256: 29.3, 512: 26.7, 1024: 25.5}}
+EP_CHOICES = (8, 16, 32, 64, 128)
+NODE_SIZE = 8
+
+
+def _mixtral(name: str, d_expert: int, n_experts: int, k: int) -> MoEArch:
+    return MoEArch(name=name, hidden=6144, d_expert=d_expert, n_experts=n_experts, k=k, M=k,
+                   n_moe_layers=56, seq=MPF_SEQ, mbs=1, gbs=MPF_GLOBAL_BATCH_SEQS)
+
+
+MIXTRAL_8X22B = _mixtral("Mixtral 8x22B", 16384, 8, 2)
+MIXTRAL_G8T8 = _mixtral("Mixtral-8x22B-G8T8", 2048, 64, 8)
+MODELS = (MIXTRAL_8X22B, MIXTRAL_G8T8)
+MPF_MFU = {
+    MIXTRAL_8X22B.name: dict(zip(MPF_CLUSTERS, (52.2, 50.7, 48.9, 44.9))),
+    MIXTRAL_G8T8.name: dict(zip(MPF_CLUSTERS, (30.0, 29.3, 26.7, 25.5))),
+}
 
 
 def eos_like(ep_ranks: int) -> Machine:
-    nodes = max(1, ep_ranks // 8)
-    m = synthetic_dgx_h100(nodes=nodes)
-    if nodes == 1:      # EP inside one node: no slow level
-        m = Machine(m.accel, replace(m.fabric, beta_inter_gbps=m.fabric.beta_intra_gbps), m.chain)
-    return m
+    """Synthetic H100 nodes holding ``ep_ranks`` expert-parallel ranks; inside a single node
+    there is no slow level, so both levels run at the intra-node rate."""
+    nodes = ep_ranks // NODE_SIZE or 1
+    machine = cd.synthetic_dgx_h100(nodes=nodes)
+    if nodes > 1:
+        return machine
+    flat = replace(machine.fabric, beta_inter_gbps=machine.fabric.beta_intra_gbps)
+    return Machine(machine.accel, flat, machine.chain)
 
 
 def tokens_per_accel(cluster: int) -> int:
@@ -36,52 +55,64 @@ def tokens_per_accel(cluster: int) -> int:
 
 
 def best_point(arch: MoEArch, cluster: int):
-    toks = tokens_per_accel(cluster)
-    if toks % MPF_SEQ:
+    """``(ep, Point)`` with the highest ceiling among the legal expert-parallel degrees."""
+    sequences, rest = divmod(tokens_per_accel(cluster), MPF_SEQ)
+    if rest:
         raise ValueError("tokens per accelerator is not a whole number of sequences")
-    a = replace(arch, mbs=toks // MPF_SEQ)
-    best = None
-    for ep in (8, 16, 32, 64, 128):
-        if ep > arch.n_experts or ep > cluster:
-            continue
-        p = evaluate(a, eos_like(ep))
-        if best is None or p.utilisation_ceiling > best[1].utilisation_ceiling:
-            best = (ep, p)
-    return best
+    shaped = replace(arch, mbs=sequences)
+    legal = [ep for ep in EP_CHOICES if ep <= min(arch.n_experts, cluster)]
+    priced = [(ep, evaluate(shaped, eos_like(ep))) for ep in legal]
+    # the first of equal ceilings wins, as a strict-improvement scan would have it
+    return max(priced, key=lambda t: t[1].utilisation_ceiling, default=None)
 
 
 def comparison() -> list:
-    out = []
+    rows = []
     for cluster in MPF_CLUSTERS:
-        for arch in (MIXTRAL_8X22B, MIXTRAL_G8T8):
-            ep, p = best_point(arch, cluster)
-            out.append((cluster, tokens_per_accel(cluster), arch.name, ep,
-                        100.0 * p.utilisation_ceiling, MPF_MFU[arch.name][cluster]))
-    return out
+        for arch in MODELS:
+            ep, point = best_point(arch, cluster)
+            rows.append((cluster, tokens_per_accel(cluster), arch.name, ep,
+                         100.0 * point.utilisation_ceiling, MPF_MFU[arch.name][cluster]))
+    return rows
+
+
+def _ledger(rows=None) -> Ledger:
+    ceiling = {(name, cluster): value for cluster, _, name, _, value, _ in rows or comparison()}
+    coarse, fine = MIXTRAL_8X22B.name, MIXTRAL_G8T8.name
+    small, large = MPF_CLUSTERS[0], MPF_CLUSTERS[-1]
+    led = Ledger()
+    led.add("granularity_ordering_holds",
+            all(ceiling[fine, c] < ceiling[coarse, c] for c in MPF_CLUSTERS))
+    led.add("endpoint_decline_holds",
+            all(ceiling[name, large] <= ceiling[name, small] for name in (coarse, fine)))
+    return led
 
 
 def checks(rows=None) -> dict:
-    by: dict = {}
-    for cluster, _, name, _, ceil, _ in rows or comparison():
-        by.setdefault(name, {})[cluster] = ceil
-    first, last = MPF_CLUSTERS[0], MPF_CLUSTERS[-1]
-    return {"granularity_ordering_holds": all(by["Mixtral-8x22B-G8T8"][c] < by["Mixtral 8x22B"][c]
-                                              for c in MPF_CLUSTERS),
-            "endpoint_decline_holds": all(v[last] <= v[first] for v in by.values())}
+    return _ledger(rows).as_dict()
+
+
+_COLUMNS = (
+    Column("cluster", "%-8d", lambda r: r[0]),
+    Column("tokens/acc", "%11d", lambda r: r[1]),
+    Column("model", "%-20s", lambda r: r[2]),
+    Column("EP*", "%4d", lambda r: r[3]),
+    Column("ceiling %", "%10.1f", lambda r: r[4]),
+    Column("published MFU", "%14.1f", lambda r: r[5]),
+)
+_VERDICTS = (("granularity_ordering_holds", "fine-grained variant lower at every size"),
+             ("endpoint_decline_holds", "no rise from the smallest to the largest cluster"))
 
 
 def main() -> None:
+    rows = comparison()
     print("Published MFU against this model's MoE-layer ceiling (synthetic H100 nodes;")
     print("ceilings are MoE-layer-only and are not MFU predictions)")
-    print("%-8s %11s %-20s %4s %10s %14s" % ("cluster", "tokens/acc", "model", "EP*", "ceiling %",
-                                             "published MFU"))
-    for cluster, toks, name, ep, ceil, mfu in comparison():
-        print("%-8d %11d %-20s %4d %10.1f %14.1f" % (cluster, toks, name, ep, ceil, mfu))
-    ck = checks()
-    print("fine-grained variant lower at every size: %s"
-          % ("holds" if ck["granularity_ordering_holds"] else "FAILS"))
-    print("no rise from the smallest to the largest cluster: %s"
-          % ("holds" if ck["endpoint_decline_holds"] else "FAILS"))
+    head, _rule, *body = render_table(_COLUMNS, rows)
+    print("\n".join([head] + body))
+    verdict = checks(rows)
+    for key, sentence in _VERDICTS:
+        print("%s: %s" % (sentence, "holds" if verdict[key] else "FAILS"))
 
 
 if __name__ == "__main__":
