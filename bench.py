@@ -297,7 +297,10 @@ def run_ours(args, rank, world, local):
                                        device=device, overlap=overlap)
     x_dev = x_host.to(device).requires_grad_(True)
     gy_flat, inv_n = gy.reshape(-1), 1.0 / gy.numel()
-    parity = parity_check(runners, cfg, rank, world, x_dev, gy, router_w, w13, w2)
+    if args.no_parity:       # profiling runs: keep the launch stream to the steps themselves
+        parity = {"skipped": True, "paths": {n: {"ok": True} for n in runners}}
+    else:
+        parity = parity_check(runners, cfg, rank, world, x_dev, gy, router_w, w13, w2)
     # end-to-end path: every step's tokens come from pinned host memory through the package's
     # input prefetcher (the copy of step i+1 runs on a side stream during step i)
     import itertools
@@ -330,12 +333,20 @@ def run_ours(args, rank, world, local):
     sampler = ClockSampler(local) if rank == 0 else None
     if sampler:
         sampler.start()          # polls through the warm-ups and every timed block of every path
+    from terracemoe_simulator_b200.utils import trace
+    if trace.enabled():
+        trace.report(group=True if world > 1 else None)      # drop the parity step's spans
     for path in runners:
         native.LAUNCHES[0] = 0
         blocks = timed(make_step(path, False), args.steps, args.warmup, world, args.repeats)
         launches = native.LAUNCHES[0] // (args.steps * args.repeats + args.warmup)    # per step
         results[path] = dict(block_stats(blocks, args.steps), launches=launches,
                              parity_ok=parity["paths"][path]["ok"])
+        if trace.enabled():      # TERRACE_TRACE=events: per-phase device spans, max over ranks
+            rep = trace.report(group=True if world > 1 else None)
+            if rank == 0:
+                print(f"--- phases of path {path} ---\n" + trace.format_report(rep),
+                      file=sys.stderr)
     clocks = sampler.stop() if sampler else None
     for path in runners:
         if path.endswith("_pull"):
@@ -398,11 +409,6 @@ def run_ours(args, rank, world, local):
                 "d2h_bytes_per_step": losses.bytes_per_read, "last_loss": last_loss},
         "gpu_launches": results[best]["launches"] * args.steps,
     }
-    from terracemoe_simulator_b200.utils import trace
-    if trace.enabled():          # TERRACE_TRACE=events: per-phase device spans, max over ranks
-        rep = trace.report(group=True if world > 1 else None)
-        if rank == 0:
-            print(trace.format_report(rep), file=sys.stderr)
     return out
 
 
@@ -501,6 +507,8 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--repeats", type=int, default=5,
                     help="timed blocks of K steps each; the median block is reported")
+    ap.add_argument("--no-parity", action="store_true",
+                    help="skip the 512-token parity step (for profiler captures)")
     ap.add_argument("--no-ab", action="store_true",
                     help="skip the remote-read schedule that is timed beside the default one")
     ap.add_argument("--nccl-arm", action="store_true",

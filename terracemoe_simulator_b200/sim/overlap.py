@@ -1,119 +1,137 @@
-"""Six one-parameter overlap families fitted on the calibration geometry and scored on the six
-holdouts of the step-level gate.  Every one of them fails it -- a pinned negative result: no
-single scalar of "how much communication hides behind compute" explains the measured step deltas.
+"""Six one-parameter overlap hypotheses, fitted on the calibration configuration and scored on
+the six holdouts of the step-level gate.
 
-Parity with the reference ``sim/overlap.py`` (``decompose`` :60-86, families :99-129,
+Every hypothesis says the same kind of thing: of the modelled step difference ``d_model``
+(two-hop minus one-hop, nothing overlapped) a part is hidden behind compute, and that part is
+proportional to some quantity of the step -- the difference itself, the number of calls, the
+fixed per-call overhead, the compute time, or the difference per micro-batch:
+
+    d_predicted = d_model - c * basis(step)
+
+The coefficient ``c`` is solved on the calibration configuration, then reported in the
+parametrisation each family is known by (e.g. ``phi = 1 - c`` for the proportional family).
+All six fail the gate -- a pinned negative result: no single scalar of "how much communication
+hides behind compute" explains the measured step differences.
+
+Public surface of the reference's ``sim/overlap.py`` (``decompose`` :60-86, families :99-129,
 ``evaluate`` :132-165).
 """
 from __future__ import annotations
 
 from dataclasses import dataclass
+from typing import Callable
 
 from .core import step_delta
-from .validate import GATE_IN_TOL, GATE_MAE, GATE_TOL, HOLDOUTS
+from .stepgate import GATE_IN_TOL, GATE_MAE, GATE_TOL, GateScore  # noqa: F401  (re-exported)
+from .validate import HOLDOUTS
 
 NEG_NAMES = {"tok2x", "tok4x", "k8m4", "n8", "n4"}
 
 
-@dataclass
+@dataclass(frozen=True)
 class Decomp:
+    """What is known about one measured configuration: the measurement (``g_meas``, ``t_off``),
+    its shape (``calls``, ``mbs``) and the model's view of it, all in ms per step."""
     name: str
     role: str
     g_meas: float
-    t_off: float
+    t_off: float        # measured one-hop step
     calls: int
     mbs: int
-    d_model: float      # modelled step delta (two-hop minus one-hop), ms
-    d_meas: float       # measured step delta, ms
-    fixed: float        # part of d_model that is chain + splits, ms
-    comm_off: float     # modelled communication of the one-hop arm, ms
-    t_comp: float       # one-hop step time minus its communication, ms
+    d_model: float      # modelled step difference (two-hop minus one-hop)
+    fixed: float        # the part of d_model that is arrival chain + splits read-back
+    comm_off: float     # modelled communication of the one-hop arm
+
+    @property
+    def d_meas(self) -> float:          # measured step difference
+        return self.t_off * (1.0 / self.g_meas - 1.0)
+
+    @property
+    def t_comp(self) -> float:          # one-hop step minus its communication
+        return self.t_off - self.comm_off
+
+    def g_from_delta(self, delta_ms: float) -> float:
+        return self.t_off / (self.t_off + delta_ms)
+
+
+def _decompose_one(cluster, h) -> Decomp:
+    priced, geom = step_delta(cluster, h.geom), h.geom
+    calls = priced["calls_per_step"]
+    overhead = cluster.splits_sync_ms + cluster.chain_us_per_row * geom.rows_hop_b() / 1e3
+    return Decomp(geom.name, h.role, h.g_measured, h.t_off_ms, calls, geom.mbs,
+                  priced["step_delta_ms"], calls * overhead, calls * priced["per_call_off_ms"])
 
 
 def decompose(cluster) -> list:
-    out = []
-    for h in HOLDOUTS:
-        d = step_delta(cluster, h.geom)
-        calls = d["calls_per_step"]
-        chain = cluster.chain_us_per_row * h.geom.rows_hop_b() / 1000.0
-        comm_off = d["per_call_off_ms"] * calls
-        out.append(Decomp(name=h.geom.name, role=h.role, g_meas=h.g_measured, t_off=h.t_off_ms,
-                          calls=calls, mbs=h.geom.mbs, d_model=d["step_delta_ms"],
-                          d_meas=h.t_off_ms / h.g_measured - h.t_off_ms,
-                          fixed=(chain + cluster.splits_sync_ms) * calls, comm_off=comm_off,
-                          t_comp=h.t_off_ms - comm_off))
-    return out
+    return [_decompose_one(cluster, h) for h in HOLDOUTS]
 
 
-@dataclass
+@dataclass(frozen=True)
 class Family:
+    """``d = d_model - c * basis``; ``shown(c)`` is the parameter the family reports."""
     key: str
     desc: str
     n_params: int
-    predict: object      # (Decomp, param) -> predicted step delta in ms
-    fit: object          # Decomp -> param that makes the calibration geometry exact
+    basis: Callable
+    shown: Callable = staticmethod(lambda c: c)
+
+    def coefficient(self, cal: Decomp) -> float:
+        b = self.basis(cal)
+        return (cal.d_model - cal.d_meas) / b if b else 0.0
+
+    def delta(self, d: Decomp, c: float) -> float:
+        return d.d_model - c * self.basis(d)
+
+
+FAMILIES = (
+    Family("M0", "naive: d = d_model (no overlap)", 0, lambda d: 0.0),
+    Family("M1", "prop: d = phi*d_model", 1, lambda d: d.d_model, lambda c: 1.0 - c),
+    Family("M2", "hide/call: d = d_model-h*calls", 1, lambda d: float(d.calls)),
+    Family("M3", "hide-fixed: d = d_model-phi*fixed", 1, lambda d: d.fixed),
+    Family("M4", "hide~comp: d = d_model-c*T_comp", 1, lambda d: d.t_comp),
+    Family("M5", "expose-mb: d = d_model*(1-lam/mbs)", 1, lambda d: d.d_model / d.mbs),
+)
 
 
 def _families() -> list:
-    return [
-        Family("M0", "naive: d = d_model (no overlap)", 0, lambda d, p: d.d_model, lambda d: 0.0),
-        Family("M1", "prop: d = phi*d_model", 1, lambda d, p: p * d.d_model,
-               lambda d: d.d_meas / d.d_model),
-        Family("M2", "hide/call: d = d_model-h*calls", 1, lambda d, p: d.d_model - p * d.calls,
-               lambda d: (d.d_model - d.d_meas) / d.calls),
-        Family("M3", "hide-fixed: d = d_model-phi*fixed", 1, lambda d, p: d.d_model - p * d.fixed,
-               lambda d: (d.d_model - d.d_meas) / d.fixed),
-        Family("M4", "hide~comp: d = d_model-c*T_comp", 1, lambda d, p: d.d_model - p * d.t_comp,
-               lambda d: (d.d_model - d.d_meas) / d.t_comp),
-        Family("M5", "expose-mb: d = d_model*(1-lam/mbs)", 1,
-               lambda d, p: d.d_model * (1.0 - p / d.mbs),
-               lambda d: (1.0 - d.d_meas / d.d_model) * d.mbs),
-    ]
+    return list(FAMILIES)
+
+
+def _score(fam: Family, cal: Decomp, holdouts) -> dict:
+    c = fam.coefficient(cal)
+    score = GateScore(NEG_NAMES)
+    for d in holdouts:
+        score.add(d.name, d.g_meas, d.g_from_delta(fam.delta(d, c)))
+    return {"param": fam.shown(c) if fam.n_params else 0.0, "mae": score.mae,
+            "in_tol": score.in_tol, "signs_ok": score.signs_ok, "n_neg": score.n_negative(),
+            "rows": list(score.rows), "desc": fam.desc, "gate": score.passed()}
 
 
 def evaluate(cluster, verbose: bool = True) -> dict:
-    decs = decompose(cluster)
-    cal = next(d for d in decs if d.role == "calibration")
-    holds = [d for d in decs if d.role == "holdout"]
-    n_neg = sum(d.name in NEG_NAMES for d in holds)
-    results = {}
-    for fam in _families():
-        p = fam.fit(cal)
-        rows, errs = [], []
-        in_tol = signs = 0
-        for d in holds:
-            g_pred = d.t_off / (d.t_off + fam.predict(d, p))
-            err = g_pred - d.g_meas
-            errs.append(abs(err))
-            in_tol += abs(err) <= GATE_TOL
-            signs += d.name in NEG_NAMES and g_pred < 1.0
-            rows.append((d.name, d.g_meas, g_pred, err))
-        mae = sum(errs) / len(errs)
-        results[fam.key] = {"param": p, "mae": mae, "in_tol": int(in_tol), "signs_ok": int(signs),
-                            "n_neg": n_neg, "rows": rows, "desc": fam.desc,
-                            "gate": mae <= GATE_MAE and in_tol >= GATE_IN_TOL and signs == n_neg}
+    parts = decompose(cluster)
+    by_role = {role: [d for d in parts if d.role == role] for role in ("calibration", "holdout")}
+    (cal,) = by_role["calibration"]
+    results = {fam.key: _score(fam, cal, by_role["holdout"]) for fam in FAMILIES}
     if verbose:
-        _report(decs, results)
+        print("\n".join(_report(parts, results)))
     return results
 
 
-def _report(decs, results) -> None:
-    print("%-7s %4s %8s %11s %11s %9s %8s" % ("geom", "mbs", "G_meas", "d_meas_ms", "d_model_ms",
-                                              "fixed", "expose"))
-    for d in decs:
-        print("%-7s %4d %8.4f %11.1f %11.1f %9.1f %8.3f" % (d.name, d.mbs, d.g_meas, d.d_meas,
-                                                            d.d_model, d.fixed,
-                                                            d.d_meas / d.d_model))
-    print()
-    print("%-4s %-36s %9s %7s %8s %6s %5s" % ("fam", "structure", "param", "MAE", "+-0.035",
-                                              "signs", "gate"))
-    for key, r in results.items():
-        print("%-4s %-36s %9.4f %7.4f %6d/6 %4d/%d %5s" % (key, r["desc"], r["param"], r["mae"],
-                                                           r["in_tol"], r["signs_ok"], r["n_neg"],
-                                                           "PASS" if r["gate"] else "FAIL"))
-    passed = [k for k, r in results.items() if r["gate"]]
-    print("families passing the gate: %s" % (", ".join(passed) if passed else
-                                             "none -- no one-parameter overlap explains the steps"))
+def _report(parts, results) -> list:
+    out = ["%-7s %4s %8s %11s %11s %9s %8s" % ("geom", "mbs", "G_meas", "d_meas_ms", "d_model_ms",
+                                               "fixed", "expose")]
+    out += ["%-7s %4d %8.4f %11.1f %11.1f %9.1f %8.3f"
+            % (d.name, d.mbs, d.g_meas, d.d_meas, d.d_model, d.fixed, d.d_meas / d.d_model)
+            for d in parts]
+    out += ["", "%-4s %-36s %9s %7s %8s %6s %5s" % ("fam", "structure", "param", "MAE", "+-0.035",
+                                                   "signs", "gate")]
+    out += ["%-4s %-36s %9.4f %7.4f %6d/6 %4d/%d %5s"
+            % (key, r["desc"], r["param"], r["mae"], r["in_tol"], r["signs_ok"], r["n_neg"],
+               "PASS" if r["gate"] else "FAIL") for key, r in results.items()]
+    winners = ", ".join(key for key, r in results.items() if r["gate"])
+    out.append("families passing the gate: %s"
+               % (winners or "none -- no one-parameter overlap explains the steps"))
+    return out
 
 
 if __name__ == "__main__":

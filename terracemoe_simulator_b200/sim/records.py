@@ -96,3 +96,31 @@ PEER_SWEEP = [(n, b, ms) for b, times in (
     (134217728, (9.0566, 8.9636, 8.9986, 8.9874, 9.0236, 9.1272, 9.3504)),
     (268435456, (17.6363, 17.4453, 17.4877, 17.4413, 17.4614, 17.5515, 17.7128)))
     for n, ms in zip((1, 2, 4, 8, 16, 32, 64), times)]
+
+
+# ---- bf16 GEMM throughput on platform A (256 samples per size) --------------------------------
+# square N x N x N problems: (N, TFLOPS)
+GEMM_TFLOPS = [(1024, 141.6), (2048, 271.1), (4096, 327.4), (8192, 296.7), (12288, 291.4),
+               (16384, 319.2)]
+# expert-FFN shapes (rows, hidden, expert width): TFLOPS
+NONSQUARE_TFLOPS = {
+    (1536, 2048, 5504): 309.7, (1536, 4096, 11008): 326.7, (1536, 7168, 2048): 328.3,
+    (3072, 2048, 5504): 324.8, (3072, 4096, 11008): 335.9, (3072, 7168, 2048): 338.0,
+    (6144, 2048, 5504): 331.4, (6144, 4096, 11008): 330.7,
+}
+# error of reading the square curve at the geometric mean of a non-square shape
+INDEX_RULE_ERROR = {"median_abs": 0.064, "bias": -0.064, "worst": 0.109}
+
+
+# ---- end-to-end steps, one-hop against two-hop (platform A, 19 MoE layers) --------------------
+# (name, groups, ranks per group, k, M, micro-batches, one-hop step ms, G = t_one / t_two, role)
+STEP_RECORDS = (
+    ("flag", 16, 8, 6, 2, 1, 4420.4, 1.0355, "calibration"),
+    ("tok2x", 16, 8, 6, 2, 2, 3343.6, 0.8845, "holdout"),
+    ("tok4x", 16, 8, 6, 2, 4, 2992.7, 0.8234, "holdout"),
+    ("k8m2", 16, 8, 8, 2, 1, 4791.7, 0.9935, "holdout"),
+    ("k8m4", 16, 8, 8, 4, 1, 4664.9, 0.9335, "holdout"),
+    ("n8", 8, 8, 6, 2, 1, 6657.5, 0.9027, "holdout"),
+    ("n4", 4, 8, 6, 2, 1, 11712.0, 0.8647, "holdout"),
+)
+STEP_MOE_LAYERS = 19
