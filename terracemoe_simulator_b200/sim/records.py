@@ -124,3 +124,53 @@ STEP_RECORDS = (
     ("n4", 4, 8, 6, 2, 1, 11712.0, 0.8647, "holdout"),
 )
 STEP_MOE_LAYERS = 19
+
+
+# ---- arrival chain of platform A: instrument readings and sweeps ------------------------------
+REFERENCE_PAIRS = 24576
+REFERENCE_INPUT_ROWS = 8192
+REFERENCE_H = 2048
+SWEEP_INPUT_ROWS = 24576
+SWEEP_QUOTA = 3
+SWEEP_PAIRS = SWEEP_INPUT_ROWS * SWEEP_QUOTA
+# (when, histogram primitive, chain ms at the reference point)
+CALIBRATION_INSTRUMENT = [("2026-08-23 00:41", "bincount", 1.1924),
+                          ("2026-08-23 01:01", "bincount", 1.1811),
+                          ("2026-08-23 08:11", "fixed_hist", 0.7810),
+                          ("2026-08-23 12:21", "fixed_hist", 0.7721),
+                          ("2026-08-24 07:06", "fixed_hist", 0.7758)]
+HISTOGRAM_CHANGE = (0.7939, 0.3270)       # histogram step alone: bincount ms -> fixed_hist ms
+# (input rows, pairs, ms on node 14, ms on node 15)
+AUGUST_ROW_SWEEP = [(1024, 3072, 0.2418, 0.2541), (2048, 6144, 0.2812, 0.2808),
+                    (4096, 12288, 0.4300, 0.4210), (8192, 24576, 0.7446, 0.7295),
+                    (16384, 49152, 1.4368, 1.3963), (24576, 73728, 2.5573, 2.4464),
+                    (32768, 98304, 3.2951, 3.3382), (49152, 147456, 4.9724, 4.9216),
+                    (65536, 196608, 6.5339, 6.4078)]
+AUGUST_WIDTH_SWEEP = [(1024, 2.3586, 2.3781), (2048, 2.5521, 2.4672), (4096, 2.8834, 2.8165),
+                      (8192, 3.8183, 3.7550)]
+ROW_SWEEP = [(1024, 0.3420), (2048, 0.3562), (4096, 0.3889), (8192, 0.4482), (12288, 0.4984),
+             (16384, 0.5809), (24576, 0.7150), (32768, 0.8494), (49152, 1.1942), (65536, 1.7768)]
+WIDTH_SWEEP = [(1024, 0.7168), (2048, 0.7235), (4096, 0.7739), (8192, 1.0025)]
+# (pairs, H, reference chain ms, live chain ms)
+LIVE_VS_REFERENCE = [(8192, 2048, 0.4685, 0.4900), (8192, 8192, 0.4854, 0.5156),
+                     (24576, 2048, 0.6855, 0.7752), (24576, 8192, 0.9955, 1.0520),
+                     (65536, 2048, 1.7767, 2.0674), (65536, 8192, 2.7319, 3.0258)]
+REFERENCE_READINGS = [("2026-08-23 instrument", 0.7810), ("2026-08-23 instrument", 0.7721),
+                      ("2026-08-24 instrument", 0.7758), ("2026-08-26 sweep, node 14", 0.7446),
+                      ("2026-08-26 sweep, node 15", 0.7295), ("2026-09-08 re-measurement", 0.7150)]
+PRE_CORRECTION_LEVEL_MS = 2.15
+US_PER_ROW = {"shipped before 2026-09-08": 0.0875, "one idle card, August": 0.0303,
+              "one idle card, September": 0.0291, "in situ, 8 cards (shipped)": 0.0424,
+              "fused design target": 0.0120}
+
+
+# ---- launch constants measured on platform A (ms) ---------------------------------------------
+LAUNCH_DEVICE_INITIATED_MS = (0.036, 0.057)
+LAUNCH_HOST_P2P_MS = (0.257, 0.268)
+PER_CALL_DEEP_QUEUE_MS = {2: 0.087, 4: 0.098, 8: 0.129, 16: 0.134}
+PER_CALL_DEEP_QUEUE_RANGE_MS = {8: (0.117, 0.133)}
+PER_CALL_HOST_EXPOSED_MS = {8: 0.255, 16: 0.283}
+PER_CALL_SPREAD = 0.15
+HOST_SUBMIT_MS = {2: 0.039, 4: 0.043, 8: 0.058, 16: 0.076}
+HOST_EXPOSURE_MS = 0.130
+LAUNCH_UPPER_BOUND_MS = 0.111
