@@ -23,6 +23,9 @@ LIB_DIR = os.path.join(HERE, "lib")
 OBJ_DIR = os.path.join(HERE, "build")
 LIB_NAME = "terrace_b200_ops.so"
 ARCH_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a"]
+# sources whose results are compared with PyTorch oracles bit for bit (router selection, plan,
+# normalisation): IEEE division and the accurate expf / rsqrtf, no --use_fast_math
+PRECISE_MATH = {"router_sm100.cu", "moe_kernels.cu"}
 
 
 def _nvcc() -> str:
@@ -68,7 +71,8 @@ def build(verbose: bool = False, force: bool = False) -> str:
     headers = sorted(f for f in os.listdir(CSRC) if f.endswith((".h", ".cuh")))
     out = os.path.join(LIB_DIR, LIB_NAME)
     stamp = os.path.join(LIB_DIR, LIB_NAME + ".stamp")
-    digest = _digest([os.path.join(CSRC, f) for f in cu + cpp + headers], torch.__version__)
+    digest = _digest([os.path.join(CSRC, f) for f in cu + cpp + headers] + [__file__],
+                     torch.__version__)
     if (not force and os.path.isfile(out) and os.path.isfile(stamp)
             and open(stamp).read().strip() == digest):
         return out
@@ -84,7 +88,8 @@ def build(verbose: bool = False, force: bool = False) -> str:
     for f in cu:
         o = os.path.join(OBJ_DIR, f + ".o")
         objs.append(o)
-        jobs.append([nvcc, *ARCH_FLAGS, "-lineinfo", "-O3", "-std=c++17", "--use_fast_math",
+        fast = [] if f in PRECISE_MATH else ["--use_fast_math"]
+        jobs.append([nvcc, *ARCH_FLAGS, "-lineinfo", "-O3", "-std=c++17", *fast,
                      "-Xcompiler", "-fPIC", "-I", CSRC, "-c", os.path.join(CSRC, f), "-o", o])
     for f in cpp:
         o = os.path.join(OBJ_DIR, f + ".o")

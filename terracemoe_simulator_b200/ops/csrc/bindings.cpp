@@ -20,6 +20,7 @@
 #include <vector>
 
 #include "launch.h"
+#include "meta.h"
 #include "symm.h"
 
 namespace {
@@ -233,6 +234,41 @@ Tup5 route_select(const Tensor& logits, const Tensor& bias, int64_t n_groups, in
                               cur_stream()),
            "route_select");
   return {idx, gates, gidx, load, aff};
+}
+
+// Router GEMM + T-Route selection in one launch: hidden [T, H] bf16, weight [E, H] bf16.
+std::tuple<Tensor, Tensor, Tensor, Tensor, Tensor> route_fused(
+    const Tensor& hidden, const Tensor& weight, const Tensor& bias, int64_t n_groups,
+    int64_t top_k, int64_t top_groups, int64_t pool) {
+  CHECK_CUDA_CONTIG(hidden);
+  CHECK_CUDA_CONTIG(weight);
+  CHECK_CUDA_CONTIG(bias);
+  TORCH_CHECK(hidden.dim() == 2 && weight.dim() == 2 && hidden.size(1) == weight.size(1) &&
+                  hidden.scalar_type() == at::kBFloat16 && weight.scalar_type() == at::kBFloat16,
+              "route_fused: bf16 hidden [T, H] and weight [E, H]");
+  TORCH_CHECK(bias.scalar_type() == at::kFloat && bias.numel() == weight.size(0),
+              "route_fused: fp32 bias [E]");
+  const int T = static_cast<int>(hidden.size(0)), H = static_cast<int>(hidden.size(1));
+  const int E = static_cast<int>(weight.size(0));
+  TORCH_CHECK(tb200_route_fused_supported(E, H, n_groups, top_k, top_groups),
+              "route_fused: unsupported router geometry (E <= 128 and E % 16 == 0 required)");
+  c10::cuda::CUDAGuard guard(hidden.device());
+  auto fopt = hidden.options().dtype(at::kFloat);
+  auto lopt = hidden.options().dtype(at::kLong);
+  Tensor idx = at::empty({T, top_k}, lopt), gidx = at::empty({T, top_groups}, lopt);
+  Tensor gates = at::empty({T, top_k}, fopt), aff = at::empty({T, top_k}, fopt);
+  Tensor load = at::zeros({E}, fopt);
+  check_rc(tb200_route_fused(hidden.data_ptr(), weight.data_ptr(), bias.data_ptr<float>(),
+                             i64(idx), gates.data_ptr<float>(), i64(gidx), load.data_ptr<float>(),
+                             aff.data_ptr<float>(), T, E, H, n_groups, top_k, top_groups, pool,
+                             status_ptr(hidden), cur_stream()),
+           "route_fused");
+  return {idx, gates, gidx, load, aff};
+}
+
+bool route_fused_supported(int64_t E, int64_t H, int64_t n_groups, int64_t top_k,
+                           int64_t top_groups) {
+  return tb200_route_fused_supported(E, H, n_groups, top_k, top_groups) != 0;
 }
 
 Tensor route_select_bwd(const Tensor& dgates, const Tensor& gates, const Tensor& aff,
@@ -524,34 +560,32 @@ TORCH_LIBRARY(terrace, m) {
   m.def("k2_pack(Tensor hidden, Tensor expert_idx, Tensor gates, int world, int n_experts, "
         "int rpn, int groups_m) -> (Tensor, Tensor, Tensor, Tensor, Tensor)");
   m.def("take_status(int device) -> int", &take_status);
-  m.def("rmsnorm_fwd(Tensor x, Tensor w, float eps) -> (Tensor, Tensor)", &rmsnorm_fwd);
-  m.def("rmsnorm_bwd(Tensor x, Tensor w, Tensor dy, Tensor rstd) -> (Tensor, Tensor)",
-        &rmsnorm_bwd);
+  m.def("rmsnorm_fwd(Tensor x, Tensor w, float eps) -> (Tensor, Tensor)");
+  m.def("rmsnorm_bwd(Tensor x, Tensor w, Tensor dy, Tensor rstd) -> (Tensor, Tensor)");
   m.def("route_select(Tensor logits, Tensor bias, int n_groups, int top_k, int top_groups, "
-        "int pool) -> (Tensor, Tensor, Tensor, Tensor, Tensor)", &route_select);
-  m.def("route_select_bwd(Tensor dgates, Tensor gates, Tensor aff, Tensor idx, int E) -> Tensor",
-        &route_select_bwd);
+        "int pool) -> (Tensor, Tensor, Tensor, Tensor, Tensor)");
+  m.def("route_fused(Tensor hidden, Tensor weight, Tensor bias, int n_groups, int top_k, "
+        "int top_groups, int pool) -> (Tensor, Tensor, Tensor, Tensor, Tensor)");
+  m.def("route_fused_supported(int E, int H, int n_groups, int top_k, int top_groups) -> bool",
+        &route_fused_supported);
+  m.def("route_select_bwd(Tensor dgates, Tensor gates, Tensor aff, Tensor idx, int E) -> Tensor");
   m.def("moe_plan(Tensor expert_idx, Tensor? gates, int E, int seg_align) -> "
-        "(Tensor, Tensor, Tensor, Tensor, Tensor, Tensor)", &moe_plan);
-  m.def("moe_scatter_rows(Tensor x, Tensor pos, int rows_out) -> Tensor", &moe_scatter_rows);
-  m.def("moe_combine(Tensor out, Tensor pos, Tensor es, Tensor? gs, int group_size) -> Tensor",
-        &moe_combine);
+        "(Tensor, Tensor, Tensor, Tensor, Tensor, Tensor)");
+  m.def("moe_scatter_rows(Tensor x, Tensor pos, int rows_out) -> Tensor");
+  m.def("moe_combine(Tensor out, Tensor pos, Tensor es, Tensor? gs, int group_size) -> Tensor");
   m.def("moe_combine_bwd(Tensor dy, Tensor out, Tensor pos, Tensor? gs, bool need_dgs) -> "
-        "(Tensor, Tensor)", &moe_combine_bwd);
-  m.def("swiglu_bwd(Tensor h13, Tensor dact) -> Tensor", &swiglu_bwd);
+        "(Tensor, Tensor)");
+  m.def("swiglu_bwd(Tensor h13, Tensor dact) -> Tensor");
   m.def("grouped_gemm(Tensor A, Tensor B, Tensor seg_start, Tensor seg_count, int mode, "
-        "int epilogue, bool save_pre, int max_ctas, int pad_align=0) -> (Tensor, Tensor)",
-        &grouped_gemm);
+        "int epilogue, bool save_pre, int max_ctas, int pad_align=0) -> (Tensor, Tensor)");
   m.def("grouped_wgrad(Tensor X, Tensor dY, Tensor seg_start, Tensor seg_count, int max_ctas, "
-        "int pad_align=0) -> Tensor", &grouped_wgrad);
+        "int pad_align=0) -> Tensor");
   m.def("grouped_wgrad_out(Tensor X, Tensor dY, Tensor(a!) dW, int g0, Tensor seg_start, "
-        "Tensor seg_count, int max_ctas, int pad_align=0) -> ()", &grouped_wgrad_out);
-  m.def("zero_pad_rows(Tensor(a!) buf, Tensor seg_start, Tensor seg_count, int align) -> ()",
-        &zero_pad_rows);
-  m.def("attn_fwd(Tensor q, Tensor k, Tensor v, bool causal, float scale) -> (Tensor, Tensor)",
-        &attn_fwd);
+        "Tensor seg_count, int max_ctas, int pad_align=0) -> ()");
+  m.def("zero_pad_rows(Tensor(a!) buf, Tensor seg_start, Tensor seg_count, int align) -> ()");
+  m.def("attn_fwd(Tensor q, Tensor k, Tensor v, bool causal, float scale) -> (Tensor, Tensor)");
   m.def("attn_bwd(Tensor q, Tensor k, Tensor v, Tensor o, Tensor d_o, Tensor lse, bool causal, "
-        "float scale) -> (Tensor, Tensor, Tensor)", &attn_bwd);
+        "float scale) -> (Tensor, Tensor, Tensor)");
   terrace_b200_register_symm(m);
 }
 
@@ -559,10 +593,28 @@ TORCH_LIBRARY_IMPL(terrace, CUDA, m) {
   m.impl("passthrough", &passthrough_cuda);
   m.impl("k1_arrival", &k1_arrival_cuda);
   m.impl("k2_pack", &k2_pack_cuda);
+  m.impl("rmsnorm_fwd", &rmsnorm_fwd);
+  m.impl("rmsnorm_bwd", &rmsnorm_bwd);
+  m.impl("route_select", &route_select);
+  m.impl("route_fused", &route_fused);
+  m.impl("route_select_bwd", &route_select_bwd);
+  m.impl("moe_plan", &moe_plan);
+  m.impl("moe_scatter_rows", &moe_scatter_rows);
+  m.impl("moe_combine", &moe_combine);
+  m.impl("moe_combine_bwd", &moe_combine_bwd);
+  m.impl("swiglu_bwd", &swiglu_bwd);
+  m.impl("grouped_gemm", &grouped_gemm);
+  m.impl("grouped_wgrad", &grouped_wgrad);
+  m.impl("grouped_wgrad_out", &grouped_wgrad_out);
+  m.impl("zero_pad_rows", &zero_pad_rows);
+  m.impl("attn_fwd", &attn_fwd);
+  m.impl("attn_bwd", &attn_bwd);
+  terrace_b200_register_symm_cuda(m);
 }
 
 TORCH_LIBRARY_IMPL(terrace, Meta, m) {
   m.impl("passthrough", &passthrough_meta);
   m.impl("k1_arrival", &k1_arrival_meta);
   m.impl("k2_pack", &k2_pack_meta);
+  terrace_b200_register_meta(m);
 }

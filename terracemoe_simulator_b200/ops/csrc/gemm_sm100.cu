@@ -27,6 +27,7 @@
 #include "host_util.h"
 #include "launch.h"
 #include "ptx_sm100.cuh"
+#include "tmap.h"
 
 #include <cuda.h>
 #include <cuda_runtime.h>
@@ -725,8 +726,8 @@ struct TmapSlot {
 };
 constexpr int TMAP_SLOTS = 512;          // direct-mapped; a collision just re-encodes
 
-static int make_tmap(CUtensorMap* out, const void* base, int rank, const uint64_t* dims,
-                     const uint64_t* strides_bytes, const uint32_t* box) {
+int make_tmap(CUtensorMap* out, const void* base, int rank, const uint64_t* dims,
+              const uint64_t* strides_bytes, const uint32_t* box) {
   static TmapSlot table[TMAP_SLOTS];
   static std::mutex mu;
   TmapKey key;

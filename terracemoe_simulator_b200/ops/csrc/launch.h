@@ -75,6 +75,13 @@ int tb200_rmsnorm_bwd(const void* x, const void* w, const void* dy, const float*
 int tb200_route_select(const float* logits, const float* bias, long long* idx, float* gates,
                        long long* group_idx, float* load, float* affinity_sel, int T, int E,
                        int n_groups, int top_k, int top_groups, int pool, cudaStream_t stream);
+// The same selection fused behind the router GEMM (router_sm100.cu): x[T, H] and w[E, H] bf16,
+// logits accumulate in TMEM and never reach memory.  E <= 128 and a multiple of 16.
+int tb200_route_fused_supported(int E, int H, int n_groups, int top_k, int top_groups);
+int tb200_route_fused(const void* x, const void* w, const float* bias, long long* idx,
+                      float* gates, long long* group_idx, float* load, float* affinity_sel, int T,
+                      int E, int H, int n_groups, int top_k, int top_groups, int pool, int* status,
+                      cudaStream_t stream);
 // dlogits[T, E] (pre-zeroed) from dgates[T, k]: through the renormalisation and the sigmoid.
 int tb200_route_select_bwd(const float* dgates, const float* gates, const float* affinity_sel,
                            const long long* idx, float* dlogits, int T, int E, int top_k,

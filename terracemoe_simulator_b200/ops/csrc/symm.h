@@ -3,3 +3,4 @@
 #include <torch/library.h>
 
 void terrace_b200_register_symm(torch::Library& m);
+void terrace_b200_register_symm_cuda(torch::Library& m);

@@ -448,38 +448,54 @@ void terrace_b200_register_symm(torch::Library& m) {
   m.def("symm_ipc_close(int ptr, int device) -> ()", &symm_ipc_close);
   m.def("symm_make_arena(int[] peers, int[] offsets, int[] geom) -> Tensor", &symm_make_arena);
   m.def("ep_plan_pass1(Tensor expert_idx, Tensor gates, int E) -> "
-        "(Tensor, Tensor, Tensor, Tensor, Tensor)", &ep_plan_pass1);
+        "(Tensor, Tensor, Tensor, Tensor, Tensor)");
   m.def("ep_plan(Tensor arena, Tensor(a!) chunk_hist, Tensor(b!)? chunka_hist, int epoch, "
-        "int seg_align=1) -> (Tensor, Tensor, Tensor, Tensor)", &ep_plan);
+        "int seg_align=1) -> (Tensor, Tensor, Tensor, Tensor)");
   m.def("ep_push(Tensor arena, Tensor x, Tensor es, Tensor rank_local, Tensor chunk_base, "
         "Tensor my_base, Tensor? gs, Tensor(a!) pos, Tensor(b!)? dgs, int dst_off, int dot_off, "
         "bool dot_local, int flag_kind, int flag_value, int le_lo, int le_hi, Tensor(c!) done, "
-        "int rowmap_off, int ret_slots) -> ()", &ep_push);
+        "int rowmap_off, int ret_slots) -> ()");
   m.def("ep_signal(Tensor arena, int kind, int first, int n, int stride, int idx, int epoch, "
-        "int wait_kind, int wait_first, int wait_n, int wait_value, Tensor like) -> ()",
-        &ep_signal);
+        "int wait_kind, int wait_first, int wait_n, int wait_value, Tensor like) -> ()");
   m.def("ep_pull_combine(Tensor arena, Tensor pos, Tensor es, Tensor? gs, int src_off, "
-        "int group_size, int wait_kind, int epoch, int local_slots=0) -> Tensor",
-        &ep_pull_combine);
+        "int group_size, int wait_kind, int epoch, int local_slots=0) -> Tensor");
   m.def("grouped_gemm_scatter(Tensor A, Tensor B, Tensor seg_start, Tensor seg_count, int mode, "
-        "Tensor row_map, Tensor scatter_base, int slots) -> ()", &grouped_gemm_scatter);
-  m.def("hopa_rank(Tensor arena, Tensor es) -> (Tensor, Tensor)", &hopa_rank);
+        "Tensor row_map, Tensor scatter_base, int slots) -> ()");
+  m.def("hopa_rank(Tensor arena, Tensor es) -> (Tensor, Tensor)");
   m.def("hopa_push(Tensor arena, Tensor x, Tensor es, Tensor gs, Tensor rank_local, "
         "Tensor chunk_base, Tensor my_base, Tensor ranka_local, Tensor chunka_base, "
         "Tensor? rowa_in, int rows_sel, bool with_header, int flag_kind, int epoch, "
-        "Tensor(a!) done) -> (Tensor, Tensor)", &hopa_push);
+        "Tensor(a!) done) -> (Tensor, Tensor)");
   m.def("arrival_push(Tensor arena, Tensor rows_a, int rows_sel, int dst_off, int dot_off, "
         "bool dot_local, bool scale_gate, bool want_dgate, int wait_kind, int data_kind, "
         "int dg_kind, int epoch, int flag_value, int le_lo, int le_hi, Tensor(a!) done, "
-        "int rowmap_off) -> ()", &arrival_push);
+        "int rowmap_off) -> ()");
   m.def("arrival_combine(Tensor arena, Tensor rows_a, int src_off, int red_sel, bool use_gate, "
         "int wait_kind, int red_kind, int epoch, Tensor(a!) done, bool push_back=False, "
-        "bool local_slots=False) -> ()", &arrival_combine);
+        "bool local_slots=False) -> ()");
   m.def("origin_combine(Tensor arena, Tensor es, Tensor rowa, int red_sel, int wait_kind, "
-        "int epoch, bool local_rows=False) -> Tensor", &origin_combine);
+        "int epoch, bool local_rows=False) -> Tensor");
   m.def("origin_pull_dgate(Tensor arena, Tensor es, Tensor rowa, int wait_kind, int epoch) -> "
-        "Tensor", &origin_pull_dgate);
+        "Tensor");
   m.def("grouped_gemm_ex(Tensor A, Tensor B, Tensor(a!) C, Tensor(b!)? C2, Tensor seg_start, "
         "Tensor seg_count, int mode, int epilogue, Tensor? arena, int wait_kind, int wait_first, "
-        "int wait_n, int epoch, int pad_align=0) -> ()", &grouped_gemm_ex);
+        "int wait_n, int epoch, int pad_align=0) -> ()");
+}
+
+// The device implementations of the ops declared above (every op that takes a CUDA tensor);
+// the host-only ops (allocation, IPC, status) stay catch-all functions.
+void terrace_b200_register_symm_cuda(torch::Library& m) {
+  m.impl("ep_plan_pass1", &ep_plan_pass1);
+  m.impl("ep_plan", &ep_plan);
+  m.impl("ep_push", &ep_push);
+  m.impl("ep_signal", &ep_signal);
+  m.impl("ep_pull_combine", &ep_pull_combine);
+  m.impl("grouped_gemm_scatter", &grouped_gemm_scatter);
+  m.impl("hopa_rank", &hopa_rank);
+  m.impl("hopa_push", &hopa_push);
+  m.impl("arrival_push", &arrival_push);
+  m.impl("arrival_combine", &arrival_combine);
+  m.impl("origin_combine", &origin_combine);
+  m.impl("origin_pull_dgate", &origin_pull_dgate);
+  m.impl("grouped_gemm_ex", &grouped_gemm_ex);
 }

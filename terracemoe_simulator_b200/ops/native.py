@@ -14,7 +14,7 @@ from __future__ import annotations
 
 import torch
 
-LIVE = {"rmsnorm": 0, "route": 0, "linear": 0, "swiglu_ffn": 0, "grouped_mm": 0,
+LIVE = {"rmsnorm": 0, "route": 0, "route_fused": 0, "linear": 0, "swiglu_ffn": 0, "grouped_mm": 0,
         "moe_experts_local": 0, "attention": 0}
 
 
@@ -24,7 +24,7 @@ LAUNCHES = [0]
 
 class _Counted:
     """Proxy of ``torch.ops.terrace`` that counts kernel launches per op call."""
-    _PER_CALL = {"rmsnorm_fwd": 1, "rmsnorm_bwd": 1, "route_select": 1, "route_select_bwd": 1,
+    _PER_CALL = {"rmsnorm_fwd": 1, "rmsnorm_bwd": 1, "route_select": 1, "route_select_bwd": 1, "route_fused": 1,
                  "moe_plan": 3, "moe_scatter_rows": 1, "moe_combine": 1, "moe_combine_bwd": 1,
                  "swiglu_bwd": 1, "grouped_gemm": 1, "grouped_wgrad": 1, "passthrough": 1,
                  "zero_pad_rows": 1,
@@ -248,13 +248,61 @@ def route_from_logits(logits, bias, cfg):
                               cfg.group_score_pool)
 
 
-def fused_route(hidden, weight, bias, cfg):
+class _RouteFused(torch.autograd.Function):
+    """Router GEMM and T-Route selection (mode ``full``, sigmoid scores) in one launch; the
+    logits stay in TMEM.  Backward: the gate gradients go back through the renormalisation and
+    the sigmoid to ``dlogits`` (one launch), then through the router GEMM to the hidden states
+    and the router weight (two launches of the dense kernels)."""
+
+    @staticmethod
+    def forward(ctx, hidden, weight, bias, n_groups, top_k, top_groups, pool):
+        h2, w = hidden.contiguous(), weight.contiguous()
+        idx, gates, gidx, load, aff = _lib().route_fused(
+            h2, w, bias.float().contiguous(), n_groups, top_k, top_groups, pool)
+        ctx.save_for_backward(h2, w, gates, aff, idx)
+        ctx.mark_non_differentiable(idx, gidx, load)
+        LIVE["route_fused"] += 1
+        return idx, gates, gidx, load
+
+    @staticmethod
+    def backward(ctx, _di, dgates, _dg, _dl):
+        h2, w, gates, aff, idx = ctx.saved_tensors
+        lib = _lib()
+        dlogits = lib.route_select_bwd(dgates.contiguous(), gates, aff, idx, w.shape[0])
+        dl = dlogits.to(h2.dtype)
+        s, c = _one_segment(h2.shape[0], h2.device)
+        dh = dw = None
+        if ctx.needs_input_grad[0]:
+            dh, _ = lib.grouped_gemm(dl, w.unsqueeze(0), s, c, 0, 0, False, 0)
+        if ctx.needs_input_grad[1]:
+            dw = lib.grouped_wgrad(dl, h2, s, c, 0)[0]
+        return dh, dw, None, None, None, None, None
+
+
+def route_fused_supported(cfg, hidden, weight) -> bool:
+    """One-launch router: bf16 hidden states and weight, at most 128 experts (multiple of 16)."""
+    if not (_bf16_cuda(hidden, weight) and hidden.shape[-1] == weight.shape[-1]):
+        return False
+    return bool(torch.ops.terrace.route_fused_supported(
+        cfg.n_experts, hidden.shape[-1], cfg.n_groups, cfg.top_k, cfg.top_groups))
+
+
+def route_hidden(hidden, weight, bias, cfg):
+    """T-Route (mode ``full``) from hidden states ``[T, H]``: ``(idx, gates fp32, group_idx,
+    load)``.  One fused launch when the geometry allows, else router GEMM + select kernel."""
     h2 = hidden.reshape(-1, hidden.shape[-1])
+    if route_fused_supported(cfg, h2, weight):
+        return _RouteFused.apply(h2, weight, bias, cfg.n_groups, cfg.top_k, cfg.top_groups,
+                                 cfg.group_score_pool)
     if dense_supported(h2, weight):
         logits = linear(h2, weight)
     else:
         logits = h2 @ weight.t().to(h2.dtype)
-    idx, gates, gidx, _load = route_from_logits(logits, bias, cfg)
+    return route_from_logits(logits, bias, cfg)
+
+
+def fused_route(hidden, weight, bias, cfg):
+    idx, gates, gidx, _load = route_hidden(hidden, weight, bias, cfg)
     return idx, gates, gidx
 
 

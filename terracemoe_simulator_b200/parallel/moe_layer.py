@@ -33,12 +33,7 @@ EP_MODES = ("local", "one_hop", "two_hop")
 def _route(x, router_w, bias, cfg):
     """Router logits + T-Route; native kernels when available."""
     if x.is_cuda and ops.custom_ops_enabled() and ops.router_supported(cfg, x):
-        if ops.dense_supported(x, router_w):
-            logits = ops.linear(x, router_w)
-        else:
-            logits = x @ router_w.t().to(x.dtype)
-        idx, gates, gidx, load = ops.route_from_logits(logits, bias, cfg)
-        return idx, gates, gidx, load
+        return ops.route_hidden(x, router_w, bias, cfg)
     aff = torch.sigmoid((x @ router_w.t().to(x.dtype)).float())
     idx, gates, gidx = t_route(aff, bias.float(), cfg, "full")
     return idx, gates, gidx, expert_load(idx, cfg.n_experts)
