@@ -129,9 +129,12 @@ size_t tb200_k2_scratch_ints(int T, int k, int groups_m, int n_nodes);
 
 // ---- symm.cu -----------------------------------------------------------------------------------
 struct Tb200Arena;
+// cap > 0: capacity per expert (rows accepted in canonical order: source rank, then token);
+// my_prefix[E] receives the rows of lower source ranks per expert, which the push kernels need
+// to decide, without any further exchange, which of their picks fall beyond the capacity.
 int tb200_ep_plan(const struct Tb200Arena* a, int* chunk_hist, int* chunka_hist, int* my_base,
-                  int* seg_start, int* seg_count, int* rows_a, int epoch, int seg_align,
-                  int* status, cudaStream_t stream);
+                  int* seg_start, int* seg_count, int* rows_a, int* my_prefix, int epoch,
+                  int seg_align, int cap, int* status, cudaStream_t stream);
 // The push kernels cover the picks of LOCAL experts [le_lo, le_hi) (0 .. epr = all) and raise the
 // owners' arrival flags to `flag_value` when their rows have landed; a step that sends in several
 // launches passes growing values, and each owner GEMM waits for the value of its expert range.
@@ -139,7 +142,8 @@ int tb200_ep_push(const struct Tb200Arena* a, const void* x, const int* es, cons
                   const int* chunk_base, const int* my_base, int* pos_out, const float* gs,
                   float* dgs, long long off_dst, long long off_dot, int T, int flag_kind,
                   int flag_value, int le_lo, int le_hi, int* done_counter, int* status,
-                  long long off_rowmap, int ret_slots, int dot_local, cudaStream_t stream);
+                  long long off_rowmap, int ret_slots, int dot_local, const int* my_prefix,
+                  int cap, cudaStream_t stream);
 int tb200_signal(const struct Tb200Arena* a, int kind, int first, int n, int stride, int idx,
                  int epoch, int wait_kind, int wait_first, int wait_n, int wait_value, int* status,
                  cudaStream_t stream);
@@ -153,7 +157,8 @@ int tb200_hopa_push(const struct Tb200Arena* a, const void* x, const int* es, co
                     const int* rank_local, const int* chunk_base, const int* my_base,
                     const int* ranka_local, const int* chunka_base, int* pos_out, int* rowa,
                     long long off_rows, int with_header, int T, int flag_kind, int epoch,
-                    int* done_counter, int* status, cudaStream_t stream);
+                    int* done_counter, int* status, const int* my_prefix, int cap,
+                    cudaStream_t stream);
 int tb200_arrival_push(const struct Tb200Arena* a, const int* rows_a, long long off_rows,
                        long long off_dst, long long off_dot, int scale_gate, int want_dgate,
                        int wait_kind, int data_kind, int dg_kind, int epoch, int flag_value,

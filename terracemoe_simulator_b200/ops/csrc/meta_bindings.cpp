@@ -136,16 +136,19 @@ std::tuple<Tensor, Tensor, Tensor, Tensor, Tensor> ep_plan_pass1(const Tensor& e
   return {i({T, k}), at::empty_like(gates), i({T, k}), i({T, k}), i({TB200_PLAN_CHUNKS, E})};
 }
 
-std::tuple<Tensor, Tensor, Tensor, Tensor> ep_plan(const Tensor& arena, Tensor chunk_hist,
-                                                   const OptTensor&, int64_t, int64_t) {
+std::tuple<Tensor, Tensor, Tensor, Tensor, Tensor> ep_plan(const Tensor& arena, Tensor chunk_hist,
+                                                           const OptTensor&, int64_t, int64_t,
+                                                           int64_t) {
   const Tb200Arena* a = arena_of(arena);
   auto i = [&](at::IntArrayRef s) { return like(chunk_hist, s, at::kInt); };
-  return {i({a->n_experts}), i({a->epr}), i({a->epr}), i({a->world, a->n_nodes})};
+  return {i({a->n_experts}), i({a->epr}), i({a->epr}), i({a->world, a->n_nodes}),
+          i({a->n_experts})};
 }
 
 void ep_push(const Tensor&, const Tensor&, const Tensor&, const Tensor&, const Tensor&,
              const Tensor&, const OptTensor&, Tensor, const OptTensor&, int64_t, int64_t, bool,
-             int64_t, int64_t, int64_t, int64_t, Tensor, int64_t, int64_t) {}
+             int64_t, int64_t, int64_t, int64_t, Tensor, int64_t, int64_t, const OptTensor&,
+             int64_t) {}
 
 void ep_signal(const Tensor&, int64_t, int64_t, int64_t, int64_t, int64_t, int64_t, int64_t,
                int64_t, int64_t, int64_t, const Tensor&) {}
@@ -167,7 +170,8 @@ std::tuple<Tensor, Tensor> hopa_rank(const Tensor& arena, const Tensor& es) {
 std::tuple<Tensor, Tensor> hopa_push(const Tensor& arena, const Tensor& x, const Tensor& es,
                                      const Tensor&, const Tensor&, const Tensor&, const Tensor&,
                                      const Tensor&, const Tensor&, const OptTensor& rowa_in,
-                                     int64_t, bool with_header, int64_t, int64_t, Tensor) {
+                                     int64_t, bool with_header, int64_t, int64_t, Tensor,
+                                     const OptTensor&, int64_t) {
   const Tb200Arena* a = arena_of(arena);
   const int64_t T = x.size(0);
   if (!with_header) return {like(es, {0}, at::kInt), *rowa_in};

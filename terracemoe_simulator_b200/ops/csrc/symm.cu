@@ -132,9 +132,12 @@ struct PlanTables {
   int* seg_start;     // [epr] local GEMM segments
   int* seg_count;     // [epr]
   int* rows_a;        // [W][N_g] Hop A rows rank s sends to group g
+  int* my_prefix;     // [E]  rows of lower source ranks in expert e (my first row's rank in e)
 };
 
-__global__ void ep_plan_kernel(Tb200Arena a, PlanTables t, int epoch, int seg_align,
+// cap > 0: every expert accepts at most `cap` rows, in canonical order (source rank, token);
+// segments shrink to min(total, cap) and the push kernels drop the picks beyond it.
+__global__ void ep_plan_kernel(Tb200Arena a, PlanTables t, int epoch, int seg_align, int cap,
                                int* status) {
   extern __shared__ int sm[];
   const int E = a.n_experts, W = a.world;
@@ -173,7 +176,7 @@ __global__ void ep_plan_kernel(Tb200Arena a, PlanTables t, int epoch, int seg_al
       total += v;
     }
     src_prefix[e] = before;
-    tot_all[e] = total;
+    tot_all[e] = (cap > 0 && total > cap) ? cap : total;
   }
   __syncthreads();
   if (static_cast<int>(threadIdx.x) < W) {          // thread o lays out owner o's segments
@@ -188,6 +191,7 @@ __global__ void ep_plan_kernel(Tb200Arena a, PlanTables t, int epoch, int seg_al
   __syncthreads();
   for (int e = threadIdx.x; e < E; e += blockDim.x) {
     t.my_base[e] = seg_g[e] + src_prefix[e];
+    t.my_prefix[e] = src_prefix[e];
     if (e / a.epr == a.rank) {
       t.seg_start[e - a.rank * a.epr] = seg_g[e];
       t.seg_count[e - a.rank * a.epr] = tot_all[e];
@@ -220,7 +224,7 @@ __global__ void ep_push_kernel(Tb200Arena a, const __nv_bfloat16* __restrict__ x
                                float* __restrict__ dgs, long long off_dst, long long off_dot,
                                int T, int flag_kind, int flag_value, int le_lo, int le_hi,
                                int* done_counter, int* status, long long off_rowmap, int ret_slots,
-                               int dot_local) {
+                               int dot_local, const int* __restrict__ my_prefix, int cap) {
   const int lane = threadIdx.x & 31;
   const int k = a.top_k, H = a.hidden;
   const int n_pairs = T * k;
@@ -232,12 +236,16 @@ __global__ void ep_push_kernel(Tb200Arena a, const __nv_bfloat16* __restrict__ x
     if (!in_chunk(e, a.n_experts, a.epr, le_lo, le_hi)) continue;
     const int r = rank_local[p];
     int pos = -1;
-    if (r >= 0 && e >= 0 && e < a.n_experts)
-      pos = my_base[e] + chunk_base[(t / per) * a.n_experts + e] + r;
+    bool dropped = false;        // beyond the expert's capacity: not an error, just not sent
+    if (r >= 0 && e >= 0 && e < a.n_experts) {
+      const int in_chunks = chunk_base[(t / per) * a.n_experts + e] + r;
+      dropped = cap > 0 && my_prefix[e] + in_chunks >= cap;
+      if (!dropped) pos = my_base[e] + in_chunks;
+    }
     if (pos_out && lane == 0) pos_out[p] = pos;
     if (pos < 0 || pos >= a.cap_rows) {
       if (lane == 0) {
-        if (status) atomicCAS(status, 0, ST_BAD_INDEX);
+        if (status && !dropped) atomicCAS(status, 0, ST_BAD_INDEX);
         if (dgs) dgs[p] = 0.f;
       }
       continue;
@@ -411,7 +419,8 @@ __global__ void hopa_push_kernel(Tb200Arena a, const __nv_bfloat16* __restrict__
                                  const int* __restrict__ ranka_local,
                                  const int* __restrict__ chunka_base, int* __restrict__ pos_out,
                                  int* __restrict__ rowa_out, long long off_rows, int with_header,
-                                 int T, int flag_kind, int epoch, int* done_counter, int* status) {
+                                 int T, int flag_kind, int epoch, int* done_counter, int* status,
+                                 const int* __restrict__ my_prefix, int cap) {
   const int lane = threadIdx.x & 31;
   const int k = a.top_k, H = a.hidden, M = a.groups_m, q = a.q;
   const int slots = a.epr * a.rpn;
@@ -440,9 +449,11 @@ __global__ void hopa_push_kernel(Tb200Arena a, const __nv_bfloat16* __restrict__
       const int p = t * k + m * q + lane;
       const int e = es[p];
       const int r = rank_local[p];
-      int pos = -1;
-      if (r >= 0 && e >= 0 && e < a.n_experts)
-        pos = my_base[e] + chunk_base[(t / per) * a.n_experts + e] + r;
+      int pos = -1;            // also what a pick beyond the expert's capacity carries
+      if (r >= 0 && e >= 0 && e < a.n_experts) {
+        const int in_chunks = chunk_base[(t / per) * a.n_experts + e] + r;
+        if (!(cap > 0 && my_prefix[e] + in_chunks >= cap)) pos = my_base[e] + in_chunks;
+      }
       pos_out[p] = pos;
       int* hdr = sect<int>(a, rep, a.off_ha_hdr) + static_cast<size_t>(dst_row) * 3 * q;
       hdr[lane] = pos;
@@ -498,7 +509,9 @@ __global__ void arrival_push_kernel(Tb200Arena a, const int* __restrict__ rows_a
     if (pos < 0 || pos >= a.cap_rows || e < 0 || e >= a.n_experts ||
         e / (a.epr * a.rpn) != my_group) {
       if (lane == 0) {
-        if (status) atomicCAS(status, 0, ST_BAD_INDEX);
+        // pos == -1 with a valid expert: the origin dropped the pick (capacity), no error
+        const bool dropped = pos == -1 && e >= 0 && e < a.n_experts;
+        if (status && !dropped) atomicCAS(status, 0, ST_BAD_INDEX);
         if (want_dgate) dgate[static_cast<size_t>(row) * q + c] = 0.f;
       }
       continue;
@@ -691,12 +704,12 @@ static bool arena_ok(const Tb200Arena* a) {
 }
 
 extern "C" int tb200_ep_plan(const Tb200Arena* a, int* chunk_hist, int* chunka_hist, int* my_base,
-                             int* seg_start, int* seg_count, int* rows_a, int epoch, int seg_align,
-                             int* status, cudaStream_t stream) {
-  if (!arena_ok(a) || seg_align < 1) return TB200_ERR_ARG;
-  PlanTables t{chunk_hist, chunka_hist, my_base, seg_start, seg_count, rows_a};
+                             int* seg_start, int* seg_count, int* rows_a, int* my_prefix,
+                             int epoch, int seg_align, int cap, int* status, cudaStream_t stream) {
+  if (!arena_ok(a) || seg_align < 1 || my_prefix == nullptr) return TB200_ERR_ARG;
+  PlanTables t{chunk_hist, chunka_hist, my_base, seg_start, seg_count, rows_a, my_prefix};
   ep_plan_kernel<<<1, 256, 4 * a->n_experts * sizeof(int), stream>>>(*a, t, epoch, seg_align,
-                                                                     status);
+                                                                     cap, status);
   return LAUNCH_OK();
 }
 
@@ -713,8 +726,10 @@ extern "C" int tb200_ep_push(const Tb200Arena* a, const void* x, const int* es,
                              int* pos_out, const float* gs, float* dgs, long long off_dst,
                              long long off_dot, int T, int flag_kind, int flag_value, int le_lo,
                              int le_hi, int* done_counter, int* status, long long off_rowmap,
-                             int ret_slots, int dot_local, cudaStream_t stream) {
+                             int ret_slots, int dot_local, const int* my_prefix, int cap,
+                             cudaStream_t stream) {
   if (!arena_ok(a) || le_lo < 0 || le_hi > a->epr || le_lo >= le_hi) return TB200_ERR_ARG;
+  if (cap > 0 && my_prefix == nullptr) return TB200_ERR_ARG;
   if ((off_rowmap >= 0 || dot_local) && ret_slots < T * a->top_k) return TB200_ERR_ARG;
   // a launch that covers a part of the experts touches about that share of the picks
   const long long items = static_cast<long long>(T) * a->top_k;
@@ -724,7 +739,7 @@ extern "C" int tb200_ep_push(const Tb200Arena* a, const void* x, const int* es,
                                              rank_local, chunk_base, my_base, pos_out, gs, dgs,
                                              off_dst, off_dot, T, flag_kind, flag_value, le_lo,
                                              le_hi, done_counter, status, off_rowmap, ret_slots,
-                                             dot_local);
+                                             dot_local, my_prefix, cap);
   return LAUNCH_OK();
 }
 
@@ -766,13 +781,14 @@ extern "C" int tb200_hopa_push(const Tb200Arena* a, const void* x, const int* es
                                const int* ranka_local, const int* chunka_base, int* pos_out,
                                int* rowa, long long off_rows, int with_header, int T,
                                int flag_kind, int epoch, int* done_counter, int* status,
-                               cudaStream_t stream) {
+                               const int* my_prefix, int cap, cudaStream_t stream) {
   if (!arena_ok(a) || T > a->tokens_cap) return TB200_ERR_ARG;
+  if (cap > 0 && my_prefix == nullptr) return TB200_ERR_ARG;
   const int blocks = warp_item_grid(static_cast<long long>(T) * a->groups_m);
   hopa_push_kernel<<<blocks, 256, 0, stream>>>(
       *a, static_cast<const __nv_bfloat16*>(x), es, gs, rank_local, chunk_base, my_base,
       ranka_local, chunka_base, pos_out, rowa, off_rows, with_header, T, flag_kind, epoch,
-      done_counter, status);
+      done_counter, status, my_prefix, cap);
   return LAUNCH_OK();
 }
 

@@ -166,22 +166,26 @@ std::tuple<Tensor, Tensor, Tensor, Tensor, Tensor> ep_plan_pass1(const Tensor& e
   return {es, gs, cols, rank_local, chunk_hist};
 }
 
-std::tuple<Tensor, Tensor, Tensor, Tensor> ep_plan(const Tensor& arena, Tensor chunk_hist,
-                                                   const c10::optional<Tensor>& chunka_hist,
-                                                   int64_t epoch, int64_t seg_align) {
+// Returns (my_base, seg_start, seg_count, rows_a, my_prefix).  cap > 0 bounds the rows every
+// expert accepts (canonical order: source rank, then token).
+std::tuple<Tensor, Tensor, Tensor, Tensor, Tensor> ep_plan(
+    const Tensor& arena, Tensor chunk_hist, const c10::optional<Tensor>& chunka_hist,
+    int64_t epoch, int64_t seg_align, int64_t cap) {
   const Tb200Arena* a = arena_of(arena);
   c10::cuda::CUDAGuard guard(chunk_hist.device());
   auto iopt = chunk_hist.options();
   Tensor my_base = at::empty({a->n_experts}, iopt);
   Tensor seg_start = at::empty({a->epr}, iopt), seg_count = at::empty({a->epr}, iopt);
   Tensor rows_a = at::zeros({a->world, a->n_nodes}, iopt);
+  Tensor my_prefix = at::empty({a->n_experts}, iopt);
   check_rc(tb200_ep_plan(a, chunk_hist.data_ptr<int>(),
                          chunka_hist.has_value() ? chunka_hist->data_ptr<int>() : nullptr,
                          my_base.data_ptr<int>(), seg_start.data_ptr<int>(),
-                         seg_count.data_ptr<int>(), rows_a.data_ptr<int>(), epoch,
-                         static_cast<int>(seg_align), st_ptr(chunk_hist), cur_stream()),
+                         seg_count.data_ptr<int>(), rows_a.data_ptr<int>(),
+                         my_prefix.data_ptr<int>(), epoch, static_cast<int>(seg_align),
+                         static_cast<int>(cap), st_ptr(chunk_hist), cur_stream()),
            "ep_plan");
-  return {my_base, seg_start, seg_count, rows_a};
+  return {my_base, seg_start, seg_count, rows_a, my_prefix};
 }
 
 // One-hop push of the picks whose local expert index lies in [le_lo, le_hi) into the owners'
@@ -195,7 +199,8 @@ void ep_push(const Tensor& arena, const Tensor& x, const Tensor& es, const Tenso
              const Tensor& chunk_base, const Tensor& my_base, const c10::optional<Tensor>& gs,
              Tensor pos, const c10::optional<Tensor>& dgs, int64_t dst_off, int64_t dot_off,
              bool dot_local, int64_t flag_kind, int64_t flag_value, int64_t le_lo, int64_t le_hi,
-             Tensor done, int64_t rowmap_off, int64_t ret_slots) {
+             Tensor done, int64_t rowmap_off, int64_t ret_slots,
+             const c10::optional<Tensor>& my_prefix, int64_t cap) {
   const Tb200Arena* a = arena_of(arena);
   TORCH_CHECK(rowmap_off < 0 || rowmap_off % 16 == 0, "ep_push: row map offset alignment");
   TORCH_CHECK(dst_off >= 0 && dst_off % 16 == 0 && dot_off % 16 == 0,
@@ -222,7 +227,9 @@ void ep_push(const Tensor& arena, const Tensor& x, const Tensor& es, const Tenso
                          want_dgs ? dgs->data_ptr<float>() : nullptr, dst_off,
                          want_dgs ? dot_off : 0, T, flag_kind, flag_value, le_lo, le_hi,
                          done.data_ptr<int>(), st_ptr(x), rowmap_off, static_cast<int>(ret_slots),
-                         dot_local ? 1 : 0, cur_stream()),
+                         dot_local ? 1 : 0,
+                         my_prefix.has_value() ? my_prefix->data_ptr<int>() : nullptr,
+                         my_prefix.has_value() ? static_cast<int>(cap) : 0, cur_stream()),
            "ep_push");
 }
 
@@ -276,7 +283,8 @@ std::tuple<Tensor, Tensor> hopa_push(const Tensor& arena, const Tensor& x, const
                                      const Tensor& ranka_local, const Tensor& chunka_base,
                                      const c10::optional<Tensor>& rowa_in, int64_t rows_sel,
                                      bool with_header, int64_t flag_kind, int64_t epoch,
-                                     Tensor done) {
+                                     Tensor done, const c10::optional<Tensor>& my_prefix,
+                                     int64_t cap) {
   const Tb200Arena* a = arena_of(arena);
   TORCH_CHECK(x.is_cuda() && x.is_contiguous() && x.scalar_type() == at::kBFloat16 &&
                   x.dim() == 2 && x.size(1) == a->hidden && x.size(0) <= a->tokens_cap,
@@ -291,7 +299,9 @@ std::tuple<Tensor, Tensor> hopa_push(const Tensor& arena, const Tensor& x, const
                            my_base.data_ptr<int>(), ranka_local.data_ptr<int>(),
                            chunka_base.data_ptr<int>(), with_header ? pos.data_ptr<int>() : nullptr,
                            rowa.data_ptr<int>(), section_offset(a, rows_sel), with_header ? 1 : 0,
-                           T, flag_kind, epoch, done.data_ptr<int>(), st_ptr(x), cur_stream()),
+                           T, flag_kind, epoch, done.data_ptr<int>(), st_ptr(x),
+                           my_prefix.has_value() ? my_prefix->data_ptr<int>() : nullptr,
+                           my_prefix.has_value() ? static_cast<int>(cap) : 0, cur_stream()),
            "hopa_push");
   return {pos, rowa};
 }
@@ -450,11 +460,11 @@ void terrace_b200_register_symm(torch::Library& m) {
   m.def("ep_plan_pass1(Tensor expert_idx, Tensor gates, int E) -> "
         "(Tensor, Tensor, Tensor, Tensor, Tensor)");
   m.def("ep_plan(Tensor arena, Tensor(a!) chunk_hist, Tensor(b!)? chunka_hist, int epoch, "
-        "int seg_align=1) -> (Tensor, Tensor, Tensor, Tensor)");
+        "int seg_align=1, int cap=0) -> (Tensor, Tensor, Tensor, Tensor, Tensor)");
   m.def("ep_push(Tensor arena, Tensor x, Tensor es, Tensor rank_local, Tensor chunk_base, "
         "Tensor my_base, Tensor? gs, Tensor(a!) pos, Tensor(b!)? dgs, int dst_off, int dot_off, "
         "bool dot_local, int flag_kind, int flag_value, int le_lo, int le_hi, Tensor(c!) done, "
-        "int rowmap_off, int ret_slots) -> ()");
+        "int rowmap_off, int ret_slots, Tensor? my_prefix=None, int cap=0) -> ()");
   m.def("ep_signal(Tensor arena, int kind, int first, int n, int stride, int idx, int epoch, "
         "int wait_kind, int wait_first, int wait_n, int wait_value, Tensor like) -> ()");
   m.def("ep_pull_combine(Tensor arena, Tensor pos, Tensor es, Tensor? gs, int src_off, "
@@ -465,7 +475,7 @@ void terrace_b200_register_symm(torch::Library& m) {
   m.def("hopa_push(Tensor arena, Tensor x, Tensor es, Tensor gs, Tensor rank_local, "
         "Tensor chunk_base, Tensor my_base, Tensor ranka_local, Tensor chunka_base, "
         "Tensor? rowa_in, int rows_sel, bool with_header, int flag_kind, int epoch, "
-        "Tensor(a!) done) -> (Tensor, Tensor)");
+        "Tensor(a!) done, Tensor? my_prefix=None, int cap=0) -> (Tensor, Tensor)");
   m.def("arrival_push(Tensor arena, Tensor rows_a, int rows_sel, int dst_off, int dot_off, "
         "bool dot_local, bool scale_gate, bool want_dgate, int wait_kind, int data_kind, "
         "int dg_kind, int epoch, int flag_value, int le_lo, int le_hi, Tensor(a!) done, "

@@ -46,6 +46,7 @@ issue 4 and 9 collectives with 1-3 host syncs per forward); the overlap window o
 """
 from __future__ import annotations
 
+import math
 import weakref
 
 import torch
@@ -306,18 +307,28 @@ class FusedEPContext:
         return torch.nonzero(bad).flatten().tolist()
 
 
-def _plan(ctx: FusedEPContext, idx, gates, mode: str, ep: int):
+def expert_capacity(capacity_factor, tokens_global: int, top_k: int, n_experts: int) -> int:
+    """Rows an expert accepts under ``capacity_factor`` (0 = unbounded); the formula of
+    ``layer.apply_capacity``."""
+    if capacity_factor is None:
+        return 0
+    return int(math.ceil(capacity_factor * tokens_global * top_k / n_experts))
+
+
+def _plan(ctx: FusedEPContext, idx, gates, mode: str, ep: int, cap: int = 0):
+    """``cap`` > 0: every expert accepts at most ``cap`` rows in canonical order (source rank,
+    then token); the picks beyond it get position -1, are not sent and contribute nothing."""
     lib = _lib()
     es, gs, cols, rank_local, chunk_hist = lib.ep_plan_pass1(
         idx.contiguous(), gates.detach().float().contiguous(), ctx.E)
     ranka = chunka = None
     if mode == "two_hop":
         ranka, chunka = lib.hopa_rank(ctx.arena, es)
-    my_base, seg_start, seg_count, rows_a = lib.ep_plan(ctx.arena, chunk_hist, chunka, ep,
-                                                        SEG_ALIGN)
+    my_base, seg_start, seg_count, rows_a, my_prefix = lib.ep_plan(
+        ctx.arena, chunk_hist, chunka, ep, SEG_ALIGN, int(cap))
     return dict(es=es, gs=gs, cols=cols, rank_local=rank_local, chunk_hist=chunk_hist,
                 ranka=ranka, chunka=chunka, my_base=my_base, seg_start=seg_start,
-                seg_count=seg_count, rows_a=rows_a)
+                seg_count=seg_count, rows_a=rows_a, my_prefix=my_prefix, cap=int(cap))
 
 
 def _push_launches(ctx, chunked: bool):
@@ -357,7 +368,8 @@ def _dispatch(ctx, p, x, mode: str, ep: int, *, backward: bool = False, chunked:
             lib.ep_push(ctx.arena, x, p["es"], p["rank_local"], p["chunk_hist"], p["my_base"],
                         p["gs"] if backward else None, pos, dgs, dst_off, dot_off, ov and backward,
                         data_kind, flag_value(ep, i, n), lo, hi, ctx.done[0:1],
-                        ctx.off["rowmap"] if (ov and not backward) else -1, ctx.ret_slots)
+                        ctx.off["rowmap"] if (ov and not backward) else -1, ctx.ret_slots,
+                        p["my_prefix"], p["cap"])
             mark(i)
         if not backward:
             p["pos"], p["rowa"] = pos, None
@@ -370,7 +382,8 @@ def _dispatch(ctx, p, x, mode: str, ep: int, *, backward: bool = False, chunked:
     else:
         pos, rowa = lib.hopa_push(ctx.arena, x, p["es"], p["gs"], p["rank_local"],
                                   p["chunk_hist"], p["my_base"], p["ranka"], p["chunka"], None,
-                                  HA_ROWS, True, FK_HOPA, ep, ctx.done[0:1])
+                                  HA_ROWS, True, FK_HOPA, ep, ctx.done[0:1], p["my_prefix"],
+                                  p["cap"])
         p["pos"], p["rowa"] = pos, rowa
     for i, n, lo, hi in launches:
         last = i == n - 1
@@ -434,7 +447,7 @@ def _combine(ctx, p, mode: str, ep: int, *, src: int, use_gate: bool, backward: 
 
 class _FusedMoE(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, x, gates, w13, w2, idx, fctx: FusedEPContext, mode: str):
+    def forward(ctx, x, gates, w13, w2, idx, fctx: FusedEPContext, mode: str, cap: int = 0):
         lib = _lib()
         need = any(ctx.needs_input_grad)
         if need:
@@ -445,7 +458,7 @@ class _FusedMoE(torch.autograd.Function):
         xc = x.contiguous()
         ov = fctx.overlap
         with trace.phase("ep.fwd.plan"):
-            p = _plan(fctx, idx, gates, mode, ep)
+            p = _plan(fctx, idx, gates, mode, ep, cap)
         with trace.phase("ep.fwd.dispatch"):
             if ov:
                 _, events = _dispatch_side(fctx, p, xc, mode, ep, backward=False)
@@ -547,18 +560,27 @@ class _FusedMoE(torch.autograd.Function):
         dgates = torch.zeros_like(dgs).scatter_(1, p["cols"].long(), dgs).to(ctx.gate_dtype)
         LIVE[f"{mode}_bwd"] += 1
         fctx.release(ctx)
-        return dx, dgates, dw13, dw2, None, None, None
+        return dx, dgates, dw13, dw2, None, None, None, None
 
 
-def fused_moe_forward(fctx: FusedEPContext, x, idx, gates, w13, w2, *, mode: str):
-    """Routed-expert output for this rank's tokens over the fused transport."""
+def fused_moe_forward(fctx: FusedEPContext, x, idx, gates, w13, w2, *, mode: str,
+                      capacity_factor=None, tokens_global=None):
+    """Routed-expert output for this rank's tokens over the fused transport.
+
+    ``capacity_factor`` bounds the rows every expert accepts to ``ceil(cf * tokens_global * k /
+    E)`` (``tokens_global`` defaults to this rank's tokens times the world size); picks beyond
+    the bound, in canonical order (source rank, then token), are dropped on the device: they are
+    not sent, occupy no GEMM row and receive no gradient -- the semantics of
+    ``layer.apply_capacity`` without its host-side counts exchange."""
     if mode == "two_hop" and not fctx.two_hop_ok:
         mode = "one_hop"          # fewer than two groups (or groups != routing groups)
     if x.shape[0] > fctx.tokens:
         raise ValueError(f"{x.shape[0]} tokens exceed the context capacity {fctx.tokens}")
     if x.dtype != torch.bfloat16 or w13.dtype != torch.bfloat16:
         raise TypeError("the fused transport moves bf16 rows")
-    return _FusedMoE.apply(x, gates, w13, w2, idx, fctx, mode)
+    cap = expert_capacity(capacity_factor, tokens_global or x.shape[0] * fctx.world, fctx.k,
+                          fctx.E)
+    return _FusedMoE.apply(x, gates, w13, w2, idx, fctx, mode, cap)
 
 
 def pipeline_depth() -> int:
@@ -651,10 +673,15 @@ def make_context(cfg: TRouteConfig, hidden: int, d_expert: int, tokens: int, **k
     return FusedEPContext(cfg, hidden, d_expert, tokens, **kw)
 
 
-def run_fused(ctx, x, idx, gates, w13, w2, *, mode: str):
+def run_fused(ctx, x, idx, gates, w13, w2, *, mode: str, capacity_factor=None,
+              tokens_global=None):
     if isinstance(ctx, PipelinedFusedEP):
+        if capacity_factor is not None:
+            raise ValueError("the token pipeline does not bound expert capacity: a slice sees "
+                             "only its own tokens")
         return ctx.forward(x, idx, gates, w13, w2, mode=mode)
-    return fused_moe_forward(ctx, x, idx, gates, w13, w2, mode=mode)
+    return fused_moe_forward(ctx, x, idx, gates, w13, w2, mode=mode,
+                             capacity_factor=capacity_factor, tokens_global=tokens_global)
 
 
 @torch.no_grad()

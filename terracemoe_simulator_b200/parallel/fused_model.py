@@ -26,16 +26,20 @@ import torch
 ST_OK, ST_TIMEOUT_FLAG, ST_BAD_INDEX, ST_TIMEOUT_COUNTS = 0, 4, 5, 6
 
 
-def plan_positions(idx_per_rank, world: int, n_experts: int, seg_align: int = 64):
+def plan_positions(idx_per_rank, world: int, n_experts: int, seg_align: int = 64, cap: int = 0):
     """``idx_per_rank[s]``: ``[T_s, k]`` expert ids of source rank s.  Returns a dict with
     ``pos[s]`` / ``owner[s]`` (``[T_s, k]``), and per owner ``seg_start[o]``, ``seg_count[o]``
-    (``[epr]``) and ``rows[o]`` (rows of the owner's buffer in use, padding included)."""
+    (``[epr]``) and ``rows[o]`` (rows of the owner's buffer in use, padding included).
+    ``cap`` > 0: an expert accepts its first ``cap`` rows in (source rank, token) order; the
+    picks beyond get position -1 and the segments shrink to ``min(total, cap)``."""
     if len(idx_per_rank) != world or n_experts % world:
         raise ValueError("one index tensor per rank, and world must divide n_experts")
     epr = n_experts // world
     counts = torch.stack([torch.bincount(i.reshape(-1), minlength=n_experts) for i in idx_per_rank])
-    total = counts.sum(0)                                            # [E]
     before = torch.cumsum(counts, 0) - counts                        # rows of lower sources, [W, E]
+    total = counts.sum(0)                                            # [E]
+    if cap > 0:
+        total = total.clamp(max=cap)
     padded = (total + seg_align - 1) // seg_align * seg_align
     seg = torch.zeros(n_experts, dtype=torch.int64)
     for o in range(world):                                           # owner-local running offset
@@ -49,8 +53,10 @@ def plan_positions(idx_per_rank, world: int, n_experts: int, seg_align: int = 64
         if int(onehot.max()) > 1:
             raise ValueError("a token may pick an expert at most once")
         earlier = torch.cumsum(onehot, 0) - onehot                   # earlier tokens picking e
-        local = earlier.gather(1, idx)
-        pos.append(seg[idx] + before[s][idx] + local)
+        within = before[s][idx] + earlier.gather(1, idx)             # rank inside the expert
+        place = seg[idx] + within
+        pos.append(torch.where(within < cap, place, torch.full_like(place, -1)) if cap > 0
+                   else place)
         owner.append(torch.div(idx, epr, rounding_mode="floor"))
     return {"pos": pos, "owner": owner,
             "seg_start": [seg[o * epr:(o + 1) * epr].clone() for o in range(world)],

@@ -40,8 +40,10 @@ def _route(x, router_w, bias, cfg):
 
 
 def routed_experts(x, idx, gates, w13, w2, cfg: TRouteConfig, *, mode: str, world: int, rpn: int,
-                   fused: bool, ctx=None):
-    """Dispatch -> expert SwiGLU -> combine for this rank's tokens, on the chosen transport."""
+                   fused: bool, ctx=None, capacity_factor=None):
+    """Dispatch -> expert SwiGLU -> combine for this rank's tokens, on the chosen transport.
+    ``capacity_factor`` is applied on the device by the fused transport only; the other
+    transports expect gates that ``layer.apply_capacity`` has already zeroed."""
     if mode not in EP_MODES:
         raise ValueError(f"unknown EP mode {mode!r}; expected one of {EP_MODES}")
     E = cfg.n_experts
@@ -63,7 +65,8 @@ def routed_experts(x, idx, gates, w13, w2, cfg: TRouteConfig, *, mode: str, worl
         return torch.zeros_like(x).index_add(0, tok, w * out)
     if fused:
         from . import fused as fz
-        return fz.run_fused(ctx, x, idx, gates, w13, w2, mode=mode)
+        return fz.run_fused(ctx, x, idx, gates, w13, w2, mode=mode,
+                            capacity_factor=capacity_factor)
     if mode == "one_hop":
         return ep_moe_forward(x, idx, gates, w13, w2, world, E, rpn=rpn)
     return ta2a_moe_forward(x, idx, gates, w13, w2, world, E, rpn=rpn, groups_m=cfg.top_groups)
@@ -245,7 +248,8 @@ class EPTerracedMoE(nn.Module):
             raise ValueError("the expert-parallel layer routes with mode 'full' only")
         idx, gates, gidx, load = _route(x, self.router.weight, self.router.bias, self.cfg)
         gates_used = gates
-        if self.capacity_factor is not None:
+        on_device = self.fused and self.world > 1      # the fused plan kernel applies the cap
+        if self.capacity_factor is not None and not on_device:
             all_load = load.clone()
             prior = torch.zeros_like(load)
             if self.world > 1:
@@ -258,7 +262,8 @@ class EPTerracedMoE(nn.Module):
                 n_tokens_global=x.shape[0] * self.world, prior_counts=prior.long())
         y = routed_experts(x, idx, gates_used, self.w13, self.w2, self.cfg, mode=self.mode,
                            world=self.world, rpn=self.rpn, fused=self.fused,
-                           ctx=self._context(x.shape[0], x.device))
+                           ctx=self._context(x.shape[0], x.device),
+                           capacity_factor=self.capacity_factor if on_device else None)
         if self.shared.w2.in_features > 0:
             y = y + self.shared(x)
         if self.training:

@@ -198,7 +198,8 @@ class _RecorderLib:
                         torch.zeros(T, k, **i32), torch.zeros(128, 16, **i32))
             if name == "ep_plan":
                 return (torch.zeros(16, **i32), torch.zeros(self.epr, **i32),
-                        torch.zeros(self.epr, **i32), torch.zeros(1, **i32))
+                        torch.zeros(self.epr, **i32), torch.zeros(1, **i32),
+                        torch.zeros(16, **i32))
             if name == "hopa_rank":
                 return torch.zeros(T, 2, **i32), torch.zeros(128, 2, **i32)
             if name == "hopa_push":
@@ -346,6 +347,46 @@ def test_fused_two_hop_orchestration_launch_sequence(monkeypatch, overlap):
     assert gates.grad.shape == gates.shape
     monkeypatch.undo()
     ops.reset()
+
+
+def test_capacity_in_the_plan_keeps_exactly_the_picks_apply_capacity_keeps():
+    """The device-side cap (canonical order: source rank, then token) against the layer-level
+    oracle ``apply_capacity`` with the lower ranks' counts as ``prior_counts``."""
+    from terracemoe_simulator_b200.layer import apply_capacity
+    from terracemoe_simulator_b200.parallel.fused import expert_capacity
+    world, E, k = 4, 16, 4
+    cfg, routed = _routing(world, 40, E, 4, k, 2, seed=31)
+    idx = [i for i, _ in routed]
+    tokens_global = sum(i.shape[0] for i in idx)
+    cap = expert_capacity(0.6, tokens_global, k, E)
+    plan = fm.plan_positions(idx, world, E, 64, cap=cap)
+    counts = torch.stack([torch.bincount(i.reshape(-1), minlength=E) for i in idx])
+    dropped = 0
+    for s in range(world):
+        prior = counts[:s].sum(0)
+        _, keep, cap_ref = apply_capacity(idx[s], routed[s][1], E, 0.6,
+                                          n_tokens_global=tokens_global, prior_counts=prior)
+        assert cap_ref == cap
+        assert torch.equal(plan["pos"][s] >= 0, keep)
+        dropped += int((~keep).sum())
+    assert dropped > 0                                    # the factor really binds
+    for o in range(world):
+        assert int(plan["seg_count"][o].max()) <= cap
+    # kept rows still tile every (shrunk) segment exactly once
+    kept_idx = [i.clone() for i in idx]
+    taken = [torch.zeros(max(plan["rows"][o], 1), dtype=torch.int64) for o in range(world)]
+    for s in range(world):
+        live = plan["pos"][s] >= 0
+        for o in range(world):
+            rows = plan["pos"][s][live & (plan["owner"][s] == o)]
+            taken[o].scatter_add_(0, rows, torch.ones_like(rows))
+    epr = E // world
+    for o in range(world):
+        assert int(taken[o].max()) <= 1
+        for le in range(epr):
+            a, n = int(plan["seg_start"][o][le]), int(plan["seg_count"][o][le])
+            assert bool((taken[o][a:a + n] == 1).all())
+    del kept_idx
 
 
 def test_arena_layout_puts_a_guard_after_every_section():

@@ -31,20 +31,22 @@ def _worker(rank, world, port, queue, M, rpn=1):
 CAPACITY = 1400          # rows per rank the arena is sized for; every rank's T stays below it
 
 
-def _fp32_oracle(rank, world, x0, idx, gates0, gy, w13_all, w2_all, dev):
+def _fp32_oracle(rank, world, x0, idx, gates0, gy, w13_all, w2_all, dev, keep=None):
     """The layer as plain fp32 PyTorch over ALL ranks' tokens and ALL experts:
     ``y[t] = sum_j gate[t, j] * (silu(x W13a) * (x W13b)) W2`` of expert ``idx[t, j]``; autograd gives
     every gradient.  Returns this rank's slices, in the order of the fused results."""
     import torch.distributed as dist
     import torch.nn.functional as F
     parts = [None] * world
-    dist.all_gather_object(parts, (x0.cpu(), idx.cpu(), gates0.cpu(), gy.cpu()))
+    mask = torch.ones_like(gates0) if keep is None else keep.to(gates0.dtype)
+    dist.all_gather_object(parts, (x0.cpu(), idx.cpu(), gates0.cpu(), gy.cpu(), mask.cpu()))
     lo = sum(p[0].shape[0] for p in parts[:rank])
     hi = lo + parts[rank][0].shape[0]
     x = torch.cat([p[0] for p in parts]).float().to(dev).requires_grad_(True)
     ids = torch.cat([p[1] for p in parts]).to(dev)
     gates = torch.cat([p[2] for p in parts]).float().to(dev).requires_grad_(True)
     g_out = torch.cat([p[3] for p in parts]).float().to(dev)
+    kept = torch.cat([p[4] for p in parts]).float().to(dev)      # 0 for picks beyond capacity
     w13 = w13_all.float().to(dev).requires_grad_(True)
     w2 = w2_all.float().to(dev).requires_grad_(True)
     y = torch.zeros_like(x)
@@ -53,7 +55,8 @@ def _fp32_oracle(rank, world, x0, idx, gates0, gy, w13_all, w2_all, dev):
         if tok.numel() == 0:
             continue
         a, b = (x[tok] @ w13[e]).chunk(2, dim=-1)
-        y = y.index_add(0, tok, gates[tok, col].unsqueeze(1) * ((F.silu(a) * b) @ w2[e]))
+        y = y.index_add(0, tok, (gates[tok, col] * kept[tok, col]).unsqueeze(1)
+                        * ((F.silu(a) * b) @ w2[e]))
     y.backward(g_out)
     epr = w13.shape[0] // world
     own = slice(rank * epr, (rank + 1) * epr)
@@ -200,6 +203,105 @@ def test_fused_groups_of_several_gpus(native_ops, world, rpn, M):
     if torch.cuda.device_count() < world:
         pytest.skip(f"needs {world} GPUs")
     _check_ranks(_run(world, M, 29720 + world + rpn, rpn=rpn), world)
+
+
+def _capacity_worker(rank, world, port, queue, rpn):
+    import torch.distributed as dist
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    os.environ["NCCL_NVLS_ENABLE"] = "0"
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world,
+                            device_id=torch.device("cuda", rank))
+    try:
+        from terracemoe_simulator_b200 import ops
+        from terracemoe_simulator_b200.layer import apply_capacity
+        from terracemoe_simulator_b200.parallel import fused as fz
+        from terracemoe_simulator_b200.routing import TRouteConfig, expert_load, t_route
+        dev = torch.device("cuda", rank)
+        E, k, H, d, T, factor = 16, 4, 256, 128, 900, 0.7
+        cfg = TRouteConfig(E, max(world // rpn, 2), k, 2)
+        g = torch.Generator().manual_seed(0)
+        w13_all = (torch.randn(E, H, 2 * d, generator=g) * H ** -0.5).bfloat16()
+        w2_all = (torch.randn(E, d, H, generator=g) * d ** -0.5).bfloat16()
+        epr = E // world
+        gx = torch.Generator().manual_seed(20 + rank)
+        x0 = torch.randn(T, H, generator=gx).bfloat16().to(dev)
+        # skewed affinities, so that some experts overflow their capacity
+        aff = (torch.rand(T, E, generator=gx) * torch.linspace(0.4, 1.0, E)).to(dev)
+        gy = torch.randn(T, H, generator=gx).bfloat16().to(dev)
+        idx, gates0, _ = t_route(aff, torch.zeros(E, device=dev), cfg)
+        loads = [torch.zeros(E, device=dev) for _ in range(world)]
+        dist.all_gather(loads, expert_load(idx, E))
+        prior = sum(loads[:rank], torch.zeros(E, device=dev)).long()
+        _, keep, cap = apply_capacity(idx, gates0, E, factor, n_tokens_global=T * world,
+                                      prior_counts=prior)
+        res = {}
+        for name, overlap in (("overlap", True), ("pull", False)):
+            ctx = fz.FusedEPContext(cfg, H, d, T, world=world, rank=rank, rpn=rpn, device=dev,
+                                    overlap=overlap)
+            for mode in ("one_hop", "two_hop"):
+                x = x0.clone().requires_grad_(True)
+                gates = gates0.clone().requires_grad_(True)
+                a = w13_all[rank * epr:(rank + 1) * epr].to(dev).requires_grad_(True)
+                b = w2_all[rank * epr:(rank + 1) * epr].to(dev).requires_grad_(True)
+                y = fz.run_fused(ctx, x, idx, gates, a, b, mode=mode, capacity_factor=factor)
+                y.backward(gy)
+                torch.cuda.synchronize()
+                res[f"{name}_{mode}"] = [t.detach().float().cpu()
+                                         for t in (y, x.grad, gates.grad, a.grad, b.grad)]
+        res["oracle"] = _fp32_oracle(rank, world, x0, idx, gates0, gy, w13_all, w2_all, dev,
+                                     keep=keep)
+        status = ops.take_status(rank)
+        queue.put((rank, res, keep.cpu(), int((~keep).sum()), status, cap))
+        dist.barrier()
+    except Exception as exc:  # noqa: BLE001
+        import traceback
+        queue.put((rank, "error", f"{type(exc).__name__}: {exc}\n{traceback.format_exc()}"))
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("world,rpn", [(2, 1), (4, 2)])
+def test_fused_capacity_on_the_device_matches_apply_capacity(native_ops, world, rpn):
+    """Capacity factor inside the plan kernel: the dropped picks are exactly those the layer-level
+    oracle drops (zero gate gradient there, non-zero elsewhere), the four fused arms agree bit
+    for bit, and outputs and gradients match the fp32 oracle with the oracle's gates zeroed."""
+    if torch.cuda.device_count() < world:
+        pytest.skip(f"needs {world} GPUs")
+    import torch.multiprocessing as mp
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    procs = [ctx.Process(target=_capacity_worker, args=(r, world, 29850 + world, q, rpn))
+             for r in range(world)]
+    for p in procs:
+        p.start()
+    out = []
+    try:
+        for _ in range(world):
+            out.append(q.get(timeout=300))
+    finally:
+        for p in procs:
+            p.join(timeout=30)
+        for p in procs:
+            if p.is_alive():
+                p.terminate()
+    total_dropped = 0
+    for item in out:
+        assert item[1] != "error", item[2]
+        rank, res, keep, dropped, status, cap = item
+        assert status == 0, (rank, status)          # a dropped pick is not an error
+        total_dropped += dropped
+        base = res["overlap_one_hop"]
+        for name in ("overlap_two_hop", "pull_one_hop", "pull_two_hop"):
+            for a, b in zip(base, res[name]):
+                assert torch.equal(a, b), name
+        for a, b in zip(base, res["oracle"]):
+            _close(a, b)
+        # the gate gradient is exactly zero where, and only where, the oracle drops the pick
+        assert bool((base[2][~keep] == 0).all())
+        assert float((base[2][keep] != 0).float().mean()) > 0.99
+    assert total_dropped > 0
 
 
 @pytest.mark.parametrize("chunks", ["1", "4"])

@@ -76,7 +76,7 @@ def test_transport_ops_answer_on_meta(lib):
     es, gs, cols, rank_local, hist = lib.ep_plan_pass1(_m(T, k, dtype=i64), _m(T, k, dtype=f32), E)
     assert _sig([es, gs, hist]) == [((T, k), i32), ((T, k), f32), ((128, E), i32)]
     assert _sig(lib.ep_plan(arena, hist, None, 1, 64)) == \
-        [((E,), i32), ((E // world,), i32), ((E // world,), i32), ((world, 2), i32)]
+        [((E,), i32), ((E // world,), i32), ((E // world,), i32), ((world, 2), i32), ((E,), i32)]
     ranka, chunka = lib.hopa_rank(arena, es)
     assert _sig([ranka, chunka]) == [((T, M), i32), ((128, 2), i32)]
     x = _m(T, H)
