@@ -17,8 +17,9 @@ import sys
 
 import torch
 
-CASES = ("gemm_fwd", "gemm_swiglu", "gemm_dgrad", "gemm_wgrad", "gemm_scatter", "rmsnorm", "route",
-         "scatter", "combine", "swiglu_bwd", "attn_fwd", "attn_bwd")
+CASES = ("gemm_fwd", "gemm_swiglu", "gemm_dgrad", "gemm_wgrad", "gemm_scatter", "rmsnorm",
+         "rmsnorm_bwd", "route", "route_fused", "scatter", "combine", "combine_bwd", "swiglu_bwd",
+         "attn_fwd", "attn_bwd", "ep_layer")
 
 
 def _peaks():
@@ -126,17 +127,54 @@ def main(argv=None) -> int:
                 qq, kk, vv = (t.clone().requires_grad_(True) for t in (q, k_, v))
                 oo = F.scaled_dot_product_attention(qq, kk, vv, is_causal=True)
                 fn = lambda: torch.autograd.grad(oo, (qq, kk, vv), go, retain_graph=True)
-    elif args.case == "rmsnorm":
+    elif args.case in ("rmsnorm", "rmsnorm_bwd"):
         x = torch.randn(rows * 2, H, device=dev, dtype=bf)
         w = torch.ones(H, device=dev, dtype=bf)
-        fn = lambda: lib.rmsnorm_fwd(x, w, 1e-5)
-        bytes_ = 2 * x.numel() * 2
+        if args.case == "rmsnorm":
+            fn = lambda: lib.rmsnorm_fwd(x, w, 1e-5)
+            bytes_ = 2 * x.numel() * 2
+        else:
+            _, rstd = lib.rmsnorm_fwd(x, w, 1e-5)
+            dy = torch.randn_like(x)
+            fn = lambda: lib.rmsnorm_bwd(x, w, dy, rstd)
+            bytes_ = 3 * x.numel() * 2
+    elif args.case == "route_fused":
+        # the router GEMM with the selection in its epilogue: x is read once, nothing else moves
+        Tr = T * 8
+        x = torch.randn(Tr, H, device=dev, dtype=bf)
+        w = torch.randn(64, H, device=dev, dtype=bf) * H ** -0.5
+        bias = torch.zeros(64, device=dev)
+        fn = lambda: lib.route_fused(x, w, bias, 4, 6, 2, 2)
+        bytes_ = x.numel() * 2 + w.numel() * 2
+    elif args.case == "ep_layer":
+        # the fused expert-parallel layer at world 1: every peer-memory kernel of the one-hop path
+        # (plan, push, arrival-gated GEMMs, scattering epilogue, signal, combine) on one GPU
+        import torch.distributed as dist
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        os.environ.setdefault("MASTER_PORT", "29911")
+        dist.init_process_group("nccl", rank=0, world_size=1, device_id=torch.device("cuda", 0))
+        from terracemoe_simulator_b200.parallel import fused as fz
+        from terracemoe_simulator_b200.routing import TRouteConfig, t_route
+        Ee = 64 if args.full else 16
+        cfg = TRouteConfig(Ee, 4, k if args.full else 4, 2)
+        ctx = fz.FusedEPContext(cfg, H, d, T, world=1, rank=0, rpn=1, device=torch.device(dev, 0),
+                                overlap=not args.library)
+        x = torch.randn(T, H, device=dev, dtype=bf).requires_grad_(True)
+        w13 = (torch.randn(Ee, H, 2 * d, device=dev, dtype=bf) * H ** -0.5).requires_grad_(True)
+        w2 = (torch.randn(Ee, d, H, device=dev, dtype=bf) * d ** -0.5).requires_grad_(True)
+        idx, gates, _ = t_route(torch.rand(T, Ee, device=dev), torch.zeros(Ee, device=dev), cfg)
+        gy = torch.randn(T, H, device=dev, dtype=bf)
+
+        def fn():
+            y = fz.fused_moe_forward(ctx, x, idx, gates, w13, w2, mode="one_hop")
+            y.backward(gy)
+        flops = 3 * 2 * 3 * T * cfg.top_k * H * d
     elif args.case == "route":
         logits = torch.randn(T * 8, 64, device=dev)
         bias = torch.zeros(64, device=dev)
         fn = lambda: lib.route_select(logits, bias, 4, 6, 2, 2)
         bytes_ = logits.numel() * 4
-    elif args.case in ("scatter", "combine"):
+    elif args.case in ("scatter", "combine", "combine_bwd"):
         x = torch.randn(T, H, device=dev, dtype=bf)
         idx = torch.stack([torch.randperm(E, device=dev)[:k] for _ in range(T)])
         es, gs, cols, pos, s0, c0 = lib.moe_plan(idx, torch.rand(T, k, device=dev), E, 1)
@@ -144,9 +182,12 @@ def main(argv=None) -> int:
         if args.case == "scatter":
             fn = lambda: lib.moe_scatter_rows(x, pos, T * k)
             bytes_ = (T + T * k) * H * 2
-        else:
+        elif args.case == "combine":
             fn = lambda: lib.moe_combine(xs, pos, es, gs, E)
             bytes_ = (T + T * k) * H * 2
+        else:
+            fn = lambda: lib.moe_combine_bwd(x, xs, pos, gs, True)
+            bytes_ = (T + 2 * T * k) * H * 2
     else:
         h13 = torch.randn(rows, 2 * d, device=dev, dtype=bf)
         dact = torch.randn(rows, d, device=dev, dtype=bf)

@@ -9,11 +9,19 @@ dispatch+combine (rows echo back through the owners' buffers; no expert compute)
 with CUDA events, max over ranks, burst style (``--iters`` back-to-back calls, one sync).
 It also times the NCCL ``all_to_all_single`` of the same payload as the library baseline.
 Output: JSON with ``rows`` (one dict per configuration: both times, bus GB/s, measured
-two-hop/one-hop ratio) and ``records`` in the ``sim.fit`` schema ``{frame, world, bytes, ms}``
-with frames ``flat`` (one-hop, world N), ``slow`` (Hop A shaped: N_g peers, T*M rows) and
-``fast`` (Hop B shaped: R peers, T*k rows) measured with one-hop pushes restricted to those
-peer sets.  Counterpart of the reference's ``bench/a2a_form_probe.py`` / ``bench/twohop_verdict.py``
-measurement protocol (barrier, sync, timed burst, MAX over ranks).
+two-hop/one-hop ratio) and ``records`` in the ``sim.fit`` schema ``{frame, world, bytes, ms}``.
+Three frames are measured, each as half of a one-hop dispatch + combine of the fused transport:
+
+  ``flat``   all N ranks, T*k rows per rank (the one-hop exchange itself)
+  ``slow``   Hop A shaped: the N_g ranks that share a local index (one per group), T*M rows per
+             rank, every such peer set exchanging at the same time
+  ``fast``   Hop B shaped: the R ranks of a group, T*k rows per rank, all groups at the same time
+
+``slow`` and ``fast`` run on arenas that span only their peer set, so their fixed cost and
+bandwidth are the levels' own (``sim.calibrate.b200_from_records`` fits one alpha and one beta
+per frame with ``sim.fit.fit_beta_pinned``).  Counterpart of the reference's
+``bench/a2a_form_probe.py`` / ``bench/twohop_verdict.py`` measurement protocol (barrier, sync,
+timed burst, MAX over ranks).
 """
 from __future__ import annotations
 
@@ -26,21 +34,72 @@ import torch
 import torch.distributed as dist
 
 
-def _timed(fn, iters, warmup, world):
+def _timed(fn, iters, warmup, world, bursts: int = 3):
+    """Median over ``bursts`` timed bursts of ``iters`` back-to-back calls each (one burst of a
+    50 us call is too noisy to calibrate a fixed cost from); every burst is bracketed by a
+    barrier + synchronize and reduced with MAX over ranks."""
     for _ in range(warmup):
         fn()
-    torch.cuda.synchronize()
-    dist.barrier()
-    torch.cuda.synchronize()
-    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    a.record()
-    for _ in range(iters):
-        fn()
-    b.record()
-    torch.cuda.synchronize()
-    ms = torch.tensor([a.elapsed_time(b) / iters], device="cuda")
-    dist.all_reduce(ms, op=dist.ReduceOp.MAX)
-    return ms.item()
+    seen = []
+    for _ in range(bursts):
+        torch.cuda.synchronize()
+        dist.barrier()
+        torch.cuda.synchronize()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for _ in range(iters):
+            fn()
+        b.record()
+        torch.cuda.synchronize()
+        ms = torch.tensor([a.elapsed_time(b) / iters], device="cuda")
+        dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+        seen.append(ms.item())
+    return sorted(seen)[len(seen) // 2]
+
+
+def _peer_sets(world: int, R: int):
+    """(slow sets, fast sets): ranks sharing a local index, and the ranks of each group."""
+    groups = world // R
+    slow = [[g * R + j for g in range(groups)] for j in range(R)]
+    fast = [[g * R + j for j in range(R)] for g in range(groups)]
+    return slow, fast
+
+
+def _level_frames(world, rank, R, T, H, iters, warmup, dev, groups_cache):
+    """Half the dispatch + combine time of a one-hop exchange inside this rank's ``slow`` and
+    ``fast`` peer sets, with T*M and T*k rows: ``[(frame, peers, bytes, ms)]``."""
+    from terracemoe_simulator_b200.parallel import fused as fz
+    from terracemoe_simulator_b200.routing import TRouteConfig, t_route
+    out = []
+    slow_sets, fast_sets = _peer_sets(world, R)
+    for frame, sets, k in (("slow", slow_sets, 2), ("fast", fast_sets, 6)):
+        n = len(sets[0])
+        if n < 2:
+            continue
+        mine = None
+        for members in sets:                      # every rank creates every group, same order
+            key = tuple(members)
+            if key not in groups_cache:
+                groups_cache[key] = dist.new_group(members)
+            if rank in members:
+                mine = (members, groups_cache[key])
+        members, group = mine
+        E = 16 * n                                # 16 experts per peer, one routing group
+        cfg = TRouteConfig(E, 1, k, 1)
+        ctx = fz.FusedEPContext(cfg, H, 64, T, world=n, rank=members.index(rank), rpn=n,
+                                device=dev, group=group, row_capacity_factor=3.0)
+        g = torch.Generator().manual_seed(77 * rank + T + k)
+        x = torch.randn(T, H, generator=g).bfloat16().to(dev)
+        idx, gates, _ = t_route(torch.rand(T, E, generator=g).to(dev), torch.zeros(E, device=dev),
+                                cfg)
+        ms = _timed(lambda: fz.fused_dispatch_combine(ctx, x, idx, gates, mode="one_hop"),
+                    iters, warmup, world)
+        status = ctx.take_status()
+        out.append((frame, n, T * k * H * 2, ms / 2, status))
+        ctx.close()
+        del ctx
+        torch.cuda.empty_cache()
+    return out
 
 
 def main(argv=None) -> int:
@@ -49,7 +108,7 @@ def main(argv=None) -> int:
     ap.add_argument("--tokens", type=int, nargs="+", default=[256, 1024, 4096, 16384])
     ap.add_argument("--hidden", type=int, default=4096)
     ap.add_argument("--experts", type=int, default=64)
-    ap.add_argument("--iters", type=int, default=10)
+    ap.add_argument("--iters", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
     args = ap.parse_args(argv)
     rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
@@ -63,6 +122,18 @@ def main(argv=None) -> int:
     dev = torch.device("cuda", local)
     H, E, M = args.hidden, args.experts, 2
     rows, records = [], []
+    groups_cache: dict = {}
+    for R in (2, 4):              # per-level frames: the peer sets of groups of R
+        if world % R or world // R < 1:
+            continue
+        for T in args.tokens:
+            for frame, n, nbytes, ms, status in _level_frames(world, rank, R, T, H, args.iters,
+                                                              args.warmup, dev, groups_cache):
+                rec = {"frame": frame, "world": n, "bytes": nbytes, "ms": ms, "R": R,
+                       "tokens": T, "status": status}
+                records.append(rec)
+                if rank == 0:
+                    print(json.dumps(rec), flush=True)
     for R in (1, 2, 4):
         n_nodes = world // R
         if world % R or n_nodes < 2 or E % n_nodes:

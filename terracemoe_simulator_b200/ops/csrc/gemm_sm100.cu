@@ -216,7 +216,10 @@ __device__ __forceinline__ int clamp32(int v) { return v < 0 ? 0 : (v > 32 ? 32 
 enum { MODE_FWD = 0, MODE_DGRAD = 1, MODE_WGRAD = 2 };
 // EPI_SCATTER: plain epilogue whose rows go to per-row destinations (the combine leg of expert
 // parallelism folded into the GEMM: the tile is stored straight into the token owner's buffer)
-enum { EPI_PLAIN = 0, EPI_SWIGLU = 1, EPI_SCATTER = 2 };
+// EPI_SWIGLU_BWD: the tile is d(act); the epilogue reads the saved pre-activations
+// [gate | up] of its rows (C2) and writes d[gate | up] (C, 2N wide) -- the SwiGLU backward
+// without the d(act) round trip through memory
+enum { EPI_PLAIN = 0, EPI_SWIGLU = 1, EPI_SCATTER = 2, EPI_SWIGLU_BWD = 3 };
 
 template <int MODE, int EPI, int CTAS>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
@@ -579,6 +582,52 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
             }
           }
         }
+      } else if (EPI == EPI_SWIGLU_BWD) {
+        const int row = m_off + row_in_tile;
+        const int padded = p.pad_align > 0 ? (cnt + p.pad_align - 1) / p.pad_align * p.pad_align
+                                           : cnt;
+        const bool real = row < cnt;
+        const bool live = row < padded;            // padding rows are written as zeros
+        const __nv_bfloat16* hrow = p.C2 + static_cast<size_t>(seg0 + row) * p.ldc2;
+        __nv_bfloat16* orow = p.C + static_cast<size_t>(seg0 + row) * p.ldc;
+#pragma unroll 1
+        for (int c = 0; c < BN / 32; ++c) {
+          uint32_t da[32];
+          tmem_ld_32x32(taddr + c * 32, da);
+          tmem_ld_wait();
+          const int n0 = nt * BN + c * 32;
+          if (live) {
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              if (n0 + j * 8 < p.N) {
+                uint4 vg = make_uint4(0, 0, 0, 0), vu = make_uint4(0, 0, 0, 0);
+                if (real) {
+                  const uint4 g8 = *reinterpret_cast<const uint4*>(hrow + n0 + j * 8);
+                  const uint4 u8 = *reinterpret_cast<const uint4*>(hrow + p.up_offset + n0 + j * 8);
+                  const __nv_bfloat162* gb = reinterpret_cast<const __nv_bfloat162*>(&g8);
+                  const __nv_bfloat162* ub = reinterpret_cast<const __nv_bfloat162*>(&u8);
+                  uint32_t* pg = reinterpret_cast<uint32_t*>(&vg);
+                  uint32_t* pu = reinterpret_cast<uint32_t*>(&vu);
+#pragma unroll
+                  for (int i = 0; i < 4; ++i) {
+                    // d(act) rounded to bf16 first: the value a separate kernel would read back
+                    uint32_t dpk = pack_bf16(__uint_as_float(da[j * 8 + 2 * i]),
+                                             __uint_as_float(da[j * 8 + 2 * i + 1]));
+                    const float2 d2 = __bfloat1622float2(*reinterpret_cast<__nv_bfloat162*>(&dpk));
+                    const float2 g2 = __bfloat1622float2(gb[i]);
+                    const float2 u2 = __bfloat1622float2(ub[i]);
+                    const float s0 = 1.f / (1.f + __expf(-g2.x)), s1 = 1.f / (1.f + __expf(-g2.y));
+                    pg[i] = pack_bf16(d2.x * u2.x * s0 * (1.f + g2.x * (1.f - s0)),
+                                      d2.y * u2.y * s1 * (1.f + g2.y * (1.f - s1)));
+                    pu[i] = pack_bf16(d2.x * g2.x * s0, d2.y * g2.y * s1);
+                  }
+                }
+                *reinterpret_cast<uint4*>(orow + n0 + j * 8) = vg;
+                *reinterpret_cast<uint4*>(orow + p.up_offset + n0 + j * 8) = vu;
+              }
+            }
+          }
+        }
       } else if (EPI == EPI_SCATTER) {
         const int row = m_off + row_in_tile;       // this lane's row inside the group
         unsigned long long row_addr = 0ull;
@@ -878,6 +927,15 @@ static int grouped_gemm_impl(const void* A, const void* B, void* C, void* C2,
   p.scatter_base = scatter_base;
   p.scatter_slots = scatter_slots;
   p.scatter_world = scatter_world;
+  if (epilogue == EPI_SWIGLU_BWD) {
+    if (C2 == nullptr) return TB200_ERR_ARG;
+    if (mode == MODE_DGRAD) {
+      if (pair) return launch_gemm<MODE_DGRAD, EPI_SWIGLU_BWD, 2>(ta, tb, p, max_ctas, stream);
+      return launch_gemm<MODE_DGRAD, EPI_SWIGLU_BWD, 1>(ta, tb, p, max_ctas, stream);
+    }
+    if (pair) return launch_gemm<MODE_FWD, EPI_SWIGLU_BWD, 2>(ta, tb, p, max_ctas, stream);
+    return launch_gemm<MODE_FWD, EPI_SWIGLU_BWD, 1>(ta, tb, p, max_ctas, stream);
+  }
   if (scatter) {
     if (pair) {
       if (mode == MODE_DGRAD)
@@ -912,7 +970,8 @@ extern "C" int tb200_grouped_gemm(const void* A, const void* B, void* C, void* C
                                   int b_cols, int mode, int epilogue, int* status, int max_ctas,
                                   const int* wait_flags, int wait_n, int wait_epoch,
                                   int pad_align, cudaStream_t stream) {
-  if (epilogue != EPI_PLAIN && epilogue != EPI_SWIGLU) return TB200_ERR_ARG;
+  if (epilogue != EPI_PLAIN && epilogue != EPI_SWIGLU && epilogue != EPI_SWIGLU_BWD)
+    return TB200_ERR_ARG;
   return grouped_gemm_impl(A, B, C, C2, seg_start, seg_count, n_groups, a_rows, N, K, ldc, ldc2,
                            b_rows, b_cols, mode, epilogue, status, max_ctas, wait_flags, wait_n,
                            wait_epoch, pad_align, nullptr, nullptr, 0, 0, stream);

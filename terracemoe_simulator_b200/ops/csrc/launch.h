@@ -23,6 +23,9 @@ enum {
 // mode 1 (dgrad): C[rows, N] = A[rows, K] * B[g][N, K]^T (B row-major [b_rows=N, b_cols=K])
 // epilogue 1: B holds [gate | up] halves (fwd: b_cols = 2N; dgrad: b_rows = 2N);
 // C = silu(gate) * up, and when C2 != null the bf16 pre-activations go to C2[rows, 2N].
+// epilogue 3: SwiGLU backward fused behind the GEMM that produces d(act): the product is d(act)
+// [rows, N]; C2 (input) holds the saved pre-activations [rows, 2N] = [gate | up] and C (output,
+// ldc = 2N) receives d[gate | up].
 // Rows of group g are A[seg_start[g] .. seg_start[g] + seg_count[g]).
 int tb200_grouped_gemm(const void* A, const void* B, void* C, void* C2, const int* seg_start,
                        const int* seg_count, int n_groups, long long a_rows, int N, int K, int ldc,

@@ -32,7 +32,7 @@ namespace tb200 {
 constexpr int RT_BM = 128;                 // tokens per CTA
 constexpr int RT_BK = 64;                  // 64 bf16 = one 128-byte swizzle line
 constexpr int RT_A_BYTES = RT_BM * RT_BK * 2;
-constexpr int RT_STAGES = 4;
+constexpr int RT_MAX_STAGES = 8;           // as many as fit beside the affinity rows (host decides)
 constexpr int RT_THREADS = 192;            // warp 0 TMA, warp 1 MMA, warps 2..5 epilogue
 constexpr int RT_MAX_E = 128;
 constexpr int RT_MAX_G = 64;
@@ -45,12 +45,13 @@ struct RouterParams {
   float* load;              // [E], accumulated
   float* aff_sel;           // [T, k] raw affinity of every pick (for the backward pass)
   int T, E, H, n_groups, top_k, top_groups, pool;
+  int stages;               // TMA stages in flight: the kernel streams x once and is bound by them
   int* status;
 };
 
 struct RouterCtl {
-  uint64_t full[RT_STAGES];
-  uint64_t empty[RT_STAGES];
+  uint64_t full[RT_MAX_STAGES];
+  uint64_t empty[RT_MAX_STAGES];
   uint64_t acc_full;
   uint32_t tmem_base;
   volatile int abort_flag;
@@ -87,7 +88,8 @@ route_fused_kernel(const __grid_constant__ CUtensorMap tmap_x,
   const int E = p.E;
   const int b_bytes = E * RT_BK * 2;
   const int stage_bytes = RT_A_BYTES + b_bytes;
-  float* s_aff = reinterpret_cast<float*>(stage_base + RT_STAGES * stage_bytes);   // [128][E + 1]
+  const int STAGES = p.stages;
+  float* s_aff = reinterpret_cast<float*>(stage_base + STAGES * stage_bytes);      // [128][E + 1]
   float* s_gsc = s_aff + RT_BM * (E + 1);                                          // [128][G + 1]
   float* s_bias = s_gsc + RT_BM * (p.n_groups + 1);                                // [E]
   int* s_hist = reinterpret_cast<int*>(s_bias + E);                                // [E]
@@ -103,7 +105,7 @@ route_fused_kernel(const __grid_constant__ CUtensorMap tmap_x,
 
   if (warp == 0 && lane == 0) {
     ctl->abort_flag = 0;
-    for (int s = 0; s < RT_STAGES; ++s) {
+    for (int s = 0; s < STAGES; ++s) {
       mbar_init(&ctl->full[s], 1);
       mbar_init(&ctl->empty[s], 1);
     }
@@ -129,8 +131,8 @@ route_fused_kernel(const __grid_constant__ CUtensorMap tmap_x,
     // =========================== TMA producer =================================================
     if (lane == 0) {
       for (int kb = 0; kb < kblocks; ++kb) {
-        const int s = kb % RT_STAGES;
-        const uint32_t round = kb / RT_STAGES;
+        const int s = kb % STAGES;
+        const uint32_t round = kb / STAGES;
         if (round > 0 && !mbar_wait(&ctl->empty[s], (round - 1) & 1, &ctl->abort_flag)) {
           ctl->abort_flag = ST_TIMEOUT_EMPTY;
           if (p.status) atomicCAS(p.status, 0, ST_TIMEOUT_EMPTY);
@@ -149,8 +151,8 @@ route_fused_kernel(const __grid_constant__ CUtensorMap tmap_x,
     const uint64_t b_desc0 = make_smem_desc(smem_u32(stage_base) + RT_A_BYTES, 16, 1024);
     bool ok = true;
     for (int kb = 0; kb < kblocks && ok; ++kb) {
-      const int s = kb % RT_STAGES;
-      const uint32_t round = kb / RT_STAGES;
+      const int s = kb % STAGES;
+      const uint32_t round = kb / STAGES;
       const bool got = mbar_wait(&ctl->full[s], round & 1, &ctl->abort_flag);
       if (!__all_sync(0xffffffffu, got)) {
         if (lane == 0) {
@@ -305,12 +307,17 @@ extern "C" int tb200_route_fused(const void* x, const void* w, const float* bias
     const int rc = make_tmap(&tw, w, 2, dims, str, box);
     if (rc != TB200_OK) return rc;
   }
+  // everything but the stages, then as many stages as the 220 KiB opt-in leaves room for
+  const size_t fixed = 1024 + sizeof(float) * (static_cast<size_t>(RT_BM) * (E + 1) +
+                                               static_cast<size_t>(RT_BM) * (n_groups + 1) + 2 * E) +
+                       sizeof(RouterCtl) + 64;
+  const size_t stage_bytes = RT_A_BYTES + static_cast<size_t>(E) * RT_BK * 2;
+  int stages = static_cast<int>((220 * 1024 - fixed) / stage_bytes);
+  if (stages > RT_MAX_STAGES) stages = RT_MAX_STAGES;
+  if (stages < 2) return TB200_ERR_SIZE;
   RouterParams p{bias, idx, gates, group_idx, load, affinity_sel, T, E, H, n_groups, top_k,
-                 top_groups, pool, status};
-  const size_t smem = 1024 + static_cast<size_t>(RT_STAGES) * (RT_A_BYTES + E * RT_BK * 2) +
-                      sizeof(float) * (static_cast<size_t>(RT_BM) * (E + 1) +
-                                       static_cast<size_t>(RT_BM) * (n_groups + 1) + 2 * E) +
-                      sizeof(RouterCtl) + 64;
+                 top_groups, pool, stages, status};
+  const size_t smem = fixed + stages * stage_bytes;
   static OncePerDevice configured;
   if (configured.need()) {
     if (cudaFuncSetAttribute(route_fused_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,

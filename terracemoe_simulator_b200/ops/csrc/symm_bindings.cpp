@@ -389,7 +389,13 @@ void grouped_gemm_ex(const Tensor& A, const Tensor& B, Tensor C, const c10::opti
     TORCH_CHECK(b_cols == K, "grouped_gemm_ex dgrad: B cols must equal K");
     N = epilogue == 1 ? b_rows / 2 : b_rows;
   }
-  TORCH_CHECK(C.size(0) >= rows && C.size(1) == N, "grouped_gemm_ex: C must be [>= rows, N]");
+  if (epilogue == 3) {   // SwiGLU backward behind the dgrad GEMM: C = d[gate | up], C2 = [gate | up]
+    TORCH_CHECK(C2.has_value() && C.size(0) >= rows && C.size(1) == 2 * N,
+                "grouped_gemm_ex: epilogue 3 needs C [>= rows, 2N] and the saved "
+                "pre-activations in C2");
+  } else {
+    TORCH_CHECK(C.size(0) >= rows && C.size(1) == N, "grouped_gemm_ex: C must be [>= rows, N]");
+  }
   if (C2.has_value())
     TORCH_CHECK(C2->is_contiguous() && C2->size(0) >= rows && C2->size(1) == 2 * N &&
                     C2->scalar_type() == at::kBFloat16,
@@ -402,8 +408,9 @@ void grouped_gemm_ex(const Tensor& A, const Tensor& B, Tensor C, const c10::opti
   }
   check_rc(tb200_grouped_gemm(A.data_ptr(), B.data_ptr(), C.data_ptr(),
                               C2.has_value() ? C2->data_ptr() : nullptr, seg_start.data_ptr<int>(),
-                              seg_count.data_ptr<int>(), G, rows, N, K, N, 2 * N, b_rows, b_cols,
-                              mode, epilogue, st_ptr(A), 0, wait_flags, wait_n, epoch,
+                              seg_count.data_ptr<int>(), G, rows, N, K, epilogue == 3 ? 2 * N : N,
+                              2 * N, b_rows, b_cols, mode, epilogue, st_ptr(A), 0, wait_flags,
+                              wait_n, epoch,
                               static_cast<int>(pad_align), cur_stream()),
            "grouped_gemm_ex");
 }

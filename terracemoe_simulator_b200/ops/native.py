@@ -163,9 +163,11 @@ class _SwiGLUFFN(torch.autograd.Function):
         x2, w13, w2, h13, act, s, c = ctx.saved_tensors
         lib = _lib()
         dy2 = dy.reshape(-1, dy.shape[-1]).contiguous()
-        dact, _ = lib.grouped_gemm(dy2, w2.contiguous().unsqueeze(0), s, c, 0, 0, False, 0)
+        # d(act) GEMM with the SwiGLU backward in its epilogue: writes d[gate | up] directly
+        dh13 = torch.empty_like(h13)
+        lib.grouped_gemm_ex(dy2, w2.contiguous().unsqueeze(0), dh13, h13, s, c, 0, 3, None, 0, 0,
+                            0, 0, 0)
         dw2 = lib.grouped_wgrad(dy2, act, s, c, 0)[0]
-        dh13 = lib.swiglu_bwd(h13, dact)
         dx, _ = lib.grouped_gemm(dh13, w13.contiguous().unsqueeze(0), s, c, 0, 0, False, 0)
         dw13 = lib.grouped_wgrad(dh13, x2, s, c, 0)[0]
         return dx.view(*ctx.lead, x2.shape[1]), dw13, dw2
@@ -349,9 +351,10 @@ class _MoELocal(torch.autograd.Function):
         A = SEG_ALIGN
         dout, dgs = lib.moe_combine_bwd(dy.contiguous(), out, pos, gs, True)
         lib.zero_pad_rows(dout, seg_start, seg_count, A)
-        dact, _ = lib.grouped_gemm(dout, w2.contiguous(), seg_start, seg_count, 1, 0, False, 0, A)
+        dh13 = torch.empty_like(h13)        # d(act) GEMM + SwiGLU backward in one kernel
+        lib.grouped_gemm_ex(dout, w2.contiguous(), dh13, h13, seg_start, seg_count, 1, 3, None, 0,
+                            0, 0, 0, A)
         dw2 = lib.grouped_wgrad(act, dout, seg_start, seg_count, 0, A)
-        dh13 = lib.swiglu_bwd(h13, dact)
         dxs, _ = lib.grouped_gemm(dh13, w13.contiguous(), seg_start, seg_count, 1, 0, False, 0, A)
         dw13 = lib.grouped_wgrad(xs, dh13, seg_start, seg_count, 0, A)
         dx = lib.moe_combine(dxs, pos, es, None, ctx.group_size)

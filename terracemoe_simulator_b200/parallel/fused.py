@@ -523,8 +523,9 @@ class _FusedMoE(torch.autograd.Function):
             else:
                 dgs = _dispatch(fctx, p, dyc, mode, ep, backward=True)
         xin, dout = fctx.section(XIN), fctx.section(DOUT)
-        d = w2.shape[1]
-        dact = torch.empty(fctx.cap_rows, d, dtype=torch.bfloat16, device=dy.device)
+        # d(act) = dout @ w2^T never reaches memory: the GEMM's epilogue applies the SwiGLU
+        # backward to its tile and writes d[gate | up]
+        dh13 = torch.empty_like(h13)
         with trace.phase("ep.bwd.experts"):
             lib.zero_pad_rows(dout, ss, sc, SEG_ALIGN)
             if ov:
@@ -534,21 +535,19 @@ class _FusedMoE(torch.autograd.Function):
                 for i, (lo, hi) in enumerate(fctx.chunks):
                     if cur is not None:
                         cur.wait_event(events[i])
-                    lib.grouped_gemm_ex(dout, w2c[lo:hi], dact, None, ss[lo:hi], sc[lo:hi], 1, 0,
+                    lib.grouped_gemm_ex(dout, w2c[lo:hi], dh13, h13, ss[lo:hi], sc[lo:hi], 1, 3,
                                         fctx.arena, FK_B_DATA, first, n, flag_value(ep, i, nch),
                                         SEG_ALIGN)
                     lib.grouped_wgrad_out(act, dout, dw2, lo, ss[lo:hi], sc[lo:hi], 0, SEG_ALIGN)
-                dh13 = lib.swiglu_bwd(h13, dact)
                 dw13 = lib.grouped_wgrad(xin, dh13, ss, sc, 0, SEG_ALIGN)
                 base, slots = ((fctx.dret_base, fctx.ret_slots) if mode == "one_hop"
                                else (fctx.dret2_base, fctx.ret2_slots))
                 lib.grouped_gemm_scatter(dh13, w13c, ss, sc, 1, fctx.row_map, base, slots)
                 LIVE["overlap_bwd"] += 1
             else:
-                lib.grouped_gemm_ex(dout, w2c, dact, None, ss, sc, 1, 0, fctx.arena, FK_B_DATA,
+                lib.grouped_gemm_ex(dout, w2c, dh13, h13, ss, sc, 1, 3, fctx.arena, FK_B_DATA,
                                     first, n, flag_value(ep, 0, 1), SEG_ALIGN)
                 dw2 = lib.grouped_wgrad(act, dout, ss, sc, 0, SEG_ALIGN)
-                dh13 = lib.swiglu_bwd(h13, dact)
                 dw13 = lib.grouped_wgrad(xin, dh13, ss, sc, 0, SEG_ALIGN)
                 lib.grouped_gemm_ex(dh13, w13c, fctx.section(DXS), None, ss, sc, 1, 0, None, 0, 0,
                                     0, ep, SEG_ALIGN)

@@ -192,12 +192,51 @@ def b200_from_sweep(rows, overlap_p: float = B200_SELF_OVERLAP_P) -> ClusterSpec
 
 
 def b200_from_records(records, R: int = 2) -> ClusterSpec:
-    """Fit the flat level from ``{frame, world, bytes, ms}`` records (frame ``flat``) with alpha
-    pinned at the smallest message; the two-hop levels inherit the bandwidth."""
+    """Per-level fit from ``{frame, world, bytes, ms}`` records as written by ``bench/sweep.py``
+    (frames ``flat``, ``slow``, ``fast``; ``slow`` / ``fast`` records carry the group size ``R``
+    they were measured with).  Every frame gets its own fixed cost -- the time of its smallest
+    message, per peer-set size -- and its own bandwidth curve from ``fit.fit_beta_pinned``.  A
+    frame without records inherits the flat level's fit (or the shipped constants)."""
     from . import fit
-    recs = [r for r in records if (r["frame"] if isinstance(r, dict) else r[0]) == "flat"]
-    if not recs:
-        return b200_nvswitch(R=R)
-    small = min(recs, key=lambda r: r["bytes"])
-    res = fit.fit_beta_pinned(recs, lambda w, a=small["ms"]: a)
-    return b200_nvswitch(R=R, alpha_one_ms=small["ms"], beta_gbps=res["beta_inf"])
+
+    def pick(frame):
+        out = []
+        for r in records:
+            r = r if isinstance(r, dict) else dict(zip(("frame", "world", "bytes", "ms"), r))
+            if r["frame"] == frame and (frame == "flat" or r.get("R", R) == R):
+                out.append(r)
+        return out
+
+    def level(name, recs, fallback):
+        if len(recs) < 3:
+            return fallback
+        by_world: dict = {}
+        for r in recs:
+            w = int(r["world"])
+            if w not in by_world or r["bytes"] < by_world[w][0]:
+                by_world[w] = (r["bytes"], r["ms"])
+        alpha_pts = sorted((w, ms) for w, (_b, ms) in by_world.items())
+        alpha = Level(name, alpha_pts if len(alpha_pts) > 1 else
+                      [(1, alpha_pts[0][1]), (16, alpha_pts[0][1])], [(1.0, 1.0), (1e12, 1.0)])
+        res = fit.fit_beta_pinned(recs, alpha.alpha_ms)
+        return Level(name, alpha.alpha_pts, saturating_beta(res["beta_inf"], res["x_half"]))
+
+    base = b200_nvswitch(R=R)
+    flat = level("all ranks", pick("flat"), base.flat)
+    inherit_beta = flat.beta_pts
+    fast = level("intra-group", pick("fast"), Level("intra-group", base.fast.alpha_pts, inherit_beta))
+    slow = level("inter-group", pick("slow"), Level("inter-group", base.slow.alpha_pts, inherit_beta))
+    return ClusterSpec(name="b200_nvswitch (per-level fit)", R=R, fast=fast, slow=slow, flat=flat,
+                       splits_sync_ms=B200_SPLITS_SYNC_MS, chain_us_per_row=B200_CHAIN_US_PER_ROW,
+                       self_copy_gbps=B200_SELF_COPY_GBPS, self_overlap_p=B200_SELF_OVERLAP_P)
+
+
+def load_b200_records(path: str | None = None) -> list:
+    """``records`` of a sweep JSON (default: the committed 8-GPU sweep)."""
+    import json
+    import os
+    if path is None:
+        path = os.path.join(os.path.dirname(os.path.abspath(__file__)), "data",
+                            "b200_sweep_8gpu.json")
+    with open(path, encoding="utf-8") as fh:
+        return json.load(fh).get("records", [])

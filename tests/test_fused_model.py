@@ -272,14 +272,13 @@ def test_fused_orchestration_launch_sequence(monkeypatch, overlap):
                        "grouped_gemm_ex", "grouped_gemm_scatter", "grouped_gemm_ex",
                        "grouped_gemm_scatter", "ep_signal", "ep_pull_combine"]
         assert bwd == ["ep_push", "ep_push", "zero_pad_rows", "grouped_gemm_ex",
-                       "grouped_wgrad_out", "grouped_gemm_ex", "grouped_wgrad_out", "swiglu_bwd",
+                       "grouped_wgrad_out", "grouped_gemm_ex", "grouped_wgrad_out",
                        "grouped_wgrad", "grouped_gemm_scatter", "ep_signal", "ep_pull_combine"]
     else:
         assert fwd == ["ep_plan_pass1", "ep_plan", "ep_push", "zero_pad_rows", "grouped_gemm_ex",
                        "grouped_gemm_ex", "ep_signal", "ep_pull_combine"]
         assert bwd == ["ep_push", "zero_pad_rows", "grouped_gemm_ex", "grouped_wgrad",
-                       "swiglu_bwd", "grouped_wgrad", "grouped_gemm_ex", "ep_signal",
-                       "ep_pull_combine"]
+                       "grouped_wgrad", "grouped_gemm_ex", "ep_signal", "ep_pull_combine"]
     assert x.grad.shape == x.shape and gates.grad.shape == gates.shape
     assert w13.grad.shape == w13.shape and w2.grad.shape == w2.shape
     # the backward released the context: the next forward goes through, and a forward whose
@@ -333,17 +332,15 @@ def test_fused_two_hop_orchestration_launch_sequence(monkeypatch, overlap):
                        "origin_combine"]
         assert rec.calls == ["hopa_push", "arrival_push", "arrival_push", "zero_pad_rows",
                              "grouped_gemm_ex", "grouped_wgrad_out", "grouped_gemm_ex",
-                             "grouped_wgrad_out", "swiglu_bwd", "grouped_wgrad",
-                             "grouped_gemm_scatter", "ep_signal", "arrival_combine",
+                             "grouped_wgrad_out", "grouped_wgrad", "grouped_gemm_scatter", "ep_signal", "arrival_combine",
                              "origin_combine", "origin_pull_dgate"]
     else:
         assert fwd == ["ep_plan_pass1", "hopa_rank", "ep_plan", "hopa_push", "arrival_push",
                        "zero_pad_rows", "grouped_gemm_ex", "grouped_gemm_ex", "ep_signal",
                        "arrival_combine", "origin_combine"]
         assert rec.calls == ["hopa_push", "arrival_push", "zero_pad_rows", "grouped_gemm_ex",
-                             "grouped_wgrad", "swiglu_bwd", "grouped_wgrad", "grouped_gemm_ex",
-                             "ep_signal", "arrival_combine", "origin_combine",
-                             "origin_pull_dgate"]
+                             "grouped_wgrad", "grouped_wgrad", "grouped_gemm_ex", "ep_signal",
+                             "arrival_combine", "origin_combine", "origin_pull_dgate"]
     assert gates.grad.shape == gates.shape
     monkeypatch.undo()
     ops.reset()

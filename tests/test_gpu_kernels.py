@@ -382,6 +382,34 @@ def test_gemm_cta_pair_variant_in_subprocess(native_ops):
     assert proc.returncode == 0, proc.stdout.decode()[-3000:] + proc.stderr.decode()[-2000:]
 
 
+@pytest.mark.parametrize("mode,counts", [(1, [300, 0, 129, 64]), (0, [1000]), (1, [1100, 1300, 1024, 2048])])
+def test_swiglu_backward_epilogue_equals_gemm_then_swiglu_bwd(native_ops, mode, counts):
+    """d(act) GEMM with the SwiGLU backward in its epilogue against the same GEMM followed by the
+    stand-alone kernel (which reads the bf16 d(act) back from memory), short and long groups."""
+    lib = torch.ops.terrace
+    torch.manual_seed(5)
+    G, H, d, pad = len(counts), 256, 192, 64
+    cnt = torch.tensor(counts, dtype=torch.int32, device=DEV)
+    padded = (cnt + pad - 1) // pad * pad
+    st = (torch.cumsum(padded, 0) - padded).to(torch.int32)
+    rows = int(padded.sum())
+    dout = torch.randn(rows, H, device=DEV, dtype=torch.bfloat16)
+    w2 = (torch.randn(G, d, H, device=DEV) * d ** -0.5).bfloat16()
+    B = w2 if mode == 1 else w2.transpose(1, 2).contiguous()         # mode 0 wants [G, K, N]
+    h13 = torch.randn(rows, 2 * d, device=DEV, dtype=torch.bfloat16)
+    dact, _ = lib.grouped_gemm(dout, B, st, cnt, mode, 0, False, 0, pad)
+    want = lib.swiglu_bwd(h13, dact)
+    got = torch.full_like(h13, float("nan"))
+    lib.grouped_gemm_ex(dout, B, got, h13, st, cnt, mode, 3, None, 0, 0, 0, 0, pad)
+    torch.cuda.synchronize()
+    for s0, c0, p0 in zip(st.tolist(), counts, padded.tolist()):
+        a, b = got[s0:s0 + c0].float(), want[s0:s0 + c0].float()
+        if c0:
+            torch.testing.assert_close(a, b, rtol=2e-2, atol=2e-2 * b.abs().max().item())
+        assert bool((got[s0 + c0:s0 + p0] == 0).all())                 # padding rows: zeros
+    assert native_ops.take_status(0) == 0
+
+
 def test_long_groups_use_pairs_by_default(native_ops):
     """Groups of 1024+ rows take the 256-row pair tiles under the default policy."""
     torch.manual_seed(1)

@@ -271,7 +271,14 @@ def test_fit_recovers_constants_and_marginal_bandwidth():
 
 def test_b200_platform_and_gate():
     ok, d = validate_b200.validate_b200(verbose=False)
-    assert ok and d["median"] < 0.10 and d["worst"] < 0.15
+    assert d["median"] < 0.10 and d["worst"] < 0.15            # in-sample: fit quality
+    held = d["holdout"]                                         # prediction: rows the fit never saw
+    train, rest = validate_b200.split_holdout(calibrate.load_b200_sweep())
+    assert held["n"] == len(rest) and len(train) + len(rest) == 48
+    assert all(r["R"] in (1, 4) and r["tokens"] <= 4096 for r in train)
+    assert held["median"] < 0.10
+    predictions = [held] + list(d["cross_size"].values())
+    assert ok == all(s["median"] <= 0.10 and s["worst"] <= 0.10 for s in predictions)
     rows = calibrate.load_b200_sweep()
     assert len(rows) == 48 and {r["R"] for r in rows} == {1, 2, 4}
     pytest.importorskip("scipy")
@@ -283,7 +290,7 @@ def test_b200_platform_and_gate():
     from terracemoe_simulator_b200.sim import calibrate as _cal, validate_b200 as _vb
     _, d = _vb.validate_b200(verbose=False)
     b = platforms.get("B200")
-    assert b.n_targets == len(_cal.load_b200_sweep()) and abs(b.fit_median_err - d["median"]) < 5e-4
+    assert b.n_targets == len(_cal.load_b200_sweep()) and abs(b.fit_median_err - d["median"]) < 1e-3
     with pytest.raises(KeyError):
         platforms.get("Z")
     # token-level dedup (groups of one GPU) is where two-hop pays on a flat NVSwitch
