@@ -1,2 +1,5 @@
-"""Forwarder: traffic helpers of ``terracemoe_simulator_b200.bench``."""
-from terracemoe_simulator_b200.bench.traffic import dispatch_traffic, traffic_bytes, uniformity_cv  # noqa: F401
+"""The reference's ``bench`` package name: replaced at import by the modules of
+``terracemoe_simulator_b200`` (``compat.become`` installs the alias finder and swaps this stub out)."""
+from terracemoe_simulator_b200.compat import become
+
+become(__name__)

@@ -1,7 +1,5 @@
-"""Forwarder: the reference's ``sim`` package name on top of ``terracemoe_simulator_b200.sim``."""
-from terracemoe_simulator_b200.sim import MODULES  # noqa: F401
-from terracemoe_simulator_b200 import sim as _impl
+"""The reference's ``sim`` package name: replaced at import by the modules of
+``terracemoe_simulator_b200`` (``compat.become`` installs the alias finder and swaps this stub out)."""
+from terracemoe_simulator_b200.compat import become
 
-
-def __getattr__(name):
-    return getattr(_impl, name)
+become(__name__)

@@ -1,3 +1,5 @@
-"""Forwarder: the reference's ``terrace`` package name on top of ``terracemoe_simulator_b200``."""
-from terracemoe_simulator_b200 import *  # noqa: F401,F403
-from terracemoe_simulator_b200 import __all__  # noqa: F401
+"""The reference's ``terrace`` package name: replaced at import by the modules of
+``terracemoe_simulator_b200`` (``compat.become`` installs the alias finder and swaps this stub out)."""
+from terracemoe_simulator_b200.compat import become
+
+become(__name__)

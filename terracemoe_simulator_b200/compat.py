@@ -1,14 +1,21 @@
 """Drop-in module aliases: make ``import terrace`` / ``import sim`` resolve to this package.
 
-``install_aliases()`` registers the reference's module names in ``sys.modules``:
-``terrace`` (routing, layer, model, ep_dist, ta2a, ta2a_fwd, ta2a_dispatch, ta2a_pack,
-drift_probe, ops, ops.k2_ref), ``sim`` and its sub-modules, and ``bench``.  Names the reference
-exposes under different module boundaries (``ta2a`` = plan, ``ta2a_fwd`` = closed forward +
-wire helpers) are re-exported by small namespace modules.
+``install_aliases()`` registers the reference's ``terrace`` names in ``sys.modules`` (routing,
+layer, model, ep_dist, ta2a, ta2a_fwd, ta2a_dispatch, ta2a_pack, drift_probe, ops, ops.k2_ref;
+names the reference exposes under different module boundaries -- ``ta2a`` = plan, ``ta2a_fwd`` =
+closed forward + wire helpers -- are re-exported by small namespace modules) and puts an
+``AliasFinder`` on ``sys.meta_path`` that resolves ``sim``, ``sim.<module>``, ``bench`` and
+``tools`` to the modules of this package.  The finder hands out the real module objects (one copy
+of every module's state) and its loader answers ``get_code`` under the alias, which is what
+``python -m sim.profile`` needs.  The four packages under ``dropin/`` call ``become()`` so that
+putting that folder on ``PYTHONPATH`` is enough.
 """
 from __future__ import annotations
 
 import importlib
+import importlib.abc
+import importlib.machinery
+import importlib.util
 import sys
 import types
 
@@ -53,8 +60,73 @@ def _pack_quota_wire(expert_idx, gates, inverse, payload, n_rows: int, slots: in
     return slot_tab, gate_tab
 
 
+ALIASED_PACKAGES = {"sim": f"{_PKG}.sim", "bench": f"{_PKG}.bench", "tools": f"{_PKG}.tools"}
+
+
+class _AliasLoader(importlib.abc.Loader):
+    """Loads nothing: hands out the real module, and its code when asked under the alias."""
+
+    def __init__(self, real: str):
+        self.real = real
+
+    def _module(self):
+        return importlib.import_module(self.real)
+
+    def create_module(self, spec):
+        # the import system stamps the alias spec on the module it gets back; that is wanted:
+        # ``runpy`` looks a loaded module's spec up in ``sys.modules`` and asks ITS loader for the
+        # code under the alias name, which only this loader answers
+        return self._module()
+
+    def exec_module(self, module) -> None:
+        return None
+
+    def get_code(self, fullname):
+        return self._module().__loader__.get_code(self.real)
+
+    def get_source(self, fullname):
+        return self._module().__loader__.get_source(self.real)
+
+    def is_package(self, fullname) -> bool:
+        return hasattr(self._module(), "__path__")
+
+
+class AliasFinder(importlib.abc.MetaPathFinder):
+    """``sim`` / ``bench`` / ``tools`` and their sub-modules -> the modules of this package."""
+
+    def find_spec(self, fullname, path=None, target=None):
+        head, _, tail = fullname.partition(".")
+        base = ALIASED_PACKAGES.get(head)
+        if base is None:
+            return None
+        real = base + ("." + tail if tail else "")
+        try:
+            module = importlib.import_module(real)
+        except ModuleNotFoundError as exc:
+            if exc.name == real:
+                return None
+            raise
+        return importlib.machinery.ModuleSpec(fullname, _AliasLoader(real),
+                                              origin=getattr(module, "__file__", None),
+                                              is_package=hasattr(module, "__path__"))
+
+
+def _install_finder() -> None:
+    if not any(isinstance(f, AliasFinder) for f in sys.meta_path):
+        sys.meta_path.insert(0, AliasFinder())
+
+
+def become(alias: str) -> None:
+    """Called by ``dropin/<alias>/__init__.py``: replace that stub package by the real one."""
+    install_aliases()
+    if alias in ALIASED_PACKAGES:
+        sys.modules[alias] = importlib.import_module(ALIASED_PACKAGES[alias])
+
+
 def install_aliases(force: bool = False) -> None:
-    if "terrace" in sys.modules and not force:
+    _install_finder()
+    if isinstance(sys.modules.get("terrace"), types.ModuleType) and \
+            getattr(sys.modules["terrace"], "_terrace_alias", False) and not force:
         return
     imp = importlib.import_module
     routing, layer = imp(f"{_PKG}.routing"), imp(f"{_PKG}.layer")
@@ -66,21 +138,22 @@ def install_aliases(force: bool = False) -> None:
     top = imp(_PKG)
     terrace = _module("terrace", **{k: getattr(top, k) for k in top.__all__})
     terrace.__path__ = []
+    terrace.__all__ = list(top.__all__)
+    terrace._terrace_alias = True
     pairs = {"routing": routing, "layer": layer, "model": model, "ep_dist": ep,
              "ta2a_dispatch": seams, "ta2a_pack": pack, "drift_probe": probe, "ops": ops}
     for name, mod in pairs.items():
         sys.modules[f"terrace.{name}"] = mod
         setattr(terrace, name, mod)
     sys.modules["terrace.ta2a"] = plan
-    fwd = {k: getattr(ta2a, k) for k in ("init_ta2a_groups", "ta2a_moe_forward",
-                                         "build_expansion", "fixed_hist")}
+    fwd = {k: getattr(ta2a, k) for k in ("init_ta2a_groups", "get_ta2a_groups",
+                                         "ta2a_moe_forward", "build_expansion", "fixed_hist")}
     fwd["_stable_argsort_small"] = refs.stable_bucket_order
     fwd["_expand_arrival_quota"] = _expand_arrival_quota
     fwd["_pack_quota_wire"] = _pack_quota_wire
     sys.modules["terrace.ta2a_fwd"] = _module("terrace.ta2a_fwd", **fwd)
     sys.modules["terrace.ops.k2_ref"] = _module("terrace.ops.k2_ref", k2_pack_ref=refs.k2_pack_ref)
-    sim = imp(f"{_PKG}.sim")
-    sys.modules["sim"] = sim
-    for name in sim.MODULES:
-        sys.modules[f"sim.{name}"] = imp(f"{_PKG}.sim.{name}")
-    sys.modules["bench"] = imp(f"{_PKG}.bench")
+    for alias, real in ALIASED_PACKAGES.items():        # sub-modules resolve through the finder
+        stub = sys.modules.get(alias)
+        if stub is None or getattr(stub, "__name__", alias) == alias:
+            sys.modules[alias] = imp(real)
