@@ -38,7 +38,8 @@ def main(argv=None) -> int:
     ap.add_argument("--tokens", type=int, default=8192)
     ap.add_argument("--capacity", type=float, default=1.25)
     ap.add_argument("--ep", default="two_hop", choices=["one_hop", "two_hop"])
-    ap.add_argument("--rpn", type=int, default=1)
+    ap.add_argument("--rpn", type=int, default=0,
+                    help="GPUs per logical group (0: world / routing groups, at least 1)")
     ap.add_argument("--nccl", action="store_true")
     ap.add_argument("--cpu", action="store_true")
     ap.add_argument("--dtype", default="bf16", choices=["bf16", "fp32"])
@@ -46,6 +47,8 @@ def main(argv=None) -> int:
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local = int(os.environ.get("LOCAL_RANK", "0"))
+    if ns.rpn <= 0:
+        ns.rpn = max(world // ns.groups, 1)
     cuda = torch.cuda.is_available() and not ns.cpu
     os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
     os.environ.setdefault("MASTER_PORT", "29543")

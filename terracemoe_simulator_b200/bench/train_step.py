@@ -4,9 +4,11 @@
     python -m torch.distributed.run --nproc-per-node 8 \
         -m terracemoe_simulator_b200.bench.train_step --ep two_hop --rpn 2
 
-Default shape: 16-layer decoder, d_model 2048, 16 heads, 64 SwiGLU experts of hidden 1024 per MoE
-layer (every layer between a dense first and a dense last layer), top-4 in 2 of 4 routing groups,
-one shared expert, 8 sequences of 4096 tokens per GPU, bf16 parameters, AdamW.  One step =
+Default shape: 16-layer decoder, d_model 2048, 16 heads, RoPE, RMSNorm, EVERY layer MoE with 64
+SwiGLU experts of hidden 1024 (``--dense-ends`` restores a dense first and last layer), top-4 in
+2 of 4 routing groups, one shared expert, balance aux loss coefficient 0.01, 8 sequences of 4096
+tokens per GPU, bf16 parameters, AdamW; with N ranks the 4 routing groups are logical groups of
+N / 4 GPUs (8 GPUs: 4 groups of 2).  One step =
 pinned host -> device copy of the token batch, forward, loss, backward, gradient average of the
 replicated parameters over the ranks, optimizer step, device -> host read of the loss (consumed one step later so that the host keeps
 launching ahead).  With N
@@ -34,7 +36,8 @@ def build_args(ns, world: int):
     return ModelArgs(vocab=ns.vocab, dim=ns.dim, n_layers=ns.layers, n_heads=ns.heads,
                      seq_len=ns.seq, n_experts=ns.experts, n_groups=ns.groups, top_k=ns.top_k,
                      top_groups=ns.top_groups, d_expert=ns.d_expert, d_shared=ns.d_shared,
-                     n_shared=1, dense_first=1, expert_backend=ns.backend,
+                     n_shared=1, dense_first=1, moe_every_layer=not ns.dense_ends,
+                     balance_aux=ns.balance_aux, expert_backend=ns.backend,
                      ep_mode=ns.ep if world > 1 else "local", ep_rpn=ns.rpn,
                      ep_fused=not ns.nccl, ce_chunk=ns.ce_chunk)
 
@@ -56,7 +59,11 @@ def main(argv=None) -> int:
     ap.add_argument("--batch", type=int, default=8, help="sequences per GPU")
     ap.add_argument("--vocab", type=int, default=32000)
     ap.add_argument("--ep", default="two_hop", choices=["one_hop", "two_hop"])
-    ap.add_argument("--rpn", type=int, default=1)
+    ap.add_argument("--rpn", type=int, default=0,
+                    help="GPUs per logical group (0: world / routing groups, at least 1)")
+    ap.add_argument("--dense-ends", action="store_true",
+                    help="dense FFN in the first and the last layer instead of MoE everywhere")
+    ap.add_argument("--balance-aux", type=float, default=0.01)
     ap.add_argument("--nccl", action="store_true", help="all_to_all arm instead of fused kernels")
     ap.add_argument("--backend", default="native", choices=["native", "grouped", "loop"])
     ap.add_argument("--dtype", default="bf16", choices=["bf16", "fp32"])
@@ -73,6 +80,8 @@ def main(argv=None) -> int:
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local = int(os.environ.get("LOCAL_RANK", "0"))
+    if ns.rpn <= 0:
+        ns.rpn = max(world // ns.groups, 1)
     cuda = torch.cuda.is_available() and not ns.cpu
     os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
     os.environ.setdefault("MASTER_PORT", "29541")
@@ -112,6 +121,7 @@ def main(argv=None) -> int:
     from ..utils.prefetch import DeferredScalar, DevicePrefetcher
     feed = DevicePrefetcher(itertools.cycle(host), device)
     losses = DeferredScalar(device)          # every step's loss reaches the host, one step late
+    health = DeferredScalar(device)          # and so does the transport's status word
 
     hb = None
     if ns.heartbeat and world > 1:
@@ -127,13 +137,18 @@ def main(argv=None) -> int:
         tok = next(feed)
         state["i"] += 1
         opt.zero_grad(set_to_none=True)
-        loss, _ = model(tok[:, :-1], tok[:, 1:])
+        loss, info = model(tok[:, :-1], tok[:, 1:])
         loss.backward()
         sync.sync()
         opt.step()
         prev = losses.push(loss)                 # device -> host read of the result (deferred)
         if prev is not None:
             state["loss"] = prev
+        if "ep_status" in info:                  # a skipped row or a wait that ran out: stop here
+            code = health.push(info["ep_status"].float().sum())
+            if code:
+                raise RuntimeError(f"expert-parallel kernels reported status {int(code)} "
+                                   "(5: routed rows exceeded the arena's row capacity)")
 
     def barrier():
         if cuda:

@@ -129,12 +129,16 @@ class Attention(nn.Module):
         native = x.is_cuda and ops.custom_ops_enabled()
         proj = native and ops.dense_supported(x, self.wqkv.weight)
         qkv = ops.linear(x, self.wqkv.weight) if proj else self.wqkv(x)
-        q, k, v = qkv.chunk(3, dim=-1)
-        q = q.view(B, T, self.nh, self.hd).transpose(1, 2)
-        k = k.view(B, T, self.nh, self.hd).transpose(1, 2)
-        v = v.view(B, T, self.nh, self.hd).transpose(1, 2)
-        q = _rope(q, cos, sin).to(v.dtype)
-        k = _rope(k, cos, sin).to(v.dtype)
+        if native and ops.rope_split_supported(qkv, self.nh):
+            # head split, RoPE and the [B, heads, T, hd] layout in one kernel
+            q, k, v = ops.rope_split(qkv, cos, sin, self.nh)
+        else:
+            q, k, v = qkv.chunk(3, dim=-1)
+            q = q.view(B, T, self.nh, self.hd).transpose(1, 2)
+            k = k.view(B, T, self.nh, self.hd).transpose(1, 2)
+            v = v.view(B, T, self.nh, self.hd).transpose(1, 2)
+            q = _rope(q, cos, sin).to(v.dtype)
+            k = _rope(k, cos, sin).to(v.dtype)
         if native and ops.attention_supported(x, self.nh):
             o = ops.attention(q, k, v, causal=True)      # tcgen05 flash attention, fwd and bwd
         else:
@@ -207,10 +211,12 @@ class TerraceLM(nn.Module):
         x = self.tok(idx)
         cos, sin = self.cos[..., :T, :], self.sin[..., :T, :]
         loads, routes, gate_l, idx_l = [], [], [], []
+        ep_status = None
         for blk in self.blocks:
             x, stats = blk(x, cos, sin)
             if stats is None:
                 continue
+            ep_status = stats.get("ep_status", ep_status)
             loads.append(stats["expert_load"])
             gate_l.append(stats["gates"])
             idx_l.append(stats["expert_idx"])
@@ -229,8 +235,10 @@ class TerraceLM(nn.Module):
         else:
             aux = lm.new_zeros(())
         loss = lm + self.args.balance_aux * aux
-        return loss, {"lm_loss": lm.detach(), "aux": aux.detach(), "loads": loads,
-                      "routes": routes}
+        info = {"lm_loss": lm.detach(), "aux": aux.detach(), "loads": loads, "routes": routes}
+        if ep_status is not None:        # device status word of the fused transport (no sync)
+            info["ep_status"] = ep_status
+        return loss, info
 
     def n_params(self) -> int:
         return sum(p.numel() for p in self.parameters())

@@ -305,7 +305,8 @@ def k2_pack(hidden, expert_idx, gates, world: int, n_experts: int, rpn: int, gro
 from .native import (  # noqa: E402
     attention, attention_shape_supported, attention_supported, dense_supported, fused_route, grouped_mm_native,
     grouped_supported, linear, moe_experts_local, moe_local_supported, rmsnorm, rmsnorm_supported,
-    route_from_logits, route_fused_supported, route_hidden, router_supported,
+    rope_split, rope_split_supported, route_from_logits, route_fused_supported, route_hidden,
+    router_supported,
     segments_from_counts, swiglu_ffn, take_status)
 
 __all__ = [

@@ -397,6 +397,52 @@ Tensor swiglu_bwd(const Tensor& h13, const Tensor& dact) {
   return dh;
 }
 
+// qkv [B, T, 3 * nh * hd] bf16 -> (q, k, v) [B, nh, T, hd]; q and k rotated (interleaved RoPE)
+std::tuple<Tensor, Tensor, Tensor> rope_split(const Tensor& qkv, const Tensor& cos_t,
+                                              const Tensor& sin_t, int64_t n_heads) {
+  CHECK_CUDA_CONTIG(qkv);
+  CHECK_CUDA_CONTIG(cos_t);
+  CHECK_CUDA_CONTIG(sin_t);
+  TORCH_CHECK(qkv.dim() == 3 && qkv.scalar_type() == at::kBFloat16 && qkv.size(2) % (3 * n_heads) == 0,
+              "rope_split: bf16 qkv [B, T, 3 * heads * head_dim]");
+  const int64_t B = qkv.size(0), T = qkv.size(1), hd = qkv.size(2) / (3 * n_heads);
+  TORCH_CHECK(hd % 8 == 0 && cos_t.scalar_type() == at::kFloat && sin_t.scalar_type() == at::kFloat &&
+                  cos_t.numel() == T * hd / 2 && sin_t.numel() == T * hd / 2,
+              "rope_split: head_dim % 8 == 0 and fp32 cos / sin tables [T, head_dim / 2]");
+  c10::cuda::CUDAGuard guard(qkv.device());
+  Tensor q = at::empty({B, n_heads, T, hd}, qkv.options());
+  Tensor k = at::empty_like(q), v = at::empty_like(q);
+  check_rc(tb200_rope_split_merge(qkv.data_ptr(), q.data_ptr(), k.data_ptr(), v.data_ptr(),
+                                  cos_t.data_ptr<float>(), sin_t.data_ptr<float>(), B, T, n_heads,
+                                  hd, 0, cur_stream()),
+           "rope_split");
+  return {q, k, v};
+}
+
+// the adjoint: (dq, dk, dv) [B, nh, T, hd] -> dqkv [B, T, 3 * nh * hd]
+Tensor rope_merge(const Tensor& dq, const Tensor& dk, const Tensor& dv, const Tensor& cos_t,
+                  const Tensor& sin_t) {
+  CHECK_CUDA_CONTIG(dq);
+  CHECK_CUDA_CONTIG(dk);
+  CHECK_CUDA_CONTIG(dv);
+  CHECK_CUDA_CONTIG(cos_t);
+  CHECK_CUDA_CONTIG(sin_t);
+  TORCH_CHECK(dq.dim() == 4 && dq.scalar_type() == at::kBFloat16 && dq.sizes() == dk.sizes() &&
+                  dq.sizes() == dv.sizes() && dk.scalar_type() == at::kBFloat16 &&
+                  dv.scalar_type() == at::kBFloat16,
+              "rope_merge: three bf16 tensors [B, heads, T, head_dim]");
+  const int64_t B = dq.size(0), nh = dq.size(1), T = dq.size(2), hd = dq.size(3);
+  TORCH_CHECK(hd % 8 == 0 && cos_t.numel() == T * hd / 2 && sin_t.numel() == T * hd / 2,
+              "rope_merge: fp32 cos / sin tables [T, head_dim / 2]");
+  c10::cuda::CUDAGuard guard(dq.device());
+  Tensor dqkv = at::empty({B, T, 3 * nh * hd}, dq.options());
+  check_rc(tb200_rope_split_merge(dqkv.data_ptr(), dq.data_ptr(), dk.data_ptr(), dv.data_ptr(),
+                                  cos_t.data_ptr<float>(), sin_t.data_ptr<float>(), B, T, nh, hd, 1,
+                                  cur_stream()),
+           "rope_merge");
+  return dqkv;
+}
+
 void zero_pad_rows(Tensor buf, const Tensor& seg_start, const Tensor& seg_count, int64_t align) {
   TORCH_CHECK(buf.is_cuda() && buf.is_contiguous() && buf.dim() == 2, "zero_pad_rows: [rows, cols]");
   TORCH_CHECK(seg_start.scalar_type() == at::kInt && seg_count.scalar_type() == at::kInt &&
@@ -582,6 +628,8 @@ TORCH_LIBRARY(terrace, m) {
         "int pad_align=0) -> Tensor");
   m.def("grouped_wgrad_out(Tensor X, Tensor dY, Tensor(a!) dW, int g0, Tensor seg_start, "
         "Tensor seg_count, int max_ctas, int pad_align=0) -> ()");
+  m.def("rope_split(Tensor qkv, Tensor cos, Tensor sin, int n_heads) -> (Tensor, Tensor, Tensor)");
+  m.def("rope_merge(Tensor dq, Tensor dk, Tensor dv, Tensor cos, Tensor sin) -> Tensor");
   m.def("zero_pad_rows(Tensor(a!) buf, Tensor seg_start, Tensor seg_count, int align) -> ()");
   m.def("attn_fwd(Tensor q, Tensor k, Tensor v, bool causal, float scale) -> (Tensor, Tensor)");
   m.def("attn_bwd(Tensor q, Tensor k, Tensor v, Tensor o, Tensor d_o, Tensor lse, bool causal, "
@@ -606,6 +654,8 @@ TORCH_LIBRARY_IMPL(terrace, CUDA, m) {
   m.impl("grouped_gemm", &grouped_gemm);
   m.impl("grouped_wgrad", &grouped_wgrad);
   m.impl("grouped_wgrad_out", &grouped_wgrad_out);
+  m.impl("rope_split", &rope_split);
+  m.impl("rope_merge", &rope_merge);
   m.impl("zero_pad_rows", &zero_pad_rows);
   m.impl("attn_fwd", &attn_fwd);
   m.impl("attn_bwd", &attn_bwd);

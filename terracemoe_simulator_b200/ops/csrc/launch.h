@@ -114,6 +114,12 @@ int tb200_moe_combine(const void* out, const int* pos, const int* es, const floa
 int tb200_moe_combine_bwd(const void* dy, const void* out, const int* pos, const float* gs,
                           void* dout, float* dgs, int T, int k, int dim, long long out_rows,
                           int* status, cudaStream_t stream);
+// RoPE fused with the head split: merge == 0 reads qkv[B, T, 3 * nh * hd] and writes q, k
+// (rotated) and v, each [B, nh, T, hd]; merge == 1 is the adjoint (gradients back into qkv
+// layout, q and k parts rotated by the opposite angle).  cos / sin: fp32 [T, hd / 2].
+int tb200_rope_split_merge(void* qkv, void* q, void* k, void* v, const float* cos_t,
+                           const float* sin_t, int B, int T, int n_heads, int head_dim, int merge,
+                           cudaStream_t stream);
 // SwiGLU backward: h13[rows, 2d] = [gate | up], dact[rows, d] -> dh13[rows, 2d]
 int tb200_swiglu_bwd(const void* h13, const void* dact, void* dh13, long long rows, int d,
                      cudaStream_t stream);

@@ -110,6 +110,17 @@ void grouped_wgrad_out(const Tensor&, const Tensor&, Tensor, int64_t, const Tens
 
 void zero_pad_rows(Tensor, const Tensor&, const Tensor&, int64_t) {}
 
+std::tuple<Tensor, Tensor, Tensor> rope_split(const Tensor& qkv, const Tensor&, const Tensor&,
+                                              int64_t n_heads) {
+  const int64_t hd = qkv.size(2) / (3 * n_heads);
+  auto one = [&]() { return like(qkv, {qkv.size(0), n_heads, qkv.size(1), hd}, qkv.scalar_type()); };
+  return {one(), one(), one()};
+}
+
+Tensor rope_merge(const Tensor& dq, const Tensor&, const Tensor&, const Tensor&, const Tensor&) {
+  return like(dq, {dq.size(0), dq.size(2), 3 * dq.size(1) * dq.size(3)}, dq.scalar_type());
+}
+
 std::tuple<Tensor, Tensor> attn_fwd(const Tensor& q, const Tensor&, const Tensor&, bool, double) {
   auto lead = q.sizes().vec();
   lead.pop_back();
@@ -216,6 +227,8 @@ void terrace_b200_register_meta(torch::Library& m) {
   TB_META(grouped_wgrad);
   TB_META(grouped_wgrad_out);
   TB_META(zero_pad_rows);
+  TB_META(rope_split);
+  TB_META(rope_merge);
   TB_META(attn_fwd);
   TB_META(attn_bwd);
   TB_META(ep_plan_pass1);

@@ -574,6 +574,52 @@ __global__ void swiglu_bwd_kernel(const __nv_bfloat16* __restrict__ h13,
 }
 
 // ---------------------------------------------------------------------------------------------
+// RoPE fused with the head split of the attention input.
+//   split:  qkv[B, T, 3 * nh * hd]  ->  q, k (rotated), v   each [B, nh, T, hd]
+//   merge:  dq, dk (rotated back), dv [B, nh, T, hd]  ->  dqkv[B, T, 3 * nh * hd]
+// Interleaved pairs (even, odd) of the head dimension rotate by the angle of (position, pair):
+//   e' = e cos - o sin,  o' = e sin + o cos      (fp32, rounded once; the adjoint rotates back)
+// One thread moves 8 elements = 4 pairs.  Replaces the slice / multiply / stack / flatten / cast /
+// transpose-copy chain of the reference's `_rope` (terrace/model.py:56-71) with one pass.
+// ---------------------------------------------------------------------------------------------
+__global__ void rope_split_merge_kernel(__nv_bfloat16* __restrict__ qkv,
+                                        __nv_bfloat16* __restrict__ q, __nv_bfloat16* __restrict__ k,
+                                        __nv_bfloat16* __restrict__ v, const float* __restrict__ cs,
+                                        const float* __restrict__ sn, int B, int T, int nh, int hd,
+                                        int merge) {
+  const int D = nh * hd;
+  const int chunks = 3 * D / 8;                      // 16-byte chunks per token
+  const long long total = static_cast<long long>(B) * T * chunks;
+  for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < total;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const long long bt = i / chunks;
+    const int c = static_cast<int>(i - bt * chunks) * 8;       // column inside [0, 3D)
+    const int b = static_cast<int>(bt / T), t = static_cast<int>(bt - static_cast<long long>(b) * T);
+    const int which = c / D, col = c - which * D;               // 0 q, 1 k, 2 v
+    const int h = col / hd, e0 = col - h * hd;
+    __nv_bfloat16* flat = qkv + bt * 3 * D + c;
+    __nv_bfloat16* head = (which == 0 ? q : which == 1 ? k : v) +
+                          ((static_cast<long long>(b) * nh + h) * T + t) * hd + e0;
+    uint4 val = *reinterpret_cast<const uint4*>(merge ? head : flat);
+    if (which < 2) {
+      __nv_bfloat162* pr = reinterpret_cast<__nv_bfloat162*>(&val);
+      const float sign = merge ? -1.0f : 1.0f;                 // the adjoint rotates by -angle
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const int pair = (e0 >> 1) + j;
+        const float co = cs[static_cast<long long>(t) * (hd / 2) + pair];
+        const float si = sign * sn[static_cast<long long>(t) * (hd / 2) + pair];
+        const float2 eo = __bfloat1622float2(pr[j]);
+        // separate roundings (no FMA contraction): the bits of the eager fp32 expression
+        pr[j] = __floats2bfloat162_rn(__fsub_rn(__fmul_rn(eo.x, co), __fmul_rn(eo.y, si)),
+                                      __fadd_rn(__fmul_rn(eo.x, si), __fmul_rn(eo.y, co)));
+      }
+    }
+    *reinterpret_cast<uint4*>(merge ? flat : head) = val;
+  }
+}
+
+// ---------------------------------------------------------------------------------------------
 // Generic stable counting sort of N items by a small key, in two kernels (used by K1 and K2).
 //   pass 1: chunk c (one warp) counts keys of its items and records each item's local rank
 //   pass 2 (one block): bucket bases (bucket-major, chunk-minor) -> base[c][b]; totals[b]
@@ -919,6 +965,22 @@ extern "C" int tb200_swiglu_bwd(const void* h13, const void* dact, void* dh13, l
   swiglu_bwd_kernel<<<sm_count() * 8, 256, 0, stream>>>(static_cast<const __nv_bfloat16*>(h13),
                                                  static_cast<const __nv_bfloat16*>(dact),
                                                  static_cast<__nv_bfloat16*>(dh13), rows, d);
+  return LAUNCH_OK();
+}
+
+extern "C" int tb200_rope_split_merge(void* qkv, void* q, void* k, void* v, const float* cos_t,
+                                      const float* sin_t, int B, int T, int n_heads, int head_dim,
+                                      int merge, cudaStream_t stream) {
+  if (B <= 0 || T <= 0) return TB200_OK;
+  if (head_dim % 8 || n_heads < 1) return TB200_ERR_ARG;
+  const long long total = static_cast<long long>(B) * T * (3 * n_heads * head_dim / 8);
+  long long blocks = (total + 255) / 256;
+  const long long cap = static_cast<long long>(sm_count()) * 16;
+  if (blocks > cap) blocks = cap;
+  rope_split_merge_kernel<<<static_cast<int>(blocks), 256, 0, stream>>>(
+      static_cast<__nv_bfloat16*>(qkv), static_cast<__nv_bfloat16*>(q),
+      static_cast<__nv_bfloat16*>(k), static_cast<__nv_bfloat16*>(v), cos_t, sin_t, B, T, n_heads,
+      head_dim, merge);
   return LAUNCH_OK();
 }
 

@@ -14,7 +14,7 @@ from __future__ import annotations
 
 import torch
 
-LIVE = {"rmsnorm": 0, "route": 0, "route_fused": 0, "linear": 0, "swiglu_ffn": 0, "grouped_mm": 0,
+LIVE = {"rmsnorm": 0, "route": 0, "route_fused": 0, "rope_split": 0, "linear": 0, "swiglu_ffn": 0, "grouped_mm": 0,
         "moe_experts_local": 0, "attention": 0}
 
 
@@ -24,7 +24,8 @@ LAUNCHES = [0]
 
 class _Counted:
     """Proxy of ``torch.ops.terrace`` that counts kernel launches per op call."""
-    _PER_CALL = {"rmsnorm_fwd": 1, "rmsnorm_bwd": 1, "route_select": 1, "route_select_bwd": 1, "route_fused": 1,
+    _PER_CALL = {"rmsnorm_fwd": 1, "rmsnorm_bwd": 1, "route_select": 1, "route_select_bwd": 1, "route_fused": 1, "rope_split": 1,
+                 "rope_merge": 1,
                  "moe_plan": 3, "moe_scatter_rows": 1, "moe_combine": 1, "moe_combine_bwd": 1,
                  "swiglu_bwd": 1, "grouped_gemm": 1, "grouped_wgrad": 1, "passthrough": 1,
                  "zero_pad_rows": 1,
@@ -390,6 +391,37 @@ class _Attention(torch.autograd.Function):
         q, k, v, o, lse = ctx.saved_tensors
         dq, dk, dv = _lib().attn_bwd(q, k, v, o, d_o.contiguous(), lse, ctx.causal, ctx.scale)
         return dq, dk, dv, None, None
+
+
+class _RopeSplit(torch.autograd.Function):
+    """``qkv [B, T, 3 * nh * hd] -> q, k, v [B, nh, T, hd]`` with interleaved RoPE applied to q and
+    k, in one pass (the backward is the same kernel run the other way)."""
+
+    @staticmethod
+    def forward(ctx, qkv, cos, sin, n_heads):
+        q, k, v = _lib().rope_split(qkv.contiguous(), cos, sin, int(n_heads))
+        ctx.save_for_backward(cos, sin)
+        LIVE["rope_split"] += 1
+        return q, k, v
+
+    @staticmethod
+    def backward(ctx, dq, dk, dv):
+        cos, sin = ctx.saved_tensors
+        return (_lib().rope_merge(dq.contiguous(), dk.contiguous(), dv.contiguous(), cos, sin),
+                None, None, None)
+
+
+def rope_split_supported(qkv, n_heads: int) -> bool:
+    return (qkv.is_cuda and qkv.dtype == torch.bfloat16 and qkv.dim() == 3
+            and qkv.shape[-1] % (3 * n_heads) == 0 and (qkv.shape[-1] // (3 * n_heads)) % 8 == 0)
+
+
+def rope_split(qkv, cos, sin, n_heads: int):
+    """``cos`` / ``sin``: the model's RoPE tables ``[..., T, hd / 2]`` (any leading ones)."""
+    T, half = qkv.shape[1], qkv.shape[-1] // (3 * n_heads) // 2
+    c = cos.reshape(-1, half)[:T].float().contiguous()
+    s = sin.reshape(-1, half)[:T].float().contiguous()
+    return _RopeSplit.apply(qkv, c, s, n_heads)
 
 
 def attention_shape_supported(q, causal: bool = True) -> bool:

@@ -134,6 +134,30 @@ def test_route_select_backward(native_ops):
     torch.testing.assert_close(logits.grad, l2.grad, rtol=1e-3, atol=1e-6)
 
 
+def test_rope_split_matches_the_eager_chain(native_ops):
+    """Head split + RoPE in one kernel against the reference formula (fp32, rounded once), forward
+    and backward."""
+    from terracemoe_simulator_b200.models.decoder import _rope
+    torch.manual_seed(6)
+    B, T, nh, hd = 2, 200, 4, 64
+    D = nh * hd
+    inv_freq = 1.0 / (10000.0 ** (torch.arange(0, hd, 2).float() / hd))
+    angle = torch.outer(torch.arange(256).float(), inv_freq).to(DEV)
+    cos, sin = angle.cos()[None, None], angle.sin()[None, None]
+    qkv = torch.randn(B, T, 3 * D, device=DEV).bfloat16().requires_grad_(True)
+    q, k, v = native_ops.rope_split(qkv, cos[..., :T, :], sin[..., :T, :], nh)
+    gq, gk, gv = (torch.randn_like(q) for _ in range(3))
+    torch.autograd.backward((q, k, v), (gq, gk, gv))
+    ref = qkv.detach().clone().requires_grad_(True)
+    rq, rk, rv = (t.view(B, T, nh, hd).transpose(1, 2) for t in ref.chunk(3, dim=-1))
+    rq = _rope(rq, cos[..., :T, :], sin[..., :T, :]).to(rv.dtype)
+    rk = _rope(rk, cos[..., :T, :], sin[..., :T, :]).to(rv.dtype)
+    assert torch.equal(q, rq) and torch.equal(k, rk) and torch.equal(v, rv)
+    torch.autograd.backward((rq, rk, rv), (gq, gk, gv))
+    torch.testing.assert_close(qkv.grad.float(), ref.grad.float(), rtol=2e-2, atol=2e-2)
+    assert q.is_contiguous() and tuple(q.shape) == (B, nh, T, hd)
+
+
 def test_route_fused_matches_fp32_oracle(native_ops):
     """Router GEMM + selection in one launch against x @ W^T in fp32 followed by ``t_route``."""
     from terracemoe_simulator_b200.ops import native
