@@ -203,7 +203,8 @@ std::tuple<Tensor, Tensor> rmsnorm_bwd(const Tensor& x, const Tensor& w, const T
   c10::cuda::CUDAGuard guard(x.device());
   const int64_t dim = x.size(-1), rows = x.numel() / dim;
   Tensor dx = at::empty_like(x);
-  const int n_partial = 148;
+  // one partial weight-gradient row per block, four blocks per SM
+  const int n_partial = 4 * at::cuda::getCurrentDeviceProperties()->multiProcessorCount;
   Tensor part = at::empty({n_partial, dim}, x.options().dtype(at::kFloat));
   check_rc(tb200_rmsnorm_bwd(x.data_ptr(), w.data_ptr(), dy.data_ptr(), rstd.data_ptr<float>(),
                              dx.data_ptr(), part.data_ptr<float>(), n_partial, rows,

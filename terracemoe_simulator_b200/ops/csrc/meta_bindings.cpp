@@ -32,8 +32,9 @@ std::tuple<Tensor, Tensor> rmsnorm_fwd(const Tensor& x, const Tensor&, double) {
 
 std::tuple<Tensor, Tensor> rmsnorm_bwd(const Tensor& x, const Tensor& w, const Tensor&,
                                        const Tensor&) {
-  // per-block partial sums of the weight gradient; the wrapper reduces over dim 0
-  return {at::empty_like(x), like(x, {148, w.numel()}, at::kFloat)};
+  // per-block partial sums of the weight gradient; the wrapper reduces over dim 0, so only the
+  // second extent matters to callers (the first is the block count of a 148-SM device)
+  return {at::empty_like(x), like(x, {4 * 148, w.numel()}, at::kFloat)};
 }
 
 std::tuple<Tensor, Tensor, Tensor, Tensor, Tensor> route_out(const Tensor& ref, int64_t T,

@@ -173,6 +173,189 @@ __global__ void rmsnorm_bwd_kernel(const T* __restrict__ x, const T* __restrict_
   }
 }
 
+// bf16 rows whose width is a multiple of 256: every lane owns 8 consecutive columns per step and
+// moves them with 16-byte accesses; one warp per row, 4 warps per block, several blocks per SM.
+// Same arithmetic and the same fixed summation order per block as the generic kernel above.
+__global__ void rmsnorm_bwd_vec_kernel(const __nv_bfloat16* __restrict__ x,
+                                       const __nv_bfloat16* __restrict__ w,
+                                       const __nv_bfloat16* __restrict__ dy,
+                                       const float* __restrict__ rstd,
+                                       __nv_bfloat16* __restrict__ dx,
+                                       float* __restrict__ dw_partial, long long rows, int dim) {
+  const int lane = threadIdx.x, warp = threadIdx.y, nwarps = blockDim.y;
+  extern __shared__ float sdw[];      // [nwarps][dim]
+  float* mydw = sdw + static_cast<size_t>(warp) * dim;
+  for (int i = lane; i < dim; i += 32) mydw[i] = 0.f;
+  const int steps = dim >> 8;
+  const long long per_block = (rows + gridDim.x - 1) / gridDim.x;
+  const long long r0 = static_cast<long long>(blockIdx.x) * per_block;
+  const long long r1 = min(rows, r0 + per_block);
+  for (long long row = r0 + warp; row < r1; row += nwarps) {
+    const uint4* xr = reinterpret_cast<const uint4*>(x + row * dim);
+    const uint4* dyr = reinterpret_cast<const uint4*>(dy + row * dim);
+    const uint4* wr = reinterpret_cast<const uint4*>(w);
+    float dot = 0.f;
+    for (int j = 0; j < steps; ++j) {
+      const int c = j * 32 + lane;
+      const uint4 xv = xr[c], gv = dyr[c], wv = wr[c];
+      const __nv_bfloat162* xb = reinterpret_cast<const __nv_bfloat162*>(&xv);
+      const __nv_bfloat162* gb = reinterpret_cast<const __nv_bfloat162*>(&gv);
+      const __nv_bfloat162* wb = reinterpret_cast<const __nv_bfloat162*>(&wv);
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const float2 xf = __bfloat1622float2(xb[u]), gf = __bfloat1622float2(gb[u]),
+                     wf = __bfloat1622float2(wb[u]);
+        dot += gf.x * wf.x * xf.x;
+        dot += gf.y * wf.y * xf.y;
+      }
+    }
+    dot = warp_sum(dot);
+    const float r = rstd[row];
+    const float cfac = dot * r * r * r / dim;
+    uint4* dxr = reinterpret_cast<uint4*>(dx + row * dim);
+    for (int j = 0; j < steps; ++j) {
+      const int c = j * 32 + lane;
+      const uint4 xv = xr[c], gv = dyr[c], wv = wr[c];      // second read: L1 / L2
+      const __nv_bfloat162* xb = reinterpret_cast<const __nv_bfloat162*>(&xv);
+      const __nv_bfloat162* gb = reinterpret_cast<const __nv_bfloat162*>(&gv);
+      const __nv_bfloat162* wb = reinterpret_cast<const __nv_bfloat162*>(&wv);
+      uint4 out;
+      __nv_bfloat162* ob = reinterpret_cast<__nv_bfloat162*>(&out);
+      float4* acc = reinterpret_cast<float4*>(mydw + c * 8);
+      float4 a0 = acc[0], a1 = acc[1];
+      float* af[2] = {reinterpret_cast<float*>(&a0), reinterpret_cast<float*>(&a1)};
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const float2 xf = __bfloat1622float2(xb[u]), gf = __bfloat1622float2(gb[u]),
+                     wf = __bfloat1622float2(wb[u]);
+        ob[u] = __floats2bfloat162_rn(gf.x * wf.x * r - xf.x * cfac, gf.y * wf.y * r - xf.y * cfac);
+        af[u >> 1][(u & 1) * 2] += gf.x * xf.x * r;
+        af[u >> 1][(u & 1) * 2 + 1] += gf.y * xf.y * r;
+      }
+      acc[0] = a0;
+      acc[1] = a1;
+      dxr[c] = out;
+    }
+  }
+  __syncthreads();
+  for (int i = threadIdx.y * 32 + lane; i < dim; i += 32 * nwarps) {
+    float acc = 0.f;
+    for (int wv = 0; wv < nwarps; ++wv) acc += sdw[static_cast<size_t>(wv) * dim + i];
+    dw_partial[static_cast<size_t>(blockIdx.x) * dim + i] = acc;
+  }
+}
+
+// bf16 rows whose width is (4..8 warps) x 256 x (1..4): the block's warps split the columns, so a lane
+// owns STEPS groups of 8 columns for the whole kernel and keeps their weight-gradient sums in
+// registers (no shared-memory accumulators, occupancy is bounded by registers only).  x and dy
+// are read once and held between the row dot product and the dx / dw pass; the dot product
+// crosses warps through a double-buffered shared array, one barrier per batch of RB rows.
+// Summation order is fixed: lane partial, warp butterfly, warps in index order.
+template <int STEPS, int RB>
+__global__ void __launch_bounds__(256)
+rmsnorm_bwd_cols_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ w,
+                        const __nv_bfloat16* __restrict__ dy, const float* __restrict__ rstd,
+                        __nv_bfloat16* __restrict__ dx, float* __restrict__ dw_partial,
+                        long long rows, int dim) {
+  const int lane = threadIdx.x, warp = threadIdx.y, nwarps = blockDim.y;
+  __shared__ float s_dot[2][RB][8];
+  // column group (of 8) owned by this lane in step j: (j * nwarps + warp) * 32 + lane
+  float wf[STEPS][8], dwacc[STEPS][8];
+#pragma unroll
+  for (int j = 0; j < STEPS; ++j) {
+    const uint4 wv = reinterpret_cast<const uint4*>(w)[(j * nwarps + warp) * 32 + lane];
+    const __nv_bfloat162* wb = reinterpret_cast<const __nv_bfloat162*>(&wv);
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      const float2 f = __bfloat1622float2(wb[u]);
+      wf[j][2 * u] = f.x;
+      wf[j][2 * u + 1] = f.y;
+      dwacc[j][2 * u] = 0.f;
+      dwacc[j][2 * u + 1] = 0.f;
+    }
+  }
+  const long long per_block = (rows + gridDim.x - 1) / gridDim.x;
+  const long long r0 = static_cast<long long>(blockIdx.x) * per_block;
+  const long long r1 = min(rows, r0 + per_block);
+  const int groups_per_row = dim >> 3;
+  int buf = 0;
+  for (long long base = r0; base < r1; base += RB, buf ^= 1) {
+    uint4 xv[RB][STEPS], gv[RB][STEPS];
+    float part[RB];
+#pragma unroll
+    for (int b = 0; b < RB; ++b) {
+      const long long row = base + b;
+      part[b] = 0.f;
+      if (row < r1) {
+        const uint4* xr = reinterpret_cast<const uint4*>(x) + row * groups_per_row;
+        const uint4* gr = reinterpret_cast<const uint4*>(dy) + row * groups_per_row;
+#pragma unroll
+        for (int j = 0; j < STEPS; ++j) {
+          xv[b][j] = xr[(j * nwarps + warp) * 32 + lane];
+          gv[b][j] = gr[(j * nwarps + warp) * 32 + lane];
+        }
+#pragma unroll
+        for (int j = 0; j < STEPS; ++j) {
+          const __nv_bfloat162* xb = reinterpret_cast<const __nv_bfloat162*>(&xv[b][j]);
+          const __nv_bfloat162* gb = reinterpret_cast<const __nv_bfloat162*>(&gv[b][j]);
+#pragma unroll
+          for (int u = 0; u < 4; ++u) {
+            const float2 xf = __bfloat1622float2(xb[u]), gf = __bfloat1622float2(gb[u]);
+            part[b] += gf.x * wf[j][2 * u] * xf.x;
+            part[b] += gf.y * wf[j][2 * u + 1] * xf.y;
+          }
+        }
+      }
+      part[b] = warp_sum(part[b]);
+      if (lane == 0) s_dot[buf][b][warp] = part[b];
+    }
+    __syncthreads();
+#pragma unroll
+    for (int b = 0; b < RB; ++b) {
+      const long long row = base + b;
+      if (row >= r1) break;
+      float dot = 0.f;
+      for (int wi = 0; wi < nwarps; ++wi) dot += s_dot[buf][b][wi];
+      const float r = rstd[row];
+      const float cfac = dot * r * r * r / dim;
+      uint4* dxr = reinterpret_cast<uint4*>(dx) + row * groups_per_row;
+#pragma unroll
+      for (int j = 0; j < STEPS; ++j) {
+        const __nv_bfloat162* xb = reinterpret_cast<const __nv_bfloat162*>(&xv[b][j]);
+        const __nv_bfloat162* gb = reinterpret_cast<const __nv_bfloat162*>(&gv[b][j]);
+        uint4 out;
+        __nv_bfloat162* ob = reinterpret_cast<__nv_bfloat162*>(&out);
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          const float2 xf = __bfloat1622float2(xb[u]), gf = __bfloat1622float2(gb[u]);
+          ob[u] = __floats2bfloat162_rn(gf.x * wf[j][2 * u] * r - xf.x * cfac,
+                                        gf.y * wf[j][2 * u + 1] * r - xf.y * cfac);
+          dwacc[j][2 * u] += gf.x * xf.x * r;
+          dwacc[j][2 * u + 1] += gf.y * xf.y * r;
+        }
+        dxr[(j * nwarps + warp) * 32 + lane] = out;
+      }
+    }
+  }
+  float* out_row = dw_partial + static_cast<size_t>(blockIdx.x) * dim;
+#pragma unroll
+  for (int j = 0; j < STEPS; ++j) {
+    float4* o = reinterpret_cast<float4*>(out_row + ((j * nwarps + warp) * 32 + lane) * 8);
+    o[0] = make_float4(dwacc[j][0], dwacc[j][1], dwacc[j][2], dwacc[j][3]);
+    o[1] = make_float4(dwacc[j][4], dwacc[j][5], dwacc[j][6], dwacc[j][7]);
+  }
+}
+
+template <int STEPS, int RB>
+static void launch_rmsnorm_bwd_cols(int warps, const void* x, const void* w, const void* dy,
+                                    const float* rstd, void* dx, float* dw_partial, int n_partial,
+                                    long long rows, int dim, cudaStream_t stream) {
+  rmsnorm_bwd_cols_kernel<STEPS, RB><<<n_partial, dim3(32, warps), 0, stream>>>(
+      static_cast<const __nv_bfloat16*>(x), static_cast<const __nv_bfloat16*>(w),
+      static_cast<const __nv_bfloat16*>(dy), rstd, static_cast<__nv_bfloat16*>(dx), dw_partial,
+      rows, dim);
+}
+
 // ---------------------------------------------------------------------------------------------
 // T-Route select, mode "full": one warp per token
 // ---------------------------------------------------------------------------------------------
@@ -835,6 +1018,36 @@ extern "C" int tb200_rmsnorm_bwd(const void* x, const void* w, const void* dy, c
                                  void* dx, float* dw_partial, int n_partial, long long rows,
                                  int dim, int is_bf16, cudaStream_t stream) {
   if (rows == 0 || n_partial <= 0) return TB200_ERR_ARG;
+  // column-split kernel: 4 to 8 warps, each lane owning 1 to 4 groups of 8 columns
+  int cols_warps = 0;
+  if (is_bf16 && dim % 256 == 0)
+    for (int wn = 8; wn >= 4 && cols_warps == 0; --wn)
+      if (dim % (wn * 256) == 0 && dim / (wn * 256) <= 4) cols_warps = wn;
+  if (cols_warps != 0) {
+    const int warps = cols_warps;
+    switch (dim / (warps * 256)) {
+      case 1: launch_rmsnorm_bwd_cols<1, 4>(warps, x, w, dy, rstd, dx, dw_partial, n_partial, rows, dim, stream); break;
+      case 2: launch_rmsnorm_bwd_cols<2, 2>(warps, x, w, dy, rstd, dx, dw_partial, n_partial, rows, dim, stream); break;
+      case 3: launch_rmsnorm_bwd_cols<3, 2>(warps, x, w, dy, rstd, dx, dw_partial, n_partial, rows, dim, stream); break;
+      default: launch_rmsnorm_bwd_cols<4, 1>(warps, x, w, dy, rstd, dx, dw_partial, n_partial, rows, dim, stream); break;
+    }
+    return LAUNCH_OK();
+  }
+  if (is_bf16 && dim % 256 == 0 && dim <= 8192) {
+    // 4 warps per block keep the per-block accumulators small enough for several blocks per SM
+    const size_t smem_vec = 4 * static_cast<size_t>(dim) * sizeof(float);
+    static OncePerDevice configured;
+    if (configured.need()) {
+      cudaFuncSetAttribute(rmsnorm_bwd_vec_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                           4 * 8192 * static_cast<int>(sizeof(float)));
+      configured.done();
+    }
+    rmsnorm_bwd_vec_kernel<<<n_partial, dim3(32, 4), smem_vec, stream>>>(
+        static_cast<const __nv_bfloat16*>(x), static_cast<const __nv_bfloat16*>(w),
+        static_cast<const __nv_bfloat16*>(dy), rstd, static_cast<__nv_bfloat16*>(dx), dw_partial,
+        rows, dim);
+    return LAUNCH_OK();
+  }
   int warps = 8;
   while (warps > 1 && static_cast<size_t>(warps) * dim * sizeof(float) > 160 * 1024) warps >>= 1;
   const size_t smem = static_cast<size_t>(warps) * dim * sizeof(float);

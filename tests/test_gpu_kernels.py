@@ -24,11 +24,19 @@ def test_passthrough_bitwise(native_ops):
     assert native_ops.OP_CALLS.get("passthrough", 0) > 0
 
 
+# widths that reach each backward kernel: generic (96), 16-byte loads (512), and the column-split
+# kernel with 4..8 warps and 1..4 column groups per lane; row counts that leave ragged row batches
+RMSNORM_SHAPES = [((37, 5), 512), ((37, 5), 96), ((3001,), 1024), ((3001,), 4096), ((1201,), 1536),
+                  ((700,), 7168), ((1000,), 6144), ((611,), 2048), ((300,), 8192), ((500,), 5120)]
+
+
+@pytest.mark.parametrize("shape", RMSNORM_SHAPES)
 @pytest.mark.parametrize("dt", [torch.float32, torch.bfloat16])
-def test_rmsnorm_fwd_bwd(native_ops, dt):
+def test_rmsnorm_fwd_bwd(native_ops, dt, shape):
     torch.manual_seed(0)
-    x = torch.randn(37, 5, 512, device=DEV).to(dt).requires_grad_(True)
-    w = (1 + 0.1 * torch.randn(512, device=DEV)).to(dt).requires_grad_(True)
+    lead, dim = shape
+    x = torch.randn(*lead, dim, device=DEV).to(dt).requires_grad_(True)
+    w = (1 + 0.1 * torch.randn(dim, device=DEV)).to(dt).requires_grad_(True)
     y = native_ops.rmsnorm(x, w, 1e-5)
     gy = torch.randn_like(y)
     y.backward(gy)
@@ -39,7 +47,8 @@ def test_rmsnorm_fwd_bwd(native_ops, dt):
     tol = 1e-5 if dt == torch.float32 else 2e-2
     torch.testing.assert_close(y.float(), yr, rtol=tol, atol=tol)
     torch.testing.assert_close(x.grad.float(), xr.grad, rtol=tol, atol=tol)
-    torch.testing.assert_close(w.grad.float(), wr.grad, rtol=tol, atol=tol * 10)
+    # the weight gradient sums over all rows: its rounding grows with the row count
+    torch.testing.assert_close(w.grad.float(), wr.grad, rtol=tol, atol=tol * 10 * max(1.0, (x.numel() / dim / 185) ** 0.5))
 
 
 K1_GEOMS = [(16, 2, 2, 8, 64), (64, 1, 2, 8, 32), (33, 3, 2, 4, 48), (128, 4, 4, 8, 16),

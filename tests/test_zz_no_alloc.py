@@ -6,8 +6,8 @@ Some users of the library cannot allocate device memory when they need a permuta
 the shared object with ctypes, calls the symbol twice in a row with different routings (the
 second call meets the first call's leftovers in the shared scratch) and checks every output
 against the regular entry point, which must agree exactly: the plan is integer bookkeeping plus
-a permutation of the gates.  The file sorts last so that a stop-at-first-failure run has already
-executed every other test.
+a permutation of the gates.  A third case sits exactly on the documented limits of the built-in
+scratch (T * k = 262144 pairs, 1024 experts).
 """
 import ctypes
 
@@ -50,6 +50,27 @@ def test_static_plan_matches_regular_entry_point(native_ops):
         torch.cuda.synchronize()
         for name, a, b in zip(("es", "gs", "cols", "pos", "seg_start", "seg_count"), got, want):
             assert torch.equal(a, b), name
+
+
+def test_static_plan_at_the_scratch_limits(native_ops):
+    """T * k = 262144 and E = 1024 use the fixed array to its last word."""
+    lib = ctypes.CDLL(native_ops.status().lib)
+    lib.tb200_moe_plan_static.restype = ctypes.c_int
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    T, k, E = 32768, 8, 1024
+    g = torch.Generator().manual_seed(9)
+    # k distinct experts per token: a random start and a random odd stride around the ring
+    start = torch.randint(0, E, (T, 1), generator=g)
+    stride = 2 * torch.randint(0, E // 2, (T, 1), generator=g) + 1
+    idx = ((start + stride * torch.arange(k)) % E).to(dev)
+    gates = torch.rand(T, k, generator=g).to(dev)
+    rc, got = _call_static(lib, idx, gates, E, 64)
+    assert rc == 0
+    want = torch.ops.terrace.moe_plan(idx, gates, E, 64)
+    torch.cuda.synchronize()
+    for name, a, b in zip(("es", "gs", "cols", "pos", "seg_start", "seg_count"), got, want):
+        assert torch.equal(a, b), name
 
 
 def test_static_plan_rejects_oversize(native_ops):
