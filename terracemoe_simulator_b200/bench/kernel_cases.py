@@ -19,7 +19,8 @@ import torch
 
 CASES = ("gemm_fwd", "gemm_swiglu", "gemm_dgrad", "gemm_wgrad", "gemm_scatter", "rmsnorm",
          "rmsnorm_bwd", "route", "route_fused", "scatter", "combine", "combine_bwd", "swiglu_bwd",
-         "attn_fwd", "attn_bwd", "ep_layer")
+         "attn_fwd", "attn_bwd", "ep_layer",
+         "k1_arrival", "k2_pack", "rope_split", "rope_merge", "route_bwd", "passthrough")
 
 
 def _peaks():
@@ -169,6 +170,52 @@ def main(argv=None) -> int:
             y = fz.fused_moe_forward(ctx, x, idx, gates, w13, w2, mode="one_hop")
             y.backward(gy)
         flops = 3 * 2 * 3 * T * cfg.top_k * H * d
+    elif args.case == "passthrough":
+        x = torch.randn(rows, H, device=dev, dtype=bf)
+        fn = lambda: lib.passthrough(x)
+        bytes_ = 2 * x.numel() * 2
+    elif args.case in ("rope_split", "rope_merge"):
+        # [B, S, 3 * heads * 128] projection output <-> three [B, heads, S, 128] tensors
+        B_, S_, nh, hd = (8, 4096, 16, 128) if args.full else (2, 4096, 16, 128)
+        qkv = torch.randn(B_, S_, 3 * nh * hd, device=dev, dtype=bf)
+        ang = torch.outer(torch.arange(S_, device=dev, dtype=torch.float32),
+                          10000.0 ** (-torch.arange(0, hd, 2, device=dev, dtype=torch.float32) / hd))
+        cos, sin = ang.cos().contiguous(), ang.sin().contiguous()
+        if args.case == "rope_split":
+            fn = lambda: lib.rope_split(qkv, cos, sin, nh)
+        else:
+            q_, k__, v_ = lib.rope_split(qkv, cos, sin, nh)
+            fn = lambda: lib.rope_merge(q_, k__, v_, cos, sin)
+        bytes_ = 2 * qkv.numel() * 2
+    elif args.case == "route_bwd":
+        Tr = T * 8
+        logits = torch.randn(Tr, 64, device=dev)
+        idx_, gates_, _, _, aff = lib.route_select(logits, torch.zeros(64, device=dev), 4, 6, 2, 2)
+        dg = torch.randn_like(gates_)
+        fn = lambda: lib.route_select_bwd(dg, gates_, aff, idx_, 64)
+        bytes_ = Tr * 64 * 4 + 4 * Tr * 6 * 4
+    elif args.case == "k2_pack":
+        # the contract op of the send side: 8 ranks in groups of 2, 64 experts, k = 6, M = 2
+        world_, rpn_, M_, q_ = 8, 2, 2, 3
+        per = 64 // (world_ // rpn_)
+        g = torch.Generator().manual_seed(3)
+        grp = torch.stack([torch.randperm(world_ // rpn_, generator=g)[:M_] for _ in range(T)])
+        pick = torch.stack([torch.cat([gr * per + torch.randperm(per, generator=g)[:q_]
+                                       for gr in row]) for row in grp]).to(dev)
+        x = torch.randn(T, H, device=dev, dtype=bf)
+        gates_ = torch.rand(T, M_ * q_, device=dev, dtype=bf)
+        fn = lambda: lib.k2_pack(x, pick, gates_, world_, 64, rpn_, M_)
+        bytes_ = (T + T * M_) * H * 2
+    elif args.case == "k1_arrival":
+        # the contract op of the arrival side: R rows, each feeding q of this group's 16 experts
+        R_, q_, epr_, rpn_ = T * 2, 3, 8, 2
+        g = torch.Generator().manual_seed(4)
+        rslot = torch.stack([torch.randperm(epr_ * rpn_, generator=g)[:q_].sort().values
+                             for _ in range(R_)]).to(dev)
+        rx = torch.randn(R_, H, device=dev, dtype=bf)
+        rgate = torch.rand(R_, q_, device=dev, dtype=bf)
+        fn = lambda: lib.k1_arrival(rx, rslot, rgate, q_, epr_, rpn_, 0)
+        bytes_ = (R_ + R_ * q_) * H * 2
     elif args.case == "route":
         logits = torch.randn(T * 8, 64, device=dev)
         bias = torch.zeros(64, device=dev)

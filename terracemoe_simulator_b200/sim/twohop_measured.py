@@ -9,6 +9,8 @@ repository's own measurements is ``sim/validate_b200.py``.
 """
 from __future__ import annotations
 
+from typing import NamedTuple
+
 from .records import TWOHOP_MEASURED as MEASURED
 
 TOKENS, K, N_GROUPS, CARDS_PER_GROUP = 4096, 6, 2, 64
@@ -19,36 +21,59 @@ MODEL_ERROR = {"slow level fed a mixture": 0.140, "slow level as a pure tier": 0
 PURE_CROSS_BOUNDARY_GBPS = 7.9
 
 
+class Run(NamedTuple):
+    """One measured configuration: the one-hop call and the four parts of the two-hop call, ms."""
+    H: int
+    M: int
+    q: int
+    one_hop: float
+    hop_a: float
+    chain: float
+    hop_b: float
+    splits: float
+
+    @property
+    def two_hop(self) -> float:
+        return sum(self[4:])
+
+    @property
+    def gain(self) -> float:
+        return self.one_hop / self.two_hop
+
+
 def two_hop_ms(row) -> float:
-    return row[4] + row[5] + row[6] + row[7]
+    return Run(*row).two_hop
 
 
 def g(row) -> float:
-    return row[3] / two_hop_ms(row)
-
-
-def every_configuration_wins() -> bool:
-    return all(g(r) > 1.0 for r in MEASURED)
+    return Run(*row).gain
 
 
 def chain_share(row) -> float:
-    return row[5] / two_hop_ms(row)
+    run = Run(*row)
+    return run.chain / run.two_hop
+
+
+def every_configuration_wins() -> bool:
+    return min(map(g, MEASURED)) > 1.0
 
 
 def main() -> None:
+    from ._text import Column, render_table
+    runs = [Run(*row) for row in MEASURED]
     print("One hop against two, measured across the %s supernode boundary." % BOUNDARY)
-    print("128 ranks, 8 nodes in each supernode, T = %d tokens per rank, k = %d." % (TOKENS, K))
-    print()
-    print("%-6s %-4s %-4s %9s %8s %8s %8s %8s %9s %7s" % ("H", "M", "q", "one hop", "hop A",
-                                                          "chain", "hop B", "splits", "two hop",
-                                                          "G"))
-    for r in MEASURED:
-        print("%-6d %-4d %-4d %9.3f %8.3f %8.3f %8.3f %8.3f %9.3f %7.3f %s"
-              % (r + (two_hop_ms(r), g(r), "WIN" if g(r) > 1 else "loss")))
-    gs = [g(r) for r in MEASURED]
-    print()
-    print("Two-hop wins in %d of %d configurations, by %.2fx to %.2fx."
-          % (sum(x > 1 for x in gs), len(gs), min(gs), max(gs)))
+    print("128 ranks, 8 nodes in each supernode, T = %d tokens per rank, k = %d.\n" % (TOKENS, K))
+    cols = [Column(name, "%-" + str(width) + "d", lambda r, i=i: r[i])
+            for i, (name, width) in enumerate((("H", 6), ("M", 4), ("q", 4)))]
+    cols += [Column(name, fmt, lambda r, i=i: r[i]) for i, name, fmt in
+             ((3, "one hop", "%9.3f"), (4, "hop A", "%8.3f"), (5, "chain", "%8.3f"),
+              (6, "hop B", "%8.3f"), (7, "splits", "%8.3f"))]
+    cols += [Column("two hop", "%9.3f", lambda r: r.two_hop), Column("G", "%7.3f", lambda r: r.gain),
+             Column("", "%-4s", lambda r: "WIN" if r.gain > 1.0 else "loss")]
+    print("\n".join(render_table(cols, runs)))
+    gains = sorted(r.gain for r in runs)
+    print("\nTwo-hop wins in %d of %d configurations, by %.2fx to %.2fx."
+          % (sum(x > 1.0 for x in gains), len(gains), gains[0], gains[-1]))
     print("Model error on G: %.0f%% median with the slow level fed a mixture, %.0f%% as a pure "
           "%.1f GB/s tier." % (100 * MODEL_ERROR["slow level fed a mixture"],
                               100 * MODEL_ERROR["slow level as a pure tier"],

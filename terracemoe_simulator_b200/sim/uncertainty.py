@@ -12,7 +12,9 @@ Parity with the reference ``sim/uncertainty.py`` (``PERTURB`` :39-51, ``mc_band`
 """
 from __future__ import annotations
 
+import itertools
 import random
+from typing import NamedTuple
 
 from .calibrate import ALPHA_PTS, X_HALF_FLAT, synthetic
 from .core import MoEGeometry, one_hop_call, two_hop_call
@@ -32,73 +34,90 @@ BISECT_STEPS = 40
 RATIO_LO, RATIO_HI = 1.0, 32.0
 
 
-def _k_m(q: int, k_base: int = 6):
-    k = k_base if k_base % q == 0 and k_base >= q else q
-    return k, max(k // q, 1)
+class Shape(NamedTuple):
+    """The routing geometry a speedup is quoted on; ``H = None`` keeps the model's default."""
+    n_groups: int = 16
+    R: int = 8
+    k: int = 6
+    M: int = 2
+    tok: int = 4096
+    H: int | None = None
+
+    @classmethod
+    def for_quota(cls, q: int, tok: int, R: int, k_base: int = 6) -> "Shape":
+        """k stays at ``k_base`` when the quota divides it, else one group of q picks."""
+        k = k_base if k_base >= q and k_base % q == 0 else q
+        return cls(R=R, k=k, M=max(1, k // q), tok=tok)
+
+    def speedup(self, cluster) -> float:
+        """one-hop time / two-hop time of one dispatch on ``cluster`` (> 1: two-hop is faster)."""
+        extra = {} if self.H is None else {"H": self.H}
+        geom = MoEGeometry(name="u", n_groups=self.n_groups, R=self.R, k=self.k, M=self.M,
+                           seq=self.tok, mbs=1, gbs=self.n_groups * self.R * self.tok, **extra)
+        return one_hop_call(cluster, geom) / two_hop_call(cluster, geom)
 
 
 def _speedup(cluster, q: int, tok: int, k_base: int = 6) -> float:
-    k, m = _k_m(q, k_base)
-    g = MoEGeometry(name="mc", n_groups=16, R=cluster.R, k=k, M=m, seq=tok, mbs=1,
-                    gbs=16 * cluster.R * tok)
-    return one_hop_call(cluster, g) / two_hop_call(cluster, g)
+    return Shape.for_quota(q, tok, cluster.R, k_base).speedup(cluster)
 
 
 def _bisect(speedup_of_ratio, lo: float = RATIO_LO, hi: float = RATIO_HI) -> float:
     """Smallest ratio in [lo, hi] at which ``speedup_of_ratio`` reaches 1 (clamped to the ends)."""
-    if speedup_of_ratio(lo) >= 1.0:
+    if not speedup_of_ratio(lo) < 1.0:
         return lo
     if speedup_of_ratio(hi) < 1.0:
         return hi
+    below, reached = lo, hi
     for _ in range(BISECT_STEPS):
-        mid = (lo + hi) / 2.0
-        if speedup_of_ratio(mid) >= 1.0:
-            hi = mid
+        probe = 0.5 * (below + reached)
+        if speedup_of_ratio(probe) < 1.0:
+            below = probe
         else:
-            lo = mid
-    return hi
+            reached = probe
+    return reached
+
+
+def _crossing(shape: Shape, chain: float, lo: float = RATIO_LO, hi: float = RATIO_HI) -> float:
+    """Break-even hierarchy ratio of ``shape`` on the synthetic cluster family."""
+    return _bisect(lambda ratio: shape.speedup(synthetic(ratio, R=shape.R, chain_us_per_row=chain)),
+                   lo, hi)
 
 
 def _perturbed(ratio: float, chain: float, f: dict):
-    c = synthetic(ratio, chain_us_per_row=chain * f["chain"], x_half=X_HALF_FLAT * f["x_half"])
-    for level, bf in ((c.fast, f["beta_fast"]), (c.slow, f["beta_slow"]), (c.flat, f["beta_slow"])):
-        level.alpha_pts = [(w, a * f["alpha"]) for w, a in level.alpha_pts]
-        level.beta_pts = [(x, b * bf) for x, b in level.beta_pts]
-    c.splits_sync_ms *= f["splits"]
-    return c
+    """The synthetic cluster with every constant scaled by its draw."""
+    cluster = synthetic(ratio, chain_us_per_row=f["chain"] * chain, x_half=f["x_half"] * X_HALF_FLAT)
+    scale_beta = {"fast": f["beta_fast"], "slow": f["beta_slow"], "flat": f["beta_slow"]}
+    for which, factor in scale_beta.items():
+        level = getattr(cluster, which)
+        level.alpha_pts = [(world, f["alpha"] * ms) for world, ms in level.alpha_pts]
+        level.beta_pts = [(size, factor * gbps) for size, gbps in level.beta_pts]
+    cluster.splits_sync_ms = f["splits"] * cluster.splits_sync_ms
+    return cluster
 
 
 def mc_band(ratio: float, chain: float, q: int = 3, tok: int = 4096, n: int = N_DRAWS,
             seed: int = SEED):
-    """(p5, median, p95) of the speedup under the ``PERTURB`` draws; reproducible by seed."""
+    """(p5, median, p95) of the speedup under the ``PERTURB`` draws; reproducible by seed (the
+    factors are drawn in table order, one set per sample)."""
     rng = random.Random(seed)
-    vals = []
-    for _ in range(n):
-        f = {name: rng.uniform(lo, hi) for name, lo, hi, _ in PERTURB}
-        vals.append(_speedup(_perturbed(ratio, chain, f), q, tok))
-    vals.sort()
-    return vals[int(0.05 * n)], vals[n // 2], vals[int(0.95 * n)]
+    draws = ({name: rng.uniform(low, high) for name, low, high, _ in PERTURB} for _ in range(n))
+    ranked = sorted(_speedup(_perturbed(ratio, chain, f), q, tok) for f in draws)
+    return tuple(ranked[i] for i in (int(0.05 * n), n // 2, int(0.95 * n)))
 
 
 def breakeven_ratio(chain: float, q: int = 3, tok: int = 4096, lo: float = RATIO_LO,
                     hi: float = RATIO_HI) -> float:
-    return _bisect(lambda r: _speedup(synthetic(r, chain_us_per_row=chain), q, tok), lo, hi)
+    return _crossing(Shape.for_quota(q, tok, R=8), chain, lo, hi)
 
 
 def breakeven_vs_hidden_width(widths=None, k: int = 6, M: int = 2, tok: int = 4096,
                               n_groups: int = 16, R: int = 8):
+    """``[(H, break-even ratio)]`` with the arrival chain priced at its measured cost for that
+    width (only measured widths are accepted)."""
     from .machine import CHAIN_H_SWEEP_MS, chain_us_per_row_at
-    out = []
-    for H in (sorted(CHAIN_H_SWEEP_MS) if widths is None else list(widths)):
-        chain = chain_us_per_row_at(H)
-
-        def s(r, H=H, chain=chain):
-            c = synthetic(r, chain_us_per_row=chain)
-            g = MoEGeometry(name="H%d" % H, n_groups=n_groups, R=R, k=k, M=M, H=H, seq=tok,
-                            mbs=1, gbs=n_groups * R * tok)
-            return one_hop_call(c, g) / two_hop_call(c, g)
-        out.append((H, _bisect(s)))
-    return out
+    chosen = sorted(CHAIN_H_SWEEP_MS) if widths is None else list(widths)
+    return [(H, _crossing(Shape(n_groups, R, k, M, tok, H), chain_us_per_row_at(H)))
+            for H in chosen]
 
 
 # ---- scale axis: what alpha does past the largest measured world ---------------------------------
@@ -115,88 +134,91 @@ EXTRAP_WORLDS = (128, 256, 512)
 
 def scale_ratio(w: int, alpha_pts=None, ratio: float = SCALE_HIERARCHY_RATIO,
                 chain: float | None = None) -> float:
+    """Speedup at world size ``w`` (groups of 8) with the fixed-cost table replaced by
+    ``alpha_pts`` on every level."""
     if chain is None:
         from .sweep import CHAIN_SCENARIOS
         chain = CHAIN_SCENARIOS[1][1]
-    c = synthetic(ratio, chain_us_per_row=chain)
-    pts = sorted(dict(ALPHA_PTS).items()) if alpha_pts is None else alpha_pts
-    for level in (c.fast, c.slow, c.flat):
-        level.alpha_pts = pts
-    g = MoEGeometry(name="scale", n_groups=w // 8, R=8, k=6, M=2, seq=4096, mbs=1, gbs=w * 4096)
-    return one_hop_call(c, g) / two_hop_call(c, g)
+    cluster = synthetic(ratio, chain_us_per_row=chain)
+    table = alpha_pts if alpha_pts is not None else sorted(dict(ALPHA_PTS).items())
+    for which in ("fast", "slow", "flat"):
+        getattr(cluster, which).alpha_pts = table
+    return Shape(n_groups=w // 8).speedup(cluster)
 
 
 def scale_treatment_curves(worlds=EXTRAP_WORLDS) -> dict:
-    base = dict(ALPHA_PTS)
-    return {label: [scale_ratio(w, sorted({**base, **override}.items())) for w in worlds]
-            for label, override in ALPHA_TREATMENTS.items()}
+    measured = dict(ALPHA_PTS)
+    curves = {}
+    for label, beyond in ALPHA_TREATMENTS.items():
+        table = sorted((measured | beyond).items())
+        curves[label] = [scale_ratio(w, table) for w in worlds]
+    return curves
 
 
 def scale_band(w: int = 512) -> tuple:
-    i = list(EXTRAP_WORLDS).index(w)
-    vals = [curve[i] for curve in scale_treatment_curves().values()]
-    return min(vals), max(vals)
+    column = EXTRAP_WORLDS.index(w)
+    at_w = [curve[column] for curve in scale_treatment_curves().values()]
+    return min(at_w), max(at_w)
 
 
 def heatmap(chain: float, q: int = 3, ratios=(1.03, 1.5, 2, 3, 4.5, 6, 8, 11, 16),
             toks=(512, 1024, 2048, 4096, 8192, 16384)):
-    grid = [[_speedup(synthetic(r, chain_us_per_row=chain), q, t) for r in ratios] for t in toks]
-    return grid, list(ratios), list(toks)
+    clusters = [synthetic(r, chain_us_per_row=chain) for r in ratios]
+    return [[_speedup(c, q, t) for c in clusters] for t in toks], list(ratios), list(toks)
+
+
+GRID_GROUPS, GRID_SIZES = (8, 16, 32), (4, 8, 16)
+GRID_ROUTINGS = ((4, 1), (4, 2), (6, 2), (6, 3), (8, 2), (8, 4))
 
 
 def geometry_grid(chain: float, tok: int = 4096):
     """Breakeven ratio over 3 group counts x 3 group sizes x 6 (k, M) pairs -> 54 rows
     ``(n_groups, R, k, M, breakeven)``."""
-    rows = []
-    for ng in (8, 16, 32):
-        for R in (4, 8, 16):
-            for k, m in ((4, 1), (4, 2), (6, 2), (6, 3), (8, 2), (8, 4)):
-                if m > ng:
-                    continue
-
-                def s(r, ng=ng, R=R, k=k, m=m):
-                    c = synthetic(r, R=R, chain_us_per_row=chain)
-                    g = MoEGeometry(name="grid", n_groups=ng, R=R, k=k, M=m, seq=tok, mbs=1,
-                                    gbs=ng * R * tok)
-                    return one_hop_call(c, g) / two_hop_call(c, g)
-                rows.append((ng, R, k, m, _bisect(s)))
-    return rows
+    cells = itertools.product(GRID_GROUPS, GRID_SIZES, GRID_ROUTINGS)
+    return [(ng, R, k, M, _crossing(Shape(ng, R, k, M, tok), chain))
+            for ng, R, (k, M) in cells if M <= ng]
 
 
 def geometry_breakeven_spread(chain: float) -> float:
-    rows = geometry_grid(chain)
-    worst = 0.0
-    for ng in (8, 16, 32):
-        for R in (4, 8, 16):
-            cell = [be for a, b, _k, _m, be in rows if a == ng and b == R]
-            if cell:
-                worst = max(worst, max(cell) - min(cell))
-    return worst
+    """Largest spread of the break-even over the routings of one (groups, size) cell."""
+    by_cell: dict = {}
+    for ng, R, _k, _m, be in geometry_grid(chain):
+        by_cell.setdefault((ng, R), []).append(be)
+    return max((max(v) - min(v) for v in by_cell.values()), default=0.0)
+
+
+BAND_RATIOS = (1.03, 2.0, 3.2, 4.5, 8.0, 15.7)
+
+
+def _anchor(label: str, value: float, holds: bool, if_holds: str, otherwise: str) -> str:
+    return "  %s = %.2f -> %s" % (label, value, if_holds if holds else otherwise)
 
 
 def main() -> None:
+    from ._text import Column, render_table
     from .sweep import CHAIN_SCENARIOS
+    tiers = dict(CHAIN_SCENARIOS)
     print("Monte Carlo uncertainty bands (%d draws, seed %d)" % (N_DRAWS, SEED))
     print("Geometry: 16 groups x 8, k=6/M=2 (q=3), T=4096; value = one-hop/two-hop "
           "(>1 = two-hop faster)")
-    for name, chain in CHAIN_SCENARIOS:
-        print("\n-- %s --" % name)
-        print("%-10s %10s %18s" % ("ratio", "median", "[p5, p95]"))
-        for r in (1.03, 2.0, 3.2, 4.5, 8.0, 15.7):
-            p5, med, p95 = mc_band(r, chain)
-            print("%-10.2f %10.2f       [%.2f, %.2f]" % (r, med, p5, p95))
+    cols = [Column("ratio", "%-10.2f", lambda row: row[0]), Column("median", "%10.2f", lambda row: row[1][1]),
+            Column("[p5, p95]", "%18s", lambda row: "[%.2f, %.2f]" % (row[1][0], row[1][2]))]
+    for tier, chain in tiers.items():
+        print("\n-- %s --" % tier)
+        print("\n".join(render_table(cols, [(r, mc_band(r, chain)) for r in BAND_RATIOS])))
     print("\nBreakeven hierarchy ratio (smallest ratio with speedup 1, q=3, T=4096):")
-    for name, chain in CHAIN_SCENARIOS:
-        print("  %-24s %.2f" % (name, breakeven_ratio(chain)))
+    for tier, chain in tiers.items():
+        print("  %-24s %.2f" % (tier, breakeven_ratio(chain)))
+    names = list(tiers)
+    flat_p95 = mc_band(1.03, tiers[names[2]])[2]
+    steep_p5 = mc_band(8.0, tiers[names[0]])[0]
     print("\nTwo robustness anchors:")
-    _, _, p95 = mc_band(1.03, CHAIN_SCENARIOS[2][1])
-    print("  flat column, zero implementation overhead: p95 = %.2f -> %s"
-          % (p95, "<=1, the negative verdict is robust to calibration error" if p95 <= 1.0
-             else "crosses the line -- tighten the written conclusion"))
-    p5, _, _ = mc_band(8.0, CHAIN_SCENARIOS[0][1])
-    print("  8x column, PyTorch chain: p5 = %.2f -> %s"
-          % (p5, "still >1, the direction conclusion is robust" if p5 > 1.0
-             else "<1: the 8x win depends on the implementation tier"))
+    print(_anchor("flat column, zero implementation overhead: p95", flat_p95, flat_p95 <= 1.0,
+                  "<=1, the negative verdict is robust to calibration error",
+                  "crosses the line -- tighten the written conclusion"))
+    print(_anchor("8x column, PyTorch chain: p5", steep_p5, steep_p5 > 1.0,
+                  "still >1, the direction conclusion is robust",
+                  "<1: the 8x win depends on the implementation tier"))
 
 
 if __name__ == "__main__":
