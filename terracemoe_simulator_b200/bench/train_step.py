@@ -193,6 +193,13 @@ def main(argv=None) -> int:
                       "ep_mode": ns.ep if world > 1 else "local", "rpn": ns.rpn,
                       "transport": "nccl" if ns.nccl else "fused", "optimizer": "AdamW",
                       "h2d_bytes_per_step": ns.batch * (ns.seq + 1) * 8, "d2h_bytes_per_step": 4}}
+    if cuda:
+        # device memory of this rank: the caching allocator's peak, and what lives outside it
+        # (the peer-memory arenas of the fused transport, one per MoE layer)
+        free_b, total_b = torch.cuda.mem_get_info(device)
+        out["memory_gib"] = {"torch_peak": round(torch.cuda.max_memory_allocated(device) / 2 ** 30, 2),
+                             "torch_reserved": round(torch.cuda.memory_reserved(device) / 2 ** 30, 2),
+                             "device_in_use": round((total_b - free_b) / 2 ** 30, 2)}
     if rank == 0:
         print(json.dumps(out), flush=True)
     if world > 1:

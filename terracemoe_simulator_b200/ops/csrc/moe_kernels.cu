@@ -488,12 +488,16 @@ __global__ void plan_pass1_kernel(const long long* __restrict__ expert_idx,
                                   float* __restrict__ gs, int* __restrict__ cols,
                                   int* __restrict__ rank_local, int* __restrict__ chunk_hist, int T,
                                   int k, int E) {
-  extern __shared__ int s_cnt[];        // [E]
+  extern __shared__ int s_cnt[];        // [E] picks so far, then [E] lane masks of the group
+  unsigned* s_mask = reinterpret_cast<unsigned*>(s_cnt + E);
   const int chunk = blockIdx.x;
   const int per = (T + PLAN_CHUNKS - 1) / PLAN_CHUNKS;
   const int t0 = chunk * per, t1 = min(T, t0 + per);
   const int lane = threadIdx.x;
-  for (int e = lane; e < E; e += 32) s_cnt[e] = 0;
+  for (int e = lane; e < E; e += 32) {
+    s_cnt[e] = 0;
+    s_mask[e] = 0u;
+  }
   __syncwarp();
   for (int tb = t0; tb < t1; tb += 32) {
     const int t = tb + lane;
@@ -523,19 +527,50 @@ __global__ void plan_pass1_kernel(const long long* __restrict__ expert_idx,
         cols[static_cast<size_t>(t) * k + j] = c_loc[j];
       }
     }
-    // ranks: tokens in lane order, picks in ascending order -> (token, expert) stable order
-    for (int j = 0; j < k; ++j) {
-      const int e = live ? e_loc[j] : -1 - lane;            // dead lanes match nobody
-      const unsigned peers = __match_any_sync(0xffffffffu, e);
-      if (live && e >= 0 && e < E) {
-        const int before = __popc(peers & ((1u << lane) - 1u));
-        rank_local[static_cast<size_t>(t) * k + j] = s_cnt[e] + before;
-      } else if (live) {
-        rank_local[static_cast<size_t>(t) * k + j] = -1;     // out-of-range id: skipped later
+    // Rank of every pick inside its expert, in TOKEN order (the canonical order the capacity
+    // rule and the host model use).  Routing gives a token distinct experts, so "lower lanes that
+    // picked e" is a bit count over a per-expert lane mask.  A group that holds a token with a
+    // repeated expert (not a top-k routing) falls back to column-major ranking, which still
+    // gives every pick a distinct in-range rank.
+    bool dup = false;
+    if (live)
+      for (int j = 1; j < k; ++j) dup |= e_loc[j] == e_loc[j - 1];
+    if (!__any_sync(0xffffffffu, dup)) {
+      if (live)
+        for (int j = 0; j < k; ++j)
+          if (e_loc[j] >= 0 && e_loc[j] < E) atomicOr(&s_mask[e_loc[j]], 1u << lane);
+      __syncwarp();
+      if (live)
+        for (int j = 0; j < k; ++j) {
+          const int e = e_loc[j];
+          rank_local[static_cast<size_t>(t) * k + j] =
+              (e >= 0 && e < E) ? s_cnt[e] + __popc(s_mask[e] & ((1u << lane) - 1u)) : -1;
+        }
+      __syncwarp();
+      if (live)
+        for (int j = 0; j < k; ++j) {
+          const int e = e_loc[j];
+          if (e >= 0 && e < E && (s_mask[e] >> lane) == 1u) s_cnt[e] += __popc(s_mask[e]);
+        }
+      __syncwarp();
+      if (live)
+        for (int j = 0; j < k; ++j)
+          if (e_loc[j] >= 0 && e_loc[j] < E) s_mask[e_loc[j]] = 0u;
+      __syncwarp();
+    } else {
+      for (int j = 0; j < k; ++j) {
+        const int e = live ? e_loc[j] : -1 - lane;            // dead lanes match nobody
+        const unsigned peers = __match_any_sync(0xffffffffu, e);
+        if (live && e >= 0 && e < E) {
+          const int before = __popc(peers & ((1u << lane) - 1u));
+          rank_local[static_cast<size_t>(t) * k + j] = s_cnt[e] + before;
+        } else if (live) {
+          rank_local[static_cast<size_t>(t) * k + j] = -1;     // out-of-range id: skipped later
+        }
+        __syncwarp();
+        if (live && e >= 0 && e < E && (peers >> lane) == 1u) s_cnt[e] += __popc(peers);
+        __syncwarp();
       }
-      __syncwarp();
-      if (live && e >= 0 && e < E && (peers >> lane) == 1u) s_cnt[e] += __popc(peers);
-      __syncwarp();
     }
   }
   for (int e = lane; e < E; e += 32) chunk_hist[static_cast<size_t>(chunk) * E + e] = s_cnt[e];
@@ -1099,12 +1134,26 @@ extern "C" size_t tb200_plan_scratch_ints(int T, int k, int E) {
   return static_cast<size_t>(T) * k + static_cast<size_t>(PLAN_CHUNKS) * E;
 }
 
+// One warp per token chunk; shared memory: [E] counters + [E] lane masks (64 KiB at E = 8192, which
+// needs the opt-in limit).
+static void launch_plan_pass1(const long long* expert_idx, const float* gates, int* es, float* gs,
+                              int* cols, int* rank_local, int* chunk_hist, int T, int k, int E,
+                              cudaStream_t stream) {
+  static OncePerDevice configured;
+  if (configured.need()) {
+    cudaFuncSetAttribute(plan_pass1_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                         2 * 8192 * static_cast<int>(sizeof(int)));
+    configured.done();
+  }
+  plan_pass1_kernel<<<PLAN_CHUNKS, 32, 2 * E * sizeof(int), stream>>>(expert_idx, gates, es, gs, cols,
+                                                                    rank_local, chunk_hist, T, k, E);
+}
+
 extern "C" int tb200_plan_pass1(const long long* expert_idx, const float* gates, int* es,
                                 float* gs, int* cols, int* rank_local, int* chunk_hist, int T,
                                 int k, int E, cudaStream_t stream) {
   if (k > PLAN_MAX_K || E > 8192) return TB200_ERR_SIZE;
-  plan_pass1_kernel<<<PLAN_CHUNKS, 32, E * sizeof(int), stream>>>(expert_idx, gates, es, gs, cols,
-                                                                rank_local, chunk_hist, T, k, E);
+  launch_plan_pass1(expert_idx, gates, es, gs, cols, rank_local, chunk_hist, T, k, E, stream);
   return LAUNCH_OK();
 }
 
@@ -1114,8 +1163,7 @@ extern "C" int tb200_moe_plan(const long long* expert_idx, const float* gates, i
   if (k > PLAN_MAX_K || E > 8192 || seg_align < 1) return TB200_ERR_SIZE;
   int* rank_local = scratch;
   int* chunk_hist = scratch + static_cast<size_t>(T) * k;
-  plan_pass1_kernel<<<PLAN_CHUNKS, 32, E * sizeof(int), stream>>>(expert_idx, gates, es, gs, cols,
-                                                                rank_local, chunk_hist, T, k, E);
+  launch_plan_pass1(expert_idx, gates, es, gs, cols, rank_local, chunk_hist, T, k, E, stream);
   plan_pass2_kernel<<<1, 256, E * sizeof(int), stream>>>(chunk_hist, seg_start, seg_count, E,
                                                          seg_align);
   if (T * k > 0)
@@ -1308,8 +1356,7 @@ extern "C" int tb200_moe_plan_static(const long long* expert_idx, const float* g
   // every word pass 2 and pass 3 read, so stale contents of an earlier call are harmless
   int* rank_local = scratch;
   int* chunk_hist = scratch + static_cast<size_t>(T) * k;
-  plan_pass1_kernel<<<PLAN_CHUNKS, 32, E * sizeof(int), stream>>>(expert_idx, gates, es, gs, cols,
-                                                                rank_local, chunk_hist, T, k, E);
+  launch_plan_pass1(expert_idx, gates, es, gs, cols, rank_local, chunk_hist, T, k, E, stream);
   plan_pass2_kernel<<<1, 256, E * sizeof(int), stream>>>(chunk_hist, seg_start, seg_count, E,
                                                          seg_align);
   if (T * k > 0)

@@ -384,27 +384,52 @@ __global__ void hopa_rank_kernel(const int* __restrict__ es, int* __restrict__ r
                                  int* __restrict__ chunka_hist, int T, int k, int groups_m,
                                  int slots, int n_nodes) {
   __shared__ int s_cnt[TB200_MAX_WORLD * 4];
+  __shared__ unsigned s_mask[TB200_MAX_WORLD * 4];
   const int lane = threadIdx.x;
   const int per = (T + TB200_PLAN_CHUNKS - 1) / TB200_PLAN_CHUNKS;
   const int t0 = blockIdx.x * per, t1 = min(T, t0 + per);
   const int q = k / groups_m;
-  for (int g = lane; g < n_nodes; g += 32) s_cnt[g] = 0;
+  for (int g = lane; g < n_nodes; g += 32) {
+    s_cnt[g] = 0;
+    s_mask[g] = 0u;
+  }
   __syncwarp();
+  // Rank of every (token, run) among the rows bound for its group, in TOKEN order: a token
+  // sends at most one run to a group, so the lower tokens of a 32-token batch that address
+  // group g are a bit count over a per-group lane mask.
   for (int tb = t0; tb < t1; tb += 32) {
     const int t = tb + lane;
     const bool live = t < t1;
-    for (int m = 0; m < groups_m; ++m) {
-      const int e = live ? es[t * k + m * q] : -1;
-      int key = (live && e >= 0) ? e / slots : -1 - lane;
-      const bool ok = live && e >= 0 && key < n_nodes;
-      if (!ok) key = -1 - lane;
-      const unsigned peers = __match_any_sync(0xffffffffu, key);
-      if (ok) ranka_local[t * groups_m + m] = s_cnt[key] + __popc(peers & ((1u << lane) - 1u));
-      else if (live) ranka_local[t * groups_m + m] = -1;
-      __syncwarp();
-      if (ok && (peers >> lane) == 1u) s_cnt[key] += __popc(peers);
-      __syncwarp();
-    }
+    auto group_of = [&](int m) {
+      const int e = es[t * k + m * q];
+      const int g = e >= 0 ? e / slots : -1;
+      return (g >= 0 && g < n_nodes) ? g : -1;
+    };
+    if (live)
+      for (int m = 0; m < groups_m; ++m) {
+        const int g = group_of(m);
+        if (g >= 0) atomicOr(&s_mask[g], 1u << lane);
+      }
+    __syncwarp();
+    if (live)
+      for (int m = 0; m < groups_m; ++m) {
+        const int g = group_of(m);
+        ranka_local[t * groups_m + m] =
+            g >= 0 ? s_cnt[g] + __popc(s_mask[g] & ((1u << lane) - 1u)) : -1;
+      }
+    __syncwarp();
+    if (live)
+      for (int m = 0; m < groups_m; ++m) {
+        const int g = group_of(m);
+        if (g >= 0 && (s_mask[g] >> lane) == 1u) s_cnt[g] += __popc(s_mask[g]);
+      }
+    __syncwarp();
+    if (live)
+      for (int m = 0; m < groups_m; ++m) {
+        const int g = group_of(m);
+        if (g >= 0) s_mask[g] = 0u;
+      }
+    __syncwarp();
   }
   for (int g = lane; g < n_nodes; g += 32) chunka_hist[blockIdx.x * n_nodes + g] = s_cnt[g];
 }

@@ -103,6 +103,28 @@ def arena_layout(sizes, guard: int = GUARD_BYTES):
     return offsets, guards, off
 
 
+def section_sizes(*, world: int, n_experts: int, hidden: int, q: int, cap_rows: int,
+                  arrival_rows: int, out_rows: int, overlap: bool, own_slots: int,
+                  rep_slots: int) -> dict:
+    """Bytes of every arena section, in layout order.  ``cap_rows``: rows of the expert-sorted
+    buffers; ``arrival_rows``: Hop A rows a representative can receive (1 when two-hop is not
+    used); ``out_rows``: rows of the owner-side output sections (1 under the overlap schedule);
+    ``own_slots`` / ``rep_slots``: return slots at the origin (one-hop) and at the
+    representative (two-hop), 1 for a path the context does not run."""
+    row = hidden * 2
+    sizes = {
+        "counts_all": world * n_experts * 4, "flags": FK_NUM * MAX_WORLD * 4,
+        "xin": cap_rows * row, "yout": out_rows * row, "dout": cap_rows * row,
+        "dxs": out_rows * row, "ha_rows": arrival_rows * row,
+        "ha_hdr": arrival_rows * 3 * q * 4, "red": arrival_rows * row,
+        "hb_rows": arrival_rows * row, "dred": arrival_rows * row, "dgate": arrival_rows * q * 4,
+    }
+    if overlap:
+        sizes.update({"ret": own_slots * row, "dret": own_slots * row, "rowmap": cap_rows * 4,
+                      "ret2": rep_slots * row, "dret2": rep_slots * row})
+    return sizes
+
+
 def chunk_ranges(epr: int, chunks: int):
     """Split the local experts ``0 .. epr`` into at most ``chunks`` contiguous ranges of (almost)
     equal length: ``[(lo, hi), ...]``."""
@@ -124,7 +146,7 @@ def flag_value(epoch: int, i: int, n: int) -> int:
 class FusedEPContext:
     def __init__(self, cfg: TRouteConfig, hidden: int, d_expert: int, tokens: int, *, world: int,
                  rank: int, rpn: int, device, group=None, row_capacity_factor: float = 2.0,
-                 overlap=None, chunks=None):
+                 overlap=None, chunks=None, modes=None):
         from .. import ops
         if not ops.custom_ops_enabled():
             raise RuntimeError("the fused transport needs the native library: "
@@ -136,7 +158,7 @@ class FusedEPContext:
         self._init_args = dict(cfg=cfg, hidden=hidden, d_expert=d_expert, tokens=tokens,
                                world=world, rank=rank, rpn=rpn, device=device, group=group,
                                row_capacity_factor=row_capacity_factor, overlap=overlap,
-                               chunks=chunks)
+                               chunks=chunks, modes=modes)
         if world > MAX_WORLD:
             raise ValueError(f"world={world} exceeds the arena limit {MAX_WORLD}")
         if cfg.n_experts % world or world % rpn:
@@ -148,7 +170,15 @@ class FusedEPContext:
         self.epr = self.E // world
         self.n_nodes = world // rpn
         self.k, self.M, self.q = cfg.top_k, cfg.top_groups, cfg.per_group_k
-        self.two_hop_ok = (self.n_nodes >= 2 and cfg.n_groups == self.n_nodes)
+        # ``modes`` names the paths the context will run (default both): the sections only the
+        # other path uses shrink to one row, which is most of the arena at training sizes
+        modes = ("one_hop", "two_hop") if modes is None else tuple(modes)
+        if not modes or any(m not in ("one_hop", "two_hop") for m in modes):
+            raise ValueError(f"modes must name one_hop and / or two_hop, got {modes!r}")
+        self.two_hop_ok = (self.n_nodes >= 2 and cfg.n_groups == self.n_nodes
+                           and "two_hop" in modes)
+        # a two-hop request on a geometry without two groups runs one-hop: keep its sections
+        self.one_hop_ok = "one_hop" in modes or not self.two_hop_ok
         self.cap_rows = _align(min(world * tokens * self.k,
                                    int(row_capacity_factor * tokens * self.k))
                                + self.epr * (SEG_ALIGN - 1), 128)
@@ -157,25 +187,17 @@ class FusedEPContext:
         self.chunks = chunk_ranges(self.epr, chunks if self.overlap else 1)
         self.ret_slots = tokens * self.k
         H = hidden
-        row = H * 2
         arows = self.n_nodes * tokens if self.two_hop_ok else 1
         self.arows = arows
         self.ret2_slots = arows * self.q
         # with the overlap schedule the second GEMM stores into return slots, so the owner-side
         # output sections are never touched
         out_rows = 1 if self.overlap else self.cap_rows
-        sizes = {
-            "counts_all": world * self.E * 4, "flags": FK_NUM * MAX_WORLD * 4,
-            "xin": self.cap_rows * row, "yout": out_rows * row, "dout": self.cap_rows * row,
-            "dxs": out_rows * row, "ha_rows": arows * row, "ha_hdr": arows * 3 * self.q * 4,
-            "red": arows * row, "hb_rows": arows * row, "dred": arows * row,
-            "dgate": arows * self.q * 4,
-        }
-        if self.overlap:
-            sizes.update({"ret": self.ret_slots * row, "dret": self.ret_slots * row,
-                          "rowmap": self.cap_rows * 4,
-                          "ret2": (self.ret2_slots if self.two_hop_ok else 1) * row,
-                          "dret2": (self.ret2_slots if self.two_hop_ok else 1) * row})
+        sizes = section_sizes(world=world, n_experts=self.E, hidden=H, q=self.q,
+                              cap_rows=self.cap_rows, arrival_rows=arows, out_rows=out_rows,
+                              overlap=self.overlap,
+                              own_slots=self.ret_slots if self.one_hop_ok else 1,
+                              rep_slots=self.ret2_slots if self.two_hop_ok else 1)
         names = list(sizes)
         assert tuple(names[:12]) == _BASE_SECTIONS
         offsets, self.guards, self.nbytes = arena_layout([sizes[n] for n in names])
@@ -234,6 +256,11 @@ class FusedEPContext:
     def next_epoch(self) -> int:
         self.epoch += 1
         return self.epoch
+
+    def check_mode(self, mode: str) -> None:
+        if mode == "one_hop" and not self.one_hop_ok:
+            raise ValueError("this context was built for two_hop only (modes=('two_hop',)): its "
+                             "one-hop return sections hold one row")
 
     def owner_wait_range(self, mode: str):
         """Which arrival flags an expert owner waits for: every rank (one-hop) or the ranks of
@@ -573,6 +600,7 @@ def fused_moe_forward(fctx: FusedEPContext, x, idx, gates, w13, w2, *, mode: str
     ``layer.apply_capacity`` without its host-side counts exchange."""
     if mode == "two_hop" and not fctx.two_hop_ok:
         mode = "one_hop"          # fewer than two groups (or groups != routing groups)
+    fctx.check_mode(mode)
     if x.shape[0] > fctx.tokens:
         raise ValueError(f"{x.shape[0]} tokens exceed the context capacity {fctx.tokens}")
     if x.dtype != torch.bfloat16 or w13.dtype != torch.bfloat16:
@@ -693,6 +721,7 @@ def fused_dispatch_combine(fctx: FusedEPContext, x, idx, gates, *, mode: str):
                           for (lo, hi), c in zip(fctx.bounds(x.shape[0]), fctx.ctxs)], dim=0)
     if mode == "two_hop" and not fctx.two_hop_ok:
         mode = "one_hop"
+    fctx.check_mode(mode)
     fctx.check_free()
     ep = fctx.next_epoch()
     p = _plan(fctx, idx, gates, mode, ep)

@@ -214,7 +214,8 @@ class EPTerracedMoE(nn.Module):
         from . import fused as fz
         self._ctx = fz.make_context(self.cfg, self.hidden, self.d_expert, tokens,
                                     world=self.world, rank=self.rank, rpn=self.rpn, device=device,
-                                    row_capacity_factor=self.row_capacity_factor)
+                                    row_capacity_factor=self.row_capacity_factor,
+                                    modes=(self.mode,) if self.mode in ("one_hop", "two_hop") else None)
 
     def reserve(self, tokens: int, device=None) -> None:
         """Collective: size the arena for ``tokens`` tokens per rank.  The old arena's peer

@@ -223,6 +223,7 @@ def _fake_context(fz, *, T, k, H, d, epr, cap, world, n_nodes, two_hop, overlap,
     c.world, c.rank, c.rpn, c.tokens, c.cap_rows, c.epoch = world, 0, 1, T, cap, 0
     c.arena, c.done = torch.zeros(1, dtype=torch.uint8), torch.zeros(8, dtype=torch.int32)
     c.two_hop_ok, c.overlap, c.ret_slots, c.ret2_slots = two_hop, overlap, T * k, n_nodes * T * 2
+    c.one_hop_ok = True
     c.E, c.epr, c.k, c.M, c.q, c.hidden, c.d_expert = 16, epr, k, 2, 2, H, d
     c.n_nodes, c.device = n_nodes, torch.device("cpu")
     c.chunks = fz.chunk_ranges(epr, chunks if overlap else 1)
@@ -384,6 +385,31 @@ def test_capacity_in_the_plan_keeps_exactly_the_picks_apply_capacity_keeps():
             a, n = int(plan["seg_start"][o][le]), int(plan["seg_count"][o][le])
             assert bool((taken[o][a:a + n] == 1).all())
     del kept_idx
+
+
+def test_single_mode_contexts_shrink_the_other_paths_sections():
+    """The decoder benchmark's layer (32768 tokens per GPU, top-4, width 2048, 8 GPUs in groups of
+    2): a context built for one path carries about half the bytes of one built for both."""
+    from terracemoe_simulator_b200.parallel import fused as fz
+    T, k, q, H, world, n_nodes = 32768, 4, 2, 2048, 8, 4
+    cap_rows = 2 * T * k
+
+    def total(one_hop, two_hop):
+        sizes = fz.section_sizes(world=world, n_experts=64, hidden=H, q=q, cap_rows=cap_rows,
+                                 arrival_rows=n_nodes * T if two_hop else 1, out_rows=1,
+                                 overlap=True, own_slots=T * k if one_hop else 1,
+                                 rep_slots=n_nodes * T * q if two_hop else 1)
+        assert list(sizes)[:12] == list(fz._BASE_SECTIONS)
+        return fz.arena_layout(list(sizes.values()))[2]
+    both, one, two = total(True, True), total(True, False), total(False, True)
+    assert one < 0.5 * both and two < 0.9 * both
+    assert one == pytest.approx((2 * cap_rows + 2 * T * k) * H * 2, rel=0.01)
+    ctx = _fake_context(fz, T=8, k=4, H=32, d=16, epr=16, cap=128, world=2, n_nodes=2,
+                        two_hop=True, overlap=True)
+    ctx.one_hop_ok = False
+    with pytest.raises(ValueError, match="built for two_hop only"):
+        ctx.check_mode("one_hop")
+    ctx.check_mode("two_hop")
 
 
 def test_arena_layout_puts_a_guard_after_every_section():

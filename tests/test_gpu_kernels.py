@@ -110,6 +110,43 @@ def test_k2_pack_bitwise(native_ops, geom, sort_rows, dt):
         assert torch.equal(a.cpu(), b)
 
 
+@pytest.mark.parametrize("T,E,k,align", [(300, 16, 4, 1), (1000, 16, 4, 64), (5000, 64, 6, 64),
+                                         (33, 8, 2, 1), (4096, 256, 8, 64)])
+def test_moe_plan_is_the_stable_counting_sort(native_ops, T, E, k, align):
+    """Rows of an expert are ordered by token (the canonical order the capacity rule relies on):
+    position = segment start + earlier tokens that picked the expert."""
+    g = torch.Generator().manual_seed(T + E)
+    idx = torch.stack([torch.randperm(E, generator=g)[:k] for _ in range(T)])
+    gates = torch.rand(T, k, generator=g)
+    es, gs, cols, pos, seg_start, seg_count = torch.ops.terrace.moe_plan(idx.to(DEV), gates.to(DEV),
+                                                                         E, align)
+    order = torch.argsort(idx, dim=1, stable=True)
+    want_es = idx.gather(1, order)
+    counts = torch.bincount(idx.reshape(-1), minlength=E)
+    padded = (counts + align - 1) // align * align
+    start = torch.cumsum(padded, 0) - padded
+    onehot = torch.zeros(T, E, dtype=torch.long).scatter_add_(1, idx, torch.ones_like(idx))
+    earlier = torch.cumsum(onehot, 0) - onehot
+    want_pos = start[want_es] + earlier.gather(1, want_es)
+    assert torch.equal(es.cpu().long(), want_es) and torch.equal(cols.cpu().long(), order)
+    assert torch.equal(gs.cpu(), gates.gather(1, order))
+    assert torch.equal(seg_count.cpu().long(), counts) and torch.equal(seg_start.cpu().long(), start)
+    assert torch.equal(pos.cpu().long(), want_pos)
+
+
+def test_moe_plan_with_a_repeated_expert_still_tiles(native_ops):
+    """Not a top-k routing (a token names an expert twice): every pick still gets its own row
+    inside the expert's segment."""
+    g = torch.Generator().manual_seed(3)
+    T, E, k = 700, 8, 4
+    idx = torch.randint(0, E, (T, k), generator=g)
+    es, _, _, pos, seg_start, seg_count = torch.ops.terrace.moe_plan(idx.to(DEV), None, E, 1)
+    pos, es = pos.cpu().long().reshape(-1), es.cpu().long().reshape(-1)
+    assert torch.equal(torch.sort(pos).values, torch.arange(T * k))
+    lo = seg_start.cpu().long()[es]
+    assert bool(((pos >= lo) & (pos < lo + seg_count.cpu().long()[es])).all())
+
+
 def test_route_select_matches_t_route(native_ops):
     from terracemoe_simulator_b200.routing import TRouteConfig, t_route
     torch.manual_seed(1)
