@@ -363,9 +363,16 @@ def run_ours(args, rank, world, local):
     usable = [p for p in runners if results[p]["parity_ok"]] or list(runners)
     best = min(usable, key=lambda p: results[p]["ms_per_step"])
     final = {}
+    if trace.enabled():
+        trace.report(group=True if world > 1 else None)      # drop the communication-only spans
     e2e_blocks = timed(make_step(best, True), args.steps, args.warmup, world, args.repeats,
                        drain=lambda: final.update(loss=losses.flush()))
     e2e = block_stats(e2e_blocks, args.steps)
+    if trace.enabled():
+        rep = trace.report(group=True if world > 1 else None)
+        if rank == 0:
+            print(f"--- phases of the end-to-end run ({best}) ---\n" + trace.format_report(rep),
+                  file=sys.stderr)
     last_loss = final.get("loss")
     tokens = TOKENS * world
     value = tokens / (results[best]["ms_per_step"] * 1e-3)

@@ -1,61 +1,114 @@
-"""Additive model of the single-MoE-layer step on B200, checked against the measured steps.
+"""Model of the single-MoE-layer step on B200, checked against the measured steps.
 
 On the reference machine the step-level gate fails: communication hides behind other work in
 ways no one-parameter overlap model captures (``sim/validate.py``, ``sim/overlap.py``).  On B200
-the fused layer has, today, no overlap at all between its phases, so the plain sum should hold:
+the layer has two schedules whose structure is known, so each gets its own sum:
 
-    step = grouped GEMMs (forward + backward, priced from the measured kernel throughput with
-           the 128-row tile quantisation of short groups)
-         + memory-bound kernels around them (measured, independent of the GPU count because the
-           tokens per GPU are fixed)
-         + 2 x (dispatch + combine)            forward and backward, from the calibrated
-                                               ``calibrate.b200_nvswitch`` call model
+    serial   (remote-read arms, ``TERRACE_EP_OVERLAP=0``): nothing overlaps,
+             step = GEMMs + memory-bound kernels + 2 x (dispatch + combine)
 
-``python -m terracemoe_simulator_b200.sim.b200_step`` prints model against measurement for the
-1-, 2- and 8-GPU runs of ``bench.py`` and the gate (every configuration within 10 %).  A gate
-that starts failing after dispatch / combine get overlapped with the GEMMs is the expected
-outcome of that optimisation, and the place to add the overlap term.
+    overlap  (default): the dispatch leaves in chunks on a side stream and the return leg rides in
+             the second GEMM's epilogue, so per direction only ``phase.ChunkedSchedule.exposed_ms``
+             stays visible: the first chunk's share of the dispatch, whatever a later chunk's
+             transfer exceeds the GEMM time it hides under, and the local reduction
+             step = GEMMs + memory-bound kernels + exposed(forward) + exposed(backward)
+
+The GEMM term is priced from the kernels' measured throughput (long groups, with the 128-row tile
+quantisation of short groups and the weight-gradient kernel's epilogue exposure), scaled by the
+SM clock: the kernel figures hold at the clock the kernels reach when timed alone, and a step
+under the 1 kW power cap runs slower the busier it keeps the GPU (1515 MHz on one GPU, where
+nothing ever waits; 1736 MHz on four), so every run carries the median clock sampled during it.  The communication term is the calibrated call model
+(``calibrate.b200_nvswitch``).  Every measured number is read from a JSON file
+(``sim/data/b200_layer_bench.json`` by default; ``--bench FILE`` takes the lines ``bench.py``
+printed), none is in this source.
+
+``python -m terracemoe_simulator_b200.sim.b200_step`` prints model against measurement for every
+measured (GPUs, path, schedule) and the gate (every configuration within 10 %).
 
 No counterpart in the reference (its phase model refuses to return a number, ``sim/phase.py``).
 """
 from __future__ import annotations
 
+import json
+import os
+
+from ._text import Column, render_table
 from .calibrate import b200_nvswitch
 from .core import MoEGeometry, one_hop_call, two_hop_call
+from .phase import ChunkedSchedule
 
 GATE = 0.10
+DATA = os.path.join(os.path.dirname(os.path.abspath(__file__)), "data", "b200_layer_bench.json")
 
 # Layer of the headline benchmark: d_model 4096, 64 experts of hidden 1408, top-6, M = 2,
 # 4096 tokens per GPU.
 HIDDEN, D_EXPERT, N_EXPERTS, TOP_K, TOP_GROUPS, TOKENS = 4096, 1408, 64, 6, 2, 4096
-
-# Measured kernel throughput with long groups (8 local experts x 3072 rows; CUDA events,
-# ``bench/kernel_cases.py``), TFLOPS: forward / dgrad kernels and the weight-gradient kernel.
-TFLOPS_FWD_DGRAD_LONG = 1300.0
-TFLOPS_WGRAD_LONG = 1240.0
-# The weight-gradient kernel reduces over a group's rows: with short groups its main loop is
-# short and the epilogue shows.  Measured 939 TFLOPS at 384 rows per expert.
-WGRAD_SHORT_ROWS, TFLOPS_WGRAD_SHORT = 384.0, 939.0
 TILE_ROWS, SEG_ALIGN = 128, 64
-# Memory-bound kernels of one step (router, plan, scatter, combine and their backward parts):
-# measured 0.45 ms on one GPU; the fused path replaces scatter / combine by push / pull kernels
-# that are priced inside the dispatch + combine term, which leaves the GEMM-side remainder
-# (SwiGLU backward 0.08, router and plan 0.06, padding and small elementwise kernels 0.1).
-ELEMENTWISE_LOCAL_MS = 0.45
-ELEMENTWISE_FUSED_MS = 0.25
-
-# (GPUs, ranks per group, path) -> measured ms per step (bench.py, CUDA events, max over ranks)
-MEASURED_MS = {
-    (1, 1, "local"): 3.27,
-    (2, 1, "one_hop"): 3.46,
-    (2, 1, "two_hop"): 3.31,
-    (8, 2, "one_hop"): 3.77,
-    (8, 2, "two_hop"): 3.70,
-}
-# dispatch + combine measured alone on one GPU (local scatter + combine), ms
-LOCAL_DISPATCH_COMBINE_MS = 0.13
+SCHEDULES = ("serial", "overlap")
 
 
+# ---- measurements ---------------------------------------------------------------------------------
+def _runs_from_bench_lines(lines) -> list:
+    """``bench.py`` JSON lines -> run records ``{n_gpus, rpn, chunks, paths: {name: ms}}``; the
+    ``*_pull`` paths of a line are the serial arms of the same run."""
+    runs = []
+    for d in lines:
+        if d.get("impl", "ours") != "ours" or "paths" not in d:
+            continue
+        runs.append({"n_gpus": d["n_gpus"], "rpn": d["config"].get("rpn", 1),
+                     "chunks": d.get("impl_detail", {}).get("chunks", 2),
+                     "schedule": d.get("impl_detail", {}).get("schedule", "overlap"),
+                     "paths": {name: p["ms_per_step"] for name, p in d["paths"].items()}})
+    return runs
+
+
+def load_bench(path: str | None = None) -> dict:
+    """The measured steps and kernel figures: either the committed file (``runs`` + ``kernels``)
+    or a file of ``bench.py`` output lines (kernel figures then come from the committed file)."""
+    with open(DATA) as f:
+        shipped = json.load(f)
+    if path is None or os.path.abspath(path) == DATA:
+        return shipped
+    with open(path) as f:
+        text = f.read().strip()
+    try:
+        given = json.loads(text)
+    except ValueError:                                   # one JSON object per line
+        given = [json.loads(row) for row in text.splitlines() if row.startswith("{")]
+    if isinstance(given, dict) and "runs" in given:
+        return {**shipped, **given}
+    lines = given if isinstance(given, list) else [given]
+    return {**shipped, "runs": _runs_from_bench_lines(lines), "source": path}
+
+
+def measured_steps(bench: dict | None = None) -> dict:
+    """``{(GPUs, ranks per group, path, schedule): ms per step}``."""
+    bench = bench or load_bench()
+    out = {}
+    for run in bench["runs"]:
+        default = run.get("schedule", "overlap")
+        for name, ms in run["paths"].items():
+            serial = name.endswith("_pull")
+            path = name[:-5] if serial else name
+            schedule = "serial" if serial or default == "serial" else "overlap"
+            if path == "local":
+                schedule = "serial"
+            out[run["n_gpus"], run["rpn"], path, schedule] = ms
+    return out
+
+
+class _Kernels:
+    """Kernel-level figures of the data file, by attribute."""
+
+    def __init__(self, table: dict):
+        self.__dict__.update(table)
+
+
+def kernels(bench: dict | None = None) -> _Kernels:
+    return _Kernels((bench or load_bench())["kernels"])
+
+
+# ---- terms ------------------------------------------------------------------------------------------
 def tile_efficiency(rows_per_expert: float) -> float:
     """Share of the MMA rows that carry data when a group of ``rows_per_expert`` rows (random
     around that mean, padded to 64) is cut into 128-row tiles: half a tile is wasted on average
@@ -65,149 +118,134 @@ def tile_efficiency(rows_per_expert: float) -> float:
     return min(1.0, rows_per_expert / slots)
 
 
-def gemm_ms(n_gpus: int) -> dict:
-    """Forward + backward grouped GEMM time of one step on each GPU."""
+def gemm_ms(n_gpus: int, kern: _Kernels | None = None, sm_mhz: float | None = None) -> dict:
+    """Forward and backward grouped GEMM time of one step on each GPU, at SM clock ``sm_mhz``
+    (default: the clock of the kernels timed alone)."""
+    kern = kern or kernels()
     rows = TOKENS * TOP_K                              # rows per GPU after dispatch (balanced)
-    local_experts = N_EXPERTS // n_gpus
-    per_expert = rows / local_experts
+    per_expert = rows / (N_EXPERTS // n_gpus)
     flops_fwd = 2.0 * rows * HIDDEN * D_EXPERT * 3     # gate, up, down
     eff = tile_efficiency(per_expert)
-    fwd_dgrad_tflops = TFLOPS_FWD_DGRAD_LONG * eff
-    # weight gradient: interpolate its epilogue exposure as 1/T = 1/T_long + c / rows
-    c = (1.0 / TFLOPS_WGRAD_SHORT - 1.0 / TFLOPS_WGRAD_LONG) * WGRAD_SHORT_ROWS
-    wgrad_tflops = 1.0 / (1.0 / TFLOPS_WGRAD_LONG + c / per_expert)
-    t_fwd_dgrad = 2.0 * flops_fwd / (fwd_dgrad_tflops * 1e12) * 1e3
-    t_wgrad = flops_fwd / (wgrad_tflops * 1e12) * 1e3
+    fwd_dgrad_tflops = kern.tflops_fwd_dgrad_long * eff
+    # weight gradient: its epilogue shows with short groups, 1/T = 1/T_long + c / rows
+    c = (1.0 / kern.tflops_wgrad_short - 1.0 / kern.tflops_wgrad_long) * kern.wgrad_short_rows
+    wgrad_tflops = 1.0 / (1.0 / kern.tflops_wgrad_long + c / per_expert)
+    derate = kern.gemm_alone_sm_mhz / sm_mhz if sm_mhz else 1.0
+    fwd = derate * flops_fwd / (fwd_dgrad_tflops * 1e9)
+    bwd = derate * (flops_fwd / (fwd_dgrad_tflops * 1e9) + flops_fwd / (wgrad_tflops * 1e9))
     return {"rows_per_expert": per_expert, "tile_efficiency": eff,
             "fwd_dgrad_tflops": fwd_dgrad_tflops, "wgrad_tflops": wgrad_tflops,
-            "ms": t_fwd_dgrad + t_wgrad}
+            "fwd_ms": fwd, "bwd_ms": bwd, "ms": fwd + bwd}
 
 
-def comm_ms(n_gpus: int, rpn: int, path: str) -> float:
+def comm_ms(n_gpus: int, rpn: int, path: str, kern: _Kernels | None = None) -> float:
     """Dispatch + combine of one direction pair (there and back), ms."""
+    kern = kern or kernels()
     if n_gpus == 1:
-        return LOCAL_DISPATCH_COMBINE_MS
+        return kern.local_dispatch_combine_ms
     n_groups = max(n_gpus // rpn, 2)
     geom = MoEGeometry(f"b200x{n_gpus}", n_groups, max(n_gpus // n_groups, 1), TOP_K, TOP_GROUPS,
                        H=HIDDEN, seq=TOKENS, gbs=n_gpus * TOKENS)
-    cluster = b200_nvswitch(R=geom.R)
     call = one_hop_call if path == "one_hop" else two_hop_call
-    return 2.0 * call(cluster, geom)                   # dispatch + combine
+    return 2.0 * call(b200_nvswitch(R=geom.R), geom)
 
 
-# measured copy bandwidth of one B200 (STREAM-style), GB/s: prices the local reduction that
-# replaces the remote pull when the expert GEMM's epilogue delivers the rows
-HBM_COPY_GBPS = 6556.0
-
-
-def local_reduce_ms() -> float:
+def local_reduce_ms(kern: _Kernels | None = None) -> float:
     """Gate-weighted reduction of k rows per token from this GPU's own return slots."""
-    read = TOKENS * TOP_K * HIDDEN * 2.0
-    write = TOKENS * HIDDEN * 2.0
-    return (read + write) / (HBM_COPY_GBPS * 1e6)
+    kern = kern or kernels()
+    moved = (TOP_K + 1) * TOKENS * HIDDEN * 2.0
+    return moved / (kern.hbm_copy_gbps * 1e6)
 
 
-def predict_ms(n_gpus: int, rpn: int, path: str, epilogue_push: bool = False) -> dict:
-    """``epilogue_push`` (one-hop only): the combine transfer rides in the second GEMM's epilogue
-    and is assumed hidden under it; what stays exposed of each dispatch + combine pair is the
-    dispatch and a local reduction.  A forecast written down before the first run of that path."""
-    g = gemm_ms(n_gpus)
-    c = comm_ms(n_gpus, rpn, path)
+def run_clock(n_gpus: int, bench: dict | None = None):
+    """Median SM clock sampled during the measured run on ``n_gpus`` GPUs (None if not recorded)."""
+    for run in (bench or load_bench())["runs"]:
+        if run["n_gpus"] == n_gpus and run.get("sm_mhz"):
+            return float(run["sm_mhz"])
+    return None
+
+
+def predict_ms(n_gpus: int, rpn: int, path: str, schedule: str = "overlap", chunks: int = 2,
+               bench: dict | None = None, sm_mhz: float | None = None) -> dict:
+    """``sm_mhz``: SM clock of the step (default: the one sampled during the measured run at
+    this GPU count, else the clock of the kernels timed alone)."""
+    if schedule not in SCHEDULES:
+        raise ValueError(f"schedule must be one of {SCHEDULES}")
+    kern = kernels(bench)
+    g = gemm_ms(n_gpus, kern, sm_mhz or run_clock(n_gpus, bench))
+    pair = comm_ms(n_gpus, rpn, path, kern)
     if n_gpus == 1:
-        total = g["ms"] + ELEMENTWISE_LOCAL_MS + LOCAL_DISPATCH_COMBINE_MS
-    elif epilogue_push:
-        if path != "one_hop":
-            raise ValueError("the scattering epilogue exists for the one-hop path only")
-        c = 0.5 * c + local_reduce_ms()
-        total = g["ms"] + ELEMENTWISE_FUSED_MS + 2.0 * c
+        exposed = 2.0 * pair
+        total = g["ms"] + kern.elementwise_local_ms + exposed
+    elif schedule == "serial":
+        exposed = 2.0 * pair                                    # forward and backward
+        total = g["ms"] + kern.elementwise_fused_ms + exposed
     else:
-        total = g["ms"] + ELEMENTWISE_FUSED_MS + 2.0 * c      # forward and backward
-    return {"gemm_ms": g["ms"], "comm_ms": c, "total_ms": total, "gemm": g}
+        plan = ChunkedSchedule(chunks=chunks, local_reduce_ms=local_reduce_ms(kern),
+                               return_hidden=kern.return_hidden)
+        one_way = 0.5 * pair
+        extra = kern.two_hop_relay_ms if path == "two_hop" else 0.0
+        exposed = (plan.exposed_ms(one_way, g["fwd_ms"], one_way)
+                   + plan.exposed_ms(one_way, g["bwd_ms"], one_way) + 2.0 * extra)
+        total = g["ms"] + kern.elementwise_fused_ms + exposed
+    return {"gemm_ms": g["ms"], "comm_ms": pair, "exposed_ms": exposed, "total_ms": total,
+            "gemm": g}
 
 
-PIPELINE_GEMM_TAIL = 0.03      # extra tail of the shorter per-slice GEMM launches (n = 2, 8 GPUs)
-
-
-def predict_pipelined_ms(n_gpus: int, rpn: int, path: str, slices: int = 2) -> dict:
-    """Token-sliced pipeline: while one slice computes, another dispatches or combines, so as long
-    as a slice's GEMMs outlast its communication only the first dispatch and the last combine
-    stay exposed, 1 / slices of the total; the GEMMs pay a small tail for their shorter launches.
-    A forecast written down before the first run of that path."""
-    if n_gpus == 1 or slices < 2:
-        return predict_ms(n_gpus, rpn, path)
-    g = gemm_ms(n_gpus)
-    c = comm_ms(n_gpus, rpn, path)
-    gemm = g["ms"] * (1.0 + PIPELINE_GEMM_TAIL)
-    per_slice_comm, per_slice_gemm = 2.0 * c / slices, gemm / slices
-    hidden_ok = per_slice_gemm >= per_slice_comm
-    exposed = 2.0 * c / slices if hidden_ok else 2.0 * c - (slices - 1) * per_slice_gemm
-    return {"gemm_ms": gemm, "comm_ms": c, "total_ms": gemm + ELEMENTWISE_FUSED_MS + exposed,
-            "hidden": hidden_ok}
-
-
-def forecast_epilogue_push(verbose: bool = True) -> list:
-    """Expected one-hop step with the combine folded into the GEMM, next to today's model and
-    measurement.  The additive model reads 2-8 % low, so the forecast is scaled by the measured /
-    modelled ratio of the same configuration."""
+# ---- gate -------------------------------------------------------------------------------------------
+def validate(verbose: bool = True, bench: dict | None = None):
+    bench = bench or load_bench()
     rows = []
-    for (n, rpn, path), measured in sorted(MEASURED_MS.items()):
-        if path != "one_hop":
-            continue
-        now = predict_ms(n, rpn, path)["total_ms"]
-        then = predict_ms(n, rpn, path, epilogue_push=True)["total_ms"]
-        rows.append((n, rpn, measured, now, then, then * measured / now))
+    for (n, rpn, path, schedule), measured in sorted(measured_steps(bench).items()):
+        p = predict_ms(n, rpn, path, schedule, bench=bench)
+        rows.append((n, rpn, path, schedule, measured, p["total_ms"], p["gemm_ms"],
+                     p["exposed_ms"], p["total_ms"] / measured - 1.0))
+    worst = max((abs(r[-1]) for r in rows), default=0.0)
+    ok = bool(rows) and worst <= GATE
     if verbose:
-        print("one-hop step with the combine transfer in the GEMM epilogue: forecast")
-        print("%4s %4s %9s %9s %9s %12s" % ("GPUs", "rpn", "measured", "model", "forecast",
-                                            "scaled (ms)"))
-        for n, rpn, m, now, then, scaled in rows:
-            print("%4d %4d %9.2f %9.2f %9.2f %12.2f" % (n, rpn, m, now, then, scaled))
-    return rows
-
-
-def validate(verbose: bool = True):
-    rows, worst = [], 0.0
-    for (n, rpn, path), measured in sorted(MEASURED_MS.items()):
-        p = predict_ms(n, rpn, path)
-        err = (p["total_ms"] - measured) / measured
-        worst = max(worst, abs(err))
-        rows.append((n, rpn, path, measured, p["total_ms"], p["gemm_ms"], p["comm_ms"], err))
-    ok = worst <= GATE
-    if verbose:
-        print("single-MoE-layer step on B200: additive model against measurement")
-        print("%4s %4s %-8s %9s %9s %9s %9s %7s" % ("GPUs", "rpn", "path", "measured", "model",
-                                                    "GEMMs", "d+c", "err"))
-        for n, rpn, path, m, t, g, c, e in rows:
-            print("%4d %4d %-8s %9.2f %9.2f %9.2f %9.2f %+6.1f%%" % (n, rpn, path, m, t, g, c,
-                                                                     100 * e))
+        cols = [Column("GPUs", "%4d", lambda r: r[0]), Column("rpn", "%4d", lambda r: r[1]),
+                Column("path", "%-8s", lambda r: r[2]), Column("schedule", "%-8s", lambda r: r[3]),
+                Column("measured", "%9.2f", lambda r: r[4]), Column("model", "%9.2f", lambda r: r[5]),
+                Column("GEMMs", "%9.2f", lambda r: r[6]), Column("exposed", "%9.2f", lambda r: r[7]),
+                Column("err", "%7s", lambda r: "%+.1f%%" % (100 * r[8]))]
+        print("single-MoE-layer step on B200: model against measurement (ms per step)")
+        print("\n".join(render_table(cols, rows)))
         print("worst error %.1f%% (gate %.0f%%)" % (100 * worst, 100 * GATE))
         print("**B200 step gate %s**" % ("PASS" if ok else "FAIL"))
     return ok, {"worst": worst, "rows": rows}
 
 
-def forecast_pipeline(verbose: bool = True, slices: int = 2) -> list:
+def overlap_gain(verbose: bool = True, bench: dict | None = None) -> list:
+    """What the overlap schedule removes, measured and modelled: serial - overlap per
+    (GPUs, path)."""
+    bench = bench or load_bench()
+    steps = measured_steps(bench)
     rows = []
-    for (n, rpn, path), measured in sorted(MEASURED_MS.items()):
-        if n == 1:
+    for (n, rpn, path, schedule), ms in sorted(steps.items()):
+        if schedule != "overlap" or (n, rpn, path, "serial") not in steps:
             continue
-        now = predict_ms(n, rpn, path)["total_ms"]
-        then = predict_pipelined_ms(n, rpn, path, slices)["total_ms"]
-        rows.append((n, rpn, path, measured, now, then, then * measured / now))
+        model = (predict_ms(n, rpn, path, "serial", bench=bench)["total_ms"]
+                 - predict_ms(n, rpn, path, "overlap", bench=bench)["total_ms"])
+        rows.append((n, rpn, path, steps[n, rpn, path, "serial"] - ms, model))
     if verbose:
-        print("step with %d token slices on %d streams: forecast" % (slices, slices))
-        print("%4s %4s %-8s %9s %9s %9s %12s" % ("GPUs", "rpn", "path", "measured", "model",
-                                                 "forecast", "scaled (ms)"))
-        for n, rpn, path, m, now, then, scaled in rows:
-            print("%4d %4d %-8s %9.2f %9.2f %9.2f %12.2f" % (n, rpn, path, m, now, then, scaled))
+        print("time removed by the overlap schedule (serial - overlap, ms per step)")
+        cols = [Column("GPUs", "%4d", lambda r: r[0]), Column("rpn", "%4d", lambda r: r[1]),
+                Column("path", "%-8s", lambda r: r[2]), Column("measured", "%9.2f", lambda r: r[3]),
+                Column("model", "%9.2f", lambda r: r[4])]
+        print("\n".join(render_table(cols, rows)))
     return rows
 
 
-def main() -> None:
-    validate()
+def main(argv=None) -> None:
+    import argparse
+    ap = argparse.ArgumentParser(description=__doc__.split("\n")[0])
+    ap.add_argument("--bench", default=None,
+                    help="file of bench.py output lines (default: the committed measurements)")
+    ns = ap.parse_args(argv)
+    bench = load_bench(ns.bench)
+    validate(bench=bench)
     print()
-    forecast_epilogue_push()
-    print()
-    forecast_pipeline()
+    overlap_gain(bench=bench)
 
 
 if __name__ == "__main__":

@@ -90,18 +90,24 @@ class ChunkedSchedule:
     """The schedule of this repository's fused transport, where the overlap is not a fitted
     efficiency but a consequence of the launch order: the dispatch goes out in ``chunks`` pushes
     on a side stream and the GEMMs of chunk c run while chunk c + 1 travels; the return leg is
-    written by the second GEMM's epilogue.  Exposed per layer: the first chunk's share of the
-    dispatch, whatever a later chunk's transfer exceeds the GEMM time it hides under, and the
-    final local reduction."""
+    written by the second GEMM's epilogue.  Exposed per direction: the first chunk's share of the
+    dispatch, whatever a later chunk's transfer exceeds the GEMM time it hides under, the part
+    of the return transfer the epilogue does not hide, and the final local reduction.
+
+    ``return_hidden`` is measured, not derived: the scattering epilogue stores 8 KiB rows over
+    NVLink from the same warps that drain the accumulators, so the second GEMM stretches while
+    it sends; on B200 a quarter of the return transfer disappears under it (2- and 4-GPU steps,
+    ``sim/b200_step.py``)."""
     chunks: int = 2
     local_reduce_ms: float = 0.05
+    return_hidden: float = 0.25
 
     def exposed_ms(self, dispatch_ms: float, expert_ms: float, return_ms: float = 0.0) -> float:
         n = max(int(self.chunks), 1)
         per_chunk_push, per_chunk_gemm = dispatch_ms / n, expert_ms / n
         spill = max(per_chunk_push - per_chunk_gemm, 0.0) * (n - 1)
-        # the return transfer rides in GEMM 2's epilogue: exposed only beyond that GEMM's time
-        tail = max(return_ms - expert_ms / 3.0, 0.0)
+        # the return transfer rides in GEMM 2's epilogue (a third of the expert time at most)
+        tail = max(return_ms * (1.0 - self.return_hidden), return_ms - expert_ms / 3.0, 0.0)
         return per_chunk_push + spill + tail + self.local_reduce_ms
 
     def layer_ms(self, dispatch_ms: float, expert_ms: float, return_ms: float = 0.0) -> float:

@@ -302,41 +302,69 @@ def test_b200_platform_and_gate():
 
 
 def test_b200_step_model_within_gate():
+    """Both schedules of the layer step, every measured (GPUs, path): the model stays inside
+    the gate, and no measured number lives in the module's source."""
     from terracemoe_simulator_b200.sim import b200_step
+    bench = b200_step.load_bench()
+    steps = b200_step.measured_steps(bench)
+    assert {k[3] for k in steps} == {"serial", "overlap"} and (1, 1, "local", "serial") in steps
     ok, d = b200_step.validate(verbose=False)
-    assert ok and d["worst"] <= b200_step.GATE and len(d["rows"]) == 5
+    assert ok and d["worst"] <= b200_step.GATE and len(d["rows"]) == len(steps) >= 9
+    kern = b200_step.kernels(bench)
     g1, g8 = b200_step.gemm_ms(1), b200_step.gemm_ms(8)
     assert g1["tile_efficiency"] < 0.9 < g8["tile_efficiency"] <= 1.0
-    assert g1["wgrad_tflops"] == pytest.approx(b200_step.TFLOPS_WGRAD_SHORT, rel=1e-6)
-    assert g8["ms"] < g1["ms"]
-    # the two-hop path is predicted (and measured) faster than one-hop at 2 and at 8 GPUs
-    for n, rpn in ((2, 1), (8, 2)):
-        assert b200_step.predict_ms(n, rpn, "two_hop")["total_ms"] \
-            < b200_step.predict_ms(n, rpn, "one_hop")["total_ms"]
-        assert b200_step.MEASURED_MS[(n, rpn, "two_hop")] < b200_step.MEASURED_MS[(n, rpn, "one_hop")]
-
-
-def test_b200_epilogue_push_forecast_is_a_gain_bounded_by_the_combine():
-    from terracemoe_simulator_b200.sim import b200_step
-    for n, rpn, measured, now, then, scaled in b200_step.forecast_epilogue_push(verbose=False):
-        one_way = 0.5 * b200_step.comm_ms(n, rpn, "one_hop")
-        assert then < now and now - then <= 2.0 * one_way          # at most the two combines
-        assert abs((now - then) - 2.0 * (one_way - b200_step.local_reduce_ms())) < 1e-9
-        assert scaled < measured
+    assert g1["wgrad_tflops"] == pytest.approx(kern.tflops_wgrad_short, rel=1e-6)
+    assert g8["ms"] < g1["ms"] and g1["fwd_ms"] + g1["bwd_ms"] == pytest.approx(g1["ms"])
+    # a slower clock stretches the GEMM term and nothing else
+    slow = b200_step.gemm_ms(1, sm_mhz=kern.gemm_alone_sm_mhz / 2)
+    assert slow["ms"] == pytest.approx(2 * g1["ms"])
     with pytest.raises(ValueError):
-        b200_step.predict_ms(8, 2, "two_hop", epilogue_push=True)
+        b200_step.predict_ms(2, 1, "one_hop", schedule="pipelined")
+    import inspect
+    src = inspect.getsource(b200_step)
+    assert "MEASURED_MS" not in src and "3.27" not in src and "1300" not in src
 
 
-def test_b200_pipeline_forecast_hides_all_but_one_slice_of_communication():
+def test_b200_step_overlap_term_follows_the_chunked_schedule():
+    """What the overlap schedule removes is what ChunkedSchedule says: all of the dispatch but
+    the first chunk, the hidden share of the return leg, minus the local reduction; two-hop
+    pays its relay on top.  Measured and modelled gains agree in sign for every (GPUs, path)."""
     from terracemoe_simulator_b200.sim import b200_step
-    for n, rpn, path, measured, now, then, scaled in b200_step.forecast_pipeline(verbose=False):
-        p = b200_step.predict_pipelined_ms(n, rpn, path, 2)
-        assert p["hidden"] and then < now and scaled < measured
-        comm = 2.0 * b200_step.comm_ms(n, rpn, path)
-        gain = now - then
-        assert abs(gain - (comm / 2 - b200_step.PIPELINE_GEMM_TAIL * b200_step.gemm_ms(n)["ms"])) < 1e-9
-    assert b200_step.predict_pipelined_ms(1, 1, "local")["total_ms"] == \
-        b200_step.predict_ms(1, 1, "local")["total_ms"]
+    from terracemoe_simulator_b200.sim.phase import ChunkedSchedule
+    kern = b200_step.kernels()
+    for n, rpn in ((2, 1), (4, 1), (8, 2)):
+        serial = b200_step.predict_ms(n, rpn, "one_hop", "serial")
+        overlap = b200_step.predict_ms(n, rpn, "one_hop", "overlap")
+        one_way = 0.5 * serial["comm_ms"]
+        plan = ChunkedSchedule(chunks=2, local_reduce_ms=b200_step.local_reduce_ms(kern),
+                               return_hidden=kern.return_hidden)
+        g = serial["gemm"]
+        want = sum(plan.exposed_ms(one_way, g[part], one_way) for part in ("fwd_ms", "bwd_ms"))
+        assert overlap["exposed_ms"] == pytest.approx(want)
+        assert serial["gemm_ms"] == overlap["gemm_ms"] and overlap["total_ms"] < serial["total_ms"]
+        two = b200_step.predict_ms(n, rpn, "two_hop", "overlap")
+        assert two["exposed_ms"] > 2 * kern.two_hop_relay_ms
+    for n, rpn, path, measured, model in b200_step.overlap_gain(verbose=False):
+        assert (measured > 0) == (model > 0), (n, path, measured, model)
+    # more chunks expose less of the dispatch; nothing hides when the GEMM is shorter than a push
+    few, many = ChunkedSchedule(chunks=2), ChunkedSchedule(chunks=4)
+    assert many.exposed_ms(0.4, 2.0, 0.0) < few.exposed_ms(0.4, 2.0, 0.0)
+    assert few.exposed_ms(0.4, 0.1, 0.0) == pytest.approx(0.2 + (0.2 - 0.05) + few.local_reduce_ms)
+
+
+def test_b200_step_reads_bench_lines(tmp_path):
+    """``--bench FILE`` takes the JSON lines bench.py prints; *_pull paths become serial arms."""
+    import json
+    from terracemoe_simulator_b200.sim import b200_step
+    line = {"impl": "ours", "n_gpus": 2, "config": {"rpn": 1}, "impl_detail": {"chunks": 2, "schedule": "overlap"},
+            "paths": {"one_hop": {"ms_per_step": 3.4}, "one_hop_pull": {"ms_per_step": 3.7}}}
+    f = tmp_path / "bench.jsonl"
+    f.write_text("noise\n" + json.dumps(line) + "\n" + json.dumps({"impl": "reference", "n_gpus": 2}) + "\n")
+    bench = b200_step.load_bench(str(f))
+    assert b200_step.measured_steps(bench) == {(2, 1, "one_hop", "overlap"): 3.4,
+                                               (2, 1, "one_hop", "serial"): 3.7}
+    ok, d = b200_step.validate(verbose=False, bench=bench)
+    assert len(d["rows"]) == 2
 
 
 def test_b200_roofline_ledger_and_fractions():
