@@ -40,6 +40,7 @@ import statistics
 import subprocess
 import sys
 import threading
+import time
 
 ROOT = os.path.dirname(os.path.abspath(__file__))
 
@@ -130,7 +131,7 @@ def timed(fn, steps: int, warmup: int, world: int, repeats: int = 1, drain=None)
     import torch.distributed as dist
     for _ in range(warmup):
         fn()
-    blocks = []
+    blocks, host = [], []
     for _ in range(repeats):
         torch.cuda.synchronize()
         if world > 1:
@@ -138,8 +139,10 @@ def timed(fn, steps: int, warmup: int, world: int, repeats: int = 1, drain=None)
         torch.cuda.synchronize()
         t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         t0.record()
+        h0 = time.perf_counter()
         for _ in range(steps):
             fn()
+        host.append((time.perf_counter() - h0) * 1e3 / steps)     # enqueue time, no sync inside
         if drain is not None:
             drain()
         t1.record()
@@ -151,6 +154,9 @@ def timed(fn, steps: int, warmup: int, world: int, repeats: int = 1, drain=None)
         if world > 1:
             dist.all_reduce(ms, op=dist.ReduceOp.MAX)
         blocks.append(ms.item())
+    # host time to enqueue one step (this rank, median block): close to the device time per step
+    # means the launch queue runs dry and the step is bound by the host
+    timed.host_ms_per_step = statistics.median(host) if host else None
     return blocks
 
 
@@ -307,7 +313,10 @@ def run_ours(args, rank, world, local):
     from terracemoe_simulator_b200.utils.prefetch import DeferredScalar, DevicePrefetcher
     host_batches = [x_host] + [x_host.clone().pin_memory() for _ in range(2)]
     feed = DevicePrefetcher(itertools.cycle(host_batches), device)
-    losses = DeferredScalar(device, lag=3)   # every step's loss is read on the host, 3 steps late
+    variant = args.e2e_variant
+    # every step's loss is read on the host, 3 steps late
+    losses = DeferredScalar(device, lag=3, side_stream=variant in ("side_read", "both"))
+    gated = variant in ("gated_h2d", "both")
 
     def make_step(path, e2e: bool):
         runner = runners[path]
@@ -315,15 +324,23 @@ def run_ours(args, rank, world, local):
         def step():
             for p in params:
                 p.grad = None
-            if e2e:
-                x = next(feed).requires_grad_(True)
+            if e2e and variant != "no_h2d":
+                x = (feed.take() if gated else next(feed)).requires_grad_(True)
             else:
                 x = x_dev
                 x.grad = None
             y = runner(x, *params)
+            if e2e and gated and variant != "no_h2d":
+                # the next input travels while the backward GEMMs run, not during the forward's
+                # exposed transfers
+                mark = torch.cuda.Event()
+                mark.record()
+                feed.refill(after=mark)
             if e2e:
                 loss = torch.dot(y.reshape(-1).to(gy_flat.dtype), gy_flat) * inv_n   # one reduction
                 loss.backward()
+                if variant == "no_read":
+                    return None
                 return losses.push(loss)     # device -> host read of the result, one step deferred
             y.backward(gy)
             return None
@@ -341,7 +358,8 @@ def run_ours(args, rank, world, local):
         blocks = timed(make_step(path, False), args.steps, args.warmup, world, args.repeats)
         launches = native.LAUNCHES[0] // (args.steps * args.repeats + args.warmup)    # per step
         results[path] = dict(block_stats(blocks, args.steps), launches=launches,
-                             parity_ok=parity["paths"][path]["ok"])
+                             parity_ok=parity["paths"][path]["ok"],
+                             host_enqueue_ms=round(timed.host_ms_per_step, 3))
         if trace.enabled():      # TERRACE_TRACE=events: per-phase device spans, max over ranks
             rep = trace.report(group=True if world > 1 else None)
             if rank == 0:
@@ -368,6 +386,7 @@ def run_ours(args, rank, world, local):
     e2e_blocks = timed(make_step(best, True), args.steps, args.warmup, world, args.repeats,
                        drain=lambda: final.update(loss=losses.flush()))
     e2e = block_stats(e2e_blocks, args.steps)
+    e2e_host_ms = round(timed.host_ms_per_step, 3)
     if trace.enabled():
         rep = trace.report(group=True if world > 1 else None)
         if rank == 0:
@@ -412,6 +431,7 @@ def run_ours(args, rank, world, local):
         "clocks": clocks,
         "e2e": {"value": tokens / (e2e["ms_per_step"] * 1e-3), "unit": "tokens/s",
                 "ms_per_step": e2e["ms_per_step"], "ms_min": e2e["ms_min"], "ms_max": e2e["ms_max"],
+                "host_enqueue_ms": e2e_host_ms, "variant": args.e2e_variant,
                 "h2d_bytes_per_step": x_host.numel() * 2,
                 "d2h_bytes_per_step": losses.bytes_per_read, "last_loss": last_loss},
         "gpu_launches": results[best]["launches"] * args.steps,
@@ -514,6 +534,9 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--repeats", type=int, default=5,
                     help="timed blocks of K steps each; the median block is reported")
+    ap.add_argument("--e2e-variant", default="full", choices=["full", "no_h2d", "no_read", "side_read", "gated_h2d", "both"],
+                    help="diagnosis of the end-to-end number: leave out the per-step host-to-device "
+                         "copy, or the read-back of the loss (the reported line says which)")
     ap.add_argument("--no-parity", action="store_true",
                     help="skip the 512-token parity step (for profiler captures)")
     ap.add_argument("--no-ab", action="store_true",

@@ -17,7 +17,13 @@ The GEMM term is priced from the kernels' measured throughput (long groups, with
 quantisation of short groups and the weight-gradient kernel's epilogue exposure), scaled by the
 SM clock: the kernel figures hold at the clock the kernels reach when timed alone, and a step
 under the 1 kW power cap runs slower the busier it keeps the GPU (1515 MHz on one GPU, where
-nothing ever waits; 1736 MHz on four), so every run carries the median clock sampled during it.  The communication term is the calibrated call model
+nothing ever waits; 1736 MHz on four; 1897 MHz on eight), so every run carries the median
+clock sampled during it.  The GEMM time follows the square root of the clock ratio, not the
+ratio itself: the sampler sees the waits, where the clock recovers, as much as the GEMMs (fit:
+the GEMMs of the one-GPU launch list, 2.63 ms, and of the 4-GPU phase spans, 2.15 ms).  The
+constants that are fitted rather than measured (the two elementwise remainders, the hidden share
+of the return transfer, the two-hop relay) come from the 1-, 2- and 4-GPU runs; the 8-GPU run is
+a prediction.  The communication term is the calibrated call model
 (``calibrate.b200_nvswitch``).  Every measured number is read from a JSON file
 (``sim/data/b200_layer_bench.json`` by default; ``--bench FILE`` takes the lines ``bench.py``
 printed), none is in this source.
@@ -130,7 +136,7 @@ def gemm_ms(n_gpus: int, kern: _Kernels | None = None, sm_mhz: float | None = No
     # weight gradient: its epilogue shows with short groups, 1/T = 1/T_long + c / rows
     c = (1.0 / kern.tflops_wgrad_short - 1.0 / kern.tflops_wgrad_long) * kern.wgrad_short_rows
     wgrad_tflops = 1.0 / (1.0 / kern.tflops_wgrad_long + c / per_expert)
-    derate = kern.gemm_alone_sm_mhz / sm_mhz if sm_mhz else 1.0
+    derate = (kern.gemm_alone_sm_mhz / sm_mhz) ** kern.clock_exponent if sm_mhz else 1.0
     fwd = derate * flops_fwd / (fwd_dgrad_tflops * 1e9)
     bwd = derate * (flops_fwd / (fwd_dgrad_tflops * 1e9) + flops_fwd / (wgrad_tflops * 1e9))
     return {"rows_per_expert": per_expert, "tile_efficiency": eff,
@@ -201,18 +207,22 @@ def validate(verbose: bool = True, bench: dict | None = None):
         rows.append((n, rpn, path, schedule, measured, p["total_ms"], p["gemm_ms"],
                      p["exposed_ms"], p["total_ms"] / measured - 1.0))
     worst = max((abs(r[-1]) for r in rows), default=0.0)
+    fitted = set(bench["kernels"].get("fitted_on_gpus", []))
+    predicted = [abs(r[-1]) for r in rows if r[0] not in fitted]
     ok = bool(rows) and worst <= GATE
     if verbose:
         cols = [Column("GPUs", "%4d", lambda r: r[0]), Column("rpn", "%4d", lambda r: r[1]),
                 Column("path", "%-8s", lambda r: r[2]), Column("schedule", "%-8s", lambda r: r[3]),
                 Column("measured", "%9.2f", lambda r: r[4]), Column("model", "%9.2f", lambda r: r[5]),
                 Column("GEMMs", "%9.2f", lambda r: r[6]), Column("exposed", "%9.2f", lambda r: r[7]),
-                Column("err", "%7s", lambda r: "%+.1f%%" % (100 * r[8]))]
+                Column("err", "%7s", lambda r: "%+.1f%%" % (100 * r[8])),
+                Column("", "%-9s", lambda r: "fitted" if r[0] in fitted else "predicted")]
         print("single-MoE-layer step on B200: model against measurement (ms per step)")
         print("\n".join(render_table(cols, rows)))
-        print("worst error %.1f%% (gate %.0f%%)" % (100 * worst, 100 * GATE))
+        print("worst error %.1f%% (gate %.0f%%); worst of the %d predicted rows %.1f%%"
+              % (100 * worst, 100 * GATE, len(predicted), 100 * max(predicted, default=0.0)))
         print("**B200 step gate %s**" % ("PASS" if ok else "FAIL"))
-    return ok, {"worst": worst, "rows": rows}
+    return ok, {"worst": worst, "rows": rows, "worst_predicted": max(predicted, default=0.0)}
 
 
 def overlap_gain(verbose: bool = True, bench: dict | None = None) -> list:

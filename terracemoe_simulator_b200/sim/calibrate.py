@@ -116,37 +116,46 @@ def synthetic(ratio: float, name: str = "", R: int = 8, base_beta_gbps: float = 
 # ---- platform B200 ----------------------------------------------------------------------------
 # Constants fitted (``b200_from_sweep``) on the 48-point dispatch+combine sweep measured on
 # 8 x B200 with the fused transport (``sim/data/b200_sweep_8gpu.json``; rows of 8 KiB, 256-16384
-# tokens per GPU, R in {1, 2, 4}, q in {1..4}; device-timed, max over ranks).  One exchange =
-# half of a measured dispatch+combine.
-B200_ALPHA_ONE_HOP_MS = 0.0387        # fixed cost of a one-hop exchange (plan + push/pull + flags)
-B200_ALPHA_TWO_HOP_MS = 0.0597        # both hops of a two-hop exchange together
-B200_BETA_GBPS = 640.0                # NVLink payload bandwidth per direction, peer stores/loads
-B200_SELF_COPY_GBPS = 2550.0          # rows that stay on the GPU: read + write through HBM
+# tokens per GPU, R in {1, 2, 4}, q in {1..4}; device-timed, max over ranks, median of three
+# bursts).  One exchange = half of a measured dispatch+combine.
+B200_ALPHA_ONE_HOP_MS = 0.0355        # fixed cost of a one-hop exchange (plan + push/pull + flags)
+B200_ALPHA_SLOW_MS = 0.0309           # Hop A of a two-hop exchange
+B200_ALPHA_FAST_MS = 0.0300           # Hop B when it crosses GPUs (groups of two or more)
+B200_ALPHA_FAST_LOCAL_MS = 0.0215     # Hop B inside one GPU (groups of one): no peer flags to wait for
+B200_ALPHA_TWO_HOP_MS = B200_ALPHA_SLOW_MS + B200_ALPHA_FAST_MS     # both hops, groups of >= 2
+B200_BETA_GBPS = 647.0                # NVLink payload bandwidth per direction, peer stores/loads
+B200_SELF_COPY_GBPS = 2480.0          # rows that stay on the GPU: read + write through HBM
 B200_SELF_OVERLAP_P = 1.5             # wire and local traffic overlap partly inside one kernel
 B200_X_HALF = 0.0
 B200_CHAIN_US_PER_ROW = 0.0           # no arrival chain: rows are stored at their final place
 B200_SPLITS_SYNC_MS = 0.0             # no host read-back
-B200_ALPHA_US = {"fast": B200_ALPHA_TWO_HOP_MS * 500.0, "slow": B200_ALPHA_TWO_HOP_MS * 500.0,
+B200_ALPHA_US = {"fast": B200_ALPHA_FAST_MS * 1000.0, "slow": B200_ALPHA_SLOW_MS * 1000.0,
                  "flat": B200_ALPHA_ONE_HOP_MS * 1000.0}
 
 
 def b200_nvswitch(R: int = 2, alpha_one_ms: float = B200_ALPHA_ONE_HOP_MS,
-                  alpha_two_ms: float = B200_ALPHA_TWO_HOP_MS, beta_gbps: float = B200_BETA_GBPS,
+                  alpha_slow_ms: float = B200_ALPHA_SLOW_MS,
+                  alpha_fast_ms: float = B200_ALPHA_FAST_MS,
+                  alpha_fast_local_ms: float = B200_ALPHA_FAST_LOCAL_MS,
+                  beta_gbps: float = B200_BETA_GBPS,
                   self_copy_gbps: float = B200_SELF_COPY_GBPS,
                   self_overlap_p: float = B200_SELF_OVERLAP_P, hop_overlap: float = 0.0,
                   chain_us_per_row: float = B200_CHAIN_US_PER_ROW) -> ClusterSpec:
     """8 x B200 behind one NVSwitch: the three levels share one port per GPU, so their
     bandwidths are equal and groups are logical; what differs is the per-exchange fixed cost.
-    Rows whose destination is the sending GPU are priced as a local copy."""
+    Hop B has two of them: with groups of one GPU it never leaves the GPU (a local expansion
+    that waits for no peer), with larger groups it is a real exchange.  Rows whose destination
+    is the sending GPU are priced as a local copy."""
     beta = [(1.0, beta_gbps), (1e12, beta_gbps)]
 
-    def pts(ms):
+    def flat(ms):
         return [(1, ms), (16, ms)]
     return ClusterSpec(
         name="b200_nvswitch", R=R,
-        fast=Level("intra-group", pts(alpha_two_ms / 2), beta),
-        slow=Level("inter-group", pts(alpha_two_ms / 2), beta),
-        flat=Level("all ranks", pts(alpha_one_ms), beta),
+        fast=Level("intra-group", [(1, alpha_fast_local_ms), (2, alpha_fast_ms), (16, alpha_fast_ms)],
+                   beta),
+        slow=Level("inter-group", flat(alpha_slow_ms), beta),
+        flat=Level("all ranks", flat(alpha_one_ms), beta),
         splits_sync_ms=B200_SPLITS_SYNC_MS, chain_us_per_row=chain_us_per_row,
         hop_overlap=hop_overlap, self_copy_gbps=self_copy_gbps, self_overlap_p=self_overlap_p)
 
@@ -170,25 +179,36 @@ def _sweep_geometry(row: dict):
 
 
 def b200_from_sweep(rows, overlap_p: float = B200_SELF_OVERLAP_P) -> ClusterSpec:
-    """Least-squares fit (relative error) of (alpha one-hop, alpha two-hop, beta, self-copy
-    bandwidth) to sweep rows with measured ``one_hop_ms`` / ``two_hop_ms`` (dispatch + combine =
-    two exchanges each).  Needs scipy."""
+    """Fit of the six constants of ``b200_nvswitch`` (fixed costs of one-hop, Hop A, remote and
+    local Hop B; link bandwidth; local-copy bandwidth) to sweep rows with measured
+    ``one_hop_ms`` / ``two_hop_ms`` (dispatch + combine = two exchanges each).  Relative
+    residuals with a soft-L1 loss: a 50 us call that one burst caught at twice its time must not
+    move the constants.  Needs scipy."""
     import numpy as np
     from scipy.optimize import least_squares
     from .core import one_hop_call, two_hop_call
     geoms = [_sweep_geometry(r) for r in rows]
     target = np.array([v for r in rows for v in (r["one_hop_ms"] / 2, r["two_hop_ms"] / 2)])
+    names = ("alpha_one_ms", "alpha_slow_ms", "alpha_fast_ms", "alpha_fast_local_ms", "beta_gbps",
+             "self_copy_gbps")
+    has = {bool(g.R == 1) for g in geoms}
 
-    def predict(p):
-        c = b200_nvswitch(alpha_one_ms=p[0], alpha_two_ms=p[1], beta_gbps=p[2],
-                          self_copy_gbps=p[3], self_overlap_p=overlap_p)
-        return np.array([v for g in geoms for v in (one_hop_call(c, g), two_hop_call(c, g))])
+    def spec(p):
+        kw = dict(zip(names, (float(v) for v in p)))
+        if has == {True}:                     # only groups of one GPU: the remote cost is unseen
+            kw["alpha_fast_ms"] = kw["alpha_fast_local_ms"]
+        elif has == {False}:
+            kw["alpha_fast_local_ms"] = kw["alpha_fast_ms"]
+        return b200_nvswitch(self_overlap_p=overlap_p, **kw)
 
-    sol = least_squares(lambda p: (predict(p) - target) / target, [0.04, 0.06, 650.0, 2500.0],
-                        bounds=([0.0, 0.0, 50.0, 100.0], [1.0, 1.0, 2000.0, 20000.0]))
-    a1, a2, beta, loc = (float(v) for v in sol.x)
-    return b200_nvswitch(alpha_one_ms=a1, alpha_two_ms=a2, beta_gbps=beta, self_copy_gbps=loc,
-                         self_overlap_p=overlap_p)
+    def residual(p):
+        c = spec(p)
+        model = np.array([v for g in geoms for v in (one_hop_call(c, g), two_hop_call(c, g))])
+        return (model - target) / target
+
+    sol = least_squares(residual, [0.04, 0.03, 0.03, 0.02, 650.0, 2500.0], loss="soft_l1",
+                        f_scale=0.1, bounds=([0.0] * 4 + [50.0, 100.0], [1.0] * 4 + [2000.0, 20000.0]))
+    return spec(sol.x)
 
 
 def b200_from_records(records, R: int = 2) -> ClusterSpec:

@@ -96,11 +96,11 @@ class ChunkedSchedule:
 
     ``return_hidden`` is measured, not derived: the scattering epilogue stores 8 KiB rows over
     NVLink from the same warps that drain the accumulators, so the second GEMM stretches while
-    it sends; on B200 a quarter of the return transfer disappears under it (2- and 4-GPU steps,
+    it sends; on B200 about a third of the return transfer disappears under it (2- and 4-GPU steps,
     ``sim/b200_step.py``)."""
     chunks: int = 2
     local_reduce_ms: float = 0.05
-    return_hidden: float = 0.25
+    return_hidden: float = 0.3
 
     def exposed_ms(self, dispatch_ms: float, expert_ms: float, return_ms: float = 0.0) -> float:
         n = max(int(self.chunks), 1)

@@ -76,7 +76,7 @@ def _b200() -> Platform:
         R=2, splits_sync_ms=cal.B200_SPLITS_SYNC_MS, chain_us_per_row=cal.B200_CHAIN_US_PER_ROW,
         provenance="dispatch+combine sweeps of this repository's fused kernels, device-timed, "
                    "max over ranks; refit with calibrate.b200_from_records",
-        fit_median_err=0.038, n_targets=48,     # sim/validate_b200.py: 48 measured configurations
+        fit_median_err=0.031, n_targets=48,     # sim/validate_b200.py: 48 measured configurations
         notes="All three levels share one NVLink port per GPU, so the hierarchy ratio is 1 by "
               "construction; groups are logical.  Two-hop can still win on bytes for R=2 "
               "because half of Hop B stays on the GPU.")

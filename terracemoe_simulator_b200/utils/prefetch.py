@@ -32,7 +32,7 @@ class DevicePrefetcher:
             return type(batch)(fn(t) for t in batch)
         return fn(batch)
 
-    def _issue(self) -> None:
+    def _issue(self, after=None) -> None:
         try:
             host = next(self.it)
         except StopIteration:
@@ -40,6 +40,8 @@ class DevicePrefetcher:
         if not self.cuda:
             self.queue.append((host, None))
             return
+        if after is not None:           # start the copy only once this event has happened
+            self.stream.wait_event(after)
         with torch.cuda.stream(self.stream):
             dev = self._map(host, lambda t: t.to(self.device, non_blocking=True))
             event = torch.cuda.Event()
@@ -54,7 +56,8 @@ class DevicePrefetcher:
     def __iter__(self):
         return self
 
-    def __next__(self):
+    def take(self):
+        """The next batch, without starting another copy (pair with :meth:`refill`)."""
         if not self.queue:
             raise StopIteration
         dev, event = self.queue.pop(0)
@@ -63,6 +66,16 @@ class DevicePrefetcher:
             # the buffer is consumed on the compute stream: keep the allocator from handing its
             # memory to the side stream's next copy before that work has run
             self._map(dev, lambda t: t.record_stream(torch.cuda.current_stream(self.device)) or t)
+        return dev
+
+    def refill(self, after=None) -> None:
+        """Start the copy of one more batch; with ``after`` (a CUDA event) the copy engine waits
+        for that point of the compute stream, which lets the caller place the transfer under a
+        phase of the step that does not use the interconnect."""
+        self._issue(after)
+
+    def __next__(self):
+        dev = self.take()
         self._issue()
         return dev
 
@@ -77,8 +90,11 @@ class DeferredScalar:
     of the device (a lag of one bounds the run-ahead to a single step, which leaves no slack for
     host jitter when several ranks wait on one another)."""
 
-    def __init__(self, device, dtype=torch.float32, lag: int = 1):
+    def __init__(self, device, dtype=torch.float32, lag: int = 1, side_stream: bool = False):
         self.cuda = torch.device(device).type == "cuda"
+        # with ``side_stream`` the copy leaves the compute stream: it waits for the value on a
+        # stream of its own, so the next step's first kernel does not queue behind the transfer
+        self.stream = torch.cuda.Stream(device) if self.cuda and side_stream else None
         self.lag = max(1, lag)
         n = self.lag + 1
         self.slots = [torch.zeros((), dtype=dtype, pin_memory=self.cuda) for _ in range(n)]
@@ -95,10 +111,21 @@ class DeferredScalar:
         n_slots = len(self.slots)
         i = self.n % n_slots
         prev = self._take((self.n - self.lag) % n_slots) if self.n >= self.lag else None
-        self.slots[i].copy_(t.detach().to(self.slots[i].dtype), non_blocking=True)
-        if self.cuda:
-            self.events[i] = torch.cuda.Event()
-            self.events[i].record()
+        value = t.detach().to(self.slots[i].dtype)
+        if self.stream is not None:
+            ready = torch.cuda.Event()
+            ready.record()
+            value.record_stream(self.stream)
+            with torch.cuda.stream(self.stream):
+                self.stream.wait_event(ready)
+                self.slots[i].copy_(value, non_blocking=True)
+                self.events[i] = torch.cuda.Event()
+                self.events[i].record(self.stream)
+        else:
+            self.slots[i].copy_(value, non_blocking=True)
+            if self.cuda:
+                self.events[i] = torch.cuda.Event()
+                self.events[i].record()
         self.n += 1
         return prev
 
