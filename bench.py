@@ -23,8 +23,10 @@ that fails the check is reported and not used for the headline.  With more than 
 remote-read schedule (``TERRACE_EP_OVERLAP=0``) is timed beside the default overlap schedule as
 the A/B arm (``paths.*_pull``).
 The ``e2e`` entry repeats the measurement through the public API with a pinned-host -> device
-copy of the step's tokens (issued one step ahead on a side stream by the package's
-``DevicePrefetcher``) and a device -> host read of every step's loss inside the timed region
+copy of every step's tokens (on a side stream, two steps ahead, by the package's
+``DevicePrefetcher``; each copy starts where the previous backward's NVLink traffic pauses,
+``FusedEPContext.link_quiet_event``, because a PCIe copy beside the peer-memory pushes slows
+them) and a device -> host read of every step's loss inside the timed region
 (``DeferredScalar``: a non-blocking copy to pinned memory, consumed three steps later, so the host
 keeps launching ahead of the device; the last value is read before the closing synchronize).
 ``--impl reference`` runs the unmodified reference (``baseline/_ref``: a plain copy of its
@@ -315,33 +317,35 @@ def run_ours(args, rank, world, local):
     feed = DevicePrefetcher(itertools.cycle(host_batches), device)
     variant = args.e2e_variant
     # every step's loss is read on the host, 3 steps late
-    losses = DeferredScalar(device, lag=3, side_stream=variant in ("side_read", "both"))
-    gated = variant in ("gated_h2d", "both")
+    losses = DeferredScalar(device, lag=3)
 
     def make_step(path, e2e: bool):
         runner = runners[path]
+        quiet = getattr(getattr(runner, "ctx", None), "link_quiet_event", lambda: None)
 
         def step():
             for p in params:
                 p.grad = None
-            if e2e and variant != "no_h2d":
-                x = (feed.take() if gated else next(feed)).requires_grad_(True)
-            else:
+            if not e2e or variant == "no_h2d":
                 x = x_dev
                 x.grad = None
+            elif variant == "ungated":
+                x = next(feed).requires_grad_(True)         # takes a batch, starts the next copy
+            else:
+                x = feed.take().requires_grad_(True)
             y = runner(x, *params)
-            if e2e and gated and variant != "no_h2d":
-                # the next input travels while the backward GEMMs run, not during the forward's
-                # exposed transfers
-                mark = torch.cuda.Event()
-                mark.record()
-                feed.refill(after=mark)
             if e2e:
                 loss = torch.dot(y.reshape(-1).to(gy_flat.dtype), gy_flat) * inv_n   # one reduction
                 loss.backward()
+                if variant in ("default", "no_read"):
+                    # A PCIe copy that runs beside the peer-memory pushes slows them (measured:
+                    # +0.35 ms per step on 4 GPUs).  The copy of a later input therefore waits
+                    # for the point of this backward where the NVLink traffic pauses -- the
+                    # weight-gradient GEMMs -- and travels under them.
+                    feed.refill(after=quiet())
                 if variant == "no_read":
                     return None
-                return losses.push(loss)     # device -> host read of the result, one step deferred
+                return losses.push(loss)     # device -> host read of the result, a few steps late
             y.backward(gy)
             return None
         return step
@@ -534,9 +538,12 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--repeats", type=int, default=5,
                     help="timed blocks of K steps each; the median block is reported")
-    ap.add_argument("--e2e-variant", default="full", choices=["full", "no_h2d", "no_read", "side_read", "gated_h2d", "both"],
-                    help="diagnosis of the end-to-end number: leave out the per-step host-to-device "
-                         "copy, or the read-back of the loss (the reported line says which)")
+    ap.add_argument("--e2e-variant", default="default",
+                    choices=["default", "ungated", "no_h2d", "no_read"],
+                    help="diagnosis of the end-to-end number (the reported line says which): "
+                         "ungated = start every host-to-device copy at once instead of under the "
+                         "weight-gradient GEMMs; no_h2d / no_read = leave out the per-step copy / "
+                         "the read-back of the loss")
     ap.add_argument("--no-parity", action="store_true",
                     help="skip the 512-token parity step (for profiler captures)")
     ap.add_argument("--no-ab", action="store_true",

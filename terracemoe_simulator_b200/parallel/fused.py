@@ -257,6 +257,21 @@ class FusedEPContext:
         self.epoch += 1
         return self.epoch
 
+    def mark_link_quiet(self) -> None:
+        """Called by the backward pass where the longest stretch without NVLink traffic begins
+        (the last dispatched gradient rows have arrived; the weight-gradient GEMMs follow)."""
+        if self.device.type != "cuda":
+            return
+        if getattr(self, "_quiet", None) is None:
+            self._quiet = torch.cuda.Event()
+        self._quiet.record(torch.cuda.current_stream(self.device))
+
+    def link_quiet_event(self):
+        """CUDA event of the latest ``mark_link_quiet`` (None before the first backward): work on
+        other streams that would compete with the peer traffic -- a host-to-device copy of the
+        next input, for one -- can wait for it and run under the weight-gradient GEMMs."""
+        return getattr(self, "_quiet", None)
+
     def check_mode(self, mode: str) -> None:
         if mode == "one_hop" and not self.one_hop_ok:
             raise ValueError("this context was built for two_hop only (modes=('two_hop',)): its "
@@ -565,6 +580,8 @@ class _FusedMoE(torch.autograd.Function):
                     lib.grouped_gemm_ex(dout, w2c[lo:hi], dh13, h13, ss[lo:hi], sc[lo:hi], 1, 3,
                                         fctx.arena, FK_B_DATA, first, n, flag_value(ep, i, nch),
                                         SEG_ALIGN)
+                    if i == nch - 1:
+                        fctx.mark_link_quiet()      # every dY row has arrived; two wgrad GEMMs follow
                     lib.grouped_wgrad_out(act, dout, dw2, lo, ss[lo:hi], sc[lo:hi], 0, SEG_ALIGN)
                 dw13 = lib.grouped_wgrad(xin, dh13, ss, sc, 0, SEG_ALIGN)
                 base, slots = ((fctx.dret_base, fctx.ret_slots) if mode == "one_hop"
@@ -574,6 +591,7 @@ class _FusedMoE(torch.autograd.Function):
             else:
                 lib.grouped_gemm_ex(dout, w2c, dh13, h13, ss, sc, 1, 3, fctx.arena, FK_B_DATA,
                                     first, n, flag_value(ep, 0, 1), SEG_ALIGN)
+                fctx.mark_link_quiet()
                 dw2 = lib.grouped_wgrad(act, dout, ss, sc, 0, SEG_ALIGN)
                 dw13 = lib.grouped_wgrad(xin, dh13, ss, sc, 0, SEG_ALIGN)
                 lib.grouped_gemm_ex(dh13, w13c, fctx.section(DXS), None, ss, sc, 1, 0, None, 0, 0,
