@@ -85,10 +85,13 @@ def main(argv=None) -> int:
     def step():
         for p in layer.parameters():
             p.grad = None
-        x = next(feed).requires_grad_(True)
+        x = feed.take().requires_grad_(True)
         y, _ = layer(x)
         loss = (y.float() * gy.float()).mean()
         loss.backward()
+        # the copy of a later input travels under this backward's weight-gradient GEMMs, where
+        # the NVLink traffic pauses (a PCIe copy beside the peer-memory pushes slows them)
+        feed.refill(after=layer.link_quiet_event())
         prev = losses.push(loss)
         if prev is not None:
             last["loss"] = prev

@@ -233,6 +233,13 @@ class EPTerracedMoE(nn.Module):
             self._ctx = None
         self._build_context(tokens, device)
 
+    def link_quiet_event(self):
+        """CUDA event at which the latest backward's NVLink traffic paused (see
+        ``FusedEPContext.link_quiet_event``); None without a fused context or before the first
+        backward.  A host-to-device copy for a later step should wait for it."""
+        ctx = getattr(self, "_ctx", None)
+        return getattr(ctx, "link_quiet_event", lambda: None)() if ctx is not None else None
+
     def check_status(self) -> int:
         """Read and clear the device status word (one host synchronisation); raises when a kernel
         reported a problem, e.g. routed rows beyond ``row_capacity_factor``."""
