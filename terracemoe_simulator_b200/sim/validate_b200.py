@@ -16,7 +16,12 @@ relative error of the ratio within 10 %.  The stricter reading -- every single r
 is reported beside it and does not hold: the rows beyond it are 256- and 1024-token calls of
 50-200 us, where one slow burst moves the measured ratio by more than that (one such row of the
 8-GPU sweep, R = 2, q = 1, 256 tokens, was caught at twice the time of its neighbours and is
-kept in the data).  It is the B200 counterpart of the reference's measured two-hop check
+kept in the data).  A fourth line per group size scores the other calibration route
+(``calibrate.b200_from_records``: one fixed cost and one bandwidth curve per level, fitted with
+``fit.fit_beta_pinned`` to the ``flat`` / ``slow`` / ``fast`` frames of the sweep).  It is the
+recipe for a machine where only collective-style exchanges can be timed, and on this transport it
+is the worse model (median 9-13 %): a frame is a whole one-hop exchange on the level's peer set,
+plan and flags included, while Hop A and Hop B share one plan.  It is reported, not gated.  It is the B200 counterpart of the reference's measured two-hop check
 (``sim/twohop_measured.py``), whose model error was 14 % in the median.
 """
 from __future__ import annotations
@@ -92,6 +97,18 @@ def validate_b200(cluster=None, rows=None, verbose: bool = True):
         if os.path.isfile(sweep_path(n)):
             other = cal.load_b200_sweep(sweep_path(n))
             report["cross_size"][n] = score(shipped, other)
+    # the other calibration route: one alpha and one saturating beta per level from the
+    # ``flat`` / ``slow`` / ``fast`` frames of the same sweep file (fit.fit_beta_pinned), scored
+    # on the rows whose group size the frames were measured with
+    report["per_level"] = {}
+    try:
+        records = cal.load_b200_records()
+    except (OSError, KeyError):
+        records = []
+    for R in sorted({r.get("R") for r in records if r.get("frame") in ("slow", "fast")} - {None}):
+        subset = [r for r in rows if r["R"] == R]
+        if subset:
+            report["per_level"][R] = score(cal.b200_from_records(records, R=R), subset)
     predictions = [s for s in [report["holdout"], *report["cross_size"].values()] if s]
     ok = bool(predictions) and all(_passes(s) for s in predictions)
     report["every_row"] = bool(predictions) and all(_every_row(s) for s in predictions)
@@ -118,6 +135,8 @@ def _lines(report, n_train, ok) -> list:
     for n, s in sorted(report["cross_size"].items()):
         out.append(line("cross-size: %d-GPU sweep" % n, s))
     small = sum(1 for _r, _q, tok, _e in report["beyond"] if tok <= 1024)
+    for R, s in sorted(report.get("per_level", {}).items()):
+        out.append(line("per-level frames, groups of %d" % R, s))
     out.append("gate on the predictions: median within %.0f %%" % (100 * GATE_MEDIAN))
     out.append("**B200 gate %s**" % ("PASS" if ok else "FAIL"))
     out.append("every predicted row within %.0f %%: %s (%d rows beyond, %d of them at 1024 tokens "
