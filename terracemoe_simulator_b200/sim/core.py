@@ -16,7 +16,6 @@ Parity with the reference ``sim/core.py``: ``Level`` :21-60, ``ClusterSpec`` :63
 """
 from __future__ import annotations
 
-import bisect
 import math
 from dataclasses import dataclass, field
 
@@ -24,21 +23,21 @@ OPERATING_POINT_BYTES = 8 * 2 ** 20     # where ClusterSpec.ratio() compares the
 
 
 def _interp(points, x: float, logx: bool = False) -> float:
-    """Piecewise-linear lookup in ``[(x, y), ...]`` (ascending x), clamped at both ends."""
+    """Piecewise-linear lookup in ``[(x, y), ...]`` (ascending x), clamped at both ends;
+    ``logx`` interpolates along log(x)."""
     if not points:
         raise ValueError("empty interpolation table: the level was never calibrated")
-    xs = [p[0] for p in points]
-    if x <= xs[0]:
-        return points[0][1]
-    if x >= xs[-1]:
-        return points[-1][1]
-    hi = bisect.bisect_right(xs, x)
-    (x0, y0), (x1, y1) = points[hi - 1], points[hi]
-    if logx:
-        w = (math.log(x) - math.log(x0)) / (math.log(x1) - math.log(x0))
-    else:
-        w = (x - x0) / (x1 - x0)
-    return y0 + w * (y1 - y0)
+    first, last = points[0], points[-1]
+    if not x > first[0]:
+        return first[1]
+    if not x < last[0]:
+        return last[1]
+    axis = math.log if logx else float
+    for (xa, ya), (xb, yb) in zip(points, points[1:]):
+        if xa <= x <= xb:
+            t = (axis(x) - axis(xa)) / (axis(xb) - axis(xa))
+            return ya + t * (yb - ya)
+    return last[1]
 
 
 @dataclass
@@ -53,6 +52,10 @@ class Level:
 
     def beta_gbps(self, per_peer_bytes: float) -> float:
         return _interp(self.beta_pts, per_peer_bytes, logx=True)
+
+    def peak_gbps(self) -> float:
+        """Bandwidth of the largest tabulated message."""
+        return self.beta_gbps(math.inf)
 
 
 @dataclass
@@ -73,8 +76,13 @@ class ClusterSpec:
     self_overlap_p: float = 1.0         # wire and local copy combine as (w^p + l^p)^(1/p)
 
     def ratio(self) -> float:
-        p = OPERATING_POINT_BYTES
-        return self.fast.beta_gbps(p) / self.slow.beta_gbps(p)
+        at = OPERATING_POINT_BYTES
+        return self.fast.beta_gbps(at) / self.slow.beta_gbps(at)
+
+    def price(self, level: Level, world: int, rows: float, row_bytes: int, stays: float) -> float:
+        """One exchange on ``level`` with this machine's combination rules."""
+        return _a2a_ms(level, world, rows, row_bytes, stays, self.combine_exponent,
+                       self.per_peer_us, self.self_copy_gbps, self.self_overlap_p)
 
 
 @dataclass
@@ -93,96 +101,98 @@ class MoEGeometry:
 
     @property
     def q(self) -> int:
-        if self.k % self.M:
+        quota, rest = divmod(self.k, self.M)
+        if rest:
             raise ValueError(f"k={self.k} is not a multiple of M={self.M}")
-        return self.k // self.M
+        return quota
 
     @property
     def ep(self) -> int:
-        return self.n_groups * self.R
+        return self.R * self.n_groups
 
     @property
     def tokens_per_rank(self) -> int:
-        return self.seq * self.mbs
+        return self.mbs * self.seq
 
     @property
     def microbatches(self) -> int:
-        per_pass = self.ep * self.mbs
-        if self.gbs % per_pass:
-            raise ValueError(f"gbs={self.gbs} is not divisible by ep*mbs={per_pass}")
-        return self.gbs // per_pass
-
-    def calls_per_step_fwd(self) -> int:
-        return self.moe_layers * self.microbatches * 2
+        count, rest = divmod(self.gbs, self.mbs * self.ep)
+        if rest:
+            raise ValueError(f"gbs={self.gbs} is not divisible by ep*mbs={self.mbs * self.ep}")
+        return count
 
     def calls_per_step_bwd(self) -> int:
-        return self.moe_layers * self.microbatches
+        return self.microbatches * self.moe_layers
+
+    def calls_per_step_fwd(self) -> int:                 # dispatch and combine
+        return 2 * self.calls_per_step_bwd()
 
     def row_bytes(self) -> int:
-        return self.H * self.bytes_per_elem
+        return self.bytes_per_elem * self.H
 
-    def rows_one_hop(self) -> int:
-        return self.tokens_per_rank * self.k
+    def rows_hop_a(self) -> int:                         # one row per (token, chosen group)
+        return self.M * self.tokens_per_rank
 
-    def rows_hop_a(self) -> int:
-        return self.tokens_per_rank * self.M
+    def rows_hop_b(self) -> int:                         # one row per (token, pick)
+        return self.k * self.tokens_per_rank
 
-    def rows_hop_b(self) -> int:
-        return self.tokens_per_rank * self.k
+    rows_one_hop = rows_hop_b
+
+
+def _p_norm(a: float, b: float, p: float) -> float:
+    """(a^p + b^p)^(1/p): the plain sum at p = 1, towards max(a, b) as p grows."""
+    return a + b if p == 1.0 else (a ** p + b ** p) ** (1.0 / p)
 
 
 def _a2a_ms(level: Level, world: int, total_rows: float, row_bytes: int, self_fraction: float,
             combine_exponent: float = 1.0, per_peer_us: float = 0.0, self_copy_gbps: float = 0.0,
             self_overlap_p: float = 1.0) -> float:
-    wire_bytes = total_rows * (1.0 - self_fraction) * row_bytes
-    peers = max(world - 1, 1)
-    alpha = level.alpha_ms(world)
-    if wire_bytes <= 0.0:
-        transfer = 0.0
-    elif per_peer_us > 0.0:
-        transfer = wire_bytes / (level.beta_gbps(1e12) * 1e6) + (world - 1) * per_peer_us / 1000.0
-    else:
-        transfer = wire_bytes / (level.beta_gbps(wire_bytes / peers) * 1e6)
+    """Time of one all-to-all: fixed cost + bytes on the wire over the bandwidth at the per-peer
+    message size (or over the peak bandwidth plus an explicit per-message cost), the rows that
+    stay on the rank optionally priced as a local copy that partly overlaps the wire."""
+    payload = row_bytes * total_rows
+    on_wire = payload * (1.0 - self_fraction)
+    wire_ms = 0.0
+    if on_wire > 0.0:
+        if per_peer_us > 0.0:
+            wire_ms = on_wire / (1e6 * level.peak_gbps()) + 1e-3 * per_peer_us * (world - 1)
+        else:
+            per_peer = on_wire / max(1, world - 1)
+            wire_ms = on_wire / (1e6 * level.beta_gbps(per_peer))
     if self_copy_gbps > 0.0:
-        local = total_rows * self_fraction * row_bytes / (self_copy_gbps * 1e6)
-        p = self_overlap_p
-        transfer = (transfer ** p + local ** p) ** (1.0 / p)
-    if combine_exponent == 1.0:
-        return alpha + transfer
-    p = combine_exponent
-    return (alpha ** p + transfer ** p) ** (1.0 / p)
+        local_ms = payload * self_fraction / (1e6 * self_copy_gbps)
+        wire_ms = _p_norm(wire_ms, local_ms, self_overlap_p)
+    return _p_norm(level.alpha_ms(world), wire_ms, combine_exponent)
 
 
 def one_hop_call(c: ClusterSpec, g: MoEGeometry) -> float:
-    return _a2a_ms(c.flat, g.ep, g.rows_one_hop(), g.row_bytes(), 1.0 / g.ep,
-                   c.combine_exponent, c.per_peer_us, c.self_copy_gbps, c.self_overlap_p)
+    return c.price(c.flat, g.ep, g.rows_one_hop(), g.row_bytes(), 1.0 / g.ep)
 
 
 def hop_a_self_fraction(g: MoEGeometry) -> float:
     """A token emits M Hop A rows of which M/N_g are expected to stay in its own group."""
-    return 1.0 / g.n_groups if g.n_groups > 1 else 1.0
+    return 1.0 / max(g.n_groups, 1)
 
 
 def two_hop_parts(c: ClusterSpec, g: MoEGeometry) -> dict:
-    hop_a = _a2a_ms(c.slow, g.n_groups, g.rows_hop_a(), g.row_bytes(), hop_a_self_fraction(g),
-                    c.combine_exponent, c.per_peer_us, c.self_copy_gbps, c.self_overlap_p)
-    hop_b = _a2a_ms(c.fast, g.R, g.rows_hop_b(), g.row_bytes(), 1.0 / g.R,
-                    c.combine_exponent, c.per_peer_us, c.self_copy_gbps, c.self_overlap_p)
-    chain = c.chain_us_per_row * g.rows_hop_b() / 1000.0
-    return {"hop_a": hop_a, "hop_b": hop_b, "splits": c.splits_sync_ms, "chain": chain}
+    pairs = g.rows_hop_b()
+    return {"hop_a": c.price(c.slow, g.n_groups, g.rows_hop_a(), g.row_bytes(),
+                             hop_a_self_fraction(g)),
+            "hop_b": c.price(c.fast, g.R, pairs, g.row_bytes(), 1.0 / g.R),
+            "splits": c.splits_sync_ms, "chain": 1e-3 * c.chain_us_per_row * pairs}
 
 
 def two_hop_call(c: ClusterSpec, g: MoEGeometry) -> float:
-    p = two_hop_parts(c, g)
-    serial = p["hop_a"] + p["hop_b"]
-    hops = serial - c.hop_overlap * min(p["hop_a"], p["hop_b"])
-    return hops + p["splits"] + p["chain"]
+    part = two_hop_parts(c, g)
+    hidden = c.hop_overlap * min(part["hop_a"], part["hop_b"])
+    return part["hop_a"] + part["hop_b"] - hidden + part["splits"] + part["chain"]
 
 
 def step_delta(c: ClusterSpec, g: MoEGeometry) -> dict:
     """Communication time two-hop minus one-hop for a whole training step: dispatch and combine
     mirror each other (x2), backward replays the forward exchanges at half the call count."""
-    on, off = two_hop_call(c, g), one_hop_call(c, g)
-    calls = 2 * (g.calls_per_step_fwd() + g.calls_per_step_bwd())
-    return {"per_call_on_ms": on, "per_call_off_ms": off, "per_call_delta_ms": on - off,
-            "calls_per_step": calls, "step_delta_ms": (on - off) * calls}
+    per_call = {"per_call_on_ms": two_hop_call(c, g), "per_call_off_ms": one_hop_call(c, g)}
+    gap = per_call["per_call_on_ms"] - per_call["per_call_off_ms"]
+    n_calls = 2 * (g.calls_per_step_bwd() + g.calls_per_step_fwd())
+    return {**per_call, "per_call_delta_ms": gap, "calls_per_step": n_calls,
+            "step_delta_ms": n_calls * gap}

@@ -130,6 +130,27 @@ def test_device_prefetcher_passthrough_and_order():
     assert [int(next(feed)[0, 0]) for _ in range(7)] == [0, 1, 2, 3, 4, 0, 1]
 
 
+def test_device_prefetcher_take_and_refill_keep_the_order():
+    """take() hands out the next batch without starting a copy; refill() starts one (on a CPU
+    device the ``after`` event is ignored): the order of batches does not change."""
+    import itertools
+    import torch
+    from terracemoe_simulator_b200.utils.prefetch import DevicePrefetcher
+    batches = [torch.full((2,), float(i)) for i in range(4)]
+    feed = DevicePrefetcher(itertools.cycle(batches), "cpu", depth=2)
+    seen = []
+    for _ in range(6):
+        seen.append(int(feed.take()[0]))
+        assert len(feed.queue) == 1
+        feed.refill(after=None)
+        assert len(feed.queue) == 2
+    assert seen == [0, 1, 2, 3, 0, 1]
+    short = DevicePrefetcher(batches[:2], "cpu", depth=2)
+    short.take(), short.take()
+    with pytest.raises(StopIteration):
+        short.take()
+
+
 def test_deferred_scalar_reads_every_value_one_step_late():
     import torch
     from terracemoe_simulator_b200.utils.prefetch import DeferredScalar
@@ -140,6 +161,9 @@ def test_deferred_scalar_reads_every_value_one_step_late():
     d3 = DeferredScalar("cpu", lag=3)
     out = [d3.push(torch.tensor(float(i))) for i in range(6)]
     assert out == [None, None, None, 0.0, 1.0, 2.0] and d3.flush() == 5.0
+    side = DeferredScalar("cpu", lag=2, side_stream=True)        # no stream on a CPU device
+    assert side.stream is None
+    assert [side.push(torch.tensor(float(i))) for i in range(4)] == [None, None, 0.0, 1.0]
 
 
 def test_route_results_record_is_consistent():

@@ -515,6 +515,28 @@ def test_device_prefetcher_on_gpu(native_ops):
     assert feed.copied_bytes >= 9 * 4 * 1024 * 1024
 
 
+def test_prefetcher_refill_after_an_event_and_side_stream_readback(native_ops):
+    """A copy gated on a compute-stream event still delivers the batches in order, and a value
+    read back on its own stream equals the one read on the compute stream."""
+    import itertools
+    from terracemoe_simulator_b200.utils.prefetch import DeferredScalar, DevicePrefetcher
+    host = [torch.full((512, 512), float(i)).pin_memory() for i in range(3)]
+    feed = DevicePrefetcher(itertools.cycle(host), DEV, depth=2)
+    plain, side = DeferredScalar(DEV, lag=2), DeferredScalar(DEV, lag=2, side_stream=True)
+    got_plain, got_side = [], []
+    for step in range(8):
+        x = feed.take()
+        y = (x @ torch.eye(512, device=DEV)).sum() / (512 * 512)
+        mark = torch.cuda.Event()
+        mark.record()
+        feed.refill(after=mark)
+        got_plain.append(plain.push(y))
+        got_side.append(side.push(y))
+    want = [None, None] + [float(i % 3) for i in range(6)]
+    assert got_plain == want and got_side == want
+    assert plain.flush() == side.flush() == float(7 % 3)
+
+
 def test_graphed_moe_forward_matches_eager(native_ops):
     """One captured CUDA graph serves any routing: replays equal eager calls bit for bit."""
     from terracemoe_simulator_b200.layer import TerracedMoE
