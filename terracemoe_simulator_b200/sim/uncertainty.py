@@ -49,12 +49,20 @@ class Shape(NamedTuple):
         k = k_base if k_base >= q and k_base % q == 0 else q
         return cls(R=R, k=k, M=max(1, k // q), tok=tok)
 
+    def geometry(self) -> MoEGeometry:
+        extra = {} if self.H is None else {"H": self.H}
+        return MoEGeometry(name="u", n_groups=self.n_groups, R=self.R, k=self.k, M=self.M,
+                           seq=self.tok, mbs=1, gbs=self.n_groups * self.R * self.tok, **extra)
+
+    def calls(self, cluster) -> tuple:
+        """(one-hop ms, two-hop ms) of one dispatch on ``cluster``."""
+        geom = self.geometry()
+        return one_hop_call(cluster, geom), two_hop_call(cluster, geom)
+
     def speedup(self, cluster) -> float:
         """one-hop time / two-hop time of one dispatch on ``cluster`` (> 1: two-hop is faster)."""
-        extra = {} if self.H is None else {"H": self.H}
-        geom = MoEGeometry(name="u", n_groups=self.n_groups, R=self.R, k=self.k, M=self.M,
-                           seq=self.tok, mbs=1, gbs=self.n_groups * self.R * self.tok, **extra)
-        return one_hop_call(cluster, geom) / two_hop_call(cluster, geom)
+        one, two = self.calls(cluster)
+        return one / two
 
 
 def _speedup(cluster, q: int, tok: int, k_base: int = 6) -> float:
