@@ -8,7 +8,7 @@ generators (``tools/gen_figures.py``, ``tools/gen_route_figures.py``, ``tools/ge
 published routing results (f1-f6, data in `tools/route_results.py`), cost-model figures computed
 live (f7-f11, f13, f16), the one-sided comparison from the B200 sweep (f12), routing
 figures computed live from ``routing.t_route`` (f14, f15), plus two figures of this package's own
-measurements on 8 x B200 (f17 measured against modelled two-hop/one-hop ratio, f18 dispatch +
+measurements on 8 x B200 (f19 layer step against its model, f17 measured against modelled two-hop/one-hop ratio, f18 dispatch +
 combine time against tokens per GPU).
 """
 from __future__ import annotations
@@ -255,6 +255,33 @@ def f18_b200_dispatch():
     return c.render()
 
 
+def f19_b200_step():
+    """The layer step on 1-8 GPUs: both schedules, one-hop and two-hop, measured against the
+    step model (constants fitted on 1-4 GPUs, 8 GPUs predicted)."""
+    from ..sim import b200_step
+    bench = b200_step.load_bench()
+    steps = b200_step.measured_steps(bench)
+    c = Chart("f19  B200: single-MoE-layer step, measured (solid) and modelled (dotted)",
+              "GPUs", "ms per step (max over ranks)")
+    arms = (("one_hop", "overlap", "#1f77b4"), ("two_hop", "overlap", "#d62728"),
+            ("one_hop", "serial", "#7fb2dd"), ("two_hop", "serial", "#eb9a9a"))
+    for path, schedule, color in arms:
+        pts = sorted((n, rpn, ms) for (n, rpn, p, s), ms in steps.items()
+                     if p == path and s == schedule)
+        if not pts:
+            continue
+        xs = [n for n, _rpn, _ms in pts]
+        c.line(xs, [ms for _n, _rpn, ms in pts], label="%s, %s" % (path.replace("_", "-"), schedule),
+               color=color)
+        c.line(xs, [b200_step.predict_ms(n, rpn, path, schedule, bench=bench)["total_ms"]
+                    for n, rpn, _ms in pts], label=None, color=color, dash="1,4", marker=False)
+    local = steps.get((1, 1, "local", "serial"))
+    if local is not None:
+        c.note("1 GPU (local kernels): %.2f ms measured, %.2f modelled"
+               % (local, b200_step.predict_ms(1, 1, "local", "serial", bench=bench)["total_ms"]))
+    return c.render()
+
+
 FIGURES = {
     "f1-loss-axis": f1_loss_axis, "f2-per-seed": f2_per_seed, "f3-downstream": f3_downstream,
     "f4-load-axis": f4_load_axis, "f5-step-neutral": f5_step_neutral,
@@ -265,7 +292,7 @@ FIGURES = {
     "f13-platform-map": f13_platform_map,
     "f14-routing-modes": f14_routing_modes, "f15-routing-costs": f15_routing_costs,
     "f16-launch-cost": f16_launch_cost, "f17-b200-ratio": f17_b200_ratio,
-    "f18-b200-dispatch": f18_b200_dispatch,
+    "f18-b200-dispatch": f18_b200_dispatch, "f19-b200-step": f19_b200_step,
 }
 
 
