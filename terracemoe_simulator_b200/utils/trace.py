@@ -11,8 +11,9 @@ device call.  On a CPU the ``events`` mode falls back to ``perf_counter``.
 
 The events are recorded on the stream the work runs on and read only in ``report()``, so tracing
 adds no host synchronisation to a step; what it measures is the *span* of each phase on its
-stream, which equals its exposed time only while nothing overlaps (true of the fused layer
-today).  The reference has no tracing; its protocol for attributing exposed time per stream is
+stream.  With the serial schedule of the fused layer that is the phase's exposed time; with
+the overlap schedule the dispatch span shrinks to its launches and the waiting shows up inside
+the "experts" and "combine" spans, which is how the exposed share is read off.  The reference has no tracing; its protocol for attributing exposed time per stream is
 prose (``docs/09-phase-model.md:49-85``), and its timing idiom is barrier / synchronize /
 perf_counter with a max over ranks (``bench/a2a_form_probe.py:47-77``).
 """

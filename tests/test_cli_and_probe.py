@@ -107,14 +107,15 @@ def test_drift_probe_notes_contracts_and_compare(monkeypatch, tmp_path):
 def test_environment_switches_are_strict(monkeypatch):
     """Unknown values raise; unset means the documented default."""
     from terracemoe_simulator_b200.utils import flags, trace
-    monkeypatch.delenv("TERRACE_EP_PUSH_BACK", raising=False)
-    assert flags.flag_bool("TERRACE_EP_PUSH_BACK") is False
+    monkeypatch.delenv("TERRACE_EP_OVERLAP", raising=False)
+    assert flags.flag_bool("TERRACE_EP_OVERLAP") is False
+    assert flags.flag_bool("TERRACE_EP_OVERLAP", True) is True       # the transport's default
     for v, want in (("1", True), ("on", True), ("0", False), ("", False), ("No", False)):
-        monkeypatch.setenv("TERRACE_EP_PUSH_BACK", v)
-        assert flags.flag_bool("TERRACE_EP_PUSH_BACK") is want
-    monkeypatch.setenv("TERRACE_EP_PUSH_BACK", "maybe")
+        monkeypatch.setenv("TERRACE_EP_OVERLAP", v)
+        assert flags.flag_bool("TERRACE_EP_OVERLAP") is want
+    monkeypatch.setenv("TERRACE_EP_OVERLAP", "maybe")
     with pytest.raises(ValueError):
-        flags.flag_bool("TERRACE_EP_PUSH_BACK")
+        flags.flag_bool("TERRACE_EP_OVERLAP")
     monkeypatch.setenv("TERRACE_ATTENTION", "flash")
     with pytest.raises(ValueError):
         flags.flag_choice("TERRACE_ATTENTION", ("native", "sdpa"), "native")
