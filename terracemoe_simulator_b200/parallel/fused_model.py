@@ -64,6 +64,48 @@ def plan_positions(idx_per_rank, world: int, n_experts: int, seg_align: int = 64
             "rows": [int(padded[o * epr:(o + 1) * epr].sum()) for o in range(world)]}
 
 
+def pass1_ranks(idx: torch.Tensor, n_experts: int, chunks: int = 128, lanes: int = 32):
+    """The first plan pass as the kernel runs it (``plan_pass1_kernel``): tokens are cut into
+    ``chunks`` ranges, a warp walks its range ``lanes`` tokens at a time and ranks every pick
+    inside its expert.  Returns ``(es, rank_local, chunk_hist)``: picks sorted ascending per
+    token, the rank of each pick among the chunk's picks of the same expert, and the per-chunk
+    histogram ``[chunks, E]``.
+
+    For a top-k routing (distinct experts per token) a pick's rank is the count so far plus the
+    LOWER lanes of the batch that picked the same expert, whatever their column: token order.
+    A batch that holds a token with a repeated expert is ranked column by column instead (still
+    distinct, in-range ranks, but not token order)."""
+    T, k = idx.shape
+    es = torch.sort(idx, dim=1).values
+    rank_local = torch.full((T, k), -1, dtype=torch.int64)
+    hist = torch.zeros(chunks, n_experts, dtype=torch.int64)
+    per = -(-T // chunks) if T else 0
+    for c in range(chunks):
+        lo, hi = c * per, min(T, (c + 1) * per)
+        seen = [0] * n_experts
+        for start in range(lo, hi, lanes):
+            batch = range(start, min(start + lanes, hi))
+            repeated = any(int(es[t, j]) == int(es[t, j - 1]) for t in batch for j in range(1, k))
+            if not repeated:
+                added = [0] * n_experts
+                for t in batch:                                  # lanes ascending = tokens ascending
+                    for j in range(k):
+                        e = int(es[t, j])
+                        if 0 <= e < n_experts:
+                            rank_local[t, j] = seen[e] + added[e]
+                            added[e] += 1
+                seen = [a + b for a, b in zip(seen, added)]
+            else:
+                for j in range(k):                               # column by column
+                    for t in batch:
+                        e = int(es[t, j])
+                        if 0 <= e < n_experts:
+                            rank_local[t, j] = seen[e]
+                            seen[e] += 1
+        hist[c] = torch.tensor(seen)
+    return es, rank_local, hist
+
+
 def check_tiling(plan, idx_per_rank, world: int, n_experts: int) -> None:
     """Every owner's segment of expert e is covered exactly once, in (source, token) order."""
     epr = n_experts // world

@@ -412,6 +412,37 @@ def test_single_mode_contexts_shrink_the_other_paths_sections():
     ctx.check_mode("two_hop")
 
 
+@pytest.mark.parametrize("T", [7, 300, 900, 5000])
+def test_first_plan_pass_ranks_picks_in_token_order(T):
+    """The ranking the plan kernel computes per chunk, replayed on the host: with distinct
+    experts per token the position of a pick inside its expert is the number of earlier tokens
+    that picked it -- the order the capacity rule and ``plan_positions`` assume; with a repeated
+    expert the ranks are still a permutation inside every expert."""
+    from terracemoe_simulator_b200.parallel import fused_model as fm
+    g = torch.Generator().manual_seed(T)
+    E, k = 16, 4
+    idx = torch.stack([torch.randperm(E, generator=g)[:k] for _ in range(T)])
+    es, rank_local, hist = fm.pass1_ranks(idx, E)
+    per = -(-T // 128)
+    base = torch.cumsum(hist, 0) - hist
+    chunk = (torch.arange(T) // per).unsqueeze(1).expand(T, k)
+    within = base[chunk, es] + rank_local
+    onehot = torch.zeros(T, E, dtype=torch.long).scatter_add_(1, idx, torch.ones_like(idx))
+    earlier = torch.cumsum(onehot, 0) - onehot
+    assert torch.equal(within, earlier.gather(1, es))
+    assert torch.equal(hist.sum(0), torch.bincount(idx.reshape(-1), minlength=E))
+    # the placement model built on the same order
+    plan = fm.plan_positions([idx], 1, E, seg_align=1)
+    assert torch.equal(plan["pos"][0].gather(1, torch.argsort(idx, dim=1, stable=True)),
+                       plan["seg_start"][0][es] + within)
+    dup = torch.randint(0, E, (T, k), generator=g)
+    es2, ranks2, hist2 = fm.pass1_ranks(dup, E)
+    within2 = (torch.cumsum(hist2, 0) - hist2)[chunk, es2] + ranks2
+    for e in range(E):
+        got = torch.sort(within2[es2 == e]).values
+        assert torch.equal(got, torch.arange(got.numel()))
+
+
 def test_arena_layout_puts_a_guard_after_every_section():
     from terracemoe_simulator_b200.parallel.fused import GUARD_BYTES, arena_layout
     sizes = [100, 4096, 1, 256 * 7 + 3]
