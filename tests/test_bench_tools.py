@@ -301,3 +301,32 @@ def test_svg2pdf_converts_every_figure(tmp_path, monkeypatch):
     for p in out:
         if p.endswith(".pdf"):
             _check_pdf(open(p, "rb").read())
+
+
+def _load_root_bench():
+    import importlib.util
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    spec = importlib.util.spec_from_file_location("root_bench", os.path.join(root, "bench.py"))
+    mod = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mod)
+    return mod
+
+
+def test_root_bench_contract_helpers():
+    """The parts of the headline benchmark that need no GPU: the configuration both arms report
+    (identical keys and values for ours and the reference), block statistics, the clock sampler's
+    summary, and the command-line surface."""
+    b = _load_root_bench()
+    for world in (1, 2, 4, 8):
+        cfg = b.bench_config(world)
+        assert {"model", "global_batch", "seq_len", "parallelism"} <= set(cfg)
+        assert cfg["global_batch"] == b.TOKENS * world and cfg["parallelism"] == "ep%d" % world
+        assert cfg["rpn"] == b.RPN[world] and world % cfg["rpn"] == 0
+        assert b.ROUTING_GROUPS[world] >= 2
+    stats = b.block_stats([70.0, 60.0, 80.0, 65.0, 90.0], steps=20)
+    assert stats == {"ms_per_step": 3.5, "ms_min": 3.0, "ms_max": 4.5, "blocks": 5}
+    src = open(b.__file__).read()
+    for flag in ("--gpus", "--steps", "--warmup", "--impl", "--repeats", "--e2e-variant",
+                 "--no-ab", "--no-parity"):
+        assert flag in src
+    assert '"gpu_launches"' in src and '"e2e"' in src and '"clocks"' in src
