@@ -246,6 +246,31 @@ def overlap_gain(verbose: bool = True, bench: dict | None = None) -> list:
     return rows
 
 
+def path_ratios(verbose: bool = True, bench: dict | None = None) -> list:
+    """two-hop / one-hop step time per (GPUs, schedule), measured and modelled: the step-level
+    counterpart of the call-level ratio gate (``sim/validate_b200.py``)."""
+    bench = bench or load_bench()
+    steps = measured_steps(bench)
+    fitted = set(bench["kernels"].get("fitted_on_gpus", []))
+    rows = []
+    for (n, rpn, path, schedule), one in sorted(steps.items()):
+        two = steps.get((n, rpn, "two_hop", schedule))
+        if path != "one_hop" or two is None:
+            continue
+        model = (predict_ms(n, rpn, "two_hop", schedule, bench=bench)["total_ms"]
+                 / predict_ms(n, rpn, "one_hop", schedule, bench=bench)["total_ms"])
+        rows.append((n, rpn, schedule, two / one, model, model / (two / one) - 1.0, n in fitted))
+    if verbose:
+        print("two-hop / one-hop step time")
+        cols = [Column("GPUs", "%4d", lambda r: r[0]), Column("rpn", "%4d", lambda r: r[1]),
+                Column("schedule", "%-8s", lambda r: r[2]), Column("measured", "%9.3f", lambda r: r[3]),
+                Column("model", "%9.3f", lambda r: r[4]),
+                Column("err", "%7s", lambda r: "%+.1f%%" % (100 * r[5])),
+                Column("", "%-9s", lambda r: "fitted" if r[6] else "predicted")]
+        print("\n".join(render_table(cols, rows)))
+    return rows
+
+
 def main(argv=None) -> None:
     import argparse
     ap = argparse.ArgumentParser(description=__doc__.split("\n")[0])
@@ -256,6 +281,8 @@ def main(argv=None) -> None:
     validate(bench=bench)
     print()
     overlap_gain(bench=bench)
+    print()
+    path_ratios(bench=bench)
 
 
 if __name__ == "__main__":

@@ -366,6 +366,18 @@ def test_b200_step_overlap_term_follows_the_chunked_schedule():
     assert few.exposed_ms(0.4, 0.1, 0.0) == pytest.approx(0.2 + (0.2 - 0.05) + few.local_reduce_ms)
 
 
+def test_b200_step_path_ratios_report_the_miss():
+    """two-hop / one-hop at step level: the fitted pairs within 3 %, the predicted ones listed
+    with their error whatever it is (the 8-GPU overlap pair is the known miss)."""
+    from terracemoe_simulator_b200.sim import b200_step
+    rows = b200_step.path_ratios(verbose=False)
+    assert len(rows) >= 6 and {r[2] for r in rows} == {"serial", "overlap"}
+    assert all(abs(r[5]) < 0.03 for r in rows if r[6])
+    predicted = [r for r in rows if not r[6]]
+    assert predicted and all(r[0] == 8 for r in predicted)
+    assert max(abs(r[5]) for r in predicted) < 0.15
+
+
 def test_b200_step_reads_bench_lines(tmp_path):
     """``--bench FILE`` takes the JSON lines bench.py prints; *_pull paths become serial arms."""
     import json
