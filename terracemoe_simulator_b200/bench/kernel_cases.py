@@ -20,7 +20,8 @@ import torch
 CASES = ("gemm_fwd", "gemm_swiglu", "gemm_dgrad", "gemm_wgrad", "gemm_scatter", "rmsnorm",
          "rmsnorm_bwd", "route", "route_fused", "scatter", "combine", "combine_bwd", "swiglu_bwd",
          "attn_fwd", "attn_bwd", "ep_layer",
-         "k1_arrival", "k2_pack", "rope_split", "rope_merge", "route_bwd", "passthrough")
+         "k1_arrival", "k2_pack", "rope_split", "rope_merge", "route_bwd", "passthrough",
+         "gemm_swiglu_bwd")
 
 
 def _peaks():
@@ -71,6 +72,7 @@ def main(argv=None) -> int:
     bf = torch.bfloat16
     hbm, tf, tag = _peaks()
     flops = bytes_ = 0
+    extra = {}
     if args.case in ("gemm_fwd", "gemm_swiglu"):
         X = torch.randn(rows, H, device=dev, dtype=bf)
         W = torch.randn(E, H, 2 * d, device=dev, dtype=bf) * H ** -0.5
@@ -82,6 +84,21 @@ def main(argv=None) -> int:
         W = torch.randn(E, H, 2 * d, device=dev, dtype=bf) * H ** -0.5
         fn = lambda: lib.grouped_gemm(dY, W, st, cnt, 1, 0, False, 0, args.pad)
         flops = 2 * rows * H * 2 * d
+    elif args.case == "gemm_swiglu_bwd":
+        # d(act) = dOut @ W2^T with the SwiGLU backward in the epilogue (d[gate | up] written
+        # directly), against the two launches it replaces (plain dgrad GEMM + swiglu_bwd)
+        dout = torch.randn(rows, H, device=dev, dtype=bf)
+        W2 = torch.randn(E, d, H, device=dev, dtype=bf) * d ** -0.5
+        h13 = torch.randn(rows, 2 * d, device=dev, dtype=bf)
+        dh13 = torch.empty_like(h13)
+        fn = lambda: lib.grouped_gemm_ex(dout, W2, dh13, h13, st, cnt, 1, 3, None, 0, 0, 0, 0,
+                                         args.pad)
+
+        def unfused():
+            dact, _ = lib.grouped_gemm(dout, W2, st, cnt, 1, 0, False, 0, args.pad)
+            return lib.swiglu_bwd(h13, dact[:rows])
+        extra["unfused_ms"] = round(_time(unfused, args.iters), 4)
+        flops = 2 * rows * H * d
     elif args.case == "gemm_scatter":
         # the scattering epilogue on one GPU: rows leave through a random permutation into a local
         # buffer; checked once against the plain kernel followed by the same permutation
@@ -249,6 +266,7 @@ def main(argv=None) -> int:
     if bytes_:
         line["gbs"] = round(bytes_ / ms / 1e6, 1)
         line["frac_of_hbm_peak"] = round(bytes_ / ms / 1e6 / hbm, 3)
+    line.update(extra)
     line["peaks"] = tag
     line["status"] = ops.take_status()
     print(json.dumps(line))
