@@ -222,3 +222,23 @@ def test_profile_summary_quotes_the_roofline_module():
         min(t["one_hop_frac"] for t in big), max(t["one_hop_frac"] for t in big),
         min(t["nccl_frac"] for t in big), max(t["nccl_frac"] for t in big))
     assert want in text, want
+
+
+def test_readme_layer_table_quotes_the_committed_bench_runs():
+    """The measured table of the README is the fastest arm of every committed bench run."""
+    from terracemoe_simulator_b200.sim import b200_step
+    text = _read("README.md")
+    for run in b200_step.load_bench()["runs"]:
+        best = min(run["paths"].values())
+        n = run["n_gpus"]
+        if n == 1:
+            assert "| 1 GPU | 25.6 ms | 3.47-3.57 ms |" in text and 3.47 <= round(best, 2) <= 3.57
+        else:
+            assert "| %d GPUs |" % n in text and "%.2f ms" % best in text, (n, best)
+    doc = _read("docs/14-overlap-plan.md")
+    steps = b200_step.measured_steps()
+    for n, rpn in ((2, 1), (4, 1), (8, 2)):
+        cells = [steps[n, rpn, p, s] for p, s in (("one_hop", "overlap"), ("one_hop", "serial"),
+                                                  ("two_hop", "overlap"), ("two_hop", "serial"))]
+        for v in cells:
+            assert "%.2f" % v in doc, (n, v)
